@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the K-quant dequantize-and-multiply hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M]
+
+Workload (N = 1): the dense 27B-class decode projection set of a layer (q 5120->6144, k/v 5120->1024,
+o 6144->5120, gate/up 5120->17408 in Q4_K; down 17408->5120 in Q6_K; 214,671,360 packed bytes), fp32
+activations N(0,1) at M = 1, over LAYERS distinct layers of seeded synthetic blocks so that every
+step streams far more than L2 from HBM.  One step = one pass over all layers' projections.
+`value` = packed weight bytes / device time (the reference's GB/s, src/hybrid/bench.rs:127-132), with
+inputs resident in HBM.  `e2e` = the same through the host-buffer C-ABI calls, host<->device copies
+inside the timed region.  Extra keys report M = 8 / 16 and the prefill dequant-GEMM.
+
+With --gpus N > 1 (under torchrun) every matrix is row-sharded over the N ranks and the partial
+outputs of each fused group (q|k|v, o, gate|up, down) are all-gathered with NCCL; total work is
+fixed, so scaling is "strong".
+
+--impl reference times the reference's CPU path for the same projections: the oracle restatement
+of its CPU dequant + matmul on all host cores, one layer per step (a bounded sample).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+Q8_0, Q4_K, Q6_K = 8, 12, 14
+# (name, rows, cols, format) of one dense 27B-class layer; groups share their input.
+LAYER = [("q", 6144, 5120, Q4_K), ("k", 1024, 5120, Q4_K), ("v", 1024, 5120, Q4_K), ("o", 5120, 6144, Q4_K),
+         ("gate", 17408, 5120, Q4_K), ("up", 17408, 5120, Q4_K), ("down", 5120, 17408, Q6_K)]
+GROUPS = [("q", "k", "v"), ("o",), ("gate", "up"), ("down",)]
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+LAYER_BYTES = sum(r * c // BLOCK[f][0] * BLOCK[f][1] for _, r, c, f in LAYER)  # 214,671,360
+LAYER_WEIGHTS = sum(r * c for _, r, c, _ in LAYER)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        reasons = []
+        for i, name in enumerate(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]):
+            if any(len(r) >= 7 and r[3 + i].lower().startswith("active") for r in self.rows):
+                reasons.append(name)
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(self.rows[0][1]), "samples": len(sm),
+                "power_w_max": max(float(r[2]) for r in self.rows if len(r) >= 7), "reasons": reasons}
+
+
+def random_blocks(fmt: int, blocks: int, seed: int) -> np.ndarray:
+    """Packed blocks with the benchmark's distributions: d (and dmin) = fp16(|N(0,1)| * 1e-2), scale
+    bytes and quant bytes uniform; draw order d -> dmin -> scales -> quants (numpy default_rng(seed))."""
+    rng = np.random.default_rng(seed)
+    out = np.empty((blocks, BLOCK[fmt][1]), dtype=np.uint8)
+    half = lambda: (np.abs(rng.standard_normal(blocks)) * 1e-2).astype(np.float16).view(np.uint8).reshape(blocks, 2)
+    if fmt == Q4_K:
+        out[:, 0:2], out[:, 2:4] = half(), half()
+        out[:, 4:16] = rng.integers(0, 256, size=(blocks, 12), dtype=np.uint8)
+        out[:, 16:144] = rng.integers(0, 256, size=(blocks, 128), dtype=np.uint8)
+    elif fmt == Q6_K:
+        out[:, 208:210] = half()
+        out[:, 192:208] = rng.integers(-128, 128, size=(blocks, 16), dtype=np.int8).view(np.uint8)
+        out[:, 0:192] = rng.integers(0, 256, size=(blocks, 192), dtype=np.uint8)
+    else:
+        out[:, 0:2] = half()
+        out[:, 2:34] = rng.integers(-127, 128, size=(blocks, 32), dtype=np.int8).view(np.uint8)
+    return out.reshape(-1)
+
+
+def random_matrix(fmt: int, rows: int, cols: int, seed: int) -> np.ndarray:
+    return random_blocks(fmt, rows * cols // BLOCK[fmt][0], seed)
+
+
+def shard_rows(rows: int, rank: int, world: int):
+    per = rows // world
+    assert per * world == rows, "rows must divide evenly over the ranks"
+    return rank * per, per
+
+
+# ---------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from ferrum_b200 import surface as S
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = S.Device(local)
+    m = args.m
+    layers = args.layers
+
+    # Weights: layer l, matrix i uses seed 7 * l + i (+ rank shard); blocks as BASELINE config 0/1.
+    mats = []
+    for l in range(layers):
+        layer = {}
+        for i, (name, rows, cols, fmt) in enumerate(LAYER):
+            _, per = shard_rows(rows, rank, world)
+            packed = random_matrix(fmt, per, cols, seed=(7 * l + i) * 64 + rank)
+            layer[name] = S.Matrix.from_packed(dev, per, cols, 1, fmt, packed)
+        mats.append(layer)
+    shapes = {name: (rows, cols) for name, rows, cols, _ in LAYER}
+    rng = np.random.default_rng(1234)
+    x_host = {g[0]: rng.standard_normal((m, shapes[g[0]][1])).astype(np.float32) for g in GROUPS}
+    x_dev = {k: torch.from_numpy(v).cuda() for k, v in x_host.items()}
+    y_dev = {name: torch.zeros(m * shapes[name][0] // world, dtype=torch.float32, device="cuda") for name in shapes}
+    gathered = {name: torch.zeros(world * m * shapes[name][0] // world, dtype=torch.float32, device="cuda")
+                for name in shapes} if world > 1 else None
+
+    def step():
+        for layer in mats:
+            for group in GROUPS:
+                x = x_dev[group[0]]
+                for name in group:
+                    S.project(dev, layer[name], x, m, y_dev[name])
+                if world > 1:
+                    for name in group:
+                        dist.all_gather_into_tensor(gathered[name], y_dev[name])
+
+    def timed(fn, steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    c0 = dev.counters().dispatches
+    with ClockSampler(local) as clocks:
+        ms = timed(step, args.steps)
+    launches = dev.counters().dispatches - c0
+    ms_per_step = ms / args.steps
+    total_bytes = layers * LAYER_BYTES  # whole job: all ranks together stream every byte once per step
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    P = peaks()
+    out = {
+        "metric": "Q4_K_M decode projection weight GB/s (27B-class dense layer set)", "value": round(value, 2),
+        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"cfg1 dense 27B decode projection set (q,k,v,o,gate,up Q4_K; down Q6_K), M={m}, "
+                               f"{layers} distinct layers = {total_bytes} packed bytes per step (inputs larger than L2)",
+                   "m": m, "layers": layers, "parallelism": f"tp{world}" if world > 1 else "single",
+                   "l2": "inputs larger than L2"},
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+    }
+
+    if rank == 0 and world == 1:
+        # Dominant kernel: the Q4_K GEMV on gate/up (50,135,040 packed bytes per launch), timed alone
+        # over `layers` distinct matrices with CUDA events on the launching stream.
+        def gate_only():
+            for layer in mats:
+                S.project(dev, layer["gate"], x_dev["gate"], m, y_dev["gate"])
+        for _ in range(3):
+            gate_only()
+        c0 = dev.counters().dispatches
+        gms = timed(gate_only, args.steps) / (args.steps * layers)
+        gate_bytes = 17408 * 5120 // 256 * 144
+        achieved = gate_bytes / (gms * 1e-3) / 1e9
+        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv_q4k (gate 17408x5120)", "achieved": round(achieved, 1),
+                           "peak": P["hbm_gbs"], "peak_source": P["source"], "unit": "GB/s",
+                           "frac": round(achieved / P["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
+                           "traffic": None, "us_per_launch": round(gms * 1e3, 2)}
+        # The other decode widths, same workload.
+        extra = {}
+        for mm in (8, 16):
+            xs = {k: torch.from_numpy(rng.standard_normal((mm, shapes[k][1])).astype(np.float32)).cuda() for k in x_dev}
+            ys = {name: torch.zeros(mm * shapes[name][0], dtype=torch.float32, device="cuda") for name in shapes}
+
+            def step_m():
+                for layer in mats:
+                    for group in GROUPS:
+                        for name in group:
+                            S.project(dev, layer[name], xs[group[0]], mm, ys[name])
+            for _ in range(2):
+                step_m()
+            t = timed(step_m, max(2, args.steps // 2)) / max(2, args.steps // 2)
+            extra[f"m{mm}_gbs"] = round(total_bytes / (t * 1e-3) / 1e9, 1)
+        out["decode_widths"] = extra
+
+        # End to end through the host-buffer C-ABI calls: pinned-staged H2D of x, D2H of y, every step.
+        y_host = {name: np.zeros((m, shapes[name][0]), dtype=np.float32) for name in shapes}
+
+        def step_host():
+            for layer in mats:
+                for group in GROUPS:
+                    S.project_many_host(dev, [layer[n] for n in group], x_host[group[0]], m, [y_host[n] for n in group])
+        for _ in range(3):
+            step_host()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_host()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / args.steps
+        h2d = layers * sum(m * shapes[g[0]][1] * 4 for g in GROUPS)
+        d2h = layers * sum(m * shapes[n][0] * 4 for n in shapes)
+        out["e2e"] = {"value": round(total_bytes / dt / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                      "d2h_bytes_per_step": d2h, "ms_per_step": round(dt * 1e3, 4)}
+
+        # CPU baseline: the oracle port on all host cores, one layer at M = 1 (a bounded sample).
+        out["cpu_baseline"] = cpu_baseline(m=m, budget_s=12.0)
+    elif rank == 0:
+        out["e2e"] = None
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU baseline / reference arm
+# ---------------------------------------------------------------------------------------------------
+
+def cpu_layer(seed0=0):
+    mats = []
+    for i, (name, rows, cols, fmt) in enumerate(LAYER):
+        mats.append((name, rows, cols, fmt, random_matrix(fmt, rows, cols, seed=seed0 + i)))
+    return mats
+
+
+def cpu_pass(ref, mats, xs, m, threads):
+    for name, rows, cols, fmt, packed in mats:
+        ref.gemv_threads(fmt, packed, rows, cols, xs[cols], m, threads)
+
+
+def cpu_baseline(m, budget_s):
+    from oracle import ref  # the CPU oracle is executed here only to be timed as the baseline
+    threads = os.cpu_count() or 1
+    mats = cpu_layer()
+    rng = np.random.default_rng(1234)
+    xs = {c: rng.standard_normal((m, c)).astype(np.float32) for c in (5120, 6144, 17408)}
+    cpu_pass(ref, mats, xs, m, threads)  # warm-up
+    best, t_start, reps = None, time.perf_counter(), 0
+    while reps < 2 or (time.perf_counter() - t_start < budget_s and reps < 20):
+        t0 = time.perf_counter()
+        cpu_pass(ref, mats, xs, m, threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+        reps += 1
+    return {"value": round(LAYER_BYTES / best / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"one layer ({LAYER_BYTES} packed bytes) at M={m}, best of {reps} passes, "
+                      f"C restatement of the reference's CPU dequant + fp32 dot, {threads} threads"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import ref  # the reference arm is the CPU oracle, timed
+    threads = os.cpu_count() or 1
+    m = args.m
+    mats = cpu_layer()
+    rng = np.random.default_rng(1234)
+    xs = {c: rng.standard_normal((m, c)).astype(np.float32) for c in (5120, 6144, 17408)}
+    steps, warm = min(args.steps, 10), min(max(args.warmup, 1), 3)
+    for _ in range(warm):
+        cpu_pass(ref, mats, xs, m, threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_pass(ref, mats, xs, m, threads)
+    dt = (time.perf_counter() - t0) / steps
+    value = round(LAYER_BYTES / dt / 1e9, 3)
+    sample = (f"each step = one layer ({LAYER_BYTES} packed bytes) at M={m} on the host cores; the C restatement of the "
+              f"reference's CPU dequant + fp32 dot (the reference itself is a macOS-only Rust/Metal crate and cannot be built here)")
+    print(json.dumps({
+        "impl": "reference", "metric": "Q4_K_M decode projection weight GB/s (27B-class dense layer set)",
+        "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"cfg1 dense 27B decode projection set, M={m}, CPU sample of one layer per step", "m": m},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--m", type=int, default=1, help="activation rows (1 = decode)")
+    ap.add_argument("--layers", type=int, default=3, help="distinct layers streamed per step")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,592 @@
+// The C ABI: device handles, buffers, weight matrices, binding checks and the dispatch policy of
+// the quantized-linear op surface (the counterpart of src/hybrid/engine.rs:3407-3500 and of the
+// checks in src/metal/mod.rs:838-897).
+#include <cstdarg>
+#include <cstring>
+#include <vector>
+
+#include "internal.h"
+
+// ------------------------------------------------------------------ errors
+
+int fq_fail(fq_device *dev, int status, const char *fmt, ...) {
+    if (dev) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        dev->error = buf;
+    }
+    return status;
+}
+
+int fq_check_cuda(fq_device *dev, cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return FQ_OK;
+    return fq_fail(dev, FQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+extern "C" const char *fq_status_name(int status) {
+    switch (status) {
+    case FQ_OK: return "ok";
+    case FQ_ERR_SHAPE: return "shape";
+    case FQ_ERR_RANGE: return "range";
+    case FQ_ERR_DEVICE: return "device mismatch";
+    case FQ_ERR_ALIAS: return "alias";
+    case FQ_ERR_WEIGHT: return "weight";
+    case FQ_ERR_SYNC: return "synchronization";
+    case FQ_ERR_TIMEOUT: return "timeout";
+    case FQ_ERR_CUDA: return "cuda";
+    case FQ_ERR_PARAM: return "parameter";
+    case FQ_ERR_UNSUPPORTED: return "unsupported";
+    default: return "unknown";
+    }
+}
+
+extern "C" const char *fq_last_error(fq_device *dev) { return dev ? dev->error.c_str() : "null device handle"; }
+
+// ------------------------------------------------------------------ enqueue bookkeeping
+
+int fq_begin_enqueue(fq_device *dev) {
+    if (!dev) return FQ_ERR_PARAM;
+    if (dev->failed) return fq_fail(dev, FQ_ERR_SYNC, "device handle holds a failed submission; call fq_device_recover");
+    if (dev->fail_after >= 0) {
+        if (dev->fail_after == 0) {
+            dev->fail_after = -1;
+            dev->failed = true;
+            return fq_fail(dev, FQ_ERR_SYNC, "injected enqueue failure");
+        }
+        dev->fail_after--;
+    }
+    return fq_check_cuda(dev, cudaSetDevice(dev->ordinal), "cudaSetDevice");
+}
+
+int fq_end_enqueue(fq_device *dev, const char *what, int kernels) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fq_fail(dev, FQ_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    }
+    dev->counters.dispatches += (uint64_t)kernels;
+    return FQ_OK;
+}
+
+int fq_check_binding(fq_device *dev, const void *p, size_t bytes, const char *name) {
+    if (!p) return fq_fail(dev, FQ_ERR_RANGE, "%s: null binding", name);
+    const uintptr_t a = (uintptr_t)p;
+    if (a & 15u) return fq_fail(dev, FQ_ERR_RANGE, "%s: binding %p is not 16-byte aligned", name, p);
+    // A pointer inside a buffer this handle allocated must stay inside it.
+    auto it = dev->allocations.upper_bound(a);
+    if (it != dev->allocations.begin()) {
+        --it;
+        if (a < it->first + it->second && a + bytes > it->first + it->second)
+            return fq_fail(dev, FQ_ERR_RANGE, "%s: %zu bytes at %p run past the end of their allocation", name, bytes, p);
+    }
+    return FQ_OK;
+}
+
+int fq_check_no_alias(fq_device *dev, const void *out, size_t out_bytes, const void *in, size_t in_bytes,
+                      const char *name) {
+    const uintptr_t o = (uintptr_t)out, i = (uintptr_t)in;
+    if (!out || !in) return FQ_OK;
+    if (o < i + in_bytes && i < o + out_bytes) return fq_fail(dev, FQ_ERR_ALIAS, "%s: output overlaps an input", name);
+    return FQ_OK;
+}
+
+// ------------------------------------------------------------------ device
+
+extern "C" int fq_device_create(int ordinal, fq_device **out) {
+    if (!out) return FQ_ERR_PARAM;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || ordinal < 0 || ordinal >= count) return FQ_ERR_DEVICE;
+    fq_device *dev = new fq_device();
+    dev->ordinal = ordinal;
+    auto bail = [&](cudaError_t err, const char *what) {
+        fprintf(stderr, "ferrum_b200: %s: %s\n", what, cudaGetErrorString(err));
+        fq_device_destroy(dev);
+        return FQ_ERR_CUDA;
+    };
+    if ((e = cudaSetDevice(ordinal)) != cudaSuccess) return bail(e, "cudaSetDevice");
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, ordinal)) != cudaSuccess) return bail(e, "cudaGetDeviceProperties");
+    if (prop.major != 10) {
+        fprintf(stderr, "ferrum_b200: device %d is sm_%d%d; this library is built for sm_100a only\n", ordinal,
+                prop.major, prop.minor);
+        delete dev;
+        return FQ_ERR_DEVICE;
+    }
+    dev->sm_count = prop.multiProcessorCount;
+    if ((e = cudaStreamCreateWithFlags(&dev->own_stream, cudaStreamNonBlocking)) != cudaSuccess) return bail(e, "cudaStreamCreate");
+    dev->stream = dev->own_stream;
+    dev->xprep_bytes = fq_gemv_scratch_bytes();
+    if ((e = cudaMalloc(&dev->xprep, dev->xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
+    if ((e = cudaMalloc(&dev->staging_dev, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "device staging");
+    if ((e = cudaMallocHost(&dev->staging_host, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "pinned staging");
+    *out = dev;
+    return FQ_OK;
+}
+
+extern "C" int fq_device_destroy(fq_device *dev) {
+    if (!dev) return FQ_ERR_PARAM;
+    cudaSetDevice(dev->ordinal);
+    if (dev->own_stream) cudaStreamSynchronize(dev->own_stream);
+    for (auto &kv : dev->allocations) cudaFree((void *)kv.first);
+    if (dev->xprep) cudaFree(dev->xprep);
+    if (dev->staging_dev) cudaFree(dev->staging_dev);
+    if (dev->staging_host) cudaFreeHost(dev->staging_host);
+    if (dev->own_stream) cudaStreamDestroy(dev->own_stream);
+    delete dev;
+    return FQ_OK;
+}
+
+extern "C" int fq_device_set_stream(fq_device *dev, void *cuda_stream) {
+    if (!dev) return FQ_ERR_PARAM;
+    dev->stream = cuda_stream ? (cudaStream_t)cuda_stream : dev->own_stream;
+    return FQ_OK;
+}
+
+extern "C" void *fq_device_stream(fq_device *dev) { return dev ? (void *)dev->stream : nullptr; }
+
+extern "C" int fq_synchronize(fq_device *dev) {
+    if (!dev) return FQ_ERR_PARAM;
+    cudaSetDevice(dev->ordinal);
+    dev->counters.synchronizes++;
+    cudaError_t e = cudaStreamSynchronize(dev->stream);
+    if (dev->fail_completion) {
+        dev->fail_completion = false;
+        dev->failed = true;
+        return fq_fail(dev, FQ_ERR_SYNC, "injected completion failure");
+    }
+    if (e != cudaSuccess) {
+        dev->failed = true;
+        return fq_fail(dev, FQ_ERR_SYNC, "stream failed: %s", cudaGetErrorString(e));
+    }
+    if (dev->failed) return fq_fail(dev, FQ_ERR_SYNC, "device handle holds a failed submission");
+    return FQ_OK;
+}
+
+extern "C" int fq_device_recover(fq_device *dev) {
+    if (!dev) return FQ_ERR_PARAM;
+    cudaSetDevice(dev->ordinal);
+    cudaError_t e = cudaStreamSynchronize(dev->stream);
+    if (e != cudaSuccess) return fq_fail(dev, FQ_ERR_SYNC, "stream is still failing: %s", cudaGetErrorString(e));
+    dev->failed = false;
+    dev->error.clear();
+    return FQ_OK;
+}
+
+extern "C" int fq_get_counters(fq_device *dev, fq_counters *out) {
+    if (!dev || !out) return FQ_ERR_PARAM;
+    *out = dev->counters;
+    return FQ_OK;
+}
+
+extern "C" int fq_set_exact(fq_device *dev, int on) {
+    if (!dev) return FQ_ERR_PARAM;
+    dev->exact = on != 0;
+    return FQ_OK;
+}
+
+extern "C" int fq_test_fail_after(fq_device *dev, int n) {
+    if (!dev) return FQ_ERR_PARAM;
+    dev->fail_after = n;
+    return FQ_OK;
+}
+
+extern "C" int fq_test_fail_completion(fq_device *dev) {
+    if (!dev) return FQ_ERR_PARAM;
+    dev->fail_completion = true;
+    return FQ_OK;
+}
+
+// ------------------------------------------------------------------ buffers
+
+extern "C" int fq_buffer_alloc(fq_device *dev, size_t bytes, void **device_ptr) {
+    if (!dev || !device_ptr || bytes == 0) return fq_fail(dev, FQ_ERR_PARAM, "buffer of %zu bytes", bytes);
+    cudaSetDevice(dev->ordinal);
+    void *p = nullptr;
+    if (int rc = fq_check_cuda(dev, cudaMalloc(&p, bytes), "cudaMalloc")) return rc;
+    dev->allocations[(uintptr_t)p] = bytes;
+    *device_ptr = p;
+    return FQ_OK;
+}
+
+extern "C" int fq_buffer_free(fq_device *dev, void *device_ptr) {
+    if (!dev) return FQ_ERR_PARAM;
+    auto it = dev->allocations.find((uintptr_t)device_ptr);
+    if (it == dev->allocations.end()) return fq_fail(dev, FQ_ERR_RANGE, "%p was not allocated by this handle", device_ptr);
+    cudaSetDevice(dev->ordinal);
+    cudaStreamSynchronize(dev->stream);
+    dev->allocations.erase(it);
+    return fq_check_cuda(dev, cudaFree(device_ptr), "cudaFree");
+}
+
+extern "C" int fq_upload(fq_device *dev, void *device_ptr, const void *host, size_t bytes) {
+    if (!dev || !host) return fq_fail(dev, FQ_ERR_PARAM, "upload arguments");
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (int rc = fq_check_binding(dev, device_ptr, bytes, "upload destination")) return rc;
+    dev->counters.bytes_uploaded += bytes;
+    return fq_check_cuda(dev, cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, dev->stream), "upload");
+}
+
+extern "C" int fq_download(fq_device *dev, void *host, const void *device_ptr, size_t bytes) {
+    if (!dev || !host) return fq_fail(dev, FQ_ERR_PARAM, "download arguments");
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (int rc = fq_check_binding(dev, device_ptr, bytes, "download source")) return rc;
+    dev->counters.bytes_downloaded += bytes;
+    if (int rc = fq_check_cuda(dev, cudaMemcpyAsync(host, device_ptr, bytes, cudaMemcpyDeviceToHost, dev->stream), "download")) return rc;
+    // A read of results is a completion point, as `Tensor::to_f32` is in the reference.
+    return fq_synchronize(dev);
+}
+
+// ------------------------------------------------------------------ matrices
+
+static float half_bits_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu;
+    uint32_t bits;
+    if (exp == 31) bits = sign | 0x7F800000u | (man << 13);
+    else if (exp == 0) {
+        // Only finiteness and sign matter here; a subnormal is finite.
+        bits = sign | (man ? 0x33800000u : 0u);
+    } else bits = sign | ((exp + 112) << 23) | (man << 13);
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+// `validate_gguf_quantized_payload` (src/quantization.rs:212-261).
+static int validate_payload(fq_device *dev, int format, const uint8_t *p, size_t len, uint32_t bb) {
+    auto finite = [](float v) { return v == v && v - v == 0.0f; };
+    for (size_t o = 0; o < len; o += bb) {
+        const uint8_t *b = p + o;
+        auto half_at = [&](int at) { return half_bits_to_float((uint16_t)(b[at] | (b[at + 1] << 8))); };
+        if (format == FQ_Q4_K) {
+            if (!finite(half_at(0)) || !finite(half_at(2))) return fq_fail(dev, FQ_ERR_WEIGHT, "Q4_K scale must be finite (block %zu)", o / bb);
+        } else if (format == FQ_Q6_K) {
+            if (!finite(half_at(208))) return fq_fail(dev, FQ_ERR_WEIGHT, "Q6_K scale must be finite (block %zu)", o / bb);
+        } else {
+            const float s = half_at(0);
+            if (!finite(s) || s < 0.0f) return fq_fail(dev, FQ_ERR_WEIGHT, "Q8_0 scale must be finite (block %zu)", o / bb);
+            for (int i = 2; i < 34; i++)
+                if (b[i] == 0x80) return fq_fail(dev, FQ_ERR_WEIGHT, "Q8_0 value -128 is outside the GGML range (block %zu)", o / bb);
+        }
+    }
+    return FQ_OK;
+}
+
+extern "C" int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint64_t cols, uint64_t experts,
+                                const void *packed, size_t len, fq_matrix **out) {
+    if (!dev || !out) return FQ_ERR_PARAM;
+    *out = nullptr;
+    uint32_t el, bb;
+    switch (format) {
+    case FQ_Q4_K: el = 256; bb = 144; break;
+    case FQ_Q6_K: el = 256; bb = 210; break;
+    case FQ_Q8_0: el = 32; bb = 34; break;
+    default: return fq_fail(dev, FQ_ERR_WEIGHT, "GGML type %d has no kernel", format);
+    }
+    if (!packed) return fq_fail(dev, FQ_ERR_PARAM, "null payload");
+    if (rows == 0 || cols == 0 || experts == 0) return fq_fail(dev, FQ_ERR_SHAPE, "empty matrix geometry");
+    if (cols % el || cols % 64) return fq_fail(dev, FQ_ERR_WEIGHT, "row width is not a whole number of blocks");
+    if (cols > FQ_MAX_COLS || rows * experts > 0x7fffffffull) return fq_fail(dev, FQ_ERR_SHAPE, "matrix geometry is out of range");
+    const uint64_t row_bytes = cols / el * bb;
+    if (row_bytes * rows * experts != len) return fq_fail(dev, FQ_ERR_WEIGHT, "byte length differs from geometry");
+    if (int rc = validate_payload(dev, format, (const uint8_t *)packed, len, bb)) return rc;
+    if (int rc = fq_check_cuda(dev, cudaSetDevice(dev->ordinal), "cudaSetDevice")) return rc;
+    fq_matrix *w = new fq_matrix();
+    w->dev = dev;
+    w->format = format;
+    w->rows = rows * experts;
+    w->cols = cols;
+    w->experts = experts;
+    w->row_bytes = row_bytes;
+    w->byte_size = len;
+    w->block_elems = el;
+    w->block_bytes = bb;
+    // 256 spare bytes let kernels read whole 16-byte words around the last block.
+    cudaError_t e = cudaMalloc((void **)&w->data, len + 256);
+    if (e == cudaSuccess) e = cudaMemsetAsync(w->data + len, 0, 256, dev->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->data, packed, len, cudaMemcpyHostToDevice, dev->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    if (e != cudaSuccess) {
+        if (w->data) cudaFree(w->data);
+        delete w;
+        return fq_check_cuda(dev, e, "weight upload");
+    }
+    dev->counters.bytes_uploaded += len;
+    *out = w;
+    return FQ_OK;
+}
+
+extern "C" int fq_matrix_destroy(fq_matrix *w) {
+    if (!w) return FQ_ERR_PARAM;
+    cudaSetDevice(w->dev->ordinal);
+    cudaStreamSynchronize(w->dev->stream);
+    cudaFree(w->data);
+    delete w;
+    return FQ_OK;
+}
+
+extern "C" int fq_matrix_get_info(const fq_matrix *w, fq_matrix_info *out) {
+    if (!w || !out) return FQ_ERR_PARAM;
+    out->rows = w->rows;
+    out->cols = w->cols;
+    out->experts = w->experts;
+    out->row_bytes = w->row_bytes;
+    out->byte_size = w->byte_size;
+    out->format = w->format;
+    return FQ_OK;
+}
+
+// ------------------------------------------------------------------ op surface
+
+static ProjectArgs base_args(const fq_matrix *w, const void *x, int xd, void *y, int yd) {
+    ProjectArgs a{};
+    a.w = w->data;
+    a.format = (uint32_t)w->format;
+    a.rows = (uint32_t)w->expert_rows();
+    a.cols = (uint32_t)w->cols;
+    a.row_bytes = (uint32_t)w->row_bytes;
+    a.x = x;
+    a.y = y;
+    a.x_dtype = xd;
+    a.y_dtype = yd;
+    a.experts = (uint32_t)w->experts;
+    return a;
+}
+
+static int check_dtype(fq_device *dev, int dt) {
+    return (dt == FQ_F32 || dt == FQ_BF16) ? FQ_OK : fq_fail(dev, FQ_ERR_UNSUPPORTED, "element type %d", dt);
+}
+
+extern "C" int fq_project(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems, size_t m,
+                          void *y, int y_dtype, size_t y_elems) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!w) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
+    if (w->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "matrix belongs to another device handle");
+    if (int rc = check_dtype(dev, x_dtype)) return rc;
+    if (int rc = check_dtype(dev, y_dtype)) return rc;
+    if (m == 0 || x_elems != m * w->cols || y_elems != m * w->rows)
+        return fq_fail(dev, FQ_ERR_SHAPE, "projection [%zu, %llu] x [%llu, %llu]^T into %zu values", m,
+                       (unsigned long long)w->cols, (unsigned long long)w->rows, (unsigned long long)w->cols, y_elems);
+    if (m > 0x7fffffffu / 8) return fq_fail(dev, FQ_ERR_SHAPE, "too many activation rows");
+    const size_t xb = x_elems * fq_dtype_size(x_dtype), yb = y_elems * fq_dtype_size(y_dtype);
+    if (int rc = fq_check_binding(dev, x, xb, "x")) return rc;
+    if (int rc = fq_check_binding(dev, y, yb, "y")) return rc;
+    if (int rc = fq_check_no_alias(dev, y, yb, x, xb, "y")) return rc;
+    ProjectArgs a = base_args(w, x, x_dtype, y, y_dtype);
+    a.rows = (uint32_t)w->rows; // a plain projection spans every stacked row
+    a.m = (uint32_t)m;
+    if (!dev->exact) {
+        int rc = FQ_ERR_UNSUPPORTED;
+        if (m <= (size_t)FQ_GEMV_MAX_M && x_dtype == FQ_F32 && y_dtype == FQ_F32) rc = fq_launch_gemv_fast(dev, a);
+        else if (x_dtype == FQ_BF16 && y_dtype == FQ_BF16) rc = fq_launch_gemm_tc(dev, a);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (int rc = fq_launch_project_exact(dev, a)) return rc;
+    return fq_end_enqueue(dev, "project", 1);
+}
+
+extern "C" int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x, size_t x_elems, const uint32_t *ids,
+                             size_t routes, size_t x_div, float *y, size_t y_elems) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!w) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
+    if (w->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "matrix belongs to another device handle");
+    const size_t rows_e = w->expert_rows();
+    if (routes == 0 || x_div == 0 || y_elems != routes * rows_e || x_elems * x_div != routes * w->cols)
+        return fq_fail(dev, FQ_ERR_SHAPE, "expert projection geometry");
+    if (int rc = fq_check_binding(dev, x, x_elems * 4, "x")) return rc;
+    if (int rc = fq_check_binding(dev, ids, routes * 4, "ids")) return rc;
+    if (int rc = fq_check_binding(dev, y, y_elems * 4, "y")) return rc;
+    if (int rc = fq_check_no_alias(dev, y, y_elems * 4, x, x_elems * 4, "y")) return rc;
+    if (int rc = fq_check_no_alias(dev, y, y_elems * 4, ids, routes * 4, "y")) return rc;
+    ProjectArgs a = base_args(w, x, FQ_F32, y, FQ_F32);
+    a.m = (uint32_t)routes;
+    a.ids = ids;
+    a.x_div = (uint32_t)x_div;
+    if (!dev->exact) {
+        int rc = fq_launch_gemv_fast(dev, a);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (int rc = fq_launch_project_id_exact(dev, a)) return rc;
+    return fq_end_enqueue(dev, "project_id", 1);
+}
+
+extern "C" int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems,
+                                const uint32_t *offsets, const uint32_t *slots, size_t groups, size_t max_rows,
+                                void *y, int y_dtype, size_t y_elems) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!w) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
+    if (w->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "matrix belongs to another device handle");
+    if (int rc = check_dtype(dev, x_dtype)) return rc;
+    if (int rc = check_dtype(dev, y_dtype)) return rc;
+    const size_t rows_e = w->expert_rows();
+    if (groups == 0 || max_rows == 0 || x_elems % w->cols || y_elems % rows_e || x_elems / w->cols != y_elems / rows_e ||
+        (!slots && groups != w->experts))
+        return fq_fail(dev, FQ_ERR_SHAPE, "grouped expert projection geometry");
+    const size_t xb = x_elems * fq_dtype_size(x_dtype), yb = y_elems * fq_dtype_size(y_dtype);
+    if (int rc = fq_check_binding(dev, x, xb, "x")) return rc;
+    if (int rc = fq_check_binding(dev, offsets, (groups + 1) * 4, "offsets")) return rc;
+    if (slots)
+        if (int rc = fq_check_binding(dev, slots, groups * 4, "slots")) return rc;
+    if (int rc = fq_check_binding(dev, y, yb, "y")) return rc;
+    if (int rc = fq_check_no_alias(dev, y, yb, x, xb, "y")) return rc;
+    ProjectArgs a = base_args(w, x, x_dtype, y, y_dtype);
+    a.offsets = offsets;
+    a.slots = slots;
+    a.groups = (uint32_t)groups;
+    a.max_rows = (uint32_t)max_rows;
+    if (int rc = fq_launch_project_grouped_exact(dev, a)) return rc;
+    return fq_end_enqueue(dev, "project_mm_id", 1);
+}
+
+extern "C" int fq_get_rows(fq_device *dev, const fq_matrix *w, const uint32_t *ids, size_t tokens, void *y, int y_dtype,
+                           size_t y_elems) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!w) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
+    if (w->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "matrix belongs to another device handle");
+    if (int rc = check_dtype(dev, y_dtype)) return rc;
+    if (tokens == 0 || y_elems != tokens * w->cols) return fq_fail(dev, FQ_ERR_SHAPE, "embedding lookup geometry");
+    if (int rc = fq_check_binding(dev, ids, tokens * 4, "ids")) return rc;
+    if (int rc = fq_check_binding(dev, y, y_elems * fq_dtype_size(y_dtype), "y")) return rc;
+    if (int rc = fq_check_no_alias(dev, y, y_elems * fq_dtype_size(y_dtype), ids, tokens * 4, "y")) return rc;
+    if (int rc = fq_launch_get_rows(dev, w, ids, (uint32_t)tokens, y, y_dtype)) return rc;
+    return fq_end_enqueue(dev, "get_rows", 1);
+}
+
+// ------------------------------------------------------------------ feed-forward blocks
+
+extern "C" int fq_dense_ffn(fq_device *dev, const fq_matrix *gate, const fq_matrix *up, const fq_matrix *down,
+                            const float *x, size_t m, float *scratch, size_t scratch_elems, float *out) {
+    if (!dev || !gate || !up || !down) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
+    const size_t width = gate->rows;
+    if (up->rows != width || up->cols != gate->cols || down->cols != width)
+        return fq_fail(dev, FQ_ERR_SHAPE, "feed-forward matrices do not chain");
+    if (scratch_elems < 3 * m * width) return fq_fail(dev, FQ_ERR_SHAPE, "feed-forward scratch holds %zu of %zu floats", scratch_elems, 3 * m * width);
+    float *g = scratch, *u = scratch + m * width, *act = scratch + 2 * m * width;
+    if (int rc = fq_project(dev, gate, x, FQ_F32, m * gate->cols, m, g, FQ_F32, m * width)) return rc;
+    if (int rc = fq_project(dev, up, x, FQ_F32, m * up->cols, m, u, FQ_F32, m * width)) return rc;
+    if (int rc = fq_glu(dev, g, u, m * width, act)) return rc;
+    return fq_project(dev, down, act, FQ_F32, m * width, m, out, FQ_F32, m * down->rows);
+}
+
+// Expert routes at or below which experts use per-route GEMVs (`MV_ID_MAX_ROUTES`,
+// src/hybrid/engine.rs:3586).
+constexpr size_t MV_ID_MAX_ROUTES = 32;
+
+static size_t align4(size_t n) { return (n + 3) & ~(size_t)3; }
+
+struct MoeScratch {
+    float *logits, *weights, *gate, *shared, *shared_tmp, *g, *u, *act, *down, *xg;
+    uint32_t *ids, *offsets, *sorted, *position;
+    size_t total;
+};
+
+static MoeScratch moe_layout(const fq_moe_ffn_desc *f, size_t m, float *base) {
+    MoeScratch s{};
+    const size_t routes = m * f->used;
+    size_t at = 0;
+    auto take = [&](size_t n) { float *p = base ? base + at : nullptr; at += align4(n); return p; };
+    s.logits = take(m * f->experts);
+    s.weights = take(routes);
+    s.gate = take(m);
+    s.shared = take(m * f->hidden);
+    s.shared_tmp = take(3 * m * f->shared_ffn);
+    s.g = take(routes * f->expert_ffn);
+    s.u = take(routes * f->expert_ffn);
+    s.act = take(routes * f->expert_ffn);
+    s.down = take(routes * f->hidden);
+    s.xg = take(routes * f->hidden);
+    s.ids = (uint32_t *)take(routes);
+    s.offsets = (uint32_t *)take(f->experts + 1);
+    s.sorted = (uint32_t *)take(routes);
+    s.position = (uint32_t *)take(routes);
+    s.total = at;
+    return s;
+}
+
+extern "C" size_t fq_moe_ffn_scratch_elems(const fq_moe_ffn_desc *f, size_t m) {
+    return f ? moe_layout(f, m, nullptr).total : 0;
+}
+
+extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float *x, size_t m, float *scratch,
+                          size_t scratch_elems, float *out) {
+    if (!dev || !f || !f->router || !f->gate_exps || !f->up_exps || !f->down_exps || !f->shared_gate || !f->shared_up ||
+        !f->shared_down)
+        return fq_fail(dev, FQ_ERR_PARAM, "incomplete MoE description");
+    const size_t experts = f->experts, used = f->used, hidden = f->hidden, ef = f->expert_ffn;
+    if (f->router->rows != experts || f->router->cols != hidden || f->gate_exps->experts != experts ||
+        f->gate_exps->expert_rows() != ef || f->gate_exps->cols != hidden || f->up_exps->experts != experts ||
+        f->up_exps->expert_rows() != ef || f->down_exps->experts != experts || f->down_exps->expert_rows() != hidden ||
+        f->down_exps->cols != ef || f->shared_gate->rows != f->shared_ffn || f->shared_down->rows != hidden)
+        return fq_fail(dev, FQ_ERR_SHAPE, "MoE matrices do not match the description");
+    MoeScratch s = moe_layout(f, m, scratch);
+    if (scratch_elems < s.total) return fq_fail(dev, FQ_ERR_SHAPE, "MoE scratch holds %zu of %zu floats", scratch_elems, s.total);
+    const size_t routes = m * used;
+    if (int rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts)) return rc;
+    const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
+    if (int rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m,
+                              f->sigmoid, f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate))
+        return rc;
+    if (int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared))
+        return rc;
+    const bool identity = routes <= MV_ID_MAX_ROUTES || dev->exact;
+    if (identity) {
+        if (int rc = fq_project_id(dev, f->gate_exps, x, m * hidden, s.ids, routes, used, s.g, routes * ef)) return rc;
+        if (int rc = fq_project_id(dev, f->up_exps, x, m * hidden, s.ids, routes, used, s.u, routes * ef)) return rc;
+        if (int rc = fq_glu(dev, s.g, s.u, routes * ef, s.act)) return rc;
+        if (int rc = fq_project_id(dev, f->down_exps, s.act, routes * ef, s.ids, routes, 1, s.down, routes * hidden)) return rc;
+    } else {
+        if (int rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position)) return rc;
+        if (int rc = fq_moe_gather(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_F32, routes * hidden, s.offsets, nullptr, experts, m, s.g, FQ_F32, routes * ef)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_F32, routes * hidden, s.offsets, nullptr, experts, m, s.u, FQ_F32, routes * ef)) return rc;
+        if (int rc = fq_glu(dev, s.g, s.u, routes * ef, s.act)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_F32, routes * ef, s.offsets, nullptr, experts, m, s.down, FQ_F32, routes * hidden)) return rc;
+    }
+    return fq_moe_combine(dev, s.down, s.weights, identity ? s.ids : s.position, s.shared, s.gate, (uint32_t)hidden,
+                          (uint32_t)used, (uint32_t)m, identity, out);
+}
+
+// ------------------------------------------------------------------ host-buffer entry points
+
+extern "C" int fq_project_many_host(fq_device *dev, const fq_matrix *const *w, size_t count, const float *x_host,
+                                    size_t m, float *const *y_host) {
+    if (!dev || !w || !x_host || !y_host || count == 0 || m == 0) return fq_fail(dev, FQ_ERR_PARAM, "host projection arguments");
+    const size_t cols = w[0]->cols;
+    size_t need = align4(m * cols) * 4;
+    for (size_t i = 0; i < count; i++) {
+        if (!w[i] || w[i]->cols != cols) return fq_fail(dev, FQ_ERR_SHAPE, "matrices sharing an input differ in width");
+        need += align4(m * w[i]->rows) * 4;
+    }
+    if (need > FQ_HOST_STAGING_BYTES) return fq_fail(dev, FQ_ERR_SHAPE, "%zu bytes exceed the %u-byte staging area", need, FQ_HOST_STAGING_BYTES);
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    float *xd = (float *)dev->staging_dev;
+    // Pageable caller memory is staged through the pinned area so the copies are asynchronous.
+    memcpy(dev->staging_host, x_host, m * cols * 4);
+    if (int rc = fq_check_cuda(dev, cudaMemcpyAsync(xd, dev->staging_host, m * cols * 4, cudaMemcpyHostToDevice, dev->stream), "x upload")) return rc;
+    dev->counters.bytes_uploaded += m * cols * 4;
+    size_t at = align4(m * cols);
+    std::vector<size_t> where(count);
+    for (size_t i = 0; i < count; i++) {
+        float *yd = (float *)dev->staging_dev + at;
+        where[i] = at;
+        if (int rc = fq_project(dev, w[i], xd, FQ_F32, m * cols, m, yd, FQ_F32, m * w[i]->rows)) return rc;
+        at += align4(m * w[i]->rows);
+    }
+    const size_t first = align4(m * cols);
+    if (int rc = fq_check_cuda(dev, cudaMemcpyAsync((float *)dev->staging_host + first, (float *)dev->staging_dev + first,
+                                                    (at - first) * 4, cudaMemcpyDeviceToHost, dev->stream), "y download")) return rc;
+    dev->counters.bytes_downloaded += (at - first) * 4;
+    if (int rc = fq_synchronize(dev)) return rc;
+    for (size_t i = 0; i < count; i++) memcpy(y_host[i], (float *)dev->staging_host + where[i], m * w[i]->rows * 4);
+    return FQ_OK;
+}
+
+extern "C" int fq_project_host(fq_device *dev, const fq_matrix *w, const float *x_host, size_t m, float *y_host) {
+    const fq_matrix *ws[1] = {w};
+    float *ys[1] = {y_host};
+    return fq_project_many_host(dev, ws, 1, x_host, m, ys);
+}

@@ -1,0 +1,91 @@
+// GGUF block layouts and the exact per-value decoders (device side).
+//
+// Layouts (little-endian, f16 = IEEE binary16), as in the reference's `block_q4_K`, `block_q6_K`,
+// `block_q8_0` (src/metal/shaders/hybrid.metal:23-26) and src/quantization.rs:50-73:
+//   Q4_K  144 B / 256 values: f16 d @0, f16 dmin @2, scales[12] @4, qs[128] @16
+//   Q6_K  210 B / 256 values: ql[128] @0, qh[64] @128, int8 scales[16] @192, f16 d @208
+//   Q8_0   34 B /  32 values: f16 d @0, int8 qs[32] @2
+//
+// The decoders reproduce the CPU formulas the reference tests against
+// (src/diffusion/tests.rs:795-864, src/hybrid/draft/gguf.rs:336-343) as explicit round-to-nearest
+// single-precision operations, so the compiler cannot contract them into FMAs and the decoded
+// weights are bit-identical to the CPU decode.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "../../include/ferrum_b200.h"
+
+template <int FMT> struct BlockTraits;
+template <> struct BlockTraits<FQ_Q4_K> { static constexpr int EL = 256, BB = 144; };
+template <> struct BlockTraits<FQ_Q6_K> { static constexpr int EL = 256, BB = 210; };
+template <> struct BlockTraits<FQ_Q8_0> { static constexpr int EL = 32, BB = 34; };
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t bits) {
+    return __half2float(__ushort_as_half(bits));
+}
+// Blocks of Q6_K and Q8_0 are only 2-byte aligned, so f16 fields are read as two bytes' worth.
+__device__ __forceinline__ float load_f16(const uint8_t *p) {
+    return f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(p));
+}
+
+// Q4_K sub-block j's 6-bit scale and minimum (`get_scale_min_k4`, hybrid.metal:417-420).
+__device__ __forceinline__ void q4k_scale_min(const uint8_t *s, int j, uint32_t &sc, uint32_t &mn) {
+    if (j < 4) {
+        sc = s[j] & 63u;
+        mn = s[j + 4] & 63u;
+    } else {
+        sc = (s[j + 4] & 0xFu) | ((uint32_t)(s[j - 4] >> 6) << 4);
+        mn = (uint32_t)(s[j + 4] >> 4) | ((uint32_t)(s[j] >> 6) << 4);
+    }
+}
+
+// ((d * sc) * q) - (dmin * m), each operation rounded on its own.
+__device__ __forceinline__ float q4k_value(float d, float dmin, uint32_t sc, uint32_t mn, uint32_t q) {
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
+}
+// (d * scale) * (q - 32)
+__device__ __forceinline__ float q6k_value(float d, int scale, uint32_t q) {
+    return __fmul_rn(__fmul_rn(d, (float)scale), (float)q - 32.0f);
+}
+
+// Value `idx` (0 .. EL-1, in the format's logical order) of one block.
+template <int FMT> __device__ __forceinline__ float decode_value(const uint8_t *b, int idx);
+
+template <> __device__ __forceinline__ float decode_value<FQ_Q4_K>(const uint8_t *b, int idx) {
+    const int j = idx >> 5, l = idx & 31;
+    uint32_t sc, mn;
+    q4k_scale_min(b + 4, j, sc, mn);
+    const uint8_t v = b[16 + 32 * (j >> 1) + l];
+    const uint32_t q = (j & 1) ? (v >> 4) : (v & 0xFu);
+    return q4k_value(load_f16(b), load_f16(b + 2), sc, mn, q);
+}
+
+template <> __device__ __forceinline__ float decode_value<FQ_Q6_K>(const uint8_t *b, int idx) {
+    const int n = idx >> 7, r = idx & 127, i = r >> 5, l = r & 31;
+    const uint8_t lo = b[64 * n + l + 32 * (i & 1)];
+    const uint32_t nib = (i < 2) ? (lo & 0xFu) : (lo >> 4);
+    const uint32_t hi = (b[128 + 32 * n + l] >> (2 * i)) & 3u;
+    const int scale = (int)(int8_t)b[192 + 8 * n + (l >> 4) + 2 * i];
+    return q6k_value(load_f16(b + 208), scale, nib | (hi << 4));
+}
+
+template <> __device__ __forceinline__ float decode_value<FQ_Q8_0>(const uint8_t *b, int idx) {
+    return __fmul_rn((float)(int)(int8_t)b[2 + idx], load_f16(b));
+}
+
+// Round to nearest even (src/hybrid/draft/gguf.rs:362-369).  cvt.rn.bf16.f32 agrees for every
+// non-NaN input; a NaN stays a quiet NaN but its payload is the canonical one.
+__device__ __forceinline__ __nv_bfloat16 to_bf16_rne(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T> __device__ __forceinline__ float load_act(const T *p);
+template <> __device__ __forceinline__ float load_act<float>(const float *p) { return *p; }
+template <> __device__ __forceinline__ float load_act<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    return __bfloat162float(*p);
+}
+template <typename T> __device__ __forceinline__ void store_act(T *p, float v);
+template <> __device__ __forceinline__ void store_act<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_act<__nv_bfloat16>(__nv_bfloat16 *p, float v) {
+    *p = to_bf16_rne(v);
+}

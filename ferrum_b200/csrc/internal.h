@@ -1,0 +1,86 @@
+// Shared declarations of the library's translation units (host side).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+
+#include "../../include/ferrum_b200.h"
+
+// Largest activation-row count the decode/verify GEMV handles with weights streamed once.
+constexpr int FQ_GEMV_MAX_M = 16;
+// Widest projection input the activation-preparation scratch is sized for.
+constexpr size_t FQ_MAX_COLS = 65536;
+
+struct fq_device {
+    int ordinal = 0;
+    int sm_count = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    std::string error;
+    bool failed = false;          // an asynchronous failure was reported; enqueues are refused
+    bool exact = false;
+    int fail_after = -1;          // test hook: enqueues left before an injected failure
+    bool fail_completion = false; // test hook: next synchronize reports failure
+    fq_counters counters{};
+    std::map<uintptr_t, size_t> allocations; // buffers handed out by fq_buffer_alloc
+    // Fixed scratch, allocated once at creation.
+    void *xprep = nullptr;        // prepared activations of the tensor-core GEMV
+    size_t xprep_bytes = 0;
+    void *staging_dev = nullptr;  // device side of the host-buffer entry points
+    void *staging_host = nullptr; // pinned host side
+};
+
+struct fq_matrix {
+    fq_device *dev = nullptr;
+    int format = 0;
+    uint64_t rows = 0, cols = 0, experts = 1, row_bytes = 0, byte_size = 0;
+    uint32_t block_elems = 0, block_bytes = 0;
+    uint8_t *data = nullptr; // device copy of the GGUF blocks, byte for byte
+    uint64_t expert_rows() const { return rows / experts; }
+};
+
+int fq_fail(fq_device *dev, int status, const char *fmt, ...);
+int fq_check_cuda(fq_device *dev, cudaError_t e, const char *what);
+// Common prologue of every enqueue: refuses a failed handle, runs the injected-failure hook,
+// makes the device current.
+int fq_begin_enqueue(fq_device *dev);
+int fq_end_enqueue(fq_device *dev, const char *what, int kernels);
+// Binding checks shared by the op surface (null, alignment, ownership range, overlap).
+int fq_check_binding(fq_device *dev, const void *p, size_t bytes, const char *name);
+int fq_check_no_alias(fq_device *dev, const void *out, size_t out_bytes, const void *in,
+                      size_t in_bytes, const char *name);
+
+inline size_t fq_dtype_size(int dtype) { return dtype == FQ_BF16 ? 2 : 4; }
+
+// Kernel launchers (one per translation unit); all enqueue on dev->stream and return a status.
+struct ProjectArgs {
+    const uint8_t *w;
+    uint32_t format, rows, cols, row_bytes; // rows = rows of one expert slice
+    const void *x;
+    void *y;
+    int x_dtype, y_dtype;
+    uint32_t m;        // activation rows (project) / routes (project_id) / 0 (grouped)
+    // expert addressing
+    const uint32_t *ids = nullptr;     // project_id: expert of each route
+    uint32_t x_div = 1;
+    const uint32_t *offsets = nullptr; // grouped: row ranges
+    const uint32_t *slots = nullptr;
+    uint32_t groups = 0, max_rows = 0;
+    uint32_t experts = 1;              // expert slices stored in w
+};
+int fq_launch_project_exact(fq_device *dev, const ProjectArgs &a);
+int fq_launch_project_id_exact(fq_device *dev, const ProjectArgs &a);
+int fq_launch_project_grouped_exact(fq_device *dev, const ProjectArgs &a);
+int fq_launch_get_rows(fq_device *dev, const fq_matrix *w, const uint32_t *ids, uint32_t tokens,
+                       void *y, int y_dtype);
+// Tensor-core decode/verify GEMV (M <= FQ_GEMV_MAX_M, F32 in/out); returns FQ_ERR_UNSUPPORTED
+// when the shape has no fast kernel so the caller can fall back to the exact one.
+int fq_launch_gemv_fast(fq_device *dev, const ProjectArgs &a);
+size_t fq_gemv_scratch_bytes();
+// tcgen05 dequant-GEMM (BF16 in/out); same fallback contract.
+int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a);

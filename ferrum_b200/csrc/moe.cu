@@ -1,0 +1,306 @@
+// Mixture-of-experts glue: routing, expert-major map, gather, combine and the gated unit.
+// Contracts follow the reference kernels h_moe_route / h_moe_map / h_moe_gather / h_moe_combine /
+// h_swiglu (src/metal/shaders/hybrid.metal:2252-2388, 1606-1613).
+#include "internal.h"
+
+namespace {
+
+constexpr int ROUTE_THREADS = 256;
+constexpr int MAX_EXPERTS = 1024; // the reference's map kernel holds counts[1024]
+
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int i = 0; i < warps; i++) total += scratch[i];
+    return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float *scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float best = -INFINITY;
+    for (int i = 0; i < warps; i++) best = fmaxf(best, scratch[i]);
+    return best;
+}
+
+// One block per token.  Scores: softmax over the logits (max, exp, sum, divide) or a logistic per
+// logit; `used` rounds of arg-max with ties to the lower index; weights divided by the picked sum
+// when `norm`; shared-expert gate = logistic(dot(x, shared_w)) or 1.
+__global__ void __launch_bounds__(ROUTE_THREADS)
+k_moe_route(const float *__restrict__ logits, const float *__restrict__ x, const float *__restrict__ shared_w,
+            uint32_t experts, uint32_t used, uint32_t hidden, int sigmoid, int norm, int shared_gate,
+            uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate) {
+    __shared__ float prob[MAX_EXPERTS];
+    __shared__ float scratch[ROUTE_THREADS / 32];
+    __shared__ float best_v[ROUTE_THREADS / 32];
+    __shared__ uint32_t best_i[ROUTE_THREADS / 32];
+    __shared__ float picked[64];
+    const uint32_t t = blockIdx.x, tid = threadIdx.x;
+    const float *row = logits + (size_t)t * experts;
+    if (sigmoid) {
+        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) prob[e] = 1.f / (1.f + expf(-row[e]));
+    } else {
+        float mx = -INFINITY;
+        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) mx = fmaxf(mx, row[e]);
+        mx = block_max(mx, scratch);
+        float part = 0.f;
+        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) {
+            const float v = expf(row[e] - mx);
+            prob[e] = v;
+            part += v;
+        }
+        const float total = block_sum(part, scratch);
+        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) prob[e] = prob[e] / total;
+    }
+    __syncthreads();
+    float picked_sum = 0.f;
+    for (uint32_t k = 0; k < used; k++) {
+        float bv = -INFINITY;
+        uint32_t bi = 0xffffffffu;
+        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) {
+            const float v = prob[e];
+            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if ((tid & 31) == 0) { best_v[tid >> 5] = bv; best_i[tid >> 5] = bi; }
+        __syncthreads();
+        bv = best_v[0];
+        bi = best_i[0];
+        for (int i = 1; i < ROUTE_THREADS / 32; i++)
+            if (best_v[i] > bv || (best_v[i] == bv && best_i[i] < bi)) { bv = best_v[i]; bi = best_i[i]; }
+        picked_sum += bv;
+        if (tid == 0) {
+            ids[(size_t)t * used + k] = bi;
+            if (k < 64) picked[k] = bv;
+            else weights[(size_t)t * used + k] = bv;
+            prob[bi] = -1.f; // scores are non-negative, so a taken expert never wins again
+        }
+        __syncthreads();
+    }
+    for (uint32_t k = tid; k < used; k += ROUTE_THREADS) {
+        const float v = k < 64 ? picked[k] : weights[(size_t)t * used + k];
+        weights[(size_t)t * used + k] = norm ? v / picked_sum : v;
+    }
+    if (shared_gate) {
+        float dot = 0.f;
+        for (uint32_t i = tid; i < hidden; i += ROUTE_THREADS) dot = fmaf(x[(size_t)t * hidden + i], shared_w[i], dot);
+        dot = block_sum(dot, scratch);
+        if (tid == 0) gate[t] = 1.f / (1.f + expf(-dot));
+    } else if (tid == 0) {
+        gate[t] = 1.f;
+    }
+}
+
+// Stable counting sort of routes by expert, one block of 32 warps.  Warp w owns the contiguous
+// slice [w*S, (w+1)*S) of routes; `cnt[w][e]` first holds the slice's count of expert e, then the
+// row where the slice's next route of expert e goes.
+__global__ void __launch_bounds__(1024)
+k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, uint32_t *__restrict__ offsets,
+          uint32_t *__restrict__ sorted, uint32_t *__restrict__ position) {
+    extern __shared__ uint32_t cnt[]; // [32][experts] + [experts + 1]
+    uint32_t *total = cnt + 32 * experts;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (uint32_t i = tid; i < 32 * experts + experts + 1; i += 1024) cnt[i] = 0;
+    __syncthreads();
+    const uint32_t slice = ((routes + 31) / 32 + 31) / 32 * 32; // multiple of 32 routes per warp
+    const uint32_t begin = warp * slice, end = min(routes, begin + slice);
+    for (uint32_t base = begin; base < end; base += 32) {
+        const uint32_t r = base + lane;
+        const bool live = r < end;
+        const uint32_t e = live ? ids[r] : 0xffffffffu;
+        const uint32_t peers = __match_any_sync(0xffffffffu, e);
+        if (live && e < experts && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+    // Per expert: totals, then an exclusive scan over experts, then per-warp bases.
+    for (uint32_t e = tid; e < experts; e += 1024) {
+        uint32_t n = 0;
+        for (int w = 0; w < 32; w++) n += cnt[w * experts + e];
+        total[e] = n;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t carry = 0;
+        for (uint32_t e0 = 0; e0 < experts; e0 += 32) {
+            const uint32_t e = e0 + lane;
+            const uint32_t n = e < experts ? total[e] : 0;
+            uint32_t incl = n;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const uint32_t o = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= (uint32_t)off) incl += o;
+            }
+            if (e < experts) {
+                total[e] = carry + incl - n;
+                offsets[e] = carry + incl - n;
+            }
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) offsets[experts] = carry;
+    }
+    __syncthreads();
+    for (uint32_t e = tid; e < experts; e += 1024) {
+        uint32_t at = total[e];
+        for (int w = 0; w < 32; w++) {
+            const uint32_t n = cnt[w * experts + e];
+            cnt[w * experts + e] = at;
+            at += n;
+        }
+    }
+    __syncthreads();
+    for (uint32_t base = begin; base < end; base += 32) {
+        const uint32_t r = base + lane;
+        const bool live = r < end;
+        const uint32_t e = live ? ids[r] : 0xffffffffu;
+        const uint32_t peers = __match_any_sync(0xffffffffu, e);
+        if (live && e < experts) {
+            const uint32_t rank = __popc(peers & ((1u << lane) - 1));
+            const uint32_t at = cnt[warp * experts + e] + rank;
+            sorted[at] = r;
+            position[r] = at;
+        }
+        __syncwarp();
+        if (live && e < experts && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
+        __syncwarp();
+    }
+}
+
+// xg[row] = x[sorted[row] / used]
+__global__ void k_moe_gather(const float *__restrict__ x, const uint32_t *__restrict__ sorted, uint32_t hidden,
+                             uint32_t used, float *__restrict__ xg) {
+    const uint32_t row = blockIdx.x;
+    const uint32_t token = sorted[row] / used;
+    const float *src = x + (size_t)token * hidden;
+    float *dst = xg + (size_t)row * hidden;
+    if ((hidden & 3u) == 0) {
+        for (uint32_t i = threadIdx.x; i < hidden / 4; i += blockDim.x)
+            reinterpret_cast<float4 *>(dst)[i] = reinterpret_cast<const float4 *>(src)[i];
+    } else {
+        for (uint32_t i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// out[t][i] = sum_s w[t][s] * down[row(t, s)][i] + gate[t] * shared[t][i]
+__global__ void k_moe_combine(const float *__restrict__ down, const float *__restrict__ weights,
+                              const uint32_t *__restrict__ position, const float *__restrict__ shared,
+                              const float *__restrict__ gate, uint32_t hidden, uint32_t used, uint32_t tokens,
+                              int identity, float *__restrict__ out) {
+    const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (size_t)tokens * hidden) return;
+    const uint32_t t = gid / hidden, i = gid % hidden;
+    float acc = 0.f;
+    for (uint32_t s = 0; s < used; s++) {
+        const uint32_t r = t * used + s;
+        const uint32_t row = identity ? r : position[r];
+        acc = fmaf(weights[r], down[(size_t)row * hidden + i], acc);
+    }
+    out[gid] = acc + gate[t] * shared[gid];
+}
+
+// out = g / (1 + exp(-g)) * u
+__global__ void k_swiglu(const float *__restrict__ g, const float *__restrict__ u, size_t n, float *__restrict__ y) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float x = g[i];
+        y[i] = x / (1.f + expf(-x)) * u[i];
+    }
+}
+
+} // namespace
+
+extern "C" int fq_moe_route(fq_device *dev, const float *logits, const float *x, const float *shared_w,
+                            uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens, int sigmoid,
+                            int norm, int shared_gate, uint32_t *ids, float *weights, float *gate) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (experts == 0 || experts > MAX_EXPERTS || used == 0 || used > experts || tokens == 0)
+        return fq_fail(dev, FQ_ERR_SHAPE, "routing %u of %u experts for %u tokens", used, experts, tokens);
+    if (int rc = fq_check_binding(dev, logits, (size_t)tokens * experts * 4, "logits")) return rc;
+    if (int rc = fq_check_binding(dev, ids, (size_t)tokens * used * 4, "ids")) return rc;
+    if (int rc = fq_check_binding(dev, weights, (size_t)tokens * used * 4, "weights")) return rc;
+    if (int rc = fq_check_binding(dev, gate, (size_t)tokens * 4, "shared gate")) return rc;
+    if (shared_gate) {
+        if (int rc = fq_check_binding(dev, x, (size_t)tokens * hidden * 4, "x")) return rc;
+        if (int rc = fq_check_binding(dev, shared_w, (size_t)hidden * 4, "shared gate weight")) return rc;
+    }
+    if (int rc = fq_check_no_alias(dev, ids, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "ids")) return rc;
+    if (int rc = fq_check_no_alias(dev, weights, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "weights")) return rc;
+    k_moe_route<<<tokens, ROUTE_THREADS, 0, dev->stream>>>(logits, x, shared_w, experts, used, hidden, sigmoid, norm,
+                                                           shared_gate, ids, weights, gate);
+    return fq_end_enqueue(dev, "moe_route", 1);
+}
+
+extern "C" int fq_moe_map(fq_device *dev, const uint32_t *ids, uint32_t experts, uint32_t routes,
+                          uint32_t *offsets, uint32_t *sorted, uint32_t *position) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (experts == 0 || experts > MAX_EXPERTS || routes == 0)
+        return fq_fail(dev, FQ_ERR_SHAPE, "map of %u routes over %u experts", routes, experts);
+    if (int rc = fq_check_binding(dev, ids, (size_t)routes * 4, "ids")) return rc;
+    if (int rc = fq_check_binding(dev, offsets, (size_t)(experts + 1) * 4, "offsets")) return rc;
+    if (int rc = fq_check_binding(dev, sorted, (size_t)routes * 4, "sorted")) return rc;
+    if (int rc = fq_check_binding(dev, position, (size_t)routes * 4, "position")) return rc;
+    const size_t smem = ((size_t)33 * experts + 1) * sizeof(uint32_t);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k_moe_map, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fq_check_cuda(dev, e, "moe_map shared memory");
+    }
+    k_moe_map<<<1, 1024, smem, dev->stream>>>(ids, experts, routes, offsets, sorted, position);
+    return fq_end_enqueue(dev, "moe_map", 1);
+}
+
+extern "C" int fq_moe_gather(fq_device *dev, const float *x, const uint32_t *sorted, uint32_t hidden,
+                             uint32_t used, uint32_t routes, float *xg) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (hidden == 0 || used == 0 || routes == 0) return fq_fail(dev, FQ_ERR_SHAPE, "gather geometry");
+    if (int rc = fq_check_binding(dev, x, (size_t)((routes + used - 1) / used) * hidden * 4, "x")) return rc;
+    if (int rc = fq_check_binding(dev, sorted, (size_t)routes * 4, "sorted")) return rc;
+    if (int rc = fq_check_binding(dev, xg, (size_t)routes * hidden * 4, "xg")) return rc;
+    if (int rc = fq_check_no_alias(dev, xg, (size_t)routes * hidden * 4, x, (size_t)((routes + used - 1) / used) * hidden * 4, "xg")) return rc;
+    k_moe_gather<<<routes, 256, 0, dev->stream>>>(x, sorted, hidden, used, xg);
+    return fq_end_enqueue(dev, "moe_gather", 1);
+}
+
+extern "C" int fq_moe_combine(fq_device *dev, const float *down, const float *weights, const uint32_t *position,
+                              const float *shared, const float *gate, uint32_t hidden, uint32_t used,
+                              uint32_t tokens, int identity, float *out) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (hidden == 0 || used == 0 || tokens == 0) return fq_fail(dev, FQ_ERR_SHAPE, "combine geometry");
+    const size_t routes = (size_t)tokens * used;
+    if (int rc = fq_check_binding(dev, down, routes * hidden * 4, "down")) return rc;
+    if (int rc = fq_check_binding(dev, weights, routes * 4, "weights")) return rc;
+    if (!identity)
+        if (int rc = fq_check_binding(dev, position, routes * 4, "position")) return rc;
+    if (int rc = fq_check_binding(dev, shared, (size_t)tokens * hidden * 4, "shared")) return rc;
+    if (int rc = fq_check_binding(dev, gate, (size_t)tokens * 4, "shared gate")) return rc;
+    if (int rc = fq_check_binding(dev, out, (size_t)tokens * hidden * 4, "out")) return rc;
+    if (int rc = fq_check_no_alias(dev, out, (size_t)tokens * hidden * 4, down, routes * hidden * 4, "out")) return rc;
+    if (int rc = fq_check_no_alias(dev, out, (size_t)tokens * hidden * 4, shared, (size_t)tokens * hidden * 4, "out")) return rc;
+    const size_t n = (size_t)tokens * hidden;
+    k_moe_combine<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(down, weights, position, shared, gate, hidden,
+                                                                       used, tokens, identity, out);
+    return fq_end_enqueue(dev, "moe_combine", 1);
+}
+
+extern "C" int fq_glu(fq_device *dev, const float *gate, const float *up, size_t n, float *out) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (n == 0) return fq_fail(dev, FQ_ERR_SHAPE, "empty gated unit");
+    if (int rc = fq_check_binding(dev, gate, n * 4, "gate")) return rc;
+    if (int rc = fq_check_binding(dev, up, n * 4, "up")) return rc;
+    if (int rc = fq_check_binding(dev, out, n * 4, "out")) return rc;
+    k_swiglu<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(gate, up, n, out);
+    return fq_end_enqueue(dev, "glu", 1);
+}

@@ -1,0 +1,308 @@
+"""Host-side mirror of the reference's quantized-linear op surface, over the C ABI.
+
+Names, argument order and error behaviour follow ``HybridModel::project / project_id /
+project_mm_id(_in) / get_rows / moe_ffn / dense_ffn`` (src/hybrid/engine.rs:2881-3500) and
+``Matrix::from_packed`` (src/hybrid/weights.rs:1301-1330).  Tensors are ``torch`` CUDA tensors, used
+only as device memory: every computation happens inside ``libferrum_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import BF16, F32, Q4_K, Q6_K, Q8_0  # noqa: F401  (re-exported)
+
+
+class FerrumError(RuntimeError):
+    """Base of the errors below; ``status`` is the C ABI status code."""
+    status = -1
+
+
+class ShapeError(FerrumError):  # Error::Shape
+    status = _lib.ERR_SHAPE
+
+
+class RangeError(FerrumError):  # Error::Range
+    status = _lib.ERR_RANGE
+
+
+class DeviceMismatch(FerrumError):  # Error::DeviceMismatch
+    status = _lib.ERR_DEVICE
+
+
+class AliasError(FerrumError):  # Error::Dispatch("... alias")
+    status = _lib.ERR_ALIAS
+
+
+class WeightError(FerrumError):  # Error::Weight / Error::Gguf
+    status = _lib.ERR_WEIGHT
+
+
+class SynchronizationError(FerrumError):  # Error::Synchronization
+    status = _lib.ERR_SYNC
+
+
+class TimeoutError_(FerrumError):
+    status = _lib.ERR_TIMEOUT
+
+
+class CudaError(FerrumError):
+    status = _lib.ERR_CUDA
+
+
+class ParameterError(FerrumError):  # Error::Parameter
+    status = _lib.ERR_PARAM
+
+
+class Unsupported(FerrumError):
+    status = _lib.ERR_UNSUPPORTED
+
+
+_BY_STATUS = {c.status: c for c in (ShapeError, RangeError, DeviceMismatch, AliasError, WeightError,
+                                    SynchronizationError, TimeoutError_, CudaError, ParameterError, Unsupported)}
+
+
+def _dtype_id(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise Unsupported(f"tensor dtype {t.dtype}")
+
+
+class Device:
+    """``MetalDevice`` counterpart: one CUDA device, one stream, fixed scratch."""
+
+    def __init__(self, ordinal: int = 0, use_torch_stream: bool = True):
+        self._L = _lib.load()
+        h = C.c_void_p()
+        rc = self._L.fq_device_create(ordinal, C.byref(h))
+        if rc != _lib.OK:
+            raise _BY_STATUS.get(rc, FerrumError)(f"fq_device_create({ordinal}) -> {self._L.fq_status_name(rc).decode()}")
+        self.handle = h
+        self.ordinal = ordinal
+        self.torch_device = torch.device("cuda", ordinal)
+        if use_torch_stream:
+            # Share torch's current stream so tensors produced by torch are ordered with the kernels.
+            self.set_stream(torch.cuda.current_stream(self.torch_device).cuda_stream)
+
+    def check(self, rc: int) -> None:
+        if rc != _lib.OK:
+            msg = self._L.fq_last_error(self.handle).decode()
+            raise _BY_STATUS.get(rc, FerrumError)(msg or self._L.fq_status_name(rc).decode())
+
+    def set_stream(self, cuda_stream: Optional[int]) -> None:
+        self.check(self._L.fq_device_set_stream(self.handle, C.c_void_p(cuda_stream or 0)))
+
+    def synchronize(self) -> None:
+        self.check(self._L.fq_synchronize(self.handle))
+
+    def recover(self) -> None:
+        self.check(self._L.fq_device_recover(self.handle))
+
+    def set_exact(self, on: bool) -> None:
+        self.check(self._L.fq_set_exact(self.handle, int(on)))
+
+    def counters(self) -> _lib.Counters:
+        c = _lib.Counters()
+        self.check(self._L.fq_get_counters(self.handle, C.byref(c)))
+        return c
+
+    def fail_after(self, n: int) -> None:
+        self.check(self._L.fq_test_fail_after(self.handle, n))
+
+    def fail_completion(self) -> None:
+        self.check(self._L.fq_test_fail_completion(self.handle))
+
+    def close(self) -> None:
+        if self.handle:
+            self._L.fq_device_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Matrix:
+    """``Matrix`` counterpart (src/hybrid/weights.rs:107-143): immutable packed blocks on the device."""
+
+    def __init__(self, device: Device, handle: C.c_void_p):
+        self.device = device
+        self.handle = handle
+        info = _lib.MatrixInfo()
+        device.check(device._L.fq_matrix_get_info(handle, C.byref(info)))
+        self.rows, self.cols, self.experts = int(info.rows), int(info.cols), int(info.experts)
+        self.row_bytes, self.format = int(info.row_bytes), int(info.format)
+        self._byte_size = int(info.byte_size)
+
+    @classmethod
+    def from_packed(cls, device: Device, rows: int, cols: int, experts: int, fmt: int, packed) -> "Matrix":
+        buf = np.ascontiguousarray(np.frombuffer(packed, dtype=np.uint8) if not isinstance(packed, np.ndarray) else packed,
+                                   dtype=np.uint8)
+        h = C.c_void_p()
+        device.check(device._L.fq_matrix_create(device.handle, fmt, rows, cols, experts,
+                                                C.c_void_p(buf.ctypes.data), buf.size, C.byref(h)))
+        return cls(device, h)
+
+    def byte_size(self) -> int:
+        return self._byte_size
+
+    def expert_rows(self) -> int:
+        return self.rows // self.experts
+
+    def close(self) -> None:
+        if self.handle and self.device.handle:
+            self.device._L.fq_matrix_destroy(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(d: Device, *tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda or t.device != d.torch_device:
+            raise DeviceMismatch(f"tensor on {t.device}, device handle on {d.torch_device}")
+        if not t.is_contiguous():
+            raise ShapeError("tensor is not contiguous")
+
+
+def project(d: Device, w: Matrix, x: torch.Tensor, m: int, y: torch.Tensor) -> None:
+    """``HybridModel::project(d, w, x, m, y)``: y[m, rows] = x[m, cols] . W^T."""
+    _need(d, x, y)
+    d.check(d._L.fq_project(d.handle, w.handle, _ptr(x), _dtype_id(x), x.numel(), m, _ptr(y), _dtype_id(y), y.numel()))
+
+
+def project_id(d: Device, w: Matrix, x: torch.Tensor, ids: torch.Tensor, routes: int, x_div: int, y: torch.Tensor) -> None:
+    """``HybridModel::project_id``: route r uses expert ids[r] on activation row r // x_div."""
+    _need(d, x, ids, y)
+    if x.dtype != torch.float32 or y.dtype != torch.float32:
+        raise Unsupported("expert GEMV is F32 in, F32 out")
+    d.check(d._L.fq_project_id(d.handle, w.handle, _ptr(x), x.numel(), _ptr(ids), routes, x_div, _ptr(y), y.numel()))
+
+
+def project_mm_id_in(d: Device, w: Matrix, x: torch.Tensor, offsets: torch.Tensor,
+                     slots: Optional[tuple], max_rows: int, y: torch.Tensor) -> None:
+    """``HybridModel::project_mm_id_in``: ``slots`` is ``None`` or ``(table, k)``."""
+    table, groups = (slots if slots is not None else (None, w.experts))
+    _need(d, x, offsets, table, y)
+    d.check(d._L.fq_project_mm_id(d.handle, w.handle, _ptr(x), _dtype_id(x), x.numel(), _ptr(offsets), _ptr(table),
+                                  groups, max_rows, _ptr(y), _dtype_id(y), y.numel()))
+
+
+def project_mm_id(d: Device, w: Matrix, x: torch.Tensor, offsets: torch.Tensor, max_rows: int, y: torch.Tensor) -> None:
+    project_mm_id_in(d, w, x, offsets, None, max_rows, y)
+
+
+def get_rows(d: Device, w: Matrix, ids: torch.Tensor, y: torch.Tensor) -> None:
+    """``HybridModel::get_rows``: y[t] = exact decode of row ids[t]."""
+    _need(d, ids, y)
+    d.check(d._L.fq_get_rows(d.handle, w.handle, _ptr(ids), ids.numel(), _ptr(y), _dtype_id(y), y.numel()))
+
+
+def moe_route(d, logits, x, shared_w, experts, used, hidden, tokens, sigmoid, norm, shared_gate, ids, weights, gate):
+    _need(d, logits, x, shared_w, ids, weights, gate)
+    d.check(d._L.fq_moe_route(d.handle, _ptr(logits), _ptr(x), _ptr(shared_w), experts, used, hidden, tokens,
+                              int(sigmoid), int(norm), int(shared_gate), _ptr(ids), _ptr(weights), _ptr(gate)))
+
+
+def moe_map(d, ids, experts, routes, offsets, sorted_, position):
+    _need(d, ids, offsets, sorted_, position)
+    d.check(d._L.fq_moe_map(d.handle, _ptr(ids), experts, routes, _ptr(offsets), _ptr(sorted_), _ptr(position)))
+
+
+def moe_gather(d, x, sorted_, hidden, used, routes, xg):
+    _need(d, x, sorted_, xg)
+    d.check(d._L.fq_moe_gather(d.handle, _ptr(x), _ptr(sorted_), hidden, used, routes, _ptr(xg)))
+
+
+def moe_combine(d, down, weights, position, shared, gate, hidden, used, tokens, identity, out):
+    _need(d, down, weights, position, shared, gate, out)
+    d.check(d._L.fq_moe_combine(d.handle, _ptr(down), _ptr(weights), _ptr(position), _ptr(shared), _ptr(gate),
+                                hidden, used, tokens, int(identity), _ptr(out)))
+
+
+def glu(d, gate, up, out):
+    _need(d, gate, up, out)
+    d.check(d._L.fq_glu(d.handle, _ptr(gate), _ptr(up), gate.numel(), _ptr(out)))
+
+
+def dense_ffn(d, gate: Matrix, up: Matrix, down: Matrix, x, m, scratch, out):
+    _need(d, x, scratch, out)
+    d.check(d._L.fq_dense_ffn(d.handle, gate.handle, up.handle, down.handle, _ptr(x), m, _ptr(scratch),
+                              scratch.numel(), _ptr(out)))
+
+
+@dataclass
+class MoeFfn:
+    """``MoeFfn`` of the reference (src/hybrid/engine.rs:2881-2906) plus its geometry."""
+    router: Matrix
+    gate_exps: Matrix
+    up_exps: Matrix
+    down_exps: Matrix
+    shared_gate: Matrix
+    shared_up: Matrix
+    shared_down: Matrix
+    shared_gate_inp: Optional[torch.Tensor]
+    experts: int
+    used: int
+    hidden: int
+    expert_ffn: int
+    shared_ffn: int
+    sigmoid: bool = False
+    norm_weights: bool = True
+
+    def desc(self) -> _lib.MoeFfnDesc:
+        return _lib.MoeFfnDesc(
+            self.router.handle, self.gate_exps.handle, self.up_exps.handle, self.down_exps.handle,
+            self.shared_gate.handle, self.shared_up.handle, self.shared_down.handle,
+            C.c_void_p(0 if self.shared_gate_inp is None else self.shared_gate_inp.data_ptr()),
+            self.experts, self.used, self.hidden, self.expert_ffn, self.shared_ffn,
+            int(self.sigmoid), int(self.norm_weights))
+
+
+def moe_ffn_scratch_elems(d: Device, f: MoeFfn, m: int) -> int:
+    desc = f.desc()
+    return int(d._L.fq_moe_ffn_scratch_elems(C.byref(desc), m))
+
+
+def moe_ffn(d: Device, f: MoeFfn, x, m, scratch, out):
+    _need(d, x, scratch, out)
+    desc = f.desc()
+    d.check(d._L.fq_moe_ffn(d.handle, C.byref(desc), _ptr(x), m, _ptr(scratch), scratch.numel(), _ptr(out)))
+
+
+def project_host(d: Device, w: Matrix, x_host: np.ndarray, m: int, y_host: np.ndarray) -> None:
+    """Host-buffer projection: upload x, project, download y, wait."""
+    assert x_host.dtype == np.float32 and y_host.dtype == np.float32
+    assert x_host.flags["C_CONTIGUOUS"] and y_host.flags["C_CONTIGUOUS"]
+    if x_host.size != m * w.cols or y_host.size != m * w.rows:
+        raise ShapeError("host projection geometry")
+    d.check(d._L.fq_project_host(d.handle, w.handle, C.c_void_p(x_host.ctypes.data), m, C.c_void_p(y_host.ctypes.data)))
+
+
+def project_many_host(d: Device, ws: Sequence[Matrix], x_host: np.ndarray, m: int, ys: Sequence[np.ndarray]) -> None:
+    n = len(ws)
+    wa = (C.c_void_p * n)(*[w.handle.value for w in ws])
+    ya = (C.c_void_p * n)(*[y.ctypes.data for y in ys])
+    for w, y in zip(ws, ys):
+        if y.size != m * w.rows or y.dtype != np.float32:
+            raise ShapeError("host projection geometry")
+    d.check(d._L.fq_project_many_host(d.handle, wa, n, C.c_void_p(x_host.ctypes.data), m, ya))

@@ -1,0 +1,197 @@
+/*
+ * ferrum_b200 — C ABI of the B200 (sm_100a) K-quant dequantize-and-multiply library.
+ *
+ * This is the boundary a Ferrum build binds in place of `MetalDevice::dispatch_hybrid` for the
+ * quantized-linear op surface.  Each entry point names the reference interface it replaces
+ * (paths are relative to the reference crate).  Conventions shared by all of them:
+ *
+ *   - every call returns an `fq_status`; nothing aborts; `fq_last_error` gives the message;
+ *   - work is ENQUEUED on the device handle's CUDA stream and runs asynchronously, like the
+ *     reference's command epochs (src/metal/mod.rs:456, 563-633); `fq_synchronize` is the only
+ *     blocking call and the place where asynchronous failures surface;
+ *   - weights are immutable packed GGUF blocks owned by the library behind `fq_matrix`
+ *     (src/tensor/mod.rs:336-385); activations and outputs are caller-owned DEVICE pointers,
+ *     16-byte aligned, that must not overlap one another (src/metal/mod.rs:854-896);
+ *   - nothing allocates device memory after `fq_device_create` / `fq_matrix_create`
+ *     (the reference: "nothing allocates after load");
+ *   - handles are not thread-safe: one host thread per device handle
+ *     (the reference's handles are `Rc`, `!Send`, `!Sync`).
+ */
+#ifndef FERRUM_B200_H
+#define FERRUM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct fq_device fq_device;
+typedef struct fq_matrix fq_matrix;
+
+/* src/error.rs: Shape, Range, DeviceMismatch, Dispatch("alias"), Weight, Synchronization. */
+typedef enum fq_status {
+    FQ_OK = 0,
+    FQ_ERR_SHAPE = 1,       /* element counts do not match the matrix geometry */
+    FQ_ERR_RANGE = 2,       /* a binding is null, misaligned or outside its allocation */
+    FQ_ERR_DEVICE = 3,      /* a handle or pointer belongs to another device */
+    FQ_ERR_ALIAS = 4,       /* an output overlaps an input or another output */
+    FQ_ERR_WEIGHT = 5,      /* packed payload rejected (length, block count, non-finite scale) */
+    FQ_ERR_SYNC = 6,        /* asynchronous failure reported at enqueue or synchronize */
+    FQ_ERR_TIMEOUT = 7,     /* a bounded device-side wait gave up */
+    FQ_ERR_CUDA = 8,        /* CUDA runtime error */
+    FQ_ERR_PARAM = 9,       /* invalid argument */
+    FQ_ERR_UNSUPPORTED = 10 /* format / dtype combination without a kernel */
+} fq_status;
+
+/* GGML type ids, as in `Format::from_type` (src/hybrid/weights.rs:47-66) and
+ * `QuantizationFormat` (src/quantization.rs:24-73). */
+typedef enum fq_format { FQ_Q8_0 = 8, FQ_Q4_K = 12, FQ_Q6_K = 14 } fq_format;
+
+/* Activation / output element types (GGML ids of F32 and BF16). */
+typedef enum fq_dtype { FQ_F32 = 0, FQ_BF16 = 30 } fq_dtype;
+
+/* `Matrix{rows, cols, experts, format, row_bytes}` (src/hybrid/weights.rs:107-115).
+ * `rows` counts all experts' rows (rows_per_expert * experts). */
+typedef struct fq_matrix_info {
+    uint64_t rows, cols, experts, row_bytes, byte_size;
+    int32_t format;
+} fq_matrix_info;
+
+/* `Counters` (src/metal/mod.rs:209-228): kernels enqueued and synchronisations since creation. */
+typedef struct fq_counters {
+    uint64_t dispatches, synchronizes, bytes_uploaded, bytes_downloaded;
+} fq_counters;
+
+/* ---- device, stream, errors ------------------------------------------------------------ */
+
+/* `MetalDevice::new` (src/metal/mod.rs:480-560).  Creates the stream and the fixed scratch. */
+int fq_device_create(int ordinal, fq_device **out);
+int fq_device_destroy(fq_device *dev);
+/* Enqueue on a caller-provided `cudaStream_t` (NULL restores the handle's own stream). */
+int fq_device_set_stream(fq_device *dev, void *cuda_stream);
+void *fq_device_stream(fq_device *dev);
+/* `MetalDevice::synchronize` (src/metal/mod.rs:633): blocks; reports asynchronous errors as
+ * FQ_ERR_SYNC and leaves the handle refusing further enqueues until `fq_device_recover`. */
+int fq_synchronize(fq_device *dev);
+int fq_device_recover(fq_device *dev);
+const char *fq_last_error(fq_device *dev);
+const char *fq_status_name(int status);
+int fq_get_counters(fq_device *dev, fq_counters *out);
+/* `FERRUM_HYBRID_EXACT` (src/hybrid/engine.rs:3435-3461, 3532-3563): when on, every projection
+ * runs the fp32 GEMV that decodes weights with the exact per-value formula, at any M. */
+int fq_set_exact(fq_device *dev, int on);
+/* Test-only host-side fault injection, the counterpart of `fail_after` / `fail_completion`
+ * (src/metal/mod.rs:368-371, 617-620, 846-853): the n-th enqueue from now fails with
+ * FQ_ERR_SYNC before anything is launched (n < 0 disarms); `fq_test_fail_completion` makes the
+ * next `fq_synchronize` report a failure.  No GPU fault is produced. */
+int fq_test_fail_after(fq_device *dev, int n);
+int fq_test_fail_completion(fq_device *dev);
+
+/* ---- caller-visible device buffers (src/metal/mod.rs:700-760 `buffer`, Tensor::from_f32) --- */
+int fq_buffer_alloc(fq_device *dev, size_t bytes, void **device_ptr);
+int fq_buffer_free(fq_device *dev, void *device_ptr);
+int fq_upload(fq_device *dev, void *device_ptr, const void *host, size_t bytes);
+int fq_download(fq_device *dev, void *host, const void *device_ptr, size_t bytes);
+
+/* ---- weights ----------------------------------------------------------------------------- */
+
+/* `Matrix::from_packed` / `gguf_matrix` (src/hybrid/weights.rs:671-736, 1301-1330) with the
+ * payload checks of `validate_gguf_quantized_payload` (src/quantization.rs:212-261).
+ * `packed` is HOST memory holding `experts` stacked slices of `rows` rows, each row
+ * cols/block_elements GGUF blocks; `len` must equal the geometry.  `cols` must be a whole number
+ * of blocks and a multiple of 64 (`PROJECTION_K_STEP`). */
+int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint64_t cols, uint64_t experts,
+                     const void *packed, size_t len, fq_matrix **out);
+int fq_matrix_destroy(fq_matrix *w);
+int fq_matrix_get_info(const fq_matrix *w, fq_matrix_info *out);
+
+/* ---- the op surface ------------------------------------------------------------------------ */
+
+/* `HybridModel::project(d, w, x, m, y)` (src/hybrid/engine.rs:3407-3500):
+ * y[m][rows] = x[m][cols] . W^T.  x_elems must be m*cols and y_elems m*rows (else FQ_ERR_SHAPE).
+ * F32 in / F32 out is the hybrid engine's contract; BF16 in / BF16 out (fp32 accumulate, RNE
+ * store) is the legacy `project_quantized` tensor path (src/ops/transformer.rs:96-297). */
+int fq_project(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems,
+               size_t m, void *y, int y_dtype, size_t y_elems);
+
+/* `HybridModel::project_id(d, w, x, ids, routes, x_div, y)` (src/hybrid/engine.rs:3114-3147):
+ * route r multiplies activation row r / x_div by the rows of expert ids[r]; F32 in and out. */
+int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x, size_t x_elems,
+                  const uint32_t *ids, size_t routes, size_t x_div, float *y, size_t y_elems);
+
+/* `HybridModel::project_mm_id_in(d, w, x, offsets, slots, max_rows, y)`
+ * (src/hybrid/engine.rs:3164-3224): rows offsets[z]..offsets[z+1] of x and y belong to group z,
+ * which uses the expert stored at slots[z] (slots == NULL: expert z).  `groups` is the number of
+ * groups (w.experts without a slot table); `max_rows` bounds any group's row count. */
+int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems,
+                     const uint32_t *offsets, const uint32_t *slots, size_t groups, size_t max_rows,
+                     void *y, int y_dtype, size_t y_elems);
+
+/* `HybridModel::get_rows(d, w, ids, y)` (src/hybrid/engine.rs:3274-3300): y[t][:] = the exact
+ * fp32 decode of row ids[t] (BF16 output = that value rounded, the legacy
+ * `embedding_gather_quantized`, src/ops/transformer.rs:299). */
+int fq_get_rows(fq_device *dev, const fq_matrix *w, const uint32_t *ids, size_t tokens, void *y,
+                int y_dtype, size_t y_elems);
+
+/* `h_moe_route` via `moe_ffn` (src/hybrid/engine.rs:2907-2924; hybrid.metal:2252-2319). */
+int fq_moe_route(fq_device *dev, const float *logits, const float *x, const float *shared_w,
+                 uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens, int sigmoid,
+                 int norm, int shared_gate, uint32_t *ids, float *weights, float *gate);
+/* `h_moe_map` (src/hybrid/engine.rs:3043-3051; hybrid.metal:2321-2358). */
+int fq_moe_map(fq_device *dev, const uint32_t *ids, uint32_t experts, uint32_t routes,
+               uint32_t *offsets, uint32_t *sorted, uint32_t *position);
+/* `h_moe_gather` (src/hybrid/engine.rs:3052-3060; hybrid.metal:2360-2369). */
+int fq_moe_gather(fq_device *dev, const float *x, const uint32_t *sorted, uint32_t hidden,
+                  uint32_t used, uint32_t routes, float *xg);
+/* `h_moe_combine` (src/hybrid/engine.rs:3068-3091; hybrid.metal:2371-2388). */
+int fq_moe_combine(fq_device *dev, const float *down, const float *weights, const uint32_t *position,
+                   const float *shared, const float *gate, uint32_t hidden, uint32_t used,
+                   uint32_t tokens, int identity, float *out);
+/* `HybridModel::glu` with SiLU = `h_swiglu` (src/hybrid/engine.rs:3094-3110; hybrid.metal:1606). */
+int fq_glu(fq_device *dev, const float *gate, const float *up, size_t n, float *out);
+
+/* `HybridModel::dense_ffn` (src/hybrid/engine.rs:3226-3243): out = down(silu(gate x) * up x).
+ * `scratch` holds 3 * m * gate.rows floats (the reference's ffn_gate / ffn_up / ffn_act). */
+int fq_dense_ffn(fq_device *dev, const fq_matrix *gate, const fq_matrix *up, const fq_matrix *down,
+                 const float *x, size_t m, float *scratch, size_t scratch_elems, float *out);
+
+/* Geometry and weights of one MoE FFN (`MoeFfn`, src/hybrid/engine.rs:2881-2906). */
+typedef struct fq_moe_ffn_desc {
+    const fq_matrix *router;      /* [experts, hidden] */
+    const fq_matrix *gate_exps;   /* experts x [expert_ffn, hidden] */
+    const fq_matrix *up_exps;     /* experts x [expert_ffn, hidden] */
+    const fq_matrix *down_exps;   /* experts x [hidden, expert_ffn] */
+    const fq_matrix *shared_gate; /* shared expert, [shared_ffn, hidden] */
+    const fq_matrix *shared_up;
+    const fq_matrix *shared_down; /* [hidden, shared_ffn] */
+    const float *shared_gate_inp; /* [hidden] or NULL */
+    uint32_t experts, used, hidden, expert_ffn, shared_ffn;
+    int32_t sigmoid, norm_weights;
+} fq_moe_ffn_desc;
+
+/* Floats of scratch `fq_moe_ffn` needs for m tokens. */
+size_t fq_moe_ffn_scratch_elems(const fq_moe_ffn_desc *f, size_t m);
+/* `HybridModel::moe_ffn` (src/hybrid/engine.rs:2881-3092): router projection, routing, shared
+ * expert, per-route expert GEMVs when m*used <= 32 (`MV_ID_MAX_ROUTES`) or the handle is exact,
+ * else map + gather + grouped expert GEMMs, then combine. */
+int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float *x, size_t m, float *scratch,
+               size_t scratch_elems, float *out);
+
+/* ---- host-buffer entry points (what a caller without device pointers uses) ----------------- */
+
+/* `project` for HOST x / y: copies x to the device, runs `fq_project` (F32), copies y back and
+ * waits.  The staging buffers are the handle's fixed scratch (m * (cols + rows) floats must fit
+ * `FQ_HOST_STAGING_BYTES`). */
+#define FQ_HOST_STAGING_BYTES (64u << 20)
+int fq_project_host(fq_device *dev, const fq_matrix *w, const float *x_host, size_t m, float *y_host);
+/* The same for several matrices that share x (q|k|v, gate|up): one upload, `count` projections,
+ * one wait.  y_host[i] receives m * rows_i floats. */
+int fq_project_many_host(fq_device *dev, const fq_matrix *const *w, size_t count, const float *x_host,
+                         size_t m, float *const *y_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FERRUM_B200_H */
