@@ -142,56 +142,87 @@ def run_ours(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    dev = S.Device(local)
-    m = args.m
-    layers = args.layers
+    # The library enqueues on its own stream; torch sees that stream as an ExternalStream so that
+    # CUDA events are recorded on the stream the kernels are launched on.
+    dev = S.Device(local, use_torch_stream=False)
+    stream = torch.cuda.ExternalStream(dev.stream_ptr(), device=torch.device("cuda", local))
+    m, layers = args.m, args.layers
 
-    # Weights: layer l, matrix i uses seed 7 * l + i (+ rank shard); blocks as BASELINE config 0/1.
+    # Weights: layer l, matrix i uses seed (7 l + i) * 64 + rank; blocks as BASELINE config 0/1.
     mats = []
     for l in range(layers):
         layer = {}
         for i, (name, rows, cols, fmt) in enumerate(LAYER):
             _, per = shard_rows(rows, rank, world)
-            packed = random_matrix(fmt, per, cols, seed=(7 * l + i) * 64 + rank)
-            layer[name] = S.Matrix.from_packed(dev, per, cols, 1, fmt, packed)
+            layer[name] = S.Matrix.from_packed(dev, per, cols, 1, fmt, random_matrix(fmt, per, cols, seed=(7 * l + i) * 64 + rank))
         mats.append(layer)
-    shapes = {name: (rows, cols) for name, rows, cols, _ in LAYER}
-    rng = np.random.default_rng(1234)
-    x_host = {g[0]: rng.standard_normal((m, shapes[g[0]][1])).astype(np.float32) for g in GROUPS}
-    x_dev = {k: torch.from_numpy(v).cuda() for k, v in x_host.items()}
-    y_dev = {name: torch.zeros(m * shapes[name][0] // world, dtype=torch.float32, device="cuda") for name in shapes}
-    gathered = {name: torch.zeros(world * m * shapes[name][0] // world, dtype=torch.float32, device="cuda")
-                for name in shapes} if world > 1 else None
+    shapes = {name: (rows // world, cols) for name, rows, cols, _ in LAYER}
 
-    def step():
+    def buffers(mm):
+        """One contiguous input buffer (a slice per group) and one output buffer (a slice per matrix)."""
+        xs, ys, xo, yo = {}, {}, 0, 0
+        for g in GROUPS:
+            xs[g[0]] = (xo, mm * shapes[g[0]][1])
+            xo += (mm * shapes[g[0]][1] + 63) // 64 * 64
+        for name in shapes:
+            ys[name] = (yo, mm * shapes[name][0])
+            yo += (mm * shapes[name][0] + 63) // 64 * 64
+        X = torch.zeros(xo, dtype=torch.float32, device="cuda")
+        Y = torch.zeros(yo, dtype=torch.float32, device="cuda")
+        return X, Y, {k: X[o:o + n] for k, (o, n) in xs.items()}, {k: Y[o:o + n] for k, (o, n) in ys.items()}
+
+    rng = np.random.default_rng(1234)
+    X, Y, x_dev, y_dev = buffers(m)
+    x_pinned = torch.from_numpy(rng.standard_normal(X.numel()).astype(np.float32)).pin_memory()
+    y_pinned = torch.zeros(Y.numel(), dtype=torch.float32).pin_memory()
+    X.copy_(x_pinned)
+    gathered = ({name: torch.zeros(world * y_dev[name].numel(), dtype=torch.float32, device="cuda") for name in shapes}
+                if world > 1 else None)
+    torch.cuda.synchronize()
+
+    def enqueue_layers(xd, yd, mm, only=None):
         for layer in mats:
             for group in GROUPS:
-                x = x_dev[group[0]]
-                for name in group:
-                    S.project(dev, layer[name], x, m, y_dev[name])
+                names = [n for n in group if only is None or n in only]
+                if names and not args.no_fuse:
+                    S.project_many(dev, [layer[n] for n in names], xd[group[0]], mm, [yd[n] for n in names])
+                else:
+                    for n in names:
+                        S.project(dev, layer[n], xd[group[0]], mm, yd[n])
                 if world > 1:
-                    for name in group:
-                        dist.all_gather_into_tensor(gathered[name], y_dev[name])
+                    for n in names:
+                        dist.all_gather_into_tensor(gathered[n], yd[n])
+
+    def make_step(xd, yd, mm, only=None):
+        if world > 1 or args.eager:  # NCCL collectives are enqueued by torch: no capture, same stream
+            return lambda: enqueue_layers(xd, yd, mm, only)
+        dev.capture_begin()
+        enqueue_layers(xd, yd, mm, only)
+        graph = dev.capture_end()
+        return graph.launch
 
     def timed(fn, steps):
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+        with torch.cuda.stream(stream):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
         return ms
 
-    for _ in range(max(args.warmup, 3)):
-        step()
+    with torch.cuda.stream(stream):
+        step = make_step(x_dev, y_dev, m)
+        for _ in range(max(args.warmup, 3)):
+            step()
     c0 = dev.counters().dispatches
     with ClockSampler(local) as clocks:
         ms = timed(step, args.steps)
@@ -209,63 +240,72 @@ def run_ours(args):
         "config": {"workload": f"cfg1 dense 27B decode projection set (q,k,v,o,gate,up Q4_K; down Q6_K), M={m}, "
                                f"{layers} distinct layers = {total_bytes} packed bytes per step (inputs larger than L2)",
                    "m": m, "layers": layers, "parallelism": f"tp{world}" if world > 1 else "single",
+                   "submission": "one captured graph per step" if world == 1 else "eager + NCCL all-gather per projection",
                    "l2": "inputs larger than L2"},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
     }
 
     if rank == 0 and world == 1:
-        # Dominant kernel: the Q4_K GEMV on gate/up (50,135,040 packed bytes per launch), timed alone
-        # over `layers` distinct matrices with CUDA events on the launching stream.
-        def gate_only():
-            for layer in mats:
-                S.project(dev, layer["gate"], x_dev["gate"], m, y_dev["gate"])
-        for _ in range(3):
-            gate_only()
-        c0 = dev.counters().dispatches
-        gms = timed(gate_only, args.steps) / (args.steps * layers)
-        gate_bytes = 17408 * 5120 // 256 * 144
-        achieved = gate_bytes / (gms * 1e-3) / 1e9
-        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv_q4k (gate 17408x5120)", "achieved": round(achieved, 1),
-                           "peak": P["hbm_gbs"], "peak_source": P["source"], "unit": "GB/s",
+        def alone(names, mm, xd, yd):
+            with torch.cuda.stream(stream):
+                fn = make_step(xd, yd, mm, only=names)
+                for _ in range(3):
+                    fn()
+            reps = max(5, args.steps)
+            return timed(fn, reps) / reps / layers  # ms per layer's worth of these projections
+
+        # Dominant kernel: the Q4_K GEMV on gate|up (one launch over 2 x 17408 rows, 100,270,080
+        # packed bytes), timed alone over `layers` distinct layers with CUDA events on its stream.
+        gms = alone(("gate", "up"), m, x_dev, y_dev)
+        pair_bytes = 2 * 17408 * 5120 // 256 * 144
+        achieved = pair_bytes / (gms * 1e-3) / 1e9
+        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv<Q4_K> (gate|up, 2 x 17408 x 5120, one launch)",
+                           "achieved": round(achieved, 1), "peak": P["hbm_gbs"], "peak_source": P["source"], "unit": "GB/s",
                            "frac": round(achieved / P["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
                            "traffic": None, "us_per_launch": round(gms * 1e3, 2)}
-        # The other decode widths, same workload.
+        per = {}
+        for names in (("q", "k", "v"), ("o",), ("gate", "up"), ("down",)):
+            t = alone(names, m, x_dev, y_dev)
+            nbytes = sum(r * c // BLOCK[f][0] * BLOCK[f][1] for n, r, c, f in LAYER if n in names)
+            per["|".join(names)] = {"us": round(t * 1e3, 2), "gbs": round(nbytes / (t * 1e-3) / 1e9, 1)}
+        out["per_group"] = per
+        if args.quick:
+            print(json.dumps({"value": out["value"], "ms_per_step": out["ms_per_step"], "roofline_gbs": out["roofline"]["achieved"],
+                              "per_group": per}), flush=True)
+            return
+        # The other decode / verify widths, same workload.
         extra = {}
-        for mm in (8, 16):
-            xs = {k: torch.from_numpy(rng.standard_normal((mm, shapes[k][1])).astype(np.float32)).cuda() for k in x_dev}
-            ys = {name: torch.zeros(mm * shapes[name][0], dtype=torch.float32, device="cuda") for name in shapes}
-
-            def step_m():
-                for layer in mats:
-                    for group in GROUPS:
-                        for name in group:
-                            S.project(dev, layer[name], xs[group[0]], mm, ys[name])
-            for _ in range(2):
-                step_m()
-            t = timed(step_m, max(2, args.steps // 2)) / max(2, args.steps // 2)
+        for mm in (4, 8, 16):
+            Xm, Ym, xs, ys = buffers(mm)
+            Xm.copy_(torch.from_numpy(rng.standard_normal(Xm.numel()).astype(np.float32)))
+            with torch.cuda.stream(stream):
+                fn = make_step(xs, ys, mm)
+                for _ in range(3):
+                    fn()
+            reps = max(3, args.steps // 2)
+            t = timed(fn, reps) / reps
             extra[f"m{mm}_gbs"] = round(total_bytes / (t * 1e-3) / 1e9, 1)
         out["decode_widths"] = extra
 
-        # End to end through the host-buffer C-ABI calls: pinned-staged H2D of x, D2H of y, every step.
-        y_host = {name: np.zeros((m, shapes[name][0]), dtype=np.float32) for name in shapes}
+        # End to end through the C ABI with HOST buffers: every step uploads the step's activations
+        # from pinned memory, replays the step, downloads every output and waits.
+        xh, yh = x_pinned.numpy(), y_pinned.numpy()
 
         def step_host():
-            for layer in mats:
-                for group in GROUPS:
-                    S.project_many_host(dev, [layer[n] for n in group], x_host[group[0]], m, [y_host[n] for n in group])
+            dev.upload(X, xh)
+            step()
+            dev.download_async(yh, Y)
+            dev.synchronize()
         for _ in range(3):
             step_host()
-        torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(args.steps):
             step_host()
-        torch.cuda.synchronize()
         dt = (time.perf_counter() - t0) / args.steps
-        h2d = layers * sum(m * shapes[g[0]][1] * 4 for g in GROUPS)
-        d2h = layers * sum(m * shapes[n][0] * 4 for n in shapes)
-        out["e2e"] = {"value": round(total_bytes / dt / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                      "d2h_bytes_per_step": d2h, "ms_per_step": round(dt * 1e3, 4)}
+        out["e2e"] = {"value": round(total_bytes / dt / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": int(xh.nbytes),
+                      "d2h_bytes_per_step": int(yh.nbytes), "ms_per_step": round(dt * 1e3, 4),
+                      "call": "fq_upload + fq_graph_launch + fq_download_async + fq_synchronize"}
 
         # CPU baseline: the oracle port on all host cores, one layer at M = 1 (a bounded sample).
         out["cpu_baseline"] = cpu_baseline(m=m, budget_s=12.0)
@@ -352,6 +392,9 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--m", type=int, default=1, help="activation rows (1 = decode)")
     ap.add_argument("--layers", type=int, default=3, help="distinct layers streamed per step")
+    ap.add_argument("--eager", action="store_true", help="enqueue every step call by call instead of replaying a graph")
+    ap.add_argument("--no-fuse", action="store_true", help="one launch per matrix instead of one per input group")
+    ap.add_argument("--quick", action="store_true", help="headline and per-group timings only")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -51,14 +51,20 @@ SIGNATURES = {
     "fq_set_exact": (_I, [_P, _I]),
     "fq_test_fail_after": (_I, [_P, _I]),
     "fq_test_fail_completion": (_I, [_P]),
+    "fq_capture_begin": (_I, [_P]),
+    "fq_capture_end": (_I, [_P, C.POINTER(_P)]),
+    "fq_graph_launch": (_I, [_P, _P]),
+    "fq_graph_destroy": (_I, [_P]),
     "fq_buffer_alloc": (_I, [_P, _Z, C.POINTER(_P)]),
     "fq_buffer_free": (_I, [_P, _P]),
     "fq_upload": (_I, [_P, _P, _P, _Z]),
     "fq_download": (_I, [_P, _P, _P, _Z]),
+    "fq_download_async": (_I, [_P, _P, _P, _Z]),
     "fq_matrix_create": (_I, [_P, _I, _U64, _U64, _U64, _P, _Z, C.POINTER(_P)]),
     "fq_matrix_destroy": (_I, [_P]),
     "fq_matrix_get_info": (_I, [_P, C.POINTER(MatrixInfo)]),
     "fq_project": (_I, [_P, _P, _P, _I, _Z, _Z, _P, _I, _Z]),
+    "fq_project_many": (_I, [_P, C.POINTER(_P), _Z, _P, _I, _Z, _Z, C.POINTER(_P), _I]),
     "fq_project_id": (_I, [_P, _P, _P, _Z, _P, _Z, _Z, _P, _Z]),
     "fq_project_mm_id": (_I, [_P, _P, _P, _I, _Z, _P, _P, _Z, _Z, _P, _I, _Z]),
     "fq_get_rows": (_I, [_P, _P, _P, _Z, _P, _I, _Z]),

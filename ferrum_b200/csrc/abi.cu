@@ -2,9 +2,11 @@
 // the quantized-linear op surface (the counterpart of src/hybrid/engine.rs:3407-3500 and of the
 // checks in src/metal/mod.rs:838-897).
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
+#include "blocks.cuh"
 #include "internal.h"
 
 // ------------------------------------------------------------------ errors
@@ -67,7 +69,8 @@ int fq_end_enqueue(fq_device *dev, const char *what, int kernels) {
         cudaGetLastError();
         return fq_fail(dev, FQ_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
     }
-    dev->counters.dispatches += (uint64_t)kernels;
+    if (dev->capturing) dev->captured_kernels += (uint64_t)kernels;
+    else dev->counters.dispatches += (uint64_t)kernels;
     return FQ_OK;
 }
 
@@ -151,6 +154,7 @@ extern "C" void *fq_device_stream(fq_device *dev) { return dev ? (void *)dev->st
 
 extern "C" int fq_synchronize(fq_device *dev) {
     if (!dev) return FQ_ERR_PARAM;
+    if (dev->capturing) return fq_fail(dev, FQ_ERR_PARAM, "fq_synchronize inside a capture");
     cudaSetDevice(dev->ordinal);
     dev->counters.synchronizes++;
     cudaError_t e = cudaStreamSynchronize(dev->stream);
@@ -201,6 +205,63 @@ extern "C" int fq_test_fail_completion(fq_device *dev) {
     return FQ_OK;
 }
 
+// ------------------------------------------------------------------ batched submission
+
+extern "C" int fq_capture_begin(fq_device *dev) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (dev->capturing) return fq_fail(dev, FQ_ERR_PARAM, "a capture is already open");
+    if (dev->stream != dev->own_stream) return fq_fail(dev, FQ_ERR_PARAM, "capture runs on the handle's own stream; restore it first");
+    if (int rc = fq_check_cuda(dev, cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) return rc;
+    dev->capturing = true;
+    dev->captured_kernels = 0;
+    return FQ_OK;
+}
+
+extern "C" int fq_capture_end(fq_device *dev, fq_graph **out) {
+    if (!dev || !out) return FQ_ERR_PARAM;
+    *out = nullptr;
+    if (!dev->capturing) return fq_fail(dev, FQ_ERR_PARAM, "no capture is open");
+    dev->capturing = false;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
+    if (e != cudaSuccess || !graph) {
+        cudaGetLastError();
+        return fq_fail(dev, FQ_ERR_CUDA, "end capture: %s", cudaGetErrorString(e));
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(graph);
+        return fq_check_cuda(dev, e, "graph instantiate");
+    }
+    fq_graph *g = new fq_graph();
+    g->dev = dev;
+    g->graph = graph;
+    g->exec = exec;
+    g->kernels = dev->captured_kernels;
+    *out = g;
+    return FQ_OK;
+}
+
+extern "C" int fq_graph_launch(fq_device *dev, fq_graph *graph) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!graph || graph->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "graph belongs to another device handle");
+    if (dev->capturing) return fq_fail(dev, FQ_ERR_PARAM, "graph launch inside a capture");
+    if (int rc = fq_check_cuda(dev, cudaGraphLaunch(graph->exec, dev->stream), "graph launch")) return rc;
+    dev->counters.dispatches += graph->kernels;
+    return FQ_OK;
+}
+
+extern "C" int fq_graph_destroy(fq_graph *graph) {
+    if (!graph) return FQ_ERR_PARAM;
+    cudaSetDevice(graph->dev->ordinal);
+    cudaStreamSynchronize(graph->dev->stream);
+    if (graph->exec) cudaGraphExecDestroy(graph->exec);
+    if (graph->graph) cudaGraphDestroy(graph->graph);
+    delete graph;
+    return FQ_OK;
+}
+
 // ------------------------------------------------------------------ buffers
 
 extern "C" int fq_buffer_alloc(fq_device *dev, size_t bytes, void **device_ptr) {
@@ -231,12 +292,16 @@ extern "C" int fq_upload(fq_device *dev, void *device_ptr, const void *host, siz
     return fq_check_cuda(dev, cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, dev->stream), "upload");
 }
 
-extern "C" int fq_download(fq_device *dev, void *host, const void *device_ptr, size_t bytes) {
+extern "C" int fq_download_async(fq_device *dev, void *host, const void *device_ptr, size_t bytes) {
     if (!dev || !host) return fq_fail(dev, FQ_ERR_PARAM, "download arguments");
     if (int rc = fq_begin_enqueue(dev)) return rc;
     if (int rc = fq_check_binding(dev, device_ptr, bytes, "download source")) return rc;
     dev->counters.bytes_downloaded += bytes;
-    if (int rc = fq_check_cuda(dev, cudaMemcpyAsync(host, device_ptr, bytes, cudaMemcpyDeviceToHost, dev->stream), "download")) return rc;
+    return fq_check_cuda(dev, cudaMemcpyAsync(host, device_ptr, bytes, cudaMemcpyDeviceToHost, dev->stream), "download");
+}
+
+extern "C" int fq_download(fq_device *dev, void *host, const void *device_ptr, size_t bytes) {
+    if (int rc = fq_download_async(dev, host, device_ptr, bytes)) return rc;
     // A read of results is a completion point, as `Tensor::to_f32` is in the reference.
     return fq_synchronize(dev);
 }
@@ -305,10 +370,30 @@ extern "C" int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint6
     w->byte_size = len;
     w->block_elems = el;
     w->block_bytes = bb;
+    w->pitch = fq_row_pitch(format, (uint32_t)cols);
+    const size_t dev_len = (size_t)w->pitch * w->rows;
+    // Q6_K is regrouped by field on the host (see blocks.cuh); the other formats upload as they are.
+    std::vector<uint8_t> regrouped;
+    const uint8_t *upload = (const uint8_t *)packed;
+    if (format == FQ_Q6_K) {
+        regrouped.assign(dev_len, 0);
+        const size_t nb = cols / 256;
+        for (size_t r = 0; r < w->rows; r++) {
+            const uint8_t *src = (const uint8_t *)packed + r * row_bytes;
+            uint8_t *dst = regrouped.data() + r * w->pitch;
+            for (size_t b = 0; b < nb; b++, src += 210) {
+                memcpy(dst + 128 * b, src, 128);
+                memcpy(dst + 128 * nb + 64 * b, src + 128, 64);
+                memcpy(dst + 192 * nb + 16 * b, src + 192, 16);
+                memcpy(dst + 208 * nb + 2 * b, src + 208, 2);
+            }
+        }
+        upload = regrouped.data();
+    }
     // 256 spare bytes let kernels read whole 16-byte words around the last block.
-    cudaError_t e = cudaMalloc((void **)&w->data, len + 256);
-    if (e == cudaSuccess) e = cudaMemsetAsync(w->data + len, 0, 256, dev->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(w->data, packed, len, cudaMemcpyHostToDevice, dev->stream);
+    cudaError_t e = cudaMalloc((void **)&w->data, dev_len + 256);
+    if (e == cudaSuccess) e = cudaMemsetAsync(w->data + dev_len, 0, 256, dev->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w->data, upload, dev_len, cudaMemcpyHostToDevice, dev->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
     if (e != cudaSuccess) {
         if (w->data) cudaFree(w->data);
@@ -348,7 +433,7 @@ static ProjectArgs base_args(const fq_matrix *w, const void *x, int xd, void *y,
     a.format = (uint32_t)w->format;
     a.rows = (uint32_t)w->expert_rows();
     a.cols = (uint32_t)w->cols;
-    a.row_bytes = (uint32_t)w->row_bytes;
+    a.row_bytes = (uint32_t)w->pitch;
     a.x = x;
     a.y = y;
     a.x_dtype = xd;
@@ -359,6 +444,17 @@ static ProjectArgs base_args(const fq_matrix *w, const void *x, int xd, void *y,
 
 static int check_dtype(fq_device *dev, int dt) {
     return (dt == FQ_F32 || dt == FQ_BF16) ? FQ_OK : fq_fail(dev, FQ_ERR_UNSUPPORTED, "element type %d", dt);
+}
+
+// Decode / verify widths: the integer kernel up to 4 activation rows (and per-route expert
+// projections), the f16 tensor-core kernel up to FQ_GEMV_MAX_M.  FQ_GEMV=f16 forces the latter.
+static int launch_decode(fq_device *dev, const ProjectArgs *a, uint32_t count) {
+    static const bool f16_only = [] { const char *e = getenv("FQ_GEMV"); return e && e[0] == 'f'; }();
+    if (!f16_only) {
+        int rc = fq_launch_gemv_i8_many(dev, a, count);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
+    return fq_launch_gemv_fast_many(dev, a, count);
 }
 
 extern "C" int fq_project(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems, size_t m,
@@ -381,12 +477,45 @@ extern "C" int fq_project(fq_device *dev, const fq_matrix *w, const void *x, int
     a.m = (uint32_t)m;
     if (!dev->exact) {
         int rc = FQ_ERR_UNSUPPORTED;
-        if (m <= (size_t)FQ_GEMV_MAX_M && x_dtype == FQ_F32 && y_dtype == FQ_F32) rc = fq_launch_gemv_fast(dev, a);
+        if (m <= (size_t)FQ_GEMV_MAX_M && x_dtype == FQ_F32 && y_dtype == FQ_F32) rc = launch_decode(dev, &a, 1);
         else if (x_dtype == FQ_BF16 && y_dtype == FQ_BF16) rc = fq_launch_gemm_tc(dev, a);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
     if (int rc = fq_launch_project_exact(dev, a)) return rc;
     return fq_end_enqueue(dev, "project", 1);
+}
+
+extern "C" int fq_project_many(fq_device *dev, const fq_matrix *const *w, size_t count, const void *x, int x_dtype,
+                               size_t x_elems, size_t m, void *const *y, int y_dtype) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!w || !y || count == 0) return fq_fail(dev, FQ_ERR_PARAM, "projection list");
+    if (int rc = check_dtype(dev, x_dtype)) return rc;
+    if (int rc = check_dtype(dev, y_dtype)) return rc;
+    constexpr size_t MAX = 8;
+    if (count > MAX) return fq_fail(dev, FQ_ERR_PARAM, "at most %zu projections share an input", MAX);
+    ProjectArgs args[MAX];
+    for (size_t i = 0; i < count; i++) {
+        if (!w[i]) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
+        if (w[i]->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "matrix belongs to another device handle");
+        if (m == 0 || x_elems != m * w[i]->cols)
+            return fq_fail(dev, FQ_ERR_SHAPE, "projection [%zu, %llu] from %zu values", m, (unsigned long long)w[i]->cols, x_elems);
+        const size_t xb = x_elems * fq_dtype_size(x_dtype), yb = m * w[i]->rows * fq_dtype_size(y_dtype);
+        if (int rc = fq_check_binding(dev, x, xb, "x")) return rc;
+        if (int rc = fq_check_binding(dev, y[i], yb, "y")) return rc;
+        if (int rc = fq_check_no_alias(dev, y[i], yb, x, xb, "y")) return rc;
+        for (size_t j = 0; j < i; j++)
+            if (int rc = fq_check_no_alias(dev, y[i], yb, y[j], m * w[j]->rows * fq_dtype_size(y_dtype), "y")) return rc;
+        args[i] = base_args(w[i], x, x_dtype, y[i], y_dtype);
+        args[i].rows = (uint32_t)w[i]->rows;
+        args[i].m = (uint32_t)m;
+    }
+    if (!dev->exact && count <= 4) {
+        int rc = launch_decode(dev, args, (uint32_t)count);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
+    for (size_t i = 0; i < count; i++)
+        if (int rc = fq_project(dev, w[i], x, x_dtype, x_elems, m, y[i], y_dtype, m * w[i]->rows)) return rc;
+    return FQ_OK;
 }
 
 extern "C" int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x, size_t x_elems, const uint32_t *ids,
@@ -407,7 +536,7 @@ extern "C" int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x,
     a.ids = ids;
     a.x_div = (uint32_t)x_div;
     if (!dev->exact) {
-        int rc = fq_launch_gemv_fast(dev, a);
+        int rc = launch_decode(dev, &a, 1);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
     if (int rc = fq_launch_project_id_exact(dev, a)) return rc;
@@ -466,8 +595,9 @@ extern "C" int fq_dense_ffn(fq_device *dev, const fq_matrix *gate, const fq_matr
         return fq_fail(dev, FQ_ERR_SHAPE, "feed-forward matrices do not chain");
     if (scratch_elems < 3 * m * width) return fq_fail(dev, FQ_ERR_SHAPE, "feed-forward scratch holds %zu of %zu floats", scratch_elems, 3 * m * width);
     float *g = scratch, *u = scratch + m * width, *act = scratch + 2 * m * width;
-    if (int rc = fq_project(dev, gate, x, FQ_F32, m * gate->cols, m, g, FQ_F32, m * width)) return rc;
-    if (int rc = fq_project(dev, up, x, FQ_F32, m * up->cols, m, u, FQ_F32, m * width)) return rc;
+    const fq_matrix *pair[2] = {gate, up};
+    void *outs[2] = {g, u};
+    if (int rc = fq_project_many(dev, pair, 2, x, FQ_F32, m * gate->cols, m, outs, FQ_F32)) return rc;
     if (int rc = fq_glu(dev, g, u, m * width, act)) return rc;
     return fq_project(dev, down, act, FQ_F32, m * width, m, out, FQ_F32, m * down->rows);
 }
@@ -570,11 +700,17 @@ extern "C" int fq_project_many_host(fq_device *dev, const fq_matrix *const *w, s
     dev->counters.bytes_uploaded += m * cols * 4;
     size_t at = align4(m * cols);
     std::vector<size_t> where(count);
+    std::vector<void *> outs(count);
     for (size_t i = 0; i < count; i++) {
-        float *yd = (float *)dev->staging_dev + at;
+        outs[i] = (float *)dev->staging_dev + at;
         where[i] = at;
-        if (int rc = fq_project(dev, w[i], xd, FQ_F32, m * cols, m, yd, FQ_F32, m * w[i]->rows)) return rc;
         at += align4(m * w[i]->rows);
+    }
+    if (count <= 8) {
+        if (int rc = fq_project_many(dev, w, count, xd, FQ_F32, m * cols, m, outs.data(), FQ_F32)) return rc;
+    } else {
+        for (size_t i = 0; i < count; i++)
+            if (int rc = fq_project(dev, w[i], xd, FQ_F32, m * cols, m, outs[i], FQ_F32, m * w[i]->rows)) return rc;
     }
     const size_t first = align4(m * cols);
     if (int rc = fq_check_cuda(dev, cudaMemcpyAsync((float *)dev->staging_host + first, (float *)dev->staging_dev + first,

@@ -50,29 +50,46 @@ __device__ __forceinline__ float q6k_value(float d, int scale, uint32_t q) {
     return __fmul_rn(__fmul_rn(d, (float)scale), (float)q - 32.0f);
 }
 
-// Value `idx` (0 .. EL-1, in the format's logical order) of one block.
-template <int FMT> __device__ __forceinline__ float decode_value(const uint8_t *b, int idx);
+// Device layouts.  Q4_K and Q8_0 rows are the GGUF bytes.  Q6_K rows are the same bytes regrouped
+// by field at load time so that every field is 16-byte aligned (210-byte blocks are not): with
+// nb blocks in the row,
+//   ql of block b at 128 b, qh at 128 nb + 64 b, scales at 192 nb + 16 b, d at 208 nb + 2 b,
+// and the row pitch is 210 nb rounded up to 16 bytes.
+__host__ __device__ inline uint32_t fq_row_pitch(int format, uint32_t cols) {
+    switch (format) {
+    case FQ_Q4_K: return cols / 256 * 144;
+    case FQ_Q6_K: return (cols / 256 * 210 + 15u) & ~15u;
+    default: return cols / 32 * 34;
+    }
+}
 
-template <> __device__ __forceinline__ float decode_value<FQ_Q4_K>(const uint8_t *b, int idx) {
+// Value `idx` (0 .. EL-1, in the format's logical order) of block `b` of a row with `nb` blocks.
+template <int FMT> __device__ __forceinline__ float decode_at(const uint8_t *row, uint32_t nb, uint32_t b, int idx);
+
+template <> __device__ __forceinline__ float decode_at<FQ_Q4_K>(const uint8_t *row, uint32_t, uint32_t b, int idx) {
+    const uint8_t *blk = row + (size_t)b * 144;
     const int j = idx >> 5, l = idx & 31;
     uint32_t sc, mn;
-    q4k_scale_min(b + 4, j, sc, mn);
-    const uint8_t v = b[16 + 32 * (j >> 1) + l];
+    q4k_scale_min(blk + 4, j, sc, mn);
+    const uint8_t v = blk[16 + 32 * (j >> 1) + l];
     const uint32_t q = (j & 1) ? (v >> 4) : (v & 0xFu);
-    return q4k_value(load_f16(b), load_f16(b + 2), sc, mn, q);
+    return q4k_value(load_f16(blk), load_f16(blk + 2), sc, mn, q);
 }
 
-template <> __device__ __forceinline__ float decode_value<FQ_Q6_K>(const uint8_t *b, int idx) {
+template <> __device__ __forceinline__ float decode_at<FQ_Q6_K>(const uint8_t *row, uint32_t nb, uint32_t b, int idx) {
+    const uint8_t *ql = row + (size_t)b * 128, *qh = row + (size_t)nb * 128 + (size_t)b * 64;
+    const uint8_t *sc = row + (size_t)nb * 192 + (size_t)b * 16, *d = row + (size_t)nb * 208 + (size_t)b * 2;
     const int n = idx >> 7, r = idx & 127, i = r >> 5, l = r & 31;
-    const uint8_t lo = b[64 * n + l + 32 * (i & 1)];
+    const uint8_t lo = ql[64 * n + l + 32 * (i & 1)];
     const uint32_t nib = (i < 2) ? (lo & 0xFu) : (lo >> 4);
-    const uint32_t hi = (b[128 + 32 * n + l] >> (2 * i)) & 3u;
-    const int scale = (int)(int8_t)b[192 + 8 * n + (l >> 4) + 2 * i];
-    return q6k_value(load_f16(b + 208), scale, nib | (hi << 4));
+    const uint32_t hi = (qh[32 * n + l] >> (2 * i)) & 3u;
+    const int scale = (int)(int8_t)sc[8 * n + (l >> 4) + 2 * i];
+    return q6k_value(load_f16(d), scale, nib | (hi << 4));
 }
 
-template <> __device__ __forceinline__ float decode_value<FQ_Q8_0>(const uint8_t *b, int idx) {
-    return __fmul_rn((float)(int)(int8_t)b[2 + idx], load_f16(b));
+template <> __device__ __forceinline__ float decode_at<FQ_Q8_0>(const uint8_t *row, uint32_t, uint32_t b, int idx) {
+    const uint8_t *blk = row + (size_t)b * 34;
+    return __fmul_rn((float)(int)(int8_t)blk[2 + idx], load_f16(blk));
 }
 
 // Round to nearest even (src/hybrid/draft/gguf.rs:362-369).  cvt.rn.bf16.f32 agrees for every

@@ -14,16 +14,15 @@ constexpr int MT = 8;    // activation rows sharing one decode
 template <int FMT, typename XT>
 __device__ __forceinline__ void row_dot(const uint8_t *wrow, uint32_t cols, const XT *x, size_t x_stride,
                                         int tokens, int lane, float (&acc)[MT]) {
-    constexpr int EL = BlockTraits<FMT>::EL, BB = BlockTraits<FMT>::BB;
+    constexpr int EL = BlockTraits<FMT>::EL;
     const uint32_t blocks = cols / EL;
 #pragma unroll
     for (int t = 0; t < MT; t++) acc[t] = 0.f;
     for (uint32_t b = 0; b < blocks; b++) {
-        const uint8_t *blk = wrow + (size_t)b * BB;
 #pragma unroll
         for (int i = 0; i < EL / 32; i++) {
             const int idx = i * 32 + lane;
-            const float w = decode_value<FMT>(blk, idx);
+            const float w = decode_at<FMT>(wrow, blocks, b, idx);
             const size_t k = (size_t)b * EL + idx;
 #pragma unroll
             for (int t = 0; t < MT; t++)
@@ -97,13 +96,13 @@ template <int FMT, typename YT>
 __global__ void __launch_bounds__(256)
 k_get_rows(const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t row_bytes,
            const uint32_t *__restrict__ ids, YT *__restrict__ y) {
-    constexpr int EL = BlockTraits<FMT>::EL, BB = BlockTraits<FMT>::BB;
+    constexpr int EL = BlockTraits<FMT>::EL;
     const uint32_t c = blockIdx.y * 256 + threadIdx.x;
     const uint32_t t = blockIdx.x;
     if (c >= cols) return;
     const uint32_t r = ids[t];
     // An id beyond the matrix decodes nothing; the row is written as zeros.
-    const float v = r < rows ? decode_value<FMT>(w + (size_t)r * row_bytes + (size_t)(c / EL) * BB, c % EL) : 0.f;
+    const float v = r < rows ? decode_at<FMT>(w + (size_t)r * row_bytes, cols / EL, c / EL, c % EL) : 0.f;
     store_act<YT>(y + (size_t)t * cols + c, v);
 }
 
@@ -168,9 +167,9 @@ int fq_launch_get_rows(fq_device *dev, const fq_matrix *w, const uint32_t *ids, 
         dim3 grid(tokens, ((uint32_t)w->cols + 255) / 256);
         if (y_dtype == FQ_BF16)
             k_get_rows<decltype(fmt)::value, __nv_bfloat16><<<grid, 256, 0, dev->stream>>>(
-                w->data, (uint32_t)w->rows, (uint32_t)w->cols, (uint32_t)w->row_bytes, ids, (__nv_bfloat16 *)y);
+                w->data, (uint32_t)w->rows, (uint32_t)w->cols, (uint32_t)w->pitch, ids, (__nv_bfloat16 *)y);
         else
             k_get_rows<decltype(fmt)::value, float><<<grid, 256, 0, dev->stream>>>(
-                w->data, (uint32_t)w->rows, (uint32_t)w->cols, (uint32_t)w->row_bytes, ids, (float *)y);
+                w->data, (uint32_t)w->rows, (uint32_t)w->cols, (uint32_t)w->pitch, ids, (float *)y);
     });
 }

@@ -1,0 +1,497 @@
+// Decode projections for 1..4 activation rows on the integer tensor path (F32 in, F32 out).
+// The reference's `h_mv_q4_k` / `h_mv_q6_k` / `h_mvb_*` (src/metal/shaders/hybrid.metal:688-756,
+// 838-897, 1330-1394) and, with routes, `h_mv_id_*` (:2390-2428).
+//
+// A K-quant GEMV on B200 is bound by instruction issue, not by HBM, if every weight costs ALU work.
+// Here the packed quants never leave the integer domain:
+//
+//   A (16 weight rows x 32 k, u8)  = the raw quants: one AND per four Q4_K weights
+//                                    (w & 0x0F0F0F0F, (w >> 4) & 0x0F0F0F0F), one LOP3 select per
+//                                    four Q6_K weights (low nibbles | two high bits);
+//   B (32 k x 8 columns, s8)       = the activations of ONE row as 16-bit integers
+//                                    x' = round(x * s) = 256 * hi + lo, both halves signed bytes,
+//                                    s a power of two per (row, superblock).  The four threads of a
+//                                    quad own k of four different scale groups, so column c of B holds
+//                                    x' only on the k slots of thread c % 4 (plane c / 4) and zeros
+//                                    elsewhere: one mma.sync m16n8k32 yields, per weight row, the
+//                                    integer dot products of four scale groups times two planes;
+//   epilogue (integers)            = sum_groups scale_g * (dot_g [- 32 * sum x' for Q6_K]),
+//                                    Q4_K minus dmin * sum_j m_j * sum x'; one I2F and one FMA with
+//                                    d / s per row and superblock.
+//
+// The result is the exact dot product of the decoded weights with the activations rounded to 16 bits
+// relative to the largest magnitude of their superblock (error <= 2^-16 of that maximum per
+// activation; llama.cpp's CUDA GEMV, which the reference's kernels derive from, rounds to 8 bits per
+// 32).  Thread (g = lane / 4, t = lane % 4) owns weight rows g, g + 8 of a 16-row tile and the same
+// bytes of every superblock as in gemv.cu (Q4_K: chunk t; Q6_K: half t / 2, run t % 2), read with
+// 128-bit loads, the next superblock always in flight.  Four warps split K; partial sums meet in
+// shared memory in a fixed order, so results are deterministic and a row-sharded matrix gives the
+// same bits as the whole one.
+#include <cstdlib>
+#include <type_traits>
+
+#include "blocks.cuh"
+#include "internal.h"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int THREADS = WARPS * 32;
+constexpr int MAX_TARGETS = 4;
+constexpr int MAX_TOKENS = 4;
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------- prepared activations
+//
+// Per group (one activation row in expert mode, else all rows) and token:
+//   plane[2][cols] s8   hi and lo bytes of x' in natural k order
+//   sx32 [cols / 32] s32   sum of x' per 32 values            (Q4_K minimum term)
+//   sx16 [2][cols / 16] s16  sum of hi / lo bytes per 16 values (Q6_K "- 32" term)
+//   isc  [cols / 256] f32  1 / s
+struct PrepI8 {
+    uint32_t cols, nblk;
+    uint32_t lo_off, sx32_off, sx16_off, isc_off, token_bytes;
+};
+
+PrepI8 prep_i8_layout(uint32_t cols) {
+    PrepI8 L;
+    L.cols = cols;
+    L.nblk = cols / 256;
+    L.lo_off = cols;
+    L.sx32_off = 2 * cols;
+    L.sx16_off = L.sx32_off + cols / 32 * 4;
+    L.isc_off = L.sx16_off + 2 * (cols / 16) * 2;
+    L.token_bytes = (L.isc_off + L.nblk * 4 + 255u) & ~255u;
+    return L;
+}
+
+// One warp per (activation row, superblock); lane l owns the eight values at 256 b + 8 l.
+__global__ void __launch_bounds__(128)
+k_prep_i8(const float *__restrict__ x, uint32_t xrows, PrepI8 L, uint8_t *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const uint32_t xr = warp / L.nblk, b = warp % L.nblk;
+    if (xr >= xrows) return;
+    const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)xr * L.cols + (size_t)b * 256 + lane * 8);
+    const float4 v0 = src[0], v1 = src[1];
+    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float amax = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        amax = fmaxf(amax, fabsf(v[i]));
+        bad |= !(fabsf(v[i]) < INFINITY);
+    }
+    const bool finite = __ballot_sync(0xffffffffu, bad) == 0u; // no NaN or infinity in the superblock
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    // s = 2^e, the largest power of two with amax * s <= 32639 (so that hi = (x' + 128) >> 8 fits a
+    // signed byte); 1 when the block is all zero or not finite (the result is then not finite either).
+    int e = 0;
+    if (amax > 0.f && finite) {
+        int ex;
+        frexpf(amax, &ex);
+        e = 15 - ex;
+        if (ldexpf(amax, e) > 32639.f) e -= 1;
+        e = max(-110, min(110, e));
+    }
+    const float s = ldexpf(1.f, e);
+    uint8_t hi[8], lo[8];
+    int sum = 0, sum_hi = 0, sum_lo = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        int q = __float2int_rn(fminf(fmaxf(v[i] * s, -32639.f), 32639.f));
+        if (!finite) q = 0; // the block's factor below is NaN in that case
+        const int h = (q + 128) >> 8, l = q - (h << 8);
+        hi[i] = (uint8_t)h;
+        lo[i] = (uint8_t)l;
+        sum += q;
+        sum_hi += h;
+        sum_lo += l;
+    }
+    uint8_t *base = out + (size_t)xr * L.token_bytes;
+    auto pack8 = [](const uint8_t *p) {
+        uint2 r;
+        r.x = p[0] | (p[1] << 8) | (p[2] << 16) | ((uint32_t)p[3] << 24);
+        r.y = p[4] | (p[5] << 8) | (p[6] << 16) | ((uint32_t)p[7] << 24);
+        return r;
+    };
+    reinterpret_cast<uint2 *>(base)[b * 32 + lane] = pack8(hi);
+    reinterpret_cast<uint2 *>(base + L.lo_off)[b * 32 + lane] = pack8(lo);
+    // 16-value sums (lane pairs) and 32-value sums (lane quads).
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if ((lane & 1) == 0) {
+        int16_t *s16 = reinterpret_cast<int16_t *>(base + L.sx16_off);
+        s16[b * 16 + (lane >> 1)] = (int16_t)sum_hi;
+        s16[L.cols / 16 + b * 16 + (lane >> 1)] = (int16_t)sum_lo;
+    }
+    if ((lane & 3) == 0) reinterpret_cast<int *>(base + L.sx32_off)[b * 8 + (lane >> 2)] = sum;
+    if (lane == 0) {
+        // A non-finite activation anywhere in the block makes the block's factor NaN.
+        reinterpret_cast<float *>(base + L.isc_off)[b] = finite ? ldexpf(1.f, -e) : __int_as_float(0x7fc00000);
+    }
+}
+
+// ---------------------------------------------------------------- helpers
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Prepared activations: written by the kernel before this one (which may still run when this grid
+// starts), so ordinary coherent loads after `pdl_wait`; volatile so guarded loads are not speculated.
+__device__ __forceinline__ uint4 ldx128(const void *p) {
+    uint4 r;
+    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint32_t ldx32(const void *p) {
+    uint32_t r;
+    asm volatile("ld.global.ca.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+// Weights: immutable, read once -> read-only path, no L1 allocation.
+__device__ __forceinline__ uint4 ldw128(const void *p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint2 ldw64(const void *p) {
+    uint2 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint32_t ldw16(const void *p) {
+    uint16_t r;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(r) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint32_t lop3_select(uint32_t a, uint32_t b, uint32_t mask) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xE4;" : "=r"(r) : "r"(a), "r"(b), "r"(mask)); // (a & mask) | (b & ~mask)
+    return r;
+}
+__device__ __forceinline__ int byte_u(uint32_t w, int i) { return (int)((w >> (8 * i)) & 0xFFu); }
+__device__ __forceinline__ int byte_s(uint32_t w, int i) { return (int)(int8_t)((w >> (8 * i)) & 0xFFu); }
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+struct Q4Raw { // header and the 32 packed bytes of chunk t
+    uint4 hdr, qa, qb;
+    __device__ __forceinline__ void load(const uint8_t *row, uint32_t, uint32_t b, int t) {
+        const uint8_t *blk = row + (size_t)b * 144;
+        hdr = ldw128(blk);
+        qa = ldw128(blk + 16 + 32 * t);
+        qb = ldw128(blk + 32 + 32 * t);
+    }
+};
+struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
+    uint4 q0, q1, qh; // ql of 32-groups 0|2 and 1|3 of half n, qh of half n: run lh (16 bytes each)
+    uint2 sc;         // the 8 scales of half t % 2 (the half whose groups this thread sums up)
+    uint32_t d;
+    __device__ __forceinline__ void load(const uint8_t *row, uint32_t nblk, uint32_t b, int t) {
+        const int n = t >> 1, lh = t & 1;
+        const uint8_t *ql = row + (size_t)b * 128 + 64 * n + 16 * lh;
+        q0 = ldw128(ql);
+        q1 = ldw128(ql + 32);
+        qh = ldw128(row + (size_t)nblk * 128 + (size_t)b * 64 + 32 * n + 16 * lh);
+        sc = ldw64(row + (size_t)nblk * 192 + (size_t)b * 16 + 8 * (t & 1));
+        d = ldw16(row + (size_t)nblk * 208 + (size_t)b * 2);
+    }
+};
+
+struct GemvTargets {
+    const uint8_t *w[MAX_TARGETS];
+    float *y[MAX_TARGETS];
+    uint32_t rows[MAX_TARGETS];
+    uint32_t tile_end[MAX_TARGETS];
+    uint32_t count;
+};
+
+// FMT: FQ_Q4_K / FQ_Q6_K; MT: activation rows (1..4).  grid.x = 16-row tiles over all targets;
+// grid.y = routes in expert mode (route r: expert ids[r], activation row r / x_div, output row r).
+template <int FMT, int MT>
+__global__ void __launch_bounds__(THREADS)
+k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *__restrict__ prep, PrepI8 L,
+          const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts) {
+    using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
+    __shared__ float red[WARPS - 1][MT * 2][8];
+
+    uint32_t which = 0, first_block = 0;
+#pragma unroll
+    for (int i = 0; i < MAX_TARGETS - 1; i++)
+        if ((uint32_t)i + 1 < T.count && blockIdx.x >= T.tile_end[i]) { which = i + 1; first_block = T.tile_end[i]; }
+    const uint8_t *__restrict__ w = T.w[which];
+    float *__restrict__ y = T.y[which];
+    const uint32_t rows = T.rows[which];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    size_t y_base = 0;
+    if (ids) {
+        pdl_wait(); // the routing that wrote `ids` must have completed
+        const uint32_t r = blockIdx.y;
+        const uint32_t e = ids[r];
+        if (e >= experts) return;
+        w += (size_t)e * rows * pitch;
+        prep += (size_t)(r / x_div) * L.token_bytes;
+        y_base = (size_t)r * rows;
+    }
+    const uint32_t tile0 = blockIdx.x - first_block;
+    const uint8_t *rowp[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) rowp[r] = w + (size_t)min(tile0 * 16 + g + r * 8, rows - 1) * pitch;
+
+    const uint32_t nblk = L.nblk;
+    const uint32_t iters = nblk > (uint32_t)warp ? (nblk - warp + WARPS - 1) / WARPS : 0;
+    auto block_of = [&](uint32_t it) { return warp + min(it, iters - 1) * WARPS; };
+    Raw cur[2], nxt[2];
+    if (iters > 0) {
+        cur[0].load(rowp[0], nblk, block_of(0), t);
+        cur[1].load(rowp[1], nblk, block_of(0), t);
+    }
+    // The loads above touch immutable weights only; the rest reads prepared activations and writes y.
+    pdl_trigger();
+    pdl_wait();
+
+    // This thread feeds column g of B: the k slots of quad thread (g & 3), plane g >> 2; only the
+    // thread that owns those k slots has anything but zeros to feed.
+    const bool feeds = (g & 3) == t;
+    const int plane = g >> 2;
+    // It reads columns 2t, 2t+1 of the accumulators: scale groups 2 (t & 1), 2 (t & 1) + 1, plane t >> 1.
+    const int u = t & 1;
+    const float plane_weight = (t >> 1) ? 1.f : 256.f;
+
+    float yacc[MT][2];
+#pragma unroll
+    for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
+
+    for (uint32_t it = 0; it < iters; it++) {
+        const uint32_t b = warp + it * WARPS;
+        nxt[0].load(rowp[0], nblk, block_of(it + 1), t);
+        nxt[1].load(rowp[1], nblk, block_of(it + 1), t);
+
+        if constexpr (FMT == FQ_Q4_K) {
+            // Activation bytes of chunk t (64 k): low-nibble MMAs use bytes 0..31, high-nibble 32..63.
+            uint4 xb[MT][4];
+            uint4 sx[MT];
+            float inv[MT];
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                const uint8_t *tok = prep + (size_t)m * L.token_bytes;
+                const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 64 * t;
+#pragma unroll
+                for (int i = 0; i < 4; i++) xb[m][i] = feeds ? ldx128(src + 16 * i) : make_uint4(0, 0, 0, 0);
+                sx[m] = ldx128(tok + L.sx32_off + (size_t)b * 32 + 16 * u); // sums of sub-blocks 4u .. 4u+3
+                inv[m] = __uint_as_float(ldx32(tok + L.isc_off + (size_t)b * 4));
+            }
+            // The four scales and minimums of sub-blocks 4u .. 4u+3, one per byte.
+            uint32_t sc4[2], mn4[2];
+            float dsc[2], dmn[2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint4 h = cur[r].hdr;
+                sc4[r] = u ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
+                mn4[r] = u ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
+                dsc[r] = f16_bits_to_f32((uint16_t)(h.x & 0xFFFFu)) * plane_weight;
+                dmn[r] = (t >> 1) ? 0.f : f16_bits_to_f32((uint16_t)(h.x >> 16)); // minimum term once per plane pair
+            }
+            // u8 operands: low nibbles (sub-block 2t) and high nibbles (sub-block 2t + 1) of the 8 words.
+            uint32_t lo[2][8], hi[2][8];
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t wd = word_of(i < 4 ? cur[r].qa : cur[r].qb, i & 3);
+                    lo[r][i] = wd & 0x0F0F0F0Fu;
+                    hi[r][i] = (wd >> 4) & 0x0F0F0F0Fu;
+                }
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int i = 0; i < 4; i++) { // words 2i, 2i+1 <-> activation bytes 8i .. 8i+7
+                    const uint4 &xl = xb[m][i >> 1], &xh = xb[m][2 + (i >> 1)];
+                    mma_u8s8(cl, lo[0][2 * i], lo[1][2 * i], lo[0][2 * i + 1], lo[1][2 * i + 1], (i & 1) ? xl.z : xl.x, (i & 1) ? xl.w : xl.y);
+                    mma_u8s8(ch, hi[0][2 * i], hi[1][2 * i], hi[0][2 * i + 1], hi[1][2 * i + 1], (i & 1) ? xh.z : xh.x, (i & 1) ? xh.w : xh.y);
+                }
+                // Columns 2t, 2t+1 = scale groups 2u, 2u+1: sub-blocks 4u (low), 4u+1 (high), 4u+2, 4u+3.
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const int dot = byte_u(sc4[r], 0) * cl[2 * r] + byte_u(sc4[r], 1) * ch[2 * r] + byte_u(sc4[r], 2) * cl[2 * r + 1] +
+                                    byte_u(sc4[r], 3) * ch[2 * r + 1];
+                    const int mins = byte_u(mn4[r], 0) * (int)sx[m].x + byte_u(mn4[r], 1) * (int)sx[m].y +
+                                     byte_u(mn4[r], 2) * (int)sx[m].z + byte_u(mn4[r], 3) * (int)sx[m].w;
+                    yacc[m][r] = fmaf(inv[m], dsc[r] * (float)dot - dmn[r] * (float)mins, yacc[m][r]);
+                }
+            }
+        } else {
+            // Q6_K: thread t = (n, lh) owns, for i = 0..3, the values 128 n + 32 i + 16 lh + [0, 16).
+            const int n = t >> 1, lh = t & 1;
+            uint4 xb[MT][4], sxv[MT];
+            float inv[MT];
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                const uint8_t *tok = prep + (size_t)m * L.token_bytes;
+                const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 128 * n + 16 * lh;
+#pragma unroll
+                for (int i = 0; i < 4; i++) xb[m][i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
+                // byte sums of the 16-groups 8u .. 8u+7 of this thread's plane (t >> 1)
+                sxv[m] = ldx128(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
+                inv[m] = __uint_as_float(ldx32(tok + L.isc_off + (size_t)b * 4));
+            }
+            uint32_t v4[2][4][4]; // [row][i][word]: four 6-bit quants, one per byte
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int wi = 0; wi < 4; wi++) {
+                        const uint32_t lw = word_of((i & 1) ? cur[r].q1 : cur[r].q0, wi), hw = word_of(cur[r].qh, wi);
+                        const uint32_t lo4 = (i < 2) ? lw : (lw >> 4);
+                        const uint32_t hi4 = i == 0 ? (hw << 4) : i == 1 ? (hw << 2) : i == 2 ? hw : (hw >> 2);
+                        v4[r][i][wi] = lop3_select(lo4, hi4, 0x0F0F0F0Fu) & 0x3F3F3F3Fu;
+                    }
+            float dd[2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) dd[r] = f16_bits_to_f32((uint16_t)cur[r].d) * plane_weight;
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                int dot[2] = {0, 0};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    int c[4] = {0, 0, 0, 0};
+                    const uint4 &xv = xb[m][i];
+                    mma_u8s8(c, v4[0][i][0], v4[1][i][0], v4[0][i][1], v4[1][i][1], xv.x, xv.y);
+                    mma_u8s8(c, v4[0][i][2], v4[1][i][2], v4[0][i][3], v4[1][i][3], xv.z, xv.w);
+                    // Columns 2t, 2t+1 = quad threads 2u, 2u+1 = (half u, runs 0 and 1): 16-groups
+                    // 8u + 2i and 8u + 2i + 1.  (q - 32) is applied as  dot - 32 * sum(x bytes).
+                    const uint32_t spair = word_of(sxv[m], i);
+                    const int s0 = (int)(int16_t)(spair & 0xFFFFu), s1 = (int)(int16_t)(spair >> 16);
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const uint32_t scw = (i < 2) ? cur[r].sc.x : cur[r].sc.y;
+                        dot[r] += byte_s(scw, 2 * (i & 1)) * (c[2 * r] - 32 * s0) + byte_s(scw, 2 * (i & 1) + 1) * (c[2 * r + 1] - 32 * s1);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 2; r++) yacc[m][r] = fmaf(inv[m] * dd[r], (float)dot[r], yacc[m][r]);
+            }
+        }
+        cur[0] = nxt[0];
+        cur[1] = nxt[1];
+    }
+    // Quad threads hold partial sums of different scale groups and planes: add them, then the warps.
+#pragma unroll
+    for (int m = 0; m < MT; m++)
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            yacc[m][r] += __shfl_xor_sync(0xffffffffu, yacc[m][r], 1);
+            yacc[m][r] += __shfl_xor_sync(0xffffffffu, yacc[m][r], 2);
+        }
+    if (warp > 0 && t == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            red[warp - 1][m * 2][g] = yacc[m][0];
+            red[warp - 1][m * 2 + 1][g] = yacc[m][1];
+        }
+    }
+    __syncthreads();
+    if (warp == 0 && t == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; m++)
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                float v = yacc[m][r];
+#pragma unroll
+                for (int ww = 0; ww < WARPS - 1; ww++) v += red[ww][m * 2 + r][g];
+                const uint32_t row = tile0 * 16 + g + r * 8;
+                if (row < rows) y[y_base + (size_t)m * rows + row] = v;
+            }
+    }
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    // FQ_PDL=0 turns programmatic dependent launch off (plain stream order), for A/B measurements.
+    static const bool pdl = [] { const char *e = getenv("FQ_PDL"); return !(e && e[0] == '0'); }();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+template <int FMT, int MT>
+cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const uint8_t *prep, const PrepI8 &L, bool expert) {
+    GemvTargets T{};
+    T.count = count;
+    uint32_t blocks = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        T.w[i] = a[i].w;
+        T.y[i] = (float *)a[i].y;
+        T.rows[i] = a[i].rows;
+        blocks += (a[i].rows + 15) / 16;
+        T.tile_end[i] = blocks;
+    }
+    dim3 grid(blocks, expert ? a[0].m : 1);
+    return launch_pdl(k_gemv_i8<FMT, MT>, grid, dim3(THREADS), dev->stream, T, a[0].row_bytes, prep, L, a[0].ids, a[0].x_div,
+                      a[0].experts);
+}
+
+} // namespace
+
+// `a[0..count)` share x, m (<= 4), format and width; expert mode takes one matrix.
+int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count) {
+    if (count == 0 || count > (uint32_t)MAX_TARGETS) return FQ_ERR_UNSUPPORTED;
+    const ProjectArgs &f = a[0];
+    if ((f.format != FQ_Q4_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
+    if (f.cols % 256 || f.row_bytes % 16) return FQ_ERR_UNSUPPORTED;
+    for (uint32_t i = 1; i < count; i++)
+        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].m != f.m || a[i].ids || f.ids ||
+            a[i].x_dtype != FQ_F32 || a[i].y_dtype != FQ_F32)
+            return FQ_ERR_UNSUPPORTED;
+    const bool expert = f.ids != nullptr;
+    uint32_t xrows, m;
+    if (expert) {
+        if (f.m > 65535) return FQ_ERR_UNSUPPORTED;
+        xrows = f.m / f.x_div; // the caller checked that x holds routes / x_div rows
+        m = 1;
+    } else {
+        if (f.m > (uint32_t)MAX_TOKENS) return FQ_ERR_UNSUPPORTED;
+        xrows = m = f.m;
+    }
+    const PrepI8 L = prep_i8_layout(f.cols);
+    // Successive projections use alternate halves of the scratch, so a preparation kernel that starts
+    // early never writes what the previous projection may still be reading from a cache.
+    if ((size_t)xrows * L.token_bytes > dev->xprep_bytes / 2) return FQ_ERR_UNSUPPORTED;
+    dev->xprep_turn ^= 1u;
+    uint8_t *prep = (uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0);
+    const uint32_t warps = xrows * L.nblk;
+    if (int rc = fq_check_cuda(dev, launch_pdl(k_prep_i8, dim3((warps + 3) / 4), dim3(128), dev->stream, (const float *)f.x, xrows, L, prep),
+                               "activation preparation launch"))
+        return rc;
+    cudaError_t e;
+    if (f.format == FQ_Q4_K) {
+        e = m == 1 ? launch<FQ_Q4_K, 1>(dev, a, count, prep, L, expert) : m == 2 ? launch<FQ_Q4_K, 2>(dev, a, count, prep, L, expert)
+          : m == 3 ? launch<FQ_Q4_K, 3>(dev, a, count, prep, L, expert) : launch<FQ_Q4_K, 4>(dev, a, count, prep, L, expert);
+    } else {
+        e = m == 1 ? launch<FQ_Q6_K, 1>(dev, a, count, prep, L, expert) : m == 2 ? launch<FQ_Q6_K, 2>(dev, a, count, prep, L, expert)
+          : m == 3 ? launch<FQ_Q6_K, 3>(dev, a, count, prep, L, expert) : launch<FQ_Q6_K, 4>(dev, a, count, prep, L, expert);
+    }
+    if (int rc = fq_check_cuda(dev, e, "gemv launch")) return rc;
+    return fq_end_enqueue(dev, "gemv_i8", 2);
+}

@@ -27,20 +27,31 @@ struct fq_device {
     int fail_after = -1;          // test hook: enqueues left before an injected failure
     bool fail_completion = false; // test hook: next synchronize reports failure
     fq_counters counters{};
+    bool capturing = false;       // between fq_capture_begin and fq_capture_end
+    uint64_t captured_kernels = 0;
     std::map<uintptr_t, size_t> allocations; // buffers handed out by fq_buffer_alloc
     // Fixed scratch, allocated once at creation.
     void *xprep = nullptr;        // prepared activations of the tensor-core GEMV
     size_t xprep_bytes = 0;
+    uint32_t xprep_turn = 0;      // successive projections alternate between the two halves of xprep
     void *staging_dev = nullptr;  // device side of the host-buffer entry points
     void *staging_host = nullptr; // pinned host side
+};
+
+struct fq_graph {
+    fq_device *dev = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;
 };
 
 struct fq_matrix {
     fq_device *dev = nullptr;
     int format = 0;
     uint64_t rows = 0, cols = 0, experts = 1, row_bytes = 0, byte_size = 0;
+    uint64_t pitch = 0; // bytes between rows of the device layout (see fq_row_pitch)
     uint32_t block_elems = 0, block_bytes = 0;
-    uint8_t *data = nullptr; // device copy of the GGUF blocks, byte for byte
+    uint8_t *data = nullptr; // device copy of the blocks in the device layout
     uint64_t expert_rows() const { return rows / experts; }
 };
 
@@ -60,7 +71,7 @@ inline size_t fq_dtype_size(int dtype) { return dtype == FQ_BF16 ? 2 : 4; }
 // Kernel launchers (one per translation unit); all enqueue on dev->stream and return a status.
 struct ProjectArgs {
     const uint8_t *w;
-    uint32_t format, rows, cols, row_bytes; // rows = rows of one expert slice
+    uint32_t format, rows, cols, row_bytes; // rows = rows of one expert slice; row_bytes = device row pitch
     const void *x;
     void *y;
     int x_dtype, y_dtype;
@@ -81,6 +92,11 @@ int fq_launch_get_rows(fq_device *dev, const fq_matrix *w, const uint32_t *ids, 
 // Tensor-core decode/verify GEMV (M <= FQ_GEMV_MAX_M, F32 in/out); returns FQ_ERR_UNSUPPORTED
 // when the shape has no fast kernel so the caller can fall back to the exact one.
 int fq_launch_gemv_fast(fq_device *dev, const ProjectArgs &a);
+// Several matrices of one format and width sharing x and m in one launch (same fallback contract).
+int fq_launch_gemv_fast_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
 size_t fq_gemv_scratch_bytes();
+// Integer tensor-core decode GEMV for 1..4 activation rows and for per-route expert projections
+// (same fallback contract).
+int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
 // tcgen05 dequant-GEMM (BF16 in/out); same fallback contract.
 int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a);

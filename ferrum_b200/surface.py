@@ -99,6 +99,10 @@ class Device:
     def set_stream(self, cuda_stream: Optional[int]) -> None:
         self.check(self._L.fq_device_set_stream(self.handle, C.c_void_p(cuda_stream or 0)))
 
+    def stream_ptr(self) -> int:
+        """The ``cudaStream_t`` enqueues currently go to."""
+        return int(self._L.fq_device_stream(self.handle) or 0)
+
     def synchronize(self) -> None:
         self.check(self._L.fq_synchronize(self.handle))
 
@@ -119,10 +123,48 @@ class Device:
     def fail_completion(self) -> None:
         self.check(self._L.fq_test_fail_completion(self.handle))
 
+    def capture_begin(self) -> None:
+        """Start recording enqueues (the handle must be on its own stream: ``set_stream(None)``)."""
+        self.check(self._L.fq_capture_begin(self.handle))
+
+    def capture_end(self) -> "Graph":
+        g = C.c_void_p()
+        self.check(self._L.fq_capture_end(self.handle, C.byref(g)))
+        return Graph(self, g)
+
+    def upload(self, dst: torch.Tensor, host: np.ndarray) -> None:
+        """Enqueue a host-to-device copy (asynchronous when ``host`` is pinned memory)."""
+        self.check(self._L.fq_upload(self.handle, C.c_void_p(dst.data_ptr()), C.c_void_p(host.ctypes.data), host.nbytes))
+
+    def download_async(self, host: np.ndarray, src: torch.Tensor) -> None:
+        """Enqueue a device-to-host copy; valid after the next ``synchronize``."""
+        self.check(self._L.fq_download_async(self.handle, C.c_void_p(host.ctypes.data), C.c_void_p(src.data_ptr()), host.nbytes))
+
     def close(self) -> None:
         if self.handle:
             self._L.fq_device_destroy(self.handle)
             self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Graph:
+    """A recorded batch of enqueues (the counterpart of one command epoch of the reference)."""
+
+    def __init__(self, device: Device, handle: C.c_void_p):
+        self.device, self.handle = device, handle
+
+    def launch(self) -> None:
+        self.device.check(self.device._L.fq_graph_launch(self.device.handle, self.handle))
+
+    def close(self) -> None:
+        if self.handle and self.device.handle:
+            self.device._L.fq_graph_destroy(self.handle)
+        self.handle = None
 
     def __del__(self):
         try:
@@ -188,6 +230,18 @@ def project(d: Device, w: Matrix, x: torch.Tensor, m: int, y: torch.Tensor) -> N
     """``HybridModel::project(d, w, x, m, y)``: y[m, rows] = x[m, cols] . W^T."""
     _need(d, x, y)
     d.check(d._L.fq_project(d.handle, w.handle, _ptr(x), _dtype_id(x), x.numel(), m, _ptr(y), _dtype_id(y), y.numel()))
+
+
+def project_many(d: Device, ws: Sequence[Matrix], x: torch.Tensor, m: int, ys: Sequence[torch.Tensor]) -> None:
+    """Projections sharing x and m (q|k|v, gate|up): one launch when the matrices share format and width."""
+    _need(d, x, *ys)
+    n = len(ws)
+    wa = (C.c_void_p * n)(*[w.handle.value for w in ws])
+    ya = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    for w, y in zip(ws, ys):
+        if y.numel() != m * w.rows:
+            raise ShapeError(f"output of {y.numel()} values for [{m}, {w.rows}]")
+    d.check(d._L.fq_project_many(d.handle, wa, n, _ptr(x), _dtype_id(x), x.numel(), m, ya, _dtype_id(ys[0])))
 
 
 def project_id(d: Device, w: Matrix, x: torch.Tensor, ids: torch.Tensor, routes: int, x_div: int, y: torch.Tensor) -> None:

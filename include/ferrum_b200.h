@@ -89,11 +89,29 @@ int fq_set_exact(fq_device *dev, int on);
 int fq_test_fail_after(fq_device *dev, int n);
 int fq_test_fail_completion(fq_device *dev);
 
+/* ---- batched submission ------------------------------------------------------------------- */
+
+/* The reference batches the dispatches of a forward pass into one command epoch
+ * (`execution_with_shared_encoder`, src/metal/mod.rs:563-633) because a 27B decode step is ~930
+ * small dispatches.  The CUDA counterpart is a captured graph: every enqueue between
+ * `fq_capture_begin` and `fq_capture_end` is recorded instead of run (on the handle's OWN stream; a
+ * caller-provided stream must be restored first), and `fq_graph_launch` replays the whole batch with
+ * one submission.  Pointers and shapes are baked in; `fq_synchronize` is refused while capturing. */
+typedef struct fq_graph fq_graph;
+int fq_capture_begin(fq_device *dev);
+int fq_capture_end(fq_device *dev, fq_graph **out);
+int fq_graph_launch(fq_device *dev, fq_graph *graph);
+int fq_graph_destroy(fq_graph *graph);
+
 /* ---- caller-visible device buffers (src/metal/mod.rs:700-760 `buffer`, Tensor::from_f32) --- */
 int fq_buffer_alloc(fq_device *dev, size_t bytes, void **device_ptr);
 int fq_buffer_free(fq_device *dev, void *device_ptr);
 int fq_upload(fq_device *dev, void *device_ptr, const void *host, size_t bytes);
+/* `fq_download` waits for the data (a read of results is a completion point, as `Tensor::to_f32`
+ * is in the reference); `fq_download_async` only enqueues the copy -- `host` should be pinned -- and
+ * the data is valid after the next `fq_synchronize`. */
 int fq_download(fq_device *dev, void *host, const void *device_ptr, size_t bytes);
+int fq_download_async(fq_device *dev, void *host, const void *device_ptr, size_t bytes);
 
 /* ---- weights ----------------------------------------------------------------------------- */
 
@@ -115,6 +133,13 @@ int fq_matrix_get_info(const fq_matrix *w, fq_matrix_info *out);
  * store) is the legacy `project_quantized` tensor path (src/ops/transformer.rs:96-297). */
 int fq_project(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems,
                size_t m, void *y, int y_dtype, size_t y_elems);
+
+/* `count` projections that share x and m, as the reference issues back to back for q|k|v
+ * (src/hybrid/engine.rs:2265-2267) and gate|up (:3239-3240).  y[i] receives m * rows_i values.
+ * Matrices of one format and width run as ONE launch over all their rows; otherwise this is
+ * `fq_project` in a loop.  Same checks and errors as `fq_project`. */
+int fq_project_many(fq_device *dev, const fq_matrix *const *w, size_t count, const void *x, int x_dtype,
+                    size_t x_elems, size_t m, void *const *y, int y_dtype);
 
 /* `HybridModel::project_id(d, w, x, ids, routes, x_div, y)` (src/hybrid/engine.rs:3114-3147):
  * route r multiplies activation row r / x_div by the rows of expert ids[r]; F32 in and out. */

@@ -467,3 +467,68 @@ def test_full_size_projection_rows_and_self_consistency(device, fmt, rows, cols,
     finally:
         device.set_exact(False)
     assert ref.rel_err(got, exact) <= TOL_F32
+
+
+# ------------------------------------------------------------------ fused launches and batched submission
+
+@pytest.mark.parametrize("fmt", [ref.Q4_K, ref.Q6_K])
+@pytest.mark.parametrize("m", [1, 3, 5, 16])
+def test_project_many_is_bit_identical_to_separate_projections(device, fmt, m):
+    """q|k|v-style fusion: one launch over several matrices gives each matrix exactly what its own
+    projection gives (same kernel, same per-row summation order)."""
+    s = S()
+    cols, rows = 1024, (96, 40, 17)
+    packed = [ref.random_matrix(fmt, r, cols, seed=30 + i) for i, r in enumerate(rows)]
+    ws = [s.Matrix.from_packed(device, r, cols, 1, fmt, p) for r, p in zip(rows, packed)]
+    x = np.random.default_rng(m).standard_normal((m, cols)).astype(np.float32)
+    xt = dev_f32(x)
+    fused = [torch.zeros(m * r, dtype=torch.float32, device="cuda") for r in rows]
+    s.project_many(device, ws, xt, m, fused)
+    device.synchronize()
+    for w, r, p, yf in zip(ws, rows, packed, fused):
+        ys = torch.zeros(m * r, dtype=torch.float32, device="cuda")
+        s.project(device, w, xt, m, ys)
+        device.synchronize()
+        assert np.array_equal(host(yf).view(np.uint32), host(ys).view(np.uint32))
+        assert ref.rel_err(host(yf).reshape(m, r), ref.matmul(fmt, p, r, cols, x, m)) <= TOL_F32
+    # mixed formats fall back to one projection each, with the same results
+    mixed = [ws[0], s.Matrix.from_packed(device, 24, cols, 1, ref.Q8_0, ref.random_matrix(ref.Q8_0, 24, cols, 40))]
+    outs = [torch.zeros(m * 96, dtype=torch.float32, device="cuda"), torch.zeros(m * 24, dtype=torch.float32, device="cuda")]
+    s.project_many(device, mixed, xt, m, outs)
+    device.synchronize()
+    assert np.array_equal(host(outs[0]).view(np.uint32), host(fused[0]).view(np.uint32))
+    assert ref.rel_err(host(outs[1]).reshape(m, 24), ref.matmul(ref.Q8_0, ref.random_matrix(ref.Q8_0, 24, cols, 40), 24, cols, x, m)) <= TOL_F32
+
+
+def test_captured_graph_replays_a_layer(device):
+    """A recorded batch (the counterpart of one command epoch) replays with new inputs in place."""
+    s = S()
+    d2 = s.Device(0, use_torch_stream=False)
+    hidden, width = 512, 768
+    gate, up = ref.random_matrix(ref.Q4_K, width, hidden, 1), ref.random_matrix(ref.Q4_K, width, hidden, 2)
+    down = ref.random_matrix(ref.Q6_K, hidden, width, 3)
+    mats = [s.Matrix.from_packed(d2, width, hidden, 1, ref.Q4_K, gate), s.Matrix.from_packed(d2, width, hidden, 1, ref.Q4_K, up),
+            s.Matrix.from_packed(d2, hidden, width, 1, ref.Q6_K, down)]
+    m = 2
+    x = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(3 * m * width, dtype=torch.float32, device="cuda")
+    out = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    with pytest.raises(s.ParameterError):
+        d2.capture_end()
+    d2.capture_begin()
+    s.dense_ffn(d2, *mats, x, m, scratch, out)
+    with pytest.raises(s.ParameterError):
+        d2.synchronize()  # refused while recording
+    graph = d2.capture_end()
+    before = d2.counters().dispatches
+    for seed in (4, 5):
+        xv = np.random.default_rng(seed).standard_normal((m, hidden)).astype(np.float32)
+        d2.upload(x, xv)
+        graph.launch()
+        d2.synchronize()
+        want = oracle_dense_ffn(gate, up, down, xv, m, hidden, width)
+        assert ref.rel_err(host(out).reshape(m, hidden), want) <= 2 * TOL_F32
+    assert d2.counters().dispatches - before == 2 * 5  # (prep + gemv) x 2 + glu, twice
+    graph.close()
+    d2.close()
