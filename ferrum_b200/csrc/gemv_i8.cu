@@ -27,6 +27,7 @@
 // 128-bit loads, the next superblock always in flight.  Four warps split K; partial sums meet in
 // shared memory in a fixed order, so results are deterministic and a row-sharded matrix gives the
 // same bits as the whole one.
+#include <algorithm>
 #include <cstdlib>
 #include <type_traits>
 
@@ -35,8 +36,7 @@
 
 namespace {
 
-constexpr int WARPS = 4;
-constexpr int THREADS = WARPS * 32;
+constexpr int MAX_WARPS = 16; // warps of a block split K between them; the count is chosen per launch
 constexpr int MAX_TARGETS = 4;
 constexpr int MAX_TOKENS = 4;
 
@@ -183,13 +183,15 @@ __device__ __forceinline__ int byte_u(uint32_t w, int i) { return (int)((w >> (8
 __device__ __forceinline__ int byte_s(uint32_t w, int i) { return (int)(int8_t)((w >> (8 * i)) & 0xFFu); }
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-struct Q4Raw { // header and the 32 packed bytes of chunk t
+// Q4_K: the header, 16 bytes of chunk t / 2 and 16 bytes of chunk 2 + t / 2 (bytes 16 (t % 2) .. of each
+// chunk's 32), so that the four threads of a quad read 64 contiguous bytes per instruction.
+struct Q4Raw {
     uint4 hdr, qa, qb;
     __device__ __forceinline__ void load(const uint8_t *row, uint32_t, uint32_t b, int t) {
         const uint8_t *blk = row + (size_t)b * 144;
         hdr = ldw128(blk);
-        qa = ldw128(blk + 16 + 32 * t);
-        qb = ldw128(blk + 32 + 32 * t);
+        qa = ldw128(blk + 16 + 16 * t);
+        qb = ldw128(blk + 80 + 16 * t);
     }
 };
 struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
@@ -207,6 +209,34 @@ struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
     }
 };
 
+// The prepared activations of one row that one thread needs for one superblock.
+//   Q4_K: xb[0] / xb[1] = the 16 activation bytes under this thread's low / high nibbles of the chunk it
+//         feeds (values 64 c + 16 (t % 2) + [0, 16), + 32), sx = sums of sub-blocks 4u .. 4u+3.
+//   Q6_K: xb[i] = the 16 bytes under its run of 32-group i, sx = byte sums of 16-groups 8u .. 8u+7.
+template <int FMT> struct Act {
+    uint4 xb[FMT == FQ_Q4_K ? 2 : 4];
+    uint4 sx;
+    float inv;
+    __device__ __forceinline__ void load(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) {
+        const int plane = g >> 2, u = t & 1;
+        if constexpr (FMT == FQ_Q4_K) {
+            const bool feeds = (t >> 1) == (g & 1);
+            const int chunk = (((g & 3) >> 1) ? 2 : 0) + (t >> 1);
+            const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 64 * chunk + 16 * (t & 1);
+#pragma unroll
+            for (int i = 0; i < 2; i++) xb[i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
+            sx = ldx128(tok + L.sx32_off + (size_t)b * 32 + 16 * u);
+        } else {
+            const bool feeds = (g & 3) == t;
+            const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 128 * (t >> 1) + 16 * (t & 1);
+#pragma unroll
+            for (int i = 0; i < 4; i++) xb[i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
+            sx = ldx128(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
+        }
+        inv = __uint_as_float(ldx32(tok + L.isc_off + (size_t)b * 4));
+    }
+};
+
 struct GemvTargets {
     const uint8_t *w[MAX_TARGETS];
     float *y[MAX_TARGETS];
@@ -218,11 +248,12 @@ struct GemvTargets {
 // FMT: FQ_Q4_K / FQ_Q6_K; MT: activation rows (1..4).  grid.x = 16-row tiles over all targets;
 // grid.y = routes in expert mode (route r: expert ids[r], activation row r / x_div, output row r).
 template <int FMT, int MT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(MT >= 3 ? 256 : MT == 2 ? 384 : MAX_WARPS * 32)
 k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *__restrict__ prep, PrepI8 L,
           const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts) {
     using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
-    __shared__ float red[WARPS - 1][MT * 2][8];
+    __shared__ float red[MAX_WARPS - 1][MT * 2][8];
+    const int WARPS = blockDim.x >> 5;
 
     uint32_t which = 0, first_block = 0;
 #pragma unroll
@@ -261,37 +292,39 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     pdl_trigger();
     pdl_wait();
 
-    // This thread feeds column g of B: the k slots of quad thread (g & 3), plane g >> 2; only the
-    // thread that owns those k slots has anything but zeros to feed.
-    const bool feeds = (g & 3) == t;
-    const int plane = g >> 2;
+    // This thread feeds column g of B (scale group g & 3, plane g >> 2) on its own k slots only, and
+    // only if those k slots belong to that scale group; everything else it feeds is zero.
+    //   Q6_K: group j = the k slots of quad thread j.
+    //   Q4_K: group j = chunk j; thread t holds chunk t / 2 in its first operand word (k slots 4t ..)
+    //         and chunk 2 + t / 2 in its second (k slots 16 + 4t ..).
+    const bool second = FMT == FQ_Q4_K && ((g & 3) >> 1); // Q4_K: the group sits in the second operand word
     // It reads columns 2t, 2t+1 of the accumulators: scale groups 2 (t & 1), 2 (t & 1) + 1, plane t >> 1.
     const int u = t & 1;
     const float plane_weight = (t >> 1) ? 1.f : 256.f;
+    // With one activation row its fragments are fetched one superblock ahead, like the weights; with
+    // more rows the registers do not allow that and they are fetched at the top of the iteration.
+    constexpr bool AHEAD = MT == 1;
+    Act<FMT> acur[MT], anxt[AHEAD ? MT : 1];
+    if (AHEAD && iters > 0) {
+#pragma unroll
+        for (int m = 0; m < MT; m++) acur[m].load(prep + (size_t)m * L.token_bytes, L, block_of(0), t, g);
+    }
 
     float yacc[MT][2];
 #pragma unroll
     for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
 
     for (uint32_t it = 0; it < iters; it++) {
-        const uint32_t b = warp + it * WARPS;
+        // Everything the next iteration needs is requested now; this one runs from registers.
         nxt[0].load(rowp[0], nblk, block_of(it + 1), t);
         nxt[1].load(rowp[1], nblk, block_of(it + 1), t);
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            if (AHEAD) anxt[m].load(prep + (size_t)m * L.token_bytes, L, block_of(it + 1), t, g);
+            else acur[m].load(prep + (size_t)m * L.token_bytes, L, block_of(it), t, g);
+        }
 
         if constexpr (FMT == FQ_Q4_K) {
-            // Activation bytes of chunk t (64 k): low-nibble MMAs use bytes 0..31, high-nibble 32..63.
-            uint4 xb[MT][4];
-            uint4 sx[MT];
-            float inv[MT];
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                const uint8_t *tok = prep + (size_t)m * L.token_bytes;
-                const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 64 * t;
-#pragma unroll
-                for (int i = 0; i < 4; i++) xb[m][i] = feeds ? ldx128(src + 16 * i) : make_uint4(0, 0, 0, 0);
-                sx[m] = ldx128(tok + L.sx32_off + (size_t)b * 32 + 16 * u); // sums of sub-blocks 4u .. 4u+3
-                inv[m] = __uint_as_float(ldx32(tok + L.isc_off + (size_t)b * 4));
-            }
             // The four scales and minimums of sub-blocks 4u .. 4u+3, one per byte.
             uint32_t sc4[2], mn4[2];
             float dsc[2], dmn[2];
@@ -303,7 +336,8 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
                 dsc[r] = f16_bits_to_f32((uint16_t)(h.x & 0xFFFFu)) * plane_weight;
                 dmn[r] = (t >> 1) ? 0.f : f16_bits_to_f32((uint16_t)(h.x >> 16)); // minimum term once per plane pair
             }
-            // u8 operands: low nibbles (sub-block 2t) and high nibbles (sub-block 2t + 1) of the 8 words.
+            // u8 operands: low nibbles (even sub-block of the chunk) and high nibbles (odd sub-block); words
+            // 0..3 from the first chunk, 4..7 from the second.
             uint32_t lo[2][8], hi[2][8];
 #pragma unroll
             for (int r = 0; r < 2; r++)
@@ -317,36 +351,24 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
             for (int m = 0; m < MT; m++) {
                 int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};
 #pragma unroll
-                for (int i = 0; i < 4; i++) { // words 2i, 2i+1 <-> activation bytes 8i .. 8i+7
-                    const uint4 &xl = xb[m][i >> 1], &xh = xb[m][2 + (i >> 1)];
-                    mma_u8s8(cl, lo[0][2 * i], lo[1][2 * i], lo[0][2 * i + 1], lo[1][2 * i + 1], (i & 1) ? xl.z : xl.x, (i & 1) ? xl.w : xl.y);
-                    mma_u8s8(ch, hi[0][2 * i], hi[1][2 * i], hi[0][2 * i + 1], hi[1][2 * i + 1], (i & 1) ? xh.z : xh.x, (i & 1) ? xh.w : xh.y);
+                for (int i = 0; i < 4; i++) { // word i of either chunk <-> activation bytes 4i .. 4i+3 of the run
+                    const uint32_t xl = word_of(acur[m].xb[0], i), xh = word_of(acur[m].xb[1], i);
+                    mma_u8s8(cl, lo[0][i], lo[1][i], lo[0][4 + i], lo[1][4 + i], second ? 0u : xl, second ? xl : 0u);
+                    mma_u8s8(ch, hi[0][i], hi[1][i], hi[0][4 + i], hi[1][4 + i], second ? 0u : xh, second ? xh : 0u);
                 }
                 // Columns 2t, 2t+1 = scale groups 2u, 2u+1: sub-blocks 4u (low), 4u+1 (high), 4u+2, 4u+3.
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     const int dot = byte_u(sc4[r], 0) * cl[2 * r] + byte_u(sc4[r], 1) * ch[2 * r] + byte_u(sc4[r], 2) * cl[2 * r + 1] +
                                     byte_u(sc4[r], 3) * ch[2 * r + 1];
-                    const int mins = byte_u(mn4[r], 0) * (int)sx[m].x + byte_u(mn4[r], 1) * (int)sx[m].y +
-                                     byte_u(mn4[r], 2) * (int)sx[m].z + byte_u(mn4[r], 3) * (int)sx[m].w;
-                    yacc[m][r] = fmaf(inv[m], dsc[r] * (float)dot - dmn[r] * (float)mins, yacc[m][r]);
+                    const uint4 &sx = acur[m].sx;
+                    const int mins = byte_u(mn4[r], 0) * (int)sx.x + byte_u(mn4[r], 1) * (int)sx.y +
+                                     byte_u(mn4[r], 2) * (int)sx.z + byte_u(mn4[r], 3) * (int)sx.w;
+                    yacc[m][r] = fmaf(acur[m].inv, dsc[r] * (float)dot - dmn[r] * (float)mins, yacc[m][r]);
                 }
             }
         } else {
             // Q6_K: thread t = (n, lh) owns, for i = 0..3, the values 128 n + 32 i + 16 lh + [0, 16).
-            const int n = t >> 1, lh = t & 1;
-            uint4 xb[MT][4], sxv[MT];
-            float inv[MT];
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                const uint8_t *tok = prep + (size_t)m * L.token_bytes;
-                const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 128 * n + 16 * lh;
-#pragma unroll
-                for (int i = 0; i < 4; i++) xb[m][i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
-                // byte sums of the 16-groups 8u .. 8u+7 of this thread's plane (t >> 1)
-                sxv[m] = ldx128(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
-                inv[m] = __uint_as_float(ldx32(tok + L.isc_off + (size_t)b * 4));
-            }
             uint32_t v4[2][4][4]; // [row][i][word]: four 6-bit quants, one per byte
 #pragma unroll
             for (int r = 0; r < 2; r++)
@@ -368,12 +390,12 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     int c[4] = {0, 0, 0, 0};
-                    const uint4 &xv = xb[m][i];
+                    const uint4 &xv = acur[m].xb[i];
                     mma_u8s8(c, v4[0][i][0], v4[1][i][0], v4[0][i][1], v4[1][i][1], xv.x, xv.y);
                     mma_u8s8(c, v4[0][i][2], v4[1][i][2], v4[0][i][3], v4[1][i][3], xv.z, xv.w);
                     // Columns 2t, 2t+1 = quad threads 2u, 2u+1 = (half u, runs 0 and 1): 16-groups
                     // 8u + 2i and 8u + 2i + 1.  (q - 32) is applied as  dot - 32 * sum(x bytes).
-                    const uint32_t spair = word_of(sxv[m], i);
+                    const uint32_t spair = word_of(acur[m].sx, i);
                     const int s0 = (int)(int16_t)(spair & 0xFFFFu), s1 = (int)(int16_t)(spair >> 16);
 #pragma unroll
                     for (int r = 0; r < 2; r++) {
@@ -382,11 +404,15 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
                     }
                 }
 #pragma unroll
-                for (int r = 0; r < 2; r++) yacc[m][r] = fmaf(inv[m] * dd[r], (float)dot[r], yacc[m][r]);
+                for (int r = 0; r < 2; r++) yacc[m][r] = fmaf(acur[m].inv * dd[r], (float)dot[r], yacc[m][r]);
             }
         }
         cur[0] = nxt[0];
         cur[1] = nxt[1];
+        if (AHEAD) {
+#pragma unroll
+            for (int m = 0; m < MT; m++) acur[m] = anxt[m];
+        }
     }
     // Quad threads hold partial sums of different scale groups and planes: add them, then the warps.
 #pragma unroll
@@ -448,7 +474,20 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
         T.tile_end[i] = blocks;
     }
     dim3 grid(blocks, expert ? a[0].m : 1);
-    return launch_pdl(k_gemv_i8<FMT, MT>, grid, dim3(THREADS), dev->stream, T, a[0].row_bytes, prep, L, a[0].ids, a[0].x_div,
+    // Warps per block = ways K is split: enough warps in the grid to keep every SM's schedulers and
+    // memory pipeline busy (about 32 per SM), at least two superblocks per warp, and among the counts
+    // that satisfy this the one that wastes the fewest warp-iterations on an uneven split.
+    const uint32_t nblk = L.nblk, want = (uint32_t)dev->sm_count * 32u;
+    const uint32_t reg_cap = MT >= 3 ? 8u : MT == 2 ? 12u : (uint32_t)MAX_WARPS; // wider variants need more registers per thread
+    const uint32_t max_k = std::max(1u, std::min(reg_cap, nblk / 2));
+    const uint32_t need = std::min(max_k, std::max(1u, (uint32_t)((want + (uint64_t)blocks * grid.y - 1) / ((uint64_t)blocks * grid.y))));
+    uint32_t warps = need;
+    uint64_t best = ~0ull;
+    for (uint32_t k = need; k <= max_k; k++) {
+        const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need); // prefer small k on ties
+        if (waste < best) { best = waste; warps = k; }
+    }
+    return launch_pdl(k_gemv_i8<FMT, MT>, grid, dim3(warps * 32), dev->stream, T, a[0].row_bytes, prep, L, a[0].ids, a[0].x_div,
                       a[0].experts);
 }
 
@@ -481,6 +520,9 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     dev->xprep_turn ^= 1u;
     uint8_t *prep = (uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0);
     const uint32_t warps = xrows * L.nblk;
+    // FQ_SKIP_PREP=1 (measurement only, results are then garbage) leaves the preparation kernel out.
+    static const bool skip_prep = [] { const char *e = getenv("FQ_SKIP_PREP"); return e && e[0] == '1'; }();
+    if (!skip_prep)
     if (int rc = fq_check_cuda(dev, launch_pdl(k_prep_i8, dim3((warps + 3) / 4), dim3(128), dev->stream, (const float *)f.x, xrows, L, prep),
                                "activation preparation launch"))
         return rc;
