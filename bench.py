@@ -288,6 +288,37 @@ def run_ours(args):
             extra[f"m{mm}_gbs"] = round(total_bytes / (t * 1e-3) / 1e9, 1)
         out["decode_widths"] = extra
 
+        # Prefill dequant-GEMM (config 2): the same 7 matrices of layer 0 at M = 512 and 2048, bf16
+        # activations and outputs, tcgen05 with fp32 accumulation; flops = 2 M N K per matrix.
+        prefill = {}
+        for mm in (512, 2048):
+            xs = {g[0]: torch.randn(mm * shapes[g[0]][1], device="cuda").to(torch.bfloat16) for g in GROUPS}
+            ys = {n: torch.zeros(mm * shapes[n][0], dtype=torch.bfloat16, device="cuda") for n in shapes}
+            torch.cuda.synchronize()
+
+            def gemm_layer():
+                for layer in mats:
+                    for group in GROUPS:
+                        for n in group:
+                            S.project(dev, layer[n], xs[group[0]], mm, ys[n])
+            with torch.cuda.stream(stream):
+                for _ in range(2):
+                    gemm_layer()
+            reps = 3
+            t = timed(gemm_layer, reps) / reps / layers
+            flops = 2.0 * mm * LAYER_WEIGHTS
+            per_mat = {}
+            for n in ("gate", "down"):
+                def one(n=n):
+                    for layer in mats:
+                        S.project(dev, layer[n], xs[[g[0] for g in GROUPS if n in g][0]], mm, ys[n])
+                tt = timed(one, reps) / reps / layers
+                per_mat[n] = round(2.0 * mm * shapes[n][0] * shapes[n][1] / (tt * 1e-3) / 1e12, 1)
+            prefill[f"m{mm}"] = {"tflops": round(flops / (t * 1e-3) / 1e12, 1), "ms_per_layer": round(t, 4),
+                                 "frac_of_measured_bf16_peak": round(flops / (t * 1e-3) / 1e12 / P["bf16_tflops"], 4),
+                                 "per_matrix_tflops": per_mat}
+        out["prefill_gemm"] = prefill
+
         # End to end through the C ABI with HOST buffers: every step uploads the step's activations
         # from pinned memory, replays the step, downloads every output and waits.
         xh, yh = x_pinned.numpy(), y_pinned.numpy()

@@ -127,6 +127,11 @@ extern "C" int fq_device_create(int ordinal, fq_device **out) {
     if ((e = cudaMalloc(&dev->xprep, dev->xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
     if ((e = cudaMalloc(&dev->staging_dev, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "device staging");
     if ((e = cudaMallocHost(&dev->staging_host, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "pinned staging");
+    void *status = nullptr;
+    if ((e = cudaHostAlloc(&status, 64, cudaHostAllocMapped)) != cudaSuccess) return bail(e, "status word");
+    dev->status_host = (volatile int *)status;
+    *dev->status_host = 0;
+    if ((e = cudaHostGetDevicePointer((void **)&dev->status_dev, status, 0)) != cudaSuccess) return bail(e, "status word mapping");
     *out = dev;
     return FQ_OK;
 }
@@ -139,6 +144,7 @@ extern "C" int fq_device_destroy(fq_device *dev) {
     if (dev->xprep) cudaFree(dev->xprep);
     if (dev->staging_dev) cudaFree(dev->staging_dev);
     if (dev->staging_host) cudaFreeHost(dev->staging_host);
+    if (dev->status_host) cudaFreeHost((void *)dev->status_host);
     if (dev->own_stream) cudaStreamDestroy(dev->own_stream);
     delete dev;
     return FQ_OK;
@@ -166,6 +172,12 @@ extern "C" int fq_synchronize(fq_device *dev) {
     if (e != cudaSuccess) {
         dev->failed = true;
         return fq_fail(dev, FQ_ERR_SYNC, "stream failed: %s", cudaGetErrorString(e));
+    }
+    if (dev->status_host && *dev->status_host != 0) {
+        const int st = *dev->status_host;
+        *dev->status_host = 0;
+        dev->failed = true;
+        return fq_fail(dev, st == FQ_ERR_TIMEOUT ? FQ_ERR_TIMEOUT : FQ_ERR_SYNC, "a kernel gave up a bounded wait (status %d)", st);
     }
     if (dev->failed) return fq_fail(dev, FQ_ERR_SYNC, "device handle holds a failed submission");
     return FQ_OK;

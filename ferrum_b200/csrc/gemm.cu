@@ -1,4 +1,369 @@
-// Prefill dequant-GEMM on tcgen05 (BF16 in, BF16 out).
+// Prefill dequant-GEMM on the 5th-generation tensor cores (BF16 activations in, BF16 out, fp32
+// accumulation in tensor memory).  The work of the reference's `q4_k_gemm_mpp*`, `q6_k_gemm_mpp`,
+// `q8_0_gemm_mpp*` (src/metal/shaders/project_mpp.metal:505-729, 1133-1212, 89-230) and, for shape,
+// of `h_mm_*` (src/metal/shaders/hybrid.metal:1411-1469).
+//
+//   Y[m][n] = sum_k X[m][k] * bf16(W[n][k])        X, Y bf16; W decoded exactly, then rounded to bf16
+//
+// One block owns 128 weight rows x 256 activation rows and walks K in steps of 64:
+//
+//   warp 0       one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the
+//                64 x 256 activation tile of each stage; the warp also owns the tensor-memory allocation;
+//   warp 1       one thread issues tcgen05.mma (M = 128 weight rows, N = 256 activation rows, K = 16,
+//                four per stage) with both operands in shared memory and the accumulator in tensor
+//                memory, and commits each stage back to the producers;
+//   warps 2..9   decode the packed blocks with the exact per-value formula (blocks.cuh), round to
+//                bf16 (RNE) and write the 128 x 64 weight tile in the same K-major 128-byte-swizzled
+//                layout the TMA produces; afterwards warps 2..5 read the accumulator back
+//                (tcgen05.ld, 32 lanes x 32 columns per load), round to bf16 and store Y.
+//
+// Weights sit on the MMA's M side and tokens on its N side, so a weight tile is decoded once per 256
+// tokens.  Every mbarrier wait is bounded: a wait that gives up records FQ_ERR_TIMEOUT in the status
+// word, the block stops issuing work, waits (bounded) for what it already issued, frees its tensor
+// memory and returns.
+#include <cuda.h>
+
+#include "blocks.cuh"
 #include "internal.h"
 
-int fq_launch_gemm_tc(fq_device *, const ProjectArgs &) { return FQ_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int BM = 128;      // weight rows per block (MMA M)
+constexpr int BN = 256;      // activation rows per block (MMA N)
+constexpr int BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int PRODUCER_WARPS = 8;
+constexpr int THREADS = (2 + PRODUCER_WARPS) * 32;
+constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+struct __align__(1024) Smem {
+    uint8_t a[STAGES][A_BYTES];
+    uint8_t b[STAGES][B_BYTES];
+    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], accum;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Bounded wait.  On giving up: record the timeout, raise the block's abort flag, report failure.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, Smem *sm, int *status) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try(bar, parity)) return true;
+        if (*(volatile uint32_t *)&sm->abort_flag) return false;
+    }
+    *(volatile int *)status = (int)FQ_ERR_TIMEOUT;
+    atomicExch(&sm->abort_flag, 1u);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D = F32, A = B = BF16, both K-major, N = 256, M = 128.
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); // .x = lo (low 16 bits), RNE
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// 32 consecutive k values of weight row `row` (a k-block of 64 is two of these: part 0 and 1), decoded
+// exactly and rounded to bf16, two per register.
+template <int FMT>
+__device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uint32_t kb, int part, uint32_t (&out)[16]) {
+    if constexpr (FMT == FQ_Q4_K) {
+        // k-block kb = chunk c of superblock b: part 0 = low nibbles (sub-block 2c), part 1 = high nibbles.
+        const uint32_t b = kb >> 2, c = kb & 3;
+        const uint8_t *blk = rowp + (size_t)b * 144;
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c), q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
+        // `get_scale_min_k4` on the three scale words (hdr.y = scales[0..3], .z = [4..7], .w = [8..11]).
+        const uint32_t j = 2 * c + part, sh = 8 * (j & 3);
+        uint32_t sc, mn;
+        if (j < 4) {
+            sc = (hdr.y >> sh) & 63u;
+            mn = (hdr.z >> sh) & 63u;
+        } else {
+            sc = ((hdr.w >> sh) & 0xFu) | ((((hdr.y >> sh) >> 6) & 3u) << 4);
+            mn = (((hdr.w >> sh) >> 4) & 0xFu) | ((((hdr.z >> sh) >> 6) & 3u) << 4);
+        }
+        const float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu)), dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
+        const float ds = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t v = part ? (w[i] >> 4) : w[i];
+            const float f0 = __fsub_rn(__fmul_rn(ds, (float)(v & 0xFu)), dm), f1 = __fsub_rn(__fmul_rn(ds, (float)((v >> 8) & 0xFu)), dm);
+            const float f2 = __fsub_rn(__fmul_rn(ds, (float)((v >> 16) & 0xFu)), dm), f3 = __fsub_rn(__fmul_rn(ds, (float)((v >> 24) & 0xFu)), dm);
+            out[2 * i] = pack_bf16(f0, f1);
+            out[2 * i + 1] = pack_bf16(f2, f3);
+        }
+    } else if constexpr (FMT == FQ_Q6_K) {
+        // k-block kb of superblock b: half n = (kb % 4) / 2, 32-groups i = 2 h and 2 h + 1 with h = kb % 2;
+        // part selects the group.  Device layout of blocks.cuh.
+        const uint32_t b = kb >> 2, n = (kb >> 1) & 1, h = kb & 1, i = 2 * h + part;
+        const uint8_t *ql = rowp + (size_t)b * 128 + 64 * n + 32 * (i & 1);
+        const uint8_t *qh = rowp + (size_t)nblk * 128 + (size_t)b * 64 + 32 * n;
+        const int8_t *sc = reinterpret_cast<const int8_t *>(rowp + (size_t)nblk * 192 + (size_t)b * 16 + 8 * n + 2 * i);
+        const float d = load_f16(rowp + (size_t)nblk * 208 + (size_t)b * 2);
+        const float ds0 = __fmul_rn(d, (float)sc[0]), ds1 = __fmul_rn(d, (float)sc[1]);
+        const uint4 l0 = *reinterpret_cast<const uint4 *>(ql), l1 = *reinterpret_cast<const uint4 *>(ql + 16);
+        const uint4 h0 = *reinterpret_cast<const uint4 *>(qh), h1 = *reinterpret_cast<const uint4 *>(qh + 16);
+        const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w}, hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t lo4 = (i < 2) ? lw[j] : (lw[j] >> 4);
+            const uint32_t hi2 = hw[j] >> (2 * i);
+            const float ds = j < 4 ? ds0 : ds1;
+            float f[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const uint32_t q = ((lo4 >> (8 * e)) & 0xFu) | (((hi2 >> (8 * e)) & 3u) << 4);
+                f[e] = __fmul_rn(ds, (float)q - 32.0f);
+            }
+            out[2 * j] = pack_bf16(f[0], f[1]);
+            out[2 * j + 1] = pack_bf16(f[2], f[3]);
+        }
+    } else {
+        // Q8_0: 34-byte blocks, 2-byte aligned; k-block kb = blocks 2 kb and 2 kb + 1.
+        const uint8_t *blk = rowp + (size_t)(2 * kb + part) * 34;
+        const float d = load_f16(blk);
+        const uint16_t *q = reinterpret_cast<const uint16_t *>(blk + 2);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t w0 = q[2 * j], w1 = q[2 * j + 1];
+            const float f0 = __fmul_rn((float)(int)(int8_t)(w0 & 0xFF), d), f1 = __fmul_rn((float)(int)(int8_t)(w0 >> 8), d);
+            const float f2 = __fmul_rn((float)(int)(int8_t)(w1 & 0xFF), d), f3 = __fmul_rn((float)(int)(int8_t)(w1 >> 8), d);
+            out[2 * j] = pack_bf16(f0, f1);
+            out[2 * j + 1] = pack_bf16(f2, f3);
+        }
+    }
+}
+
+// grid (ceil(rows / 128), ceil(m / 256)).  `xmap` describes X as a [m][cols] bf16 tensor, box 64 x 256,
+// 128-byte swizzle.
+template <int FMT>
+__global__ void __launch_bounds__(THREADS, 1)
+k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t pitch,
+          __nv_bfloat16 *__restrict__ y, uint32_t m, uint32_t b_bytes, int *status) {
+    extern __shared__ uint8_t smem_raw[];
+    Smem *sm = reinterpret_cast<Smem *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
+    const uint32_t k_iters = cols / BK;
+    constexpr uint32_t nblk_div = FMT == FQ_Q8_0 ? 32 : 256;
+    const uint32_t nblk = cols / nblk_div;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&sm->full_a[s], PRODUCER_WARPS * 32);
+            mbar_init(&sm->full_b[s], 1);
+            mbar_init(&sm->empty[s], 1);
+        }
+        mbar_init(&sm->accum, 1);
+        sm->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&xmap) : "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *(volatile uint32_t *)&sm->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t issued = 0;
+            for (uint32_t it = 0; it < k_iters; it++) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&sm->empty[s], ((it / STAGES) & 1) ^ 1, sm, status)) break;
+                mbar_expect_tx(&sm->full_b[s], b_bytes);
+                tma_load_2d(sm->b[s], &xmap, (int)(it * BK), (int)m0, &sm->full_b[s]);
+                issued = it + 1;
+            }
+            // On an abort the copies already issued still land: wait for them (bounded) before the
+            // block's shared memory goes away.
+            if (*(volatile uint32_t *)&sm->abort_flag) {
+                for (uint32_t it = issued > STAGES ? issued - STAGES : 0; it < issued; it++) {
+                    const int s = it % STAGES;
+                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(&sm->full_b[s], (it / STAGES) & 1); i++) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            for (uint32_t it = 0; it < k_iters && ok; it++) {
+                const int s = it % STAGES;
+                const uint32_t parity = (it / STAGES) & 1;
+                ok = mbar_wait(&sm->full_a[s], parity, sm, status) && mbar_wait(&sm->full_b[s], parity, sm, status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t adesc = umma_desc(smem_u32(sm->a[s])), bdesc = umma_desc(smem_u32(sm->b[s]));
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++) // 16 bf16 = 32 bytes = 2 descriptor units along K
+                    umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, (it | k) != 0);
+                umma_commit(&sm->empty[s]); // the stage's shared memory is free once these MMAs have read it
+            }
+            umma_commit(&sm->accum); // arrives when every MMA issued so far has completed
+        }
+    } else {
+        // Producers: thread p owns weight row p / 2 of the tile and k part p % 2 of each stage.
+        const int p = threadIdx.x - 64, r = p >> 1, part = p & 1;
+        const bool live = n0 + r < rows;
+        const uint8_t *rowp = w + (size_t)min(n0 + r, rows - 1) * pitch;
+        for (uint32_t it = 0; it < k_iters; it++) {
+            const int s = it % STAGES;
+            uint32_t v[16];
+            decode32<FMT>(rowp, nblk, it, part, v); // global loads and arithmetic overlap the wait below
+            if (!live) {
+#pragma unroll
+                for (int i = 0; i < 16; i++) v[i] = 0u;
+            }
+            if (!mbar_wait(&sm->empty[s], ((it / STAGES) & 1) ^ 1, sm, status)) break;
+            uint8_t *tile_row = sm->a[s] + r * 128;
+#pragma unroll
+            for (int c = 0; c < 4; c++) { // 16-byte chunk 4 part + c of the row, at its swizzled place
+                const int chunk = (4 * part + c) ^ (r & 7);
+                *reinterpret_cast<uint4 *>(tile_row + 16 * chunk) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> tensor-core reads
+            mbar_arrive(&sm->full_a[s]);
+        }
+        // Epilogue: warps 2..5 cover the four 32-lane quarters of tensor memory (quarter = warp % 4).
+        if (warp < 6) {
+            const int quarter = warp & 3;
+            const bool ok = mbar_wait(&sm->accum, 0, sm, status);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t row = n0 + 32 * quarter + lane;
+            if (ok) {
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t acc[32];
+                    tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + c0, acc);
+                    if (row < rows) {
+#pragma unroll
+                        for (int c = 0; c < 32; c++) {
+                            const uint32_t tok = m0 + c0 + c;
+                            if (tok < m) y[(size_t)tok * rows + row] = __float2bfloat16_rn(__uint_as_float(acc[c]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        // Outstanding MMAs must have finished before the accumulator columns are released.
+        if (lane == 0 && *(volatile uint32_t *)&sm->abort_flag)
+            for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(&sm->accum, 0); i++) {}
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiled)p;
+    }();
+    return fn;
+}
+
+template <int FMT> int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, int *status) {
+    const size_t smem = sizeof(Smem) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fq_check_cuda(dev, e, "gemm shared memory");
+        configured = true;
+    }
+    dim3 grid((a.rows + BM - 1) / BM, (a.m + BN - 1) / BN);
+    k_gemm_tc<FMT><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (__nv_bfloat16 *)a.y, a.m, b_bytes, status);
+    return FQ_OK;
+}
+
+} // namespace
+
+int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
+    if (a.x_dtype != FQ_BF16 || a.y_dtype != FQ_BF16 || a.cols % BK || a.ids || a.offsets) return FQ_ERR_UNSUPPORTED;
+    if (a.format != FQ_Q4_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
+    if (a.format == FQ_Q4_K && (a.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
+    if (a.m < 32) return FQ_ERR_UNSUPPORTED; // narrow inputs: the fp32 kernels serve them
+    EncodeTiled encode = encode_fn();
+    if (!encode) return FQ_ERR_UNSUPPORTED;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {a.cols, a.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.cols * 2};
+    // A box may not be taller than the tensor; rows past the end of a later tile are zero-filled.
+    const uint32_t box_rows = a.m < (uint32_t)BN ? a.m : (uint32_t)BN;
+    const cuuint32_t box[2] = {BK, box_rows}, elem[2] = {1, 1};
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.x), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fq_fail(dev, FQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    int rc = a.format == FQ_Q4_K ? launch<FQ_Q4_K>(dev, a, map, box_rows * BK * 2, dev->status_dev)
+             : a.format == FQ_Q6_K ? launch<FQ_Q6_K>(dev, a, map, box_rows * BK * 2, dev->status_dev)
+                                   : launch<FQ_Q8_0>(dev, a, map, box_rows * BK * 2, dev->status_dev);
+    if (rc != FQ_OK) return rc;
+    return fq_end_enqueue(dev, "gemm_tc", 1);
+}

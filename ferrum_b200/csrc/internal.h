@@ -36,6 +36,9 @@ struct fq_device {
     uint32_t xprep_turn = 0;      // successive projections alternate between the two halves of xprep
     void *staging_dev = nullptr;  // device side of the host-buffer entry points
     void *staging_host = nullptr; // pinned host side
+    // One word in mapped pinned host memory that kernels set when a bounded wait gives up.
+    volatile int *status_host = nullptr;
+    int *status_dev = nullptr;
 };
 
 struct fq_graph {

@@ -532,3 +532,62 @@ def test_captured_graph_replays_a_layer(device):
     assert d2.counters().dispatches - before == 2 * 5  # (prep + gemv) x 2 + glu, twice
     graph.close()
     d2.close()
+
+
+# ------------------------------------------------------------------ prefill dequant-GEMM (tensor memory path)
+
+def run_project_bf16(device, fmt, packed, rows, cols, xb, m):
+    s = S()
+    w = s.Matrix.from_packed(device, rows, cols, 1, fmt, packed)
+    xt = dev_f32(xb).to(torch.bfloat16).contiguous()
+    y = torch.full((m * rows,), float("nan"), dtype=torch.bfloat16, device="cuda")
+    s.project(device, w, xt, m, y)
+    device.synchronize()
+    return y
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("m,cols,rows", [(200, 512, 100), (35, 512, 65), (1025, 256, 65), (512, 1024, 384), (300, 2048, 129)])
+def test_bf16_gemm_matches_the_cpu_dequant(device, fmt, m, cols, rows):
+    """bf16 x bf16-rounded weights, fp32 accumulate, bf16 out (src/ops/transformer.rs:3116-3160,
+    src/diffusion/tests.rs:716-760): token and output counts that are not whole tiles."""
+    packed = blocks_for(fmt, rows, cols, "random", seed=m)
+    xb = ref.round_bf16(np.random.default_rng(m + 1).standard_normal((m, cols)).astype(np.float32))
+    dense_b = ref.round_bf16(ref.dequant(fmt, packed)).reshape(rows, cols)
+    want = xb.astype(np.float64) @ dense_b.astype(np.float64).T
+    got = run_project_bf16(device, fmt, packed, rows, cols, xb, m).float().cpu().numpy().reshape(m, rows)
+    assert np.abs(want).max() > 0.1
+    err = np.abs(got - want).max() / np.abs(want).max()
+    assert err <= TOL_BF16, err
+    # fp32 accumulation of bf16 operands leaves only the final bf16 rounding: far inside the bar
+    assert err <= 6e-3, err
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_bf16_gemm_weight_tiles_are_bit_exact(device, fmt):
+    """X = identity makes Y the weight tile itself: it must equal bf16_rne(exact fp32 decode) bit for bit."""
+    rows, cols = 200, 512
+    packed = blocks_for(fmt, rows, cols, "random", seed=77)
+    eye = np.eye(cols, dtype=np.float32)
+    y = run_project_bf16(device, fmt, packed, rows, cols, eye, cols)
+    got = y.view(torch.int16).cpu().numpy().view(np.uint16).reshape(cols, rows)
+    want = ref.to_bf16(ref.dequant(fmt, packed)).reshape(rows, cols).T
+    # An accumulated sum cannot keep the sign of a zero weight (-0 + 0 = +0); everything else is bit-equal.
+    zero = (want & 0x7FFF) == 0
+    assert np.array_equal(got[~zero], want[~zero]) and not (got[zero] & 0x7FFF).any()
+
+
+@pytest.mark.parametrize("fmt,rows,cols", [(ref.Q4_K, 6144, 5120), (ref.Q6_K, 5120, 17408)])
+def test_full_size_prefill_rows(device, fmt, rows, cols):
+    """Config 2 shapes at M = 512: a random subset of output rows against the oracle."""
+    m = 512
+    packed = ref.random_matrix(fmt, rows, cols, seed=11)
+    xb = ref.round_bf16(np.random.default_rng(12).standard_normal((m, cols)).astype(np.float32))
+    got = run_project_bf16(device, fmt, packed, rows, cols, xb, m).float().cpu().numpy().reshape(m, rows)
+    rb = ref.row_bytes(fmt, cols)
+    pick = np.sort(np.random.default_rng(5).choice(rows, 16, replace=False))
+    sub = np.concatenate([packed[r * rb:(r + 1) * rb] for r in pick])
+    dense_b = ref.round_bf16(ref.dequant(fmt, sub)).reshape(len(pick), cols)
+    want = xb.astype(np.float64) @ dense_b.astype(np.float64).T
+    assert np.abs(got[:, pick] - want).max() / np.abs(got).max() <= TOL_BF16
+    assert np.isfinite(got).all()
