@@ -28,6 +28,8 @@
 // shared memory in a fixed order, so results are deterministic and a row-sharded matrix gives the
 // same bits as the whole one.
 #include <algorithm>
+#include <cstdarg>
+#include <cstdio>
 #include <cstdlib>
 #include <type_traits>
 
@@ -536,4 +538,111 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     }
     if (int rc = fq_check_cuda(dev, e, "gemv launch")) return rc;
     return fq_end_enqueue(dev, "gemv_i8", 2);
+}
+
+// ---------------------------------------------------------------- allocation-free entry point
+//
+// `fq_gemv_q4k_static` is for callers that must not allocate device memory at all: code running
+// inside a memory pool that has already handed every byte to the model, a plugin loaded into a
+// process whose allocator is owned by someone else, or a call site between the begin and end of a
+// phase in which cudaMalloc would serialise the device.  `fq_device_create` and `fq_matrix_create`
+// both allocate, so this entry point takes neither handle: the caller passes device pointers to the
+// packed Q4_K rows (GGUF bytes, 16-byte aligned), to the activations and to the output, plus a stream.
+// The prepared activations, which the handle-based path keeps in scratch it allocated at creation,
+// live here in a fixed array that is part of the library image.
+constexpr size_t STATIC_SCRATCH_BYTES = FQ_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) uint8_t g_static_scratch[STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// Device address of g_static_scratch per device ordinal.  In host code the array's name is only a
+// stand-in for the symbol; the address a kernel can use comes from cudaGetSymbolAddress, taken once
+// per device with that device current.
+constexpr int MAX_DEVICES = 64;
+uint8_t *g_static_ptr[MAX_DEVICES];
+int g_static_sms[MAX_DEVICES];
+
+int static_fail(char *err, size_t err_len, int status, const char *fmt, ...) {
+    if (err && err_len) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(err, err_len, fmt, ap);
+        va_end(ap);
+    }
+    return status;
+}
+
+template <int MT>
+cudaError_t launch_static(const uint8_t *w, uint32_t rows, uint32_t pitch, float *y, const uint8_t *prep, const PrepI8 &L,
+                          int sm_count, cudaStream_t stream) {
+    GemvTargets T{};
+    T.count = 1;
+    T.w[0] = w;
+    T.y[0] = y;
+    T.rows[0] = rows;
+    const uint32_t blocks = (rows + 15) / 16;
+    T.tile_end[0] = blocks;
+    // Same choice of warps per block as the handle-based path.
+    const uint32_t nblk = L.nblk, want = (uint32_t)sm_count * 32u;
+    const uint32_t reg_cap = MT >= 3 ? 8u : MT == 2 ? 12u : (uint32_t)MAX_WARPS;
+    const uint32_t max_k = std::max(1u, std::min(reg_cap, nblk / 2));
+    const uint32_t need = std::min(max_k, std::max(1u, (want + blocks - 1) / blocks));
+    uint32_t warps = need;
+    uint64_t best = ~0ull;
+    for (uint32_t k = need; k <= max_k; k++) {
+        const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need);
+        if (waste < best) { best = waste; warps = k; }
+    }
+    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u);
+    return cudaPeekAtLastError();
+}
+
+} // namespace
+
+extern "C" int fq_gemv_q4k_static(const void *w_packed, uint64_t rows, uint64_t cols, const float *x, uint32_t m, float *y,
+                                  void *cuda_stream, char *err, size_t err_len) {
+    if (!w_packed || !x || !y) return static_fail(err, err_len, FQ_ERR_RANGE, "null binding");
+    if (((uintptr_t)w_packed | (uintptr_t)x | (uintptr_t)y) & 15u)
+        return static_fail(err, err_len, FQ_ERR_RANGE, "bindings must be 16-byte aligned");
+    if (rows == 0 || rows > 0x7fffffffull || cols == 0 || cols % 256 || cols > FQ_MAX_COLS)
+        return static_fail(err, err_len, FQ_ERR_SHAPE, "Q4_K geometry %llu x %llu (cols must be a multiple of 256)",
+                           (unsigned long long)rows, (unsigned long long)cols);
+    if (m == 0 || m > (uint32_t)MAX_TOKENS)
+        return static_fail(err, err_len, FQ_ERR_SHAPE, "%u activation rows; this entry point serves 1..%d", m, MAX_TOKENS);
+    const PrepI8 L = prep_i8_layout((uint32_t)cols);
+    if ((size_t)m * L.token_bytes > STATIC_SCRATCH_BYTES)
+        return static_fail(err, err_len, FQ_ERR_SHAPE,
+                           "%u rows of %llu activations need %zu bytes of prepared activations; the fixed scratch holds %zu",
+                           m, (unsigned long long)cols, (size_t)m * L.token_bytes, STATIC_SCRATCH_BYTES);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+        return static_fail(err, err_len, FQ_ERR_DEVICE, "no current CUDA device: %s", cudaGetErrorString(e));
+    if (!g_static_ptr[dev]) {
+        // First call on this device: resolve the array's device address (and the SM count).
+        uint8_t *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return static_fail(err, err_len, FQ_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || sms <= 0) return static_fail(err, err_len, FQ_ERR_CUDA, "SM count: %s", cudaGetErrorString(e));
+        g_static_sms[dev] = sms;
+        g_static_ptr[dev] = p;
+    }
+    uint8_t *prep = g_static_ptr[dev];
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const uint32_t warps = m * L.nblk;
+    // Every byte the GEMV reads from the scratch is rewritten here first, so nothing has to start at zero.
+    k_prep_i8<<<(warps + 3) / 4, 128, 0, stream>>>(x, m, L, prep);
+    if ((e = cudaPeekAtLastError()) != cudaSuccess)
+        return static_fail(err, err_len, FQ_ERR_CUDA, "activation preparation launch: %s", cudaGetErrorString(e));
+    const uint32_t pitch = (uint32_t)(cols / 256 * 144);
+    const uint8_t *w = (const uint8_t *)w_packed;
+    e = m == 1 ? launch_static<1>(w, (uint32_t)rows, pitch, y, prep, L, g_static_sms[dev], stream)
+      : m == 2 ? launch_static<2>(w, (uint32_t)rows, pitch, y, prep, L, g_static_sms[dev], stream)
+      : m == 3 ? launch_static<3>(w, (uint32_t)rows, pitch, y, prep, L, g_static_sms[dev], stream)
+               : launch_static<4>(w, (uint32_t)rows, pitch, y, prep, L, g_static_sms[dev], stream);
+    if (e != cudaSuccess) return static_fail(err, err_len, FQ_ERR_CUDA, "gemv launch: %s", cudaGetErrorString(e));
+    return FQ_OK;
 }

@@ -216,6 +216,31 @@ int fq_project_host(fq_device *dev, const fq_matrix *w, const float *x_host, siz
 int fq_project_many_host(fq_device *dev, const fq_matrix *const *w, size_t count, const float *x_host,
                          size_t m, float *const *y_host);
 
+/* ---- allocation-free decode projection ------------------------------------------------------- */
+
+/* No counterpart in the reference (its backend allocates its buffers at load and has no notion of a
+ * caller that may not).  For callers that cannot allocate device memory at all -- code running after a
+ * memory pool has taken every byte, a plugin inside a process whose allocator belongs to someone else,
+ * a latency-critical section where cudaMalloc would serialise the device -- and so cannot use
+ * `fq_device_create` / `fq_matrix_create`, which both allocate.
+ *
+ *   y[m][rows] = x[m][cols] . W^T,  W = `rows` rows of cols / 256 Q4_K blocks (GGUF bytes), 1 <= m <= 4.
+ *
+ * All pointers are DEVICE pointers, 16-byte aligned, on the current device; the work is enqueued on
+ * `cuda_stream` and is complete when that stream reaches it.  Same kernels and same results as
+ * `fq_project` on a Q4_K matrix.  The prepared activations live in a fixed array inside the library
+ * image (FQ_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the process exits);
+ * m * (about 2.4 * cols) bytes must fit, otherwise the call returns FQ_ERR_SHAPE and says so in `err`.
+ * The call itself uses no cudaMalloc, cudaFree or other allocating routine.  The first call on each
+ * device also looks up the array's device address: make that call before any stream capture.  Every
+ * call on a device shares the one array (each call rewrites all of it that it reads, so nothing is
+ * carried over), hence two calls whose kernels may overlap on the GPU -- different streams, no
+ * ordering -- race; calls on one stream, or ordered by events, are safe.  `err` (may be NULL) receives
+ * a message when the status is not FQ_OK. */
+#define FQ_STATIC_SCRATCH_BYTES (256u << 10)
+int fq_gemv_q4k_static(const void *w_packed, uint64_t rows, uint64_t cols, const float *x, uint32_t m, float *y,
+                       void *cuda_stream, char *err, size_t err_len);
+
 #ifdef __cplusplus
 }
 #endif
