@@ -158,8 +158,12 @@ def run_ours(args):
         mats.append(layer)
     shapes = {name: (rows // world, cols) for name, rows, cols, _ in LAYER}
 
-    def buffers(mm):
-        """One contiguous input buffer (a slice per group) and one output buffer (a slice per matrix)."""
+    comm_box = {}
+
+    def buffers(mm, shared=False):
+        """One contiguous input buffer (a slice per group) and one output buffer (a slice per matrix).  With
+        `shared` (more than one rank) the outputs live in the exchange buffer: per input group a region
+        [world][span], this rank writing slice `rank`, gathered with one peer-push all-gather."""
         xs, ys, xo, yo = {}, {}, 0, 0
         for g in GROUPS:
             xs[g[0]] = (xo, mm * shapes[g[0]][1])
@@ -168,16 +172,31 @@ def run_ours(args):
             ys[name] = (yo, mm * shapes[name][0])
             yo += (mm * shapes[name][0] + 63) // 64 * 64
         X = torch.zeros(xo, dtype=torch.float32, device="cuda")
+        # Outputs of one input group are adjacent: one all-gather per group moves them together.
+        span_of = {g[0]: (ys[g[0]][0], ys[g[-1]][0] + (ys[g[-1]][1] + 63) // 64 * 64) for g in GROUPS}
+        if shared and not args.nccl:
+            comm = S.Comm(dev, rank, world, world * yo * 4)
+            comm_box["comm"] = comm
+            regions, yv = {}, {}
+            for g in GROUPS:
+                lo, hi = span_of[g[0]]
+                region = world * lo * 4
+                regions[g[0]] = (region, (hi - lo) * 4)
+                for n in g:
+                    yv[n] = comm.view(region + rank * (hi - lo) * 4 + (ys[n][0] - lo) * 4, ys[n][1])
+            Y = comm.view(0, world * yo)
+            return X, Y, {k: X[o:o + n] for k, (o, n) in xs.items()}, yv, regions
         Y = torch.zeros(yo, dtype=torch.float32, device="cuda")
-        return X, Y, {k: X[o:o + n] for k, (o, n) in xs.items()}, {k: Y[o:o + n] for k, (o, n) in ys.items()}
+        spans = {k: Y[lo:hi] for k, (lo, hi) in span_of.items()}
+        return X, Y, {k: X[o:o + n] for k, (o, n) in xs.items()}, {k: Y[o:o + n] for k, (o, n) in ys.items()}, spans
 
     rng = np.random.default_rng(1234)
-    X, Y, x_dev, y_dev = buffers(m)
+    X, Y, x_dev, y_dev, y_spans = buffers(m, shared=world > 1)
     x_pinned = torch.from_numpy(rng.standard_normal(X.numel()).astype(np.float32)).pin_memory()
     y_pinned = torch.zeros(Y.numel(), dtype=torch.float32).pin_memory()
     X.copy_(x_pinned)
-    gathered = ({name: torch.zeros(world * y_dev[name].numel(), dtype=torch.float32, device="cuda") for name in shapes}
-                if world > 1 else None)
+    gathered = ({k: torch.zeros(world * v.numel(), dtype=torch.float32, device="cuda") for k, v in y_spans.items()}
+                if world > 1 and args.nccl else None)
     torch.cuda.synchronize()
 
     def enqueue_layers(xd, yd, mm, only=None):
@@ -189,12 +208,14 @@ def run_ours(args):
                 else:
                     for n in names:
                         S.project(dev, layer[n], xd[group[0]], mm, yd[n])
-                if world > 1:
-                    for n in names:
-                        dist.all_gather_into_tensor(gathered[n], yd[n])
+                if world > 1 and only is None:
+                    if args.nccl:
+                        dist.all_gather_into_tensor(gathered[group[0]], y_spans[group[0]])
+                    else:
+                        comm_box["comm"].all_gather(*y_spans[group[0]])
 
     def make_step(xd, yd, mm, only=None):
-        if world > 1 or args.eager:  # NCCL collectives are enqueued by torch: no capture, same stream
+        if (world > 1 and args.nccl) or args.eager:  # NCCL collectives are enqueued by torch: no capture, same stream
             return lambda: enqueue_layers(xd, yd, mm, only)
         dev.capture_begin()
         enqueue_layers(xd, yd, mm, only)
@@ -240,7 +261,9 @@ def run_ours(args):
         "config": {"workload": f"cfg1 dense 27B decode projection set (q,k,v,o,gate,up Q4_K; down Q6_K), M={m}, "
                                f"{layers} distinct layers = {total_bytes} packed bytes per step (inputs larger than L2)",
                    "m": m, "layers": layers, "parallelism": f"tp{world}" if world > 1 else "single",
-                   "submission": "one captured graph per step" if world == 1 else "eager + NCCL all-gather per projection",
+                   "submission": ("one captured graph per step" if world == 1 else
+                                  "eager + one NCCL all-gather per input group" if args.nccl else
+                                  "one captured graph per step incl. one peer-push all-gather per input group (q|k|v, o, gate|up, down)"),
                    "l2": "inputs larger than L2"},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
@@ -277,7 +300,7 @@ def run_ours(args):
         # The other decode / verify widths, same workload.
         extra = {}
         for mm in (4, 8, 16):
-            Xm, Ym, xs, ys = buffers(mm)
+            Xm, Ym, xs, ys, _ = buffers(mm)
             Xm.copy_(torch.from_numpy(rng.standard_normal(Xm.numel()).astype(np.float32)))
             with torch.cuda.stream(stream):
                 fn = make_step(xs, ys, mm)
@@ -425,6 +448,7 @@ def main():
     ap.add_argument("--layers", type=int, default=3, help="distinct layers streamed per step")
     ap.add_argument("--eager", action="store_true", help="enqueue every step call by call instead of replaying a graph")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per matrix instead of one per input group")
+    ap.add_argument("--nccl", action="store_true", help="multi-GPU: gather with NCCL (torch.distributed) instead of the peer-push kernel")
     ap.add_argument("--quick", action="store_true", help="headline and per-group timings only")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -1,0 +1,174 @@
+// All-gather of row-sharded projection outputs over NVLink peer memory (one process per GPU).
+//
+// The reference is single-GPU; this is the exchange step of this build's tensor-parallel sharding.  The
+// payloads are tiny (M = 1: a few KB per rank and projection), so the cost is latency, and a library
+// collective per projection would cost more than the projection.  Each rank owns one "symmetric" buffer
+// (same size and layout on every rank, mapped into every peer through CUDA IPC).  A projection writes its
+// shard straight into its own slice of the gathered region; `fq_comm_all_gather` is then ONE small kernel:
+// block p stores the local shard into peer p's copy of the region (plain peer stores), publishes a sequence
+// number in peer p's flag word (release, system scope), and waits -- bounded -- until peer p's sequence number
+// for the same call site has arrived locally.  When the kernel ends every shard is in local memory, and stream
+// order makes it visible to whatever runs next.  Nothing here uses multicast or TMA; the kernel can be
+// captured into a graph because sequence numbers live in device memory.
+#include <algorithm>
+#include <cstring>
+
+#include "internal.h"
+
+constexpr int FQ_COMM_MAX_WORLD = 8;
+constexpr uint32_t FQ_COMM_SLOTS = 2048;      // distinct call sites before flag words are reused
+constexpr uint32_t COMM_WAIT_LIMIT = 1u << 24;
+
+struct fq_comm {
+    fq_device *dev = nullptr;
+    int rank = 0, world = 1;
+    size_t bytes = 0;       // payload bytes of the symmetric buffer
+    uint8_t *local = nullptr; // payload, then flags[FQ_COMM_SLOTS][FQ_COMM_MAX_WORLD]
+    uint32_t *seq = nullptr;  // local only: last sequence number used per (slot, peer)
+    uint8_t *peer[FQ_COMM_MAX_WORLD] = {};
+    bool opened = false;
+    uint32_t next_slot = 0;
+};
+
+namespace {
+
+struct Peers {
+    uint8_t *base[FQ_COMM_MAX_WORLD];
+};
+
+// grid (world - 1, chunks): block (p, c) copies chunk c of the shard to the p-th other rank; chunk 0's block
+// also does the handshake with that rank.
+__global__ void __launch_bounds__(256)
+k_all_gather_push(const __grid_constant__ Peers peers, int rank, int world, size_t payload_bytes, size_t region_off,
+                  size_t shard_bytes, uint32_t slot, uint32_t *seq, int *status) {
+    // Launched with programmatic stream serialization: let the next kernel stage itself, then wait for the
+    // projection that produced the local shard.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int other = (int)blockIdx.x < rank ? (int)blockIdx.x : (int)blockIdx.x + 1;
+    const size_t mine = region_off + (size_t)rank * shard_bytes;
+    const uint4 *src = reinterpret_cast<const uint4 *>(peers.base[rank] + mine);
+    uint4 *dst = reinterpret_cast<uint4 *>(peers.base[other] + mine);
+    const size_t n16 = shard_bytes / 16;
+    for (size_t i = (size_t)blockIdx.y * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.y * blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+    __syncthreads();
+    // The chunks of one peer are counted in before the flag is raised.
+    __shared__ bool last;
+    uint32_t *done = seq + (size_t)FQ_COMM_SLOTS * FQ_COMM_MAX_WORLD * 2 + (size_t)slot * FQ_COMM_MAX_WORLD + other;
+    if (threadIdx.x == 0) last = atomicAdd(done, 1u) + 1u == gridDim.y;
+    __syncthreads();
+    if (!last || threadIdx.x != 0) return;
+    *done = 0;
+    uint32_t *my_seq = seq + (size_t)slot * FQ_COMM_MAX_WORLD + other;
+    const uint32_t expect = *my_seq + 1u;
+    *my_seq = expect;
+    __threadfence_system();
+    // flags[slot][sender] on the receiving rank
+    uint32_t *remote_flag = reinterpret_cast<uint32_t *>(peers.base[other] + payload_bytes) + (size_t)slot * FQ_COMM_MAX_WORLD + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote_flag), "r"(expect) : "memory");
+    const uint32_t *local_flag = reinterpret_cast<const uint32_t *>(peers.base[rank] + payload_bytes) + (size_t)slot * FQ_COMM_MAX_WORLD + other;
+    for (uint32_t i = 0; i < COMM_WAIT_LIMIT; i++) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flag) : "memory");
+        if ((int32_t)(v - expect) >= 0) return;
+        __nanosleep(20);
+    }
+    *(volatile int *)status = (int)FQ_ERR_TIMEOUT; // the peer never arrived: report, do not hang
+}
+
+size_t flag_bytes() { return (size_t)FQ_COMM_SLOTS * FQ_COMM_MAX_WORLD * sizeof(uint32_t); }
+
+} // namespace
+
+extern "C" int fq_comm_create(fq_device *dev, int rank, int world, size_t bytes, fq_comm **out) {
+    if (!dev || !out) return FQ_ERR_PARAM;
+    *out = nullptr;
+    if (world < 1 || world > FQ_COMM_MAX_WORLD || rank < 0 || rank >= world || bytes == 0 || bytes % 256)
+        return fq_fail(dev, FQ_ERR_PARAM, "communicator of rank %d / %d with %zu bytes (a multiple of 256, at most %d ranks)", rank, world, bytes, FQ_COMM_MAX_WORLD);
+    if (int rc = fq_check_cuda(dev, cudaSetDevice(dev->ordinal), "cudaSetDevice")) return rc;
+    fq_comm *c = new fq_comm();
+    c->dev = dev;
+    c->rank = rank;
+    c->world = world;
+    c->bytes = bytes;
+    cudaError_t e = cudaMalloc((void **)&c->local, bytes + flag_bytes());
+    if (e == cudaSuccess) e = cudaMemset(c->local, 0, bytes + flag_bytes());
+    if (e == cudaSuccess) e = cudaMalloc((void **)&c->seq, flag_bytes() * 3);
+    if (e == cudaSuccess) e = cudaMemset(c->seq, 0, flag_bytes() * 3);
+    if (e != cudaSuccess) {
+        if (c->local) cudaFree(c->local);
+        if (c->seq) cudaFree(c->seq);
+        delete c;
+        return fq_check_cuda(dev, e, "symmetric buffer");
+    }
+    c->peer[rank] = c->local;
+    c->opened = world == 1;
+    *out = c;
+    return FQ_OK;
+}
+
+extern "C" int fq_comm_handle(fq_comm *c, void *out64) {
+    if (!c || !out64) return FQ_ERR_PARAM;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    if (int rc = fq_check_cuda(c->dev, cudaIpcGetMemHandle(&h, c->local), "cudaIpcGetMemHandle")) return rc;
+    memcpy(out64, &h, 64);
+    return FQ_OK;
+}
+
+extern "C" int fq_comm_open(fq_comm *c, const void *handles) {
+    if (!c || !handles) return FQ_ERR_PARAM;
+    cudaSetDevice(c->dev->ordinal);
+    for (int r = 0; r < c->world; r++) {
+        if (r == c->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)handles + 64 * r, 64);
+        void *p = nullptr;
+        if (int rc = fq_check_cuda(c->dev, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) return rc;
+        c->peer[r] = (uint8_t *)p;
+    }
+    c->opened = true;
+    return FQ_OK;
+}
+
+extern "C" void *fq_comm_buffer(fq_comm *c) { return c ? c->local : nullptr; }
+
+extern "C" int fq_comm_all_gather(fq_device *dev, fq_comm *c, size_t region_offset, size_t shard_bytes) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!c || c->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "communicator belongs to another device handle");
+    if (!c->opened) return fq_fail(dev, FQ_ERR_PARAM, "communicator peers are not opened");
+    if (shard_bytes == 0 || shard_bytes % 16 || region_offset % 16 || region_offset + shard_bytes * c->world > c->bytes)
+        return fq_fail(dev, FQ_ERR_RANGE, "gather of %zu bytes per rank at offset %zu does not fit %zu bytes", shard_bytes, region_offset, c->bytes);
+    if (c->world == 1) return FQ_OK;
+    Peers peers{};
+    for (int r = 0; r < c->world; r++) peers.base[r] = c->peer[r];
+    const uint32_t slot = c->next_slot;
+    c->next_slot = (c->next_slot + 1) % FQ_COMM_SLOTS;
+    const unsigned chunks = (unsigned)std::min<size_t>(32, std::max<size_t>(1, shard_bytes / (256 * 16 * 4)));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(c->world - 1, chunks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (int rc = fq_check_cuda(dev, cudaLaunchKernelEx(&cfg, k_all_gather_push, peers, c->rank, c->world, c->bytes, region_offset,
+                                                       shard_bytes, slot, c->seq, dev->status_dev), "all-gather launch"))
+        return rc;
+    return fq_end_enqueue(dev, "all_gather", 1);
+}
+
+extern "C" int fq_comm_destroy(fq_comm *c) {
+    if (!c) return FQ_ERR_PARAM;
+    cudaSetDevice(c->dev->ordinal);
+    cudaStreamSynchronize(c->dev->stream);
+    for (int r = 0; r < c->world; r++)
+        if (r != c->rank && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
+    cudaFree(c->local);
+    cudaFree(c->seq);
+    delete c;
+    return FQ_OK;
+}

@@ -152,6 +152,50 @@ class Device:
             pass
 
 
+class Comm:
+    """Tensor-parallel exchange over NVLink peer memory: this rank's symmetric buffer plus every peer's,
+    mapped through CUDA IPC.  The 64-byte handles travel through ``torch.distributed`` (plumbing only)."""
+
+    def __init__(self, device: Device, rank: int, world: int, nbytes: int, group=None):
+        import torch.distributed as dist
+        self.device, self.rank, self.world = device, rank, world
+        self.nbytes = (nbytes + 255) // 256 * 256
+        h = C.c_void_p()
+        device.check(device._L.fq_comm_create(device.handle, rank, world, self.nbytes, C.byref(h)))
+        self.handle = h
+        if world > 1:
+            mine = (C.c_ubyte * 64)()
+            device.check(device._L.fq_comm_handle(h, mine))
+            every = [None] * world
+            dist.all_gather_object(every, bytes(mine), group=group)  # works on gloo and nccl groups alike
+            raw = b"".join(every)
+            device.check(device._L.fq_comm_open(h, raw))
+            dist.barrier(group=group)
+        self.base = int(device._L.fq_comm_buffer(h))
+
+    def view(self, offset_bytes: int, numel: int, dtype=torch.float32) -> torch.Tensor:
+        """A torch view of ``numel`` elements of the local buffer (no copy)."""
+        item = torch.empty((), dtype=dtype).element_size()
+        assert offset_bytes % 16 == 0 and offset_bytes + numel * item <= self.nbytes
+
+        class _Ptr:
+            pass
+        holder = _Ptr()
+        holder.__cuda_array_interface__ = {"shape": (numel,), "typestr": {4: "<f4", 2: "<u2", 1: "|u1"}[item],
+                                           "data": (self.base + offset_bytes, False), "version": 2}
+        t = torch.as_tensor(holder, device=self.device.torch_device)
+        return t.view(dtype) if t.dtype != dtype else t
+
+    def all_gather(self, offset_bytes: int, shard_bytes: int) -> None:
+        """Rank r's slice is ``[offset + r * shard, + shard)``; afterwards (in stream order) all are local."""
+        self.device.check(self.device._L.fq_comm_all_gather(self.device.handle, self.handle, offset_bytes, shard_bytes))
+
+    def close(self) -> None:
+        if self.handle and self.device.handle:
+            self.device._L.fq_comm_destroy(self.handle)
+        self.handle = None
+
+
 class Graph:
     """A recorded batch of enqueues (the counterpart of one command epoch of the reference)."""
 

@@ -216,6 +216,28 @@ int fq_project_host(fq_device *dev, const fq_matrix *w, const float *x_host, siz
 int fq_project_many_host(fq_device *dev, const fq_matrix *const *w, size_t count, const float *x_host,
                          size_t m, float *const *y_host);
 
+/* ---- tensor-parallel exchange (no counterpart in the single-GPU reference) -------------------- */
+
+/* Row-sharded projections: rank r holds rows [r N / g, (r + 1) N / g) of every matrix and computes its
+ * slice of the output; the slices are gathered over NVLink peer memory.  One process per GPU.
+ *   fq_comm_create   allocates this rank's symmetric buffer (`bytes`, a multiple of 256) and its flag words;
+ *   fq_comm_handle   writes the 64-byte CUDA IPC handle of that buffer, to be exchanged out of band
+ *                    (e.g. one torch.distributed all_gather of 64 bytes);
+ *   fq_comm_open     maps every peer's buffer from the `world` x 64 handle bytes, ordered by rank;
+ *   fq_comm_buffer   the local buffer: projections write their outputs into it;
+ *   fq_comm_all_gather  for the region [offset, offset + world * shard_bytes): this rank's slice
+ *                    [offset + rank * shard_bytes, + shard_bytes) must have been written by work enqueued
+ *                    before the call; after it (in stream order) the region holds every rank's slice.  All
+ *                    ranks must enqueue the same sequence of gathers.  A peer that never arrives makes the
+ *                    kernel give up after a bounded wait; `fq_synchronize` then returns FQ_ERR_TIMEOUT. */
+typedef struct fq_comm fq_comm;
+int fq_comm_create(fq_device *dev, int rank, int world, size_t bytes, fq_comm **out);
+int fq_comm_handle(fq_comm *comm, void *out64);
+int fq_comm_open(fq_comm *comm, const void *handles);
+void *fq_comm_buffer(fq_comm *comm);
+int fq_comm_all_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size_t shard_bytes);
+int fq_comm_destroy(fq_comm *comm);
+
 /* ---- allocation-free decode projection ------------------------------------------------------- */
 
 /* No counterpart in the reference (its backend allocates its buffers at load and has no notion of a
