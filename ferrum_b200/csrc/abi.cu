@@ -579,6 +579,10 @@ extern "C" int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *
     a.slots = slots;
     a.groups = (uint32_t)groups;
     a.max_rows = (uint32_t)max_rows;
+    if (!dev->exact) {
+        int rc = fq_launch_gemm_tc_grouped(dev, a, (uint32_t)(x_elems / w->cols));
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
     if (int rc = fq_launch_project_grouped_exact(dev, a)) return rc;
     return fq_end_enqueue(dev, "project_mm_id", 1);
 }

@@ -29,18 +29,17 @@
 namespace {
 
 constexpr int BM = 128;      // weight rows per block (MMA M)
-constexpr int BN = 256;      // activation rows per block (MMA N)
+// Activation rows per block (MMA N): 256 for dense prefill, 64 for expert groups (about 32 rows each).
 constexpr int BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int STAGES = 4;
 constexpr int PRODUCER_WARPS = 8;
 constexpr int THREADS = (2 + PRODUCER_WARPS) * 32;
-constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-struct __align__(1024) Smem {
+template <int BN> struct __align__(1024) Smem {
     uint8_t a[STAGES][A_BYTES];
-    uint8_t b[STAGES][B_BYTES];
+    uint8_t b[STAGES][BN * BK * 2];
     uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], accum;
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -66,7 +65,7 @@ __device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  On giving up: record the timeout, raise the block's abort flag, report failure.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, Smem *sm, int *status) {
+template <class SM> __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SM *sm, int *status) {
     for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
         if (mbar_try(bar, parity)) return true;
         if (*(volatile uint32_t *)&sm->abort_flag) return false;
@@ -87,12 +86,14 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
 }
-// Instruction descriptor, kind::f16: D = F32, A = B = BF16, both K-major, N = 256, M = 128.
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// Instruction descriptor, kind::f16: D = F32, A = B = BF16, both K-major, N = bn, M = 128.
+constexpr uint32_t idesc_for(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
@@ -188,16 +189,35 @@ __device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uin
     }
 }
 
-// grid (ceil(rows / 128), ceil(m / 256)).  `xmap` describes X as a [m][cols] bf16 tensor, box 64 x 256,
-// 128-byte swizzle.
-template <int FMT>
+__device__ __forceinline__ void store_out(float *p, float v) { *p = v; }
+__device__ __forceinline__ void store_out(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+// grid (ceil(rows / 128), ceil(m / BN)[, groups]).  `xmap` describes X as a [m][cols] bf16 tensor, box
+// 64 x BN, 128-byte swizzle.  GROUPED (`h_mm_id*`, src/metal/shaders/hybrid.metal:2430-2523): block z
+// serves activation rows offsets[z] .. offsets[z+1] with the expert stored at slots[z] (or z); a tile that
+// runs past its group reads the next group's rows and simply does not store them.
+template <int FMT, int BN, typename YT, bool GROUPED>
 __global__ void __launch_bounds__(THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t pitch,
-          __nv_bfloat16 *__restrict__ y, uint32_t m, uint32_t b_bytes, int *status) {
+          YT *__restrict__ y, uint32_t m, uint32_t b_bytes, const uint32_t *__restrict__ offsets,
+          const uint32_t *__restrict__ slots, uint32_t experts, int *status) {
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t IDESC = idesc_for(BN);
     extern __shared__ uint8_t smem_raw[];
-    Smem *sm = reinterpret_cast<Smem *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    using SM = Smem<BN>;
+    SM *sm = reinterpret_cast<SM *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
+    uint32_t m0 = blockIdx.y * BN, m_end = m;
+    if (GROUPED) {
+        const uint32_t z = blockIdx.z, first = offsets[z], count = offsets[z + 1] - first;
+        if (blockIdx.y * BN >= count) return; // uniform for the block: nothing was set up yet
+        const uint32_t e = slots ? slots[z] : z;
+        if (e >= experts) return;
+        w += (size_t)e * rows * pitch;
+        m0 = first + blockIdx.y * BN;
+        m_end = first + count;
+    }
+    const uint32_t n0 = blockIdx.x * BM;
     const uint32_t k_iters = cols / BK;
     constexpr uint32_t nblk_div = FMT == FQ_Q8_0 ? 32 : 256;
     const uint32_t nblk = cols / nblk_div;
@@ -254,7 +274,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
                 const uint64_t adesc = umma_desc(smem_u32(sm->a[s])), bdesc = umma_desc(smem_u32(sm->b[s]));
 #pragma unroll
                 for (int k = 0; k < BK / 16; k++) // 16 bf16 = 32 bytes = 2 descriptor units along K
-                    umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, (it | k) != 0);
+                    umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (it | k) != 0);
                 umma_commit(&sm->empty[s]); // the stage's shared memory is free once these MMAs have read it
             }
             umma_commit(&sm->accum); // arrives when every MMA issued so far has completed
@@ -296,7 +316,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
 #pragma unroll
                         for (int c = 0; c < 32; c++) {
                             const uint32_t tok = m0 + c0 + c;
-                            if (tok < m) y[(size_t)tok * rows + row] = __float2bfloat16_rn(__uint_as_float(acc[c]));
+                            if (tok < m_end) store_out(y + (size_t)tok * rows + row, __uint_as_float(acc[c]));
                         }
                     }
                 }
@@ -329,16 +349,55 @@ EncodeTiled encode_fn() {
     return fn;
 }
 
-template <int FMT> int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, int *status) {
-    const size_t smem = sizeof(Smem) + 1024;
+// X as bf16 when the caller's activations are F32 (the grouped expert path of the hybrid engine).
+__global__ void k_to_bf16(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, size_t n) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        const float4 v = *reinterpret_cast<const float4 *>(x + i);
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2 *>(out + i) = make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+    } else {
+        for (size_t j = i; j < n; j++) out[j] = __float2bfloat16_rn(x[j]);
+    }
+}
+
+template <int FMT, int BN, typename YT, bool GROUPED>
+int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows, int *status) {
+    const size_t smem = sizeof(Smem<BN>) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<FMT, BN, YT, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fq_check_cuda(dev, e, "gemm shared memory");
         configured = true;
     }
-    dim3 grid((a.rows + BM - 1) / BM, (a.m + BN - 1) / BN);
-    k_gemm_tc<FMT><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (__nv_bfloat16 *)a.y, a.m, b_bytes, status);
+    dim3 grid((a.rows + BM - 1) / BM, GROUPED ? (a.max_rows + BN - 1) / BN : (m_rows + BN - 1) / BN, GROUPED ? a.groups : 1);
+    k_gemm_tc<FMT, BN, YT, GROUPED><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
+                                                                          a.offsets, a.slots, a.experts, status);
+    return FQ_OK;
+}
+
+template <int BN, typename YT, bool GROUPED>
+int launch_fmt(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows) {
+    switch (a.format) {
+    case FQ_Q4_K: return launch<FQ_Q4_K, BN, YT, GROUPED>(dev, a, map, b_bytes, m_rows, dev->status_dev);
+    case FQ_Q6_K: return launch<FQ_Q6_K, BN, YT, GROUPED>(dev, a, map, b_bytes, m_rows, dev->status_dev);
+    default: return launch<FQ_Q8_0, BN, YT, GROUPED>(dev, a, map, b_bytes, m_rows, dev->status_dev);
+    }
+}
+
+int make_map(fq_device *dev, CUtensorMap *map, const void *x, uint32_t cols, uint32_t m_rows, uint32_t bn, uint32_t *b_bytes) {
+    EncodeTiled encode = encode_fn();
+    if (!encode) return FQ_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {cols, m_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    // A box may not be taller than the tensor; rows past the end of a later tile are zero-filled.
+    const uint32_t box_rows = m_rows < bn ? m_rows : bn;
+    const cuuint32_t box[2] = {BK, box_rows}, elem[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fq_fail(dev, FQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    *b_bytes = box_rows * BK * 2;
     return FQ_OK;
 }
 
@@ -349,21 +408,36 @@ int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
     if (a.format != FQ_Q4_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
     if (a.format == FQ_Q4_K && (a.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
     if (a.m < 32) return FQ_ERR_UNSUPPORTED; // narrow inputs: the fp32 kernels serve them
-    EncodeTiled encode = encode_fn();
-    if (!encode) return FQ_ERR_UNSUPPORTED;
     CUtensorMap map;
-    const cuuint64_t dims[2] = {a.cols, a.m};
-    const cuuint64_t strides[1] = {(cuuint64_t)a.cols * 2};
-    // A box may not be taller than the tensor; rows past the end of a later tile are zero-filled.
-    const uint32_t box_rows = a.m < (uint32_t)BN ? a.m : (uint32_t)BN;
-    const cuuint32_t box[2] = {BK, box_rows}, elem[2] = {1, 1};
-    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.x), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fq_fail(dev, FQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-    int rc = a.format == FQ_Q4_K ? launch<FQ_Q4_K>(dev, a, map, box_rows * BK * 2, dev->status_dev)
-             : a.format == FQ_Q6_K ? launch<FQ_Q6_K>(dev, a, map, box_rows * BK * 2, dev->status_dev)
-                                   : launch<FQ_Q8_0>(dev, a, map, box_rows * BK * 2, dev->status_dev);
-    if (rc != FQ_OK) return rc;
+    uint32_t b_bytes = 0;
+    if (int rc = make_map(dev, &map, a.x, a.cols, a.m, 256, &b_bytes)) return rc;
+    if (int rc = launch_fmt<256, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m)) return rc;
     return fq_end_enqueue(dev, "gemm_tc", 1);
+}
+
+// Expert-sorted rows (`project_mm_id_in`): x is [total_rows][cols], F32 (converted to bf16 into the
+// handle's scratch first) or BF16; y is F32 or BF16 accordingly.
+int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t total_rows) {
+    if (a.cols % BK || !a.offsets || a.x_dtype != a.y_dtype) return FQ_ERR_UNSUPPORTED;
+    if (a.format != FQ_Q4_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
+    if (a.format == FQ_Q4_K && (a.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
+    if (a.groups > 65535 || total_rows == 0) return FQ_ERR_UNSUPPORTED;
+    const void *xb = a.x;
+    int kernels = 1;
+    if (a.x_dtype == FQ_F32) {
+        const size_t n = (size_t)total_rows * a.cols;
+        if (n * 2 > dev->xprep_bytes / 2) return FQ_ERR_UNSUPPORTED;
+        dev->xprep_turn ^= 1u;
+        __nv_bfloat16 *tmp = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0));
+        k_to_bf16<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, dev->stream>>>((const float *)a.x, tmp, n);
+        xb = tmp;
+        kernels = 2;
+    }
+    CUtensorMap map;
+    uint32_t b_bytes = 0;
+    if (int rc = make_map(dev, &map, xb, a.cols, total_rows, 64, &b_bytes)) return rc;
+    int rc = a.y_dtype == FQ_F32 ? launch_fmt<64, float, true>(dev, a, map, b_bytes, total_rows)
+                                 : launch_fmt<64, __nv_bfloat16, true>(dev, a, map, b_bytes, total_rows);
+    if (rc != FQ_OK) return rc;
+    return fq_end_enqueue(dev, "gemm_tc_grouped", kernels);
 }

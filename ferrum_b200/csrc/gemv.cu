@@ -615,7 +615,7 @@ int launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const uint8_t *
 
 } // namespace
 
-size_t fq_gemv_scratch_bytes() { return (size_t)32 << 20; }
+size_t fq_gemv_scratch_bytes() { return (size_t)96 << 20; }
 
 // `a[0..count)` share x, m, format and width (checked here); expert mode takes one matrix.
 int fq_launch_gemv_fast_many(fq_device *dev, const ProjectArgs *a, uint32_t count) {

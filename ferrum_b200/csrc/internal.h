@@ -103,3 +103,5 @@ size_t fq_gemv_scratch_bytes();
 int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
 // tcgen05 dequant-GEMM (BF16 in/out); same fallback contract.
 int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a);
+// The same over expert-sorted activation rows (a.offsets / a.slots / a.groups / a.max_rows); F32 or BF16.
+int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t total_rows);

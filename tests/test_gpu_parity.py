@@ -200,14 +200,17 @@ def test_project_id_and_grouped(device, fmt, exact):
         y7 = torch.zeros(7 * rows, dtype=torch.float32, device="cuda")
         s.project_mm_id(device, w, dev_f32(x7), dev_u32(offsets), 7, y7)
         device.synchronize()
-        assert ref.rel_err(host(y7).reshape(-1, rows), ref.matmul_grouped(fmt, packed, rows, cols, x7, offsets)) <= TOL_F32
+        # the expert-sorted GEMM is a bf16 tensor-core path (bar 2e-2; the reference's own F16-tile kernel is
+        # checked at 5e-3, src/hybrid/iq_tests.rs:1289-1299); exact mode keeps fp32
+        tol_g = TOL_F32 if exact else TOL_BF16
+        assert ref.rel_err(host(y7).reshape(-1, rows), ref.matmul_grouped(fmt, packed, rows, cols, x7, offsets)) <= tol_g
         # arena slots: group z is stored at table[z] (src/hybrid/iq_tests.rs:1782)
         table, offs = np.array([2, 0], dtype=np.uint32), np.array([0, 3, 5], dtype=np.uint32)
         x5 = ref.xorshift_f32(5 * cols, 13)
         y5 = torch.zeros(5 * rows, dtype=torch.float32, device="cuda")
         s.project_mm_id_in(device, w, dev_f32(x5), dev_u32(offs), (dev_u32(table), 2), 5, y5)
         device.synchronize()
-        assert ref.rel_err(host(y5).reshape(-1, rows), ref.matmul_grouped(fmt, packed, rows, cols, x5, offs, table)) <= TOL_F32
+        assert ref.rel_err(host(y5).reshape(-1, rows), ref.matmul_grouped(fmt, packed, rows, cols, x5, offs, table)) <= tol_g
     finally:
         device.set_exact(False)
 
@@ -364,7 +367,8 @@ def test_moe_ffn(device, m):
     u = ref.matmul_id(ref.Q4_K, up_e, ef, hidden, x, ids, used)
     dn = ref.matmul_id(ref.Q6_K, down_e, hidden, ef, ref.swiglu(g, u), ids, 1)
     want = ref.moe_combine(dn, wts, ids, shared, gate, hidden, used, m, identity=True)
-    assert ref.rel_err(host(out).reshape(m, hidden), want) <= 3 * TOL_F32
+    # m = 40 runs three chained bf16 expert GEMMs; the smaller cases stay on the fp32-accurate GEMVs
+    assert ref.rel_err(host(out).reshape(m, hidden), want) <= (3 * TOL_F32 if m * used <= 32 else TOL_BF16)
 
 
 # ------------------------------------------------------------------ error behaviour and the boundary
@@ -591,3 +595,29 @@ def test_full_size_prefill_rows(device, fmt, rows, cols):
     want = xb.astype(np.float64) @ dense_b.astype(np.float64).T
     assert np.abs(got[:, pick] - want).max() / np.abs(got).max() <= TOL_BF16
     assert np.isfinite(got).all()
+
+
+def test_grouped_expert_gemm_config3_shape(device):
+    """Config 3 geometry, scaled to 32 experts: gate 512 x 2048 Q4_K per expert, 1024 routes sorted by expert
+    with uneven group sizes (some empty), F32 in / F32 out through the tensor-memory path."""
+    s = S()
+    experts, rows_e, cols, routes = 32, 512, 2048, 1024
+    packed = ref.random_matrix(ref.Q4_K, experts * rows_e, cols, seed=61)
+    w = s.Matrix.from_packed(device, rows_e, cols, experts, ref.Q4_K, packed)
+    rng = np.random.default_rng(62)
+    ids = np.sort(rng.integers(0, experts, routes)).astype(np.uint32)
+    ids[ids == 7] = 8  # an expert nobody picked
+    counts = np.bincount(ids, minlength=experts)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32)
+    x = rng.standard_normal((routes, cols)).astype(np.float32)
+    y = torch.full((routes * rows_e,), float("nan"), dtype=torch.float32, device="cuda")
+    s.project_mm_id(device, w, dev_f32(x), dev_u32(offsets), int(counts.max()), y)
+    device.synchronize()
+    got = host(y).reshape(routes, rows_e)
+    assert np.isfinite(got).all()
+    pick = rng.choice(routes, 24, replace=False)
+    rb = ref.row_bytes(ref.Q4_K, cols)
+    for r in pick:
+        e = int(ids[r])
+        want = ref.matmul(ref.Q4_K, packed[e * rows_e * rb:(e + 1) * rows_e * rb], rows_e, cols, x[r], 1)[0]
+        assert np.abs(got[r] - want).max() / np.abs(got).max() <= TOL_BF16
