@@ -331,16 +331,22 @@ def run_ours(args):
             t = timed(gemm_layer, reps) / reps / layers
             flops = 2.0 * mm * LAYER_WEIGHTS
             per_mat = {}
-            for n in ("gate", "down"):
+            for n in ("q", "k", "o", "gate", "down"):
                 def one(n=n):
                     for layer in mats:
                         S.project(dev, layer[n], xs[[g[0] for g in GROUPS if n in g][0]], mm, ys[n])
                 tt = timed(one, reps) / reps / layers
                 per_mat[n] = round(2.0 * mm * shapes[n][0] * shapes[n][1] / (tt * 1e-3) / 1e12, 1)
+                per_mat[n + "_us"] = round(tt * 1e3, 1)
             prefill[f"m{mm}"] = {"tflops": round(flops / (t * 1e-3) / 1e12, 1), "ms_per_layer": round(t, 4),
                                  "frac_of_measured_bf16_peak": round(flops / (t * 1e-3) / 1e12 / P["bf16_tflops"], 4),
                                  "per_matrix_tflops": per_mat}
         out["prefill_gemm"] = prefill
+
+        # MoE FFN (config 3), 35B-A3B-class: hidden 2048, 256 experts (gate/up 2048->512 Q4_K, down 512->2048
+        # Q6_K) + shared expert, Q8_0 router, softmax -> top-8 -> renormalise.  T = 1 takes the per-route GEMVs,
+        # T = 1024 the expert-sorted tensor-core GEMM.  GB/s = packed bytes of the weights a call must read.
+        out["moe_ffn"] = moe_bench(S, dev, stream, torch, timed_ms=timed)
 
         # End to end through the C ABI with HOST buffers: every step uploads the step's activations
         # from pinned memory, replays the step, downloads every output and waits.
@@ -370,6 +376,37 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def moe_bench(S, dev, stream, torch, timed_ms):
+    H, E, F, USED = 2048, 256, 512, 8
+    M = S.Matrix.from_packed
+    f = S.MoeFfn(M(dev, E, H, 1, Q8_0, random_matrix(Q8_0, E, H, 900)),
+                 M(dev, F, H, E, Q4_K, random_matrix(Q4_K, E * F, H, 901)), M(dev, F, H, E, Q4_K, random_matrix(Q4_K, E * F, H, 902)),
+                 M(dev, H, F, E, Q6_K, random_matrix(Q6_K, E * H, F, 903)),
+                 M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 904)), M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 905)),
+                 M(dev, H, F, 1, Q6_K, random_matrix(Q6_K, H, F, 906)), None, E, USED, H, F, F, False, True)
+    per_expert = 2 * (F * H // 256 * 144) + H * F // 256 * 210
+    router_bytes = E * H // 32 * 34
+    res = {}
+    for T in (1, 1024):
+        x = (torch.randn(T * H, device="cuda") * 0.12).contiguous()
+        scratch = torch.zeros(S.moe_ffn_scratch_elems(dev, f, T), dtype=torch.float32, device="cuda")
+        o = torch.zeros(T * H, dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        dev.capture_begin()
+        S.moe_ffn(dev, f, x, T, scratch, o)
+        g = dev.capture_end()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                g.launch()
+        reps = 10
+        ms = timed_ms(g.launch, reps) / reps
+        touched = (min(E, T * USED) if T == 1 else E) * per_expert + per_expert + router_bytes
+        flops = 2.0 * T * (USED + 1) * 3 * F * H
+        res[f"t{T}"] = {"us": round(ms * 1e3, 1), "weight_gbs": round(touched / (ms * 1e-3) / 1e9, 1),
+                        "tflops": round(flops / (ms * 1e-3) / 1e12, 2), "weight_bytes": touched}
+    return res
 
 
 # ---------------------------------------------------------------------------------------------------

@@ -127,6 +127,10 @@ extern "C" int fq_device_create(int ordinal, fq_device **out) {
     if ((e = cudaMalloc(&dev->xprep, dev->xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
     if ((e = cudaMalloc(&dev->staging_dev, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "device staging");
     if ((e = cudaMallocHost(&dev->staging_host, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "pinned staging");
+    dev->gemm_ws_bytes = (size_t)96 << 20;
+    if ((e = cudaMalloc((void **)&dev->gemm_ws, dev->gemm_ws_bytes)) != cudaSuccess) return bail(e, "gemm workspace");
+    if ((e = cudaMalloc((void **)&dev->gemm_counters, dev->gemm_tiles_max * sizeof(uint32_t))) != cudaSuccess) return bail(e, "gemm counters");
+    if ((e = cudaMemset(dev->gemm_counters, 0, dev->gemm_tiles_max * sizeof(uint32_t))) != cudaSuccess) return bail(e, "gemm counters");
     void *status = nullptr;
     if ((e = cudaHostAlloc(&status, 64, cudaHostAllocMapped)) != cudaSuccess) return bail(e, "status word");
     dev->status_host = (volatile int *)status;
@@ -143,6 +147,8 @@ extern "C" int fq_device_destroy(fq_device *dev) {
     for (auto &kv : dev->allocations) cudaFree((void *)kv.first);
     if (dev->xprep) cudaFree(dev->xprep);
     if (dev->staging_dev) cudaFree(dev->staging_dev);
+    if (dev->gemm_ws) cudaFree(dev->gemm_ws);
+    if (dev->gemm_counters) cudaFree(dev->gemm_counters);
     if (dev->staging_host) cudaFreeHost(dev->staging_host);
     if (dev->status_host) cudaFreeHost((void *)dev->status_host);
     if (dev->own_stream) cudaStreamDestroy(dev->own_stream);

@@ -23,6 +23,8 @@
 // memory and returns.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "blocks.cuh"
 #include "internal.h"
 
@@ -31,16 +33,19 @@ namespace {
 constexpr int BM = 128;      // weight rows per block (MMA M)
 // Activation rows per block (MMA N): 256 for dense prefill, 64 for expert groups (about 32 rows each).
 constexpr int BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int STAGES = 4;
+constexpr int A_STAGES = 4;  // ring of decoded weight tiles
 constexpr int PRODUCER_WARPS = 8;
 constexpr int THREADS = (2 + PRODUCER_WARPS) * 32;
 constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
+// Ring of activation tiles: 4 deep, or 2 deep for the 512-row tile (64 KB per stage).
+template <int BN> constexpr int b_stages() { return BN > 256 ? 2 : 4; }
+
 template <int BN> struct __align__(1024) Smem {
-    uint8_t a[STAGES][A_BYTES];
-    uint8_t b[STAGES][BN * BK * 2];
-    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES], accum;
+    uint8_t a[A_STAGES][A_BYTES];
+    uint8_t b[b_stages<BN>()][BN * BK * 2];
+    uint64_t full_a[A_STAGES], empty_a[A_STAGES], full_b[b_stages<BN>()], empty_b[b_stages<BN>()], accum;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -116,6 +121,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+// Small unsigned integer -> float without the conversion unit: the integer placed in the mantissa of 2^23,
+// minus 2^23 (+ bias).  Exact, and it keeps the quarter-rate I2F pipe out of the producers' inner loop.
+__device__ __forceinline__ float small_to_float(uint32_t q, float bias = 0.f) {
+    return __fsub_rn(__uint_as_float(0x4B000000u | q), 8388608.0f + bias);
+}
+
 // 32 consecutive k values of weight row `row` (a k-block of 64 is two of these: part 0 and 1), decoded
 // exactly and rounded to bf16, two per register.
 template <int FMT>
@@ -142,8 +153,11 @@ __device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uin
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const uint32_t v = part ? (w[i] >> 4) : w[i];
-            const float f0 = __fsub_rn(__fmul_rn(ds, (float)(v & 0xFu)), dm), f1 = __fsub_rn(__fmul_rn(ds, (float)((v >> 8) & 0xFu)), dm);
-            const float f2 = __fsub_rn(__fmul_rn(ds, (float)((v >> 16) & 0xFu)), dm), f3 = __fsub_rn(__fmul_rn(ds, (float)((v >> 24) & 0xFu)), dm);
+            const uint32_t n4 = v & 0x0F0F0F0Fu; // one quant per byte; each byte moves into a float mantissa with one PRMT
+            const float f0 = __fsub_rn(__fmul_rn(ds, small_to_float(__byte_perm(n4, 0, 0x4440))), dm);
+            const float f1 = __fsub_rn(__fmul_rn(ds, small_to_float(__byte_perm(n4, 0, 0x4441))), dm);
+            const float f2 = __fsub_rn(__fmul_rn(ds, small_to_float(__byte_perm(n4, 0, 0x4442))), dm);
+            const float f3 = __fsub_rn(__fmul_rn(ds, small_to_float(__byte_perm(n4, 0, 0x4443))), dm);
             out[2 * i] = pack_bf16(f0, f1);
             out[2 * i + 1] = pack_bf16(f2, f3);
         }
@@ -161,17 +175,17 @@ __device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uin
         const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w}, hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
         for (int j = 0; j < 8; j++) {
+            // four 6-bit quants, one per byte: low nibbles from ql, bits 4..5 from qh (one select for all four)
             const uint32_t lo4 = (i < 2) ? lw[j] : (lw[j] >> 4);
-            const uint32_t hi2 = hw[j] >> (2 * i);
+            const uint32_t hi4 = i == 0 ? (hw[j] << 4) : i == 1 ? (hw[j] << 2) : i == 2 ? hw[j] : (hw[j] >> 2);
+            const uint32_t q4 = ((lo4 & 0x0F0F0F0Fu) | (hi4 & 0x30303030u));
             const float ds = j < 4 ? ds0 : ds1;
-            float f[4];
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const uint32_t q = ((lo4 >> (8 * e)) & 0xFu) | (((hi2 >> (8 * e)) & 3u) << 4);
-                f[e] = __fmul_rn(ds, (float)q - 32.0f);
-            }
-            out[2 * j] = pack_bf16(f[0], f[1]);
-            out[2 * j + 1] = pack_bf16(f[2], f[3]);
+            const float f0 = __fmul_rn(ds, small_to_float(__byte_perm(q4, 0, 0x4440), 32.0f)); // q - 32, exact
+            const float f1 = __fmul_rn(ds, small_to_float(__byte_perm(q4, 0, 0x4441), 32.0f));
+            const float f2 = __fmul_rn(ds, small_to_float(__byte_perm(q4, 0, 0x4442), 32.0f));
+            const float f3 = __fmul_rn(ds, small_to_float(__byte_perm(q4, 0, 0x4443), 32.0f));
+            out[2 * j] = pack_bf16(f0, f1);
+            out[2 * j + 1] = pack_bf16(f2, f3);
         }
     } else {
         // Q8_0: 34-byte blocks, 2-byte aligned; k-block kb = blocks 2 kb and 2 kb + 1.
@@ -181,8 +195,9 @@ __device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uin
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const uint32_t w0 = q[2 * j], w1 = q[2 * j + 1];
-            const float f0 = __fmul_rn((float)(int)(int8_t)(w0 & 0xFF), d), f1 = __fmul_rn((float)(int)(int8_t)(w0 >> 8), d);
-            const float f2 = __fmul_rn((float)(int)(int8_t)(w1 & 0xFF), d), f3 = __fmul_rn((float)(int)(int8_t)(w1 >> 8), d);
+            // signed byte b -> (b ^ 0x80) - 128
+            const float f0 = __fmul_rn(small_to_float((w0 & 0xFFu) ^ 0x80u, 128.f), d), f1 = __fmul_rn(small_to_float((w0 >> 8) ^ 0x80u, 128.f), d);
+            const float f2 = __fmul_rn(small_to_float((w1 & 0xFFu) ^ 0x80u, 128.f), d), f3 = __fmul_rn(small_to_float((w1 >> 8) ^ 0x80u, 128.f), d);
             out[2 * j] = pack_bf16(f0, f1);
             out[2 * j + 1] = pack_bf16(f2, f3);
         }
@@ -200,9 +215,10 @@ template <int FMT, int BN, typename YT, bool GROUPED>
 __global__ void __launch_bounds__(THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t pitch,
           YT *__restrict__ y, uint32_t m, uint32_t b_bytes, const uint32_t *__restrict__ offsets,
-          const uint32_t *__restrict__ slots, uint32_t experts, int *status) {
+          const uint32_t *__restrict__ slots, uint32_t experts, uint32_t splits, float *__restrict__ ws, int *status) {
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-    constexpr uint32_t IDESC = idesc_for(BN);
+    constexpr int NSUB = BN > 256 ? BN / 256 : 1, MMA_N = BN / NSUB, B_STAGES = b_stages<BN>();
+    constexpr uint32_t IDESC = idesc_for(MMA_N);
     extern __shared__ uint8_t smem_raw[];
     using SM = Smem<BN>;
     SM *sm = reinterpret_cast<SM *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -218,15 +234,25 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         m_end = first + count;
     }
     const uint32_t n0 = blockIdx.x * BM;
-    const uint32_t k_iters = cols / BK;
+    // Split K (dense only, blockIdx.z = split): a matrix with few row tiles still fills the machine; the
+    // partial accumulators go to a workspace and a small kernel adds them in split order.
+    uint32_t k_first = 0, k_iters = cols / BK;
+    if (!GROUPED && splits > 1) {
+        const uint32_t per = (k_iters + splits - 1) / splits;
+        k_first = blockIdx.z * per;
+        k_iters = k_first < k_iters ? min(per, k_iters - k_first) : 0;
+    }
     constexpr uint32_t nblk_div = FMT == FQ_Q8_0 ? 32 : 256;
     const uint32_t nblk = cols / nblk_div;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < A_STAGES; s++) {
             mbar_init(&sm->full_a[s], PRODUCER_WARPS * 32);
+            mbar_init(&sm->empty_a[s], 1);
+        }
+        for (int s = 0; s < B_STAGES; s++) {
             mbar_init(&sm->full_b[s], 1);
-            mbar_init(&sm->empty[s], 1);
+            mbar_init(&sm->empty_b[s], 1);
         }
         mbar_init(&sm->accum, 1);
         sm->abort_flag = 0;
@@ -247,18 +273,20 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         if (lane == 0) {
             uint32_t issued = 0;
             for (uint32_t it = 0; it < k_iters; it++) {
-                const int s = it % STAGES;
-                if (!mbar_wait(&sm->empty[s], ((it / STAGES) & 1) ^ 1, sm, status)) break;
-                mbar_expect_tx(&sm->full_b[s], b_bytes);
-                tma_load_2d(sm->b[s], &xmap, (int)(it * BK), (int)m0, &sm->full_b[s]);
+                const int s = it % B_STAGES;
+                if (!mbar_wait(&sm->empty_b[s], ((it / B_STAGES) & 1) ^ 1, sm, status)) break;
+                mbar_expect_tx(&sm->full_b[s], b_bytes * NSUB);
+#pragma unroll
+                for (int h = 0; h < NSUB; h++) // a TMA box is at most 256 rows
+                    tma_load_2d(sm->b[s] + h * (MMA_N * BK * 2), &xmap, (int)((k_first + it) * BK), (int)(m0 + h * MMA_N), &sm->full_b[s]);
                 issued = it + 1;
             }
             // On an abort the copies already issued still land: wait for them (bounded) before the
             // block's shared memory goes away.
             if (*(volatile uint32_t *)&sm->abort_flag) {
-                for (uint32_t it = issued > STAGES ? issued - STAGES : 0; it < issued; it++) {
-                    const int s = it % STAGES;
-                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(&sm->full_b[s], (it / STAGES) & 1); i++) {}
+                for (uint32_t it = issued > (uint32_t)B_STAGES ? issued - B_STAGES : 0; it < issued; it++) {
+                    const int s = it % B_STAGES;
+                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(&sm->full_b[s], (it / B_STAGES) & 1); i++) {}
                 }
             }
         }
@@ -266,16 +294,19 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         if (lane == 0) {
             bool ok = true;
             for (uint32_t it = 0; it < k_iters && ok; it++) {
-                const int s = it % STAGES;
-                const uint32_t parity = (it / STAGES) & 1;
-                ok = mbar_wait(&sm->full_a[s], parity, sm, status) && mbar_wait(&sm->full_b[s], parity, sm, status);
+                const int sa = it % A_STAGES, sb = it % B_STAGES;
+                ok = mbar_wait(&sm->full_a[sa], (it / A_STAGES) & 1, sm, status) && mbar_wait(&sm->full_b[sb], (it / B_STAGES) & 1, sm, status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = umma_desc(smem_u32(sm->a[s])), bdesc = umma_desc(smem_u32(sm->b[s]));
+                const uint64_t adesc = umma_desc(smem_u32(sm->a[sa])), bdesc = umma_desc(smem_u32(sm->b[sb]));
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++) // 16 bf16 = 32 bytes = 2 descriptor units along K
-                    umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (it | k) != 0);
-                umma_commit(&sm->empty[s]); // the stage's shared memory is free once these MMAs have read it
+                for (int h = 0; h < NSUB; h++) // each 256-row half of the activation tile has its own accumulator columns
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) // 16 bf16 = 32 bytes = 2 descriptor units along K
+                        umma_bf16(tmem + h * MMA_N, adesc + 2 * k, bdesc + (uint64_t)(h * (MMA_N * BK * 2 / 16)) + 2 * k, IDESC, (it | k) != 0);
+                // both rings get their stage back once these MMAs have read it
+                umma_commit(&sm->empty_a[sa]);
+                umma_commit(&sm->empty_b[sb]);
             }
             umma_commit(&sm->accum); // arrives when every MMA issued so far has completed
         }
@@ -285,14 +316,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         const bool live = n0 + r < rows;
         const uint8_t *rowp = w + (size_t)min(n0 + r, rows - 1) * pitch;
         for (uint32_t it = 0; it < k_iters; it++) {
-            const int s = it % STAGES;
+            const int s = it % A_STAGES;
             uint32_t v[16];
-            decode32<FMT>(rowp, nblk, it, part, v); // global loads and arithmetic overlap the wait below
+            decode32<FMT>(rowp, nblk, k_first + it, part, v); // global loads and arithmetic overlap the wait below
             if (!live) {
 #pragma unroll
                 for (int i = 0; i < 16; i++) v[i] = 0u;
             }
-            if (!mbar_wait(&sm->empty[s], ((it / STAGES) & 1) ^ 1, sm, status)) break;
+            if (!mbar_wait(&sm->empty_a[s], ((it / A_STAGES) & 1) ^ 1, sm, status)) break;
             uint8_t *tile_row = sm->a[s] + r * 128;
 #pragma unroll
             for (int c = 0; c < 4; c++) { // 16-byte chunk 4 part + c of the row, at its swizzled place
@@ -305,10 +336,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         // Epilogue: warps 2..5 cover the four 32-lane quarters of tensor memory (quarter = warp % 4).
         if (warp < 6) {
             const int quarter = warp & 3;
-            const bool ok = mbar_wait(&sm->accum, 0, sm, status);
+            if (!mbar_wait(&sm->accum, 0, sm, status)) atomicExch(&sm->abort_flag, 1u);
+            asm volatile("bar.sync 1, 128;" ::: "memory"); // the four epilogue warps agree on whether to go on
+            const bool ok = *(volatile uint32_t *)&sm->abort_flag == 0;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t row = n0 + 32 * quarter + lane;
-            if (ok) {
+            if (ok && (GROUPED || splits <= 1)) {
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t acc[32];
                     tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + c0, acc);
@@ -319,6 +352,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
                             if (tok < m_end) store_out(y + (size_t)tok * rows + row, __uint_as_float(acc[c]));
                         }
                     }
+                }
+            } else if (ok) {
+                // This split's partial tile, column-major ([col][row]) so that both these stores and the
+                // reduction kernel's loads are coalesced.
+                const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
+                float *mine = ws + ((size_t)tile * splits + blockIdx.z) * BN * BM + 32 * quarter + lane;
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t acc[32];
+                    tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + c0, acc);
+#pragma unroll
+                    for (int c = 0; c < 32; c++) mine[(size_t)(c0 + c) * BM] = __uint_as_float(acc[c]);
                 }
             }
         }
@@ -361,6 +405,29 @@ __global__ void k_to_bf16(const float *__restrict__ x, __nv_bfloat16 *__restrict
     }
 }
 
+// Sum of the split-K partial tiles, in split order (deterministic), rounded and stored as Y.
+// ws[tile][split][col][row]; one thread per four consecutive weight rows of one activation row.
+template <int BN, typename YT>
+__global__ void __launch_bounds__(256)
+k_splitk_reduce(const float *__restrict__ ws, uint32_t splits, uint32_t n_tiles, uint32_t rows, uint32_t m, YT *__restrict__ y, size_t total) {
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const uint32_t r4 = e % (BM / 4), col = (e / (BM / 4)) % BN, tile = (uint32_t)(e / ((size_t)(BM / 4) * BN));
+    const uint32_t row = (tile % n_tiles) * BM + 4 * r4, tok = (tile / n_tiles) * BN + col;
+    if (tok >= m || row >= rows) return;
+    const float *p = ws + (((size_t)tile * splits) * BN + col) * BM + 4 * r4;
+    float4 sum = __ldcg(reinterpret_cast<const float4 *>(p));
+    for (uint32_t z = 1; z < splits; z++) {
+        const float4 v = __ldcg(reinterpret_cast<const float4 *>(p + (size_t)z * BN * BM));
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    const float o[4] = {sum.x, sum.y, sum.z, sum.w};
+    YT *dst = y + (size_t)tok * rows + row;
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+        if (row + i < rows) store_out(dst + i, o[i]);
+}
+
 template <int FMT, int BN, typename YT, bool GROUPED>
 int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows, int *status) {
     const size_t smem = sizeof(Smem<BN>) + 1024;
@@ -371,8 +438,27 @@ int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_
         configured = true;
     }
     dim3 grid((a.rows + BM - 1) / BM, GROUPED ? (a.max_rows + BN - 1) / BN : (m_rows + BN - 1) / BN, GROUPED ? a.groups : 1);
+    uint32_t splits = 1;
+    if (!GROUPED) {
+        // Few tiles: split K so that about one block per SM runs, each with at least 8 stages, within the
+        // workspace and the counter table.
+        const uint32_t tiles = grid.x * grid.y, k_iters = a.cols / BK;
+        if (tiles * 4 < (uint32_t)dev->sm_count * 3) {
+            splits = std::min<uint32_t>({(uint32_t)dev->sm_count / tiles, std::max(1u, k_iters / 8), 16u});
+            const size_t per_split = (size_t)tiles * BM * BN * sizeof(float);
+            splits = (uint32_t)std::min<size_t>(splits, dev->gemm_ws_bytes / per_split);
+            if (splits < 1) splits = 1;
+            const uint32_t per = (k_iters + splits - 1) / splits;
+            splits = (k_iters + per - 1) / per; // no split is left without work
+        }
+        grid.z = splits;
+    }
     k_gemm_tc<FMT, BN, YT, GROUPED><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
-                                                                          a.offsets, a.slots, a.experts, status);
+                                                                          a.offsets, a.slots, a.experts, splits, dev->gemm_ws, status);
+    if (splits > 1) {
+        const size_t total = (size_t)grid.x * grid.y * BN * (BM / 4);
+        k_splitk_reduce<BN, YT><<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(dev->gemm_ws, splits, grid.x, a.rows, m_rows, (YT *)a.y, total);
+    }
     return FQ_OK;
 }
 
@@ -411,7 +497,11 @@ int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
     CUtensorMap map;
     uint32_t b_bytes = 0;
     if (int rc = make_map(dev, &map, a.x, a.cols, a.m, 256, &b_bytes)) return rc;
-    if (int rc = launch_fmt<256, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m)) return rc;
+    // 512 activation rows per block (two accumulators sharing each decoded weight tile) once there are
+    // enough rows to fill them; the TMA box stays 256 rows.
+    if (a.m >= 384) {
+        if (int rc = launch_fmt<512, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m)) return rc;
+    } else if (int rc = launch_fmt<256, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m)) return rc;
     return fq_end_enqueue(dev, "gemm_tc", 1);
 }
 

@@ -36,6 +36,11 @@ struct fq_device {
     uint32_t xprep_turn = 0;      // successive projections alternate between the two halves of xprep
     void *staging_dev = nullptr;  // device side of the host-buffer entry points
     void *staging_host = nullptr; // pinned host side
+    // Split-K workspace of the prefill GEMM: partial fp32 tiles and one arrival counter per tile.
+    float *gemm_ws = nullptr;
+    size_t gemm_ws_bytes = 0;
+    uint32_t *gemm_counters = nullptr;
+    uint32_t gemm_tiles_max = 4096;
     // One word in mapped pinned host memory that kernels set when a bounded wait gives up.
     volatile int *status_host = nullptr;
     int *status_dev = nullptr;
