@@ -35,6 +35,7 @@ constexpr int BM = 128;      // weight rows per block (MMA M)
 constexpr int BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int A_STAGES = 4;  // ring of decoded weight tiles
 constexpr int PRODUCER_WARPS = 8;
+constexpr int PREFETCH = 3;  // k-blocks of packed bytes in flight per producer thread
 constexpr int THREADS = (2 + PRODUCER_WARPS) * 32;
 constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
@@ -127,16 +128,52 @@ __device__ __forceinline__ float small_to_float(uint32_t q, float bias = 0.f) {
     return __fsub_rn(__uint_as_float(0x4B000000u | q), 8388608.0f + bias);
 }
 
-// 32 consecutive k values of weight row `row` (a k-block of 64 is two of these: part 0 and 1), decoded
-// exactly and rounded to bf16, two per register.
+// The packed bytes one producer thread needs for 32 consecutive k values of its weight row (a k-block of 64
+// is two of these: part 0 and 1).  Loading and decoding are separate so that the loads of later k-blocks are
+// in flight while the current one is decoded: a thread's stream is otherwise bound by memory latency.
+template <int FMT> struct Raw;
+template <> struct Raw<FQ_Q4_K> { uint4 hdr, q0, q1; };
+template <> struct Raw<FQ_Q6_K> { uint4 l0, l1, h0, h1; uint32_t sc, d; };
+template <> struct Raw<FQ_Q8_0> { uint32_t q[8]; uint32_t d; };
+
 template <int FMT>
-__device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uint32_t kb, int part, uint32_t (&out)[16]) {
+__device__ __forceinline__ Raw<FMT> load_raw(const uint8_t *rowp, uint32_t nblk, uint32_t kb, int part) {
+    Raw<FMT> r;
     if constexpr (FMT == FQ_Q4_K) {
         // k-block kb = chunk c of superblock b: part 0 = low nibbles (sub-block 2c), part 1 = high nibbles.
-        const uint32_t b = kb >> 2, c = kb & 3;
-        const uint8_t *blk = rowp + (size_t)b * 144;
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c), q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
+        const uint8_t *blk = rowp + (size_t)(kb >> 2) * 144;
+        const uint32_t c = kb & 3;
+        r.hdr = *reinterpret_cast<const uint4 *>(blk);
+        r.q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c);
+        r.q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
+    } else if constexpr (FMT == FQ_Q6_K) {
+        // k-block kb of superblock b: half n = (kb % 4) / 2, 32-groups i = 2 h and 2 h + 1 with h = kb % 2;
+        // part selects the group.  Device layout of blocks.cuh.
+        const uint32_t b = kb >> 2, n = (kb >> 1) & 1, h = kb & 1, i = 2 * h + part;
+        const uint8_t *ql = rowp + (size_t)b * 128 + 64 * n + 32 * (i & 1);
+        const uint8_t *qh = rowp + (size_t)nblk * 128 + (size_t)b * 64 + 32 * n;
+        r.l0 = *reinterpret_cast<const uint4 *>(ql);
+        r.l1 = *reinterpret_cast<const uint4 *>(ql + 16);
+        r.h0 = *reinterpret_cast<const uint4 *>(qh);
+        r.h1 = *reinterpret_cast<const uint4 *>(qh + 16);
+        r.sc = *reinterpret_cast<const uint16_t *>(rowp + (size_t)nblk * 192 + (size_t)b * 16 + 8 * n + 2 * i);
+        r.d = *reinterpret_cast<const uint16_t *>(rowp + (size_t)nblk * 208 + (size_t)b * 2);
+    } else {
+        // Q8_0: 34-byte blocks, 2-byte aligned; k-block kb = blocks 2 kb and 2 kb + 1.
+        const uint16_t *blk = reinterpret_cast<const uint16_t *>(rowp + (size_t)(2 * kb + part) * 34);
+        r.d = blk[0];
+#pragma unroll
+        for (int j = 0; j < 8; j++) r.q[j] = (uint32_t)blk[1 + 2 * j] | ((uint32_t)blk[2 + 2 * j] << 16);
+    }
+    return r;
+}
+
+// Raw bytes -> 32 weights decoded exactly and rounded to bf16, two per register.
+template <int FMT>
+__device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int part, uint32_t (&out)[16]) {
+    if constexpr (FMT == FQ_Q4_K) {
+        const uint32_t c = kb & 3;
+        const uint4 hdr = r.hdr;
         // `get_scale_min_k4` on the three scale words (hdr.y = scales[0..3], .z = [4..7], .w = [8..11]).
         const uint32_t j = 2 * c + part, sh = 8 * (j & 3);
         uint32_t sc, mn;
@@ -148,8 +185,8 @@ __device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uin
             mn = (((hdr.w >> sh) >> 4) & 0xFu) | ((((hdr.z >> sh) >> 6) & 3u) << 4);
         }
         const float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu)), dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
-        const float ds = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
-        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const float ds = __fmul_rn(d, small_to_float(sc)), dm = __fmul_rn(dmin, small_to_float(mn));
+        const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const uint32_t v = part ? (w[i] >> 4) : w[i];
@@ -162,17 +199,13 @@ __device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uin
             out[2 * i + 1] = pack_bf16(f2, f3);
         }
     } else if constexpr (FMT == FQ_Q6_K) {
-        // k-block kb of superblock b: half n = (kb % 4) / 2, 32-groups i = 2 h and 2 h + 1 with h = kb % 2;
-        // part selects the group.  Device layout of blocks.cuh.
-        const uint32_t b = kb >> 2, n = (kb >> 1) & 1, h = kb & 1, i = 2 * h + part;
-        const uint8_t *ql = rowp + (size_t)b * 128 + 64 * n + 32 * (i & 1);
-        const uint8_t *qh = rowp + (size_t)nblk * 128 + (size_t)b * 64 + 32 * n;
-        const int8_t *sc = reinterpret_cast<const int8_t *>(rowp + (size_t)nblk * 192 + (size_t)b * 16 + 8 * n + 2 * i);
-        const float d = load_f16(rowp + (size_t)nblk * 208 + (size_t)b * 2);
-        const float ds0 = __fmul_rn(d, (float)sc[0]), ds1 = __fmul_rn(d, (float)sc[1]);
-        const uint4 l0 = *reinterpret_cast<const uint4 *>(ql), l1 = *reinterpret_cast<const uint4 *>(ql + 16);
-        const uint4 h0 = *reinterpret_cast<const uint4 *>(qh), h1 = *reinterpret_cast<const uint4 *>(qh + 16);
-        const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w}, hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        const uint32_t h = kb & 1, i = 2 * h + part;
+        const float d = f16_bits_to_f32((uint16_t)r.d);
+        // signed scale s -> (s ^ 0x80) - 128 without the conversion unit
+        const float ds0 = __fmul_rn(d, small_to_float((r.sc & 0xFFu) ^ 0x80u, 128.f));
+        const float ds1 = __fmul_rn(d, small_to_float(((r.sc >> 8) & 0xFFu) ^ 0x80u, 128.f));
+        const uint32_t lw[8] = {r.l0.x, r.l0.y, r.l0.z, r.l0.w, r.l1.x, r.l1.y, r.l1.z, r.l1.w};
+        const uint32_t hw[8] = {r.h0.x, r.h0.y, r.h0.z, r.h0.w, r.h1.x, r.h1.y, r.h1.z, r.h1.w};
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             // four 6-bit quants, one per byte: low nibbles from ql, bits 4..5 from qh (one select for all four)
@@ -188,16 +221,15 @@ __device__ __forceinline__ void decode32(const uint8_t *rowp, uint32_t nblk, uin
             out[2 * j + 1] = pack_bf16(f2, f3);
         }
     } else {
-        // Q8_0: 34-byte blocks, 2-byte aligned; k-block kb = blocks 2 kb and 2 kb + 1.
-        const uint8_t *blk = rowp + (size_t)(2 * kb + part) * 34;
-        const float d = load_f16(blk);
-        const uint16_t *q = reinterpret_cast<const uint16_t *>(blk + 2);
+        const float d = f16_bits_to_f32((uint16_t)r.d);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const uint32_t w0 = q[2 * j], w1 = q[2 * j + 1];
             // signed byte b -> (b ^ 0x80) - 128
-            const float f0 = __fmul_rn(small_to_float((w0 & 0xFFu) ^ 0x80u, 128.f), d), f1 = __fmul_rn(small_to_float((w0 >> 8) ^ 0x80u, 128.f), d);
-            const float f2 = __fmul_rn(small_to_float((w1 & 0xFFu) ^ 0x80u, 128.f), d), f3 = __fmul_rn(small_to_float((w1 >> 8) ^ 0x80u, 128.f), d);
+            const uint32_t u = r.q[j] ^ 0x80808080u;
+            const float f0 = __fmul_rn(small_to_float(__byte_perm(u, 0, 0x4440), 128.f), d);
+            const float f1 = __fmul_rn(small_to_float(__byte_perm(u, 0, 0x4441), 128.f), d);
+            const float f2 = __fmul_rn(small_to_float(__byte_perm(u, 0, 0x4442), 128.f), d);
+            const float f3 = __fmul_rn(small_to_float(__byte_perm(u, 0, 0x4443), 128.f), d);
             out[2 * j] = pack_bf16(f0, f1);
             out[2 * j + 1] = pack_bf16(f2, f3);
         }
@@ -315,34 +347,47 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         const int p = threadIdx.x - 64, r = p >> 1, part = p & 1;
         const bool live = n0 + r < rows;
         const uint8_t *rowp = w + (size_t)min(n0 + r, rows - 1) * pitch;
-        for (uint32_t it = 0; it < k_iters; it++) {
-            const int s = it % A_STAGES;
-            uint32_t v[16];
-            decode32<FMT>(rowp, nblk, k_first + it, part, v); // global loads and arithmetic overlap the wait below
-            if (!live) {
+        // PREFETCH k-blocks of packed bytes are in flight per thread while one is decoded.
+        const uint32_t last = k_first + (k_iters ? k_iters - 1 : 0);
+        Raw<FMT> ring[PREFETCH];
 #pragma unroll
-                for (int i = 0; i < 16; i++) v[i] = 0u;
-            }
-            if (!mbar_wait(&sm->empty_a[s], ((it / A_STAGES) & 1) ^ 1, sm, status)) break;
-            uint8_t *tile_row = sm->a[s] + r * 128;
+        for (int j = 0; j < PREFETCH; j++) ring[j] = load_raw<FMT>(rowp, nblk, min(k_first + j, last), part);
+        bool go = true;
+        for (uint32_t it0 = 0; it0 < k_iters && go; it0 += PREFETCH) {
 #pragma unroll
-            for (int c = 0; c < 4; c++) { // 16-byte chunk 4 part + c of the row, at its swizzled place
-                const int chunk = (4 * part + c) ^ (r & 7);
-                *reinterpret_cast<uint4 *>(tile_row + 16 * chunk) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+            for (int j = 0; j < PREFETCH; j++) {
+                const uint32_t it = it0 + j;
+                if (it >= k_iters) break;
+                const int s = it % A_STAGES;
+                uint32_t v[16];
+                decode_raw<FMT>(ring[j], k_first + it, part, v);
+                ring[j] = load_raw<FMT>(rowp, nblk, min(k_first + it + PREFETCH, last), part);
+                if (!live) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v[i] = 0u;
+                }
+                if (!mbar_wait(&sm->empty_a[s], ((it / A_STAGES) & 1) ^ 1, sm, status)) { go = false; break; }
+                uint8_t *tile_row = sm->a[s] + r * 128;
+#pragma unroll
+                for (int c = 0; c < 4; c++) { // 16-byte chunk 4 part + c of the row, at its swizzled place
+                    const int chunk = (4 * part + c) ^ (r & 7);
+                    *reinterpret_cast<uint4 *>(tile_row + 16 * chunk) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> tensor-core reads
+                mbar_arrive(&sm->full_a[s]);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> tensor-core reads
-            mbar_arrive(&sm->full_a[s]);
         }
-        // Epilogue: warps 2..5 cover the four 32-lane quarters of tensor memory (quarter = warp % 4).
-        if (warp < 6) {
-            const int quarter = warp & 3;
+        // Epilogue: a warp may read the 32 tensor-memory lanes of quarter warp % 4; warps 2..5 take the first
+        // half of the accumulator columns, warps 6..9 the second.
+        {
+            const int quarter = warp & 3, c_begin = warp < 6 ? 0 : BN / 2, c_end = warp < 6 ? BN / 2 : BN;
             if (!mbar_wait(&sm->accum, 0, sm, status)) atomicExch(&sm->abort_flag, 1u);
-            asm volatile("bar.sync 1, 128;" ::: "memory"); // the four epilogue warps agree on whether to go on
+            asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight epilogue warps agree on whether to go on
             const bool ok = *(volatile uint32_t *)&sm->abort_flag == 0;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t row = n0 + 32 * quarter + lane;
             if (ok && (GROUPED || splits <= 1)) {
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                     uint32_t acc[32];
                     tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + c0, acc);
                     if (row < rows) {
@@ -358,7 +403,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
                 // reduction kernel's loads are coalesced.
                 const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
                 float *mine = ws + ((size_t)tile * splits + blockIdx.z) * BN * BM + 32 * quarter + lane;
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                     uint32_t acc[32];
                     tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + c0, acc);
 #pragma unroll
