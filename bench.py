@@ -475,6 +475,36 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_prefill_probe(args):
+    """One matrix of the layer set at M bf16 activation rows, `steps` launches: the small case a profiler
+    capture of the prefill kernel runs on.  Prints the mean device time per launch."""
+    import torch
+    from ferrum_b200 import surface as S
+
+    name, m = args.prefill_probe.split(":")
+    m = int(m)
+    _, rows, cols, fmt = next(e for e in LAYER if e[0] == name)
+    torch.cuda.set_device(0)
+    dev = S.Device(0, use_torch_stream=False)
+    stream = torch.cuda.ExternalStream(dev.stream_ptr(), device=torch.device("cuda", 0))
+    w = S.Matrix.from_packed(dev, rows, cols, 1, fmt, random_matrix(fmt, rows, cols, seed=3))
+    x = torch.randn(m * cols, device="cuda").to(torch.bfloat16)
+    y = torch.zeros(m * rows, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            S.project(dev, w, x, m, y)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            S.project(dev, w, x, m, y)
+        e1.record()
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    print(json.dumps({"probe": "prefill", "matrix": name, "rows": rows, "cols": cols, "m": m, "us_per_launch": round(us, 2),
+                      "tflops": round(2.0 * rows * cols * m / us / 1e6, 1)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -487,8 +517,12 @@ def main():
     ap.add_argument("--no-fuse", action="store_true", help="one launch per matrix instead of one per input group")
     ap.add_argument("--nccl", action="store_true", help="multi-GPU: gather with NCCL (torch.distributed) instead of the peer-push kernel")
     ap.add_argument("--quick", action="store_true", help="headline and per-group timings only")
+    ap.add_argument("--prefill-probe", default=None, metavar="NAME:M",
+                    help="time only the bf16 prefill GEMM of one matrix of the layer set (q, k, o, gate, down ...) at M rows")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.prefill_probe:
+        run_prefill_probe(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

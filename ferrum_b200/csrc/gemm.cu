@@ -33,20 +33,25 @@ namespace {
 constexpr int BM = 128;      // weight rows per block (MMA M)
 // Activation rows per block (MMA N): 256 for dense prefill, 64 for expert groups (about 32 rows each).
 constexpr int BK = 64;       // k per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int A_STAGES = 4;  // ring of decoded weight tiles
 constexpr int PRODUCER_WARPS = 8;
 constexpr int PREFETCH = 3;  // k-blocks of packed bytes in flight per producer thread
 constexpr int THREADS = (2 + PRODUCER_WARPS) * 32;
 constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-// Ring of activation tiles: 4 deep, or 2 deep for the 512-row tile (64 KB per stage).
-template <int BN> constexpr int b_stages() { return BN > 256 ? 2 : 4; }
+// Two rings in shared memory.  A: decoded 128 x 64 weight tiles (16 KB each).  B: activation tiles of at most
+// 256 rows x 64 (one TMA box, one MMA N extent; a 512-row block uses two per k-block, each released on its own
+// so that its reload starts as early as possible).  For the 512-row block the B ring is what keeps the tensor
+// pipe fed (64 KB per k-block is about what an SM can take in from L2 in the time the MMAs need), so it gets
+// the larger share of the 227 KB.
+template <int BN> constexpr int a_stages() { return 4; }
+template <int BN> constexpr int b_slots() { return 4; }
+template <int BN> constexpr int mma_n() { return BN > 256 ? 256 : BN; }
 
 template <int BN> struct __align__(1024) Smem {
-    uint8_t a[A_STAGES][A_BYTES];
-    uint8_t b[b_stages<BN>()][BN * BK * 2];
-    uint64_t full_a[A_STAGES], empty_a[A_STAGES], full_b[b_stages<BN>()], empty_b[b_stages<BN>()], accum;
+    uint8_t a[a_stages<BN>()][A_BYTES];
+    uint8_t b[b_slots<BN>()][mma_n<BN>() * BK * 2];
+    uint64_t full_a[a_stages<BN>()], empty_a[a_stages<BN>()], full_b[b_slots<BN>()], empty_b[b_slots<BN>()], accum;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -239,40 +244,81 @@ __device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int p
 __device__ __forceinline__ void store_out(float *p, float v) { *p = v; }
 __device__ __forceinline__ void store_out(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
-// grid (ceil(rows / 128), ceil(m / BN)[, groups]).  `xmap` describes X as a [m][cols] bf16 tensor, box
-// 64 x BN, 128-byte swizzle.  GROUPED (`h_mm_id*`, src/metal/shaders/hybrid.metal:2430-2523): block z
-// serves activation rows offsets[z] .. offsets[z+1] with the expert stored at slots[z] (or z); a tile that
-// runs past its group reads the next group's rows and simply does not store them.
+// Epilogue, run by the eight producer warps: a warp may read the 32 tensor-memory lanes of
+// quarter warp % 4; warps 2..5 take the first half of the accumulator columns, warps 6..9 the second.
+// A complete tile is rounded and stored to Y; a partial one (a K range only) goes to `part` as fp32,
+// column-major ([col][row]) so that these stores and the fix-up kernel's loads are coalesced.
+template <int BN, typename YT>
+__device__ __forceinline__ void epilogue(uint32_t tmem, int warp, int lane, uint32_t n0, uint32_t rows, uint32_t m0, uint32_t m_end,
+                                      YT *__restrict__ y, float *__restrict__ part) {
+    const int quarter = warp & 3, c_begin = warp < 6 ? 0 : BN / 2, c_end = warp < 6 ? BN / 2 : BN;
+    const uint32_t row = n0 + 32 * quarter + lane;
+    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+        uint32_t acc[32];
+        tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + c0, acc);
+        if (part) {
+            float *mine = part + 32 * quarter + lane;
+#pragma unroll
+            for (int c = 0; c < 32; c++) mine[(size_t)(c0 + c) * BM] = __uint_as_float(acc[c]);
+        } else if (row < rows) {
+#pragma unroll
+            for (int c = 0; c < 32; c++) {
+                const uint32_t tok = m0 + c0 + c;
+                if (tok < m_end) store_out(y + (size_t)tok * rows + row, __uint_as_float(acc[c]));
+            }
+        }
+    }
+}
+
+// `xmap` describes X as a [m][cols] bf16 tensor, box 64 x min(BN, 256), 128-byte swizzle; `b_bytes` is one box.
+//
+// Dense (grid.x blocks): tile t covers weight rows (t % tiles_x) * 128.. and activation rows
+// (t / tiles_x) * BN...  Blocks 0 .. full_tiles-1 compute one whole tile each (whole waves of the machine: the
+// blocks of a wave walk K together, so the activation k-slices they share stay in L2).  The remaining tiles,
+// too few to fill a wave, are split along K: block full_tiles + i computes k-blocks [z * per, (z + 1) * per)
+// of tile full_tiles + i / splits, z = i % splits, and leaves fp32 partial sums in workspace slot i, which
+// k_fixup adds up in split order.
+//
+// GROUPED (`h_mm_id*`, src/metal/shaders/hybrid.metal:2430-2523; grid (ceil(rows / 128), ceil(max_rows / BN),
+// groups)): block z serves activation rows offsets[z] .. offsets[z+1] with the expert stored at slots[z]
+// (or z); one tile per block; a tile that runs past its group reads the next group's rows and does not
+// store them.
 template <int FMT, int BN, typename YT, bool GROUPED>
 __global__ void __launch_bounds__(THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t pitch,
           YT *__restrict__ y, uint32_t m, uint32_t b_bytes, const uint32_t *__restrict__ offsets,
-          const uint32_t *__restrict__ slots, uint32_t experts, uint32_t splits, float *__restrict__ ws, int *status) {
+          const uint32_t *__restrict__ slots, uint32_t experts, uint32_t tiles_x, uint32_t full_tiles, uint32_t splits, uint32_t per,
+          float *__restrict__ ws, int *status) {
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-    constexpr int NSUB = BN > 256 ? BN / 256 : 1, MMA_N = BN / NSUB, B_STAGES = b_stages<BN>();
+    constexpr int NSUB = BN > 256 ? BN / 256 : 1, MMA_N = BN / NSUB, A_STAGES = a_stages<BN>(), B_SLOTS = b_slots<BN>();
     constexpr uint32_t IDESC = idesc_for(MMA_N);
     extern __shared__ uint8_t smem_raw[];
     using SM = Smem<BN>;
     SM *sm = reinterpret_cast<SM *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint32_t m0 = blockIdx.y * BN, m_end = m;
+    uint32_t k_first = 0, k_iters = cols / BK, n0, m0, m_end = m;
+    float *partial = nullptr;
     if (GROUPED) {
         const uint32_t z = blockIdx.z, first = offsets[z], count = offsets[z + 1] - first;
         if (blockIdx.y * BN >= count) return; // uniform for the block: nothing was set up yet
         const uint32_t e = slots ? slots[z] : z;
         if (e >= experts) return;
         w += (size_t)e * rows * pitch;
+        n0 = blockIdx.x * BM;
         m0 = first + blockIdx.y * BN;
         m_end = first + count;
-    }
-    const uint32_t n0 = blockIdx.x * BM;
-    // Split K (dense only, blockIdx.z = split): a matrix with few row tiles still fills the machine; the
-    // partial accumulators go to a workspace and a small kernel adds them in split order.
-    uint32_t k_first = 0, k_iters = cols / BK;
-    if (!GROUPED && splits > 1) {
-        const uint32_t per = (k_iters + splits - 1) / splits;
-        k_first = blockIdx.z * per;
-        k_iters = k_first < k_iters ? min(per, k_iters - k_first) : 0;
+    } else {
+        uint32_t t = blockIdx.x;
+        if (t >= full_tiles) {
+            const uint32_t i = t - full_tiles, z = i % splits;
+            t = full_tiles + i / splits;
+            k_first = z * per;
+            if (k_first >= k_iters) return; // the launcher leaves no split without work
+            k_iters = min(per, k_iters - k_first);
+            partial = ws + (size_t)i * BN * BM;
+        }
+        n0 = (t % tiles_x) * BM;
+        m0 = (t / tiles_x) * BN;
     }
     constexpr uint32_t nblk_div = FMT == FQ_Q8_0 ? 32 : 256;
     const uint32_t nblk = cols / nblk_div;
@@ -282,7 +328,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
             mbar_init(&sm->full_a[s], PRODUCER_WARPS * 32);
             mbar_init(&sm->empty_a[s], 1);
         }
-        for (int s = 0; s < B_STAGES; s++) {
+        for (int s = 0; s < B_SLOTS; s++) {
             mbar_init(&sm->full_b[s], 1);
             mbar_init(&sm->empty_b[s], 1);
         }
@@ -304,21 +350,23 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
     if (warp == 0) {
         if (lane == 0) {
             uint32_t issued = 0;
-            for (uint32_t it = 0; it < k_iters; it++) {
-                const int s = it % B_STAGES;
-                if (!mbar_wait(&sm->empty_b[s], ((it / B_STAGES) & 1) ^ 1, sm, status)) break;
-                mbar_expect_tx(&sm->full_b[s], b_bytes * NSUB);
+            bool ok = true;
+            for (uint32_t it = 0; it < k_iters && ok; it++) {
 #pragma unroll
-                for (int h = 0; h < NSUB; h++) // a TMA box is at most 256 rows
-                    tma_load_2d(sm->b[s] + h * (MMA_N * BK * 2), &xmap, (int)((k_first + it) * BK), (int)(m0 + h * MMA_N), &sm->full_b[s]);
-                issued = it + 1;
+                for (int h = 0; h < NSUB; h++) {
+                    const uint32_t ib = it * NSUB + h, s = ib % B_SLOTS;
+                    if (!(ok = mbar_wait(&sm->empty_b[s], ((ib / B_SLOTS) & 1) ^ 1, sm, status))) break;
+                    mbar_expect_tx(&sm->full_b[s], b_bytes);
+                    tma_load_2d(sm->b[s], &xmap, (int)((k_first + it) * BK), (int)(m0 + h * MMA_N), &sm->full_b[s]);
+                    issued = ib + 1;
+                }
             }
             // On an abort the copies already issued still land: wait for them (bounded) before the
             // block's shared memory goes away.
             if (*(volatile uint32_t *)&sm->abort_flag) {
-                for (uint32_t it = issued > (uint32_t)B_STAGES ? issued - B_STAGES : 0; it < issued; it++) {
-                    const int s = it % B_STAGES;
-                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(&sm->full_b[s], (it / B_STAGES) & 1); i++) {}
+                for (uint32_t ib = issued > (uint32_t)B_SLOTS ? issued - B_SLOTS : 0; ib < issued; ib++) {
+                    const uint32_t s = ib % B_SLOTS;
+                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(&sm->full_b[s], (ib / B_SLOTS) & 1); i++) {}
                 }
             }
         }
@@ -326,21 +374,23 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         if (lane == 0) {
             bool ok = true;
             for (uint32_t it = 0; it < k_iters && ok; it++) {
-                const int sa = it % A_STAGES, sb = it % B_STAGES;
-                ok = mbar_wait(&sm->full_a[sa], (it / A_STAGES) & 1, sm, status) && mbar_wait(&sm->full_b[sb], (it / B_STAGES) & 1, sm, status);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = umma_desc(smem_u32(sm->a[sa])), bdesc = umma_desc(smem_u32(sm->b[sb]));
+                const int sa = it % A_STAGES;
+                if (!mbar_wait(&sm->full_a[sa], (it / A_STAGES) & 1, sm, status)) break;
+                const uint64_t adesc = umma_desc(smem_u32(sm->a[sa]));
 #pragma unroll
-                for (int h = 0; h < NSUB; h++) // each 256-row half of the activation tile has its own accumulator columns
+                for (int h = 0; h < NSUB; h++) { // each 256-row part of the activation tile has its own accumulator columns
+                    const uint32_t ib = it * NSUB + h, sb = ib % B_SLOTS;
+                    if (!(ok = mbar_wait(&sm->full_b[sb], (ib / B_SLOTS) & 1, sm, status))) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t bdesc = umma_desc(smem_u32(sm->b[sb]));
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) // 16 bf16 = 32 bytes = 2 descriptor units along K
-                        umma_bf16(tmem + h * MMA_N, adesc + 2 * k, bdesc + (uint64_t)(h * (MMA_N * BK * 2 / 16)) + 2 * k, IDESC, (it | k) != 0);
-                // both rings get their stage back once these MMAs have read it
-                umma_commit(&sm->empty_a[sa]);
-                umma_commit(&sm->empty_b[sb]);
+                        umma_bf16(tmem + h * MMA_N, adesc + 2 * k, bdesc + 2 * k, IDESC, (it | k) != 0);
+                    umma_commit(&sm->empty_b[sb]); // the slot is free once these MMAs have read it
+                }
+                if (ok) umma_commit(&sm->empty_a[sa]);
             }
-            umma_commit(&sm->accum); // arrives when every MMA issued so far has completed
+            if (ok) umma_commit(&sm->accum); // arrives when every MMA issued so far has completed
         }
     } else {
         // Producers: thread p owns weight row p / 2 of the tile and k part p % 2 of each stage.
@@ -348,7 +398,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         const bool live = n0 + r < rows;
         const uint8_t *rowp = w + (size_t)min(n0 + r, rows - 1) * pitch;
         // PREFETCH k-blocks of packed bytes are in flight per thread while one is decoded.
-        const uint32_t last = k_first + (k_iters ? k_iters - 1 : 0);
+        const uint32_t last = k_first + k_iters - 1;
         Raw<FMT> ring[PREFETCH];
 #pragma unroll
         for (int j = 0; j < PREFETCH; j++) ring[j] = load_raw<FMT>(rowp, nblk, min(k_first + j, last), part);
@@ -377,39 +427,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
                 mbar_arrive(&sm->full_a[s]);
             }
         }
-        // Epilogue: a warp may read the 32 tensor-memory lanes of quarter warp % 4; warps 2..5 take the first
-        // half of the accumulator columns, warps 6..9 the second.
-        {
-            const int quarter = warp & 3, c_begin = warp < 6 ? 0 : BN / 2, c_end = warp < 6 ? BN / 2 : BN;
-            if (!mbar_wait(&sm->accum, 0, sm, status)) atomicExch(&sm->abort_flag, 1u);
-            asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight epilogue warps agree on whether to go on
-            const bool ok = *(volatile uint32_t *)&sm->abort_flag == 0;
+        // Epilogue, all eight producer warps.
+        if (!mbar_wait(&sm->accum, 0, sm, status)) atomicExch(&sm->abort_flag, 1u);
+        asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight warps agree on whether to go on
+        if (*(volatile uint32_t *)&sm->abort_flag == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t row = n0 + 32 * quarter + lane;
-            if (ok && (GROUPED || splits <= 1)) {
-                for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-                    uint32_t acc[32];
-                    tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + c0, acc);
-                    if (row < rows) {
-#pragma unroll
-                        for (int c = 0; c < 32; c++) {
-                            const uint32_t tok = m0 + c0 + c;
-                            if (tok < m_end) store_out(y + (size_t)tok * rows + row, __uint_as_float(acc[c]));
-                        }
-                    }
-                }
-            } else if (ok) {
-                // This split's partial tile, column-major ([col][row]) so that both these stores and the
-                // reduction kernel's loads are coalesced.
-                const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
-                float *mine = ws + ((size_t)tile * splits + blockIdx.z) * BN * BM + 32 * quarter + lane;
-                for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-                    uint32_t acc[32];
-                    tmem_ld32(tmem + ((uint32_t)(32 * quarter) << 16) + c0, acc);
-#pragma unroll
-                    for (int c = 0; c < 32; c++) mine[(size_t)(c0 + c) * BM] = __uint_as_float(acc[c]);
-                }
-            }
+            epilogue<BN, YT>(tmem, warp, lane, n0, rows, m0, m_end, y, partial);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -450,17 +473,18 @@ __global__ void k_to_bf16(const float *__restrict__ x, __nv_bfloat16 *__restrict
     }
 }
 
-// Sum of the split-K partial tiles, in split order (deterministic), rounded and stored as Y.
-// ws[tile][split][col][row]; one thread per four consecutive weight rows of one activation row.
+// The tiles that were split along K: their fp32 partial sums added in split order (deterministic), rounded and
+// stored as Y.  One thread per four consecutive weight rows of one activation row of a split tile.
 template <int BN, typename YT>
 __global__ void __launch_bounds__(256)
-k_splitk_reduce(const float *__restrict__ ws, uint32_t splits, uint32_t n_tiles, uint32_t rows, uint32_t m, YT *__restrict__ y, size_t total) {
+k_fixup(const float *__restrict__ ws, uint32_t full_tiles, uint32_t splits, uint32_t tiles_x, uint32_t rows, uint32_t m, YT *__restrict__ y,
+        size_t total) {
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= total) return;
-    const uint32_t r4 = e % (BM / 4), col = (e / (BM / 4)) % BN, tile = (uint32_t)(e / ((size_t)(BM / 4) * BN));
-    const uint32_t row = (tile % n_tiles) * BM + 4 * r4, tok = (tile / n_tiles) * BN + col;
+    const uint32_t r4 = e % (BM / 4), col = (e / (BM / 4)) % BN, i = (uint32_t)(e / ((size_t)(BM / 4) * BN)), tile = full_tiles + i;
+    const uint32_t row = (tile % tiles_x) * BM + 4 * r4, tok = (tile / tiles_x) * BN + col;
     if (tok >= m || row >= rows) return;
-    const float *p = ws + (((size_t)tile * splits) * BN + col) * BM + 4 * r4;
+    const float *p = ws + (((size_t)i * splits) * BN + col) * BM + 4 * r4;
     float4 sum = __ldcg(reinterpret_cast<const float4 *>(p));
     for (uint32_t z = 1; z < splits; z++) {
         const float4 v = __ldcg(reinterpret_cast<const float4 *>(p + (size_t)z * BN * BM));
@@ -469,8 +493,8 @@ k_splitk_reduce(const float *__restrict__ ws, uint32_t splits, uint32_t n_tiles,
     const float o[4] = {sum.x, sum.y, sum.z, sum.w};
     YT *dst = y + (size_t)tok * rows + row;
 #pragma unroll
-    for (int i = 0; i < 4; i++)
-        if (row + i < rows) store_out(dst + i, o[i]);
+    for (int j = 0; j < 4; j++)
+        if (row + j < rows) store_out(dst + j, o[j]);
 }
 
 template <int FMT, int BN, typename YT, bool GROUPED>
@@ -482,27 +506,33 @@ int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_
         if (e != cudaSuccess) return fq_check_cuda(dev, e, "gemm shared memory");
         configured = true;
     }
-    dim3 grid((a.rows + BM - 1) / BM, GROUPED ? (a.max_rows + BN - 1) / BN : (m_rows + BN - 1) / BN, GROUPED ? a.groups : 1);
-    uint32_t splits = 1;
-    if (!GROUPED) {
-        // Few tiles: split K so that about one block per SM runs, each with at least 8 stages, within the
-        // workspace and the counter table.
-        const uint32_t tiles = grid.x * grid.y, k_iters = a.cols / BK;
-        if (tiles * 4 < (uint32_t)dev->sm_count * 3) {
-            splits = std::min<uint32_t>({(uint32_t)dev->sm_count / tiles, std::max(1u, k_iters / 8), 16u});
-            const size_t per_split = (size_t)tiles * BM * BN * sizeof(float);
-            splits = (uint32_t)std::min<size_t>(splits, dev->gemm_ws_bytes / per_split);
-            if (splits < 1) splits = 1;
-            const uint32_t per = (k_iters + splits - 1) / splits;
-            splits = (k_iters + per - 1) / per; // no split is left without work
-        }
-        grid.z = splits;
+    const uint32_t tiles_x = (a.rows + BM - 1) / BM, k_iters = a.cols / BK;
+    if (GROUPED) {
+        dim3 grid(tiles_x, (a.max_rows + BN - 1) / BN, a.groups);
+        k_gemm_tc<FMT, BN, YT, GROUPED><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
+                                                                              a.offsets, a.slots, a.experts, tiles_x, 0, 1, k_iters, dev->gemm_ws, status);
+        return FQ_OK;
     }
-    k_gemm_tc<FMT, BN, YT, GROUPED><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
-                                                                          a.offsets, a.slots, a.experts, splits, dev->gemm_ws, status);
+    // Whole waves of tiles run one tile per block.  A remainder that would fill less than three quarters of a
+    // wave is split along K into about one block per SM, each with at least 8 k-blocks and a workspace slot.
+    const uint32_t tiles = tiles_x * ((m_rows + BN - 1) / BN), sms = (uint32_t)dev->sm_count;
+    const uint32_t rest = tiles % sms;
+    uint32_t full = tiles, splits = 1, per = k_iters;
+    if (rest && rest * 4 < sms * 3) {
+        const uint32_t cap = (uint32_t)std::min<size_t>(sms / rest, dev->gemm_ws_bytes / ((size_t)rest * BN * BM * sizeof(float)));
+        const uint32_t want = std::min({cap, std::max(1u, k_iters / 8), 16u});
+        if (want > 1) {
+            per = (k_iters + want - 1) / want;
+            splits = (k_iters + per - 1) / per; // no split is left without work
+            full = tiles - rest;
+        }
+    }
+    const uint32_t blocks = full + (tiles - full) * splits;
+    k_gemm_tc<FMT, BN, YT, GROUPED><<<blocks, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
+                                                                            a.offsets, a.slots, a.experts, tiles_x, full, splits, per, dev->gemm_ws, status);
     if (splits > 1) {
-        const size_t total = (size_t)grid.x * grid.y * BN * (BM / 4);
-        k_splitk_reduce<BN, YT><<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(dev->gemm_ws, splits, grid.x, a.rows, m_rows, (YT *)a.y, total);
+        const size_t threads = (size_t)(tiles - full) * BN * (BM / 4);
+        k_fixup<BN, YT><<<(unsigned)((threads + 255) / 256), 256, 0, dev->stream>>>(dev->gemm_ws, full, splits, tiles_x, a.rows, m_rows, (YT *)a.y, threads);
     }
     return FQ_OK;
 }

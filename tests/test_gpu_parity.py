@@ -568,6 +568,24 @@ def test_bf16_gemm_matches_the_cpu_dequant(device, fmt, m, cols, rows):
 
 
 @pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("m,cols,rows", [(2048, 512, 10240), (1100, 768, 5000), (600, 256, 19200)])
+def test_bf16_gemm_whole_waves_plus_split_tail(device, fmt, m, cols, rows):
+    """More tiles than SMs but not whole waves: the tiles of the last, partly filled wave are split along K and
+    summed by the fix-up kernel; the others are computed whole."""
+    packed = ref.random_matrix(fmt, rows, cols, seed=m)
+    xb = ref.round_bf16(np.random.default_rng(m + 1).standard_normal((m, cols)).astype(np.float32))
+    dense_b = ref.round_bf16(ref.dequant(fmt, packed)).reshape(rows, cols)
+    want = xb @ dense_b.T
+    got = run_project_bf16(device, fmt, packed, rows, cols, xb, m).float().cpu().numpy().reshape(m, rows)
+    assert np.isfinite(got).all()
+    err = np.abs(got - want).max() / np.abs(want).max()
+    assert err <= 6e-3, err
+    # the same call again gives the same bits (fixed summation order)
+    again = run_project_bf16(device, fmt, packed, rows, cols, xb, m).float().cpu().numpy().reshape(m, rows)
+    assert np.array_equal(got, again)
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
 def test_bf16_gemm_weight_tiles_are_bit_exact(device, fmt):
     """X = identity makes Y the weight tile itself: it must equal bf16_rne(exact fp32 decode) bit for bit."""
     rows, cols = 200, 512
