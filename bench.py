@@ -406,6 +406,19 @@ def moe_bench(S, dev, stream, torch, timed_ms):
         flops = 2.0 * T * (USED + 1) * 3 * F * H
         res[f"t{T}"] = {"us": round(ms * 1e3, 1), "weight_gbs": round(touched / (ms * 1e-3) / 1e9, 1),
                         "tflops": round(flops / (ms * 1e-3) / 1e12, 2), "weight_bytes": touched}
+    # The same model's Q8_0 output head at M = 1 (65,536 of its 151,936 rows: 142 MB, larger than L2).
+    rows = 65536
+    head = M(dev, rows, H, 1, Q8_0, random_matrix(Q8_0, rows, H, 907))
+    x = (torch.randn(H, device="cuda") * 0.12).contiguous()
+    yh = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    dev.capture_begin()
+    S.project(dev, head, x, 1, yh)
+    g = dev.capture_end()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            g.launch()
+    ms = timed_ms(g.launch, 20) / 20
+    res["q8_0_head_m1"] = {"us": round(ms * 1e3, 1), "gbs": round(rows * (H // 32 * 34) / (ms * 1e-3) / 1e9, 1)}
     return res
 
 

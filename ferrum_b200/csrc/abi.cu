@@ -390,7 +390,7 @@ extern "C" int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint6
     w->block_bytes = bb;
     w->pitch = fq_row_pitch(format, (uint32_t)cols);
     const size_t dev_len = (size_t)w->pitch * w->rows;
-    // Q6_K is regrouped by field on the host (see blocks.cuh); the other formats upload as they are.
+    // Q6_K and Q8_0 are regrouped by field on the host (see blocks.cuh); Q4_K uploads as it is.
     std::vector<uint8_t> regrouped;
     const uint8_t *upload = (const uint8_t *)packed;
     if (format == FQ_Q6_K) {
@@ -404,6 +404,18 @@ extern "C" int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint6
                 memcpy(dst + 128 * nb + 64 * b, src + 128, 64);
                 memcpy(dst + 192 * nb + 16 * b, src + 192, 16);
                 memcpy(dst + 208 * nb + 2 * b, src + 208, 2);
+            }
+        }
+        upload = regrouped.data();
+    } else if (format == FQ_Q8_0) {
+        regrouped.assign(dev_len, 0);
+        const size_t nb = cols / 32;
+        for (size_t r = 0; r < w->rows; r++) {
+            const uint8_t *src = (const uint8_t *)packed + r * row_bytes;
+            uint8_t *dst = regrouped.data() + r * w->pitch;
+            for (size_t b = 0; b < nb; b++, src += 34) {
+                memcpy(dst + 32 * nb + 2 * b, src, 2);
+                memcpy(dst + 32 * b, src + 2, 32);
             }
         }
         upload = regrouped.data();
@@ -468,6 +480,10 @@ static int check_dtype(fq_device *dev, int dt) {
 // projections), the f16 tensor-core kernel up to FQ_GEMV_MAX_M.  FQ_GEMV=f16 forces the latter.
 static int launch_decode(fq_device *dev, const ProjectArgs *a, uint32_t count) {
     static const bool f16_only = [] { const char *e = getenv("FQ_GEMV"); return e && e[0] == 'f'; }();
+    if (count == 1 && a[0].format == FQ_Q8_0) {
+        int rc = fq_launch_gemv_q8(dev, a[0]);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
     if (!f16_only) {
         int rc = fq_launch_gemv_i8_many(dev, a, count);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
@@ -496,7 +512,7 @@ extern "C" int fq_project(fq_device *dev, const fq_matrix *w, const void *x, int
     if (!dev->exact) {
         int rc = FQ_ERR_UNSUPPORTED;
         if (m <= (size_t)FQ_GEMV_MAX_M && x_dtype == FQ_F32 && y_dtype == FQ_F32) rc = launch_decode(dev, &a, 1);
-        else if (x_dtype == FQ_BF16 && y_dtype == FQ_BF16) rc = fq_launch_gemm_tc(dev, a);
+        else if (x_dtype == y_dtype) rc = fq_launch_gemm_tc(dev, a);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
     if (int rc = fq_launch_project_exact(dev, a)) return rc;
@@ -677,7 +693,14 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
     MoeScratch s = moe_layout(f, m, scratch);
     if (scratch_elems < s.total) return fq_fail(dev, FQ_ERR_SHAPE, "MoE scratch holds %zu of %zu floats", scratch_elems, s.total);
     const size_t routes = m * used;
-    if (int rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts)) return rc;
+    {
+        // The router keeps fp32 arithmetic at every width: expert choice is a comparison of its outputs.
+        const int keep = dev->exact;
+        if (m > (size_t)FQ_GEMV_MAX_M) dev->exact = 1;
+        const int rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts);
+        dev->exact = keep;
+        if (rc) return rc;
+    }
     const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
     if (int rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m,
                               f->sigmoid, f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate))
@@ -692,11 +715,13 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
         if (int rc = fq_project_id(dev, f->down_exps, s.act, routes * ef, s.ids, routes, 1, s.down, routes * hidden)) return rc;
     } else {
         if (int rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position)) return rc;
-        if (int rc = fq_moe_gather(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_F32, routes * hidden, s.offsets, nullptr, experts, m, s.g, FQ_F32, routes * ef)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_F32, routes * hidden, s.offsets, nullptr, experts, m, s.u, FQ_F32, routes * ef)) return rc;
-        if (int rc = fq_glu(dev, s.g, s.u, routes * ef, s.act)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_F32, routes * ef, s.offsets, nullptr, experts, m, s.down, FQ_F32, routes * hidden)) return rc;
+        // Expert-sorted rows through the tensor-core GEMM: activations rounded to bf16 once (at the gather and
+        // at the gated unit), fp32 accumulation and fp32 results.
+        if (int rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.g, FQ_F32, routes * ef)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.u, FQ_F32, routes * ef)) return rc;
+        if (int rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, s.act)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_BF16, routes * ef, s.offsets, nullptr, experts, m, s.down, FQ_F32, routes * hidden)) return rc;
     }
     return fq_moe_combine(dev, s.down, s.weights, identity ? s.ids : s.position, s.shared, s.gate, (uint32_t)hidden,
                           (uint32_t)used, (uint32_t)m, identity, out);

@@ -50,16 +50,17 @@ __device__ __forceinline__ float q6k_value(float d, int scale, uint32_t q) {
     return __fmul_rn(__fmul_rn(d, (float)scale), (float)q - 32.0f);
 }
 
-// Device layouts.  Q4_K and Q8_0 rows are the GGUF bytes.  Q6_K rows are the same bytes regrouped
-// by field at load time so that every field is 16-byte aligned (210-byte blocks are not): with
-// nb blocks in the row,
-//   ql of block b at 128 b, qh at 128 nb + 64 b, scales at 192 nb + 16 b, d at 208 nb + 2 b,
-// and the row pitch is 210 nb rounded up to 16 bytes.
+// Device layouts.  Q4_K rows are the GGUF bytes.  Q6_K and Q8_0 rows are the same bytes regrouped by
+// field at load time so that every field is 16-byte aligned (210- and 34-byte blocks are not): with nb
+// blocks in the row,
+//   Q6_K: ql of block b at 128 b, qh at 128 nb + 64 b, scales at 192 nb + 16 b, d at 208 nb + 2 b,
+//   Q8_0: qs of block b at 32 b, d at 32 nb + 2 b,
+// and the row pitch is the packed row size (210 nb, 34 nb) rounded up to 16 bytes.
 __host__ __device__ inline uint32_t fq_row_pitch(int format, uint32_t cols) {
     switch (format) {
     case FQ_Q4_K: return cols / 256 * 144;
     case FQ_Q6_K: return (cols / 256 * 210 + 15u) & ~15u;
-    default: return cols / 32 * 34;
+    default: return (cols / 32 * 34 + 15u) & ~15u;
     }
 }
 
@@ -87,9 +88,8 @@ template <> __device__ __forceinline__ float decode_at<FQ_Q6_K>(const uint8_t *r
     return q6k_value(load_f16(d), scale, nib | (hi << 4));
 }
 
-template <> __device__ __forceinline__ float decode_at<FQ_Q8_0>(const uint8_t *row, uint32_t, uint32_t b, int idx) {
-    const uint8_t *blk = row + (size_t)b * 34;
-    return __fmul_rn((float)(int)(int8_t)blk[2 + idx], load_f16(blk));
+template <> __device__ __forceinline__ float decode_at<FQ_Q8_0>(const uint8_t *row, uint32_t nb, uint32_t b, int idx) {
+    return __fmul_rn((float)(int)(int8_t)row[(size_t)b * 32 + idx], load_f16(row + (size_t)nb * 32 + (size_t)b * 2));
 }
 
 // Round to nearest even (src/hybrid/draft/gguf.rs:362-369).  cvt.rn.bf16.f32 agrees for every

@@ -164,11 +164,11 @@ __device__ __forceinline__ Raw<FMT> load_raw(const uint8_t *rowp, uint32_t nblk,
         r.sc = *reinterpret_cast<const uint16_t *>(rowp + (size_t)nblk * 192 + (size_t)b * 16 + 8 * n + 2 * i);
         r.d = *reinterpret_cast<const uint16_t *>(rowp + (size_t)nblk * 208 + (size_t)b * 2);
     } else {
-        // Q8_0: 34-byte blocks, 2-byte aligned; k-block kb = blocks 2 kb and 2 kb + 1.
-        const uint16_t *blk = reinterpret_cast<const uint16_t *>(rowp + (size_t)(2 * kb + part) * 34);
-        r.d = blk[0];
-#pragma unroll
-        for (int j = 0; j < 8; j++) r.q[j] = (uint32_t)blk[1 + 2 * j] | ((uint32_t)blk[2 + 2 * j] << 16);
+        // Q8_0 (device layout of blocks.cuh): k-block kb = blocks 2 kb and 2 kb + 1; part selects the block.
+        const uint32_t b = 2 * kb + part;
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(rowp + (size_t)b * 32), q1 = *reinterpret_cast<const uint4 *>(rowp + (size_t)b * 32 + 16);
+        r.q[0] = q0.x, r.q[1] = q0.y, r.q[2] = q0.z, r.q[3] = q0.w, r.q[4] = q1.x, r.q[5] = q1.y, r.q[6] = q1.z, r.q[7] = q1.w;
+        r.d = *reinterpret_cast<const uint16_t *>(rowp + (size_t)nblk * 32 + (size_t)b * 2);
     }
     return r;
 }
@@ -279,8 +279,8 @@ __device__ __forceinline__ void epilogue(uint32_t tmem, int warp, int lane, uint
 // of tile full_tiles + i / splits, z = i % splits, and leaves fp32 partial sums in workspace slot i, which
 // k_fixup adds up in split order.
 //
-// GROUPED (`h_mm_id*`, src/metal/shaders/hybrid.metal:2430-2523; grid (ceil(rows / 128), ceil(max_rows / BN),
-// groups)): block z serves activation rows offsets[z] .. offsets[z+1] with the expert stored at slots[z]
+// GROUPED (`h_mm_id*`, src/metal/shaders/hybrid.metal:2430-2523; grid (ceil(rows / 128), activation tiles of
+// all groups)): group z serves activation rows offsets[z] .. offsets[z+1] with the expert stored at slots[z]
 // (or z); one tile per block; a tile that runs past its group reads the next group's rows and does not
 // store them.
 template <int FMT, int BN, typename YT, bool GROUPED>
@@ -299,13 +299,39 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
     uint32_t k_first = 0, k_iters = cols / BK, n0, m0, m_end = m;
     float *partial = nullptr;
     if (GROUPED) {
-        const uint32_t z = blockIdx.z, first = offsets[z], count = offsets[z + 1] - first;
-        if (blockIdx.y * BN >= count) return; // uniform for the block: nothing was set up yet
+        // blockIdx.y counts activation tiles over all groups in order; `full_tiles` holds the group count.
+        // Every warp finds (group z, tile ty of that group) for itself: 32 groups per step, tile counts
+        // prefix-summed with shuffles.
+        const uint32_t groups = full_tiles, ft = blockIdx.y;
+        uint32_t z = 0, ty = 0, base = 0;
+        bool found = false;
+        for (uint32_t g0 = 0; g0 < groups && !found; g0 += 32) {
+            const uint32_t g = g0 + lane;
+            const uint32_t cnt = g < groups ? offsets[g + 1] - offsets[g] : 0u, t = (cnt + BN - 1) / BN;
+            uint32_t incl = t;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t n = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += n;
+            }
+            const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+            if (ft < base + total) {
+                const uint32_t hit = __ballot_sync(0xffffffffu, ft >= base + incl - t && ft < base + incl);
+                const int src = __ffs(hit) - 1;
+                z = g0 + src;
+                ty = ft - (base + __shfl_sync(0xffffffffu, incl - t, src));
+                found = true;
+            } else {
+                base += total;
+            }
+        }
+        if (!found) return; // uniform for the block: nothing was set up yet
+        const uint32_t first = offsets[z], count = offsets[z + 1] - first;
         const uint32_t e = slots ? slots[z] : z;
         if (e >= experts) return;
         w += (size_t)e * rows * pitch;
         n0 = blockIdx.x * BM;
-        m0 = first + blockIdx.y * BN;
+        m0 = first + ty * BN;
         m_end = first + count;
     } else {
         uint32_t t = blockIdx.x;
@@ -508,9 +534,13 @@ int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_
     }
     const uint32_t tiles_x = (a.rows + BM - 1) / BM, k_iters = a.cols / BK;
     if (GROUPED) {
-        dim3 grid(tiles_x, (a.max_rows + BN - 1) / BN, a.groups);
+        // At most one partly filled tile per group on top of the full ones (m_rows = all groups' rows).
+        const uint32_t per_group = (a.max_rows + BN - 1) / BN;
+        const uint32_t tiles_y = (uint32_t)std::min<uint64_t>((uint64_t)per_group * a.groups, (uint64_t)m_rows / BN + a.groups);
+        if (tiles_y > 65535) return FQ_ERR_UNSUPPORTED;
+        dim3 grid(tiles_x, tiles_y, 1);
         k_gemm_tc<FMT, BN, YT, GROUPED><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
-                                                                              a.offsets, a.slots, a.experts, tiles_x, 0, 1, k_iters, dev->gemm_ws, status);
+                                                                              a.offsets, a.slots, a.experts, tiles_x, a.groups, 1, k_iters, dev->gemm_ws, status);
         return FQ_OK;
     }
     // Whole waves of tiles run one tile per block.  A remainder that would fill less than three quarters of a
@@ -564,38 +594,56 @@ int make_map(fq_device *dev, CUtensorMap *map, const void *x, uint32_t cols, uin
 
 } // namespace
 
+// X as bf16 in the handle's scratch (the halves of which successive calls alternate between), or null if
+// it does not fit.
+static const void *x_as_bf16(fq_device *dev, const void *x, size_t n) {
+    if (n * 2 > dev->xprep_bytes / 2) return nullptr;
+    dev->xprep_turn ^= 1u;
+    __nv_bfloat16 *tmp = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0));
+    k_to_bf16<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, dev->stream>>>((const float *)x, tmp, n);
+    return tmp;
+}
+
+// Dense projection with at least 32 activation rows: BF16 in / BF16 out, or F32 in / F32 out with X rounded to
+// bf16 first (the reference's wide F32 path likewise multiplies a 16-bit weight tile, `h_mm_*`,
+// src/metal/shaders/hybrid.metal:1411-1469).
 int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
-    if (a.x_dtype != FQ_BF16 || a.y_dtype != FQ_BF16 || a.cols % BK || a.ids || a.offsets) return FQ_ERR_UNSUPPORTED;
+    if (a.x_dtype != a.y_dtype || a.cols % BK || a.ids || a.offsets) return FQ_ERR_UNSUPPORTED;
     if (a.format != FQ_Q4_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
     if (a.format == FQ_Q4_K && (a.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
-    if (a.m < 32) return FQ_ERR_UNSUPPORTED; // narrow inputs: the fp32 kernels serve them
+    if (a.m <= (uint32_t)FQ_GEMV_MAX_M) return FQ_ERR_UNSUPPORTED; // decode and verify widths: the fp32 kernels serve them
+    const void *xb = a.x;
+    int kernels = 1;
+    if (a.x_dtype == FQ_F32) {
+        if (!(xb = x_as_bf16(dev, a.x, (size_t)a.m * a.cols))) return FQ_ERR_UNSUPPORTED;
+        kernels = 2;
+    }
     CUtensorMap map;
     uint32_t b_bytes = 0;
-    if (int rc = make_map(dev, &map, a.x, a.cols, a.m, 256, &b_bytes)) return rc;
+    if (int rc = make_map(dev, &map, xb, a.cols, a.m, 256, &b_bytes)) return rc;
     // 512 activation rows per block (two accumulators sharing each decoded weight tile) once there are
     // enough rows to fill them; the TMA box stays 256 rows.
-    if (a.m >= 384) {
-        if (int rc = launch_fmt<512, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m)) return rc;
-    } else if (int rc = launch_fmt<256, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m)) return rc;
-    return fq_end_enqueue(dev, "gemm_tc", 1);
+    int rc;
+    if (a.y_dtype == FQ_F32)
+        rc = a.m >= 384 ? launch_fmt<512, float, false>(dev, a, map, b_bytes, a.m) : launch_fmt<256, float, false>(dev, a, map, b_bytes, a.m);
+    else
+        rc = a.m >= 384 ? launch_fmt<512, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m)
+                        : launch_fmt<256, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m);
+    if (rc != FQ_OK) return rc;
+    return fq_end_enqueue(dev, "gemm_tc", kernels);
 }
 
 // Expert-sorted rows (`project_mm_id_in`): x is [total_rows][cols], F32 (converted to bf16 into the
-// handle's scratch first) or BF16; y is F32 or BF16 accordingly.
+// handle's scratch first) or BF16; y is F32 or BF16.
 int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t total_rows) {
-    if (a.cols % BK || !a.offsets || a.x_dtype != a.y_dtype) return FQ_ERR_UNSUPPORTED;
+    if (a.cols % BK || !a.offsets) return FQ_ERR_UNSUPPORTED;
     if (a.format != FQ_Q4_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
     if (a.format == FQ_Q4_K && (a.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
     if (a.groups > 65535 || total_rows == 0) return FQ_ERR_UNSUPPORTED;
     const void *xb = a.x;
     int kernels = 1;
     if (a.x_dtype == FQ_F32) {
-        const size_t n = (size_t)total_rows * a.cols;
-        if (n * 2 > dev->xprep_bytes / 2) return FQ_ERR_UNSUPPORTED;
-        dev->xprep_turn ^= 1u;
-        __nv_bfloat16 *tmp = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0));
-        k_to_bf16<<<(unsigned)((n / 4 + 255) / 256 + 1), 256, 0, dev->stream>>>((const float *)a.x, tmp, n);
-        xb = tmp;
+        if (!(xb = x_as_bf16(dev, a.x, (size_t)total_rows * a.cols))) return FQ_ERR_UNSUPPORTED;
         kernels = 2;
     }
     CUtensorMap map;

@@ -107,6 +107,12 @@ size_t fq_gemv_scratch_bytes();
 // (same fallback contract).
 int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
 // tcgen05 dequant-GEMM (BF16 in/out); same fallback contract.
+// Q8_0 integer-dot GEMV (M <= FQ_GEMV_MAX_M, F32 in/out, no routes); FQ_ERR_UNSUPPORTED otherwise.
+int fq_launch_gemv_q8(fq_device *dev, const ProjectArgs &a);
 int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a);
 // The same over expert-sorted activation rows (a.offsets / a.slots / a.groups / a.max_rows); F32 or BF16.
 int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t total_rows);
+// Expert-sorted activations and the gated unit with bf16 results (inputs of the grouped tensor-core GEMM).
+int fq_launch_moe_gather_bf16(fq_device *dev, const float *x, const uint32_t *sorted, uint32_t hidden, uint32_t used, uint32_t routes,
+                              void *xg);
+int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_t n, void *out);

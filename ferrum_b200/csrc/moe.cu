@@ -1,6 +1,8 @@
 // Mixture-of-experts glue: routing, expert-major map, gather, combine and the gated unit.
 // Contracts follow the reference kernels h_moe_route / h_moe_map / h_moe_gather / h_moe_combine /
 // h_swiglu (src/metal/shaders/hybrid.metal:2252-2388, 1606-1613).
+#include <cuda_bf16.h>
+
 #include "internal.h"
 
 namespace {
@@ -221,7 +223,45 @@ __global__ void k_swiglu(const float *__restrict__ g, const float *__restrict__ 
     }
 }
 
+// The two kernels above with bf16 results, for the tensor-core expert GEMM that follows them.
+__global__ void k_moe_gather_bf16(const float *__restrict__ x, const uint32_t *__restrict__ sorted, uint32_t hidden,
+                                  uint32_t used, __nv_bfloat16 *__restrict__ xg) {
+    const uint32_t row = blockIdx.x;
+    const float *src = x + (size_t)(sorted[row] / used) * hidden;
+    __nv_bfloat16 *dst = xg + (size_t)row * hidden;
+    if ((hidden & 3u) == 0) {
+        for (uint32_t i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4 *>(src)[i];
+            const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+            reinterpret_cast<uint2 *>(dst)[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = __float2bfloat16_rn(src[i]);
+    }
+}
+
+__global__ void k_swiglu_bf16(const float *__restrict__ g, const float *__restrict__ u, size_t n, __nv_bfloat16 *__restrict__ y) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float x = g[i];
+        y[i] = __float2bfloat16_rn(x / (1.f + expf(-x)) * u[i]);
+    }
+}
+
 } // namespace
+
+int fq_launch_moe_gather_bf16(fq_device *dev, const float *x, const uint32_t *sorted, uint32_t hidden, uint32_t used, uint32_t routes,
+                              void *xg) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    k_moe_gather_bf16<<<routes, 256, 0, dev->stream>>>(x, sorted, hidden, used, (__nv_bfloat16 *)xg);
+    return fq_end_enqueue(dev, "moe_gather", 1);
+}
+
+int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_t n, void *out) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    k_swiglu_bf16<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(gate, up, n, (__nv_bfloat16 *)out);
+    return fq_end_enqueue(dev, "glu", 1);
+}
 
 extern "C" int fq_moe_route(fq_device *dev, const float *logits, const float *x, const float *shared_w,
                             uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens, int sigmoid,

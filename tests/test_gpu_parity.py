@@ -130,8 +130,21 @@ def test_project_m64_and_bf16(device, fmt):
     rows, cols = 65, 512
     packed = blocks_for(fmt, rows, cols, "random", seed=5)
     x = np.random.default_rng(6).standard_normal((64, cols)).astype(np.float32)
+    want64 = ref.matmul(fmt, packed, rows, cols, x, 64, mode=0)
+    # F32 in / F32 out wider than the verify widths: operands rounded to 16 bits for the tensor cores, as the
+    # reference's wide path does with its weight tile (src/metal/shaders/hybrid.metal:1411-1469) ...
     got = run_project(device, fmt, packed, rows, cols, x, 64)
-    assert ref.rel_err(got, ref.matmul(fmt, packed, rows, cols, x, 64, mode=0)) <= TOL_F32
+    assert ref.rel_err(got, want64) <= TOL_BF16
+    # ... and m = 17, the narrowest such call
+    got = run_project(device, fmt, packed, rows, cols, x[:17], 17)
+    assert ref.rel_err(got, want64[:17]) <= TOL_BF16
+    # ... unless exact arithmetic is asked for
+    device.set_exact(True)
+    try:
+        got = run_project(device, fmt, packed, rows, cols, x, 64)
+    finally:
+        device.set_exact(False)
+    assert ref.rel_err(got, want64) <= TOL_F32
     # bf16 in / bf16 out, M = 35 (src/ops/transformer.rs:3116-3160): operands rounded to bf16.
     xb = ref.round_bf16(x[:35])
     want = ref.matmul(fmt, packed, rows, cols, xb, 35, mode=0)
