@@ -37,7 +37,9 @@ constexpr int PRODUCER_WARPS = 8;
 constexpr int PREFETCH = 3;  // k-blocks of packed bytes in flight per producer thread
 constexpr int THREADS = (2 + PRODUCER_WARPS) * 32;
 constexpr uint32_t A_BYTES = BM * BK * 2;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;          // attempts, where a wait only drains what is in flight
+constexpr uint32_t WAIT_HINT_NS = 20000;          // how long one attempt may park the thread
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull; // a wait gives up after two seconds
 
 // Two rings in shared memory.  A: decoded 128 x 64 weight tiles (16 KB each).  B: activation tiles of at most
 // 256 rows x 64 (one TMA box, one MMA N extent; a 512-row block uses two per k-block, each released on its own
@@ -67,20 +69,30 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+// One attempt; the hardware may park the thread for up to `hint_ns` while the phase is still open, so a
+// waiting thread does not burn issue slots that the decoding warps need.
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity, uint32_t hint_ns = 0) {
     uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
                  : "=r"(ok)
-                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
                  : "memory");
     return ok != 0;
 }
-// Bounded wait.  On giving up: record the timeout, raise the block's abort flag, report failure.
+__device__ __forceinline__ uint64_t now_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait (WAIT_LIMIT_NS of wall time).  On giving up: record the timeout, raise the block's abort
+// flag, report failure.
 template <class SM> __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SM *sm, int *status) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try(bar, parity)) return true;
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t t0 = now_ns();
+    do {
+        if (mbar_try(bar, parity, WAIT_HINT_NS)) return true;
         if (*(volatile uint32_t *)&sm->abort_flag) return false;
-    }
+    } while (now_ns() - t0 < WAIT_LIMIT_NS);
     *(volatile int *)status = (int)FQ_ERR_TIMEOUT;
     atomicExch(&sm->abort_flag, 1u);
     return false;
@@ -191,15 +203,19 @@ __device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int p
         }
         const float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu)), dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
         const float ds = __fmul_rn(d, small_to_float(sc)), dm = __fmul_rn(dmin, small_to_float(mn));
+        // fl(ds * q) in one FMA: with Q = 2^23 + q (the quant dropped into the mantissa of 2^23),
+        // ds * Q - ds * 2^23 is rounded once, and ds * 2^23 is exact, so the result is the correctly rounded
+        // product, the same bits as converting q and multiplying.
+        const float ds23 = -__fmul_rn(ds, 8388608.0f);
         const uint32_t w[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const uint32_t v = part ? (w[i] >> 4) : w[i];
             const uint32_t n4 = v & 0x0F0F0F0Fu; // one quant per byte; each byte moves into a float mantissa with one PRMT
-            const float f0 = __fsub_rn(__fmul_rn(ds, small_to_float(__byte_perm(n4, 0, 0x4440))), dm);
-            const float f1 = __fsub_rn(__fmul_rn(ds, small_to_float(__byte_perm(n4, 0, 0x4441))), dm);
-            const float f2 = __fsub_rn(__fmul_rn(ds, small_to_float(__byte_perm(n4, 0, 0x4442))), dm);
-            const float f3 = __fsub_rn(__fmul_rn(ds, small_to_float(__byte_perm(n4, 0, 0x4443))), dm);
+            const float f0 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7440)), ds23), dm);
+            const float f1 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7441)), ds23), dm);
+            const float f2 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7442)), ds23), dm);
+            const float f3 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7443)), ds23), dm);
             out[2 * i] = pack_bf16(f0, f1);
             out[2 * i + 1] = pack_bf16(f2, f3);
         }
@@ -284,7 +300,7 @@ __device__ __forceinline__ void epilogue(uint32_t tmem, int warp, int lane, uint
 // (or z); one tile per block; a tile that runs past its group reads the next group's rows and does not
 // store them.
 template <int FMT, int BN, typename YT, bool GROUPED>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, GROUPED ? 2 : 1) // two expert-tile blocks share an SM: one's set-up and epilogue overlap the other's main loop
 k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t pitch,
           YT *__restrict__ y, uint32_t m, uint32_t b_bytes, const uint32_t *__restrict__ offsets,
           const uint32_t *__restrict__ slots, uint32_t experts, uint32_t tiles_x, uint32_t full_tiles, uint32_t splits, uint32_t per,
