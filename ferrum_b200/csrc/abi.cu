@@ -693,14 +693,7 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
     MoeScratch s = moe_layout(f, m, scratch);
     if (scratch_elems < s.total) return fq_fail(dev, FQ_ERR_SHAPE, "MoE scratch holds %zu of %zu floats", scratch_elems, s.total);
     const size_t routes = m * used;
-    {
-        // The router keeps fp32 arithmetic at every width: expert choice is a comparison of its outputs.
-        const int keep = dev->exact;
-        if (m > (size_t)FQ_GEMV_MAX_M) dev->exact = 1;
-        const int rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts);
-        dev->exact = keep;
-        if (rc) return rc;
-    }
+    if (int rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts)) return rc;
     const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
     if (int rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m,
                               f->sigmoid, f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate))

@@ -185,9 +185,19 @@ __device__ __forceinline__ Raw<FMT> load_raw(const uint8_t *rowp, uint32_t nblk,
     return r;
 }
 
-// Raw bytes -> 32 weights decoded exactly and rounded to bf16, two per register.
+// Two decoded weights as a bf16 pair: the values rounded to bf16, or (lo) what that rounding dropped.
+__device__ __forceinline__ uint32_t pack_term(float a, float b, bool lo) {
+    if (lo) {
+        a -= __bfloat162float(__float2bfloat16_rn(a));
+        b -= __bfloat162float(__float2bfloat16_rn(b));
+    }
+    return pack_bf16(a, b);
+}
+
+// Raw bytes -> 32 weights decoded exactly and rounded to bf16 (or, with `lo`, the bf16 of the rounding
+// residue), two per register.
 template <int FMT>
-__device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int part, uint32_t (&out)[16]) {
+__device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int part, bool lo, uint32_t (&out)[16]) {
     if constexpr (FMT == FQ_Q4_K) {
         const uint32_t c = kb & 3;
         const uint4 hdr = r.hdr;
@@ -216,8 +226,8 @@ __device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int p
             const float f1 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7441)), ds23), dm);
             const float f2 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7442)), ds23), dm);
             const float f3 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7443)), ds23), dm);
-            out[2 * i] = pack_bf16(f0, f1);
-            out[2 * i + 1] = pack_bf16(f2, f3);
+            out[2 * i] = pack_term(f0, f1, lo);
+            out[2 * i + 1] = pack_term(f2, f3, lo);
         }
     } else if constexpr (FMT == FQ_Q6_K) {
         const uint32_t h = kb & 1, i = 2 * h + part;
@@ -238,8 +248,8 @@ __device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int p
             const float f1 = __fmul_rn(ds, small_to_float(__byte_perm(q4, 0, 0x4441), 32.0f));
             const float f2 = __fmul_rn(ds, small_to_float(__byte_perm(q4, 0, 0x4442), 32.0f));
             const float f3 = __fmul_rn(ds, small_to_float(__byte_perm(q4, 0, 0x4443), 32.0f));
-            out[2 * j] = pack_bf16(f0, f1);
-            out[2 * j + 1] = pack_bf16(f2, f3);
+            out[2 * j] = pack_term(f0, f1, lo);
+            out[2 * j + 1] = pack_term(f2, f3, lo);
         }
     } else {
         const float d = f16_bits_to_f32((uint16_t)r.d);
@@ -251,8 +261,8 @@ __device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int p
             const float f1 = __fmul_rn(small_to_float(__byte_perm(u, 0, 0x4441), 128.f), d);
             const float f2 = __fmul_rn(small_to_float(__byte_perm(u, 0, 0x4442), 128.f), d);
             const float f3 = __fmul_rn(small_to_float(__byte_perm(u, 0, 0x4443), 128.f), d);
-            out[2 * j] = pack_bf16(f0, f1);
-            out[2 * j + 1] = pack_bf16(f2, f3);
+            out[2 * j] = pack_term(f0, f1, lo);
+            out[2 * j + 1] = pack_term(f2, f3, lo);
         }
     }
 }
@@ -299,12 +309,18 @@ __device__ __forceinline__ void epilogue(uint32_t tmem, int warp, int lane, uint
 // all groups)): group z serves activation rows offsets[z] .. offsets[z+1] with the expert stored at slots[z]
 // (or z); one tile per block; a tile that runs past its group reads the next group's rows and does not
 // store them.
-template <int FMT, int BN, typename YT, bool GROUPED>
-__global__ void __launch_bounds__(THREADS, GROUPED ? 2 : 1) // two expert-tile blocks share an SM: one's set-up and epilogue overlap the other's main loop
+//
+// MODE 2 (dense, F32 callers): near-fp32 products from bf16 operands.  Both operands are split in two bf16
+// terms (v = hi + lo, lo = bf16(v - hi)) and every k-block is walked three times: hi x hi, hi x lo, lo x hi
+// (w_hi, w_hi, w_lo against x_hi, x_lo, x_hi); the caller lays X out as [m][3 * cols] in that order.  The
+// dropped lo x lo term and the residuals are 2^-17 of a product.
+template <int FMT, int BN, typename YT, int MODE>
+__global__ void __launch_bounds__(THREADS, MODE == 1 ? 2 : 1) // two expert-tile blocks share an SM: one's set-up and epilogue overlap the other's main loop
 k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t pitch,
           YT *__restrict__ y, uint32_t m, uint32_t b_bytes, const uint32_t *__restrict__ offsets,
           const uint32_t *__restrict__ slots, uint32_t experts, uint32_t tiles_x, uint32_t full_tiles, uint32_t splits, uint32_t per,
           float *__restrict__ ws, int *status) {
+    constexpr bool GROUPED = MODE == 1, PRECISE = MODE == 2;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     constexpr int NSUB = BN > 256 ? BN / 256 : 1, MMA_N = BN / NSUB, A_STAGES = a_stages<BN>(), B_SLOTS = b_slots<BN>();
     constexpr uint32_t IDESC = idesc_for(MMA_N);
@@ -312,7 +328,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
     using SM = Smem<BN>;
     SM *sm = reinterpret_cast<SM *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint32_t k_first = 0, k_iters = cols / BK, n0, m0, m_end = m;
+    uint32_t k_first = 0, k_iters = cols / BK * (PRECISE ? 3 : 1), n0, m0, m_end = m; // in units: (k-block, term)
     float *partial = nullptr;
     if (GROUPED) {
         // blockIdx.y counts activation tiles over all groups in order; `full_tiles` holds the group count.
@@ -443,7 +459,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
         const uint32_t last = k_first + k_iters - 1;
         Raw<FMT> ring[PREFETCH];
 #pragma unroll
-        for (int j = 0; j < PREFETCH; j++) ring[j] = load_raw<FMT>(rowp, nblk, min(k_first + j, last), part);
+        for (int j = 0; j < PREFETCH; j++) ring[j] = load_raw<FMT>(rowp, nblk, min(k_first + j, last) / (PRECISE ? 3 : 1), part);
         bool go = true;
         for (uint32_t it0 = 0; it0 < k_iters && go; it0 += PREFETCH) {
 #pragma unroll
@@ -452,8 +468,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
                 if (it >= k_iters) break;
                 const int s = it % A_STAGES;
                 uint32_t v[16];
-                decode_raw<FMT>(ring[j], k_first + it, part, v);
-                ring[j] = load_raw<FMT>(rowp, nblk, min(k_first + it + PREFETCH, last), part);
+                const uint32_t unit = k_first + it;
+                decode_raw<FMT>(ring[j], unit / (PRECISE ? 3 : 1), part, PRECISE && unit % 3 == 2, v);
+                ring[j] = load_raw<FMT>(rowp, nblk, min(unit + PREFETCH, last) / (PRECISE ? 3 : 1), part);
                 if (!live) {
 #pragma unroll
                     for (int i = 0; i < 16; i++) v[i] = 0u;
@@ -515,6 +532,21 @@ __global__ void k_to_bf16(const float *__restrict__ x, __nv_bfloat16 *__restrict
     }
 }
 
+// X (fp32) as two bf16 terms laid out for MODE 2: k-block b of a row becomes the three 64-wide blocks
+// hi, lo, hi at 3 b, 3 b + 1, 3 b + 2, with hi = bf16(x) and lo = bf16(x - hi).
+__global__ void k_split3(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, uint32_t cols, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t row = i / cols;
+    const uint32_t k = (uint32_t)(i % cols), b = k / BK, j = k % BK;
+    const float v = x[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+    __nv_bfloat16 *dst = out + row * (size_t)cols * 3 + (size_t)b * 3 * BK + j;
+    dst[0] = hi;
+    dst[BK] = lo;
+    dst[2 * BK] = hi;
+}
+
 // The tiles that were split along K: their fp32 partial sums added in split order (deterministic), rounded and
 // stored as Y.  One thread per four consecutive weight rows of one activation row of a split tile.
 template <int BN, typename YT>
@@ -539,23 +571,24 @@ k_fixup(const float *__restrict__ ws, uint32_t full_tiles, uint32_t splits, uint
         if (row + j < rows) store_out(dst + j, o[j]);
 }
 
-template <int FMT, int BN, typename YT, bool GROUPED>
+template <int FMT, int BN, typename YT, int MODE>
 int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows, int *status) {
+    constexpr bool GROUPED = MODE == 1;
     const size_t smem = sizeof(Smem<BN>) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<FMT, BN, YT, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<FMT, BN, YT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fq_check_cuda(dev, e, "gemm shared memory");
         configured = true;
     }
-    const uint32_t tiles_x = (a.rows + BM - 1) / BM, k_iters = a.cols / BK;
+    const uint32_t tiles_x = (a.rows + BM - 1) / BM, k_iters = a.cols / BK * (MODE == 2 ? 3 : 1);
     if (GROUPED) {
         // At most one partly filled tile per group on top of the full ones (m_rows = all groups' rows).
         const uint32_t per_group = (a.max_rows + BN - 1) / BN;
         const uint32_t tiles_y = (uint32_t)std::min<uint64_t>((uint64_t)per_group * a.groups, (uint64_t)m_rows / BN + a.groups);
         if (tiles_y > 65535) return FQ_ERR_UNSUPPORTED;
         dim3 grid(tiles_x, tiles_y, 1);
-        k_gemm_tc<FMT, BN, YT, GROUPED><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
+        k_gemm_tc<FMT, BN, YT, MODE><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
                                                                               a.offsets, a.slots, a.experts, tiles_x, a.groups, 1, k_iters, dev->gemm_ws, status);
         return FQ_OK;
     }
@@ -574,7 +607,7 @@ int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_
         }
     }
     const uint32_t blocks = full + (tiles - full) * splits;
-    k_gemm_tc<FMT, BN, YT, GROUPED><<<blocks, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
+    k_gemm_tc<FMT, BN, YT, MODE><<<blocks, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
                                                                             a.offsets, a.slots, a.experts, tiles_x, full, splits, per, dev->gemm_ws, status);
     if (splits > 1) {
         const size_t threads = (size_t)(tiles - full) * BN * (BM / 4);
@@ -583,12 +616,12 @@ int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_
     return FQ_OK;
 }
 
-template <int BN, typename YT, bool GROUPED>
+template <int BN, typename YT, int MODE>
 int launch_fmt(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows) {
     switch (a.format) {
-    case FQ_Q4_K: return launch<FQ_Q4_K, BN, YT, GROUPED>(dev, a, map, b_bytes, m_rows, dev->status_dev);
-    case FQ_Q6_K: return launch<FQ_Q6_K, BN, YT, GROUPED>(dev, a, map, b_bytes, m_rows, dev->status_dev);
-    default: return launch<FQ_Q8_0, BN, YT, GROUPED>(dev, a, map, b_bytes, m_rows, dev->status_dev);
+    case FQ_Q4_K: return launch<FQ_Q4_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev);
+    case FQ_Q6_K: return launch<FQ_Q6_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev);
+    default: return launch<FQ_Q8_0, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev);
     }
 }
 
@@ -620,32 +653,44 @@ static const void *x_as_bf16(fq_device *dev, const void *x, size_t n) {
     return tmp;
 }
 
-// Dense projection with at least 32 activation rows: BF16 in / BF16 out, or F32 in / F32 out with X rounded to
-// bf16 first (the reference's wide F32 path likewise multiplies a 16-bit weight tile, `h_mm_*`,
-// src/metal/shaders/hybrid.metal:1411-1469).
+// Dense projection wider than the verify widths.  BF16 in / BF16 out: one bf16 product per weight (the legacy
+// `*_gemm_mpp*` contract: bf16 operands, fp32 accumulation, bf16 RNE out).  F32 in / F32 out: the three-term
+// split of k_gemm_tc's MODE 2, in slices of activation rows whose split copy fits the handle's scratch.
 int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
     if (a.x_dtype != a.y_dtype || a.cols % BK || a.ids || a.offsets) return FQ_ERR_UNSUPPORTED;
     if (a.format != FQ_Q4_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
     if (a.format == FQ_Q4_K && (a.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
     if (a.m <= (uint32_t)FQ_GEMV_MAX_M) return FQ_ERR_UNSUPPORTED; // decode and verify widths: the fp32 kernels serve them
-    const void *xb = a.x;
-    int kernels = 1;
-    if (a.x_dtype == FQ_F32) {
-        if (!(xb = x_as_bf16(dev, a.x, (size_t)a.m * a.cols))) return FQ_ERR_UNSUPPORTED;
-        kernels = 2;
-    }
     CUtensorMap map;
     uint32_t b_bytes = 0;
-    if (int rc = make_map(dev, &map, xb, a.cols, a.m, 256, &b_bytes)) return rc;
-    // 512 activation rows per block (two accumulators sharing each decoded weight tile) once there are
-    // enough rows to fill them; the TMA box stays 256 rows.
-    int rc;
-    if (a.y_dtype == FQ_F32)
-        rc = a.m >= 384 ? launch_fmt<512, float, false>(dev, a, map, b_bytes, a.m) : launch_fmt<256, float, false>(dev, a, map, b_bytes, a.m);
-    else
-        rc = a.m >= 384 ? launch_fmt<512, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m)
-                        : launch_fmt<256, __nv_bfloat16, false>(dev, a, map, b_bytes, a.m);
-    if (rc != FQ_OK) return rc;
+    if (a.x_dtype == FQ_BF16) {
+        if (int rc = make_map(dev, &map, a.x, a.cols, a.m, 256, &b_bytes)) return rc;
+        // 512 activation rows per block (two accumulators sharing each decoded weight tile) once there are
+        // enough rows to fill them; the TMA box stays 256 rows.
+        const int rc = a.m >= 384 ? launch_fmt<512, __nv_bfloat16, 0>(dev, a, map, b_bytes, a.m)
+                                  : launch_fmt<256, __nv_bfloat16, 0>(dev, a, map, b_bytes, a.m);
+        if (rc != FQ_OK) return rc;
+        return fq_end_enqueue(dev, "gemm_tc", 1);
+    }
+    const size_t half = dev->xprep_bytes / 2, row_bytes3 = (size_t)a.cols * 3 * sizeof(__nv_bfloat16);
+    uint32_t slice = (uint32_t)std::min<size_t>(a.m, half / row_bytes3);
+    if (slice < a.m) slice = slice >= 512 ? (slice & ~511u) : (slice & ~255u); // whole tiles per slice
+    if (slice == 0) return FQ_ERR_UNSUPPORTED;
+    int kernels = 0;
+    for (uint32_t m0 = 0; m0 < a.m; m0 += slice) {
+        const uint32_t mm = std::min(slice, a.m - m0);
+        dev->xprep_turn ^= 1u;
+        __nv_bfloat16 *x3 = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? half : 0));
+        const size_t n = (size_t)mm * a.cols;
+        k_split3<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>((const float *)a.x + (size_t)m0 * a.cols, x3, a.cols, n);
+        if (int rc = make_map(dev, &map, x3, a.cols * 3, mm, 256, &b_bytes)) return rc;
+        ProjectArgs s = a;
+        s.m = mm;
+        s.y = (float *)a.y + (size_t)m0 * a.rows;
+        const int rc = mm >= 384 ? launch_fmt<512, float, 2>(dev, s, map, b_bytes, mm) : launch_fmt<256, float, 2>(dev, s, map, b_bytes, mm);
+        if (rc != FQ_OK) return rc;
+        kernels += 2;
+    }
     return fq_end_enqueue(dev, "gemm_tc", kernels);
 }
 
@@ -665,8 +710,8 @@ int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t tot
     CUtensorMap map;
     uint32_t b_bytes = 0;
     if (int rc = make_map(dev, &map, xb, a.cols, total_rows, 64, &b_bytes)) return rc;
-    int rc = a.y_dtype == FQ_F32 ? launch_fmt<64, float, true>(dev, a, map, b_bytes, total_rows)
-                                 : launch_fmt<64, __nv_bfloat16, true>(dev, a, map, b_bytes, total_rows);
+    int rc = a.y_dtype == FQ_F32 ? launch_fmt<64, float, 1>(dev, a, map, b_bytes, total_rows)
+                                 : launch_fmt<64, __nv_bfloat16, 1>(dev, a, map, b_bytes, total_rows);
     if (rc != FQ_OK) return rc;
     return fq_end_enqueue(dev, "gemm_tc_grouped", kernels);
 }
