@@ -18,6 +18,7 @@
 //
 // Device layout of a Q8_0 row (blocks.cuh): the quants of all blocks first (cols bytes, natural order),
 // then the f16 scales (2 bytes per block).
+#include <algorithm>
 #include <cstdlib>
 
 #include "blocks.cuh"
@@ -57,70 +58,73 @@ k_gemv_q8(const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t 
         const bool finite = __ballot_sync(0xffffffffu, !(fabsf(v) < INFINITY)) == 0u;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        // s = 2^e, the largest power of two with amax * s <= 32639: amax = f * 2^ex with f in [0.5, 1), so
+        // e = 15 - ex, one less when f * 2^15 > 32639.  Exponents straight from the float's bits.
         int e = 0;
         if (amax > 0.f && finite) {
-            int ex;
-            frexpf(amax, &ex);
-            e = 15 - ex;
-            if (ldexpf(amax, e) > 32639.f) e -= 1;
-            e = max(-110, min(110, e));
+            const int ex = (int)(__float_as_uint(amax) >> 23) - 126;
+            e = max(-110, min(110, 15 - ex));
+            if (amax * __uint_as_float((uint32_t)(127 + e) << 23) > 32639.f) e -= 1;
         }
-        int q = __float2int_rn(fminf(fmaxf(v * ldexpf(1.f, e), -32639.f), 32639.f));
+        int q = __float2int_rn(fminf(fmaxf(v * __uint_as_float((uint32_t)(127 + e) << 23), -32639.f), 32639.f));
         if (!finite) q = 0; // the block's factor below is NaN in that case
         const int h = (q + 128) >> 8;
         hi[(size_t)mrow * cols + 32 * b + lane] = (int8_t)h;
         lo[(size_t)mrow * cols + 32 * b + lane] = (int8_t)(q - (h << 8));
-        if (lane == 0) isc[mrow * nb + b] = finite ? ldexpf(1.f, -e) : __int_as_float(0x7fc00000);
+        if (lane == 0) isc[mrow * nb + b] = finite ? __uint_as_float((uint32_t)(127 - e) << 23) : __int_as_float(0x7fc00000);
     }
     __syncthreads();
 
-    // 2. Rows.  Lane l: bytes 16 l .. 16 l + 15 of each 512-byte chunk = half of block 16 c + l / 2.
-    const uint32_t row0 = (blockIdx.x * WARPS + warp) * RPW;
-    if (row0 >= rows) return;
-    float acc[RPW][MT];
+    // 2. Rows.  A warp takes groups of RPW rows, strided over the grid (the grid is a few blocks per SM, so
+    // the quantisation above is paid once per many rows).  Lane l: bytes 16 l .. 16 l + 15 of each 512-byte
+    // chunk = half of block 16 c + l / 2.
+    const uint32_t groups = (rows + RPW - 1) / RPW, chunks = (cols + 511) / 512;
+    for (uint32_t g = blockIdx.x * WARPS + warp; g < groups; g += gridDim.x * WARPS) {
+        const uint32_t row0 = g * RPW;
+        float acc[RPW][MT];
 #pragma unroll
-    for (int r = 0; r < RPW; r++)
+        for (int r = 0; r < RPW; r++)
 #pragma unroll
-        for (int t = 0; t < MT; t++) acc[r][t] = 0.f;
-    const uint8_t *rp[RPW];
+            for (int t = 0; t < MT; t++) acc[r][t] = 0.f;
+        const uint8_t *rp[RPW];
 #pragma unroll
-    for (int r = 0; r < RPW; r++) rp[r] = w + (size_t)min(row0 + r, rows - 1) * pitch;
-
-    const uint32_t chunks = (cols + 511) / 512;
-    for (uint32_t c = 0; c < chunks; c++) {
-        const uint32_t k = 512 * c + 16 * lane;
-        const bool live = k < cols;
-        const uint32_t kk = live ? k : 0, b = kk / 32;
-        uint4 q[RPW];
-        float d[RPW];
+        for (int r = 0; r < RPW; r++) rp[r] = w + (size_t)min(row0 + r, rows - 1) * pitch;
+#pragma unroll 2
+        for (uint32_t c = 0; c < chunks; c++) {
+            const uint32_t k = 512 * c + 16 * lane;
+            const bool live = k < cols;
+            const uint32_t kk = live ? k : 0, b = kk / 32;
+            uint4 q[RPW];
+            float d[RPW];
 #pragma unroll
-        for (int r = 0; r < RPW; r++) q[r] = ldg_stream(rp[r] + kk);
+            for (int r = 0; r < RPW; r++) q[r] = ldg_stream(rp[r] + kk);
 #pragma unroll
-        for (int r = 0; r < RPW; r++) d[r] = load_f16(rp[r] + cols + 2 * b);
+            for (int r = 0; r < RPW; r++) d[r] = load_f16(rp[r] + cols + 2 * b);
 #pragma unroll
-        for (int t = 0; t < MT; t++) {
-            const int4 xh = *reinterpret_cast<const int4 *>(hi + (size_t)t * cols + kk);
-            const int4 xl = *reinterpret_cast<const int4 *>(lo + (size_t)t * cols + kk);
-            const float s = live ? isc[t * nb + b] : 0.f; // lanes past the row's end contribute nothing
+            for (int t = 0; t < MT; t++) {
+                const int4 xh = *reinterpret_cast<const int4 *>(hi + (size_t)t * cols + kk);
+                const int4 xl = *reinterpret_cast<const int4 *>(lo + (size_t)t * cols + kk);
+                const float s = live ? isc[t * nb + b] : 0.f; // lanes past the row's end contribute nothing
 #pragma unroll
-            for (int r = 0; r < RPW; r++) {
-                int dh = __dp4a((int)q[r].x, xh.x, 0), dl = __dp4a((int)q[r].x, xl.x, 0);
-                dh = __dp4a((int)q[r].y, xh.y, dh), dl = __dp4a((int)q[r].y, xl.y, dl);
-                dh = __dp4a((int)q[r].z, xh.z, dh), dl = __dp4a((int)q[r].z, xl.z, dl);
-                dh = __dp4a((int)q[r].w, xh.w, dh), dl = __dp4a((int)q[r].w, xl.w, dl);
-                acc[r][t] = fmaf((float)(dh * 256 + dl), d[r] * s, acc[r][t]);
+                for (int r = 0; r < RPW; r++) {
+                    int dh = __dp4a((int)q[r].x, xh.x, 0), dl = __dp4a((int)q[r].x, xl.x, 0);
+                    dh = __dp4a((int)q[r].y, xh.y, dh), dl = __dp4a((int)q[r].y, xl.y, dl);
+                    dh = __dp4a((int)q[r].z, xh.z, dh), dl = __dp4a((int)q[r].z, xl.z, dl);
+                    dh = __dp4a((int)q[r].w, xh.w, dh), dl = __dp4a((int)q[r].w, xl.w, dl);
+                    acc[r][t] = fmaf((float)(dh * 256 + dl), d[r] * s, acc[r][t]);
+                }
             }
         }
+#pragma unroll
+        for (int r = 0; r < RPW; r++)
+#pragma unroll
+            for (int t = 0; t < MT; t++) {
+                float v = acc[r][t];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                if (lane == 0 && row0 + r < rows) y[(size_t)t * rows + row0 + r] = v;
+            }
     }
-#pragma unroll
-    for (int r = 0; r < RPW; r++)
-#pragma unroll
-        for (int t = 0; t < MT; t++) {
-            float v = acc[r][t];
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-            if (lane == 0 && row0 + r < rows) y[(size_t)t * rows + row0 + r] = v;
-        }
 }
 
 template <typename... KArgs, typename... Args>
@@ -149,9 +153,9 @@ cudaError_t launch(fq_device *dev, const ProjectArgs &a, const float *x, float *
         if (e != cudaSuccess) return e;
         configured = MT * (2 * MAX_COLS_Q8 + MAX_COLS_Q8 / 8);
     }
-    const uint32_t per_block = WARPS * RPW;
-    return launch_pdl(k_gemv_q8<MT, RPW>, dim3((a.rows + per_block - 1) / per_block), dim3(WARPS * 32), smem, dev->stream, a.w, a.rows,
-                      a.cols, a.row_bytes, x, y);
+    const uint32_t per_block = WARPS * RPW, need = (a.rows + per_block - 1) / per_block;
+    const uint32_t grid = std::min<uint32_t>(need, (uint32_t)dev->sm_count * 4);
+    return launch_pdl(k_gemv_q8<MT, RPW>, dim3(grid), dim3(WARPS * 32), smem, dev->stream, a.w, a.rows, a.cols, a.row_bytes, x, y);
 }
 
 template <int RPW> cudaError_t launch_m(fq_device *dev, const ProjectArgs &a, const float *x, float *y, uint32_t mt) {
