@@ -82,7 +82,9 @@ SIGNATURES = {
     "fq_comm_open": (_I, [_P, _P]),
     "fq_comm_buffer": (_P, [_P]),
     "fq_comm_all_gather": (_I, [_P, _P, _Z, _Z]),
+    "fq_comm_all_gather_rows": (_I, [_P, _P, _Z, _Z, _P, _U32, _Z]),
     "fq_comm_destroy": (_I, [_P]),
+    "fq_moe_ffn_ep": (_I, [_P, _P, _Z, C.POINTER(MoeFfnDesc), _U32, _P, _Z, _P, _Z, _P]),
     "fq_gemv_q4k_static": (_I, [_P, _U64, _U64, _P, _U32, _P, _P, C.c_char_p, _Z]),
     "fq_project_many_host": (_I, [_P, C.POINTER(_P), _Z, _P, _Z, C.POINTER(_P)]),
 }

@@ -710,14 +710,66 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
         if (int rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position)) return rc;
         // Expert-sorted rows through the tensor-core GEMM: activations rounded to bf16 once (at the gather and
         // at the gated unit), fp32 accumulation and fp32 results.
-        if (int rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg)) return rc;
+        if (int rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, nullptr, 0, s.xg)) return rc;
         if (int rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.g, FQ_F32, routes * ef)) return rc;
         if (int rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.u, FQ_F32, routes * ef)) return rc;
-        if (int rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, s.act)) return rc;
+        if (int rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, nullptr, 0, (uint32_t)ef, s.act)) return rc;
         if (int rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_BF16, routes * ef, s.offsets, nullptr, experts, m, s.down, FQ_F32, routes * hidden)) return rc;
     }
     return fq_moe_combine(dev, s.down, s.weights, identity ? s.ids : s.position, s.shared, s.gate, (uint32_t)hidden,
                           (uint32_t)used, (uint32_t)m, identity, out);
+}
+
+
+// Expert-parallel MoE block: this rank stores experts [expert_first, expert_first + local) of `f->experts`
+// (the expert matrices of `f` hold only those), x and the router are replicated, every rank routes all tokens
+// and maps them expert-major; it then computes the rows of its own experts (always in expert-sorted order, so
+// that a rank's rows are one contiguous run), the runs are exchanged through the communicator's symmetric
+// buffer, and every rank combines.  Per-row arithmetic is that of `fq_moe_ffn`, so the result has the same bits.
+extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset, const fq_moe_ffn_desc *f, uint32_t expert_first,
+                             const float *x, size_t m, float *scratch, size_t scratch_elems, float *out) {
+    if (!dev || !comm || !f || !f->router || !f->gate_exps || !f->up_exps || !f->down_exps || !f->shared_gate || !f->shared_up ||
+        !f->shared_down)
+        return fq_fail(dev, FQ_ERR_PARAM, "incomplete MoE description");
+    const size_t experts = f->experts, used = f->used, hidden = f->hidden, ef = f->expert_ffn, local = f->gate_exps->experts;
+    const int world = fq_comm_world(comm), rank = fq_comm_rank(comm);
+    if (f->router->rows != experts || f->router->cols != hidden || f->gate_exps->expert_rows() != ef || f->gate_exps->cols != hidden ||
+        f->up_exps->experts != local || f->up_exps->expert_rows() != ef || f->down_exps->experts != local ||
+        f->down_exps->expert_rows() != hidden || f->down_exps->cols != ef || f->shared_gate->rows != f->shared_ffn ||
+        f->shared_down->rows != hidden || local * (size_t)world != experts || expert_first != (size_t)rank * local)
+        return fq_fail(dev, FQ_ERR_SHAPE, "MoE matrices do not match the description or the expert split");
+    MoeScratch s = moe_layout(f, m, scratch);
+    if (scratch_elems < s.total) return fq_fail(dev, FQ_ERR_SHAPE, "MoE scratch holds %zu of %zu floats", scratch_elems, s.total);
+    const size_t routes = m * used;
+    if (region_offset % 16 || region_offset + routes * hidden * 4 > fq_comm_bytes(comm))
+        return fq_fail(dev, FQ_ERR_RANGE, "%zu expert rows of %zu floats at offset %zu do not fit the symmetric buffer", routes, hidden, region_offset);
+    float *down = (float *)(fq_comm_local(comm) + region_offset);
+    if (int rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts)) return rc;
+    const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
+    if (int rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m,
+                              f->sigmoid, f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate))
+        return rc;
+    if (int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared))
+        return rc;
+    if (int rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position)) return rc;
+    const uint32_t *mine = s.offsets + expert_first; // mine[0] .. mine[local]: this rank's run of rows
+    if (routes <= MV_ID_MAX_ROUTES || dev->exact) {
+        uint32_t *local_ids = (uint32_t *)s.logits; // the logits are consumed by now, and routes <= m * experts
+        if (int rc = fq_moe_gather(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg)) return rc;
+        if (int rc = fq_launch_moe_local_ids(dev, s.ids, s.sorted, (uint32_t)routes, expert_first, (uint32_t)local, local_ids)) return rc;
+        if (int rc = fq_project_id(dev, f->gate_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, routes * ef)) return rc;
+        if (int rc = fq_project_id(dev, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.u, routes * ef)) return rc;
+        if (int rc = fq_glu(dev, s.g, s.u, routes * ef, s.act)) return rc;
+        if (int rc = fq_project_id(dev, f->down_exps, s.act, routes * ef, local_ids, routes, 1, down, routes * hidden)) return rc;
+    } else {
+        if (int rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, mine, (uint32_t)local, s.xg)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.g, FQ_F32, routes * ef)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.u, FQ_F32, routes * ef)) return rc;
+        if (int rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, mine, (uint32_t)local, (uint32_t)ef, s.act)) return rc;
+        if (int rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_BF16, routes * ef, mine, nullptr, local, m, down, FQ_F32, routes * hidden)) return rc;
+    }
+    if (int rc = fq_comm_all_gather_rows(dev, comm, region_offset, hidden * 4, s.offsets, (uint32_t)local, routes)) return rc;
+    return fq_moe_combine(dev, down, s.weights, s.position, s.shared, s.gate, (uint32_t)hidden, (uint32_t)used, (uint32_t)m, 0, out);
 }
 
 // ------------------------------------------------------------------ host-buffer entry points

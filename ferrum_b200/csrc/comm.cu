@@ -38,15 +38,23 @@ struct Peers {
 
 // grid (world - 1, chunks): block (p, c) copies chunk c of the shard to the p-th other rank; chunk 0's block
 // also does the handshake with that rank.
+// With `bounds` (device memory, written by an earlier kernel of the stream) the shards are runs of rows of
+// unequal length: rank r owns rows bounds[r * stride] .. bounds[(r + 1) * stride] of `shard_bytes` bytes each,
+// laid out from region_off in row order (the expert-sorted rows of an expert-parallel MoE block).
 __global__ void __launch_bounds__(256)
 k_all_gather_push(const __grid_constant__ Peers peers, int rank, int world, size_t payload_bytes, size_t region_off,
-                  size_t shard_bytes, uint32_t slot, uint32_t *seq, int *status) {
+                  size_t shard_bytes, const uint32_t *__restrict__ bounds, uint32_t stride, uint32_t slot, uint32_t *seq, int *status) {
     // Launched with programmatic stream serialization: let the next kernel stage itself, then wait for the
     // projection that produced the local shard.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int other = (int)blockIdx.x < rank ? (int)blockIdx.x : (int)blockIdx.x + 1;
-    const size_t mine = region_off + (size_t)rank * shard_bytes;
+    size_t mine = region_off + (size_t)rank * shard_bytes;
+    if (bounds) {
+        const uint32_t lo = bounds[(size_t)rank * stride], hi = bounds[(size_t)(rank + 1) * stride];
+        mine = region_off + (size_t)lo * shard_bytes;
+        shard_bytes *= hi - lo;
+    }
     const uint4 *src = reinterpret_cast<const uint4 *>(peers.base[rank] + mine);
     uint4 *dst = reinterpret_cast<uint4 *>(peers.base[other] + mine);
     const size_t n16 = shard_bytes / 16;
@@ -133,19 +141,18 @@ extern "C" int fq_comm_open(fq_comm *c, const void *handles) {
 }
 
 extern "C" void *fq_comm_buffer(fq_comm *c) { return c ? c->local : nullptr; }
+uint8_t *fq_comm_local(fq_comm *c) { return c->local; }
+size_t fq_comm_bytes(const fq_comm *c) { return c->bytes; }
+int fq_comm_rank(const fq_comm *c) { return c->rank; }
+int fq_comm_world(const fq_comm *c) { return c->world; }
 
-extern "C" int fq_comm_all_gather(fq_device *dev, fq_comm *c, size_t region_offset, size_t shard_bytes) {
-    if (int rc = fq_begin_enqueue(dev)) return rc;
-    if (!c || c->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "communicator belongs to another device handle");
-    if (!c->opened) return fq_fail(dev, FQ_ERR_PARAM, "communicator peers are not opened");
-    if (shard_bytes == 0 || shard_bytes % 16 || region_offset % 16 || region_offset + shard_bytes * c->world > c->bytes)
-        return fq_fail(dev, FQ_ERR_RANGE, "gather of %zu bytes per rank at offset %zu does not fit %zu bytes", shard_bytes, region_offset, c->bytes);
-    if (c->world == 1) return FQ_OK;
+static int launch_gather(fq_device *dev, fq_comm *c, size_t region_offset, size_t shard_bytes, const uint32_t *bounds, uint32_t stride,
+                         size_t most_bytes) {
     Peers peers{};
     for (int r = 0; r < c->world; r++) peers.base[r] = c->peer[r];
     const uint32_t slot = c->next_slot;
     c->next_slot = (c->next_slot + 1) % FQ_COMM_SLOTS;
-    const unsigned chunks = (unsigned)std::min<size_t>(32, std::max<size_t>(1, shard_bytes / (256 * 16 * 4)));
+    const unsigned chunks = (unsigned)std::min<size_t>(32, std::max<size_t>(1, most_bytes / (256 * 16 * 4)));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(c->world - 1, chunks);
     cfg.blockDim = dim3(256);
@@ -156,9 +163,31 @@ extern "C" int fq_comm_all_gather(fq_device *dev, fq_comm *c, size_t region_offs
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (int rc = fq_check_cuda(dev, cudaLaunchKernelEx(&cfg, k_all_gather_push, peers, c->rank, c->world, c->bytes, region_offset,
-                                                       shard_bytes, slot, c->seq, dev->status_dev), "all-gather launch"))
+                                                       shard_bytes, bounds, stride, slot, c->seq, dev->status_dev), "all-gather launch"))
         return rc;
     return fq_end_enqueue(dev, "all_gather", 1);
+}
+
+extern "C" int fq_comm_all_gather(fq_device *dev, fq_comm *c, size_t region_offset, size_t shard_bytes) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!c || c->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "communicator belongs to another device handle");
+    if (!c->opened) return fq_fail(dev, FQ_ERR_PARAM, "communicator peers are not opened");
+    if (shard_bytes == 0 || shard_bytes % 16 || region_offset % 16 || region_offset + shard_bytes * c->world > c->bytes)
+        return fq_fail(dev, FQ_ERR_RANGE, "gather of %zu bytes per rank at offset %zu does not fit %zu bytes", shard_bytes, region_offset, c->bytes);
+    if (c->world == 1) return FQ_OK;
+    return launch_gather(dev, c, region_offset, shard_bytes, nullptr, 0, shard_bytes);
+}
+
+extern "C" int fq_comm_all_gather_rows(fq_device *dev, fq_comm *c, size_t region_offset, size_t row_bytes, const uint32_t *bounds,
+                                       uint32_t stride, size_t total_rows) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!c || c->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "communicator belongs to another device handle");
+    if (!c->opened) return fq_fail(dev, FQ_ERR_PARAM, "communicator peers are not opened");
+    if (row_bytes == 0 || row_bytes % 16 || region_offset % 16 || stride == 0 || total_rows == 0 || region_offset + row_bytes * total_rows > c->bytes)
+        return fq_fail(dev, FQ_ERR_RANGE, "gather of %zu rows of %zu bytes at offset %zu does not fit %zu bytes", total_rows, row_bytes, region_offset, c->bytes);
+    if (int rc = fq_check_binding(dev, bounds, ((size_t)c->world * stride + 1) * 4, "bounds")) return rc;
+    if (c->world == 1) return FQ_OK;
+    return launch_gather(dev, c, region_offset, row_bytes, bounds, stride, row_bytes * total_rows / c->world);
 }
 
 extern "C" int fq_comm_destroy(fq_comm *c) {

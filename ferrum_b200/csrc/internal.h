@@ -113,6 +113,18 @@ int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a);
 // The same over expert-sorted activation rows (a.offsets / a.slots / a.groups / a.max_rows); F32 or BF16.
 int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t total_rows);
 // Expert-sorted activations and the gated unit with bf16 results (inputs of the grouped tensor-core GEMM).
+// `range` (may be null) limits the work to rows [range[0], range[stride]): the experts one rank owns.
 int fq_launch_moe_gather_bf16(fq_device *dev, const float *x, const uint32_t *sorted, uint32_t hidden, uint32_t used, uint32_t routes,
-                              void *xg);
-int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_t n, void *out);
+                              const uint32_t *range, uint32_t stride, void *xg);
+int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_t n, const uint32_t *range, uint32_t stride, uint32_t width,
+                       void *out);
+// out[row] = expert of expert-sorted row `row` minus `first`, or an id that names no expert when it is not one
+// of the `count` experts from `first`.
+int fq_launch_moe_local_ids(fq_device *dev, const uint32_t *ids, const uint32_t *sorted, uint32_t routes, uint32_t first, uint32_t count,
+                            uint32_t *out);
+// The symmetric buffer of a communicator and its geometry (comm.cu).
+struct fq_comm;
+uint8_t *fq_comm_local(fq_comm *c);
+size_t fq_comm_bytes(const fq_comm *c);
+int fq_comm_rank(const fq_comm *c);
+int fq_comm_world(const fq_comm *c);

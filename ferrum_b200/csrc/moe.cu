@@ -224,9 +224,12 @@ __global__ void k_swiglu(const float *__restrict__ g, const float *__restrict__ 
 }
 
 // The two kernels above with bf16 results, for the tensor-core expert GEMM that follows them.
+// `range` (may be null): two row indices; rows outside [range[0], range[stride]) are skipped (the rows of
+// experts another rank owns).
 __global__ void k_moe_gather_bf16(const float *__restrict__ x, const uint32_t *__restrict__ sorted, uint32_t hidden,
-                                  uint32_t used, __nv_bfloat16 *__restrict__ xg) {
+                                  uint32_t used, const uint32_t *__restrict__ range, uint32_t stride, __nv_bfloat16 *__restrict__ xg) {
     const uint32_t row = blockIdx.x;
+    if (range && (row < range[0] || row >= range[stride])) return;
     const float *src = x + (size_t)(sorted[row] / used) * hidden;
     __nv_bfloat16 *dst = xg + (size_t)row * hidden;
     if ((hidden & 3u) == 0) {
@@ -240,27 +243,47 @@ __global__ void k_moe_gather_bf16(const float *__restrict__ x, const uint32_t *_
     }
 }
 
-__global__ void k_swiglu_bf16(const float *__restrict__ g, const float *__restrict__ u, size_t n, __nv_bfloat16 *__restrict__ y) {
+__global__ void k_swiglu_bf16(const float *__restrict__ g, const float *__restrict__ u, size_t n, const uint32_t *__restrict__ range,
+                              uint32_t stride, uint32_t width, __nv_bfloat16 *__restrict__ y) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (range && (i < (size_t)range[0] * width || i >= (size_t)range[stride] * width)) return;
     if (i < n) {
         const float x = g[i];
         y[i] = __float2bfloat16_rn(x / (1.f + expf(-x)) * u[i]);
     }
 }
 
+// Expert of each expert-sorted row, relative to the first expert this rank stores; rows of other ranks'
+// experts get an id no matrix has, which the per-route kernels skip.
+__global__ void k_moe_local_ids(const uint32_t *__restrict__ ids, const uint32_t *__restrict__ sorted, uint32_t routes, uint32_t first,
+                                uint32_t count, uint32_t *__restrict__ out) {
+    const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= routes) return;
+    const uint32_t e = ids[sorted[row]];
+    out[row] = (e >= first && e - first < count) ? e - first : 0xFFFFFFFFu;
+}
+
 } // namespace
 
 int fq_launch_moe_gather_bf16(fq_device *dev, const float *x, const uint32_t *sorted, uint32_t hidden, uint32_t used, uint32_t routes,
-                              void *xg) {
+                              const uint32_t *range, uint32_t stride, void *xg) {
     if (int rc = fq_begin_enqueue(dev)) return rc;
-    k_moe_gather_bf16<<<routes, 256, 0, dev->stream>>>(x, sorted, hidden, used, (__nv_bfloat16 *)xg);
+    k_moe_gather_bf16<<<routes, 256, 0, dev->stream>>>(x, sorted, hidden, used, range, stride, (__nv_bfloat16 *)xg);
     return fq_end_enqueue(dev, "moe_gather", 1);
 }
 
-int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_t n, void *out) {
+int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_t n, const uint32_t *range, uint32_t stride, uint32_t width,
+                       void *out) {
     if (int rc = fq_begin_enqueue(dev)) return rc;
-    k_swiglu_bf16<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(gate, up, n, (__nv_bfloat16 *)out);
+    k_swiglu_bf16<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(gate, up, n, range, stride, width, (__nv_bfloat16 *)out);
     return fq_end_enqueue(dev, "glu", 1);
+}
+
+int fq_launch_moe_local_ids(fq_device *dev, const uint32_t *ids, const uint32_t *sorted, uint32_t routes, uint32_t first, uint32_t count,
+                            uint32_t *out) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    k_moe_local_ids<<<(routes + 255) / 256, 256, 0, dev->stream>>>(ids, sorted, routes, first, count, out);
+    return fq_end_enqueue(dev, "moe_local_ids", 1);
 }
 
 extern "C" int fq_moe_route(fq_device *dev, const float *logits, const float *x, const float *shared_w,

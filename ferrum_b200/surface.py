@@ -190,6 +190,12 @@ class Comm:
         """Rank r's slice is ``[offset + r * shard, + shard)``; afterwards (in stream order) all are local."""
         self.device.check(self.device._L.fq_comm_all_gather(self.device.handle, self.handle, offset_bytes, shard_bytes))
 
+    def all_gather_rows(self, offset_bytes: int, row_bytes: int, bounds, stride: int, total_rows: int) -> None:
+        """Runs of rows of unequal length: rank r owns rows ``bounds[r * stride] .. bounds[(r + 1) * stride]``
+        (``bounds``: a device tensor of uint32/int32)."""
+        self.device.check(self.device._L.fq_comm_all_gather_rows(self.device.handle, self.handle, offset_bytes, row_bytes,
+                                                                  _ptr(bounds), stride, total_rows))
+
     def close(self) -> None:
         if self.handle and self.device.handle:
             self.device._L.fq_comm_destroy(self.handle)
@@ -385,6 +391,16 @@ def moe_ffn(d: Device, f: MoeFfn, x, m, scratch, out):
     _need(d, x, scratch, out)
     desc = f.desc()
     d.check(d._L.fq_moe_ffn(d.handle, C.byref(desc), _ptr(x), m, _ptr(scratch), scratch.numel(), _ptr(out)))
+
+
+def moe_ffn_ep(d: Device, comm: Comm, offset_bytes: int, f: MoeFfn, expert_first: int, x, m, scratch, out):
+    """Expert-parallel ``moe_ffn``: the expert matrices of ``f`` hold this rank's experts
+    ``[expert_first, expert_first + E / world)``; the expert rows are exchanged through ``comm``'s buffer at
+    ``offset_bytes``.  ``out`` is complete on every rank."""
+    _need(d, x, scratch, out)
+    desc = f.desc()
+    d.check(d._L.fq_moe_ffn_ep(d.handle, comm.handle, offset_bytes, C.byref(desc), expert_first, _ptr(x), m, _ptr(scratch),
+                               scratch.numel(), _ptr(out)))
 
 
 def project_host(d: Device, w: Matrix, x_host: np.ndarray, m: int, y_host: np.ndarray) -> None:

@@ -236,7 +236,25 @@ int fq_comm_handle(fq_comm *comm, void *out64);
 int fq_comm_open(fq_comm *comm, const void *handles);
 void *fq_comm_buffer(fq_comm *comm);
 int fq_comm_all_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size_t shard_bytes);
+/* The same exchange for runs of rows of unequal length: the region is `total_rows` rows of `row_bytes`
+ * bytes (a multiple of 16) from `region_offset`; rank r owns rows bounds[r * stride] .. bounds[(r + 1) * stride].
+ * `bounds` is DEVICE memory (world * stride + 1 words) that work enqueued earlier may still be writing --
+ * e.g. the expert offsets of `fq_moe_map`, with stride = experts per rank. */
+int fq_comm_all_gather_rows(fq_device *dev, fq_comm *comm, size_t region_offset, size_t row_bytes, const uint32_t *bounds,
+                            uint32_t stride, size_t total_rows);
 int fq_comm_destroy(fq_comm *comm);
+
+/* ---- expert-parallel MoE block (no counterpart in the single-GPU reference) -------------------- */
+
+/* `fq_moe_ffn` with the experts sharded over the ranks of `comm`: rank r stores experts
+ * [r E / g, (r + 1) E / g) -- the expert matrices of `f` hold only those (`f->experts` stays E), and
+ * `expert_first` = r E / g.  x, the router and the shared expert are replicated.  Every rank routes all
+ * tokens, computes the expert-sorted rows of its own experts into the symmetric buffer at `region_offset`
+ * (m * used * hidden floats must fit), the runs are exchanged with `fq_comm_all_gather_rows`, and every rank
+ * combines: `out` is complete on every rank and equals `fq_moe_ffn` on one GPU bit for bit.  All ranks
+ * must make the same calls in the same order.  Scratch as for `fq_moe_ffn`. */
+int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset, const fq_moe_ffn_desc *f, uint32_t expert_first,
+                  const float *x, size_t m, float *scratch, size_t scratch_elems, float *out);
 
 /* ---- allocation-free decode projection ------------------------------------------------------- */
 

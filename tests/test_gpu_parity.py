@@ -395,6 +395,33 @@ def test_moe_ffn(device, m):
     assert ref.rel_err(host(out).reshape(m, hidden), want) <= (3 * TOL_F32 if m * used <= 32 else TOL_BF16)
 
 
+@pytest.mark.parametrize("m", [2, 40])
+def test_moe_ffn_expert_parallel_on_one_rank_is_bit_identical(device, m):
+    """`moe_ffn_ep` with a communicator of one rank: the expert-sorted order it always works in (gathered rows,
+    local expert ids, position-indexed combine) gives the bits of `moe_ffn`."""
+    s = S()
+    experts, used, hidden, ef = 16, 4, 512, 256
+    M = s.Matrix.from_packed
+    f = s.MoeFfn(M(device, experts, hidden, 1, ref.Q8_0, ref.random_matrix(ref.Q8_0, experts, hidden, 10)),
+                 M(device, ef, hidden, experts, ref.Q4_K, ref.random_matrix(ref.Q4_K, experts * ef, hidden, 11)),
+                 M(device, ef, hidden, experts, ref.Q4_K, ref.random_matrix(ref.Q4_K, experts * ef, hidden, 12)),
+                 M(device, hidden, ef, experts, ref.Q6_K, ref.random_matrix(ref.Q6_K, experts * hidden, ef, 13)),
+                 M(device, ef, hidden, 1, ref.Q4_K, ref.random_matrix(ref.Q4_K, ef, hidden, 14)),
+                 M(device, ef, hidden, 1, ref.Q4_K, ref.random_matrix(ref.Q4_K, ef, hidden, 15)),
+                 M(device, hidden, ef, 1, ref.Q6_K, ref.random_matrix(ref.Q6_K, hidden, ef, 16)),
+                 None, experts, used, hidden, ef, ef, False, True)
+    x = dev_f32((np.random.default_rng(m).standard_normal((m, hidden)) * 0.12).astype(np.float32))
+    n = s.moe_ffn_scratch_elems(device, f, m)
+    out1 = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
+    s.moe_ffn(device, f, x, m, torch.zeros(n, dtype=torch.float32, device="cuda"), out1)
+    comm = s.Comm(device, 0, 1, 4096 + m * used * hidden * 4)
+    out2 = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
+    s.moe_ffn_ep(device, comm, 4096, f, 0, x, m, torch.zeros(n, dtype=torch.float32, device="cuda"), out2)
+    device.synchronize()
+    assert torch.equal(out1, out2)
+    comm.close()
+
+
 # ------------------------------------------------------------------ error behaviour and the boundary
 
 def test_errors_follow_the_reference(device):

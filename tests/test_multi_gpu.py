@@ -67,3 +67,59 @@ def test_two_ranks_gather_a_sharded_projection(tmp_path):
     import torch.multiprocessing as mp
     mp.spawn(_rank, args=(2, _port(), str(tmp_path)), nprocs=2, join=True)
     assert os.path.exists(tmp_path / "ok0") and os.path.exists(tmp_path / "ok1")
+
+
+def _ep_rank(rank, world, port, out_dir):
+    import torch.distributed as dist
+    from ferrum_b200 import surface as S
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        d = S.Device(rank, use_torch_stream=False)
+        experts, used, hidden, ef = 16, 4, 512, 256
+        local = experts // world
+        M = S.Matrix.from_packed
+        gate_e, up_e = ref.random_matrix(ref.Q4_K, experts * ef, hidden, 11), ref.random_matrix(ref.Q4_K, experts * ef, hidden, 12)
+        down_e = ref.random_matrix(ref.Q6_K, experts * hidden, ef, 13)
+
+        def experts_of(packed, fmt, rows_e, cols, first, count):  # the stacked layout slices contiguously
+            rb = ref.row_bytes(fmt, cols)
+            return packed[first * rows_e * rb:(first + count) * rows_e * rb]
+
+        shared = [M(d, experts, hidden, 1, ref.Q8_0, ref.random_matrix(ref.Q8_0, experts, hidden, 10)),
+                  M(d, ef, hidden, 1, ref.Q4_K, ref.random_matrix(ref.Q4_K, ef, hidden, 14)),
+                  M(d, ef, hidden, 1, ref.Q4_K, ref.random_matrix(ref.Q4_K, ef, hidden, 15)),
+                  M(d, hidden, ef, 1, ref.Q6_K, ref.random_matrix(ref.Q6_K, hidden, ef, 16))]
+        whole = S.MoeFfn(shared[0], M(d, ef, hidden, experts, ref.Q4_K, gate_e), M(d, ef, hidden, experts, ref.Q4_K, up_e),
+                         M(d, hidden, ef, experts, ref.Q6_K, down_e), shared[1], shared[2], shared[3], None, experts, used, hidden, ef, ef,
+                         False, True)
+        first = rank * local
+        mine = S.MoeFfn(shared[0], M(d, ef, hidden, local, ref.Q4_K, experts_of(gate_e, ref.Q4_K, ef, hidden, first, local)),
+                        M(d, ef, hidden, local, ref.Q4_K, experts_of(up_e, ref.Q4_K, ef, hidden, first, local)),
+                        M(d, hidden, ef, local, ref.Q6_K, experts_of(down_e, ref.Q6_K, hidden, ef, first, local)),
+                        shared[1], shared[2], shared[3], None, experts, used, hidden, ef, ef, False, True)
+        comm = S.Comm(d, rank, world, 4096 + 64 * used * hidden * 4)
+        for m in (1, 3, 40):  # per-route GEMVs (m * used <= 32) and the grouped tensor-core GEMM
+            x = torch.from_numpy((np.random.default_rng(m).standard_normal((m, hidden)) * 0.12).astype(np.float32)).cuda()
+            n = S.moe_ffn_scratch_elems(d, whole, m)
+            want = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
+            S.moe_ffn(d, whole, x, m, torch.zeros(n, dtype=torch.float32, device="cuda"), want)
+            got = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
+            S.moe_ffn_ep(d, comm, 4096, mine, first, x, m, torch.zeros(n, dtype=torch.float32, device="cuda"), got)
+            d.synchronize()
+            assert torch.equal(got, want), (rank, m)
+            dist.barrier()  # nobody overwrites the symmetric buffer while a peer still combines from it
+        open(os.path.join(out_dir, f"ep{rank}"), "w").write("ok")
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_split_the_experts(tmp_path):
+    """Expert parallelism: each rank stores half of the experts; the exchanged result has the single-GPU bits."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_ep_rank, args=(2, _port(), str(tmp_path)), nprocs=2, join=True)
+    assert os.path.exists(tmp_path / "ep0") and os.path.exists(tmp_path / "ep1")
