@@ -203,6 +203,11 @@ def run_ours(args):
         for layer in mats:
             for group in GROUPS:
                 names = [n for n in group if only is None or n in only]
+                if world > 1 and only is None and not args.nccl and not args.no_fuse:
+                    # compute and exchange in one launch per input group
+                    S.project_many_gather(dev, comm_box["comm"], *y_spans[group[0]], [layer[n] for n in names], xd[group[0]], mm,
+                                          [yd[n] for n in names])
+                    continue
                 if names and not args.no_fuse:
                     S.project_many(dev, [layer[n] for n in names], xd[group[0]], mm, [yd[n] for n in names])
                 else:
@@ -263,7 +268,7 @@ def run_ours(args):
                    "m": m, "layers": layers, "parallelism": f"tp{world}" if world > 1 else "single",
                    "submission": ("one captured graph per step" if world == 1 else
                                   "eager + one NCCL all-gather per input group" if args.nccl else
-                                  "one captured graph per step incl. one peer-push all-gather per input group (q|k|v, o, gate|up, down)"),
+                                  "one captured graph per step; per input group (q|k|v, o, gate|up, down) one kernel computes the row shard and pushes it to every peer over NVLink"),
                    "l2": "inputs larger than L2"},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
@@ -369,13 +374,52 @@ def run_ours(args):
 
         # CPU baseline: the oracle port on all host cores, one layer at M = 1 (a bounded sample).
         out["cpu_baseline"] = cpu_baseline(m=m, budget_s=12.0)
-    elif rank == 0:
-        out["e2e"] = None
+    else:
+        # Expert parallelism over the same ranks (config 3 sharded by expert): every rank takes part.
+        ep = moe_ep_bench(S, dev, stream, torch, dist, timed, rank, world)
+        if rank == 0:
+            out["e2e"] = None
+            out["moe_ffn_ep"] = ep
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def moe_ep_bench(S, dev, stream, torch, dist, timed_ms, rank, world):
+    """Config 3 with the 256 experts split over the ranks (router, shared expert and x replicated); the
+    expert-sorted rows are exchanged by the peer-push all-gather inside the captured step."""
+    H, E, F, USED = 2048, 256, 512, 8
+    local = E // world
+    M = S.Matrix.from_packed
+    f = S.MoeFfn(M(dev, E, H, 1, Q8_0, random_matrix(Q8_0, E, H, 900)),
+                 M(dev, F, H, local, Q4_K, random_matrix(Q4_K, local * F, H, 901 + 16 * rank)),
+                 M(dev, F, H, local, Q4_K, random_matrix(Q4_K, local * F, H, 902 + 16 * rank)),
+                 M(dev, H, F, local, Q6_K, random_matrix(Q6_K, local * H, F, 903 + 16 * rank)),
+                 M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 904)), M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 905)),
+                 M(dev, H, F, 1, Q6_K, random_matrix(Q6_K, H, F, 906)), None, E, USED, H, F, F, False, True)
+    comm = S.Comm(dev, rank, world, 4096 + 1024 * USED * H * 4)
+    res = {}
+    for T in (1, 1024):
+        torch.manual_seed(7)  # the same tokens, hence the same routing, on every rank
+        x = (torch.randn(T * H, device="cuda") * 0.12).contiguous()
+        scratch = torch.zeros(S.moe_ffn_scratch_elems(dev, f, T), dtype=torch.float32, device="cuda")
+        o = torch.zeros(T * H, dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        dev.capture_begin()
+        S.moe_ffn_ep(dev, comm, 4096, f, rank * local, x, T, scratch, o)
+        g = dev.capture_end()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                g.launch()
+        reps = 10
+        ms = timed_ms(g.launch, reps) / reps
+        res[f"t{T}"] = {"us": round(ms * 1e3, 1), "experts_per_rank": local, "exchange_bytes": T * USED * H * 4}
+    dev.synchronize()
+    dist.barrier()
+    comm.close()
+    return res
 
 
 def moe_bench(S, dev, stream, torch, timed_ms):

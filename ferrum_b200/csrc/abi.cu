@@ -547,9 +547,40 @@ extern "C" int fq_project_many(fq_device *dev, const fq_matrix *const *w, size_t
         int rc = launch_decode(dev, args, (uint32_t)count);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
+    dev->tp_push = nullptr; // separate launches cannot share one fused exchange
     for (size_t i = 0; i < count; i++)
         if (int rc = fq_project(dev, w[i], x, x_dtype, x_elems, m, y[i], y_dtype, m * w[i]->rows)) return rc;
     return FQ_OK;
+}
+
+// Row-sharded `fq_project_many`: every y[i] lies in this rank's slice [region_offset + rank * shard_bytes,
+// + shard_bytes) of a gathered region of the communicator's symmetric buffer.  Decode widths on the integer
+// kernel exchange inside the projection kernel; anything else projects first and gathers the region with
+// the copy kernel.
+extern "C" int fq_project_many_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size_t shard_bytes, const fq_matrix *const *w,
+                                      size_t count, const void *x, int x_dtype, size_t x_elems, size_t m, void *const *y, int y_dtype) {
+    if (!dev || !comm || !w || !y || count == 0) return fq_fail(dev, FQ_ERR_PARAM, "projection list");
+    const int world = fq_comm_world(comm), rank = fq_comm_rank(comm);
+    if (y_dtype != FQ_F32) return fq_fail(dev, FQ_ERR_UNSUPPORTED, "gathered projections are F32");
+    if (shard_bytes == 0 || shard_bytes % 16 || region_offset % 16 || region_offset + shard_bytes * world > fq_comm_bytes(comm))
+        return fq_fail(dev, FQ_ERR_RANGE, "gather of %zu bytes per rank at offset %zu does not fit the symmetric buffer", shard_bytes, region_offset);
+    const uint8_t *mine = fq_comm_local(comm) + region_offset + (size_t)rank * shard_bytes;
+    for (size_t i = 0; i < count; i++) {
+        if (!w[i]) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
+        const uint8_t *p = (const uint8_t *)y[i];
+        if (p < mine || p + m * w[i]->rows * 4 > mine + shard_bytes)
+            return fq_fail(dev, FQ_ERR_RANGE, "output %zu lies outside this rank's slice of the region", i);
+    }
+    if (world == 1) return fq_project_many(dev, w, count, x, x_dtype, x_elems, m, y, y_dtype);
+    TpPush push{};
+    if (int rc = fq_comm_begin_push(comm, mine, shard_bytes, &push)) return fq_fail(dev, rc, "communicator peers are not opened");
+    dev->tp_push = &push;
+    dev->tp_pushed = false;
+    const int rc = fq_project_many(dev, w, count, x, x_dtype, x_elems, m, y, y_dtype);
+    dev->tp_push = nullptr;
+    if (rc) return rc;
+    if (dev->tp_pushed) return FQ_OK;
+    return fq_comm_all_gather(dev, comm, region_offset, shard_bytes);
 }
 
 extern "C" int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x, size_t x_elems, const uint32_t *ids,

@@ -141,6 +141,22 @@ extern "C" int fq_comm_open(fq_comm *c, const void *handles) {
 }
 
 extern "C" void *fq_comm_buffer(fq_comm *c) { return c ? c->local : nullptr; }
+int fq_comm_begin_push(fq_comm *c, const void *y, size_t bytes, TpPush *out) {
+    const uint8_t *p = (const uint8_t *)y;
+    if (!c->opened || p < c->local || p + bytes > c->local + c->bytes) return FQ_ERR_RANGE;
+    for (int r = 0; r < FQ_COMM_MAX_WORLD; r++) out->peer[r] = r < c->world ? c->peer[r] : nullptr;
+    out->world = (uint32_t)c->world;
+    out->rank = (uint32_t)c->rank;
+    out->slot = c->next_slot;
+    c->next_slot = (c->next_slot + 1) % FQ_COMM_SLOTS;
+    out->seq = c->seq;
+    out->counter = c->seq + (size_t)FQ_COMM_SLOTS * FQ_COMM_MAX_WORLD * 2 + (size_t)out->slot * FQ_COMM_MAX_WORLD; // the slot's chunk counters
+    out->flag_off = c->bytes;
+    out->slice_off = (size_t)(p - c->local);
+    out->slice_bytes = bytes;
+    out->status = c->dev->status_dev;
+    return FQ_OK;
+}
 uint8_t *fq_comm_local(fq_comm *c) { return c->local; }
 size_t fq_comm_bytes(const fq_comm *c) { return c->bytes; }
 int fq_comm_rank(const fq_comm *c) { return c->rank; }

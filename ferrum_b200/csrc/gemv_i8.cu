@@ -239,6 +239,51 @@ template <int FMT> struct Act {
     }
 };
 
+// End of a launch whose outputs are one rank's slice of a gathered region: the last block to get here copies
+// the slice to every peer, raises this rank's sequence flag there and waits (bounded) until every peer's flag
+// for the same exchange has arrived.
+__device__ __forceinline__ void tp_finish(const TpPush &P) {
+    __shared__ bool last;
+    __threadfence(); // this block's outputs, before the block is counted in
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(P.counter, 1u) + 1u == gridDim.x * gridDim.y * gridDim.z;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    const uint4 *src = reinterpret_cast<const uint4 *>(P.peer[P.rank] + P.slice_off);
+    const size_t n16 = P.slice_bytes / 16;
+    for (uint32_t p = 0; p < P.world; p++) {
+        if (p == P.rank) continue;
+        uint4 *dst = reinterpret_cast<uint4 *>(P.peer[p] + P.slice_off);
+        for (size_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i); // from L2: other blocks wrote it
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    *P.counter = 0;
+    uint32_t expect[8];
+    for (uint32_t p = 0; p < P.world; p++) {
+        if (p == P.rank) continue;
+        uint32_t *my_seq = P.seq + (size_t)P.slot * 8 + p;
+        expect[p] = *my_seq + 1u;
+        *my_seq = expect[p];
+        uint32_t *remote = reinterpret_cast<uint32_t *>(P.peer[p] + P.flag_off) + (size_t)P.slot * 8 + P.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(expect[p]) : "memory");
+    }
+    for (uint32_t p = 0; p < P.world; p++) {
+        if (p == P.rank) continue;
+        const uint32_t *local = reinterpret_cast<const uint32_t *>(P.peer[P.rank] + P.flag_off) + (size_t)P.slot * 8 + p;
+        bool arrived = false;
+        for (uint32_t i = 0; i < (1u << 24) && !arrived; i++) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
+            arrived = (int32_t)(v - expect[p]) >= 0;
+            if (!arrived) __nanosleep(20);
+        }
+        if (!arrived) *(volatile int *)P.status = (int)FQ_ERR_TIMEOUT; // the peer never arrived: report, do not hang
+    }
+}
+
 struct GemvTargets {
     const uint8_t *w[MAX_TARGETS];
     float *y[MAX_TARGETS];
@@ -247,48 +292,61 @@ struct GemvTargets {
     uint32_t count;
 };
 
-// FMT: FQ_Q4_K / FQ_Q6_K; MT: activation rows (1..4).  grid.x = 16-row tiles over all targets;
+// FMT: FQ_Q4_K / FQ_Q6_K; MT: activation rows (1..4).  grid.x = persistent blocks over the 16-row tiles of all targets;
 // grid.y = routes in expert mode (route r: expert ids[r], activation row r / x_div, output row r).
 template <int FMT, int MT>
 __global__ void __launch_bounds__(MT >= 3 ? 256 : MT == 2 ? 384 : MAX_WARPS * 32)
 k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *__restrict__ prep, PrepI8 L,
-          const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts) {
+          const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts, const __grid_constant__ TpPush P) {
     using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
-    __shared__ float red[MAX_WARPS - 1][MT * 2][8];
+    __shared__ float red[2][MAX_WARPS - 1][MT * 2][8];
     const int WARPS = blockDim.x >> 5;
-
-    uint32_t which = 0, first_block = 0;
-#pragma unroll
-    for (int i = 0; i < MAX_TARGETS - 1; i++)
-        if ((uint32_t)i + 1 < T.count && blockIdx.x >= T.tile_end[i]) { which = i + 1; first_block = T.tile_end[i]; }
-    const uint8_t *__restrict__ w = T.w[which];
-    float *__restrict__ y = T.y[which];
-    const uint32_t rows = T.rows[which];
-
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    size_t y_base = 0;
+
+    // Blocks are persistent: block b takes the 16-row tiles b, b + gridDim.x, ... of the launch (all targets
+    // counted through), so that a block's set-up is paid once and the weight stream of its next tile is
+    // already in flight while the current one is reduced and stored.
+    const uint32_t total_tiles = T.tile_end[T.count - 1];
+    size_t expert_off = 0, y_base = 0;
     if (ids) {
         pdl_wait(); // the routing that wrote `ids` must have completed
         const uint32_t r = blockIdx.y;
         const uint32_t e = ids[r];
         if (e >= experts) return;
-        w += (size_t)e * rows * pitch;
+        expert_off = (size_t)e * T.rows[0] * pitch;
         prep += (size_t)(r / x_div) * L.token_bytes;
-        y_base = (size_t)r * rows;
+        y_base = (size_t)r * T.rows[0];
     }
-    const uint32_t tile0 = blockIdx.x - first_block;
-    const uint8_t *rowp[2];
+    struct Tile {
+        const uint8_t *rowp[2];
+        float *y;
+        uint32_t rows, tile0;
+    };
+    auto tile_at = [&](uint32_t tile) {
+        uint32_t which = 0, first_block = 0;
 #pragma unroll
-    for (int r = 0; r < 2; r++) rowp[r] = w + (size_t)min(tile0 * 16 + g + r * 8, rows - 1) * pitch;
+        for (int i = 0; i < MAX_TARGETS - 1; i++)
+            if ((uint32_t)i + 1 < T.count && tile >= T.tile_end[i]) { which = i + 1; first_block = T.tile_end[i]; }
+        Tile q;
+        q.rows = T.rows[which];
+        q.tile0 = tile - first_block;
+        q.y = T.y[which];
+        const uint8_t *w = T.w[which] + expert_off;
+#pragma unroll
+        for (int r = 0; r < 2; r++) q.rowp[r] = w + (size_t)min(q.tile0 * 16 + g + r * 8, q.rows - 1) * pitch;
+        return q;
+    };
+    uint32_t tile = blockIdx.x;
+    Tile here = tile_at(tile);
 
     const uint32_t nblk = L.nblk;
     const uint32_t iters = nblk > (uint32_t)warp ? (nblk - warp + WARPS - 1) / WARPS : 0;
     auto block_of = [&](uint32_t it) { return warp + min(it, iters - 1) * WARPS; };
     Raw cur[2], nxt[2];
     if (iters > 0) {
-        cur[0].load(rowp[0], nblk, block_of(0), t);
-        cur[1].load(rowp[1], nblk, block_of(0), t);
+        cur[0].load(here.rowp[0], nblk, block_of(0), t);
+        cur[1].load(here.rowp[1], nblk, block_of(0), t);
     }
     // The loads above touch immutable weights only; the rest reads prepared activations and writes y.
     pdl_trigger();
@@ -316,13 +374,20 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
 #pragma unroll
     for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
 
+    for (uint32_t buf = 0;; buf ^= 1u) {
+    const uint32_t next_tile = tile + gridDim.x;
+    const bool more = next_tile < total_tiles;
+    const Tile next = more ? tile_at(next_tile) : here;
     for (uint32_t it = 0; it < iters; it++) {
-        // Everything the next iteration needs is requested now; this one runs from registers.
-        nxt[0].load(rowp[0], nblk, block_of(it + 1), t);
-        nxt[1].load(rowp[1], nblk, block_of(it + 1), t);
+        // Everything the next iteration needs is requested now; this one runs from registers.  After a
+        // tile's last superblock that is the first superblock of the block's next tile.
+        const bool wrap = it + 1 == iters && more;
+        const uint32_t nb_next = wrap ? block_of(0) : block_of(it + 1);
+        nxt[0].load(wrap ? next.rowp[0] : here.rowp[0], nblk, nb_next, t);
+        nxt[1].load(wrap ? next.rowp[1] : here.rowp[1], nblk, nb_next, t);
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            if (AHEAD) anxt[m].load(prep + (size_t)m * L.token_bytes, L, block_of(it + 1), t, g);
+            if (AHEAD) anxt[m].load(prep + (size_t)m * L.token_bytes, L, nb_next, t, g);
             else acur[m].load(prep + (size_t)m * L.token_bytes, L, block_of(it), t, g);
         }
 
@@ -427,11 +492,11 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     if (warp > 0 && t == 0) {
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            red[warp - 1][m * 2][g] = yacc[m][0];
-            red[warp - 1][m * 2 + 1][g] = yacc[m][1];
+            red[buf][warp - 1][m * 2][g] = yacc[m][0];
+            red[buf][warp - 1][m * 2 + 1][g] = yacc[m][1];
         }
     }
-    __syncthreads();
+    __syncthreads(); // one barrier per tile: the two halves of `red` alternate
     if (warp == 0 && t == 0) {
 #pragma unroll
         for (int m = 0; m < MT; m++)
@@ -439,11 +504,18 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
             for (int r = 0; r < 2; r++) {
                 float v = yacc[m][r];
 #pragma unroll
-                for (int ww = 0; ww < WARPS - 1; ww++) v += red[ww][m * 2 + r][g];
-                const uint32_t row = tile0 * 16 + g + r * 8;
-                if (row < rows) y[y_base + (size_t)m * rows + row] = v;
+                for (int ww = 0; ww < WARPS - 1; ww++) v += red[buf][ww][m * 2 + r][g];
+                const uint32_t row = here.tile0 * 16 + g + r * 8;
+                if (row < here.rows) here.y[y_base + (size_t)m * here.rows + row] = v;
             }
     }
+    if (!more) break;
+    tile = next_tile;
+    here = next;
+#pragma unroll
+    for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
+    }
+    if (P.world > 1) tp_finish(P);
 }
 
 template <typename... KArgs, typename... Args>
@@ -489,8 +561,23 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
         const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need); // prefer small k on ties
         if (waste < best) { best = waste; warps = k; }
     }
+    // Persistent blocks: as many as stay resident at once (fewer with routes in grid.y), each walking its tiles.
+    static int occupancy[MAX_WARPS + 1] = {};
+    if (!occupancy[warps]) {
+        int occ = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_i8<FMT, MT>, (int)warps * 32, 0) != cudaSuccess || occ < 1) occ = 1;
+        occupancy[warps] = occ;
+    }
+    const uint32_t resident = (uint32_t)dev->sm_count * (uint32_t)occupancy[warps];
+    grid.x = std::min(blocks, std::max(1u, resident / grid.y));
+    TpPush push{};
+    if (dev->tp_push && !expert) { // one launch covers every target: it can do the exchange itself
+        push = *dev->tp_push;
+        dev->tp_push = nullptr;
+        dev->tp_pushed = true;
+    }
     return launch_pdl(k_gemv_i8<FMT, MT>, grid, dim3(warps * 32), dev->stream, T, a[0].row_bytes, prep, L, a[0].ids, a[0].x_div,
-                      a[0].experts);
+                      a[0].experts, push);
 }
 
 } // namespace
@@ -593,7 +680,7 @@ cudaError_t launch_static(const uint8_t *w, uint32_t rows, uint32_t pitch, float
         const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need);
         if (waste < best) { best = waste; warps = k; }
     }
-    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u);
+    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u, TpPush{});
     return cudaPeekAtLastError();
 }
 

@@ -28,6 +28,8 @@ struct fq_device {
     bool fail_completion = false; // test hook: next synchronize reports failure
     fq_counters counters{};
     bool capturing = false;       // between fq_capture_begin and fq_capture_end
+    const struct TpPush *tp_push = nullptr; // set while a projection that exchanges its own output is enqueued
+    bool tp_pushed = false;                 // the kernel that was launched took tp_push
     uint64_t captured_kernels = 0;
     std::map<uintptr_t, size_t> allocations; // buffers handed out by fq_buffer_alloc
     // Fixed scratch, allocated once at creation.
@@ -122,6 +124,24 @@ int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_
 // of the `count` experts from `first`.
 int fq_launch_moe_local_ids(fq_device *dev, const uint32_t *ids, const uint32_t *sorted, uint32_t routes, uint32_t first, uint32_t count,
                             uint32_t *out);
+// Fused exchange of a row-sharded projection (comm.cu, gemv_i8.cu): the kernel that computes this rank's
+// output rows writes them into its slice of the symmetric buffer; the last of its blocks to finish copies the
+// slice to the same offset of every peer's buffer (peer stores over NVLink), raises this rank's sequence flag
+// on every peer and waits -- bounded -- for theirs, so when the kernel has ended every rank's rows are in
+// local memory.  world <= 1 turns it off.
+struct TpPush {
+    uint8_t *peer[8];    // symmetric buffers by rank (peer[rank] is the local one)
+    uint32_t world, rank, slot;
+    uint32_t *seq;       // local: last sequence number used per (slot, peer)
+    uint32_t *counter;   // local: blocks of this launch that have finished
+    size_t flag_off;     // flags[slot][sender] start here in every buffer
+    size_t slice_off, slice_bytes; // this rank's slice of the gathered region (multiples of 16)
+    int *status;
+};
+struct fq_comm;
+// Fills `out` for the next exchange of `c` (takes a flag slot); FQ_ERR_RANGE unless [y, y + bytes) lies in
+// the local symmetric buffer.
+int fq_comm_begin_push(fq_comm *c, const void *y, size_t bytes, TpPush *out);
 // The symmetric buffer of a communicator and its geometry (comm.cu).
 struct fq_comm;
 uint8_t *fq_comm_local(fq_comm *c);

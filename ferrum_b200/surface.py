@@ -294,6 +294,18 @@ def project_many(d: Device, ws: Sequence[Matrix], x: torch.Tensor, m: int, ys: S
     d.check(d._L.fq_project_many(d.handle, wa, n, _ptr(x), _dtype_id(x), x.numel(), m, ya, _dtype_id(ys[0])))
 
 
+def project_many_gather(d: Device, comm: "Comm", offset_bytes: int, shard_bytes: int, ws: Sequence[Matrix], x: torch.Tensor, m: int,
+                        ys: Sequence[torch.Tensor]) -> None:
+    """Row-sharded ``project_many`` whose outputs (views of ``comm``'s buffer inside this rank's slice of the
+    region) are exchanged by the projection kernel itself at decode widths, else by ``comm.all_gather``."""
+    _need(d, x, *ys)
+    n = len(ws)
+    wa = (C.c_void_p * n)(*[w.handle.value for w in ws])
+    ya = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    d.check(d._L.fq_project_many_gather(d.handle, comm.handle, offset_bytes, shard_bytes, wa, n, _ptr(x), _dtype_id(x), x.numel(), m,
+                                        ya, _dtype_id(ys[0])))
+
+
 def project_id(d: Device, w: Matrix, x: torch.Tensor, ids: torch.Tensor, routes: int, x_div: int, y: torch.Tensor) -> None:
     """``HybridModel::project_id``: route r uses expert ids[r] on activation row r // x_div."""
     _need(d, x, ids, y)

@@ -39,6 +39,25 @@ def shard_packed(packed: np.ndarray, fmt: int, rows: int, cols: int, rank: int, 
     return np.ascontiguousarray(view[:, first:first + per, :]).reshape(-1)
 
 
+def expert_range(experts: int, rank: int, world: int) -> Tuple[int, int]:
+    """First expert and expert count of ``rank`` under expert parallelism (``experts`` must divide evenly)."""
+    return shard_range(experts, rank, world)
+
+
+def shard_experts(packed: np.ndarray, fmt: int, rows_e: int, cols: int, experts: int, rank: int, world: int) -> np.ndarray:
+    """The GGUF bytes of ``rank``'s experts of a stacked ``[experts, rows_e, cols]`` matrix: one contiguous slice
+    (`expert_matrix`, src/quantization.rs:136-139)."""
+    el, bb = BLOCK[fmt]
+    if cols % el:
+        raise ValueError("row width is not a whole number of blocks")
+    per_expert = cols // el * bb * rows_e
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    if packed.size != per_expert * experts:
+        raise ValueError("byte length differs from geometry")
+    first, count = expert_range(experts, rank, world)
+    return packed[first * per_expert:(first + count) * per_expert]
+
+
 def gathered_to_rows(gathered, m: int, rows: int, world: int):
     """``all_gather_into_tensor`` concatenates rank outputs ``[world][m][rows / world]``; the projection's
     output is ``[m][rows]``.  Works on torch tensors and numpy arrays (a view plus one transposing copy)."""

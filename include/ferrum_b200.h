@@ -243,6 +243,15 @@ int fq_comm_all_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size
 int fq_comm_all_gather_rows(fq_device *dev, fq_comm *comm, size_t region_offset, size_t row_bytes, const uint32_t *bounds,
                             uint32_t stride, size_t total_rows);
 int fq_comm_destroy(fq_comm *comm);
+/* `fq_project_many` on row shards with the exchange included: every y[i] (F32) must lie in this rank's
+ * slice [region_offset + rank * shard_bytes, + shard_bytes) of a gathered region of the symmetric buffer;
+ * when the call's work has run, the region holds every rank's slice, as after `fq_comm_all_gather`.  At
+ * decode widths (m <= 4, Q4_K / Q6_K) the projection kernel stores its results to every peer itself and its
+ * last block does the handshake -- one launch for compute and exchange; other shapes project, then gather
+ * the region.  A region may be written again only after another exchange of the same communicator has
+ * completed in between. */
+int fq_project_many_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size_t shard_bytes, const fq_matrix *const *w,
+                           size_t count, const void *x, int x_dtype, size_t x_elems, size_t m, void *const *y, int y_dtype);
 
 /* ---- expert-parallel MoE block (no counterpart in the single-GPU reference) -------------------- */
 

@@ -54,6 +54,29 @@ def _rank(rank, world, port, out_dir):
             d.synchronize()
         got = tp.gathered_to_rows(comm.view(4096, world * m * per), m, rows, world).cpu().numpy()
         assert ref.rel_err(got, ref.matmul(ref.Q4_K, packed, rows, cols, x.cpu().numpy(), m)) <= 1e-3
+        # compute and exchange in one kernel (decode widths), q|k-like pair sharing x; m = 8 takes the
+        # project-then-gather route of the same call
+        rows2 = 256
+        per2 = rows2 // world
+        packed2 = ref.random_matrix(ref.Q4_K, rows2, cols, seed=7)
+        w2 = S.Matrix.from_packed(d, per2, cols, 1, ref.Q4_K, tp.shard_packed(packed2, ref.Q4_K, rows2, cols, rank, world))
+        for mm in (1, 4, 8):
+            xm = torch.from_numpy(np.random.default_rng(20 + mm).standard_normal((mm, cols)).astype(np.float32)).cuda()
+            shard = mm * (per + per2) * 4  # this rank's slice: [mm][per] then [mm][per2]
+            region = 65536
+            ya = comm.view(region + rank * shard, mm * per)
+            yb = comm.view(region + rank * shard + mm * per * 4, mm * per2)
+            for rep in range(2):
+                S.project_many_gather(d, comm, region, shard, [w, w2], xm * float(rep + 1), mm, [ya, yb])
+                comm.all_gather(4096, 16)  # another exchange before the region is written again
+                d.synchronize()
+                full = comm.view(region, world * shard // 4).cpu().numpy().reshape(world, -1)
+                got_a = np.concatenate([full[r, :mm * per].reshape(mm, per) for r in range(world)], axis=1)
+                got_b = np.concatenate([full[r, mm * per:].reshape(mm, per2) for r in range(world)], axis=1)
+                xs = (xm * float(rep + 1)).cpu().numpy()
+                assert ref.rel_err(got_a, ref.matmul(ref.Q4_K, packed, rows, cols, xs, mm)) <= 1e-3, (rank, mm, rep)
+                assert ref.rel_err(got_b, ref.matmul(ref.Q4_K, packed2, rows2, cols, xs, mm)) <= 1e-3, (rank, mm, rep)
+                dist.barrier()
         dist.barrier()
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
         comm.close()

@@ -47,7 +47,60 @@ def test_two_cpu_ranks_reassemble_the_projection(tmp_path, fmt):
     assert np.load(out).shape == (m, rows)
 
 
+def _ep_rank_main(rank, world, port, out_path):
+    """Expert parallelism on CPU ranks: replicated routing, each rank computes the expert-sorted rows of its own
+    experts (the oracle stands in for the kernels), the runs are exchanged, every rank combines."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        experts, used, hidden, ef, m = 8, 2, 256, 256, 5
+        gate_e = ref.random_matrix(ref.Q4_K, experts * ef, hidden, 1)
+        down_e = ref.random_matrix(ref.Q6_K, experts * hidden, ef, 2)
+        x = (np.random.default_rng(3).standard_normal((m, hidden)) * 0.3).astype(np.float32)
+        logits = np.random.default_rng(4).standard_normal((m, experts)).astype(np.float32)
+        ids, wts, gate = ref.moe_route(logits, x, x[0], experts, used, hidden, m, False, True, False)
+        offsets, sorted_, position = ref.moe_map(ids, experts)
+        routes = m * used
+        first, count = tp.expert_range(experts, rank, world)
+        lo, hi = int(offsets[first]), int(offsets[first + count])
+        xg = x[np.asarray(sorted_) // used]  # expert-sorted activation rows
+        sorted_ids = np.asarray(ids).reshape(-1)[np.asarray(sorted_)]
+        my_gate = tp.shard_experts(gate_e, ref.Q4_K, ef, hidden, experts, rank, world)
+        my_down = tp.shard_experts(down_e, ref.Q6_K, hidden, ef, experts, rank, world)
+        rows = np.zeros((routes, hidden), dtype=np.float32)
+        if hi > lo:
+            local = (sorted_ids[lo:hi] - first).astype(np.uint32)
+            h = ref.matmul_id(ref.Q4_K, my_gate, ef, hidden, xg[lo:hi], local, 1)
+            rows[lo:hi] = ref.matmul_id(ref.Q6_K, my_down, hidden, ef, h, local, 1)
+        # variable-length all-gather: every rank contributes its run of rows
+        runs = [None] * world
+        dist.all_gather_object(runs, (lo, hi, rows[lo:hi].copy()))
+        full = np.zeros_like(rows)
+        for a, b, part in runs:
+            full[a:b] = part
+        zero = np.zeros((m, hidden), dtype=np.float32)
+        got = ref.moe_combine(full, wts, position, zero, gate, hidden, used, m, identity=False)
+        # one rank with every expert, identity order
+        h1 = ref.matmul_id(ref.Q4_K, gate_e, ef, hidden, x, ids, used)
+        d1 = ref.matmul_id(ref.Q6_K, down_e, hidden, ef, h1, ids, 1)
+        want = ref.moe_combine(d1, wts, ids, zero, gate, hidden, used, m, identity=True)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), "expert-parallel result differs from one rank"
+        if rank == 0:
+            np.save(out_path, got)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_cpu_ranks_split_the_experts(tmp_path):
+    out = str(tmp_path / "moe.npy")
+    mp.spawn(_ep_rank_main, args=(2, free_port(), out), nprocs=2, join=True)
+    assert np.load(out).shape == (5, 256)
+
+
 def test_shard_arithmetic():
+    assert tp.expert_range(256, 5, 8) == (160, 32)
+    e = ref.random_matrix(ref.Q6_K, 4 * 2, 256, seed=2)  # 4 experts x 2 rows
+    assert np.array_equal(tp.shard_experts(e, ref.Q6_K, 2, 256, 4, 1, 2), e[2 * 2 * 210:])
     assert tp.shard_range(17408, 3, 8) == (6528, 2176)
     with pytest.raises(ValueError):
         tp.shard_range(10, 0, 4)
