@@ -69,15 +69,10 @@ PrepI8 prep_i8_layout(uint32_t cols) {
     return L;
 }
 
-// One warp per (activation row, superblock); lane l owns the eight values at 256 b + 8 l.
-__global__ void __launch_bounds__(128)
-k_prep_i8(const float *__restrict__ x, uint32_t xrows, PrepI8 L, uint8_t *__restrict__ out) {
-    pdl_trigger();
-    pdl_wait();
-    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    const uint32_t xr = warp / L.nblk, b = warp % L.nblk;
-    if (xr >= xrows) return;
-    const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)xr * L.cols + (size_t)b * 256 + lane * 8);
+// Superblock b of one activation row, by one warp (lane l owns the eight values at 256 b + 8 l), written in
+// the layout above at `base` (global or shared memory).
+__device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base) {
+    const float4 *src = reinterpret_cast<const float4 *>(xrow + (size_t)b * 256 + lane * 8);
     const float4 v0 = src[0], v1 = src[1];
     const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     float amax = 0.f;
@@ -114,7 +109,6 @@ k_prep_i8(const float *__restrict__ x, uint32_t xrows, PrepI8 L, uint8_t *__rest
         sum_hi += h;
         sum_lo += l;
     }
-    uint8_t *base = out + (size_t)xr * L.token_bytes;
     auto pack8 = [](const uint8_t *p) {
         uint2 r;
         r.x = p[0] | (p[1] << 8) | (p[2] << 16) | ((uint32_t)p[3] << 24);
@@ -140,6 +134,17 @@ k_prep_i8(const float *__restrict__ x, uint32_t xrows, PrepI8 L, uint8_t *__rest
     }
 }
 
+// One warp per (activation row, superblock).
+__global__ void __launch_bounds__(128)
+k_prep_i8(const float *__restrict__ x, uint32_t xrows, PrepI8 L, uint8_t *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const uint32_t xr = warp / L.nblk, b = warp % L.nblk;
+    if (xr >= xrows) return;
+    prep_superblock(x + (size_t)xr * L.cols, b, lane, L, out + (size_t)xr * L.token_bytes);
+}
+
 // ---------------------------------------------------------------- helpers
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -160,6 +165,24 @@ __device__ __forceinline__ uint32_t ldx32(const void *p) {
     asm volatile("ld.global.ca.u32 %0, [%1];" : "=r"(r) : "l"(p));
     return r;
 }
+// The same from shared memory (generic pointer in, shared-state-space load out).
+__device__ __forceinline__ uint4 lds128(const void *p) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return r;
+}
+__device__ __forceinline__ uint2 lds64(const void *p) {
+    uint2 r;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return r;
+}
+__device__ __forceinline__ uint32_t lds32(const void *p) {
+    uint32_t r;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return r;
+}
+template <bool SH> __device__ __forceinline__ uint4 ldx128_at(const void *p) { return SH ? lds128(p) : ldx128(p); }
+template <bool SH> __device__ __forceinline__ uint32_t ldx32_at(const void *p) { return SH ? lds32(p) : ldx32(p); }
 // Weights: immutable, read once -> read-only path, no L1 allocation.
 __device__ __forceinline__ uint4 ldw128(const void *p) {
     uint4 r;
@@ -195,6 +218,14 @@ struct Q4Raw {
         qa = ldw128(blk + 16 + 16 * t);
         qb = ldw128(blk + 80 + 16 * t);
     }
+    // From a staged row segment of `k` consecutive superblocks (144 bytes each), superblock `b` of it.
+    __device__ __forceinline__ void load_staged(const uint8_t *seg, const uint8_t *, uint32_t, uint32_t, uint32_t, uint32_t b, int t) {
+        const uint8_t *blk = seg + (size_t)b * 144;
+        hdr = lds128(blk);
+        qa = lds128(blk + 16 + 16 * t);
+        qb = lds128(blk + 80 + 16 * t);
+    }
+    static constexpr uint32_t STAGED_BYTES = 144; // per superblock and row
 };
 struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
     uint4 q0, q1, qh; // ql of 32-groups 0|2 and 1|3 of half n, qh of half n: run lh (16 bytes each)
@@ -209,6 +240,18 @@ struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
         sc = ldw64(row + (size_t)nblk * 192 + (size_t)b * 16 + 8 * (t & 1));
         d = ldw16(row + (size_t)nblk * 208 + (size_t)b * 2);
     }
+    // From a staged row segment of `k` consecutive superblocks, planes [ql k x 128][qh k x 64][scales k x 16];
+    // the 2-byte d comes from the row in global memory (superblock `gb` of `nblk`).
+    __device__ __forceinline__ void load_staged(const uint8_t *seg, const uint8_t *row, uint32_t nblk, uint32_t gb, uint32_t k, uint32_t b, int t) {
+        const int n = t >> 1, lh = t & 1;
+        const uint8_t *ql = seg + (size_t)b * 128 + 64 * n + 16 * lh;
+        q0 = lds128(ql);
+        q1 = lds128(ql + 32);
+        qh = lds128(seg + (size_t)k * 128 + (size_t)b * 64 + 32 * n + 16 * lh);
+        sc = lds64(seg + (size_t)k * 192 + (size_t)b * 16 + 8 * (t & 1));
+        d = ldw16(row + (size_t)nblk * 208 + (size_t)gb * 2);
+    }
+    static constexpr uint32_t STAGED_BYTES = 208; // per superblock and row
 };
 
 // The prepared activations of one row that one thread needs for one superblock.
@@ -219,25 +262,127 @@ template <int FMT> struct Act {
     uint4 xb[FMT == FQ_Q4_K ? 2 : 4];
     uint4 sx;
     float inv;
-    __device__ __forceinline__ void load(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) {
+    __device__ __forceinline__ void load(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) { load_at<false>(tok, L, b, t, g); }
+    // SH: `tok` points into shared memory.
+    template <bool SH> __device__ __forceinline__ void load_at(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) {
         const int plane = g >> 2, u = t & 1;
         if constexpr (FMT == FQ_Q4_K) {
             const bool feeds = (t >> 1) == (g & 1);
             const int chunk = (((g & 3) >> 1) ? 2 : 0) + (t >> 1);
             const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 64 * chunk + 16 * (t & 1);
 #pragma unroll
-            for (int i = 0; i < 2; i++) xb[i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
-            sx = ldx128(tok + L.sx32_off + (size_t)b * 32 + 16 * u);
+            for (int i = 0; i < 2; i++) xb[i] = feeds ? ldx128_at<SH>(src + 32 * i) : make_uint4(0, 0, 0, 0);
+            sx = ldx128_at<SH>(tok + L.sx32_off + (size_t)b * 32 + 16 * u);
         } else {
             const bool feeds = (g & 3) == t;
             const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 128 * (t >> 1) + 16 * (t & 1);
 #pragma unroll
-            for (int i = 0; i < 4; i++) xb[i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
-            sx = ldx128(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
+            for (int i = 0; i < 4; i++) xb[i] = feeds ? ldx128_at<SH>(src + 32 * i) : make_uint4(0, 0, 0, 0);
+            sx = ldx128_at<SH>(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
         }
-        inv = __uint_as_float(ldx32(tok + L.isc_off + (size_t)b * 4));
+        inv = __uint_as_float(ldx32_at<SH>(tok + L.isc_off + (size_t)b * 4));
     }
 };
+
+// One superblock of a 16-row tile against MT prepared activation rows: adds into yacc[m][r] this thread's
+// share (its scale groups and plane) of rows g and g + 8.
+template <int FMT, int MT, typename RawT>
+__device__ __forceinline__ void superblock_dot(const RawT (&cur)[2], const Act<FMT> (&acur)[MT], int t, int g, float (&yacc)[MT][2]) {
+    // This thread feeds column g of B (scale group g & 3, plane g >> 2) on its own k slots only, and
+    // only if those k slots belong to that scale group; everything else it feeds is zero.
+    //   Q6_K: group j = the k slots of quad thread j.
+    //   Q4_K: group j = chunk j; thread t holds chunk t / 2 in its first operand word (k slots 4t ..)
+    //         and chunk 2 + t / 2 in its second (k slots 16 + 4t ..).
+    const bool second = FMT == FQ_Q4_K && ((g & 3) >> 1); // Q4_K: the group sits in the second operand word
+    // It reads columns 2t, 2t+1 of the accumulators: scale groups 2 (t & 1), 2 (t & 1) + 1, plane t >> 1.
+    const int u = t & 1;
+    const float plane_weight = (t >> 1) ? 1.f : 256.f;
+    (void)second;
+    (void)u;
+    if constexpr (FMT == FQ_Q4_K) {
+        // The four scales and minimums of sub-blocks 4u .. 4u+3, one per byte.
+        uint32_t sc4[2], mn4[2];
+        float dsc[2], dmn[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint4 h = cur[r].hdr;
+            sc4[r] = u ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
+            mn4[r] = u ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
+            dsc[r] = f16_bits_to_f32((uint16_t)(h.x & 0xFFFFu)) * plane_weight;
+            dmn[r] = (t >> 1) ? 0.f : f16_bits_to_f32((uint16_t)(h.x >> 16)); // minimum term once per plane pair
+        }
+        // u8 operands: low nibbles (even sub-block of the chunk) and high nibbles (odd sub-block); words
+        // 0..3 from the first chunk, 4..7 from the second.
+        uint32_t lo[2][8], hi[2][8];
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t wd = word_of(i < 4 ? cur[r].qa : cur[r].qb, i & 3);
+                lo[r][i] = wd & 0x0F0F0F0Fu;
+                hi[r][i] = (wd >> 4) & 0x0F0F0F0Fu;
+            }
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int i = 0; i < 4; i++) { // word i of either chunk <-> activation bytes 4i .. 4i+3 of the run
+                const uint32_t xl = word_of(acur[m].xb[0], i), xh = word_of(acur[m].xb[1], i);
+                mma_u8s8(cl, lo[0][i], lo[1][i], lo[0][4 + i], lo[1][4 + i], second ? 0u : xl, second ? xl : 0u);
+                mma_u8s8(ch, hi[0][i], hi[1][i], hi[0][4 + i], hi[1][4 + i], second ? 0u : xh, second ? xh : 0u);
+            }
+            // Columns 2t, 2t+1 = scale groups 2u, 2u+1: sub-blocks 4u (low), 4u+1 (high), 4u+2, 4u+3.
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const int dot = byte_u(sc4[r], 0) * cl[2 * r] + byte_u(sc4[r], 1) * ch[2 * r] + byte_u(sc4[r], 2) * cl[2 * r + 1] +
+                                byte_u(sc4[r], 3) * ch[2 * r + 1];
+                const uint4 &sx = acur[m].sx;
+                const int mins = byte_u(mn4[r], 0) * (int)sx.x + byte_u(mn4[r], 1) * (int)sx.y +
+                                 byte_u(mn4[r], 2) * (int)sx.z + byte_u(mn4[r], 3) * (int)sx.w;
+                yacc[m][r] = fmaf(acur[m].inv, dsc[r] * (float)dot - dmn[r] * (float)mins, yacc[m][r]);
+            }
+        }
+    } else {
+        // Q6_K: thread t = (n, lh) owns, for i = 0..3, the values 128 n + 32 i + 16 lh + [0, 16).
+        uint32_t v4[2][4][4]; // [row][i][word]: four 6-bit quants, one per byte
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int wi = 0; wi < 4; wi++) {
+                    const uint32_t lw = word_of((i & 1) ? cur[r].q1 : cur[r].q0, wi), hw = word_of(cur[r].qh, wi);
+                    const uint32_t lo4 = (i < 2) ? lw : (lw >> 4);
+                    const uint32_t hi4 = i == 0 ? (hw << 4) : i == 1 ? (hw << 2) : i == 2 ? hw : (hw >> 2);
+                    v4[r][i][wi] = lop3_select(lo4, hi4, 0x0F0F0F0Fu) & 0x3F3F3F3Fu;
+                }
+        float dd[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) dd[r] = f16_bits_to_f32((uint16_t)cur[r].d) * plane_weight;
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            int dot[2] = {0, 0};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                int c[4] = {0, 0, 0, 0};
+                const uint4 &xv = acur[m].xb[i];
+                mma_u8s8(c, v4[0][i][0], v4[1][i][0], v4[0][i][1], v4[1][i][1], xv.x, xv.y);
+                mma_u8s8(c, v4[0][i][2], v4[1][i][2], v4[0][i][3], v4[1][i][3], xv.z, xv.w);
+                // Columns 2t, 2t+1 = quad threads 2u, 2u+1 = (half u, runs 0 and 1): 16-groups
+                // 8u + 2i and 8u + 2i + 1.  (q - 32) is applied as  dot - 32 * sum(x bytes).
+                const uint32_t spair = word_of(acur[m].sx, i);
+                const int s0 = (int)(int16_t)(spair & 0xFFFFu), s1 = (int)(int16_t)(spair >> 16);
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const uint32_t scw = (i < 2) ? cur[r].sc.x : cur[r].sc.y;
+                    dot[r] += byte_s(scw, 2 * (i & 1)) * (c[2 * r] - 32 * s0) + byte_s(scw, 2 * (i & 1) + 1) * (c[2 * r + 1] - 32 * s1);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; r++) yacc[m][r] = fmaf(acur[m].inv * dd[r], (float)dot[r], yacc[m][r]);
+        }
+    }
+}
 
 // End of a launch whose outputs are one rank's slice of a gathered region: the last block to get here copies
 // the slice to every peer, raises this rank's sequence flag there and waits (bounded) until every peer's flag
@@ -352,15 +497,6 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     pdl_trigger();
     pdl_wait();
 
-    // This thread feeds column g of B (scale group g & 3, plane g >> 2) on its own k slots only, and
-    // only if those k slots belong to that scale group; everything else it feeds is zero.
-    //   Q6_K: group j = the k slots of quad thread j.
-    //   Q4_K: group j = chunk j; thread t holds chunk t / 2 in its first operand word (k slots 4t ..)
-    //         and chunk 2 + t / 2 in its second (k slots 16 + 4t ..).
-    const bool second = FMT == FQ_Q4_K && ((g & 3) >> 1); // Q4_K: the group sits in the second operand word
-    // It reads columns 2t, 2t+1 of the accumulators: scale groups 2 (t & 1), 2 (t & 1) + 1, plane t >> 1.
-    const int u = t & 1;
-    const float plane_weight = (t >> 1) ? 1.f : 256.f;
     // With one activation row its fragments are fetched one superblock ahead, like the weights; with
     // more rows the registers do not allow that and they are fetched at the top of the iteration.
     constexpr bool AHEAD = MT == 1;
@@ -391,89 +527,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
             else acur[m].load(prep + (size_t)m * L.token_bytes, L, block_of(it), t, g);
         }
 
-        if constexpr (FMT == FQ_Q4_K) {
-            // The four scales and minimums of sub-blocks 4u .. 4u+3, one per byte.
-            uint32_t sc4[2], mn4[2];
-            float dsc[2], dmn[2];
-#pragma unroll
-            for (int r = 0; r < 2; r++) {
-                const uint4 h = cur[r].hdr;
-                sc4[r] = u ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
-                mn4[r] = u ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
-                dsc[r] = f16_bits_to_f32((uint16_t)(h.x & 0xFFFFu)) * plane_weight;
-                dmn[r] = (t >> 1) ? 0.f : f16_bits_to_f32((uint16_t)(h.x >> 16)); // minimum term once per plane pair
-            }
-            // u8 operands: low nibbles (even sub-block of the chunk) and high nibbles (odd sub-block); words
-            // 0..3 from the first chunk, 4..7 from the second.
-            uint32_t lo[2][8], hi[2][8];
-#pragma unroll
-            for (int r = 0; r < 2; r++)
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const uint32_t wd = word_of(i < 4 ? cur[r].qa : cur[r].qb, i & 3);
-                    lo[r][i] = wd & 0x0F0F0F0Fu;
-                    hi[r][i] = (wd >> 4) & 0x0F0F0F0Fu;
-                }
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int i = 0; i < 4; i++) { // word i of either chunk <-> activation bytes 4i .. 4i+3 of the run
-                    const uint32_t xl = word_of(acur[m].xb[0], i), xh = word_of(acur[m].xb[1], i);
-                    mma_u8s8(cl, lo[0][i], lo[1][i], lo[0][4 + i], lo[1][4 + i], second ? 0u : xl, second ? xl : 0u);
-                    mma_u8s8(ch, hi[0][i], hi[1][i], hi[0][4 + i], hi[1][4 + i], second ? 0u : xh, second ? xh : 0u);
-                }
-                // Columns 2t, 2t+1 = scale groups 2u, 2u+1: sub-blocks 4u (low), 4u+1 (high), 4u+2, 4u+3.
-#pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    const int dot = byte_u(sc4[r], 0) * cl[2 * r] + byte_u(sc4[r], 1) * ch[2 * r] + byte_u(sc4[r], 2) * cl[2 * r + 1] +
-                                    byte_u(sc4[r], 3) * ch[2 * r + 1];
-                    const uint4 &sx = acur[m].sx;
-                    const int mins = byte_u(mn4[r], 0) * (int)sx.x + byte_u(mn4[r], 1) * (int)sx.y +
-                                     byte_u(mn4[r], 2) * (int)sx.z + byte_u(mn4[r], 3) * (int)sx.w;
-                    yacc[m][r] = fmaf(acur[m].inv, dsc[r] * (float)dot - dmn[r] * (float)mins, yacc[m][r]);
-                }
-            }
-        } else {
-            // Q6_K: thread t = (n, lh) owns, for i = 0..3, the values 128 n + 32 i + 16 lh + [0, 16).
-            uint32_t v4[2][4][4]; // [row][i][word]: four 6-bit quants, one per byte
-#pragma unroll
-            for (int r = 0; r < 2; r++)
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-#pragma unroll
-                    for (int wi = 0; wi < 4; wi++) {
-                        const uint32_t lw = word_of((i & 1) ? cur[r].q1 : cur[r].q0, wi), hw = word_of(cur[r].qh, wi);
-                        const uint32_t lo4 = (i < 2) ? lw : (lw >> 4);
-                        const uint32_t hi4 = i == 0 ? (hw << 4) : i == 1 ? (hw << 2) : i == 2 ? hw : (hw >> 2);
-                        v4[r][i][wi] = lop3_select(lo4, hi4, 0x0F0F0F0Fu) & 0x3F3F3F3Fu;
-                    }
-            float dd[2];
-#pragma unroll
-            for (int r = 0; r < 2; r++) dd[r] = f16_bits_to_f32((uint16_t)cur[r].d) * plane_weight;
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                int dot[2] = {0, 0};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    int c[4] = {0, 0, 0, 0};
-                    const uint4 &xv = acur[m].xb[i];
-                    mma_u8s8(c, v4[0][i][0], v4[1][i][0], v4[0][i][1], v4[1][i][1], xv.x, xv.y);
-                    mma_u8s8(c, v4[0][i][2], v4[1][i][2], v4[0][i][3], v4[1][i][3], xv.z, xv.w);
-                    // Columns 2t, 2t+1 = quad threads 2u, 2u+1 = (half u, runs 0 and 1): 16-groups
-                    // 8u + 2i and 8u + 2i + 1.  (q - 32) is applied as  dot - 32 * sum(x bytes).
-                    const uint32_t spair = word_of(acur[m].sx, i);
-                    const int s0 = (int)(int16_t)(spair & 0xFFFFu), s1 = (int)(int16_t)(spair >> 16);
-#pragma unroll
-                    for (int r = 0; r < 2; r++) {
-                        const uint32_t scw = (i < 2) ? cur[r].sc.x : cur[r].sc.y;
-                        dot[r] += byte_s(scw, 2 * (i & 1)) * (c[2 * r] - 32 * s0) + byte_s(scw, 2 * (i & 1) + 1) * (c[2 * r + 1] - 32 * s1);
-                    }
-                }
-#pragma unroll
-                for (int r = 0; r < 2; r++) yacc[m][r] = fmaf(acur[m].inv * dd[r], (float)dot[r], yacc[m][r]);
-            }
-        }
+        superblock_dot<FMT, MT>(cur, acur, t, g, yacc);
         cur[0] = nxt[0];
         cur[1] = nxt[1];
         if (AHEAD) {
@@ -518,6 +572,208 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     if (P.world > 1) tp_finish(P);
 }
 
+// ---------------------------------------------------------------- staged variant
+//
+// The same arithmetic with the weights staged through shared memory by the copy engine instead of through
+// registers: what a warp can keep in flight with register prefetch is one superblock per thread, which caps
+// the stream at about 60% of what HBM delivers; a ring of bulk copies has no such limit.
+//
+//   warp k (producer)   lanes 0..15 each own one row of the block's current 16-row tile and issue, per stage,
+//                       one bulk copy (Q4_K) or three (Q6_K planes) of that row's next `k` superblocks into the
+//                       ring, completing on the stage's mbarrier.  Weights are immutable, so the producer starts
+//                       at once: the ring fills while the kernel before this one is still running.
+//   warps 0..k-1        wait for the activations of the kernel before (griddepcontrol.wait), prepare them (16-bit
+//                       integers, sums, scale: no separate preparation launch) into shared memory once, then per stage: warp c takes superblock c of the
+//                       stage (rows g, g + 8 per thread, as in the register variant), releases the stage, and at
+//                       the end of a tile the warps' partial sums meet in shared memory.
+//
+// Blocks are persistent (tiles b, b + gridDim.x, ...).  Every wait is bounded; a wait that gives up records
+// FQ_ERR_TIMEOUT, raises the block's abort flag and from then on no wait blocks any more: the block runs its
+// control flow to the end (with meaningless sums) so that every barrier is still reached by every warp.
+constexpr int RING_STAGES_MAX = 8;
+constexpr uint32_t RING_WAIT_NS = 2000000000u;
+
+struct RingCfg {
+    uint32_t k;          // consumer warps = superblocks per stage
+    uint32_t stages;     // ring depth
+    uint32_t row_stride; // bytes between the segments of consecutive rows in a stage (padded against bank conflicts)
+    uint32_t act_bytes;  // MT * token_bytes
+};
+
+__device__ __forceinline__ uint32_t s_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool ring_try(uint64_t *bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok)
+                 : "r"(s_addr(bar)), "r"(parity), "r"(hint_ns)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void ring_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, int *status) {
+    if (ring_try(bar, parity, 0)) return;
+    if (*abort_flag) return;
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        if (ring_try(bar, parity, 20000) || *abort_flag) return;
+        uint64_t now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - t0 > RING_WAIT_NS) break;
+    }
+    *(volatile int *)status = (int)FQ_ERR_TIMEOUT;
+    *abort_flag = 1u;
+}
+__device__ __forceinline__ void bulk_copy(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(s_addr(dst)), "l"(src), "r"(bytes), "r"(s_addr(bar))
+                 : "memory");
+}
+
+template <int FMT, int MT>
+__global__ void __launch_bounds__(MT >= 3 ? 288 : MT == 2 ? 416 : 544)
+k_gemv_ring(const __grid_constant__ GemvTargets T, uint32_t pitch, const float *__restrict__ x, PrepI8 L, RingCfg R,
+            const __grid_constant__ TpPush P, int *status) {
+    using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    __shared__ uint64_t full[RING_STAGES_MAX], empty[RING_STAGES_MAX];
+    __shared__ float red[2][MAX_WARPS - 1][MT * 2][8];
+    __shared__ uint32_t abort_flag;
+    const uint32_t k = R.k, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    uint8_t *act = ring_smem, *ring = ring_smem + R.act_bytes;
+    const uint32_t stage_bytes = 16 * R.row_stride, nblk = L.nblk, spt = (nblk + k - 1) / k; // stages per tile
+    const uint32_t total_tiles = T.tile_end[T.count - 1];
+
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < R.stages; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(&full[s])), "r"(1u));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(&empty[s])), "r"(k));
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    volatile uint32_t *aborted = &abort_flag;
+
+    auto tile_rows = [&](uint32_t tile, uint32_t &rows, uint32_t &tile0, float *&y) -> const uint8_t * {
+        uint32_t which = 0, first_block = 0;
+#pragma unroll
+        for (int i = 0; i < MAX_TARGETS - 1; i++)
+            if ((uint32_t)i + 1 < T.count && tile >= T.tile_end[i]) { which = i + 1; first_block = T.tile_end[i]; }
+        rows = T.rows[which];
+        tile0 = tile - first_block;
+        y = T.y[which];
+        return T.w[which];
+    };
+
+    if (warp == k) {
+        // ---- producer
+        uint32_t it = 0, s = 0, phase = 0; // stage it % stages, phase (it / stages) % 2, kept by counting
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            uint32_t rows, tile0;
+            float *y;
+            const uint8_t *w = tile_rows(tile, rows, tile0, y);
+            const uint8_t *row = w + (size_t)min(tile0 * 16 + (lane & 15), rows - 1) * pitch;
+            for (uint32_t j = 0; j < spt; j++, it++, s = s + 1 == R.stages ? 0 : s + 1, phase ^= (s == 0)) {
+                const uint32_t b0 = j * k, nsb = min(k, nblk - b0);
+                ring_wait(&empty[s], phase ^ 1u, aborted, status);
+                if (lane == 0)
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_addr(&full[s])), "r"(16u * nsb * Raw::STAGED_BYTES) : "memory");
+                __syncwarp();
+                if (lane < 16 && !*aborted) {
+                    uint8_t *dst = ring + (size_t)s * stage_bytes + (size_t)lane * R.row_stride;
+                    if constexpr (FMT == FQ_Q4_K) {
+                        bulk_copy(dst, row + (size_t)b0 * 144, nsb * 144, &full[s]);
+                    } else {
+                        bulk_copy(dst, row + (size_t)b0 * 128, nsb * 128, &full[s]);
+                        bulk_copy(dst + (size_t)k * 128, row + (size_t)nblk * 128 + (size_t)b0 * 64, nsb * 64, &full[s]);
+                        bulk_copy(dst + (size_t)k * 192, row + (size_t)nblk * 192 + (size_t)b0 * 16, nsb * 16, &full[s]);
+                    }
+                }
+            }
+        }
+        // Copies still in flight land in this block's shared memory: after an abort, give them (bounded) time.
+        if (*aborted && lane == 0)
+            for (uint32_t back = 0; back < R.stages && back < it; back++) {
+                const uint32_t i2 = it - 1 - back;
+                for (uint32_t n = 0; n < 1000u && !ring_try(&full[i2 % R.stages], (i2 / R.stages) & 1u, 20000); n++) {}
+            }
+    } else {
+        // ---- consumers
+        pdl_wait(); // the activations are the output of the kernel before
+        // Every block prepares the activations for itself, straight into shared memory (k_prep_i8's arithmetic).
+        for (uint32_t i = warp; i < MT * nblk; i += k) prep_superblock(x + (size_t)(i / nblk) * L.cols, i % nblk, lane, L, act + (size_t)(i / nblk) * L.token_bytes);
+        asm volatile("bar.sync 1, %0;" ::"r"(k * 32) : "memory");
+        float yacc[MT][2];
+#pragma unroll
+        for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
+        uint32_t s = 0, phase = 0, buf = 0;
+        // This thread's two row segments inside a stage, and where its warp's superblock sits in them.
+        const uint32_t seg0 = (uint32_t)g * R.row_stride, seg1 = (uint32_t)(g + 8) * R.row_stride;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, buf ^= 1u) {
+            uint32_t rows, tile0;
+            float *y;
+            const uint8_t *w = tile_rows(tile, rows, tile0, y);
+            const uint8_t *rowp[2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) rowp[r] = w + (size_t)min(tile0 * 16 + g + r * 8, rows - 1) * pitch;
+            const uint8_t *stage = ring + (size_t)s * stage_bytes;
+            for (uint32_t j = 0, b = warp; j < spt; j++, b += k) {
+                ring_wait(&full[s], phase, aborted, status);
+                if (b < nblk) {
+                    Raw cur[2];
+                    Act<FMT> acur[MT];
+                    cur[0].load_staged(stage + seg0, rowp[0], nblk, b, k, warp, t);
+                    cur[1].load_staged(stage + seg1, rowp[1], nblk, b, k, warp, t);
+#pragma unroll
+                    for (int m = 0; m < MT; m++) acur[m].template load_at<true>(act + (size_t)m * L.token_bytes, L, b, t, g);
+                    superblock_dot<FMT, MT>(cur, acur, t, g, yacc);
+                }
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_addr(&empty[s])) : "memory");
+                if (++s == R.stages) {
+                    s = 0;
+                    phase ^= 1u;
+                    stage = ring;
+                } else {
+                    stage += stage_bytes;
+                }
+            }
+            // Quad threads hold partial sums of different scale groups and planes: add them, then the warps.
+#pragma unroll
+            for (int m = 0; m < MT; m++)
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    yacc[m][r] += __shfl_xor_sync(0xffffffffu, yacc[m][r], 1);
+                    yacc[m][r] += __shfl_xor_sync(0xffffffffu, yacc[m][r], 2);
+                }
+            if (warp > 0 && t == 0) {
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    red[buf][warp - 1][m * 2][g] = yacc[m][0];
+                    red[buf][warp - 1][m * 2 + 1][g] = yacc[m][1];
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(k * 32) : "memory"); // one barrier per tile: the halves of `red` alternate
+            if (warp == 0 && t == 0) {
+#pragma unroll
+                for (int m = 0; m < MT; m++)
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        float v = yacc[m][r];
+                        for (uint32_t ww = 0; ww + 1 < k; ww++) v += red[buf][ww][m * 2 + r][g];
+                        const uint32_t row = tile0 * 16 + g + r * 8;
+                        if (row < rows) y[(size_t)m * rows + row] = v;
+                    }
+            }
+#pragma unroll
+            for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
+        }
+    }
+    if (P.world > 1) tp_finish(P);
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg{};
@@ -533,6 +789,82 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStre
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// The staged kernel for one launch, or cudaErrorNotSupported when its shared-memory needs do not fit (the
+// caller then takes the register variant).
+template <int FMT, int MT>
+cudaError_t launch_ring(fq_device *dev, const ProjectArgs *a, uint32_t count, const PrepI8 &L) {
+    using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
+    GemvTargets T{};
+    T.count = count;
+    uint32_t blocks = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        T.w[i] = a[i].w;
+        T.y[i] = (float *)a[i].y;
+        T.rows[i] = a[i].rows;
+        blocks += (a[i].rows + 15) / 16;
+        T.tile_end[i] = blocks;
+    }
+    // Consumer warps = superblocks per stage: as many as the registers of the variant allow, at least two
+    // superblocks per warp and tile, and the count that wastes the fewest warp slots on an uneven split.
+    const uint32_t nblk = L.nblk, cap = MT >= 3 ? 8u : MT == 2 ? 12u : (uint32_t)MAX_WARPS;
+    const uint32_t max_k = std::max(1u, std::min(cap, nblk / 2));
+    uint32_t k = max_k;
+    uint64_t best = ~0ull;
+    for (uint32_t c = std::max(1u, (max_k + 1) / 2); c <= max_k; c++) {
+        const uint64_t per = (nblk + c - 1) / c, waste = (per * c - nblk) * 1000 / nblk;
+        if (waste <= best) { best = waste; k = c; }
+    }
+    RingCfg R{};
+    R.k = k;
+    const uint32_t seg = k * Raw::STAGED_BYTES;
+    // Two adjacent rows are read by one quarter-warp: pad so that they fall on different banks.
+    const uint32_t want_mod = FMT == FQ_Q4_K ? 64u : 32u;
+    R.row_stride = seg + ((want_mod + 128u - seg % 128u) % 128u);
+    R.act_bytes = MT * L.token_bytes;
+    const uint32_t stage_bytes = 16 * R.row_stride, threads = (k + 1) * 32;
+    static bool configured = false;
+    constexpr uint32_t SMEM_MAX = 216 * 1024; // plus up to 8 KB of static shared memory: inside the 227 KB a block may have
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(k_gemv_ring<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    // As many blocks per SM as the threads allow (up to 4) while each still has a ring of at least 3 stages.
+    static const uint32_t per_sm_cap = [] { const char *e = getenv("FQ_RING_PER_SM"); return e ? (uint32_t)atoi(e) : 4u; }();
+    uint32_t per_sm = std::max(1u, std::min(per_sm_cap, 2048u / threads)), smem = 0;
+    for (;; per_sm--) {
+        const uint32_t budget = SMEM_MAX / per_sm - 6 * 1024;
+        if (budget > R.act_bytes && (budget - R.act_bytes) / stage_bytes >= 3) {
+            static const uint32_t stage_cap = [] { const char *e = getenv("FQ_RING_STAGES"); return e ? (uint32_t)atoi(e) : (uint32_t)RING_STAGES_MAX; }();
+            R.stages = std::min<uint32_t>(stage_cap, (budget - R.act_bytes) / stage_bytes);
+            smem = R.act_bytes + R.stages * stage_bytes;
+            break;
+        }
+        if (per_sm == 1) return cudaErrorNotSupported;
+    }
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_ring<FMT, MT>, (int)threads, smem) != cudaSuccess || occ < 1) return cudaErrorNotSupported;
+    const uint32_t grid = std::min(blocks, (uint32_t)dev->sm_count * (uint32_t)occ);
+    TpPush push{};
+    if (dev->tp_push) { // one launch covers every target: it can do the exchange itself
+        push = *dev->tp_push;
+        dev->tp_push = nullptr;
+        dev->tp_pushed = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = dev->stream;
+    static const bool pdl = [] { const char *e = getenv("FQ_PDL"); return !(e && e[0] == '0'); }();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k_gemv_ring<FMT, MT>, T, a[0].row_bytes, (const float *)a[0].x, L, R, push, dev->status_dev);
 }
 
 template <int FMT, int MT>
@@ -603,6 +935,25 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
         xrows = m = f.m;
     }
     const PrepI8 L = prep_i8_layout(f.cols);
+    // Two variants of the same arithmetic.  Measured on B200, both are bound by instruction issue once their
+    // weight stream is up (the register variant has the shorter inner loop and is a few percent faster on the
+    // large matrices, the staged one starts faster and wins on the small ones), and alternating between them
+    // costs more than either gains, because their shared-memory configurations differ.  The register variant
+    // is the default; FQ_GEMV=staged selects the staged kernel for every launch it supports.
+    static const bool ring_only = [] { const char *e = getenv("FQ_GEMV"); return e && e[0] == 's'; }();
+    if (!expert && ring_only) {
+        cudaError_t e;
+        if (f.format == FQ_Q4_K)
+            e = m == 1 ? launch_ring<FQ_Q4_K, 1>(dev, a, count, L) : m == 2 ? launch_ring<FQ_Q4_K, 2>(dev, a, count, L)
+              : m == 3 ? launch_ring<FQ_Q4_K, 3>(dev, a, count, L) : launch_ring<FQ_Q4_K, 4>(dev, a, count, L);
+        else
+            e = m == 1 ? launch_ring<FQ_Q6_K, 1>(dev, a, count, L) : m == 2 ? launch_ring<FQ_Q6_K, 2>(dev, a, count, L)
+              : m == 3 ? launch_ring<FQ_Q6_K, 3>(dev, a, count, L) : launch_ring<FQ_Q6_K, 4>(dev, a, count, L);
+        if (e != cudaErrorNotSupported) {
+            if (int rc = fq_check_cuda(dev, e, "gemv launch")) return rc;
+            return fq_end_enqueue(dev, "gemv_ring", 1);
+        }
+    }
     // Successive projections use alternate halves of the scratch, so a preparation kernel that starts
     // early never writes what the previous projection may still be reading from a cache.
     if ((size_t)xrows * L.token_bytes > dev->xprep_bytes / 2) return FQ_ERR_UNSUPPORTED;

@@ -584,7 +584,8 @@ def test_captured_graph_replays_a_layer(device):
         d2.synchronize()
         want = oracle_dense_ffn(gate, up, down, xv, m, hidden, width)
         assert ref.rel_err(host(out).reshape(m, hidden), want) <= 2 * TOL_F32
-    assert d2.counters().dispatches - before == 2 * 5  # (prep + gemv) x 2 + glu, twice
+    # gate|up, the gated unit, down: (prep + gemv) x 2 + glu per replay, or three kernels with the staged GEMV
+    assert d2.counters().dispatches - before in (2 * 5, 2 * 3)
     graph.close()
     d2.close()
 
