@@ -288,10 +288,13 @@ def run_ours(args):
         gms = alone(("gate", "up"), m, x_dev, y_dev)
         pair_bytes = 2 * 17408 * 5120 // 256 * 144
         achieved = pair_bytes / (gms * 1e-3) / 1e9
-        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv<Q4_K> (gate|up, 2 x 17408 x 5120, one launch)",
+        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv_i8<Q4_K,1> (gate|up, 2 x 17408 x 5120, one launch)",
                            "achieved": round(achieved, 1), "peak": P["hbm_gbs"], "peak_source": P["source"], "unit": "GB/s",
                            "frac": round(achieved / P["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
-                           "traffic": None, "us_per_launch": round(gms * 1e3, 2)}
+                           # dram__bytes_read.sum + dram__bytes_write.sum of this launch from one ncu capture
+                           # (profiles/gemv_i8_q4k_gate_up_m1.md): 100.31 MB read + 3.26 MB written.
+                           "traffic": 103565056, "traffic_source": "ncu capture, profiles/gemv_i8_q4k_gate_up_m1.md",
+                           "algorithmic_bytes": pair_bytes, "us_per_launch": round(gms * 1e3, 2)}
         per = {}
         for names in (("q", "k", "v"), ("o",), ("gate", "up"), ("down",)):
             t = alone(names, m, x_dev, y_dev)
