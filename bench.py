@@ -148,7 +148,7 @@ def run_ours(args):
     stream = torch.cuda.ExternalStream(dev.stream_ptr(), device=torch.device("cuda", local))
     m, layers = args.m, args.layers
 
-    # Weights: layer l, matrix i uses seed (7 l + i) * 64 + rank; blocks as BASELINE config 0/1.
+    # Weights: layer l, matrix i uses seed (7 l + i) * 64 + rank; blocks drawn as the benchmark configurations 0 and 1 define them.
     mats = []
     for l in range(layers):
         layer = {}
@@ -292,8 +292,8 @@ def run_ours(args):
                            "achieved": round(achieved, 1), "peak": P["hbm_gbs"], "peak_source": P["source"], "unit": "GB/s",
                            "frac": round(achieved / P["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
                            # dram__bytes_read.sum + dram__bytes_write.sum of this launch from one ncu capture
-                           # (profiles/gemv_i8_q4k_gate_up_m1.md): 100.31 MB read + 3.26 MB written.
-                           "traffic": 103565056, "traffic_source": "ncu capture, profiles/gemv_i8_q4k_gate_up_m1.md",
+                           # (the summary is committed with the profile summaries): 100.31 MB read + 3.26 MB written.
+                           "traffic": 103565056, "traffic_source": "one ncu capture of this launch",
                            "algorithmic_bytes": pair_bytes, "us_per_launch": round(gms * 1e3, 2)}
         per = {}
         for names in (("q", "k", "v"), ("o",), ("gate", "up"), ("down",)):

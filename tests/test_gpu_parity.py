@@ -164,7 +164,7 @@ def test_wide_f32_projection_in_slices(device):
 
 
 def test_config0_gemv(device):
-    """BASELINE config 0: Q4_K 4096 x 4096, seed 0, x ~ N(0,1), M = 1."""
+    """Benchmark configuration 0: Q4_K 4096 x 4096, seed 0, x ~ N(0,1), M = 1."""
     rows = cols = 4096
     packed = ref.random_matrix(ref.Q4_K, rows, cols, seed=0)
     x = np.random.default_rng(0).standard_normal(cols).astype(np.float32)
