@@ -378,10 +378,33 @@ def run_ours(args):
         # CPU baseline: the oracle port on all host cores, one layer at M = 1 (a bounded sample).
         out["cpu_baseline"] = cpu_baseline(m=m, budget_s=12.0)
     else:
+        # End to end on every rank: upload this step's (replicated) activations from pinned memory, replay the
+        # step (projections + exchanges), download the gathered outputs, wait; wall clock, max over ranks.
+        e2e = None
+        if not args.nccl:
+            xh, yh = x_pinned.numpy(), y_pinned.numpy()
+
+            def step_host():
+                dev.upload(X, xh)
+                step()
+                dev.download_async(yh, Y)
+                dev.synchronize()
+            for _ in range(3):
+                step_host()
+            dist.barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                step_host()
+            dt = torch.tensor([(time.perf_counter() - t0) / args.steps], device="cuda")
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            dt = float(dt.item())
+            e2e = {"value": round(total_bytes / dt / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": int(xh.nbytes),
+                   "d2h_bytes_per_step": int(yh.nbytes), "ms_per_step": round(dt * 1e3, 4),
+                   "call": "per rank: fq_upload + fq_graph_launch (projections + exchanges) + fq_download_async + fq_synchronize"}
         # Expert parallelism over the same ranks (config 3 sharded by expert): every rank takes part.
         ep = moe_ep_bench(S, dev, stream, torch, dist, timed, rank, world)
         if rank == 0:
-            out["e2e"] = None
+            out["e2e"] = e2e
             out["moe_ffn_ep"] = ep
     if rank == 0:
         print(json.dumps(out), flush=True)
