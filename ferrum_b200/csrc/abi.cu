@@ -123,14 +123,17 @@ extern "C" int fq_device_create(int ordinal, fq_device **out) {
     dev->sm_count = prop.multiProcessorCount;
     if ((e = cudaStreamCreateWithFlags(&dev->own_stream, cudaStreamNonBlocking)) != cudaSuccess) return bail(e, "cudaStreamCreate");
     dev->stream = dev->own_stream;
+    if ((e = cudaStreamCreateWithFlags(&dev->side_stream, cudaStreamNonBlocking)) != cudaSuccess) return bail(e, "cudaStreamCreate");
+    if ((e = cudaEventCreateWithFlags(&dev->fork_event, cudaEventDisableTiming)) != cudaSuccess) return bail(e, "cudaEventCreate");
+    if ((e = cudaEventCreateWithFlags(&dev->join_event, cudaEventDisableTiming)) != cudaSuccess) return bail(e, "cudaEventCreate");
+    dev->side_xprep_bytes = (size_t)4 << 20;
+    if ((e = cudaMalloc(&dev->side_xprep, dev->side_xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
     dev->xprep_bytes = fq_gemv_scratch_bytes();
     if ((e = cudaMalloc(&dev->xprep, dev->xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
     if ((e = cudaMalloc(&dev->staging_dev, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "device staging");
     if ((e = cudaMallocHost(&dev->staging_host, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "pinned staging");
     dev->gemm_ws_bytes = (size_t)96 << 20;
     if ((e = cudaMalloc((void **)&dev->gemm_ws, dev->gemm_ws_bytes)) != cudaSuccess) return bail(e, "gemm workspace");
-    if ((e = cudaMalloc((void **)&dev->gemm_counters, dev->gemm_tiles_max * sizeof(uint32_t))) != cudaSuccess) return bail(e, "gemm counters");
-    if ((e = cudaMemset(dev->gemm_counters, 0, dev->gemm_tiles_max * sizeof(uint32_t))) != cudaSuccess) return bail(e, "gemm counters");
     void *status = nullptr;
     if ((e = cudaHostAlloc(&status, 64, cudaHostAllocMapped)) != cudaSuccess) return bail(e, "status word");
     dev->status_host = (volatile int *)status;
@@ -146,9 +149,15 @@ extern "C" int fq_device_destroy(fq_device *dev) {
     if (dev->own_stream) cudaStreamSynchronize(dev->own_stream);
     for (auto &kv : dev->allocations) cudaFree((void *)kv.first);
     if (dev->xprep) cudaFree(dev->xprep);
+    if (dev->side_xprep) cudaFree(dev->side_xprep);
+    if (dev->side_stream) {
+        cudaStreamSynchronize(dev->side_stream);
+        cudaStreamDestroy(dev->side_stream);
+    }
+    if (dev->fork_event) cudaEventDestroy(dev->fork_event);
+    if (dev->join_event) cudaEventDestroy(dev->join_event);
     if (dev->staging_dev) cudaFree(dev->staging_dev);
     if (dev->gemm_ws) cudaFree(dev->gemm_ws);
-    if (dev->gemm_counters) cudaFree(dev->gemm_counters);
     if (dev->staging_host) cudaFreeHost(dev->staging_host);
     if (dev->status_host) cudaFreeHost((void *)dev->status_host);
     if (dev->own_stream) cudaStreamDestroy(dev->own_stream);
@@ -656,6 +665,96 @@ extern "C" int fq_get_rows(fq_device *dev, const fq_matrix *w, const uint32_t *i
 
 // ------------------------------------------------------------------ feed-forward blocks
 
+// A branch of independent work on the side stream: everything enqueued between side_begin and side_end runs
+// after what `stream` held at side_begin and concurrently with what `stream` gets until side_end, after which
+// `stream` waits for the branch.  Works the same while `stream` is being captured (fork / join by events).
+struct SideBranch {
+    fq_device *dev;
+    cudaStream_t main;
+    void *xprep;
+    size_t xprep_bytes;
+    bool on;
+};
+static SideBranch side_begin(fq_device *dev) {
+    SideBranch b{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
+    if (!dev->side_stream) return b;
+    if (cudaEventRecord(dev->fork_event, dev->stream) != cudaSuccess || cudaStreamWaitEvent(dev->side_stream, dev->fork_event, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return b;
+    }
+    dev->stream = dev->side_stream;
+    dev->xprep = dev->side_xprep;
+    dev->xprep_bytes = dev->side_xprep_bytes;
+    b.on = true;
+    return b;
+}
+// End of the branch's enqueues: later calls go to `stream` again (and run beside the branch).
+static int side_detach(SideBranch &b) {
+    if (!b.on) return FQ_OK;
+    fq_device *dev = b.dev;
+    const cudaError_t e = cudaEventRecord(dev->join_event, dev->side_stream);
+    dev->stream = b.main;
+    dev->xprep = b.xprep;
+    dev->xprep_bytes = b.xprep_bytes;
+    return fq_check_cuda(dev, e, "side stream event");
+}
+// `stream` waits for the branch.
+static int side_join(SideBranch &b) {
+    if (!b.on) return FQ_OK;
+    b.on = false;
+    return fq_check_cuda(b.dev, cudaStreamWaitEvent(b.dev->stream, b.dev->join_event, 0), "joining the side stream");
+}
+
+// y = W . (silu(g) * u): at decode widths the gated unit is computed inside the projection's activation
+// preparation (no separate launch, no round trip of `act`); otherwise `fq_glu` into `act`, then the projection.
+// With `ids` (routes, one activation row each) W is an expert stack.
+static int project_gated(fq_device *dev, const fq_matrix *w, const float *g, const float *u, float *act, size_t rows_x, const uint32_t *ids,
+                         float *y) {
+    const size_t width = w->cols, rows_e = w->expert_rows();
+    if (!dev->exact) {
+        if (int rc = fq_begin_enqueue(dev)) return rc;
+        if (int rc = fq_check_binding(dev, g, rows_x * width * 4, "gate")) return rc;
+        if (int rc = fq_check_binding(dev, u, rows_x * width * 4, "up")) return rc;
+        if (int rc = fq_check_binding(dev, y, rows_x * rows_e * 4, "y")) return rc;
+        ProjectArgs a = base_args(w, g, FQ_F32, y, FQ_F32);
+        a.x_up = u;
+        a.m = (uint32_t)rows_x;
+        if (ids) {
+            a.ids = ids;
+            a.x_div = 1;
+        } else {
+            a.rows = (uint32_t)w->rows;
+        }
+        const int rc = fq_launch_gemv_i8_many(dev, &a, 1);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (int rc = fq_glu(dev, g, u, rows_x * width, act)) return rc;
+    if (ids) return fq_project_id(dev, w, act, rows_x * width, ids, rows_x, 1, y, rows_x * rows_e);
+    return fq_project(dev, w, act, FQ_F32, rows_x * width, rows_x, y, FQ_F32, rows_x * rows_e);
+}
+
+// Two expert stacks of one shape (gate and up) on the same routes: one launch at decode widths.
+static int project_id_pair(fq_device *dev, const fq_matrix *w0, const fq_matrix *w1, const float *x, size_t x_elems, const uint32_t *ids,
+                           size_t routes, size_t x_div, float *y0, float *y1) {
+    if (!dev->exact && w0->format == w1->format && w0->cols == w1->cols && w0->expert_rows() == w1->expert_rows() && w0->experts == w1->experts) {
+        if (int rc = fq_begin_enqueue(dev)) return rc;
+        ProjectArgs a[2] = {base_args(w0, x, FQ_F32, y0, FQ_F32), base_args(w1, x, FQ_F32, y1, FQ_F32)};
+        for (ProjectArgs &p : a) {
+            p.m = (uint32_t)routes;
+            p.ids = ids;
+            p.x_div = (uint32_t)x_div;
+        }
+        if (int rc = fq_check_binding(dev, x, x_elems * 4, "x")) return rc;
+        if (int rc = fq_check_binding(dev, ids, routes * 4, "ids")) return rc;
+        if (int rc = fq_check_binding(dev, y0, routes * w0->expert_rows() * 4, "y")) return rc;
+        if (int rc = fq_check_binding(dev, y1, routes * w1->expert_rows() * 4, "y")) return rc;
+        const int rc = fq_launch_gemv_i8_many(dev, a, 2);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (int rc = fq_project_id(dev, w0, x, x_elems, ids, routes, x_div, y0, routes * w0->expert_rows())) return rc;
+    return fq_project_id(dev, w1, x, x_elems, ids, routes, x_div, y1, routes * w1->expert_rows());
+}
+
 extern "C" int fq_dense_ffn(fq_device *dev, const fq_matrix *gate, const fq_matrix *up, const fq_matrix *down,
                             const float *x, size_t m, float *scratch, size_t scratch_elems, float *out) {
     if (!dev || !gate || !up || !down) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
@@ -667,8 +766,7 @@ extern "C" int fq_dense_ffn(fq_device *dev, const fq_matrix *gate, const fq_matr
     const fq_matrix *pair[2] = {gate, up};
     void *outs[2] = {g, u};
     if (int rc = fq_project_many(dev, pair, 2, x, FQ_F32, m * gate->cols, m, outs, FQ_F32)) return rc;
-    if (int rc = fq_glu(dev, g, u, m * width, act)) return rc;
-    return fq_project(dev, down, act, FQ_F32, m * width, m, out, FQ_F32, m * down->rows);
+    return project_gated(dev, down, g, u, act, m, nullptr, out);
 }
 
 // Expert routes at or below which experts use per-route GEMVs (`MV_ID_MAX_ROUTES`,
@@ -724,29 +822,33 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
     MoeScratch s = moe_layout(f, m, scratch);
     if (scratch_elems < s.total) return fq_fail(dev, FQ_ERR_SHAPE, "MoE scratch holds %zu of %zu floats", scratch_elems, s.total);
     const size_t routes = m * used;
-    if (int rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts)) return rc;
-    const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
-    if (int rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m,
-                              f->sigmoid, f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate))
-        return rc;
-    if (int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared))
-        return rc;
     const bool identity = routes <= MV_ID_MAX_ROUTES || dev->exact;
-    if (identity) {
-        if (int rc = fq_project_id(dev, f->gate_exps, x, m * hidden, s.ids, routes, used, s.g, routes * ef)) return rc;
-        if (int rc = fq_project_id(dev, f->up_exps, x, m * hidden, s.ids, routes, used, s.u, routes * ef)) return rc;
-        if (int rc = fq_glu(dev, s.g, s.u, routes * ef, s.act)) return rc;
-        if (int rc = fq_project_id(dev, f->down_exps, s.act, routes * ef, s.ids, routes, 1, s.down, routes * hidden)) return rc;
-    } else {
-        if (int rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position)) return rc;
+    // The shared expert depends on x only: at decode widths (small kernels, latency-bound) it runs on the side
+    // stream beside the router and the routed experts; at wide inputs its GEMMs share the handle's workspace
+    // with the rest, so it stays in line.
+    SideBranch side = (identity && !dev->exact) ? side_begin(dev) : SideBranch{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
+    int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared);
+    if (int rc2 = side_detach(side)) rc = rc ? rc : rc2;
+    const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
+    if (!rc) rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts);
+    if (!rc)
+        rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m, f->sigmoid,
+                          f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate);
+    if (!rc && identity) {
+        rc = project_id_pair(dev, f->gate_exps, f->up_exps, x, m * hidden, s.ids, routes, used, s.g, s.u);
+        if (!rc) rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, s.ids, s.down);
+    } else if (!rc) {
         // Expert-sorted rows through the tensor-core GEMM: activations rounded to bf16 once (at the gather and
         // at the gated unit), fp32 accumulation and fp32 results.
-        if (int rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, nullptr, 0, s.xg)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.g, FQ_F32, routes * ef)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.u, FQ_F32, routes * ef)) return rc;
-        if (int rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, nullptr, 0, (uint32_t)ef, s.act)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_BF16, routes * ef, s.offsets, nullptr, experts, m, s.down, FQ_F32, routes * hidden)) return rc;
+        rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position);
+        if (!rc) rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, nullptr, 0, s.xg);
+        if (!rc) rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.g, FQ_F32, routes * ef);
+        if (!rc) rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.u, FQ_F32, routes * ef);
+        if (!rc) rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, nullptr, 0, (uint32_t)ef, s.act);
+        if (!rc) rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_BF16, routes * ef, s.offsets, nullptr, experts, m, s.down, FQ_F32, routes * hidden);
     }
+    if (int rc2 = side_join(side)) rc = rc ? rc : rc2; // also after an error: a capture must not end with the branch open
+    if (rc) return rc;
     return fq_moe_combine(dev, s.down, s.weights, identity ? s.ids : s.position, s.shared, s.gate, (uint32_t)hidden,
                           (uint32_t)used, (uint32_t)m, identity, out);
 }
@@ -788,10 +890,8 @@ extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset
         uint32_t *local_ids = (uint32_t *)s.logits; // the logits are consumed by now, and routes <= m * experts
         if (int rc = fq_moe_gather(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg)) return rc;
         if (int rc = fq_launch_moe_local_ids(dev, s.ids, s.sorted, (uint32_t)routes, expert_first, (uint32_t)local, local_ids)) return rc;
-        if (int rc = fq_project_id(dev, f->gate_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, routes * ef)) return rc;
-        if (int rc = fq_project_id(dev, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.u, routes * ef)) return rc;
-        if (int rc = fq_glu(dev, s.g, s.u, routes * ef, s.act)) return rc;
-        if (int rc = fq_project_id(dev, f->down_exps, s.act, routes * ef, local_ids, routes, 1, down, routes * hidden)) return rc;
+        if (int rc = project_id_pair(dev, f->gate_exps, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, s.u)) return rc;
+        if (int rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, local_ids, down)) return rc;
     } else {
         if (int rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, mine, (uint32_t)local, s.xg)) return rc;
         if (int rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.g, FQ_F32, routes * ef)) return rc;

@@ -71,10 +71,19 @@ PrepI8 prep_i8_layout(uint32_t cols) {
 
 // Superblock b of one activation row, by one warp (lane l owns the eight values at 256 b + 8 l), written in
 // the layout above at `base` (global or shared memory).
-__device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base) {
+// With `urow` the activations are the gated unit silu(x) * u, x / (1 + exp(-x)) * u as `k_swiglu` computes it.
+__device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base,
+                                                const float *__restrict__ urow = nullptr) {
     const float4 *src = reinterpret_cast<const float4 *>(xrow + (size_t)b * 256 + lane * 8);
     const float4 v0 = src[0], v1 = src[1];
-    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    if (urow) {
+        const float4 *us = reinterpret_cast<const float4 *>(urow + (size_t)b * 256 + lane * 8);
+        const float4 u0 = us[0], u1 = us[1];
+        const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v[i] / (1.f + expf(-v[i])) * u[i];
+    }
     float amax = 0.f;
     bool bad = false;
 #pragma unroll
@@ -136,13 +145,13 @@ __device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, 
 
 // One warp per (activation row, superblock).
 __global__ void __launch_bounds__(128)
-k_prep_i8(const float *__restrict__ x, uint32_t xrows, PrepI8 L, uint8_t *__restrict__ out) {
+k_prep_i8(const float *__restrict__ x, const float *__restrict__ x_up, uint32_t xrows, PrepI8 L, uint8_t *__restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const uint32_t xr = warp / L.nblk, b = warp % L.nblk;
     if (xr >= xrows) return;
-    prep_superblock(x + (size_t)xr * L.cols, b, lane, L, out + (size_t)xr * L.token_bytes);
+    prep_superblock(x + (size_t)xr * L.cols, b, lane, L, out + (size_t)xr * L.token_bytes, x_up ? x_up + (size_t)xr * L.cols : nullptr);
 }
 
 // ---------------------------------------------------------------- helpers
@@ -631,8 +640,8 @@ __device__ __forceinline__ void bulk_copy(void *dst, const void *src, uint32_t b
 
 template <int FMT, int MT>
 __global__ void __launch_bounds__(MT >= 3 ? 288 : MT == 2 ? 416 : 544)
-k_gemv_ring(const __grid_constant__ GemvTargets T, uint32_t pitch, const float *__restrict__ x, PrepI8 L, RingCfg R,
-            const __grid_constant__ TpPush P, int *status) {
+k_gemv_ring(const __grid_constant__ GemvTargets T, uint32_t pitch, const float *__restrict__ x, const float *__restrict__ x_up, PrepI8 L,
+            RingCfg R, const __grid_constant__ TpPush P, int *status) {
     using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
     extern __shared__ __align__(128) uint8_t ring_smem[];
     __shared__ uint64_t full[RING_STAGES_MAX], empty[RING_STAGES_MAX];
@@ -703,7 +712,9 @@ k_gemv_ring(const __grid_constant__ GemvTargets T, uint32_t pitch, const float *
         // ---- consumers
         pdl_wait(); // the activations are the output of the kernel before
         // Every block prepares the activations for itself, straight into shared memory (k_prep_i8's arithmetic).
-        for (uint32_t i = warp; i < MT * nblk; i += k) prep_superblock(x + (size_t)(i / nblk) * L.cols, i % nblk, lane, L, act + (size_t)(i / nblk) * L.token_bytes);
+        for (uint32_t i = warp; i < MT * nblk; i += k)
+            prep_superblock(x + (size_t)(i / nblk) * L.cols, i % nblk, lane, L, act + (size_t)(i / nblk) * L.token_bytes,
+                            x_up ? x_up + (size_t)(i / nblk) * L.cols : nullptr);
         asm volatile("bar.sync 1, %0;" ::"r"(k * 32) : "memory");
         float yacc[MT][2];
 #pragma unroll
@@ -864,7 +875,7 @@ cudaError_t launch_ring(fq_device *dev, const ProjectArgs *a, uint32_t count, co
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, k_gemv_ring<FMT, MT>, T, a[0].row_bytes, (const float *)a[0].x, L, R, push, dev->status_dev);
+    return cudaLaunchKernelEx(&cfg, k_gemv_ring<FMT, MT>, T, a[0].row_bytes, (const float *)a[0].x, a[0].x_up, L, R, push, dev->status_dev);
 }
 
 template <int FMT, int MT>
@@ -921,9 +932,10 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     if ((f.format != FQ_Q4_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
     if (f.cols % 256 || f.row_bytes % 16) return FQ_ERR_UNSUPPORTED;
     for (uint32_t i = 1; i < count; i++)
-        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].m != f.m || a[i].ids || f.ids ||
-            a[i].x_dtype != FQ_F32 || a[i].y_dtype != FQ_F32)
-            return FQ_ERR_UNSUPPORTED;
+        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].m != f.m || a[i].ids != f.ids ||
+            a[i].x_div != f.x_div || a[i].experts != f.experts || (f.ids && a[i].rows != f.rows) || a[i].x_dtype != FQ_F32 ||
+            a[i].y_dtype != FQ_F32)
+            return FQ_ERR_UNSUPPORTED; // with routes the targets are expert stacks of one shape (gate and up)
     const bool expert = f.ids != nullptr;
     uint32_t xrows, m;
     if (expert) {
@@ -963,7 +975,7 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     // FQ_SKIP_PREP=1 (measurement only, results are then garbage) leaves the preparation kernel out.
     static const bool skip_prep = [] { const char *e = getenv("FQ_SKIP_PREP"); return e && e[0] == '1'; }();
     if (!skip_prep)
-    if (int rc = fq_check_cuda(dev, launch_pdl(k_prep_i8, dim3((warps + 3) / 4), dim3(128), dev->stream, (const float *)f.x, xrows, L, prep),
+    if (int rc = fq_check_cuda(dev, launch_pdl(k_prep_i8, dim3((warps + 3) / 4), dim3(128), dev->stream, (const float *)f.x, f.x_up, xrows, L, prep),
                                "activation preparation launch"))
         return rc;
     cudaError_t e;
@@ -1072,7 +1084,7 @@ extern "C" int fq_gemv_q4k_static(const void *w_packed, uint64_t rows, uint64_t 
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const uint32_t warps = m * L.nblk;
     // Every byte the GEMV reads from the scratch is rewritten here first, so nothing has to start at zero.
-    k_prep_i8<<<(warps + 3) / 4, 128, 0, stream>>>(x, m, L, prep);
+    k_prep_i8<<<(warps + 3) / 4, 128, 0, stream>>>(x, nullptr, m, L, prep);
     if ((e = cudaPeekAtLastError()) != cudaSuccess)
         return static_fail(err, err_len, FQ_ERR_CUDA, "activation preparation launch: %s", cudaGetErrorString(e));
     const uint32_t pitch = (uint32_t)(cols / 256 * 144);

@@ -21,6 +21,12 @@ struct fq_device {
     int sm_count = 0;
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;
+    // A second stream with its own small activation scratch, for a branch of work that is independent of what
+    // runs on `stream` (the shared expert beside the routed experts at decode widths); joined back by events.
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t fork_event = nullptr, join_event = nullptr;
+    void *side_xprep = nullptr;
+    size_t side_xprep_bytes = 0;
     std::string error;
     bool failed = false;          // an asynchronous failure was reported; enqueues are refused
     bool exact = false;
@@ -41,8 +47,6 @@ struct fq_device {
     // Split-K workspace of the prefill GEMM: partial fp32 tiles and one arrival counter per tile.
     float *gemm_ws = nullptr;
     size_t gemm_ws_bytes = 0;
-    uint32_t *gemm_counters = nullptr;
-    uint32_t gemm_tiles_max = 4096;
     // One word in mapped pinned host memory that kernels set when a bounded wait gives up.
     volatile int *status_host = nullptr;
     int *status_dev = nullptr;
@@ -83,6 +87,7 @@ struct ProjectArgs {
     const uint8_t *w;
     uint32_t format, rows, cols, row_bytes; // rows = rows of one expert slice; row_bytes = device row pitch
     const void *x;
+    const float *x_up = nullptr; // decode kernels only: the activations are silu(x) * x_up (the gated unit, fused into their preparation)
     void *y;
     int x_dtype, y_dtype;
     uint32_t m;        // activation rows (project) / routes (project_id) / 0 (grouped)
