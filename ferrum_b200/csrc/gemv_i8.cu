@@ -509,7 +509,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     // With one activation row its fragments are fetched one superblock ahead, like the weights; with
     // more rows the registers do not allow that and they are fetched at the top of the iteration.
     constexpr bool AHEAD = MT == 1;
-    Act<FMT> acur[MT], anxt[AHEAD ? MT : 1];
+    Act<FMT> acur[MT], anxt[MT]; // anxt is used with AHEAD only
     if (AHEAD && iters > 0) {
 #pragma unroll
         for (int m = 0; m < MT; m++) acur[m].load(prep + (size_t)m * L.token_bytes, L, block_of(0), t, g);
@@ -523,25 +523,37 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     const uint32_t next_tile = tile + gridDim.x;
     const bool more = next_tile < total_tiles;
     const Tile next = more ? tile_at(next_tile) : here;
-    for (uint32_t it = 0; it < iters; it++) {
-        // Everything the next iteration needs is requested now; this one runs from registers.  After a
-        // tile's last superblock that is the first superblock of the block's next tile.
+    // One superblock: everything the next one needs is requested first (after a tile's last superblock that is
+    // the first superblock of the block's next tile), then this one runs from registers.
+    auto step = [&](const Raw (&c)[2], Raw (&n)[2], Act<FMT> (&ac)[MT], Act<FMT> (&an)[MT], uint32_t it) {
         const bool wrap = it + 1 == iters && more;
         const uint32_t nb_next = wrap ? block_of(0) : block_of(it + 1);
-        nxt[0].load(wrap ? next.rowp[0] : here.rowp[0], nblk, nb_next, t);
-        nxt[1].load(wrap ? next.rowp[1] : here.rowp[1], nblk, nb_next, t);
+        n[0].load(wrap ? next.rowp[0] : here.rowp[0], nblk, nb_next, t);
+        n[1].load(wrap ? next.rowp[1] : here.rowp[1], nblk, nb_next, t);
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            if (AHEAD) anxt[m].load(prep + (size_t)m * L.token_bytes, L, nb_next, t, g);
-            else acur[m].load(prep + (size_t)m * L.token_bytes, L, block_of(it), t, g);
+            if (AHEAD) an[m].load(prep + (size_t)m * L.token_bytes, L, nb_next, t, g);
+            else ac[m].load(prep + (size_t)m * L.token_bytes, L, block_of(it), t, g);
         }
-
-        superblock_dot<FMT, MT>(cur, acur, t, g, yacc);
-        cur[0] = nxt[0];
-        cur[1] = nxt[1];
-        if (AHEAD) {
+        superblock_dot<FMT, MT>(c, ac, t, g, yacc);
+    };
+    if (FMT == FQ_Q4_K && (iters & 1u) == 0) {
+        // An even count: the two register sets swap roles instead of being copied (Q4_K only: with Q6_K's larger
+        // register sets the second copy of the loop body spills).
+        for (uint32_t it = 0; it < iters; it += 2) {
+            step(cur, nxt, acur, anxt, it);
+            if (AHEAD) step(nxt, cur, anxt, acur, it + 1);
+            else step(nxt, cur, acur, anxt, it + 1);
+        }
+    } else {
+        for (uint32_t it = 0; it < iters; it++) {
+            step(cur, nxt, acur, anxt, it);
+            cur[0] = nxt[0];
+            cur[1] = nxt[1];
+            if (AHEAD) {
 #pragma unroll
-            for (int m = 0; m < MT; m++) acur[m] = anxt[m];
+                for (int m = 0; m < MT; m++) acur[m] = anxt[m];
+            }
         }
     }
     // Quad threads hold partial sums of different scale groups and planes: add them, then the warps.
@@ -901,7 +913,8 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
     uint32_t warps = need;
     uint64_t best = ~0ull;
     for (uint32_t k = need; k <= max_k; k++) {
-        const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need); // prefer small k on ties
+        // prefer small k on ties, and an even count per warp (its register sets then swap instead of being copied)
+        const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need) + ((per & 1) && nblk % k == 0 ? 2 : 0);
         if (waste < best) { best = waste; warps = k; }
     }
     // Persistent blocks: as many as stay resident at once (fewer with routes in grid.y), each walking its tiles.
