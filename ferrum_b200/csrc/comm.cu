@@ -11,6 +11,7 @@
 // order makes it visible to whatever runs next.  Nothing here uses multicast or TMA; the kernel can be
 // captured into a graph because sequence numbers live in device memory.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "internal.h"
@@ -100,8 +101,9 @@ extern "C" int fq_comm_create(fq_device *dev, int rank, int world, size_t bytes,
     c->rank = rank;
     c->world = world;
     c->bytes = bytes;
-    cudaError_t e = cudaMalloc((void **)&c->local, bytes + flag_bytes());
-    if (e == cudaSuccess) e = cudaMemset(c->local, 0, bytes + flag_bytes());
+    // payload | flag words | mirror of {value, sequence number} slots for the fused exchange (8 bytes per float)
+    cudaError_t e = cudaMalloc((void **)&c->local, bytes + flag_bytes() + 2 * bytes);
+    if (e == cudaSuccess) e = cudaMemset(c->local, 0, bytes + flag_bytes() + 2 * bytes);
     if (e == cudaSuccess) e = cudaMalloc((void **)&c->seq, flag_bytes() * 3);
     if (e == cudaSuccess) e = cudaMemset(c->seq, 0, flag_bytes() * 3);
     if (e != cudaSuccess) {
@@ -147,11 +149,13 @@ int fq_comm_begin_push(fq_comm *c, const void *y, size_t bytes, TpPush *out) {
     for (int r = 0; r < FQ_COMM_MAX_WORLD; r++) out->peer[r] = r < c->world ? c->peer[r] : nullptr;
     out->world = (uint32_t)c->world;
     out->rank = (uint32_t)c->rank;
+    static const uint32_t mode = [] { const char *e = getenv("FQ_TP_MODE"); return e ? (uint32_t)atoi(e) : 3u; }();
+    out->mode = mode;
     out->slot = c->next_slot;
     c->next_slot = (c->next_slot + 1) % FQ_COMM_SLOTS;
-    out->seq = c->seq;
+    out->epoch = c->seq + (size_t)FQ_COMM_SLOTS * FQ_COMM_MAX_WORLD; // a word of the local bookkeeping array nothing else uses
     out->counter = c->seq + (size_t)FQ_COMM_SLOTS * FQ_COMM_MAX_WORLD * 2 + (size_t)out->slot * FQ_COMM_MAX_WORLD; // the slot's chunk counters
-    out->flag_off = c->bytes;
+    out->mirror_off = c->bytes + flag_bytes();
     out->slice_off = (size_t)(p - c->local);
     out->slice_bytes = bytes;
     out->status = c->dev->status_dev;

@@ -393,48 +393,42 @@ __device__ __forceinline__ void superblock_dot(const RawT (&cur)[2], const Act<F
     }
 }
 
-// End of a launch whose outputs are one rank's slice of a gathered region: the last block to get here copies
-// the slice to every peer, raises this rank's sequence flag there and waits (bounded) until every peer's flag
-// for the same exchange has arrived.
-__device__ __forceinline__ void tp_finish(const TpPush &P) {
-    __shared__ bool last;
-    __threadfence(); // this block's outputs, before the block is counted in
-    __syncthreads();
-    if (threadIdx.x == 0) last = atomicAdd(P.counter, 1u) + 1u == gridDim.x * gridDim.y * gridDim.z;
-    __syncthreads();
-    if (!last) return;
-    __threadfence();
-    const uint4 *src = reinterpret_cast<const uint4 *>(P.peer[P.rank] + P.slice_off);
-    const size_t n16 = P.slice_bytes / 16;
-    for (uint32_t p = 0; p < P.world; p++) {
-        if (p == P.rank) continue;
-        uint4 *dst = reinterpret_cast<uint4 *>(P.peer[p] + P.slice_off);
-        for (size_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i); // from L2: other blocks wrote it
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x != 0) return;
-    *P.counter = 0;
-    uint32_t expect[8];
-    for (uint32_t p = 0; p < P.world; p++) {
-        if (p == P.rank) continue;
-        uint32_t *my_seq = P.seq + (size_t)P.slot * 8 + p;
-        expect[p] = *my_seq + 1u;
-        *my_seq = expect[p];
-        uint32_t *remote = reinterpret_cast<uint32_t *>(P.peer[p] + P.flag_off) + (size_t)P.slot * 8 + P.rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(expect[p]) : "memory");
-    }
-    for (uint32_t p = 0; p < P.world; p++) {
-        if (p == P.rank) continue;
-        const uint32_t *local = reinterpret_cast<const uint32_t *>(P.peer[P.rank] + P.flag_off) + (size_t)P.slot * 8 + p;
-        bool arrived = false;
-        for (uint32_t i = 0; i < (1u << 24) && !arrived; i++) {
-            uint32_t v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
-            arrived = (int32_t)(v - expect[p]) >= 0;
-            if (!arrived) __nanosleep(20);
+// Row-sharded launches (TpPush, internal.h).  tp_seq: the sequence number of this exchange, read by every block
+// once the kernel before has finished.  tp_store: one output value to the mirror of every peer, tagged.
+// tp_finish: this block's share of the incoming slots, then the bookkeeping by the last block.
+__device__ __forceinline__ uint32_t tp_seq(const TpPush &P) { return *(volatile uint32_t *)P.epoch + 1u; }
+__device__ __forceinline__ void tp_store(const TpPush &P, uint32_t seq, const float *dst, float v) {
+    const size_t off = (size_t)((const uint8_t *)dst - P.peer[P.rank]);
+    for (uint32_t p = 0; p < P.world; p++)
+        if (p != P.rank)
+            asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(P.peer[p] + P.mirror_off + 2 * off), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+__device__ __forceinline__ void tp_finish(const TpPush &P, uint32_t seq) {
+    const uint32_t blocks = gridDim.x * gridDim.y * gridDim.z, block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (P.mode & 2u) {
+        const size_t per_rank = P.slice_bytes / 4, incoming = per_rank * (P.world - 1);
+        const size_t lo = incoming * block / blocks, hi = incoming * (block + 1) / blocks;
+        for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            uint32_t p = (uint32_t)(i / per_rank);
+            const size_t j = i % per_rank;
+            if (p >= P.rank) p++; // the senders, skipping this rank
+            const size_t off = P.slice_off + ((size_t)p - P.rank) * P.slice_bytes + 4 * j; // wraps correctly for p < rank
+            const uint8_t *slot = P.peer[P.rank] + P.mirror_off + 2 * off;
+            uint32_t v = 0, tag = 0;
+            bool arrived = false;
+            for (uint32_t n = 0; n < (1u << 22) && !arrived; n++) {
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(tag) : "l"(slot) : "memory");
+                arrived = tag == seq;
+                if (!arrived && n > 16) __nanosleep(64);
+            }
+            if (arrived) *reinterpret_cast<uint32_t *>(P.peer[P.rank] + off) = v;
+            else *(volatile int *)P.status = (int)FQ_ERR_TIMEOUT; // the peer never sent: report, do not hang
         }
-        if (!arrived) *(volatile int *)P.status = (int)FQ_ERR_TIMEOUT; // the peer never arrived: report, do not hang
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(P.counter, 1u) + 1u == blocks) {
+        *P.counter = 0;
+        *(volatile uint32_t *)P.epoch = seq; // every block has read it by now
     }
 }
 
@@ -505,6 +499,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     // The loads above touch immutable weights only; the rest reads prepared activations and writes y.
     pdl_trigger();
     pdl_wait();
+    const uint32_t seq = P.world > 1 ? tp_seq(P) : 0u;
 
     // With one activation row its fragments are fetched one superblock ahead, like the weights; with
     // more rows the registers do not allow that and they are fetched at the top of the iteration.
@@ -581,7 +576,11 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
 #pragma unroll
                 for (int ww = 0; ww < WARPS - 1; ww++) v += red[buf][ww][m * 2 + r][g];
                 const uint32_t row = here.tile0 * 16 + g + r * 8;
-                if (row < here.rows) here.y[y_base + (size_t)m * here.rows + row] = v;
+                if (row < here.rows) {
+                    float *dst = &here.y[y_base + (size_t)m * here.rows + row];
+                    *dst = v;
+                    if (P.world > 1 && (P.mode & 1u)) tp_store(P, seq, dst, v);
+                }
             }
     }
     if (!more) break;
@@ -590,7 +589,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
 #pragma unroll
     for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
     }
-    if (P.world > 1) tp_finish(P);
+    if (P.world > 1) tp_finish(P, seq);
 }
 
 // ---------------------------------------------------------------- staged variant
@@ -676,6 +675,7 @@ k_gemv_ring(const __grid_constant__ GemvTargets T, uint32_t pitch, const float *
     }
     __syncthreads();
     volatile uint32_t *aborted = &abort_flag;
+    uint32_t seq = 0; // of the fused exchange, if any
 
     auto tile_rows = [&](uint32_t tile, uint32_t &rows, uint32_t &tile0, float *&y) -> const uint8_t * {
         uint32_t which = 0, first_block = 0;
@@ -723,6 +723,7 @@ k_gemv_ring(const __grid_constant__ GemvTargets T, uint32_t pitch, const float *
     } else {
         // ---- consumers
         pdl_wait(); // the activations are the output of the kernel before
+        if (P.world > 1) seq = tp_seq(P);
         // Every block prepares the activations for itself, straight into shared memory (k_prep_i8's arithmetic).
         for (uint32_t i = warp; i < MT * nblk; i += k)
             prep_superblock(x + (size_t)(i / nblk) * L.cols, i % nblk, lane, L, act + (size_t)(i / nblk) * L.token_bytes,
@@ -787,14 +788,21 @@ k_gemv_ring(const __grid_constant__ GemvTargets T, uint32_t pitch, const float *
                         float v = yacc[m][r];
                         for (uint32_t ww = 0; ww + 1 < k; ww++) v += red[buf][ww][m * 2 + r][g];
                         const uint32_t row = tile0 * 16 + g + r * 8;
-                        if (row < rows) y[(size_t)m * rows + row] = v;
+                        if (row < rows) {
+                            float *dst = &y[(size_t)m * rows + row];
+                            *dst = v;
+                            if (P.world > 1 && (P.mode & 1u)) tp_store(P, seq, dst, v);
+                        }
                     }
             }
 #pragma unroll
             for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
         }
     }
-    if (P.world > 1) tp_finish(P);
+    if (P.world > 1) {
+        if (warp == k) seq = tp_seq(P); // the producer warp: by now the kernel before has long finished
+        tp_finish(P, seq);
+    }
 }
 
 template <typename... KArgs, typename... Args>

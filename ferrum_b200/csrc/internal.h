@@ -129,18 +129,23 @@ int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_
 // of the `count` experts from `first`.
 int fq_launch_moe_local_ids(fq_device *dev, const uint32_t *ids, const uint32_t *sorted, uint32_t routes, uint32_t first, uint32_t count,
                             uint32_t *out);
-// Fused exchange of a row-sharded projection (comm.cu, gemv_i8.cu): the kernel that computes this rank's
-// output rows writes them into its slice of the symmetric buffer; the last of its blocks to finish copies the
-// slice to the same offset of every peer's buffer (peer stores over NVLink), raises this rank's sequence flag
-// on every peer and waits -- bounded -- for theirs, so when the kernel has ended every rank's rows are in
-// local memory.  world <= 1 turns it off.
+// Fused exchange of a row-sharded projection (comm.cu, gemv_i8.cu), without fences or a separate copy: next to
+// its payload every symmetric buffer has a mirror of 8-byte slots {value, sequence number}, one per payload
+// float.  The kernel that computes this rank's output rows stores each value into its own payload slice and,
+// paired with the exchange's sequence number in ONE 8-byte peer store over NVLink, into the mirror of every
+// peer (a value and its tag arrive together, so no ordering between stores is needed).  Before it ends, every
+// block takes a share of the slots the peers send to this rank, polls each -- bounded -- until its tag is the
+// current sequence number, and moves the value into the payload; when the kernel has ended every rank's rows
+// are in local memory.  The sequence number counts the communicator's fused exchanges in device memory (the
+// last block to finish advances it; all ranks make the same calls, so it is the same everywhere and never
+// repeats for a slot), so a captured graph can replay the exchange.  world <= 1 turns it off.
 struct TpPush {
     uint8_t *peer[8];    // symmetric buffers by rank (peer[rank] is the local one)
-    uint32_t world, rank, slot;
-    uint32_t *seq;       // local: last sequence number used per (slot, peer)
+    uint32_t world, rank, slot, mode; // mode: 1 send | 2 receive (3 = both; anything else is for measurements)
+    uint32_t *epoch;     // local: number of fused exchanges this communicator has completed (the same on every rank)
     uint32_t *counter;   // local: blocks of this launch that have finished
-    size_t flag_off;     // flags[slot][sender] start here in every buffer
-    size_t slice_off, slice_bytes; // this rank's slice of the gathered region (multiples of 16)
+    size_t mirror_off;   // the mirror starts here in every buffer: payload float at byte o <-> slot at mirror_off + 2 o
+    size_t slice_off, slice_bytes; // this rank's slice of the gathered region; rank p's is (p - rank) slices away
     int *status;
 };
 struct fq_comm;

@@ -246,10 +246,13 @@ int fq_comm_destroy(fq_comm *comm);
 /* `fq_project_many` on row shards with the exchange included: every y[i] (F32) must lie in this rank's
  * slice [region_offset + rank * shard_bytes, + shard_bytes) of a gathered region of the symmetric buffer;
  * when the call's work has run, the region holds every rank's slice, as after `fq_comm_all_gather`.  At
- * decode widths (m <= 4, Q4_K / Q6_K) the projection kernel stores its results to every peer itself and its
- * last block does the handshake -- one launch for compute and exchange; other shapes project, then gather
- * the region.  A region may be written again only after another exchange of the same communicator has
- * completed in between. */
+ * decode widths (m <= 4, Q4_K / Q6_K) there is ONE launch for compute and exchange and no fence: the
+ * projection kernel stores every output value, paired with the exchange's sequence number in one 8-byte
+ * store, into a mirror area of every peer's buffer, and before it ends its blocks collect the values the
+ * peers sent (polling each slot, bounded, for the current sequence number).  Other shapes project, then
+ * gather the region with the copy kernel.  A region may be written again only after another exchange of the
+ * same communicator has completed in between.  The buffer `fq_comm_create` allocates is three times `bytes`
+ * plus the flag words (payload, flags, mirror). */
 int fq_project_many_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size_t shard_bytes, const fq_matrix *const *w,
                            size_t count, const void *x, int x_dtype, size_t x_elems, size_t m, void *const *y, int y_dtype);
 
