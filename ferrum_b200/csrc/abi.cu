@@ -580,8 +580,7 @@ extern "C" int fq_project_many_gather(fq_device *dev, fq_comm *comm, size_t regi
         if (p < mine || p + m * w[i]->rows * 4 > mine + shard_bytes)
             return fq_fail(dev, FQ_ERR_RANGE, "output %zu lies outside this rank's slice of the region", i);
     }
-    static const bool skip_exchange = [] { const char *e = getenv("FQ_TP_SKIP"); return e && e[0] == '1'; }(); // measurement only
-    if (world == 1 || skip_exchange) return fq_project_many(dev, w, count, x, x_dtype, x_elems, m, y, y_dtype);
+    if (world == 1) return fq_project_many(dev, w, count, x, x_dtype, x_elems, m, y, y_dtype);
     TpPush push{};
     if (int rc = fq_comm_begin_push(comm, mine, shard_bytes, &push)) return fq_fail(dev, rc, "communicator peers are not opened");
     dev->tp_push = &push;
