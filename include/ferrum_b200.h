@@ -220,7 +220,8 @@ int fq_project_many_host(fq_device *dev, const fq_matrix *const *w, size_t count
 
 /* Row-sharded projections: rank r holds rows [r N / g, (r + 1) N / g) of every matrix and computes its
  * slice of the output; the slices are gathered over NVLink peer memory.  One process per GPU.
- *   fq_comm_create   allocates this rank's symmetric buffer (`bytes`, a multiple of 256) and its flag words;
+ *   fq_comm_create   allocates this rank's symmetric buffer (`bytes` of payload, a multiple of 256), its flag
+ *                    words and a mirror area of 2 x `bytes` for the fused exchange of `fq_project_many_gather`;
  *   fq_comm_handle   writes the 64-byte CUDA IPC handle of that buffer, to be exchanged out of band
  *                    (e.g. one torch.distributed all_gather of 64 bytes);
  *   fq_comm_open     maps every peer's buffer from the `world` x 64 handle bytes, ordered by rank;
