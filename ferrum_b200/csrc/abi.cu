@@ -877,28 +877,33 @@ extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset
     if (region_offset % 16 || region_offset + routes * hidden * 4 > fq_comm_bytes(comm))
         return fq_fail(dev, FQ_ERR_RANGE, "%zu expert rows of %zu floats at offset %zu do not fit the symmetric buffer", routes, hidden, region_offset);
     float *down = (float *)(fq_comm_local(comm) + region_offset);
-    if (int rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts)) return rc;
+    const bool narrow = (routes <= MV_ID_MAX_ROUTES && !dev->exact);
+    // As in fq_moe_ffn: at decode widths the (replicated) shared expert runs on the side stream.
+    SideBranch side = narrow ? side_begin(dev) : SideBranch{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
+    int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared);
+    if (int rc2 = side_detach(side)) rc = rc ? rc : rc2;
     const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
-    if (int rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m,
-                              f->sigmoid, f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate))
-        return rc;
-    if (int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared))
-        return rc;
-    if (int rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position)) return rc;
+    if (!rc) rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts);
+    if (!rc)
+        rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m, f->sigmoid,
+                          f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate);
+    if (!rc) rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position);
     const uint32_t *mine = s.offsets + expert_first; // mine[0] .. mine[local]: this rank's run of rows
-    if (routes <= MV_ID_MAX_ROUTES || dev->exact) {
+    if (!rc && (routes <= MV_ID_MAX_ROUTES || dev->exact)) {
         uint32_t *local_ids = (uint32_t *)s.logits; // the logits are consumed by now, and routes <= m * experts
-        if (int rc = fq_moe_gather(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg)) return rc;
-        if (int rc = fq_launch_moe_local_ids(dev, s.ids, s.sorted, (uint32_t)routes, expert_first, (uint32_t)local, local_ids)) return rc;
-        if (int rc = project_id_pair(dev, f->gate_exps, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, s.u)) return rc;
-        if (int rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, local_ids, down)) return rc;
-    } else {
-        if (int rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, mine, (uint32_t)local, s.xg)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.g, FQ_F32, routes * ef)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.u, FQ_F32, routes * ef)) return rc;
-        if (int rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, mine, (uint32_t)local, (uint32_t)ef, s.act)) return rc;
-        if (int rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_BF16, routes * ef, mine, nullptr, local, m, down, FQ_F32, routes * hidden)) return rc;
+        rc = fq_moe_gather(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg);
+        if (!rc) rc = fq_launch_moe_local_ids(dev, s.ids, s.sorted, (uint32_t)routes, expert_first, (uint32_t)local, local_ids);
+        if (!rc) rc = project_id_pair(dev, f->gate_exps, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, s.u);
+        if (!rc) rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, local_ids, down);
+    } else if (!rc) {
+        rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, mine, (uint32_t)local, s.xg);
+        if (!rc) rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.g, FQ_F32, routes * ef);
+        if (!rc) rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.u, FQ_F32, routes * ef);
+        if (!rc) rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, mine, (uint32_t)local, (uint32_t)ef, s.act);
+        if (!rc) rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_BF16, routes * ef, mine, nullptr, local, m, down, FQ_F32, routes * hidden);
     }
+    if (int rc2 = side_join(side)) rc = rc ? rc : rc2; // also after an error: a capture must not end with the branch open
+    if (rc) return rc;
     if (int rc = fq_comm_all_gather_rows(dev, comm, region_offset, hidden * 4, s.offsets, (uint32_t)local, routes)) return rc;
     return fq_moe_combine(dev, down, s.weights, s.position, s.shared, s.gate, (uint32_t)hidden, (uint32_t)used, (uint32_t)m, 0, out);
 }
