@@ -332,9 +332,8 @@ def run_ours(args):
 
             def gemm_layer():
                 for layer in mats:
-                    for group in GROUPS:
-                        for n in group:
-                            S.project(dev, layer[n], xs[group[0]], mm, ys[n])
+                    for group in GROUPS:  # matrices that share an input go out as one launch
+                        S.project_many(dev, [layer[n] for n in group], xs[group[0]], mm, [ys[n] for n in group])
             with torch.cuda.stream(stream):
                 for _ in range(2):
                     gemm_layer()

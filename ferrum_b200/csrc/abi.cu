@@ -553,7 +553,7 @@ extern "C" int fq_project_many(fq_device *dev, const fq_matrix *const *w, size_t
         args[i].m = (uint32_t)m;
     }
     if (!dev->exact && count <= 4) {
-        int rc = launch_decode(dev, args, (uint32_t)count);
+        int rc = m <= (size_t)FQ_GEMV_MAX_M ? launch_decode(dev, args, (uint32_t)count) : fq_launch_gemm_tc_many(dev, args, (uint32_t)count);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
     dev->tp_push = nullptr; // separate launches cannot share one fused exchange

@@ -314,12 +314,22 @@ __device__ __forceinline__ void epilogue(uint32_t tmem, int warp, int lane, uint
 // terms (v = hi + lo, lo = bf16(v - hi)) and every k-block is walked three times: hi x hi, hi x lo, lo x hi
 // (w_hi, w_hi, w_lo against x_hi, x_lo, x_hi); the caller lays X out as [m][3 * cols] in that order.  The
 // dropped lo x lo term and the residuals are 2^-17 of a product.
+// Up to four matrices of one format and width that share X (q|k|v, gate|up): their row tiles are counted
+// through, so one launch fills the machine where the small ones alone would not.
+struct GemmMany {
+    const uint8_t *w[4];
+    void *y[4];
+    uint32_t rows[4];
+    uint32_t tx_end[4]; // row tiles up to and including matrix i
+    uint32_t count;     // <= 1: the kernel's own w / rows / y arguments
+};
+
 template <int FMT, int BN, typename YT, int MODE>
 __global__ void __launch_bounds__(THREADS, MODE == 1 ? 2 : 1) // two expert-tile blocks share an SM: one's set-up and epilogue overlap the other's main loop
 k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t pitch,
           YT *__restrict__ y, uint32_t m, uint32_t b_bytes, const uint32_t *__restrict__ offsets,
           const uint32_t *__restrict__ slots, uint32_t experts, uint32_t tiles_x, uint32_t full_tiles, uint32_t splits, uint32_t per,
-          float *__restrict__ ws, int *status) {
+          float *__restrict__ ws, int *status, const __grid_constant__ GemmMany many) {
     constexpr bool GROUPED = MODE == 1, PRECISE = MODE == 2;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     constexpr int NSUB = BN > 256 ? BN / 256 : 1, MMA_N = BN / NSUB, A_STAGES = a_stages<BN>(), B_SLOTS = b_slots<BN>();
@@ -375,7 +385,18 @@ k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ 
             k_iters = min(per, k_iters - k_first);
             partial = ws + (size_t)i * BN * BM;
         }
-        n0 = (t % tiles_x) * BM;
+        uint32_t tx = t % tiles_x;
+        if (many.count > 1) { // tiles_x counts the row tiles of all the matrices
+            uint32_t which = 0, first = 0;
+#pragma unroll
+            for (int i = 0; i < 3; i++)
+                if ((uint32_t)i + 1 < many.count && tx >= many.tx_end[i]) { which = i + 1; first = many.tx_end[i]; }
+            w = many.w[which];
+            y = (YT *)many.y[which];
+            rows = many.rows[which];
+            tx -= first;
+        }
+        n0 = tx * BM;
         m0 = (t / tiles_x) * BN;
     }
     constexpr uint32_t nblk_div = FMT == FQ_Q8_0 ? 32 : 256;
@@ -552,11 +573,21 @@ __global__ void k_split3(const float *__restrict__ x, __nv_bfloat16 *__restrict_
 template <int BN, typename YT>
 __global__ void __launch_bounds__(256)
 k_fixup(const float *__restrict__ ws, uint32_t full_tiles, uint32_t splits, uint32_t tiles_x, uint32_t rows, uint32_t m, YT *__restrict__ y,
-        size_t total) {
+        size_t total, const __grid_constant__ GemmMany many) {
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= total) return;
     const uint32_t r4 = e % (BM / 4), col = (e / (BM / 4)) % BN, i = (uint32_t)(e / ((size_t)(BM / 4) * BN)), tile = full_tiles + i;
-    const uint32_t row = (tile % tiles_x) * BM + 4 * r4, tok = (tile / tiles_x) * BN + col;
+    uint32_t tx = tile % tiles_x;
+    if (many.count > 1) {
+        uint32_t which = 0, first = 0;
+#pragma unroll
+        for (int q = 0; q < 3; q++)
+            if ((uint32_t)q + 1 < many.count && tx >= many.tx_end[q]) { which = q + 1; first = many.tx_end[q]; }
+        y = (YT *)many.y[which];
+        rows = many.rows[which];
+        tx -= first;
+    }
+    const uint32_t row = tx * BM + 4 * r4, tok = (tile / tiles_x) * BN + col;
     if (tok >= m || row >= rows) return;
     const float *p = ws + (((size_t)i * splits) * BN + col) * BM + 4 * r4;
     float4 sum = __ldcg(reinterpret_cast<const float4 *>(p));
@@ -572,7 +603,7 @@ k_fixup(const float *__restrict__ ws, uint32_t full_tiles, uint32_t splits, uint
 }
 
 template <int FMT, int BN, typename YT, int MODE>
-int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows, int *status) {
+int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows, int *status, const GemmMany &many) {
     constexpr bool GROUPED = MODE == 1;
     const size_t smem = sizeof(Smem<BN>) + 1024;
     static bool configured = false;
@@ -581,7 +612,7 @@ int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_
         if (e != cudaSuccess) return fq_check_cuda(dev, e, "gemm shared memory");
         configured = true;
     }
-    const uint32_t tiles_x = (a.rows + BM - 1) / BM, k_iters = a.cols / BK * (MODE == 2 ? 3 : 1);
+    const uint32_t tiles_x = many.count > 1 ? many.tx_end[many.count - 1] : (a.rows + BM - 1) / BM, k_iters = a.cols / BK * (MODE == 2 ? 3 : 1);
     if (GROUPED) {
         // At most one partly filled tile per group on top of the full ones (m_rows = all groups' rows).
         const uint32_t per_group = (a.max_rows + BN - 1) / BN;
@@ -589,7 +620,7 @@ int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_
         if (tiles_y > 65535) return FQ_ERR_UNSUPPORTED;
         dim3 grid(tiles_x, tiles_y, 1);
         k_gemm_tc<FMT, BN, YT, MODE><<<grid, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
-                                                                              a.offsets, a.slots, a.experts, tiles_x, a.groups, 1, k_iters, dev->gemm_ws, status);
+                                                                              a.offsets, a.slots, a.experts, tiles_x, a.groups, 1, k_iters, dev->gemm_ws, status, many);
         return FQ_OK;
     }
     // Whole waves of tiles run one tile per block.  A remainder that would fill less than three quarters of a
@@ -608,20 +639,20 @@ int launch(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_
     }
     const uint32_t blocks = full + (tiles - full) * splits;
     k_gemm_tc<FMT, BN, YT, MODE><<<blocks, THREADS, smem, dev->stream>>>(map, a.w, a.rows, a.cols, a.row_bytes, (YT *)a.y, m_rows, b_bytes,
-                                                                            a.offsets, a.slots, a.experts, tiles_x, full, splits, per, dev->gemm_ws, status);
+                                                                            a.offsets, a.slots, a.experts, tiles_x, full, splits, per, dev->gemm_ws, status, many);
     if (splits > 1) {
         const size_t threads = (size_t)(tiles - full) * BN * (BM / 4);
-        k_fixup<BN, YT><<<(unsigned)((threads + 255) / 256), 256, 0, dev->stream>>>(dev->gemm_ws, full, splits, tiles_x, a.rows, m_rows, (YT *)a.y, threads);
+        k_fixup<BN, YT><<<(unsigned)((threads + 255) / 256), 256, 0, dev->stream>>>(dev->gemm_ws, full, splits, tiles_x, a.rows, m_rows, (YT *)a.y, threads, many);
     }
     return FQ_OK;
 }
 
 template <int BN, typename YT, int MODE>
-int launch_fmt(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows) {
+int launch_fmt(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows, const GemmMany &many = GemmMany{}) {
     switch (a.format) {
-    case FQ_Q4_K: return launch<FQ_Q4_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev);
-    case FQ_Q6_K: return launch<FQ_Q6_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev);
-    default: return launch<FQ_Q8_0, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev);
+    case FQ_Q4_K: return launch<FQ_Q4_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev, many);
+    case FQ_Q6_K: return launch<FQ_Q6_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev, many);
+    default: return launch<FQ_Q8_0, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev, many);
     }
 }
 
@@ -692,6 +723,36 @@ int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
         kernels += 2;
     }
     return fq_end_enqueue(dev, "gemm_tc", kernels);
+}
+
+// `a[0..count)` share X, m, format and width (BF16 in / BF16 out, no routes): one launch over all their row tiles.
+int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count) {
+    if (count < 2 || count > 4) return FQ_ERR_UNSUPPORTED;
+    const ProjectArgs &f = a[0];
+    if (f.x_dtype != FQ_BF16 || f.y_dtype != FQ_BF16 || f.cols % BK || f.ids || f.offsets) return FQ_ERR_UNSUPPORTED;
+    if (f.format != FQ_Q4_K && f.format != FQ_Q6_K && f.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
+    if (f.format == FQ_Q4_K && (f.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
+    if (f.m <= (uint32_t)FQ_GEMV_MAX_M) return FQ_ERR_UNSUPPORTED;
+    GemmMany many{};
+    many.count = count;
+    uint32_t tx = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].m != f.m || a[i].ids || a[i].offsets ||
+            a[i].x_dtype != FQ_BF16 || a[i].y_dtype != FQ_BF16 || a[i].row_bytes != f.row_bytes)
+            return FQ_ERR_UNSUPPORTED;
+        many.w[i] = a[i].w;
+        many.y[i] = a[i].y;
+        many.rows[i] = a[i].rows;
+        tx += (a[i].rows + BM - 1) / BM;
+        many.tx_end[i] = tx;
+    }
+    CUtensorMap map;
+    uint32_t b_bytes = 0;
+    if (int rc = make_map(dev, &map, f.x, f.cols, f.m, 256, &b_bytes)) return rc;
+    const int rc = f.m >= 384 ? launch_fmt<512, __nv_bfloat16, 0>(dev, f, map, b_bytes, f.m, many)
+                              : launch_fmt<256, __nv_bfloat16, 0>(dev, f, map, b_bytes, f.m, many);
+    if (rc != FQ_OK) return rc;
+    return fq_end_enqueue(dev, "gemm_tc", 1);
 }
 
 // Expert-sorted rows (`project_mm_id_in`): x is [total_rows][cols], F32 (converted to bf16 into the

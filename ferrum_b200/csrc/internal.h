@@ -117,6 +117,8 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
 // Q8_0 integer-dot GEMV (M <= FQ_GEMV_MAX_M, F32 in/out, no routes); FQ_ERR_UNSUPPORTED otherwise.
 int fq_launch_gemv_q8(fq_device *dev, const ProjectArgs &a);
 int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a);
+// 2..4 matrices of one format and width sharing X (BF16 in/out, wider than the verify widths) in one launch.
+int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
 // The same over expert-sorted activation rows (a.offsets / a.slots / a.groups / a.max_rows); F32 or BF16.
 int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t total_rows);
 // Expert-sorted activations and the gated unit with bf16 results (inputs of the grouped tensor-core GEMM).

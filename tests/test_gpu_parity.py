@@ -639,6 +639,30 @@ def test_bf16_gemm_whole_waves_plus_split_tail(device, fmt, m, cols, rows):
 
 
 @pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("m", [100, 700])
+def test_bf16_project_many_is_one_launch_with_the_same_bits(device, fmt, m):
+    """q|k|v-like matrices sharing X at a prefill width: one tensor-core launch over all their row tiles returns
+    what the separate projections return, bit for bit (whole tiles and K-split tail tiles alike)."""
+    s = S()
+    cols, rows = 1024, (300, 65, 128)
+    xb = ref.round_bf16(np.random.default_rng(m).standard_normal((m, cols)).astype(np.float32))
+    xt = dev_f32(xb).to(torch.bfloat16).contiguous()
+    packed = [ref.random_matrix(fmt, r, cols, seed=50 + i) for i, r in enumerate(rows)]
+    ws = [s.Matrix.from_packed(device, r, cols, 1, fmt, p) for r, p in zip(rows, packed)]
+    alone = [torch.full((m * r,), float("nan"), dtype=torch.bfloat16, device="cuda") for r in rows]
+    for w, y in zip(ws, alone):
+        s.project(device, w, xt, m, y)
+    fused = [torch.full((m * r,), float("nan"), dtype=torch.bfloat16, device="cuda") for r in rows]
+    before = device.counters().dispatches
+    s.project_many(device, ws, xt, m, fused)
+    device.synchronize()
+    for a, f, r, p in zip(alone, fused, rows, packed):
+        assert torch.equal(a.view(torch.int16), f.view(torch.int16))
+        want = xb.astype(np.float64) @ ref.round_bf16(ref.dequant(fmt, p)).reshape(r, cols).astype(np.float64).T
+        assert np.abs(f.float().cpu().numpy().reshape(m, r) - want).max() / np.abs(want).max() <= 6e-3
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
 def test_bf16_gemm_weight_tiles_are_bit_exact(device, fmt):
     """X = identity makes Y the weight tile itself: it must equal bf16_rne(exact fp32 decode) bit for bit."""
     rows, cols = 200, 512
