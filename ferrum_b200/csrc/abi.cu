@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
+#include <utility>
 #include <vector>
 
 #include "blocks.cuh"
@@ -128,8 +129,18 @@ extern "C" int fq_device_create(int ordinal, fq_device **out) {
     if ((e = cudaEventCreateWithFlags(&dev->join_event, cudaEventDisableTiming)) != cudaSuccess) return bail(e, "cudaEventCreate");
     dev->side_xprep_bytes = (size_t)4 << 20;
     if ((e = cudaMalloc(&dev->side_xprep, dev->side_xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
-    dev->xprep_bytes = fq_gemv_scratch_bytes();
+    dev->xprep_bytes = FQ_GEMV_SCRATCH_BYTES;
     if ((e = cudaMalloc(&dev->xprep, dev->xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
+    dev->nt_ws_bytes = (size_t)48 << 20;
+    dev->nt_counter_count = 1u << 18;
+    dev->side_nt_ws_bytes = (size_t)4 << 20;
+    dev->side_nt_counter_count = 1u << 14;
+    if ((e = cudaMalloc(&dev->nt_ws, dev->nt_ws_bytes)) != cudaSuccess) return bail(e, "slice workspace");
+    if ((e = cudaMalloc(&dev->side_nt_ws, dev->side_nt_ws_bytes)) != cudaSuccess) return bail(e, "slice workspace");
+    if ((e = cudaMalloc((void **)&dev->nt_counters, (size_t)dev->nt_counter_count * 4)) != cudaSuccess) return bail(e, "slice counters");
+    if ((e = cudaMalloc((void **)&dev->side_nt_counters, (size_t)dev->side_nt_counter_count * 4)) != cudaSuccess) return bail(e, "slice counters");
+    if ((e = cudaMemset(dev->nt_counters, 0, (size_t)dev->nt_counter_count * 4)) != cudaSuccess) return bail(e, "slice counters");
+    if ((e = cudaMemset(dev->side_nt_counters, 0, (size_t)dev->side_nt_counter_count * 4)) != cudaSuccess) return bail(e, "slice counters");
     if ((e = cudaMalloc(&dev->staging_dev, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "device staging");
     if ((e = cudaMallocHost(&dev->staging_host, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "pinned staging");
     dev->gemm_ws_bytes = (size_t)96 << 20;
@@ -150,6 +161,10 @@ extern "C" int fq_device_destroy(fq_device *dev) {
     for (auto &kv : dev->allocations) cudaFree((void *)kv.first);
     if (dev->xprep) cudaFree(dev->xprep);
     if (dev->side_xprep) cudaFree(dev->side_xprep);
+    if (dev->nt_ws) cudaFree(dev->nt_ws);
+    if (dev->side_nt_ws) cudaFree(dev->side_nt_ws);
+    if (dev->nt_counters) cudaFree(dev->nt_counters);
+    if (dev->side_nt_counters) cudaFree(dev->side_nt_counters);
     if (dev->side_stream) {
         cudaStreamSynchronize(dev->side_stream);
         cudaStreamDestroy(dev->side_stream);
@@ -192,6 +207,7 @@ extern "C" int fq_synchronize(fq_device *dev) {
         const int st = *dev->status_host;
         *dev->status_host = 0;
         dev->failed = true;
+        if (st == FQ_ERR_WEIGHT) return fq_fail(dev, FQ_ERR_WEIGHT, "router produced invalid logits");
         return fq_fail(dev, st == FQ_ERR_TIMEOUT ? FQ_ERR_TIMEOUT : FQ_ERR_SYNC, "a kernel gave up a bounded wait (status %d)", st);
     }
     if (dev->failed) return fq_fail(dev, FQ_ERR_SYNC, "device handle holds a failed submission");
@@ -241,6 +257,7 @@ extern "C" int fq_capture_begin(fq_device *dev) {
     if (int rc = fq_check_cuda(dev, cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal), "begin capture")) return rc;
     dev->capturing = true;
     dev->captured_kernels = 0;
+    dev->cap_comm = nullptr;
     return FQ_OK;
 }
 
@@ -266,6 +283,11 @@ extern "C" int fq_capture_end(fq_device *dev, fq_graph **out) {
     g->graph = graph;
     g->exec = exec;
     g->kernels = dev->captured_kernels;
+    g->comm = dev->cap_comm;
+    g->first_off = dev->cap_first_off;
+    g->first_bytes = dev->cap_first_bytes;
+    g->last_off = dev->cap_last_off;
+    g->last_bytes = dev->cap_last_bytes;
     *out = g;
     return FQ_OK;
 }
@@ -274,6 +296,7 @@ extern "C" int fq_graph_launch(fq_device *dev, fq_graph *graph) {
     if (int rc = fq_begin_enqueue(dev)) return rc;
     if (!graph || graph->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "graph belongs to another device handle");
     if (dev->capturing) return fq_fail(dev, FQ_ERR_PARAM, "graph launch inside a capture");
+    if (int rc = fq_comm_note_graph(dev, graph)) return rc;
     if (int rc = fq_check_cuda(dev, cudaGraphLaunch(graph->exec, dev->stream), "graph launch")) return rc;
     dev->counters.dispatches += graph->kernels;
     return FQ_OK;
@@ -485,19 +508,15 @@ static int check_dtype(fq_device *dev, int dt) {
     return (dt == FQ_F32 || dt == FQ_BF16) ? FQ_OK : fq_fail(dev, FQ_ERR_UNSUPPORTED, "element type %d", dt);
 }
 
-// Decode / verify widths: the integer kernel up to 4 activation rows (and per-route expert
-// projections), the f16 tensor-core kernel up to FQ_GEMV_MAX_M.  FQ_GEMV=f16 forces the latter.
+// Decode / verify widths (F32 in and out): Q8_0 on the integer-dot kernel, Q4_K / Q6_K on the integer tensor
+// path -- one activation row (and per-route expert projections) in gemv_i8.cu, 2..16 rows in gemv_nt.cu.
 static int launch_decode(fq_device *dev, const ProjectArgs *a, uint32_t count) {
-    static const bool f16_only = [] { const char *e = getenv("FQ_GEMV"); return e && e[0] == 'f'; }();
     if (count == 1 && a[0].format == FQ_Q8_0) {
         int rc = fq_launch_gemv_q8(dev, a[0]);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
-    if (!f16_only) {
-        int rc = fq_launch_gemv_i8_many(dev, a, count);
-        if (rc != FQ_ERR_UNSUPPORTED) return rc;
-    }
-    return fq_launch_gemv_fast_many(dev, a, count);
+    if (a[0].m == 1 || a[0].ids) return fq_launch_gemv_i8_many(dev, a, count);
+    return fq_launch_gemv_nt_many(dev, a, count);
 }
 
 extern "C" int fq_project(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems, size_t m,
@@ -569,27 +588,35 @@ extern "C" int fq_project_many(fq_device *dev, const fq_matrix *const *w, size_t
 extern "C" int fq_project_many_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size_t shard_bytes, const fq_matrix *const *w,
                                       size_t count, const void *x, int x_dtype, size_t x_elems, size_t m, void *const *y, int y_dtype) {
     if (!dev || !comm || !w || !y || count == 0) return fq_fail(dev, FQ_ERR_PARAM, "projection list");
+    if (fq_comm_device(comm) != dev) return fq_fail(dev, FQ_ERR_DEVICE, "communicator belongs to another device handle");
     const int world = fq_comm_world(comm), rank = fq_comm_rank(comm);
     if (y_dtype != FQ_F32) return fq_fail(dev, FQ_ERR_UNSUPPORTED, "gathered projections are F32");
     if (shard_bytes == 0 || shard_bytes % 16 || region_offset % 16 || region_offset + shard_bytes * world > fq_comm_bytes(comm))
         return fq_fail(dev, FQ_ERR_RANGE, "gather of %zu bytes per rank at offset %zu does not fit the symmetric buffer", shard_bytes, region_offset);
+    // The outputs tile this rank's slice from its start, in order, without gaps (what follows them is padding
+    // that no rank sends or waits for).
     const uint8_t *mine = fq_comm_local(comm) + region_offset + (size_t)rank * shard_bytes;
+    size_t covered = 0;
     for (size_t i = 0; i < count; i++) {
         if (!w[i]) return fq_fail(dev, FQ_ERR_PARAM, "null matrix");
-        const uint8_t *p = (const uint8_t *)y[i];
-        if (p < mine || p + m * w[i]->rows * 4 > mine + shard_bytes)
-            return fq_fail(dev, FQ_ERR_RANGE, "output %zu lies outside this rank's slice of the region", i);
+        if ((const uint8_t *)y[i] != mine + covered)
+            return fq_fail(dev, FQ_ERR_RANGE, "output %zu does not follow the output before it from the start of this rank's slice", i);
+        covered += m * w[i]->rows * 4;
     }
+    if (covered > shard_bytes) return fq_fail(dev, FQ_ERR_RANGE, "%zu bytes of outputs exceed the slice of %zu bytes", covered, shard_bytes);
     if (world == 1) return fq_project_many(dev, w, count, x, x_dtype, x_elems, m, y, y_dtype);
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (int rc = fq_comm_note_region(dev, comm, region_offset, shard_bytes * world)) return rc;
     TpPush push{};
     if (int rc = fq_comm_begin_push(comm, mine, shard_bytes, &push)) return fq_fail(dev, rc, "communicator peers are not opened");
+    push.covered_bytes = covered;
     dev->tp_push = &push;
     dev->tp_pushed = false;
     const int rc = fq_project_many(dev, w, count, x, x_dtype, x_elems, m, y, y_dtype);
     dev->tp_push = nullptr;
     if (rc) return rc;
     if (dev->tp_pushed) return FQ_OK;
-    return fq_comm_all_gather(dev, comm, region_offset, shard_bytes);
+    return fq_comm_all_gather_unchecked(dev, comm, region_offset, shard_bytes);
 }
 
 extern "C" int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x, size_t x_elems, const uint32_t *ids,
@@ -617,6 +644,9 @@ extern "C" int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x,
     return fq_end_enqueue(dev, "project_id", 1);
 }
 
+// Average rows per expert up to which grouped F32 projections take the integer kernel of gemv_nt.cu.
+constexpr size_t GROUPED_NT_MAX_AVG_ROWS = 48;
+
 extern "C" int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems,
                                 const uint32_t *offsets, const uint32_t *slots, size_t groups, size_t max_rows,
                                 void *y, int y_dtype, size_t y_elems) {
@@ -642,7 +672,13 @@ extern "C" int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *
     a.groups = (uint32_t)groups;
     a.max_rows = (uint32_t)max_rows;
     if (!dev->exact) {
-        int rc = fq_launch_gemm_tc_grouped(dev, a, (uint32_t)(x_elems / w->cols));
+        const uint32_t total_rows = (uint32_t)(x_elems / w->cols);
+        int rc = FQ_ERR_UNSUPPORTED;
+        // Few rows per expert: the problem is weight-streaming, not arithmetic; the integer kernel with the rows
+        // on the MMA's N side unpacks every weight once per sixteen rows.  Otherwise the tcgen05 GEMM.
+        if (x_dtype == FQ_F32 && y_dtype == FQ_F32 && total_rows <= GROUPED_NT_MAX_AVG_ROWS * groups)
+            rc = fq_launch_gemv_nt_grouped(dev, &a, 1, total_rows, nullptr, 1);
+        if (rc == FQ_ERR_UNSUPPORTED) rc = fq_launch_gemm_tc_grouped(dev, a, total_rows);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
     if (int rc = fq_launch_project_grouped_exact(dev, a)) return rc;
@@ -675,6 +711,15 @@ struct SideBranch {
     size_t xprep_bytes;
     bool on;
 };
+// The scratch areas kernels of the two streams must not share.
+static void swap_side_scratch(fq_device *dev) {
+    std::swap(dev->xprep, dev->side_xprep);
+    std::swap(dev->xprep_bytes, dev->side_xprep_bytes);
+    std::swap(dev->nt_ws, dev->side_nt_ws);
+    std::swap(dev->nt_ws_bytes, dev->side_nt_ws_bytes);
+    std::swap(dev->nt_counters, dev->side_nt_counters);
+    std::swap(dev->nt_counter_count, dev->side_nt_counter_count);
+}
 static SideBranch side_begin(fq_device *dev) {
     SideBranch b{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
     if (!dev->side_stream) return b;
@@ -683,8 +728,7 @@ static SideBranch side_begin(fq_device *dev) {
         return b;
     }
     dev->stream = dev->side_stream;
-    dev->xprep = dev->side_xprep;
-    dev->xprep_bytes = dev->side_xprep_bytes;
+    swap_side_scratch(dev);
     b.on = true;
     return b;
 }
@@ -694,8 +738,7 @@ static int side_detach(SideBranch &b) {
     fq_device *dev = b.dev;
     const cudaError_t e = cudaEventRecord(dev->join_event, dev->side_stream);
     dev->stream = b.main;
-    dev->xprep = b.xprep;
-    dev->xprep_bytes = b.xprep_bytes;
+    swap_side_scratch(dev);
     return fq_check_cuda(dev, e, "side stream event");
 }
 // `stream` waits for the branch.
@@ -804,6 +847,26 @@ static MoeScratch moe_layout(const fq_moe_ffn_desc *f, size_t m, float *base) {
     return s;
 }
 
+// Routed experts over expert-sorted rows with few rows per expert: gate and up as two targets of one launch that
+// gathers the rows itself (row r of the sorted set is token sorted[r] / used), then the down projection whose
+// activation preparation computes the gated unit.  `offsets[0 .. groups]` bound the rows of the experts the
+// matrices hold.  FQ_ERR_UNSUPPORTED when the shapes have no such kernel (nothing is enqueued then).
+static int moe_experts_nt(fq_device *dev, const fq_moe_ffn_desc *f, const float *x, const MoeScratch &s, const uint32_t *offsets, uint32_t groups,
+                          size_t routes, float *down) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    ProjectArgs gu[2] = {base_args(f->gate_exps, x, FQ_F32, s.g, FQ_F32), base_args(f->up_exps, x, FQ_F32, s.u, FQ_F32)};
+    for (ProjectArgs &p : gu) {
+        p.offsets = offsets;
+        p.groups = groups;
+    }
+    ProjectArgs dn = base_args(f->down_exps, s.g, FQ_F32, down, FQ_F32);
+    dn.x_up = s.u;
+    dn.offsets = offsets;
+    dn.groups = groups;
+    if (int rc = fq_launch_gemv_nt_grouped(dev, gu, 2, (uint32_t)routes, s.sorted, f->used)) return rc;
+    return fq_launch_gemv_nt_grouped(dev, &dn, 1, (uint32_t)routes, nullptr, 1);
+}
+
 extern "C" size_t fq_moe_ffn_scratch_elems(const fq_moe_ffn_desc *f, size_t m) {
     return f ? moe_layout(f, m, nullptr).total : 0;
 }
@@ -841,11 +904,16 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
         // Expert-sorted rows through the tensor-core GEMM: activations rounded to bf16 once (at the gather and
         // at the gated unit), fp32 accumulation and fp32 results.
         rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position);
+        int nt = FQ_ERR_UNSUPPORTED;
+        if (!rc && routes <= GROUPED_NT_MAX_AVG_ROWS * experts) nt = moe_experts_nt(dev, f, x, s, s.offsets, (uint32_t)experts, routes, s.down);
+        if (nt != FQ_ERR_UNSUPPORTED) rc = rc ? rc : nt;
+        else {
         if (!rc) rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, nullptr, 0, s.xg);
         if (!rc) rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.g, FQ_F32, routes * ef);
         if (!rc) rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, s.offsets, nullptr, experts, m, s.u, FQ_F32, routes * ef);
         if (!rc) rc = fq_launch_glu_bf16(dev, s.g, s.u, routes * ef, nullptr, 0, (uint32_t)ef, s.act);
         if (!rc) rc = fq_project_mm_id(dev, f->down_exps, s.act, FQ_BF16, routes * ef, s.offsets, nullptr, experts, m, s.down, FQ_F32, routes * hidden);
+        }
     }
     if (int rc2 = side_join(side)) rc = rc ? rc : rc2; // also after an error: a capture must not end with the branch open
     if (rc) return rc;
@@ -895,7 +963,10 @@ extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset
         if (!rc) rc = fq_launch_moe_local_ids(dev, s.ids, s.sorted, (uint32_t)routes, expert_first, (uint32_t)local, local_ids);
         if (!rc) rc = project_id_pair(dev, f->gate_exps, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, s.u);
         if (!rc) rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, local_ids, down);
-    } else if (!rc) {
+    } else if (!rc && routes <= GROUPED_NT_MAX_AVG_ROWS * experts &&
+               (rc = moe_experts_nt(dev, f, x, s, mine, (uint32_t)local, routes, down)) != FQ_ERR_UNSUPPORTED) {
+        // done (or failed) on the integer kernel
+    } else if (!rc || rc == FQ_ERR_UNSUPPORTED) {
         rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, mine, (uint32_t)local, s.xg);
         if (!rc) rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.g, FQ_F32, routes * ef);
         if (!rc) rc = fq_project_mm_id(dev, f->up_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.u, FQ_F32, routes * ef);

@@ -18,7 +18,6 @@
 
 constexpr int FQ_COMM_MAX_WORLD = 8;
 constexpr uint32_t FQ_COMM_SLOTS = 2048;      // distinct call sites before flag words are reused
-constexpr uint32_t COMM_WAIT_LIMIT = 1u << 24;
 
 struct fq_comm {
     fq_device *dev = nullptr;
@@ -29,6 +28,11 @@ struct fq_comm {
     uint8_t *peer[FQ_COMM_MAX_WORLD] = {};
     bool opened = false;
     uint32_t next_slot = 0;
+    uint64_t wait_ns = 2000000000ull; // wall-time limit of every device-side wait for a peer
+    uint8_t *fake_peer = nullptr;     // fq_comm_open_local: a second local buffer standing in for the peers
+    // The region of the exchange enqueued last (eagerly or by the last graph replayed): the next exchange must
+    // not touch it, because a rank that runs ahead would overwrite what a slower peer is still reading.
+    size_t last_off = 0, last_bytes = 0;
 };
 
 namespace {
@@ -44,7 +48,8 @@ struct Peers {
 // laid out from region_off in row order (the expert-sorted rows of an expert-parallel MoE block).
 __global__ void __launch_bounds__(256)
 k_all_gather_push(const __grid_constant__ Peers peers, int rank, int world, size_t payload_bytes, size_t region_off,
-                  size_t shard_bytes, const uint32_t *__restrict__ bounds, uint32_t stride, uint32_t slot, uint32_t *seq, int *status) {
+                  size_t shard_bytes, const uint32_t *__restrict__ bounds, uint32_t stride, uint32_t slot, uint32_t *seq, uint64_t wait_ns,
+                  int *status) {
     // Launched with programmatic stream serialization: let the next kernel stage itself, then wait for the
     // projection that produced the local shard.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -77,11 +82,18 @@ k_all_gather_push(const __grid_constant__ Peers peers, int rank, int world, size
     uint32_t *remote_flag = reinterpret_cast<uint32_t *>(peers.base[other] + payload_bytes) + (size_t)slot * FQ_COMM_MAX_WORLD + rank;
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote_flag), "r"(expect) : "memory");
     const uint32_t *local_flag = reinterpret_cast<const uint32_t *>(peers.base[rank] + payload_bytes) + (size_t)slot * FQ_COMM_MAX_WORLD + other;
-    for (uint32_t i = 0; i < COMM_WAIT_LIMIT; i++) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; i++) {
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flag) : "memory");
         if ((int32_t)(v - expect) >= 0) return;
         __nanosleep(20);
+        if ((i & 63u) == 63u) { // wall-time limit
+            uint64_t now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > wait_ns) break;
+        }
     }
     *(volatile int *)status = (int)FQ_ERR_TIMEOUT; // the peer never arrived: report, do not hang
 }
@@ -142,15 +154,70 @@ extern "C" int fq_comm_open(fq_comm *c, const void *handles) {
     return FQ_OK;
 }
 
+// Test-only: a communicator of world 2 whose "peer" is a second local buffer that nothing ever writes, so that
+// every wait for the peer runs out (on one GPU, without a second process).
+extern "C" int fq_comm_open_local(fq_comm *c) {
+    if (!c) return FQ_ERR_PARAM;
+    if (c->world != 2 || c->opened) return fq_fail(c->dev, FQ_ERR_PARAM, "a local stand-in peer needs an unopened communicator of two ranks");
+    cudaSetDevice(c->dev->ordinal);
+    const size_t total = c->bytes + flag_bytes() + 2 * c->bytes;
+    cudaError_t e = cudaMalloc((void **)&c->fake_peer, total);
+    if (e == cudaSuccess) e = cudaMemset(c->fake_peer, 0, total);
+    if (int rc = fq_check_cuda(c->dev, e, "stand-in peer buffer")) return rc;
+    c->peer[1 - c->rank] = c->fake_peer;
+    c->opened = true;
+    return FQ_OK;
+}
+
+// Wall-time limit of the device-side waits of this communicator's exchanges (default 2 s).
+extern "C" int fq_comm_set_wait_ns(fq_comm *c, uint64_t ns) {
+    if (!c || ns == 0) return FQ_ERR_PARAM;
+    c->wait_ns = ns;
+    return FQ_OK;
+}
+
 extern "C" void *fq_comm_buffer(fq_comm *c) { return c ? c->local : nullptr; }
+
+// Every exchange passes here before it is enqueued: consecutive exchanges of a communicator must use disjoint
+// regions.  While the handle records a graph, the graph remembers its first and last region instead, and
+// `fq_graph_launch` repeats the check against what ran before it.
+int fq_comm_note_region(fq_device *dev, fq_comm *c, size_t off, size_t bytes) {
+    if (c->world == 1) return FQ_OK;
+    if (dev->capturing) {
+        if (dev->cap_comm && dev->cap_comm != c) return fq_fail(dev, FQ_ERR_PARAM, "one communicator per recorded graph");
+        if (dev->cap_comm && off < dev->cap_last_off + dev->cap_last_bytes && dev->cap_last_off < off + bytes)
+            return fq_fail(dev, FQ_ERR_PARAM, "exchange region [%zu, +%zu) was also the region of the exchange before it; alternate regions", off, bytes);
+        if (!dev->cap_comm) {
+            dev->cap_comm = c;
+            dev->cap_first_off = off;
+            dev->cap_first_bytes = bytes;
+        }
+        dev->cap_last_off = off;
+        dev->cap_last_bytes = bytes;
+        return FQ_OK;
+    }
+    if (c->last_bytes && off < c->last_off + c->last_bytes && c->last_off < off + bytes)
+        return fq_fail(dev, FQ_ERR_PARAM, "exchange region [%zu, +%zu) was also the region of the exchange before it; alternate regions", off, bytes);
+    c->last_off = off;
+    c->last_bytes = bytes;
+    return FQ_OK;
+}
+int fq_comm_note_graph(fq_device *dev, const fq_graph *g) {
+    fq_comm *c = g->comm;
+    if (!c) return FQ_OK;
+    if (c->last_bytes && g->first_off < c->last_off + c->last_bytes && c->last_off < g->first_off + g->first_bytes)
+        return fq_fail(dev, FQ_ERR_PARAM, "the graph's first exchange uses the region of the exchange before it; alternate regions");
+    c->last_off = g->last_off;
+    c->last_bytes = g->last_bytes;
+    return FQ_OK;
+}
 int fq_comm_begin_push(fq_comm *c, const void *y, size_t bytes, TpPush *out) {
     const uint8_t *p = (const uint8_t *)y;
     if (!c->opened || p < c->local || p + bytes > c->local + c->bytes) return FQ_ERR_RANGE;
     for (int r = 0; r < FQ_COMM_MAX_WORLD; r++) out->peer[r] = r < c->world ? c->peer[r] : nullptr;
     out->world = (uint32_t)c->world;
     out->rank = (uint32_t)c->rank;
-    static const uint32_t mode = [] { const char *e = getenv("FQ_TP_MODE"); return e ? (uint32_t)atoi(e) : 3u; }();
-    out->mode = mode;
+    out->pad = 0;
     out->slot = c->next_slot;
     c->next_slot = (c->next_slot + 1) % FQ_COMM_SLOTS;
     out->epoch = c->seq + (size_t)FQ_COMM_SLOTS * FQ_COMM_MAX_WORLD; // a word of the local bookkeeping array nothing else uses
@@ -158,10 +225,13 @@ int fq_comm_begin_push(fq_comm *c, const void *y, size_t bytes, TpPush *out) {
     out->mirror_off = c->bytes + flag_bytes();
     out->slice_off = (size_t)(p - c->local);
     out->slice_bytes = bytes;
+    out->covered_bytes = bytes; // the caller lowers it when its outputs do not fill the slice
+    out->wait_ns = c->wait_ns;
     out->status = c->dev->status_dev;
     return FQ_OK;
 }
 uint8_t *fq_comm_local(fq_comm *c) { return c->local; }
+fq_device *fq_comm_device(const fq_comm *c) { return c->dev; }
 size_t fq_comm_bytes(const fq_comm *c) { return c->bytes; }
 int fq_comm_rank(const fq_comm *c) { return c->rank; }
 int fq_comm_world(const fq_comm *c) { return c->world; }
@@ -183,7 +253,7 @@ static int launch_gather(fq_device *dev, fq_comm *c, size_t region_offset, size_
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (int rc = fq_check_cuda(dev, cudaLaunchKernelEx(&cfg, k_all_gather_push, peers, c->rank, c->world, c->bytes, region_offset,
-                                                       shard_bytes, bounds, stride, slot, c->seq, dev->status_dev), "all-gather launch"))
+                                                       shard_bytes, bounds, stride, slot, c->seq, c->wait_ns, dev->status_dev), "all-gather launch"))
         return rc;
     return fq_end_enqueue(dev, "all_gather", 1);
 }
@@ -195,6 +265,13 @@ extern "C" int fq_comm_all_gather(fq_device *dev, fq_comm *c, size_t region_offs
     if (shard_bytes == 0 || shard_bytes % 16 || region_offset % 16 || region_offset + shard_bytes * c->world > c->bytes)
         return fq_fail(dev, FQ_ERR_RANGE, "gather of %zu bytes per rank at offset %zu does not fit %zu bytes", shard_bytes, region_offset, c->bytes);
     if (c->world == 1) return FQ_OK;
+    if (int rc = fq_comm_note_region(dev, c, region_offset, shard_bytes * c->world)) return rc;
+    return launch_gather(dev, c, region_offset, shard_bytes, nullptr, 0, shard_bytes);
+}
+
+// The gather of a region whose use has been noted already (the fallback of fq_project_many_gather).
+int fq_comm_all_gather_unchecked(fq_device *dev, fq_comm *c, size_t region_offset, size_t shard_bytes) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
     return launch_gather(dev, c, region_offset, shard_bytes, nullptr, 0, shard_bytes);
 }
 
@@ -207,6 +284,7 @@ extern "C" int fq_comm_all_gather_rows(fq_device *dev, fq_comm *c, size_t region
         return fq_fail(dev, FQ_ERR_RANGE, "gather of %zu rows of %zu bytes at offset %zu does not fit %zu bytes", total_rows, row_bytes, region_offset, c->bytes);
     if (int rc = fq_check_binding(dev, bounds, ((size_t)c->world * stride + 1) * 4, "bounds")) return rc;
     if (c->world == 1) return FQ_OK;
+    if (int rc = fq_comm_note_region(dev, c, region_offset, row_bytes * total_rows)) return rc;
     return launch_gather(dev, c, region_offset, row_bytes, bounds, stride, row_bytes * total_rows / c->world);
 }
 
@@ -215,7 +293,8 @@ extern "C" int fq_comm_destroy(fq_comm *c) {
     cudaSetDevice(c->dev->ordinal);
     cudaStreamSynchronize(c->dev->stream);
     for (int r = 0; r < c->world; r++)
-        if (r != c->rank && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
+        if (r != c->rank && c->peer[r] && c->peer[r] != c->fake_peer) cudaIpcCloseMemHandle(c->peer[r]);
+    if (c->fake_peer) cudaFree(c->fake_peer);
     cudaFree(c->local);
     cudaFree(c->seq);
     delete c;

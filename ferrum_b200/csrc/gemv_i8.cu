@@ -34,16 +34,16 @@
 #include <type_traits>
 
 #include "blocks.cuh"
+#include "gemv_common.cuh"
 #include "internal.h"
 
 namespace {
+using namespace fqk;
 
 constexpr int MAX_WARPS = 16; // warps of a block split K between them; the count is chosen per launch
 constexpr int MAX_TARGETS = 4;
 constexpr int MAX_TOKENS = 4;
 
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------- prepared activations
 //
@@ -84,46 +84,12 @@ __device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, 
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = v[i] / (1.f + expf(-v[i])) * u[i];
     }
-    float amax = 0.f;
-    bool bad = false;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        amax = fmaxf(amax, fabsf(v[i]));
-        bad |= !(fabsf(v[i]) < INFINITY);
-    }
-    const bool finite = __ballot_sync(0xffffffffu, bad) == 0u; // no NaN or infinity in the superblock
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    // s = 2^e, the largest power of two with amax * s <= 32639 (so that hi = (x' + 128) >> 8 fits a
-    // signed byte); 1 when the block is all zero or not finite (the result is then not finite either).
-    int e = 0;
-    if (amax > 0.f && finite) {
-        int ex;
-        frexpf(amax, &ex);
-        e = 15 - ex;
-        if (ldexpf(amax, e) > 32639.f) e -= 1;
-        e = max(-110, min(110, e));
-    }
-    const float s = ldexpf(1.f, e);
-    uint8_t hi[8], lo[8];
-    int sum = 0, sum_hi = 0, sum_lo = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        int q = __float2int_rn(fminf(fmaxf(v[i] * s, -32639.f), 32639.f));
-        if (!finite) q = 0; // the block's factor below is NaN in that case
-        const int h = (q + 128) >> 8, l = q - (h << 8);
-        hi[i] = (uint8_t)h;
-        lo[i] = (uint8_t)l;
-        sum += q;
-        sum_hi += h;
-        sum_lo += l;
-    }
-    auto pack8 = [](const uint8_t *p) {
-        uint2 r;
-        r.x = p[0] | (p[1] << 8) | (p[2] << 16) | ((uint32_t)p[3] << 24);
-        r.y = p[4] | (p[5] << 8) | (p[6] << 16) | ((uint32_t)p[7] << 24);
-        return r;
-    };
+    const Quant8 q = quantize8(v);
+    const bool finite = q.finite;
+    const int e = q.e;
+    int sum = q.sum, sum_hi = q.sum_hi, sum_lo = q.sum_lo;
+    auto pack8 = [](const uint8_t *p) { return make_uint2(pack4(p), pack4(p + 4)); };
+    const uint8_t *hi = q.hi, *lo = q.lo;
     reinterpret_cast<uint2 *>(base)[b * 32 + lane] = pack8(hi);
     reinterpret_cast<uint2 *>(base + L.lo_off)[b * 32 + lane] = pack8(lo);
     // 16-value sums (lane pairs) and 32-value sums (lane quads).
@@ -156,67 +122,6 @@ k_prep_i8(const float *__restrict__ x, const float *__restrict__ x_up, uint32_t 
 
 // ---------------------------------------------------------------- helpers
 
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// Prepared activations: written by the kernel before this one (which may still run when this grid
-// starts), so ordinary coherent loads after `pdl_wait`; volatile so guarded loads are not speculated.
-__device__ __forceinline__ uint4 ldx128(const void *p) {
-    uint4 r;
-    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
-    return r;
-}
-__device__ __forceinline__ uint32_t ldx32(const void *p) {
-    uint32_t r;
-    asm volatile("ld.global.ca.u32 %0, [%1];" : "=r"(r) : "l"(p));
-    return r;
-}
-// The same from shared memory (generic pointer in, shared-state-space load out).
-__device__ __forceinline__ uint4 lds128(const void *p) {
-    uint4 r;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-    return r;
-}
-__device__ __forceinline__ uint2 lds64(const void *p) {
-    uint2 r;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-    return r;
-}
-__device__ __forceinline__ uint32_t lds32(const void *p) {
-    uint32_t r;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-    return r;
-}
-template <bool SH> __device__ __forceinline__ uint4 ldx128_at(const void *p) { return SH ? lds128(p) : ldx128(p); }
-template <bool SH> __device__ __forceinline__ uint32_t ldx32_at(const void *p) { return SH ? lds32(p) : ldx32(p); }
-// Weights: immutable, read once -> read-only path, no L1 allocation.
-__device__ __forceinline__ uint4 ldw128(const void *p) {
-    uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
-    return r;
-}
-__device__ __forceinline__ uint2 ldw64(const void *p) {
-    uint2 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
-    return r;
-}
-__device__ __forceinline__ uint32_t ldw16(const void *p) {
-    uint16_t r;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(r) : "l"(p));
-    return r;
-}
-__device__ __forceinline__ uint32_t lop3_select(uint32_t a, uint32_t b, uint32_t mask) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xE4;" : "=r"(r) : "r"(a), "r"(b), "r"(mask)); // (a & mask) | (b & ~mask)
-    return r;
-}
-__device__ __forceinline__ int byte_u(uint32_t w, int i) { return (int)((w >> (8 * i)) & 0xFFu); }
-__device__ __forceinline__ int byte_s(uint32_t w, int i) { return (int)(int8_t)((w >> (8 * i)) & 0xFFu); }
-__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
-
 // Q4_K: the header, 16 bytes of chunk t / 2 and 16 bytes of chunk 2 + t / 2 (bytes 16 (t % 2) .. of each
 // chunk's 32), so that the four threads of a quad read 64 contiguous bytes per instruction.
 struct Q4Raw {
@@ -227,14 +132,6 @@ struct Q4Raw {
         qa = ldw128(blk + 16 + 16 * t);
         qb = ldw128(blk + 80 + 16 * t);
     }
-    // From a staged row segment of `k` consecutive superblocks (144 bytes each), superblock `b` of it.
-    __device__ __forceinline__ void load_staged(const uint8_t *seg, const uint8_t *, uint32_t, uint32_t, uint32_t, uint32_t b, int t) {
-        const uint8_t *blk = seg + (size_t)b * 144;
-        hdr = lds128(blk);
-        qa = lds128(blk + 16 + 16 * t);
-        qb = lds128(blk + 80 + 16 * t);
-    }
-    static constexpr uint32_t STAGED_BYTES = 144; // per superblock and row
 };
 struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
     uint4 q0, q1, qh; // ql of 32-groups 0|2 and 1|3 of half n, qh of half n: run lh (16 bytes each)
@@ -249,18 +146,6 @@ struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
         sc = ldw64(row + (size_t)nblk * 192 + (size_t)b * 16 + 8 * (t & 1));
         d = ldw16(row + (size_t)nblk * 208 + (size_t)b * 2);
     }
-    // From a staged row segment of `k` consecutive superblocks, planes [ql k x 128][qh k x 64][scales k x 16];
-    // the 2-byte d comes from the row in global memory (superblock `gb` of `nblk`).
-    __device__ __forceinline__ void load_staged(const uint8_t *seg, const uint8_t *row, uint32_t nblk, uint32_t gb, uint32_t k, uint32_t b, int t) {
-        const int n = t >> 1, lh = t & 1;
-        const uint8_t *ql = seg + (size_t)b * 128 + 64 * n + 16 * lh;
-        q0 = lds128(ql);
-        q1 = lds128(ql + 32);
-        qh = lds128(seg + (size_t)k * 128 + (size_t)b * 64 + 32 * n + 16 * lh);
-        sc = lds64(seg + (size_t)k * 192 + (size_t)b * 16 + 8 * (t & 1));
-        d = ldw16(row + (size_t)nblk * 208 + (size_t)gb * 2);
-    }
-    static constexpr uint32_t STAGED_BYTES = 208; // per superblock and row
 };
 
 // The prepared activations of one row that one thread needs for one superblock.
@@ -271,25 +156,23 @@ template <int FMT> struct Act {
     uint4 xb[FMT == FQ_Q4_K ? 2 : 4];
     uint4 sx;
     float inv;
-    __device__ __forceinline__ void load(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) { load_at<false>(tok, L, b, t, g); }
-    // SH: `tok` points into shared memory.
-    template <bool SH> __device__ __forceinline__ void load_at(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) {
+    __device__ __forceinline__ void load(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) {
         const int plane = g >> 2, u = t & 1;
         if constexpr (FMT == FQ_Q4_K) {
             const bool feeds = (t >> 1) == (g & 1);
             const int chunk = (((g & 3) >> 1) ? 2 : 0) + (t >> 1);
             const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 64 * chunk + 16 * (t & 1);
 #pragma unroll
-            for (int i = 0; i < 2; i++) xb[i] = feeds ? ldx128_at<SH>(src + 32 * i) : make_uint4(0, 0, 0, 0);
-            sx = ldx128_at<SH>(tok + L.sx32_off + (size_t)b * 32 + 16 * u);
+            for (int i = 0; i < 2; i++) xb[i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
+            sx = ldx128(tok + L.sx32_off + (size_t)b * 32 + 16 * u);
         } else {
             const bool feeds = (g & 3) == t;
             const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 128 * (t >> 1) + 16 * (t & 1);
 #pragma unroll
-            for (int i = 0; i < 4; i++) xb[i] = feeds ? ldx128_at<SH>(src + 32 * i) : make_uint4(0, 0, 0, 0);
-            sx = ldx128_at<SH>(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
+            for (int i = 0; i < 4; i++) xb[i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
+            sx = ldx128(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
         }
-        inv = __uint_as_float(ldx32_at<SH>(tok + L.isc_off + (size_t)b * 4));
+        inv = __uint_as_float(ldx32(tok + L.isc_off + (size_t)b * 4));
     }
 };
 
@@ -390,45 +273,6 @@ __device__ __forceinline__ void superblock_dot(const RawT (&cur)[2], const Act<F
 #pragma unroll
             for (int r = 0; r < 2; r++) yacc[m][r] = fmaf(acur[m].inv * dd[r], (float)dot[r], yacc[m][r]);
         }
-    }
-}
-
-// Row-sharded launches (TpPush, internal.h).  tp_seq: the sequence number of this exchange, read by every block
-// once the kernel before has finished.  tp_store: one output value to the mirror of every peer, tagged.
-// tp_finish: this block's share of the incoming slots, then the bookkeeping by the last block.
-__device__ __forceinline__ uint32_t tp_seq(const TpPush &P) { return *(volatile uint32_t *)P.epoch + 1u; }
-__device__ __forceinline__ void tp_store(const TpPush &P, uint32_t seq, const float *dst, float v) {
-    const size_t off = (size_t)((const uint8_t *)dst - P.peer[P.rank]);
-    for (uint32_t p = 0; p < P.world; p++)
-        if (p != P.rank)
-            asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(P.peer[p] + P.mirror_off + 2 * off), "r"(__float_as_uint(v)), "r"(seq) : "memory");
-}
-__device__ __forceinline__ void tp_finish(const TpPush &P, uint32_t seq) {
-    const uint32_t blocks = gridDim.x * gridDim.y * gridDim.z, block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-    if (P.mode & 2u) {
-        const size_t per_rank = P.slice_bytes / 4, incoming = per_rank * (P.world - 1);
-        const size_t lo = incoming * block / blocks, hi = incoming * (block + 1) / blocks;
-        for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-            uint32_t p = (uint32_t)(i / per_rank);
-            const size_t j = i % per_rank;
-            if (p >= P.rank) p++; // the senders, skipping this rank
-            const size_t off = P.slice_off + ((size_t)p - P.rank) * P.slice_bytes + 4 * j; // wraps correctly for p < rank
-            const uint8_t *slot = P.peer[P.rank] + P.mirror_off + 2 * off;
-            uint32_t v = 0, tag = 0;
-            bool arrived = false;
-            for (uint32_t n = 0; n < (1u << 22) && !arrived; n++) {
-                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(tag) : "l"(slot) : "memory");
-                arrived = tag == seq;
-                if (!arrived && n > 16) __nanosleep(64);
-            }
-            if (arrived) *reinterpret_cast<uint32_t *>(P.peer[P.rank] + off) = v;
-            else *(volatile int *)P.status = (int)FQ_ERR_TIMEOUT; // the peer never sent: report, do not hang
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0 && atomicAdd(P.counter, 1u) + 1u == blocks) {
-        *P.counter = 0;
-        *(volatile uint32_t *)P.epoch = seq; // every block has read it by now
     }
 }
 
@@ -579,7 +423,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
                 if (row < here.rows) {
                     float *dst = &here.y[y_base + (size_t)m * here.rows + row];
                     *dst = v;
-                    if (P.world > 1 && (P.mode & 1u)) tp_store(P, seq, dst, v);
+                    if (P.world > 1) tp_store(P, seq, dst, v);
                 }
             }
     }
@@ -590,312 +434,6 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
     }
     if (P.world > 1) tp_finish(P, seq);
-}
-
-// ---------------------------------------------------------------- staged variant
-//
-// The same arithmetic with the weights staged through shared memory by the copy engine instead of through
-// registers: what a warp can keep in flight with register prefetch is one superblock per thread, which caps
-// the stream at about 60% of what HBM delivers; a ring of bulk copies has no such limit.
-//
-//   warp k (producer)   lanes 0..15 each own one row of the block's current 16-row tile and issue, per stage,
-//                       one bulk copy (Q4_K) or three (Q6_K planes) of that row's next `k` superblocks into the
-//                       ring, completing on the stage's mbarrier.  Weights are immutable, so the producer starts
-//                       at once: the ring fills while the kernel before this one is still running.
-//   warps 0..k-1        wait for the activations of the kernel before (griddepcontrol.wait), prepare them (16-bit
-//                       integers, sums, scale: no separate preparation launch) into shared memory once, then per stage: warp c takes superblock c of the
-//                       stage (rows g, g + 8 per thread, as in the register variant), releases the stage, and at
-//                       the end of a tile the warps' partial sums meet in shared memory.
-//
-// Blocks are persistent (tiles b, b + gridDim.x, ...).  Every wait is bounded; a wait that gives up records
-// FQ_ERR_TIMEOUT, raises the block's abort flag and from then on no wait blocks any more: the block runs its
-// control flow to the end (with meaningless sums) so that every barrier is still reached by every warp.
-constexpr int RING_STAGES_MAX = 8;
-constexpr uint32_t RING_WAIT_NS = 2000000000u;
-
-struct RingCfg {
-    uint32_t k;          // consumer warps = superblocks per stage
-    uint32_t stages;     // ring depth
-    uint32_t row_stride; // bytes between the segments of consecutive rows in a stage (padded against bank conflicts)
-    uint32_t act_bytes;  // MT * token_bytes
-};
-
-__device__ __forceinline__ uint32_t s_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ bool ring_try(uint64_t *bar, uint32_t parity, uint32_t hint_ns) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok)
-                 : "r"(s_addr(bar)), "r"(parity), "r"(hint_ns)
-                 : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void ring_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, int *status) {
-    if (ring_try(bar, parity, 0)) return;
-    if (*abort_flag) return;
-    uint64_t t0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-    for (;;) {
-        if (ring_try(bar, parity, 20000) || *abort_flag) return;
-        uint64_t now;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        if (now - t0 > RING_WAIT_NS) break;
-    }
-    *(volatile int *)status = (int)FQ_ERR_TIMEOUT;
-    *abort_flag = 1u;
-}
-__device__ __forceinline__ void bulk_copy(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(s_addr(dst)), "l"(src), "r"(bytes), "r"(s_addr(bar))
-                 : "memory");
-}
-
-template <int FMT, int MT>
-__global__ void __launch_bounds__(MT >= 3 ? 288 : MT == 2 ? 416 : 544)
-k_gemv_ring(const __grid_constant__ GemvTargets T, uint32_t pitch, const float *__restrict__ x, const float *__restrict__ x_up, PrepI8 L,
-            RingCfg R, const __grid_constant__ TpPush P, int *status) {
-    using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
-    extern __shared__ __align__(128) uint8_t ring_smem[];
-    __shared__ uint64_t full[RING_STAGES_MAX], empty[RING_STAGES_MAX];
-    __shared__ float red[2][MAX_WARPS - 1][MT * 2][8];
-    __shared__ uint32_t abort_flag;
-    const uint32_t k = R.k, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    uint8_t *act = ring_smem, *ring = ring_smem + R.act_bytes;
-    const uint32_t stage_bytes = 16 * R.row_stride, nblk = L.nblk, spt = (nblk + k - 1) / k; // stages per tile
-    const uint32_t total_tiles = T.tile_end[T.count - 1];
-
-    pdl_trigger();
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < R.stages; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(&full[s])), "r"(1u));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(&empty[s])), "r"(k));
-        }
-        abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    volatile uint32_t *aborted = &abort_flag;
-    uint32_t seq = 0; // of the fused exchange, if any
-
-    auto tile_rows = [&](uint32_t tile, uint32_t &rows, uint32_t &tile0, float *&y) -> const uint8_t * {
-        uint32_t which = 0, first_block = 0;
-#pragma unroll
-        for (int i = 0; i < MAX_TARGETS - 1; i++)
-            if ((uint32_t)i + 1 < T.count && tile >= T.tile_end[i]) { which = i + 1; first_block = T.tile_end[i]; }
-        rows = T.rows[which];
-        tile0 = tile - first_block;
-        y = T.y[which];
-        return T.w[which];
-    };
-
-    if (warp == k) {
-        // ---- producer
-        uint32_t it = 0, s = 0, phase = 0; // stage it % stages, phase (it / stages) % 2, kept by counting
-        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            uint32_t rows, tile0;
-            float *y;
-            const uint8_t *w = tile_rows(tile, rows, tile0, y);
-            const uint8_t *row = w + (size_t)min(tile0 * 16 + (lane & 15), rows - 1) * pitch;
-            for (uint32_t j = 0; j < spt; j++, it++, s = s + 1 == R.stages ? 0 : s + 1, phase ^= (s == 0)) {
-                const uint32_t b0 = j * k, nsb = min(k, nblk - b0);
-                ring_wait(&empty[s], phase ^ 1u, aborted, status);
-                if (lane == 0)
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_addr(&full[s])), "r"(16u * nsb * Raw::STAGED_BYTES) : "memory");
-                __syncwarp();
-                if (lane < 16 && !*aborted) {
-                    uint8_t *dst = ring + (size_t)s * stage_bytes + (size_t)lane * R.row_stride;
-                    if constexpr (FMT == FQ_Q4_K) {
-                        bulk_copy(dst, row + (size_t)b0 * 144, nsb * 144, &full[s]);
-                    } else {
-                        bulk_copy(dst, row + (size_t)b0 * 128, nsb * 128, &full[s]);
-                        bulk_copy(dst + (size_t)k * 128, row + (size_t)nblk * 128 + (size_t)b0 * 64, nsb * 64, &full[s]);
-                        bulk_copy(dst + (size_t)k * 192, row + (size_t)nblk * 192 + (size_t)b0 * 16, nsb * 16, &full[s]);
-                    }
-                }
-            }
-        }
-        // Copies still in flight land in this block's shared memory: after an abort, give them (bounded) time.
-        if (*aborted && lane == 0)
-            for (uint32_t back = 0; back < R.stages && back < it; back++) {
-                const uint32_t i2 = it - 1 - back;
-                for (uint32_t n = 0; n < 1000u && !ring_try(&full[i2 % R.stages], (i2 / R.stages) & 1u, 20000); n++) {}
-            }
-    } else {
-        // ---- consumers
-        pdl_wait(); // the activations are the output of the kernel before
-        if (P.world > 1) seq = tp_seq(P);
-        // Every block prepares the activations for itself, straight into shared memory (k_prep_i8's arithmetic).
-        for (uint32_t i = warp; i < MT * nblk; i += k)
-            prep_superblock(x + (size_t)(i / nblk) * L.cols, i % nblk, lane, L, act + (size_t)(i / nblk) * L.token_bytes,
-                            x_up ? x_up + (size_t)(i / nblk) * L.cols : nullptr);
-        asm volatile("bar.sync 1, %0;" ::"r"(k * 32) : "memory");
-        float yacc[MT][2];
-#pragma unroll
-        for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
-        uint32_t s = 0, phase = 0, buf = 0;
-        // This thread's two row segments inside a stage, and where its warp's superblock sits in them.
-        const uint32_t seg0 = (uint32_t)g * R.row_stride, seg1 = (uint32_t)(g + 8) * R.row_stride;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, buf ^= 1u) {
-            uint32_t rows, tile0;
-            float *y;
-            const uint8_t *w = tile_rows(tile, rows, tile0, y);
-            const uint8_t *rowp[2];
-#pragma unroll
-            for (int r = 0; r < 2; r++) rowp[r] = w + (size_t)min(tile0 * 16 + g + r * 8, rows - 1) * pitch;
-            const uint8_t *stage = ring + (size_t)s * stage_bytes;
-            for (uint32_t j = 0, b = warp; j < spt; j++, b += k) {
-                ring_wait(&full[s], phase, aborted, status);
-                if (b < nblk) {
-                    Raw cur[2];
-                    Act<FMT> acur[MT];
-                    cur[0].load_staged(stage + seg0, rowp[0], nblk, b, k, warp, t);
-                    cur[1].load_staged(stage + seg1, rowp[1], nblk, b, k, warp, t);
-#pragma unroll
-                    for (int m = 0; m < MT; m++) acur[m].template load_at<true>(act + (size_t)m * L.token_bytes, L, b, t, g);
-                    superblock_dot<FMT, MT>(cur, acur, t, g, yacc);
-                }
-                __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_addr(&empty[s])) : "memory");
-                if (++s == R.stages) {
-                    s = 0;
-                    phase ^= 1u;
-                    stage = ring;
-                } else {
-                    stage += stage_bytes;
-                }
-            }
-            // Quad threads hold partial sums of different scale groups and planes: add them, then the warps.
-#pragma unroll
-            for (int m = 0; m < MT; m++)
-#pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    yacc[m][r] += __shfl_xor_sync(0xffffffffu, yacc[m][r], 1);
-                    yacc[m][r] += __shfl_xor_sync(0xffffffffu, yacc[m][r], 2);
-                }
-            if (warp > 0 && t == 0) {
-#pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    red[buf][warp - 1][m * 2][g] = yacc[m][0];
-                    red[buf][warp - 1][m * 2 + 1][g] = yacc[m][1];
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(k * 32) : "memory"); // one barrier per tile: the halves of `red` alternate
-            if (warp == 0 && t == 0) {
-#pragma unroll
-                for (int m = 0; m < MT; m++)
-#pragma unroll
-                    for (int r = 0; r < 2; r++) {
-                        float v = yacc[m][r];
-                        for (uint32_t ww = 0; ww + 1 < k; ww++) v += red[buf][ww][m * 2 + r][g];
-                        const uint32_t row = tile0 * 16 + g + r * 8;
-                        if (row < rows) {
-                            float *dst = &y[(size_t)m * rows + row];
-                            *dst = v;
-                            if (P.world > 1 && (P.mode & 1u)) tp_store(P, seq, dst, v);
-                        }
-                    }
-            }
-#pragma unroll
-            for (int m = 0; m < MT; m++) yacc[m][0] = yacc[m][1] = 0.f;
-        }
-    }
-    if (P.world > 1) {
-        if (warp == k) seq = tp_seq(P); // the producer warp: by now the kernel before has long finished
-        tp_finish(P, seq);
-    }
-}
-
-template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = stream;
-    // FQ_PDL=0 turns programmatic dependent launch off (plain stream order), for A/B measurements.
-    static const bool pdl = [] { const char *e = getenv("FQ_PDL"); return !(e && e[0] == '0'); }();
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
-
-// The staged kernel for one launch, or cudaErrorNotSupported when its shared-memory needs do not fit (the
-// caller then takes the register variant).
-template <int FMT, int MT>
-cudaError_t launch_ring(fq_device *dev, const ProjectArgs *a, uint32_t count, const PrepI8 &L) {
-    using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
-    GemvTargets T{};
-    T.count = count;
-    uint32_t blocks = 0;
-    for (uint32_t i = 0; i < count; i++) {
-        T.w[i] = a[i].w;
-        T.y[i] = (float *)a[i].y;
-        T.rows[i] = a[i].rows;
-        blocks += (a[i].rows + 15) / 16;
-        T.tile_end[i] = blocks;
-    }
-    // Consumer warps = superblocks per stage: as many as the registers of the variant allow, at least two
-    // superblocks per warp and tile, and the count that wastes the fewest warp slots on an uneven split.
-    const uint32_t nblk = L.nblk, cap = MT >= 3 ? 8u : MT == 2 ? 12u : (uint32_t)MAX_WARPS;
-    const uint32_t max_k = std::max(1u, std::min(cap, nblk / 2));
-    uint32_t k = max_k;
-    uint64_t best = ~0ull;
-    for (uint32_t c = std::max(1u, (max_k + 1) / 2); c <= max_k; c++) {
-        const uint64_t per = (nblk + c - 1) / c, waste = (per * c - nblk) * 1000 / nblk;
-        if (waste <= best) { best = waste; k = c; }
-    }
-    RingCfg R{};
-    R.k = k;
-    const uint32_t seg = k * Raw::STAGED_BYTES;
-    // Two adjacent rows are read by one quarter-warp: pad so that they fall on different banks.
-    const uint32_t want_mod = FMT == FQ_Q4_K ? 64u : 32u;
-    R.row_stride = seg + ((want_mod + 128u - seg % 128u) % 128u);
-    R.act_bytes = MT * L.token_bytes;
-    const uint32_t stage_bytes = 16 * R.row_stride, threads = (k + 1) * 32;
-    static bool configured = false;
-    constexpr uint32_t SMEM_MAX = 216 * 1024; // plus up to 8 KB of static shared memory: inside the 227 KB a block may have
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(k_gemv_ring<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    // As many blocks per SM as the threads allow (up to 4) while each still has a ring of at least 3 stages.
-    static const uint32_t per_sm_cap = [] { const char *e = getenv("FQ_RING_PER_SM"); return e ? (uint32_t)atoi(e) : 4u; }();
-    uint32_t per_sm = std::max(1u, std::min(per_sm_cap, 2048u / threads)), smem = 0;
-    for (;; per_sm--) {
-        const uint32_t budget = SMEM_MAX / per_sm - 6 * 1024;
-        if (budget > R.act_bytes && (budget - R.act_bytes) / stage_bytes >= 3) {
-            static const uint32_t stage_cap = [] { const char *e = getenv("FQ_RING_STAGES"); return e ? (uint32_t)atoi(e) : (uint32_t)RING_STAGES_MAX; }();
-            R.stages = std::min<uint32_t>(stage_cap, (budget - R.act_bytes) / stage_bytes);
-            smem = R.act_bytes + R.stages * stage_bytes;
-            break;
-        }
-        if (per_sm == 1) return cudaErrorNotSupported;
-    }
-    int occ = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_ring<FMT, MT>, (int)threads, smem) != cudaSuccess || occ < 1) return cudaErrorNotSupported;
-    const uint32_t grid = std::min(blocks, (uint32_t)dev->sm_count * (uint32_t)occ);
-    TpPush push{};
-    if (dev->tp_push) { // one launch covers every target: it can do the exchange itself
-        push = *dev->tp_push;
-        dev->tp_push = nullptr;
-        dev->tp_pushed = true;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(threads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = dev->stream;
-    static const bool pdl = [] { const char *e = getenv("FQ_PDL"); return !(e && e[0] == '0'); }();
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, k_gemv_ring<FMT, MT>, T, a[0].row_bytes, (const float *)a[0].x, a[0].x_up, L, R, push, dev->status_dev);
 }
 
 template <int FMT, int MT>
@@ -940,13 +478,13 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
         dev->tp_push = nullptr;
         dev->tp_pushed = true;
     }
-    return launch_pdl(k_gemv_i8<FMT, MT>, grid, dim3(warps * 32), dev->stream, T, a[0].row_bytes, prep, L, a[0].ids, a[0].x_div,
+    return launch_pdl(k_gemv_i8<FMT, MT>, grid, dim3(warps * 32), 0, dev->stream, T, a[0].row_bytes, prep, L, a[0].ids, a[0].x_div,
                       a[0].experts, push);
 }
 
 } // namespace
 
-// `a[0..count)` share x, m (<= 4), format and width; expert mode takes one matrix.
+// `a[0..count)` share x, format and width; one activation row, or routes (expert mode: one activation row per route).
 int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count) {
     if (count == 0 || count > (uint32_t)MAX_TARGETS) return FQ_ERR_UNSUPPORTED;
     const ProjectArgs &f = a[0];
@@ -964,49 +502,22 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
         xrows = f.m / f.x_div; // the caller checked that x holds routes / x_div rows
         m = 1;
     } else {
-        if (f.m > (uint32_t)MAX_TOKENS) return FQ_ERR_UNSUPPORTED;
+        if (f.m != 1) return FQ_ERR_UNSUPPORTED; // 2..16 activation rows: gemv_nt.cu
         xrows = m = f.m;
     }
     const PrepI8 L = prep_i8_layout(f.cols);
-    // Two variants of the same arithmetic.  Measured on B200, both are bound by instruction issue once their
-    // weight stream is up (the register variant has the shorter inner loop and is a few percent faster on the
-    // large matrices, the staged one starts faster and wins on the small ones), and alternating between them
-    // costs more than either gains, because their shared-memory configurations differ.  The register variant
-    // is the default; FQ_GEMV=staged selects the staged kernel for every launch it supports.
-    static const bool ring_only = [] { const char *e = getenv("FQ_GEMV"); return e && e[0] == 's'; }();
-    if (!expert && ring_only) {
-        cudaError_t e;
-        if (f.format == FQ_Q4_K)
-            e = m == 1 ? launch_ring<FQ_Q4_K, 1>(dev, a, count, L) : m == 2 ? launch_ring<FQ_Q4_K, 2>(dev, a, count, L)
-              : m == 3 ? launch_ring<FQ_Q4_K, 3>(dev, a, count, L) : launch_ring<FQ_Q4_K, 4>(dev, a, count, L);
-        else
-            e = m == 1 ? launch_ring<FQ_Q6_K, 1>(dev, a, count, L) : m == 2 ? launch_ring<FQ_Q6_K, 2>(dev, a, count, L)
-              : m == 3 ? launch_ring<FQ_Q6_K, 3>(dev, a, count, L) : launch_ring<FQ_Q6_K, 4>(dev, a, count, L);
-        if (e != cudaErrorNotSupported) {
-            if (int rc = fq_check_cuda(dev, e, "gemv launch")) return rc;
-            return fq_end_enqueue(dev, "gemv_ring", 1);
-        }
-    }
     // Successive projections use alternate halves of the scratch, so a preparation kernel that starts
     // early never writes what the previous projection may still be reading from a cache.
     if ((size_t)xrows * L.token_bytes > dev->xprep_bytes / 2) return FQ_ERR_UNSUPPORTED;
     dev->xprep_turn ^= 1u;
     uint8_t *prep = (uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0);
     const uint32_t warps = xrows * L.nblk;
-    // FQ_SKIP_PREP=1 (measurement only, results are then garbage) leaves the preparation kernel out.
-    static const bool skip_prep = [] { const char *e = getenv("FQ_SKIP_PREP"); return e && e[0] == '1'; }();
-    if (!skip_prep)
-    if (int rc = fq_check_cuda(dev, launch_pdl(k_prep_i8, dim3((warps + 3) / 4), dim3(128), dev->stream, (const float *)f.x, f.x_up, xrows, L, prep),
+    if (int rc = fq_check_cuda(dev, launch_pdl(k_prep_i8, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, xrows, L, prep),
                                "activation preparation launch"))
         return rc;
     cudaError_t e;
-    if (f.format == FQ_Q4_K) {
-        e = m == 1 ? launch<FQ_Q4_K, 1>(dev, a, count, prep, L, expert) : m == 2 ? launch<FQ_Q4_K, 2>(dev, a, count, prep, L, expert)
-          : m == 3 ? launch<FQ_Q4_K, 3>(dev, a, count, prep, L, expert) : launch<FQ_Q4_K, 4>(dev, a, count, prep, L, expert);
-    } else {
-        e = m == 1 ? launch<FQ_Q6_K, 1>(dev, a, count, prep, L, expert) : m == 2 ? launch<FQ_Q6_K, 2>(dev, a, count, prep, L, expert)
-          : m == 3 ? launch<FQ_Q6_K, 3>(dev, a, count, prep, L, expert) : launch<FQ_Q6_K, 4>(dev, a, count, prep, L, expert);
-    }
+    if (f.format == FQ_Q4_K) e = launch<FQ_Q4_K, 1>(dev, a, count, prep, L, expert);
+    else e = launch<FQ_Q6_K, 1>(dev, a, count, prep, L, expert);
     if (int rc = fq_check_cuda(dev, e, "gemv launch")) return rc;
     return fq_end_enqueue(dev, "gemv_i8", 2);
 }

@@ -1,0 +1,697 @@
+// Verify-width projections (2..16 activation rows) and grouped expert projections with few rows per expert,
+// on the integer tensor path with the ACTIVATION ROWS ON THE MMA's N SIDE (F32 in, F32 out).  The reference's
+// `h_mvb_*` / `h_mms_*` (src/metal/shaders/hybrid.metal:1330-1394, 1419-1495; dispatch
+// src/hybrid/engine.rs:3438-3460) and, over expert-sorted rows, `h_mm_id_*` (hybrid.metal:2430-2523).
+//
+// Every packed weight is unpacked once and serves eight or sixteen activation rows:
+//
+//   A (16 weight rows x k)  Q4_K: one 32-value sub-block, raw nibbles as u8 (one AND per four weights, a shift
+//                           more for the high nibbles); Q6_K: one 16-value scale group as s8 = 4 (q - 32)
+//                           (two shifts and two LOP3 per four weights; the factor 4 goes into d);
+//   B (k x 8 rows of x)     the activations as 16-bit integers x' = round(x * s) = 256 hi + lo, both halves
+//                           signed bytes, s a power of two per (row, superblock): two MMAs (hi, lo) on the same A;
+//   per scale group         acc_hi += scale * c_hi, acc_lo += scale * c_lo in integers (and, Q4_K, the minimums
+//                           times the activation sums); once per superblock one conversion and FMA with d / s.
+//
+// The result is the exact dot product of the decoded weights with activations rounded to 16 bits relative to the
+// largest magnitude of their superblock, as in gemv_i8.cu.
+//
+// Organisation: a block keeps the prepared activations of ONE K slice (dense) or of one tile of sixteen
+// expert-sorted rows (grouped) resident in shared memory -- it quantises them itself from x, so there is no
+// preparation launch -- and its warps each take 16-row weight tiles against them.  A warp streams the packed
+// superblocks of its tiles through a private ring in shared memory with 16-byte asynchronous copies (several
+// superblocks in flight per warp, no registers held, no block-wide barrier in the main loop; the ring runs on
+// across tile borders) and reads MMA fragments from there: thread (g = lane / 4, t = lane % 4) owns weight rows
+// g, g + 8 and, since the k order inside a scale group is free, the bytes 8t.. (Q4_K) or 4t.. (Q6_K) of each run,
+// so that shared-memory reads are conflict-free, and the activations are stored in exactly the order the B
+// fragments want (16 bytes per thread and 32 values).  K is cut into as many slices as it takes for a slice of
+// activations to fit and for every SM to get its share of warps; with more than one slice the partial sums go
+// to a workspace and the last warp to arrive at a tile adds them in slice order (deterministic).
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+
+#include "blocks.cuh"
+#include "gemv_common.cuh"
+#include "internal.h"
+
+namespace {
+using namespace fqk;
+
+constexpr int NT_MAX_TARGETS = 4;
+constexpr uint32_t NT_SMEM_MAX = 222 * 1024;
+
+template <int FMT> struct StageNT;
+template <> struct StageNT<FQ_Q4_K> {
+    static constexpr uint32_t ROW = 144, PIECES = 16 * 9, BYTES = 16 * 144;
+};
+template <> struct StageNT<FQ_Q6_K> { // per row ql[128] | qh[64] | scales[16]; then 4 bytes per row holding d
+    static constexpr uint32_t ROW = 208, PIECES = 16 * 13, BYTES = 16 * 208 + 64;
+};
+
+struct NtJob {
+    const uint8_t *w[NT_MAX_TARGETS];
+    float *y[NT_MAX_TARGETS];
+    uint32_t rows[NT_MAX_TARGETS];     // rows of one target (of one expert slice when grouped)
+    uint32_t tile_end[NT_MAX_TARGETS]; // 16-row tiles, counted through the targets
+    uint32_t count;
+    uint32_t pitch, cols, nblk;
+    const float *x, *x_up; // activations; with x_up the gated unit silu(x) * x_up
+    uint32_t m;            // dense: activation rows
+    uint32_t slices;       // dense: K slices
+    uint32_t nb_max;       // superblocks of the longest slice
+    float4 *ws;            // partial sums [tile][slice][lane][NT]
+    uint32_t *counters;    // arrivals per tile
+    // grouped: activation rows [offsets[i], offsets[i + 1]) belong to expert slots ? slots[i] : i
+    const uint32_t *offsets, *slots, *src; // src (may be null): prepared row r is row src[r] / src_div of x
+    uint32_t groups, src_div, total_rows;
+};
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// MMAs whose accumulator starts at zero (the zero register four times: nothing to initialise).
+__device__ __forceinline__ void mma_u8s8_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void mma_s8s8_k16_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+// Resident activations of a block: TOK = 8 NT rows, `nb` superblocks each.
+//   frag [row][nb][8 groups of 32][4 threads][16 bytes]   Q4_K  values 8t .. 8t+7 of the group:  hi[8] | lo[8]
+//                                                         Q6_K  values 4t .. 4t+3 of each half:  hi[4] | lo[4] | hi[4] | lo[4]
+//        (row stride 512 nb + 64, so that the rows g, g + 1 a quarter-warp reads fall on different banks)
+//   sx   [row][nb][3 planes][8] s8   the sums of x' per 32 values as three signed base-256 digits, most
+//                                    significant first: the B operand of the MMA that multiplies them with the
+//                                    eight Q4_K minimums of a superblock (row stride = 2 words mod 32: no conflicts)
+//   inv  [row][nb] f32               1 / s (odd row stride)
+struct ActSmem {
+    uint8_t *frag;
+    uint8_t *sx;
+    float *inv;
+    uint32_t row_stride, sx_stride, inv_stride;
+};
+__host__ __device__ inline uint32_t nt_sx_stride(uint32_t nb) { return 24 * nb + ((8 + 128 - (24 * nb) % 128) % 128); } // bytes
+__host__ __device__ inline uint32_t nt_inv_stride(uint32_t nb) { return nb | 1u; }                                     // floats
+// Bytes of the resident set (a multiple of 16: the warps' rings follow it).
+__host__ __device__ inline uint32_t nt_act_bytes(uint32_t tok, uint32_t nb) {
+    return (tok * (nb * 512 + 64) + tok * nt_sx_stride(nb) + tok * nt_inv_stride(nb) * 4 + 15u) & ~15u;
+}
+
+// One superblock (index `bb` within the block's slice) of a 16-row tile whose packed bytes lie in `stage`,
+// against NT tiles of eight activation rows: adds into yacc[nt][i], i = 2 r + c, the contribution to weight row
+// g + 8 r and activation row 8 nt + 2 t + c.
+template <int FMT, int NT>
+__device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSmem &A, uint32_t bb, bool odd_b, int g, int t, float (&yacc)[NT][4]) {
+    int ah[NT][4], al[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) ah[nt][i] = al[nt][i] = 0;
+    const uint8_t *fragp[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) fragp[nt] = A.frag + (size_t)(8 * nt + g) * A.row_stride + (size_t)bb * 512 + 16 * t;
+    if constexpr (FMT == FQ_Q4_K) {
+        const uint8_t *r0 = stage + g * 144, *r1 = r0 + 8 * 144;
+        // Scales and minimums of sub-blocks 0..3 and 4..7, one per byte (`get_scale_min_k4`).
+        uint32_t sc4[2][2], mn4[2][2];
+        float d[2], dmin[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint4 h = *reinterpret_cast<const uint4 *>(r ? r1 : r0);
+            sc4[r][0] = h.y & 0x3F3F3F3Fu;
+            mn4[r][0] = h.z & 0x3F3F3F3Fu;
+            sc4[r][1] = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+            mn4[r][1] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+            d[r] = f16_bits_to_f32((uint16_t)(h.x & 0xFFFFu));
+            dmin[r] = f16_bits_to_f32((uint16_t)(h.x >> 16));
+        }
+        // The minimum term sum_j m_j * sx_j by three MMAs per tile: A holds the eight minimums of each row on
+        // k slots 0..7 (threads 0 and 1 of a quad), B the digits of the sums.
+        int am[NT][4];
+        {
+            const uint32_t ma0 = t == 0 ? mn4[0][0] : t == 1 ? mn4[0][1] : 0u, ma1 = t == 0 ? mn4[1][0] : t == 1 ? mn4[1][1] : 0u;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const uint8_t *sp = A.sx + (size_t)(8 * nt + g) * A.sx_stride + (size_t)bb * 24 + 4 * (t & 1);
+                int c2[4], c1[4], c0[4];
+                mma_u8s8_z(c2, ma0, ma1, 0u, 0u, *reinterpret_cast<const uint32_t *>(sp), 0u);
+                mma_u8s8_z(c1, ma0, ma1, 0u, 0u, *reinterpret_cast<const uint32_t *>(sp + 8), 0u);
+                mma_u8s8_z(c0, ma0, ma1, 0u, 0u, *reinterpret_cast<const uint32_t *>(sp + 16), 0u);
+#pragma unroll
+                for (int i = 0; i < 4; i++) am[nt][i] = (c2[i] * 256 + c1[i]) * 256 + c0[i];
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const uint2 q0 = *reinterpret_cast<const uint2 *>(r0 + 16 + 32 * c + 8 * t), q1 = *reinterpret_cast<const uint2 *>(r1 + 16 + 32 * c + 8 * t);
+#pragma unroll
+            for (int half = 0; half < 2; half++) { // low nibbles = sub-block 2c, high nibbles = sub-block 2c + 1
+                const int j = 2 * c + half;
+                const uint32_t a0 = (half ? q0.x >> 4 : q0.x) & 0x0F0F0F0Fu, a1 = (half ? q1.x >> 4 : q1.x) & 0x0F0F0F0Fu;
+                const uint32_t a2 = (half ? q0.y >> 4 : q0.y) & 0x0F0F0F0Fu, a3 = (half ? q1.y >> 4 : q1.y) & 0x0F0F0F0Fu;
+                const int s0 = byte_u(sc4[0][j >> 2], j & 3), s1 = byte_u(sc4[1][j >> 2], j & 3);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint4 f = *reinterpret_cast<const uint4 *>(fragp[nt] + 64 * j);
+                    int ch[4], cl[4];
+                    mma_u8s8_z(ch, a0, a1, a2, a3, f.x, f.y);
+                    mma_u8s8_z(cl, a0, a1, a2, a3, f.z, f.w);
+                    ah[nt][0] += s0 * ch[0];
+                    ah[nt][1] += s0 * ch[1];
+                    ah[nt][2] += s1 * ch[2];
+                    ah[nt][3] += s1 * ch[3];
+                    al[nt][0] += s0 * cl[0];
+                    al[nt][1] += s0 * cl[1];
+                    al[nt][2] += s1 * cl[2];
+                    al[nt][3] += s1 * cl[3];
+                }
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float inv = A.inv[(size_t)(8 * nt + 2 * t + (i & 1)) * A.inv_stride + bb];
+                const float dot = fmaf(256.f, (float)ah[nt][i], (float)al[nt][i]);
+                yacc[nt][i] = fmaf(inv, d[i >> 1] * dot - dmin[i >> 1] * (float)am[nt][i], yacc[nt][i]);
+            }
+    } else {
+        const uint8_t *r0 = stage + g * 208, *r1 = r0 + 8 * 208;
+        float d4[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint32_t dd = *reinterpret_cast<const uint32_t *>(stage + 16 * 208 + 4 * (g + 8 * r));
+            d4[r] = f16_bits_to_f32((uint16_t)(odd_b ? dd >> 16 : dd & 0xFFFFu)) * 0.25f;
+        }
+        const uint4 sc0 = *reinterpret_cast<const uint4 *>(r0 + 192), sc1 = *reinterpret_cast<const uint4 *>(r1 + 192);
+#pragma unroll
+        for (int n = 0; n < 2; n++) {
+            uint32_t hw[2][2]; // [row][lh]
+#pragma unroll
+            for (int lh = 0; lh < 2; lh++) {
+                hw[0][lh] = *reinterpret_cast<const uint32_t *>(r0 + 128 + 32 * n + 16 * lh + 4 * t);
+                hw[1][lh] = *reinterpret_cast<const uint32_t *>(r1 + 128 + 32 * n + 16 * lh + 4 * t);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) { // 32 values 128 n + 32 i ..: scale groups 8n + 2i (first 16) and 8n + 2i + 1
+                uint4 f[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) f[nt] = *reinterpret_cast<const uint4 *>(fragp[nt] + 64 * (4 * n + i));
+#pragma unroll
+                for (int lh = 0; lh < 2; lh++) {
+                    uint32_t a[2];
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const uint32_t lw = *reinterpret_cast<const uint32_t *>((r ? r1 : r0) + 64 * n + 32 * (i & 1) + 16 * lh + 4 * t);
+                        const uint32_t lo4 = (i < 2) ? (lw << 2) : (lw >> 2); // the nibble in bits 2..5
+                        const uint32_t h = hw[r][lh];
+                        const uint32_t hi2 = i == 0 ? (h << 6) : i == 1 ? (h << 4) : i == 2 ? (h << 2) : h; // the two high bits in bits 6..7
+                        // ((q ^ 32) << 2) read as s8 = 4 (q - 32)
+                        a[r] = lop3_and_xor(lop3_select(lo4, hi2, 0x3C3C3C3Cu), 0xFCFCFCFCu, 0x80808080u);
+                    }
+                    const int gidx = 8 * n + 2 * i + lh;
+                    const int s0 = byte_s(word_of(sc0, gidx >> 2), gidx & 3), s1 = byte_s(word_of(sc1, gidx >> 2), gidx & 3);
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        int ch[4], cl[4];
+                        mma_s8s8_k16_z(ch, a[0], a[1], lh ? f[nt].z : f[nt].x);
+                        mma_s8s8_k16_z(cl, a[0], a[1], lh ? f[nt].w : f[nt].y);
+                        ah[nt][0] += s0 * ch[0];
+                        ah[nt][1] += s0 * ch[1];
+                        ah[nt][2] += s1 * ch[2];
+                        ah[nt][3] += s1 * ch[3];
+                        al[nt][0] += s0 * cl[0];
+                        al[nt][1] += s0 * cl[1];
+                        al[nt][2] += s1 * cl[2];
+                        al[nt][3] += s1 * cl[3];
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float inv = A.inv[(size_t)(8 * nt + 2 * t + (i & 1)) * A.inv_stride + bb];
+                yacc[nt][i] = fmaf(inv * d4[i >> 1], fmaf(256.f, (float)ah[nt][i], (float)al[nt][i]), yacc[nt][i]);
+            }
+    }
+}
+
+// Quantises the eight values (v0, v1) of this lane -- values 8 lane .. of one superblock of one activation row,
+// with `gated` the gated unit silu(v) * u -- into slot (tok, bb) of the resident set; one warp.  !have: zeros.
+template <int FMT>
+__device__ __forceinline__ void prep_resident(const ActSmem &A, uint32_t tok, uint32_t bb, bool have, bool gated, const float4 &v0, const float4 &v1,
+                                              const float4 &u0, const float4 &u1, uint32_t lane) {
+    uint8_t *frag = A.frag + (size_t)tok * A.row_stride + (size_t)bb * 512;
+    uint8_t *sxp = A.sx + (size_t)tok * A.sx_stride + (size_t)bb * 24;
+    float *invp = A.inv + (size_t)tok * A.inv_stride + bb;
+    if (!have) {
+        *reinterpret_cast<uint4 *>(frag + 16 * lane) = make_uint4(0u, 0u, 0u, 0u);
+        if (lane < 6) reinterpret_cast<uint32_t *>(sxp)[lane] = 0u;
+        if (lane == 0) *invp = 0.f;
+        return;
+    }
+    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    if (gated) {
+        const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v[i] / (1.f + expf(-v[i])) * u[i];
+    }
+    const Quant8 q = quantize8(v);
+    if constexpr (FMT == FQ_Q4_K) {
+        // 32-value group lane / 4, thread lane % 4
+        *reinterpret_cast<uint4 *>(frag + 16 * lane) = make_uint4(pack4(q.hi), pack4(q.hi + 4), pack4(q.lo), pack4(q.lo + 4));
+    } else {
+        // The lane's values sit in half (lane % 4) / 2 of the group; its first four belong to thread
+        // 2 (lane % 2), the other four to the thread after it.
+        uint8_t *dst = frag + 64 * (lane >> 2) + 8 * ((lane & 3) >> 1) + 32 * (lane & 1);
+        *reinterpret_cast<uint2 *>(dst) = make_uint2(pack4(q.hi), pack4(q.lo));
+        *reinterpret_cast<uint2 *>(dst + 16) = make_uint2(pack4(q.hi + 4), pack4(q.lo + 4));
+    }
+    int sum = q.sum;
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if ((lane & 3) == 0) { // three signed base-256 digits of the sum
+        const int p0 = ((sum + 128) & 0xFF) - 128, rem = (sum - p0) >> 8, p1 = ((rem + 128) & 0xFF) - 128, p2 = (rem - p1) >> 8;
+        sxp[lane >> 2] = (uint8_t)p2;
+        sxp[8 + (lane >> 2)] = (uint8_t)p1;
+        sxp[16 + (lane >> 2)] = (uint8_t)p0;
+    }
+    // A non-finite activation anywhere in the superblock makes its factor NaN.
+    if (lane == 0) *invp = q.finite ? ldexpf(1.f, -q.e) : __int_as_float(0x7fc00000);
+}
+
+// FMT: FQ_Q4_K / FQ_Q6_K; NT: tiles of eight activation rows; STAGES: superblocks in flight per warp;
+// GROUPED: block = (expert, tile of 8 NT expert-sorted rows), else block = (K slice, share of the row tiles).
+template <int FMT, int NT, int STAGES, bool GROUPED>
+__global__ void __launch_bounds__(512, 1)
+k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
+    using St = StageNT<FMT>;
+    constexpr uint32_t TOK = 8 * NT;
+    extern __shared__ __align__(128) uint8_t nt_smem[];
+    __shared__ uint32_t job_group, job_row0, job_cnt;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+
+    // The block's job.
+    uint32_t b0 = 0, nb = J.nblk, slice = 0, first, stride, m = J.m, xrow0 = 0;
+    size_t expert_off = 0; // rows to skip in every target
+    if constexpr (GROUPED) {
+        pdl_wait(); // the routing map is the output of an earlier kernel of the stream
+        if (warp == 0) {
+            // Tile blockIdx.x of all groups' row tiles, counted through the groups (32 at a time).
+            uint32_t base = 0, found = 0xffffffffu, row0 = 0, cnt = 0;
+            for (uint32_t g0 = 0; g0 < J.groups && found == 0xffffffffu; g0 += 32) {
+                const uint32_t gi = g0 + lane;
+                const uint32_t lo = gi < J.groups ? J.offsets[gi] : 0, hi = gi < J.groups ? J.offsets[gi + 1] : 0;
+                const uint32_t n = hi > lo ? (hi - lo + TOK - 1) / TOK : 0;
+                uint32_t incl = n;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if ((int)lane >= o) incl += v;
+                }
+                const uint32_t excl = base + incl - n;
+                const bool mine = blockIdx.x >= excl && blockIdx.x < excl + n;
+                const uint32_t who = __ballot_sync(0xffffffffu, mine);
+                if (who) {
+                    const int src_lane = __ffs(who) - 1;
+                    found = g0 + src_lane;
+                    const uint32_t tile_in = blockIdx.x - __shfl_sync(0xffffffffu, excl, src_lane);
+                    const uint32_t glo = __shfl_sync(0xffffffffu, lo, src_lane), ghi = __shfl_sync(0xffffffffu, hi, src_lane);
+                    row0 = glo + tile_in * TOK;
+                    cnt = min(TOK, ghi - row0);
+                }
+                base += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) {
+                job_group = found;
+                job_row0 = row0;
+                job_cnt = cnt;
+            }
+        }
+        __syncthreads();
+        if (job_group == 0xffffffffu) return; // more blocks than tiles
+        const uint32_t e = J.slots ? J.slots[job_group] : job_group;
+        expert_off = (size_t)e * J.rows[0];
+        m = job_cnt;
+        xrow0 = job_row0;
+        first = warp;
+        stride = W;
+    } else {
+        slice = blockIdx.x % J.slices;
+        b0 = (uint32_t)((uint64_t)slice * J.nblk / J.slices);
+        nb = (uint32_t)((uint64_t)(slice + 1) * J.nblk / J.slices) - b0;
+        first = (blockIdx.x / J.slices) * W + warp;
+        stride = (gridDim.x / J.slices) * W;
+    }
+    const uint32_t total_tiles = J.tile_end[J.count - 1];
+
+    ActSmem A;
+    A.row_stride = J.nb_max * 512 + 64;
+    A.sx_stride = nt_sx_stride(J.nb_max);
+    A.inv_stride = nt_inv_stride(J.nb_max);
+    A.frag = nt_smem;
+    A.sx = nt_smem + (size_t)TOK * A.row_stride;
+    A.inv = reinterpret_cast<float *>(A.sx + (size_t)TOK * A.sx_stride);
+    uint8_t *ring = nt_smem + nt_act_bytes(TOK, J.nb_max) + (size_t)warp * STAGES * St::BYTES;
+
+    struct Tile {
+        const uint8_t *w; // first row of the target (of the expert's slice of it)
+        float *y;
+        uint32_t rows, row0;
+    };
+    auto tile_at = [&](uint32_t tile) {
+        uint32_t which = 0, first_tile = 0;
+#pragma unroll
+        for (int i = 0; i < NT_MAX_TARGETS - 1; i++)
+            if ((uint32_t)i + 1 < J.count && tile >= J.tile_end[i]) { which = i + 1; first_tile = J.tile_end[i]; }
+        Tile q;
+        q.rows = J.rows[which];
+        q.row0 = (tile - first_tile) * 16;
+        q.w = J.w[which] + expert_off * J.pitch; // grouped targets share one shape
+        q.y = J.y[which];
+        return q;
+    };
+
+    // Producer side of the warp's ring: item = (tile, superblock of the slice), in the order they are consumed.
+    // A lane copies the same 16-byte pieces of every item, so their offsets from the tile's first row are
+    // worked out once per tile.  Q4_K: piece p = lane + 32 i is bytes 16 (p % 9) .. of row p / 9.  Q6_K: pieces
+    // 0..127 are ql (row p / 8), 128..191 qh (row / 4), 192..207 the scales, 208..223 the 4 bytes holding d.
+    constexpr int NP = FMT == FQ_Q4_K ? 5 : 7;
+    uint32_t p_tile = first, p_bb = 0, p_stage = 0;
+    const uint8_t *p_base = nullptr;
+    uint32_t p_off[NP];
+    auto piece_row = [&](int i) -> uint32_t {
+        const uint32_t p = lane + 32 * i;
+        if constexpr (FMT == FQ_Q4_K) return p / 9;
+        return i < 4 ? p / 8 : i < 6 ? (p - 128) / 4 : (lane & 15);
+    };
+    auto start_tile = [&](uint32_t tile) {
+        const Tile q = tile_at(tile);
+        p_base = q.w + (size_t)q.row0 * J.pitch;
+        const uint32_t last = q.rows - 1 - q.row0; // rows past the end of the target read its last row
+#pragma unroll
+        for (int i = 0; i < NP; i++) {
+            const uint32_t p = lane + 32 * i, r = min(piece_row(i), last);
+            uint32_t in_row;
+            if constexpr (FMT == FQ_Q4_K) in_row = 16 * (p % 9);
+            else in_row = i < 4 ? 16 * (p % 8) : i < 6 ? J.nblk * 128 + 16 * (p % 4) : lane < 16 ? J.nblk * 192 : J.nblk * 208;
+            p_off[i] = r * J.pitch + in_row;
+        }
+    };
+    if (p_tile < total_tiles) start_tile(p_tile);
+    auto issue = [&]() {
+        if (p_tile < total_tiles) {
+            uint8_t *dst = ring + (size_t)p_stage * St::BYTES;
+            const uint32_t b = b0 + p_bb;
+#pragma unroll
+            for (int i = 0; i < NP; i++) {
+                const uint32_t p = lane + 32 * i;
+                if constexpr (FMT == FQ_Q4_K) {
+                    if (p < St::PIECES) cp_async16(dst + 16 * p, p_base + (p_off[i] + b * 144));
+                } else {
+                    if (i < 4) cp_async16(dst + 208 * (p / 8) + 16 * (p % 8), p_base + (p_off[i] + b * 128));
+                    else if (i < 6) cp_async16(dst + 208 * ((p - 128) / 4) + 128 + 16 * (p % 4), p_base + (p_off[i] + b * 64));
+                    else if (lane < 16) cp_async16(dst + 208 * lane + 192, p_base + (p_off[i] + b * 16));
+                    else cp_async4(dst + 16 * 208 + 4 * (lane - 16), p_base + (p_off[i] + (b & ~1u) * 2)); // the aligned 4 bytes that hold d
+                }
+            }
+            if (++p_bb == nb) {
+                p_bb = 0;
+                p_tile += stride;
+                if (p_tile < total_tiles) start_tile(p_tile);
+            }
+        }
+        cp_async_commit();
+        p_stage = p_stage + 1 == STAGES ? 0 : p_stage + 1;
+    };
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; i++) issue();
+    // The copies above read immutable weights only; the rest reads activations and writes y.
+    pdl_trigger();
+    if constexpr (!GROUPED) pdl_wait();
+    const uint32_t seq = P.world > 1 ? tp_seq(P) : 0u;
+
+    // The block's resident activations: warp-tasks (row, superblock), two in flight per warp.
+    {
+        const uint32_t tasks = TOK * nb;
+        auto fetch = [&](uint32_t i, bool &have, float4 &v0, float4 &v1, float4 &u0, float4 &u1) {
+            const uint32_t tok = i / nb, bb = i - tok * nb;
+            have = i < tasks && tok < m;
+            if (!have) return;
+            size_t r = xrow0 + tok;
+            if (GROUPED && J.src) r = J.src[r] / J.src_div;
+            const float4 *sp = reinterpret_cast<const float4 *>(J.x + r * J.cols + (size_t)(b0 + bb) * 256 + lane * 8);
+            v0 = sp[0];
+            v1 = sp[1];
+            if (J.x_up) {
+                const float4 *up = reinterpret_cast<const float4 *>(J.x_up + r * J.cols + (size_t)(b0 + bb) * 256 + lane * 8);
+                u0 = up[0];
+                u1 = up[1];
+            }
+        };
+        const bool gated = J.x_up != nullptr;
+        for (uint32_t i = warp; i < tasks; i += 2 * W) {
+            bool have_a, have_b;
+            float4 a0, a1, au0, au1, c0, c1, cu0, cu1;
+            a0 = a1 = au0 = au1 = c0 = c1 = cu0 = cu1 = make_float4(0.f, 0.f, 0.f, 0.f);
+            fetch(i, have_a, a0, a1, au0, au1);
+            fetch(i + W, have_b, c0, c1, cu0, cu1);
+            prep_resident<FMT>(A, i / nb, i % nb, have_a, gated, a0, a1, au0, au1, lane);
+            if (i + W < tasks) prep_resident<FMT>(A, (i + W) / nb, (i + W) % nb, have_b, gated, c0, c1, cu0, cu1, lane);
+        }
+    }
+    __syncthreads();
+
+    uint32_t c_stage = 0;
+    for (uint32_t tile = first; tile < total_tiles; tile += stride) {
+        const Tile here = tile_at(tile);
+        float yacc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) yacc[nt][i] = 0.f;
+        for (uint32_t bb = 0; bb < nb; bb++) {
+            issue();
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+            superblock_nt<FMT, NT>(ring + (size_t)c_stage * St::BYTES, A, bb, ((b0 + bb) & 1u) != 0, g, t, yacc);
+            __syncwarp();
+            c_stage = c_stage + 1 == STAGES ? 0 : c_stage + 1;
+        }
+        bool store = true;
+        if (!GROUPED && J.slices > 1) {
+            // Partial sums of this slice; the last warp to arrive at the tile adds all slices in slice order.
+            float4 *part = J.ws + ((size_t)tile * J.slices) * 32 * NT;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) part[((size_t)slice * 32 + lane) * NT + nt] = make_float4(yacc[nt][0], yacc[nt][1], yacc[nt][2], yacc[nt][3]);
+            __threadfence();
+            __syncwarp();
+            uint32_t arrived = 0;
+            if (lane == 0) arrived = atomicAdd(J.counters + tile, 1u);
+            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+            store = arrived + 1 == J.slices;
+            if (store) {
+                __threadfence();
+                if (lane == 0) J.counters[tile] = 0;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (uint32_t s = 0; s < J.slices; s++) {
+                        const float4 p = __ldcg(&part[((size_t)s * 32 + lane) * NT + nt]);
+                        acc.x += p.x;
+                        acc.y += p.y;
+                        acc.z += p.z;
+                        acc.w += p.w;
+                    }
+                    yacc[nt][0] = acc.x;
+                    yacc[nt][1] = acc.y;
+                    yacc[nt][2] = acc.z;
+                    yacc[nt][3] = acc.w;
+                }
+            }
+        }
+        if (store) {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t row = here.row0 + g + (i >> 1) * 8, tok = 8 * nt + 2 * t + (i & 1);
+                    if (row < here.rows && tok < m) {
+                        float *dst = &here.y[(size_t)(xrow0 + tok) * here.rows + row];
+                        *dst = yacc[nt][i];
+                        if (!GROUPED && P.world > 1) tp_store(P, seq, dst, yacc[nt][i]);
+                    }
+                }
+        }
+    }
+    cp_async_wait<0>();
+    if (!GROUPED && P.world > 1) tp_finish(P, seq);
+}
+
+struct NtShape {
+    uint32_t warps, stages, slices, nb_max, smem, grid;
+};
+
+template <int FMT, int NT, bool GROUPED> void (*nt_kernel(int stages))(NtJob, TpPush) {
+    return stages >= 4 ? k_nt<FMT, NT, 4, GROUPED> : stages == 3 ? k_nt<FMT, NT, 3, GROUPED> : k_nt<FMT, NT, 2, GROUPED>;
+}
+
+// Chooses warps per block, ring depth and K slices for `tiles16` 16-row tiles of `nblk` superblocks.
+template <int FMT, int NT> bool nt_shape(const fq_device *dev, uint32_t tiles16, uint32_t nblk, bool grouped, NtShape &S) {
+    using St = StageNT<FMT>;
+    constexpr uint32_t TOK = 8 * NT;
+    S.warps = 16;
+    // Fewest slices: a slice of activations must fit beside a ring of two stages per warp.
+    const uint32_t ring2 = S.warps * 2 * St::BYTES;
+    uint32_t nb_fit = 0;
+    while (nb_fit < nblk && nt_act_bytes(TOK, nb_fit + 1) + ring2 <= NT_SMEM_MAX) nb_fit++;
+    if (nb_fit == 0) return false;
+    uint32_t slices = (nblk + nb_fit - 1) / nb_fit;
+    if (grouped) {
+        if (slices > 1) return false; // an expert's whole K is resident
+    } else {
+        // More slices give more warps a tile when rows are few, at the price of a shorter run per tile with a fixed
+        // cost per run (and, beyond one slice, the partial sums).  Estimated time in units of one superblock of
+        // one tile: rounds of tiles per warp x (superblocks per slice + overhead) + the block's preparation.
+        const uint32_t sms = (uint32_t)dev->sm_count;
+        double best = 1e30;
+        uint32_t pick = slices;
+        for (uint32_t s = slices; s <= std::min(nblk, sms); s++) {
+            const uint32_t per_slice = (sms / s) * S.warps, nbm = (nblk + s - 1) / s;
+            const uint32_t rounds = (tiles16 + per_slice - 1) / per_slice;
+            const double cost = rounds * (nbm + (s > 1 ? 1.5 : 0.3)) + 0.25 * nbm * TOK / 16.0;
+            if (cost < best - 1e-9) { best = cost; pick = s; }
+        }
+        slices = pick;
+    }
+    S.slices = slices;
+    S.nb_max = (nblk + slices - 1) / slices;
+    const size_t act = nt_act_bytes(TOK, S.nb_max);
+    S.stages = (uint32_t)std::min<size_t>(4, (NT_SMEM_MAX - act) / ((size_t)S.warps * St::BYTES));
+    if (S.stages < 2) return false;
+    S.smem = (uint32_t)(act + (size_t)S.warps * S.stages * St::BYTES);
+    S.grid = grouped ? 0 : std::max(1u, (uint32_t)dev->sm_count / slices) * slices;
+    return true;
+}
+
+template <int FMT, int NT, bool GROUPED> cudaError_t nt_launch(fq_device *dev, const NtJob &J, const NtShape &S, uint32_t grid, const TpPush &push) {
+    auto kernel = nt_kernel<FMT, NT, GROUPED>((int)S.stages);
+    static bool configured[5] = {};
+    if (!configured[S.stages]) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NT_SMEM_MAX);
+        if (e != cudaSuccess) return e;
+        configured[S.stages] = true;
+    }
+    return launch_pdl(kernel, dim3(grid), dim3(S.warps * 32), S.smem, dev->stream, J, push);
+}
+
+template <int FMT, int NT> int launch_dense(fq_device *dev, const ProjectArgs *a, uint32_t count) {
+    NtJob J{};
+    J.count = count;
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        J.w[i] = a[i].w;
+        J.y[i] = (float *)a[i].y;
+        J.rows[i] = a[i].rows;
+        tiles += (a[i].rows + 15) / 16;
+        J.tile_end[i] = tiles;
+    }
+    J.pitch = a[0].row_bytes;
+    J.cols = a[0].cols;
+    J.nblk = a[0].cols / 256;
+    J.x = (const float *)a[0].x;
+    J.x_up = a[0].x_up;
+    J.m = a[0].m;
+    NtShape S;
+    if (!nt_shape<FMT, NT>(dev, tiles, J.nblk, false, S)) return FQ_ERR_UNSUPPORTED;
+    J.slices = S.slices;
+    J.nb_max = S.nb_max;
+    J.ws = (float4 *)dev->nt_ws;
+    J.counters = dev->nt_counters;
+    if (S.slices > 1 && ((size_t)tiles * S.slices * 32 * NT * sizeof(float4) > dev->nt_ws_bytes || tiles > dev->nt_counter_count))
+        return FQ_ERR_UNSUPPORTED;
+    TpPush push{};
+    if (dev->tp_push) { // one launch covers every target: it can do the exchange itself
+        push = *dev->tp_push;
+        dev->tp_push = nullptr;
+        dev->tp_pushed = true;
+    }
+    if (int rc = fq_check_cuda(dev, nt_launch<FMT, NT, false>(dev, J, S, S.grid, push), "gemv launch")) return rc;
+    return fq_end_enqueue(dev, "gemv_nt", 1);
+}
+
+} // namespace
+
+// `a[0..count)` share x, m (2..16), format and width.
+int fq_launch_gemv_nt_many(fq_device *dev, const ProjectArgs *a, uint32_t count) {
+    if (count == 0 || count > (uint32_t)NT_MAX_TARGETS) return FQ_ERR_UNSUPPORTED;
+    const ProjectArgs &f = a[0];
+    if ((f.format != FQ_Q4_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
+    if (f.cols % 256 || f.row_bytes % 16 || f.ids || f.m < 2 || f.m > 16) return FQ_ERR_UNSUPPORTED;
+    for (uint32_t i = 1; i < count; i++)
+        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].m != f.m || a[i].ids ||
+            a[i].x_dtype != FQ_F32 || a[i].y_dtype != FQ_F32)
+            return FQ_ERR_UNSUPPORTED;
+    if (f.format == FQ_Q4_K) return f.m <= 8 ? launch_dense<FQ_Q4_K, 1>(dev, a, count) : launch_dense<FQ_Q4_K, 2>(dev, a, count);
+    return f.m <= 8 ? launch_dense<FQ_Q6_K, 1>(dev, a, count) : launch_dense<FQ_Q6_K, 2>(dev, a, count);
+}
+
+// Grouped expert projection over expert-sorted rows (F32 in, F32 out), up to two expert stacks of one shape
+// sharing the rows (gate and up).  `src` (may be null): row r of the sorted set is row src[r] / src_div of x, so
+// the gather needs no pass of its own; `a[0].x_up`: the activations are the gated unit silu(x) * x_up.
+int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t count, uint32_t total_rows, const uint32_t *src, uint32_t src_div) {
+    if (count == 0 || count > 2) return FQ_ERR_UNSUPPORTED;
+    const ProjectArgs &f = a[0];
+    if ((f.format != FQ_Q4_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
+    if (f.cols % 256 || f.row_bytes % 16 || !f.offsets || f.groups == 0 || total_rows == 0) return FQ_ERR_UNSUPPORTED;
+    for (uint32_t i = 1; i < count; i++)
+        if (a[i].format != f.format || a[i].cols != f.cols || a[i].rows != f.rows || a[i].x != f.x || a[i].offsets != f.offsets ||
+            a[i].slots != f.slots || a[i].groups != f.groups || a[i].experts != f.experts)
+            return FQ_ERR_UNSUPPORTED;
+    NtJob J{};
+    J.count = count;
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        J.w[i] = a[i].w;
+        J.y[i] = (float *)a[i].y;
+        J.rows[i] = a[i].rows;
+        tiles += (a[i].rows + 15) / 16;
+        J.tile_end[i] = tiles;
+    }
+    J.pitch = f.row_bytes;
+    J.cols = f.cols;
+    J.nblk = f.cols / 256;
+    J.x = (const float *)f.x;
+    J.x_up = f.x_up;
+    J.slices = 1;
+    J.offsets = f.offsets;
+    J.slots = f.slots;
+    J.src = src;
+    J.src_div = src_div ? src_div : 1;
+    J.groups = f.groups;
+    J.total_rows = total_rows;
+    NtShape S;
+    const bool q4 = f.format == FQ_Q4_K;
+    if (!(q4 ? nt_shape<FQ_Q4_K, 2>(dev, tiles, J.nblk, true, S) : nt_shape<FQ_Q6_K, 2>(dev, tiles, J.nblk, true, S))) return FQ_ERR_UNSUPPORTED;
+    J.nb_max = S.nb_max;
+    // Every group has at most ceil(rows / 16) <= rows / 16 + 1 tiles of sixteen rows.
+    const uint32_t grid = total_rows / 16 + f.groups;
+    const cudaError_t e = q4 ? nt_launch<FQ_Q4_K, 2, true>(dev, J, S, grid, TpPush{}) : nt_launch<FQ_Q6_K, 2, true>(dev, J, S, grid, TpPush{});
+    if (int rc = fq_check_cuda(dev, e, "grouped gemv launch")) return rc;
+    return fq_end_enqueue(dev, "gemv_nt_grouped", 1);
+}

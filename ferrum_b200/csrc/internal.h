@@ -37,6 +37,9 @@ struct fq_device {
     const struct TpPush *tp_push = nullptr; // set while a projection that exchanges its own output is enqueued
     bool tp_pushed = false;                 // the kernel that was launched took tp_push
     uint64_t captured_kernels = 0;
+    // Exchanges recorded by the open capture: their communicator, and the first and the last region.
+    struct fq_comm *cap_comm = nullptr;
+    size_t cap_first_off = 0, cap_first_bytes = 0, cap_last_off = 0, cap_last_bytes = 0;
     std::map<uintptr_t, size_t> allocations; // buffers handed out by fq_buffer_alloc
     // Fixed scratch, allocated once at creation.
     void *xprep = nullptr;        // prepared activations of the tensor-core GEMV
@@ -44,6 +47,12 @@ struct fq_device {
     uint32_t xprep_turn = 0;      // successive projections alternate between the two halves of xprep
     void *staging_dev = nullptr;  // device side of the host-buffer entry points
     void *staging_host = nullptr; // pinned host side
+    // K-slice workspace of the verify-width GEMV (partial sums and one arrival counter per 16-row tile); the side
+    // stream has its own.
+    void *nt_ws = nullptr, *side_nt_ws = nullptr;
+    size_t nt_ws_bytes = 0, side_nt_ws_bytes = 0;
+    uint32_t *nt_counters = nullptr, *side_nt_counters = nullptr;
+    uint32_t nt_counter_count = 0, side_nt_counter_count = 0;
     // Split-K workspace of the prefill GEMM: partial fp32 tiles and one arrival counter per tile.
     float *gemm_ws = nullptr;
     size_t gemm_ws_bytes = 0;
@@ -57,6 +66,8 @@ struct fq_graph {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     uint64_t kernels = 0;
+    struct fq_comm *comm = nullptr; // set when the graph holds exchanges
+    size_t first_off = 0, first_bytes = 0, last_off = 0, last_bytes = 0;
 };
 
 struct fq_matrix {
@@ -104,15 +115,18 @@ int fq_launch_project_id_exact(fq_device *dev, const ProjectArgs &a);
 int fq_launch_project_grouped_exact(fq_device *dev, const ProjectArgs &a);
 int fq_launch_get_rows(fq_device *dev, const fq_matrix *w, const uint32_t *ids, uint32_t tokens,
                        void *y, int y_dtype);
-// Tensor-core decode/verify GEMV (M <= FQ_GEMV_MAX_M, F32 in/out); returns FQ_ERR_UNSUPPORTED
-// when the shape has no fast kernel so the caller can fall back to the exact one.
-int fq_launch_gemv_fast(fq_device *dev, const ProjectArgs &a);
-// Several matrices of one format and width sharing x and m in one launch (same fallback contract).
-int fq_launch_gemv_fast_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
-size_t fq_gemv_scratch_bytes();
-// Integer tensor-core decode GEMV for 1..4 activation rows and for per-route expert projections
-// (same fallback contract).
+// Bytes of the per-handle activation scratch (two halves used alternately).
+constexpr size_t FQ_GEMV_SCRATCH_BYTES = (size_t)96 << 20;
+// Kernel launchers return FQ_ERR_UNSUPPORTED when the shape has no fast kernel, so that the caller can fall
+// back to the exact one.
+// Integer tensor-core decode GEMV for one activation row and for per-route expert projections; several
+// matrices of one format and width sharing x in one launch.
 int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
+// The same for 2..16 activation rows (activation rows on the MMA's N side).
+int fq_launch_gemv_nt_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
+// Grouped expert projection over expert-sorted rows (a[i].offsets / slots / groups) for one or two expert stacks
+// of one shape (F32 in and out); row r of the sorted set is row src[r] / src_div of x (src null: row r).
+int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t count, uint32_t total_rows, const uint32_t *src, uint32_t src_div);
 // tcgen05 dequant-GEMM (BF16 in/out); same fallback contract.
 // Q8_0 integer-dot GEMV (M <= FQ_GEMV_MAX_M, F32 in/out, no routes); FQ_ERR_UNSUPPORTED otherwise.
 int fq_launch_gemv_q8(fq_device *dev, const ProjectArgs &a);
@@ -143,17 +157,25 @@ int fq_launch_moe_local_ids(fq_device *dev, const uint32_t *ids, const uint32_t 
 // repeats for a slot), so a captured graph can replay the exchange.  world <= 1 turns it off.
 struct TpPush {
     uint8_t *peer[8];    // symmetric buffers by rank (peer[rank] is the local one)
-    uint32_t world, rank, slot, mode; // mode: 1 send | 2 receive (3 = both; anything else is for measurements)
+    uint32_t world, rank, slot, pad;
     uint32_t *epoch;     // local: number of fused exchanges this communicator has completed (the same on every rank)
     uint32_t *counter;   // local: blocks of this launch that have finished
     size_t mirror_off;   // the mirror starts here in every buffer: payload float at byte o <-> slot at mirror_off + 2 o
     size_t slice_off, slice_bytes; // this rank's slice of the gathered region; rank p's is (p - rank) slices away
+    size_t covered_bytes;          // leading bytes of every slice that the projection outputs fill (the rest is padding)
+    uint64_t wait_ns;              // wall-time limit of a block's wait for incoming values
     int *status;
 };
 struct fq_comm;
 // Fills `out` for the next exchange of `c` (takes a flag slot); FQ_ERR_RANGE unless [y, y + bytes) lies in
 // the local symmetric buffer.
 int fq_comm_begin_push(fq_comm *c, const void *y, size_t bytes, TpPush *out);
+// Bookkeeping of exchange regions (consecutive exchanges must use disjoint regions): before every exchange is
+// enqueued, and before a graph that holds exchanges is replayed.  FQ_ERR_PARAM on a reuse.
+int fq_comm_note_region(fq_device *dev, fq_comm *c, size_t off, size_t bytes);
+int fq_comm_note_graph(fq_device *dev, const struct fq_graph *g);
+fq_device *fq_comm_device(const fq_comm *c);
+int fq_comm_all_gather_unchecked(fq_device *dev, fq_comm *c, size_t region_offset, size_t shard_bytes);
 // The symmetric buffer of a communicator and its geometry (comm.cu).
 struct fq_comm;
 uint8_t *fq_comm_local(fq_comm *c);

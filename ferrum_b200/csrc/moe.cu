@@ -40,7 +40,7 @@ __device__ __forceinline__ float block_max(float v, float *scratch) {
 __global__ void __launch_bounds__(ROUTE_THREADS)
 k_moe_route(const float *__restrict__ logits, const float *__restrict__ x, const float *__restrict__ shared_w,
             uint32_t experts, uint32_t used, uint32_t hidden, int sigmoid, int norm, int shared_gate,
-            uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate) {
+            uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate, int *status) {
     __shared__ float prob[MAX_EXPERTS];
     __shared__ float scratch[ROUTE_THREADS / 32];
     __shared__ float best_v[ROUTE_THREADS / 32];
@@ -48,6 +48,24 @@ k_moe_route(const float *__restrict__ logits, const float *__restrict__ x, const
     __shared__ float picked[64];
     const uint32_t t = blockIdx.x, tid = threadIdx.x;
     const float *row = logits + (size_t)t * experts;
+    // A NaN or an infinity among the logits has no ranking (the reference's router refuses such a row:
+    // "router produced invalid logits", src/nn/moe.rs:392-397): report it through the status word, give the token
+    // the first `used` experts with weight zero so that everything downstream stays in range, and stop.
+    {
+        int bad = 0;
+        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) bad |= !(fabsf(row[e]) < INFINITY);
+        if (__syncthreads_or(bad)) {
+            if (tid == 0) {
+                *(volatile int *)status = (int)FQ_ERR_WEIGHT;
+                gate[t] = 0.f;
+            }
+            for (uint32_t k = tid; k < used; k += ROUTE_THREADS) {
+                ids[(size_t)t * used + k] = k;
+                weights[(size_t)t * used + k] = 0.f;
+            }
+            return;
+        }
+    }
     if (sigmoid) {
         for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) prob[e] = 1.f / (1.f + expf(-row[e]));
     } else {
@@ -153,7 +171,10 @@ k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, u
             }
             carry += __shfl_sync(0xffffffffu, incl, 31);
         }
-        if (lane == 0) offsets[experts] = carry;
+        if (lane == 0) {
+            offsets[experts] = carry;
+            total[experts] = carry;
+        }
     }
     __syncthreads();
     for (uint32_t e = tid; e < experts; e += 1024) {
@@ -175,11 +196,15 @@ k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, u
             const uint32_t at = cnt[warp * experts + e] + rank;
             sorted[at] = r;
             position[r] = at;
+        } else if (live) {
+            position[r] = 0; // an id that names no expert: the route belongs to no row
         }
         __syncwarp();
         if (live && e < experts && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
         __syncwarp();
     }
+    // Rows past the last expert's (only there when some id named no expert) point at route 0.
+    for (uint32_t i = total[experts] + tid; i < routes; i += 1024) sorted[i] = 0;
 }
 
 // xg[row] = x[sorted[row] / used]
@@ -303,7 +328,7 @@ extern "C" int fq_moe_route(fq_device *dev, const float *logits, const float *x,
     if (int rc = fq_check_no_alias(dev, ids, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "ids")) return rc;
     if (int rc = fq_check_no_alias(dev, weights, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "weights")) return rc;
     k_moe_route<<<tokens, ROUTE_THREADS, 0, dev->stream>>>(logits, x, shared_w, experts, used, hidden, sigmoid, norm,
-                                                           shared_gate, ids, weights, gate);
+                                                           shared_gate, ids, weights, gate, dev->status_dev);
     return fq_end_enqueue(dev, "moe_route", 1);
 }
 
