@@ -84,6 +84,8 @@ SIGNATURES = {
     "fq_comm_all_gather": (_I, [_P, _P, _Z, _Z]),
     "fq_comm_all_gather_rows": (_I, [_P, _P, _Z, _Z, _P, _U32, _Z]),
     "fq_comm_destroy": (_I, [_P]),
+    "fq_comm_set_wait_ns": (_I, [_P, _U64]),
+    "fq_comm_open_local": (_I, [_P]),
     "fq_project_many_gather": (_I, [_P, _P, _Z, _Z, C.POINTER(_P), _Z, _P, _I, _Z, _Z, C.POINTER(_P), _I]),
     "fq_moe_ffn_ep": (_I, [_P, _P, _Z, C.POINTER(MoeFfnDesc), _U32, _P, _Z, _P, _Z, _P]),
     "fq_gemv_q4k_static": (_I, [_P, _U64, _U64, _P, _U32, _P, _P, C.c_char_p, _Z]),

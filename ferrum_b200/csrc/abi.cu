@@ -768,7 +768,7 @@ static int project_gated(fq_device *dev, const fq_matrix *w, const float *g, con
         } else {
             a.rows = (uint32_t)w->rows;
         }
-        const int rc = fq_launch_gemv_i8_many(dev, &a, 1);
+        const int rc = (ids || rows_x == 1) ? fq_launch_gemv_i8_many(dev, &a, 1) : fq_launch_gemv_nt_many(dev, &a, 1);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
     if (int rc = fq_glu(dev, g, u, rows_x * width, act)) return rc;

@@ -56,15 +56,15 @@ struct NtJob {
     uint32_t tile_end[NT_MAX_TARGETS]; // 16-row tiles, counted through the targets
     uint32_t count;
     uint32_t pitch, cols, nblk;
-    const float *x, *x_up; // activations; with x_up the gated unit silu(x) * x_up
+    const uint8_t *prep;   // prepared activations (k_prep_nt), row r at r * 544 nblk
     uint32_t m;            // dense: activation rows
     uint32_t slices;       // dense: K slices
     uint32_t nb_max;       // superblocks of the longest slice
     float4 *ws;            // partial sums [tile][slice][lane][NT]
     uint32_t *counters;    // arrivals per tile
     // grouped: activation rows [offsets[i], offsets[i + 1]) belong to expert slots ? slots[i] : i
-    const uint32_t *offsets, *slots, *src; // src (may be null): prepared row r is row src[r] / src_div of x
-    uint32_t groups, src_div, total_rows;
+    const uint32_t *offsets, *slots;
+    uint32_t groups, total_rows;
 };
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *src) {
@@ -88,25 +88,90 @@ __device__ __forceinline__ void mma_s8s8_k16_z(int (&c)[4], uint32_t a0, uint32_
                  : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
 
-// Resident activations of a block: TOK = 8 NT rows, `nb` superblocks each.
-//   frag [row][nb][8 groups of 32][4 threads][16 bytes]   Q4_K  values 8t .. 8t+7 of the group:  hi[8] | lo[8]
-//                                                         Q6_K  values 4t .. 4t+3 of each half:  hi[4] | lo[4] | hi[4] | lo[4]
-//        (row stride 512 nb + 64, so that the rows g, g + 1 a quarter-warp reads fall on different banks)
-//   sx   [row][nb][3 planes][8] s8   the sums of x' per 32 values as three signed base-256 digits, most
-//                                    significant first: the B operand of the MMA that multiplies them with the
-//                                    eight Q4_K minimums of a superblock (row stride = 2 words mod 32: no conflicts)
-//   inv  [row][nb] f32               1 / s (odd row stride)
+// Prepared activations.  In global memory (written once per projection by k_prep_nt), per activation row:
+//   frag [nblk][8 groups of 32][4 threads][16 bytes]   what thread t of a quad feeds for a group:
+//                                                      Q4_K  values 8t .. 8t+7:               hi[8] | lo[8]
+//                                                      Q6_K  values 4t .. 4t+3 of each half:  hi[4] | lo[4] | hi[4] | lo[4]
+//   rec  [nblk][32 bytes]   per superblock: the sums of x' per 32 values as three signed base-256 digits, most
+//                           significant first, 8 bytes each (the B operand of the MMA that multiplies them with
+//                           the eight Q4_K minimums), then 1 / s as f32, then 4 spare bytes.
+// A block copies the superblocks of its slice of TOK = 8 NT rows into shared memory: frag rows with stride
+// 512 nb + 64 (rows g, g + 1 of a quarter-warp on different banks), rec rows with a stride of 4 words mod 32.
+struct PrepNT {
+    uint32_t cols, nblk, rec_off, token_bytes;
+};
+__host__ __device__ inline PrepNT prep_nt_layout(uint32_t cols) {
+    PrepNT L;
+    L.cols = cols;
+    L.nblk = cols / 256;
+    L.rec_off = L.nblk * 512;
+    L.token_bytes = L.nblk * 544;
+    return L;
+}
 struct ActSmem {
     uint8_t *frag;
-    uint8_t *sx;
-    float *inv;
-    uint32_t row_stride, sx_stride, inv_stride;
+    uint8_t *rec;
+    uint32_t row_stride, rec_stride;
 };
-__host__ __device__ inline uint32_t nt_sx_stride(uint32_t nb) { return 24 * nb + ((8 + 128 - (24 * nb) % 128) % 128); } // bytes
-__host__ __device__ inline uint32_t nt_inv_stride(uint32_t nb) { return nb | 1u; }                                     // floats
+// 16 bytes past a multiple of 128: rows stay 16-byte aligned for the copies, and the eight rows a warp reads
+// records of fall on different banks.
+__host__ __device__ inline uint32_t nt_rec_stride(uint32_t nb) { return 32 * nb + ((16 + 128 - (32 * nb) % 128) % 128); } // bytes
 // Bytes of the resident set (a multiple of 16: the warps' rings follow it).
 __host__ __device__ inline uint32_t nt_act_bytes(uint32_t tok, uint32_t nb) {
-    return (tok * (nb * 512 + 64) + tok * nt_sx_stride(nb) + tok * nt_inv_stride(nb) * 4 + 15u) & ~15u;
+    return (tok * (nb * 512 + 64) + tok * nt_rec_stride(nb) + 15u) & ~15u;
+}
+
+// One warp per (activation row, superblock); lane l owns the eight values at 256 b + 8 l.
+//   src    (may be null) row i of the prepared set is row src[i] / src_div of x (expert-sorted routes);
+//   range  (may be null) only rows [range[0], range[range_stride]) are prepared (the experts one rank owns);
+//   x_up   (may be null) the activations are the gated unit silu(x) * x_up, as `k_swiglu` computes it.
+template <int FMT>
+__global__ void __launch_bounds__(128)
+k_prep_nt(const float *__restrict__ x, const float *__restrict__ x_up, uint32_t xrows, const uint32_t *__restrict__ src, uint32_t src_div,
+          const uint32_t *__restrict__ range, uint32_t range_stride, PrepNT L, uint8_t *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const uint32_t xr = warp / L.nblk, b = warp % L.nblk;
+    if (xr >= xrows) return;
+    if (range && (xr < range[0] || xr >= range[range_stride])) return;
+    const size_t srow = src ? src[xr] / src_div : xr;
+    const float4 *sp = reinterpret_cast<const float4 *>(x + srow * L.cols + (size_t)b * 256 + lane * 8);
+    const float4 v0 = sp[0], v1 = sp[1];
+    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    if (x_up) {
+        const float4 *us = reinterpret_cast<const float4 *>(x_up + srow * L.cols + (size_t)b * 256 + lane * 8);
+        const float4 u0 = us[0], u1 = us[1];
+        const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v[i] / (1.f + expf(-v[i])) * u[i];
+    }
+    const Quant8 q = quantize8(v);
+    uint8_t *base = out + (size_t)xr * L.token_bytes, *frag = base + (size_t)b * 512, *rec = base + L.rec_off + (size_t)b * 32;
+    if constexpr (FMT == FQ_Q4_K) {
+        // 32-value group lane / 4, thread lane % 4
+        *reinterpret_cast<uint4 *>(frag + 16 * lane) = make_uint4(pack4(q.hi), pack4(q.hi + 4), pack4(q.lo), pack4(q.lo + 4));
+    } else {
+        // The lane's values sit in half (lane % 4) / 2 of the group; its first four belong to thread
+        // 2 (lane % 2), the other four to the thread after it.
+        uint8_t *dst = frag + 64 * (lane >> 2) + 8 * ((lane & 3) >> 1) + 32 * (lane & 1);
+        *reinterpret_cast<uint2 *>(dst) = make_uint2(pack4(q.hi), pack4(q.lo));
+        *reinterpret_cast<uint2 *>(dst + 16) = make_uint2(pack4(q.hi + 4), pack4(q.lo + 4));
+    }
+    int sum = q.sum;
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if ((lane & 3) == 0) { // three signed base-256 digits of the sum
+        const int p0 = ((sum + 128) & 0xFF) - 128, rem = (sum - p0) >> 8, p1 = ((rem + 128) & 0xFF) - 128, p2 = (rem - p1) >> 8;
+        rec[lane >> 2] = (uint8_t)p2;
+        rec[8 + (lane >> 2)] = (uint8_t)p1;
+        rec[16 + (lane >> 2)] = (uint8_t)p0;
+    }
+    // A non-finite activation anywhere in the superblock makes its factor NaN.
+    if (lane == 0) {
+        *reinterpret_cast<float *>(rec + 24) = q.finite ? ldexpf(1.f, -q.e) : __int_as_float(0x7fc00000);
+        *reinterpret_cast<uint32_t *>(rec + 28) = 0u;
+    }
 }
 
 // One superblock (index `bb` within the block's slice) of a 16-row tile whose packed bytes lie in `stage`,
@@ -144,7 +209,7 @@ __device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSme
             const uint32_t ma0 = t == 0 ? mn4[0][0] : t == 1 ? mn4[0][1] : 0u, ma1 = t == 0 ? mn4[1][0] : t == 1 ? mn4[1][1] : 0u;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const uint8_t *sp = A.sx + (size_t)(8 * nt + g) * A.sx_stride + (size_t)bb * 24 + 4 * (t & 1);
+                const uint8_t *sp = A.rec + (size_t)(8 * nt + g) * A.rec_stride + (size_t)bb * 32 + 4 * (t & 1);
                 int c2[4], c1[4], c0[4];
                 mma_u8s8_z(c2, ma0, ma1, 0u, 0u, *reinterpret_cast<const uint32_t *>(sp), 0u);
                 mma_u8s8_z(c1, ma0, ma1, 0u, 0u, *reinterpret_cast<const uint32_t *>(sp + 8), 0u);
@@ -183,7 +248,7 @@ __device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSme
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const float inv = A.inv[(size_t)(8 * nt + 2 * t + (i & 1)) * A.inv_stride + bb];
+                const float inv = *reinterpret_cast<const float *>(A.rec + (size_t)(8 * nt + 2 * t + (i & 1)) * A.rec_stride + (size_t)bb * 32 + 24);
                 const float dot = fmaf(256.f, (float)ah[nt][i], (float)al[nt][i]);
                 yacc[nt][i] = fmaf(inv, d[i >> 1] * dot - dmin[i >> 1] * (float)am[nt][i], yacc[nt][i]);
             }
@@ -244,54 +309,10 @@ __device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSme
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const float inv = A.inv[(size_t)(8 * nt + 2 * t + (i & 1)) * A.inv_stride + bb];
+                const float inv = *reinterpret_cast<const float *>(A.rec + (size_t)(8 * nt + 2 * t + (i & 1)) * A.rec_stride + (size_t)bb * 32 + 24);
                 yacc[nt][i] = fmaf(inv * d4[i >> 1], fmaf(256.f, (float)ah[nt][i], (float)al[nt][i]), yacc[nt][i]);
             }
     }
-}
-
-// Quantises the eight values (v0, v1) of this lane -- values 8 lane .. of one superblock of one activation row,
-// with `gated` the gated unit silu(v) * u -- into slot (tok, bb) of the resident set; one warp.  !have: zeros.
-template <int FMT>
-__device__ __forceinline__ void prep_resident(const ActSmem &A, uint32_t tok, uint32_t bb, bool have, bool gated, const float4 &v0, const float4 &v1,
-                                              const float4 &u0, const float4 &u1, uint32_t lane) {
-    uint8_t *frag = A.frag + (size_t)tok * A.row_stride + (size_t)bb * 512;
-    uint8_t *sxp = A.sx + (size_t)tok * A.sx_stride + (size_t)bb * 24;
-    float *invp = A.inv + (size_t)tok * A.inv_stride + bb;
-    if (!have) {
-        *reinterpret_cast<uint4 *>(frag + 16 * lane) = make_uint4(0u, 0u, 0u, 0u);
-        if (lane < 6) reinterpret_cast<uint32_t *>(sxp)[lane] = 0u;
-        if (lane == 0) *invp = 0.f;
-        return;
-    }
-    float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    if (gated) {
-        const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = v[i] / (1.f + expf(-v[i])) * u[i];
-    }
-    const Quant8 q = quantize8(v);
-    if constexpr (FMT == FQ_Q4_K) {
-        // 32-value group lane / 4, thread lane % 4
-        *reinterpret_cast<uint4 *>(frag + 16 * lane) = make_uint4(pack4(q.hi), pack4(q.hi + 4), pack4(q.lo), pack4(q.lo + 4));
-    } else {
-        // The lane's values sit in half (lane % 4) / 2 of the group; its first four belong to thread
-        // 2 (lane % 2), the other four to the thread after it.
-        uint8_t *dst = frag + 64 * (lane >> 2) + 8 * ((lane & 3) >> 1) + 32 * (lane & 1);
-        *reinterpret_cast<uint2 *>(dst) = make_uint2(pack4(q.hi), pack4(q.lo));
-        *reinterpret_cast<uint2 *>(dst + 16) = make_uint2(pack4(q.hi + 4), pack4(q.lo + 4));
-    }
-    int sum = q.sum;
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if ((lane & 3) == 0) { // three signed base-256 digits of the sum
-        const int p0 = ((sum + 128) & 0xFF) - 128, rem = (sum - p0) >> 8, p1 = ((rem + 128) & 0xFF) - 128, p2 = (rem - p1) >> 8;
-        sxp[lane >> 2] = (uint8_t)p2;
-        sxp[8 + (lane >> 2)] = (uint8_t)p1;
-        sxp[16 + (lane >> 2)] = (uint8_t)p0;
-    }
-    // A non-finite activation anywhere in the superblock makes its factor NaN.
-    if (lane == 0) *invp = q.finite ? ldexpf(1.f, -q.e) : __int_as_float(0x7fc00000);
 }
 
 // FMT: FQ_Q4_K / FQ_Q6_K; NT: tiles of eight activation rows; STAGES: superblocks in flight per warp;
@@ -362,11 +383,9 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
 
     ActSmem A;
     A.row_stride = J.nb_max * 512 + 64;
-    A.sx_stride = nt_sx_stride(J.nb_max);
-    A.inv_stride = nt_inv_stride(J.nb_max);
+    A.rec_stride = nt_rec_stride(J.nb_max);
     A.frag = nt_smem;
-    A.sx = nt_smem + (size_t)TOK * A.row_stride;
-    A.inv = reinterpret_cast<float *>(A.sx + (size_t)TOK * A.sx_stride);
+    A.rec = nt_smem + (size_t)TOK * A.row_stride;
     uint8_t *ring = nt_smem + nt_act_bytes(TOK, J.nb_max) + (size_t)warp * STAGES * St::BYTES;
 
     struct Tile {
@@ -446,34 +465,23 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
     if constexpr (!GROUPED) pdl_wait();
     const uint32_t seq = P.world > 1 ? tp_seq(P) : 0u;
 
-    // The block's resident activations: warp-tasks (row, superblock), two in flight per warp.
+    // The block's resident activations: 16-byte pieces of the prepared rows (per row 32 nb of fragments and
+    // 2 nb of records), copied asynchronously; rows the job does not have are zero.
     {
-        const uint32_t tasks = TOK * nb;
-        auto fetch = [&](uint32_t i, bool &have, float4 &v0, float4 &v1, float4 &u0, float4 &u1) {
-            const uint32_t tok = i / nb, bb = i - tok * nb;
-            have = i < tasks && tok < m;
-            if (!have) return;
-            size_t r = xrow0 + tok;
-            if (GROUPED && J.src) r = J.src[r] / J.src_div;
-            const float4 *sp = reinterpret_cast<const float4 *>(J.x + r * J.cols + (size_t)(b0 + bb) * 256 + lane * 8);
-            v0 = sp[0];
-            v1 = sp[1];
-            if (J.x_up) {
-                const float4 *up = reinterpret_cast<const float4 *>(J.x_up + r * J.cols + (size_t)(b0 + bb) * 256 + lane * 8);
-                u0 = up[0];
-                u1 = up[1];
+        const uint32_t per_row = 34 * nb, pieces = TOK * per_row;
+        const size_t tok_bytes = (size_t)J.nblk * 544;
+        for (uint32_t i = threadIdx.x; i < pieces; i += blockDim.x) {
+            const uint32_t tok = i / per_row, p = i - tok * per_row;
+            uint8_t *dst = p < 32 * nb ? A.frag + (size_t)tok * A.row_stride + 16 * p : A.rec + (size_t)tok * A.rec_stride + 16 * (p - 32 * nb);
+            if (tok < m) {
+                const uint8_t *row = J.prep + (size_t)(xrow0 + tok) * tok_bytes;
+                cp_async16(dst, p < 32 * nb ? row + (size_t)b0 * 512 + 16 * p : row + (size_t)J.nblk * 512 + (size_t)b0 * 32 + 16 * (p - 32 * nb));
+            } else {
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
             }
-        };
-        const bool gated = J.x_up != nullptr;
-        for (uint32_t i = warp; i < tasks; i += 2 * W) {
-            bool have_a, have_b;
-            float4 a0, a1, au0, au1, c0, c1, cu0, cu1;
-            a0 = a1 = au0 = au1 = c0 = c1 = cu0 = cu1 = make_float4(0.f, 0.f, 0.f, 0.f);
-            fetch(i, have_a, a0, a1, au0, au1);
-            fetch(i + W, have_b, c0, c1, cu0, cu1);
-            prep_resident<FMT>(A, i / nb, i % nb, have_a, gated, a0, a1, au0, au1, lane);
-            if (i + W < tasks) prep_resident<FMT>(A, (i + W) / nb, (i + W) % nb, have_b, gated, c0, c1, cu0, cu1, lane);
         }
+        cp_async_commit();
+        cp_async_wait<0>();
     }
     __syncthreads();
 
@@ -600,6 +608,23 @@ template <int FMT, int NT, bool GROUPED> cudaError_t nt_launch(fq_device *dev, c
     return launch_pdl(kernel, dim3(grid), dim3(S.warps * 32), S.smem, dev->stream, J, push);
 }
 
+// Prepares `xrows` activation rows into the handle's scratch (its two halves alternate, so a preparation that
+// starts early never writes what the projection before may still be reading) and returns where, or null when
+// they do not fit.
+uint8_t *launch_prep(fq_device *dev, int format, const ProjectArgs &f, uint32_t xrows, const uint32_t *src, uint32_t src_div, const uint32_t *range,
+                     uint32_t range_stride, cudaError_t &e) {
+    const PrepNT L = prep_nt_layout(f.cols);
+    if ((size_t)xrows * L.token_bytes > dev->xprep_bytes / 2) return nullptr;
+    dev->xprep_turn ^= 1u;
+    uint8_t *prep = (uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0);
+    const uint32_t warps = xrows * L.nblk;
+    if (format == FQ_Q4_K)
+        e = launch_pdl(k_prep_nt<FQ_Q4_K>, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, xrows, src, src_div, range, range_stride, L, prep);
+    else
+        e = launch_pdl(k_prep_nt<FQ_Q6_K>, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, xrows, src, src_div, range, range_stride, L, prep);
+    return prep;
+}
+
 template <int FMT, int NT> int launch_dense(fq_device *dev, const ProjectArgs *a, uint32_t count) {
     NtJob J{};
     J.count = count;
@@ -614,8 +639,6 @@ template <int FMT, int NT> int launch_dense(fq_device *dev, const ProjectArgs *a
     J.pitch = a[0].row_bytes;
     J.cols = a[0].cols;
     J.nblk = a[0].cols / 256;
-    J.x = (const float *)a[0].x;
-    J.x_up = a[0].x_up;
     J.m = a[0].m;
     NtShape S;
     if (!nt_shape<FMT, NT>(dev, tiles, J.nblk, false, S)) return FQ_ERR_UNSUPPORTED;
@@ -625,6 +648,9 @@ template <int FMT, int NT> int launch_dense(fq_device *dev, const ProjectArgs *a
     J.counters = dev->nt_counters;
     if (S.slices > 1 && ((size_t)tiles * S.slices * 32 * NT * sizeof(float4) > dev->nt_ws_bytes || tiles > dev->nt_counter_count))
         return FQ_ERR_UNSUPPORTED;
+    cudaError_t e = cudaSuccess;
+    if (!(J.prep = launch_prep(dev, FMT, a[0], a[0].m, nullptr, 1, nullptr, 0, e))) return FQ_ERR_UNSUPPORTED;
+    if (int rc = fq_check_cuda(dev, e, "activation preparation launch")) return rc;
     TpPush push{};
     if (dev->tp_push) { // one launch covers every target: it can do the exchange itself
         push = *dev->tp_push;
@@ -632,7 +658,7 @@ template <int FMT, int NT> int launch_dense(fq_device *dev, const ProjectArgs *a
         dev->tp_pushed = true;
     }
     if (int rc = fq_check_cuda(dev, nt_launch<FMT, NT, false>(dev, J, S, S.grid, push), "gemv launch")) return rc;
-    return fq_end_enqueue(dev, "gemv_nt", 1);
+    return fq_end_enqueue(dev, "gemv_nt", 2);
 }
 
 } // namespace
@@ -676,22 +702,22 @@ int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t cou
     J.pitch = f.row_bytes;
     J.cols = f.cols;
     J.nblk = f.cols / 256;
-    J.x = (const float *)f.x;
-    J.x_up = f.x_up;
     J.slices = 1;
     J.offsets = f.offsets;
     J.slots = f.slots;
-    J.src = src;
-    J.src_div = src_div ? src_div : 1;
     J.groups = f.groups;
     J.total_rows = total_rows;
     NtShape S;
     const bool q4 = f.format == FQ_Q4_K;
     if (!(q4 ? nt_shape<FQ_Q4_K, 2>(dev, tiles, J.nblk, true, S) : nt_shape<FQ_Q6_K, 2>(dev, tiles, J.nblk, true, S))) return FQ_ERR_UNSUPPORTED;
     J.nb_max = S.nb_max;
+    cudaError_t e = cudaSuccess;
+    // The rows of the experts in `offsets` (a rank's share when the matrices hold only some experts).
+    if (!(J.prep = launch_prep(dev, (int)f.format, f, total_rows, src, src_div ? src_div : 1, f.offsets, f.groups, e))) return FQ_ERR_UNSUPPORTED;
+    if (int rc = fq_check_cuda(dev, e, "activation preparation launch")) return rc;
     // Every group has at most ceil(rows / 16) <= rows / 16 + 1 tiles of sixteen rows.
     const uint32_t grid = total_rows / 16 + f.groups;
-    const cudaError_t e = q4 ? nt_launch<FQ_Q4_K, 2, true>(dev, J, S, grid, TpPush{}) : nt_launch<FQ_Q6_K, 2, true>(dev, J, S, grid, TpPush{});
+    e = q4 ? nt_launch<FQ_Q4_K, 2, true>(dev, J, S, grid, TpPush{}) : nt_launch<FQ_Q6_K, 2, true>(dev, J, S, grid, TpPush{});
     if (int rc = fq_check_cuda(dev, e, "grouped gemv launch")) return rc;
-    return fq_end_enqueue(dev, "gemv_nt_grouped", 1);
+    return fq_end_enqueue(dev, "gemv_nt_grouped", 2);
 }

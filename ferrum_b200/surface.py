@@ -156,14 +156,18 @@ class Comm:
     """Tensor-parallel exchange over NVLink peer memory: this rank's symmetric buffer plus every peer's,
     mapped through CUDA IPC.  The 64-byte handles travel through ``torch.distributed`` (plumbing only)."""
 
-    def __init__(self, device: Device, rank: int, world: int, nbytes: int, group=None):
+    def __init__(self, device: Device, rank: int, world: int, nbytes: int, group=None, local_peer: bool = False):
+        """``local_peer`` (tests only, world 2): the peer is a second buffer on this GPU that nothing writes,
+        so every wait for it runs out."""
         import torch.distributed as dist
         self.device, self.rank, self.world = device, rank, world
         self.nbytes = (nbytes + 255) // 256 * 256
         h = C.c_void_p()
         device.check(device._L.fq_comm_create(device.handle, rank, world, self.nbytes, C.byref(h)))
         self.handle = h
-        if world > 1:
+        if local_peer:
+            device.check(device._L.fq_comm_open_local(h))
+        elif world > 1:
             mine = (C.c_ubyte * 64)()
             device.check(device._L.fq_comm_handle(h, mine))
             every = [None] * world
@@ -185,6 +189,10 @@ class Comm:
                                            "data": (self.base + offset_bytes, False), "version": 2}
         t = torch.as_tensor(holder, device=self.device.torch_device)
         return t.view(dtype) if t.dtype != dtype else t
+
+    def set_wait_ns(self, ns: int) -> None:
+        """Wall-time limit of the device-side waits for a peer."""
+        self.device.check(self.device._L.fq_comm_set_wait_ns(self.handle, ns))
 
     def all_gather(self, offset_bytes: int, shard_bytes: int) -> None:
         """Rank r's slice is ``[offset + r * shard, + shard)``; afterwards (in stream order) all are local."""

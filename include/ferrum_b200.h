@@ -244,15 +244,31 @@ int fq_comm_all_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size
 int fq_comm_all_gather_rows(fq_device *dev, fq_comm *comm, size_t region_offset, size_t row_bytes, const uint32_t *bounds,
                             uint32_t stride, size_t total_rows);
 int fq_comm_destroy(fq_comm *comm);
+/* Wall-time limit (nanoseconds, default 2 s) of every device-side wait of this communicator's exchanges: a
+ * kernel that has waited this long for a peer records FQ_ERR_TIMEOUT and returns; `fq_synchronize` reports it
+ * and `fq_device_recover` makes the handle usable again.  The counterpart of the reference's failed command
+ * epoch (src/metal/mod.rs:598-625) for a peer that never arrives. */
+int fq_comm_set_wait_ns(fq_comm *comm, uint64_t ns);
+/* Test-only, in place of `fq_comm_open` on a communicator of two ranks: the "peer" is a second buffer on
+ * this GPU that nothing ever writes, so every wait for the peer runs out -- the give-up path can be tested on
+ * one GPU without a second process and without a fault (the reference's failure tests,
+ * src/metal/mod.rs:1196-1303, inject on the host as well). */
+int fq_comm_open_local(fq_comm *comm);
+/* Exchange regions: consecutive exchanges of one communicator (`fq_comm_all_gather`, `fq_comm_all_gather_rows`,
+ * `fq_project_many_gather`, `fq_moe_ffn_ep`, and the first exchange of a replayed graph against what ran before
+ * it) must use regions that do not overlap.  A rank that runs ahead writes its peers' copy of the region it is
+ * exchanging; if that region were the one of the exchange before, a slower peer might still be reading it.
+ * With another exchange in between the writer cannot be that far ahead.  A reuse is refused with FQ_ERR_PARAM. */
 /* `fq_project_many` on row shards with the exchange included: every y[i] (F32) must lie in this rank's
- * slice [region_offset + rank * shard_bytes, + shard_bytes) of a gathered region of the symmetric buffer;
+ * slice [region_offset + rank * shard_bytes, + shard_bytes) of a gathered region of the symmetric buffer,
+ * y[0] at the start of the slice and every y[i + 1] directly after y[i] (FQ_ERR_RANGE otherwise; what is left
+ * of the slice after the last output is padding that is neither sent nor waited for);
  * when the call's work has run, the region holds every rank's slice, as after `fq_comm_all_gather`.  At
- * decode widths (m <= 4, Q4_K / Q6_K) there is ONE launch for compute and exchange and no fence: the
+ * decode and verify widths (m <= 16, Q4_K / Q6_K) there is ONE launch for compute and exchange and no fence: the
  * projection kernel stores every output value, paired with the exchange's sequence number in one 8-byte
  * store, into a mirror area of every peer's buffer, and before it ends its blocks collect the values the
  * peers sent (polling each slot, bounded, for the current sequence number).  Other shapes project, then
- * gather the region with the copy kernel.  A region may be written again only after another exchange of the
- * same communicator has completed in between.  The buffer `fq_comm_create` allocates is three times `bytes`
+ * gather the region with the copy kernel.  The buffer `fq_comm_create` allocates is three times `bytes`
  * plus the flag words (payload, flags, mirror). */
 int fq_project_many_gather(fq_device *dev, fq_comm *comm, size_t region_offset, size_t shard_bytes, const fq_matrix *const *w,
                            size_t count, const void *x, int x_dtype, size_t x_elems, size_t m, void *const *y, int y_dtype);

@@ -1,0 +1,193 @@
+"""Parity at the sizes the benchmark configurations state, and the failure paths that need a GPU but no fault.
+
+Config 1: the o and gate/up shapes at decode and verify widths.  Config 2: M = 2048 on gate and down.  Config 3:
+the whole MoE block with 256 experts, top-8, T = 1 and 1024 (sampled tokens against the oracle composition; the
+reference's expert-path tests are src/hybrid/iq_tests.rs:1686-1814).  Failure paths: a device-side wait that
+runs out (the counterpart of src/metal/mod.rs:1196-1303) and a router row without a ranking
+(src/nn/moe.rs:392-397).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-3
+TOL_BF16 = 2e-2
+
+
+def S():
+    from ferrum_b200 import surface
+    return surface
+
+
+def dev_f32(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+def rows_of(packed, fmt, cols, pick):
+    rb = ref.row_bytes(fmt, cols)
+    return np.concatenate([packed[r * rb:(r + 1) * rb] for r in pick])
+
+
+@pytest.mark.parametrize("rows,cols", [(5120, 6144), (17408, 5120)])
+@pytest.mark.parametrize("m", [1, 8, 16])
+def test_config1_o_and_gate_shapes(device, rows, cols, m):
+    s = S()
+    fmt = ref.Q4_K
+    packed = ref.random_matrix(fmt, rows, cols, seed=rows % 89)
+    x = np.random.default_rng(m + 3).standard_normal((m, cols)).astype(np.float32)
+    w = s.Matrix.from_packed(device, rows, cols, 1, fmt, packed)
+    y = torch.full((m * rows,), float("nan"), dtype=torch.float32, device="cuda")
+    s.project(device, w, dev_f32(x), m, y)
+    device.synchronize()
+    got = host(y).reshape(m, rows)
+    assert np.isfinite(got).all()
+    pick = np.sort(np.random.default_rng(6).choice(rows, 24, replace=False))
+    want = ref.matmul(fmt, rows_of(packed, fmt, cols, pick), len(pick), cols, x, m, mode=0)
+    assert np.abs(got[:, pick] - want).max() / np.abs(got).max() <= TOL_F32
+
+
+@pytest.mark.parametrize("fmt,rows,cols", [(ref.Q4_K, 17408, 5120), (ref.Q6_K, 5120, 17408)])
+def test_config2_m2048_rows(device, fmt, rows, cols):
+    s = S()
+    m = 2048
+    packed = ref.random_matrix(fmt, rows, cols, seed=21)
+    xb = ref.round_bf16(np.random.default_rng(22).standard_normal((m, cols)).astype(np.float32))
+    w = s.Matrix.from_packed(device, rows, cols, 1, fmt, packed)
+    y = torch.zeros(m * rows, dtype=torch.bfloat16, device="cuda")
+    s.project(device, w, torch.from_numpy(xb).cuda().to(torch.bfloat16), m, y)
+    device.synchronize()
+    got = y.float().cpu().numpy().reshape(m, rows)
+    assert np.isfinite(got).all()
+    pick = np.sort(np.random.default_rng(7).choice(rows, 12, replace=False))
+    dense_b = ref.round_bf16(ref.dequant(fmt, rows_of(packed, fmt, cols, pick))).reshape(len(pick), cols)
+    want = xb.astype(np.float64) @ dense_b.astype(np.float64).T
+    assert np.abs(got[:, pick] - want).max() / np.abs(got).max() <= TOL_BF16
+
+
+def expert_rows(packed, fmt, rows_e, cols, e):
+    rb = ref.row_bytes(fmt, cols)
+    return packed[e * rows_e * rb:(e + 1) * rows_e * rb]
+
+
+@pytest.fixture(scope="module")
+def config3():
+    experts, used, hidden, ef = 256, 8, 2048, 512
+    mats = dict(router=ref.random_matrix(ref.Q8_0, experts, hidden, 70),
+                gate=ref.random_matrix(ref.Q4_K, experts * ef, hidden, 71), up=ref.random_matrix(ref.Q4_K, experts * ef, hidden, 72),
+                down=ref.random_matrix(ref.Q6_K, experts * hidden, ef, 73),
+                sg=ref.random_matrix(ref.Q4_K, ef, hidden, 74), su=ref.random_matrix(ref.Q4_K, ef, hidden, 75),
+                sd=ref.random_matrix(ref.Q6_K, hidden, ef, 76))
+    return experts, used, hidden, ef, mats
+
+
+@pytest.mark.parametrize("tokens", [1, 1024])
+def test_config3_moe_block(device, config3, tokens):
+    """35B-A3B-class block: 256 experts + shared, top-8, hidden 2048, expert width 512.  T = 1 takes the per-route
+    projections, T = 1024 the grouped kernel over expert-sorted rows; sampled tokens against the oracle."""
+    s = S()
+    experts, used, hidden, ef, mats = config3
+    M = s.Matrix.from_packed
+    f = s.MoeFfn(M(device, experts, hidden, 1, ref.Q8_0, mats["router"]), M(device, ef, hidden, experts, ref.Q4_K, mats["gate"]),
+                 M(device, ef, hidden, experts, ref.Q4_K, mats["up"]), M(device, hidden, ef, experts, ref.Q6_K, mats["down"]),
+                 M(device, ef, hidden, 1, ref.Q4_K, mats["sg"]), M(device, ef, hidden, 1, ref.Q4_K, mats["su"]),
+                 M(device, hidden, ef, 1, ref.Q6_K, mats["sd"]), None, experts, used, hidden, ef, ef, False, True)
+    x = (np.random.default_rng(tokens).standard_normal((tokens, hidden)) * 0.06).astype(np.float32)
+    scratch = torch.zeros(s.moe_ffn_scratch_elems(device, f, tokens), dtype=torch.float32, device="cuda")
+    out = torch.full((tokens * hidden,), float("nan"), dtype=torch.float32, device="cuda")
+    s.moe_ffn(device, f, dev_f32(x), tokens, scratch, out)
+    device.synchronize()
+    got = host(out).reshape(tokens, hidden)
+    assert np.isfinite(got).all()
+    checked = 0
+    for t in np.random.default_rng(9).permutation(tokens)[:12]:
+        xt = x[t:t + 1]
+        logits = ref.matmul(ref.Q8_0, mats["router"], experts, hidden, xt, 1)
+        p = np.sort(np.exp(logits[0] - logits[0].max()))[::-1]
+        if (p[used - 1] - p[used]) < 1e-3 * p[used - 1]:
+            continue  # the eighth and ninth expert are too close for a 16-bit-activation router to be held to
+        ids, wts, gate = ref.moe_route(logits, xt, xt[0], experts, used, hidden, 1, False, True, False)
+        g = np.stack([ref.matmul(ref.Q4_K, expert_rows(mats["gate"], ref.Q4_K, ef, hidden, int(e)), ef, hidden, xt, 1)[0] for e in ids.ravel()])
+        u = np.stack([ref.matmul(ref.Q4_K, expert_rows(mats["up"], ref.Q4_K, ef, hidden, int(e)), ef, hidden, xt, 1)[0] for e in ids.ravel()])
+        act = ref.swiglu(g, u)
+        dn = np.stack([ref.matmul(ref.Q6_K, expert_rows(mats["down"], ref.Q6_K, hidden, ef, int(e)), hidden, ef, act[i:i + 1], 1)[0]
+                       for i, e in enumerate(ids.ravel())])
+        gs = ref.matmul(ref.Q4_K, mats["sg"], ef, hidden, xt, 1)
+        us = ref.matmul(ref.Q4_K, mats["su"], ef, hidden, xt, 1)
+        shared = ref.matmul(ref.Q6_K, mats["sd"], hidden, ef, ref.swiglu(gs, us), 1)
+        want = ref.moe_combine(dn, wts, ids, shared, gate, hidden, used, 1, identity=True)[0]
+        assert np.abs(got[t] - want).max() / np.abs(want).max() <= 3 * TOL_F32, f"token {t}"
+        checked += 1
+        if checked == 4:
+            break
+    assert checked >= 1
+
+
+def test_a_wait_for_an_absent_peer_runs_out(device):
+    """A communicator of two ranks whose peer is a buffer nothing writes: the exchange kernels give up after the
+    (shortened) wall-time limit, `synchronize` reports a timeout, and after `recover` the handle works again."""
+    s = S()
+    rows, cols = 256, 1024
+    packed = ref.random_matrix(ref.Q4_K, rows, cols, seed=3)
+    w = s.Matrix.from_packed(device, rows, cols, 1, ref.Q4_K, packed)
+    x = np.random.default_rng(1).standard_normal((1, cols)).astype(np.float32)
+    xd = dev_f32(x)
+    comm = s.Comm(device, 0, 2, 1 << 16, local_peer=True)
+    comm.set_wait_ns(2_000_000)  # 2 ms
+    # The copy-kernel exchange.
+    comm.all_gather(0, 1024)
+    with pytest.raises(s.TimeoutError_):
+        device.synchronize()
+    device.recover()
+    # The exchange fused into the projection kernel, at one and at four activation rows.
+    for m, region in ((1, 8192), (4, 16384)):
+        xm = dev_f32(np.repeat(x, m, axis=0))
+        y = comm.view(region, m * rows)
+        s.project_many_gather(device, comm, region, m * rows * 4, [w], xm, m, [y])
+        with pytest.raises(s.TimeoutError_):
+            device.synchronize()
+        with pytest.raises(s.SynchronizationError):
+            s.project(device, w, xd, 1, torch.zeros(rows, dtype=torch.float32, device="cuda"))  # a failed handle refuses work
+        device.recover()
+        # the local slice was computed all the same
+        want = ref.matmul(ref.Q4_K, packed, rows, cols, np.repeat(x, m, axis=0), m)
+        assert ref.rel_err(host(y).reshape(m, rows), want) <= TOL_F32
+    # Reusing the region of the exchange before is refused up front.
+    with pytest.raises(s.ParameterError):
+        comm.all_gather(16384, 1024)
+    comm.close()
+    out = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    s.project(device, w, xd, 1, out)
+    device.synchronize()
+    assert ref.rel_err(host(out).reshape(1, rows), ref.matmul(ref.Q4_K, packed, rows, cols, x, 1)) <= TOL_F32
+
+
+def test_router_refuses_logits_without_a_ranking(device):
+    """A NaN or an infinity among the logits: the token gets in-range experts with zero weight, nothing reads out
+    of range, and `synchronize` reports the row as the reference's router does."""
+    s = S()
+    experts, used, hidden, tokens = 64, 8, 128, 5
+    rng = np.random.default_rng(2)
+    logits = rng.standard_normal((tokens, experts)).astype(np.float32)
+    logits[1, 7] = np.nan
+    logits[3, 0] = np.inf
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    ids = torch.full((tokens * used,), -1, dtype=torch.int32, device="cuda")
+    wts = torch.full((tokens * used,), float("nan"), dtype=torch.float32, device="cuda")
+    gate = torch.zeros(tokens, dtype=torch.float32, device="cuda")
+    s.moe_route(device, dev_f32(logits), dev_f32(x), dev_f32(x[0]), experts, used, hidden, tokens, False, True, False, ids, wts, gate)
+    with pytest.raises(s.WeightError):
+        device.synchronize()
+    device.recover()
+    got_ids = ids.cpu().numpy().view(np.uint32).reshape(tokens, used)
+    assert (got_ids < experts).all()
+    assert (wts.cpu().numpy().reshape(tokens, used)[[1, 3]] == 0).all()
+    want_ids, want_w, _ = ref.moe_route(logits[[0, 2, 4]], x[[0, 2, 4]], x[0], experts, used, hidden, 3, False, True, False)
+    assert np.array_equal(got_ids[[0, 2, 4]], want_ids.reshape(3, used))
