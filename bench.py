@@ -11,13 +11,17 @@ step streams far more than L2 from HBM.  One step = one pass over all layers' pr
 inputs resident in HBM.  `e2e` = the same through the host-buffer C-ABI calls, host<->device copies
 inside the timed region.  Extra keys report M = 8 / 16 and the prefill dequant-GEMM.
 
-With --gpus N > 1 (under torchrun) every matrix is row-sharded over the N ranks, each fused group
-(q|k|v, o, gate|up, down) computes its row shard and exchanges it over NVLink peer memory in one
-launch, and the step covers LAYERS x N layers: every rank streams the same bytes per step whatever N
-is, so scaling is "weak" and `value` is the aggregate of all ranks.
+With --gpus N > 1 (under torchrun) the workload is the tensor-parallel sweep: a 64-layer stack of the same
+layer set (448 matrices, 13,738,967,040 packed bytes), every matrix row-sharded over the N ranks, each fused
+group (q|k|v, o, gate|up, down) computing its row shard and exchanging it over NVLink peer memory in one
+launch.  Total work is fixed ("strong" scaling), `value` is the aggregate of all ranks at M = 1, and the
+line also carries the M = 8 figure and the per-layer latency.  Before the timed region every rank's shard of
+layer 0 is checked: the gathered rows against the CPU oracle on the whole matrix, and an expert-parallel MoE
+block against the single-GPU block bit for bit; the line carries the result under `parity` and the run
+fails if it is off.
 
 --impl reference times the reference's CPU path for the same projections: the oracle restatement
-of its CPU dequant + matmul on all host cores, one layer per step (a bounded sample).
+of its CPU dequant + matmul on all host cores, `--layers` layers per step.
 """
 from __future__ import annotations
 
@@ -42,6 +46,19 @@ GROUPS = [("q", "k", "v"), ("o",), ("gate", "up"), ("down",)]
 BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
 LAYER_BYTES = sum(r * c // BLOCK[f][0] * BLOCK[f][1] for _, r, c, f in LAYER)  # 214,671,360
 LAYER_WEIGHTS = sum(r * c for _, r, c, _ in LAYER)
+
+
+def profile_value(name: str, key: str):
+    """`key: value` line of a tracked profile summary (profiles/<name>), or None."""
+    path = os.path.join(ROOT, "profiles", name)
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.strip().startswith(key + ":"):
+                    return int(line.split(":", 1)[1].strip().split()[0])
+    except OSError:
+        pass
+    return None
 
 
 def peaks():
@@ -147,51 +164,73 @@ def run_ours(args):
     # CUDA events are recorded on the stream the kernels are launched on.
     dev = S.Device(local, use_torch_stream=False)
     stream = torch.cuda.ExternalStream(dev.stream_ptr(), device=torch.device("cuda", local))
-    # Weak scaling: every rank streams the same number of bytes per step whatever N is (its 1/N share of
-    # `--layers` x N layers), so the per-GPU stream stays far larger than L2.
-    m, layers = args.m, args.layers * world
+    # One GPU: `--layers` distinct layers per step (far more than L2).  More GPUs: the 64-layer stack, every
+    # matrix sharded by rows, so a rank streams 1 / N of 13.7 GB per step.
+    from ferrum_b200 import tp
+    m = args.m
+    layers = args.layers if world == 1 else (args.tp_layers or 64)
+    distinct = min(layers, 3)
 
-    # Weights: layer l, matrix i uses seed (7 l + i) * 64 + rank; blocks drawn as the benchmark configurations 0 and 1 define them.
+    # Weights: layer l, matrix i is drawn from seed 7 l + i -- the same whole matrix on every rank, of which the
+    # rank keeps its rows; blocks as the benchmark configurations 0 and 1 define them.  The stack repeats
+    # `distinct` layers' bytes in separate device copies (the stream does not care what the bytes are).
+    host_layers = []
+    for l in range(distinct):
+        layer = {}
+        for i, (name, rows, cols, fmt) in enumerate(LAYER):
+            full = random_matrix(fmt, rows, cols, seed=7 * l + i)
+            layer[name] = (full if world == 1 else tp.shard_packed(full, fmt, rows, cols, rank, world), full if l == 0 else None)
+        host_layers.append(layer)
     mats = []
     for l in range(layers):
         layer = {}
-        for i, (name, rows, cols, fmt) in enumerate(LAYER):
-            _, per = shard_rows(rows, rank, world)
-            layer[name] = S.Matrix.from_packed(dev, per, cols, 1, fmt, random_matrix(fmt, per, cols, seed=(7 * l + i) * 64 + rank))
+        for name, rows, cols, fmt in LAYER:
+            layer[name] = S.Matrix.from_packed(dev, rows // world, cols, 1, fmt, host_layers[l % distinct][name][0])
         mats.append(layer)
     shapes = {name: (rows // world, cols) for name, rows, cols, _ in LAYER}
+    full_layer0 = {name: host_layers[0][name][1] for name, _, _, _ in LAYER}
 
     comm_box = {}
 
-    def buffers(mm, shared=False):
-        """One contiguous input buffer (a slice per group) and one output buffer (a slice per matrix).  With
-        `shared` (more than one rank) the outputs live in the exchange buffer: per input group a region
-        [world][span], this rank writing slice `rank`, gathered with one peer-push all-gather."""
+    def layout(mm):
+        """Offsets (in floats) of the per-group inputs and the per-matrix outputs for `mm` activation rows."""
         xs, ys, xo, yo = {}, {}, 0, 0
         for g in GROUPS:
             xs[g[0]] = (xo, mm * shapes[g[0]][1])
             xo += (mm * shapes[g[0]][1] + 63) // 64 * 64
-        for name in shapes:
-            ys[name] = (yo, mm * shapes[name][0])
-            yo += (mm * shapes[name][0] + 63) // 64 * 64
+        # Outputs of one input group are adjacent, without gaps: one exchange per group moves them together.
+        for g in GROUPS:
+            for name in g:
+                ys[name] = (yo, mm * shapes[name][0])
+                yo += (mm * shapes[name][0] + 3) // 4 * 4
+            yo = (yo + 63) // 64 * 64
+        span_of = {g[0]: (ys[g[0]][0], (ys[g[-1]][0] + ys[g[-1]][1] + 63) // 64 * 64) for g in GROUPS}
+        return xs, ys, xo, yo, span_of
+
+    def buffers(mm, shared=False, region_base=0):
+        """One contiguous input buffer (a slice per group) and one output buffer (a slice per matrix).  With
+        `shared` (more than one rank) the outputs live in the exchange buffer from byte `region_base`: per input
+        group a region [world][span], this rank writing slice `rank`."""
+        xs, ys, xo, yo, span_of = layout(mm)
         X = torch.zeros(xo, dtype=torch.float32, device="cuda")
-        # Outputs of one input group are adjacent: one all-gather per group moves them together.
-        span_of = {g[0]: (ys[g[0]][0], ys[g[-1]][0] + (ys[g[-1]][1] + 63) // 64 * 64) for g in GROUPS}
         if shared and not args.nccl:
-            comm = S.Comm(dev, rank, world, world * yo * 4)
-            comm_box["comm"] = comm
+            comm = comm_box["comm"]
             regions, yv = {}, {}
             for g in GROUPS:
                 lo, hi = span_of[g[0]]
-                region = world * lo * 4
+                region = region_base + world * lo * 4
                 regions[g[0]] = (region, (hi - lo) * 4)
                 for n in g:
                     yv[n] = comm.view(region + rank * (hi - lo) * 4 + (ys[n][0] - lo) * 4, ys[n][1])
-            Y = comm.view(0, world * yo)
+            Y = comm.view(region_base, world * yo)
             return X, Y, {k: X[o:o + n] for k, (o, n) in xs.items()}, yv, regions
         Y = torch.zeros(yo, dtype=torch.float32, device="cuda")
         spans = {k: Y[lo:hi] for k, (lo, hi) in span_of.items()}
         return X, Y, {k: X[o:o + n] for k, (o, n) in xs.items()}, {k: Y[o:o + n] for k, (o, n) in ys.items()}, spans
+
+    if world > 1 and not args.nccl:
+        # One symmetric buffer for the run: the regions of the headline width, then those of M = 8.
+        comm_box["comm"] = S.Comm(dev, rank, world, world * (layout(m)[3] + layout(8)[3]) * 4)
 
     rng = np.random.default_rng(1234)
     X, Y, x_dev, y_dev, y_spans = buffers(m, shared=world > 1)
@@ -248,6 +287,14 @@ def run_ours(args):
                 ms = float(t.item())
         return ms
 
+    parity = None
+    if world > 1 and not args.nccl:
+        parity = tp_parity(S, dev, torch, dist, comm_box["comm"], mats[0], full_layer0, x_pinned.numpy(), x_dev, y_dev, y_spans, m, rank, world)
+        parity.update(ep_parity(S, dev, torch, dist, rank, world))
+        if rank == 0 and not (parity["tp_rel_err"] <= 1e-3 and parity["ep_bits_equal"]):
+            print(json.dumps({"error": "sharded results differ from the single-GPU results", "parity": parity}), flush=True)
+            raise SystemExit(1)
+
     with torch.cuda.stream(stream):
         step = make_step(x_dev, y_dev, m)
         for _ in range(max(args.warmup, 3)):
@@ -264,10 +311,12 @@ def run_ours(args):
     out = {
         "metric": "Q4_K_M decode projection weight GB/s (27B-class dense layer set)", "value": round(value, 2),
         "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"cfg1 dense 27B decode projection set (q,k,v,o,gate,up Q4_K; down Q6_K), M={m}, "
-                               f"{layers} distinct layers = {total_bytes} packed bytes per step (inputs larger than L2)",
+        "config": {"workload": (f"cfg1 dense 27B decode projection set (q,k,v,o,gate,up Q4_K; down Q6_K), M={m}, "
+                                f"{layers} distinct layers = {total_bytes} packed bytes per step (inputs larger than L2)") if world == 1 else
+                               (f"cfg4 tensor-parallel sweep: {layers}-layer dense stack of the cfg1 layer set ({7 * layers} Q4_K/Q6_K matrices, "
+                                f"{total_bytes} packed bytes), M={m}, every matrix row-sharded over {world} GPUs, one exchange per input group"),
                    "m": m, "layers": layers, "parallelism": f"tp{world}" if world > 1 else "single",
                    "submission": ("one captured graph per step" if world == 1 else
                                   "eager + one NCCL all-gather per input group" if args.nccl else
@@ -275,7 +324,12 @@ def run_ours(args):
                    "l2": "inputs larger than L2"},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
+        "per_layer_us": round(ms_per_step * 1e3 / layers, 2),
+        "roofline_step": {"bytes_per_step_per_gpu": total_bytes // world, "achieved_per_gpu": round(value / world, 1), "peak": peaks()["hbm_gbs"],
+                          "frac": round(value / world / peaks()["hbm_gbs"], 4), "unit": "GB/s"},
     }
+    if parity is not None:
+        out["parity"] = parity
 
     if rank == 0 and world == 1:
         def alone(names, mm, xd, yd):
@@ -294,9 +348,9 @@ def run_ours(args):
         out["roofline"] = {"bound": "hbm", "kernel": "k_gemv_i8<Q4_K,1> (gate|up, 2 x 17408 x 5120, one launch)",
                            "achieved": round(achieved, 1), "peak": P["hbm_gbs"], "peak_source": P["source"], "unit": "GB/s",
                            "frac": round(achieved / P["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
-                           # dram__bytes_read.sum + dram__bytes_write.sum of this launch from one ncu capture
-                           # (the summary is committed with the profile summaries): 100.31 MB read + 3.26 MB written.
-                           "traffic": 103565056, "traffic_source": "one ncu capture of this launch",
+                           # dram__bytes_read.sum + dram__bytes_write.sum of this launch, from the tracked ncu summary
+                           "traffic": profile_value("gemv_i8_q4k_gate_up_m1.md", "dram_bytes_per_launch"),
+                           "traffic_source": "profiles/gemv_i8_q4k_gate_up_m1.md (one ncu capture of this launch)",
                            "algorithmic_bytes": pair_bytes, "us_per_launch": round(gms * 1e3, 2)}
         per = {}
         for names in (("q", "k", "v"), ("o",), ("gate", "up"), ("down",)):
@@ -403,10 +457,29 @@ def run_ours(args):
             e2e = {"value": round(total_bytes / dt / 1e9, 2), "unit": "GB/s", "h2d_bytes_per_step": int(xh.nbytes),
                    "d2h_bytes_per_step": int(yh.nbytes), "ms_per_step": round(dt * 1e3, 4),
                    "call": "per rank: fq_upload + fq_graph_launch (projections + exchanges) + fq_download_async + fq_synchronize"}
+        # The verify width of the sweep: the same stack at M = 8.
+        tp_m8 = None
+        if not args.nccl and m != 8:
+            X8, Y8, x8, y8, spans8 = buffers(8, shared=True, region_base=Y.numel() * 4)
+            X8.copy_(torch.from_numpy(rng.standard_normal(X8.numel()).astype(np.float32)))
+            saved = dict(y_spans)
+            y_spans.clear()
+            y_spans.update(spans8)
+            with torch.cuda.stream(stream):
+                step8 = make_step(x8, y8, 8)
+                for _i in range(3):
+                    step8()
+            reps = max(3, args.steps // 2)
+            t8 = timed(step8, reps) / reps
+            y_spans.clear()
+            y_spans.update(saved)
+            tp_m8 = {"value": round(total_bytes / (t8 * 1e-3) / 1e9, 2), "unit": "GB/s", "ms_per_step": round(t8, 4),
+                     "per_layer_us": round(t8 * 1e3 / layers, 2)}
         # Expert parallelism over the same ranks (config 3 sharded by expert): every rank takes part.
         ep = moe_ep_bench(S, dev, stream, torch, dist, timed, rank, world)
         if rank == 0:
             out["e2e"] = e2e
+            out["tp_m8"] = tp_m8
             out["moe_ffn_ep"] = ep
     if rank == 0:
         print(json.dumps(out), flush=True)
@@ -415,19 +488,89 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def tp_parity(S, dev, torch, dist, comm, layer0, full0, x_host, x_dev, y_dev, y_spans, m, rank, world):
+    """Sharded projections of layer 0 with the exchange, once per input group: every rank's gathered rows must be
+    what the CPU oracle computes from the whole matrix (sampled rows, max |d| / max |y| <= 1e-3).  Checked on
+    rank 0, which sees the rows of every rank after the exchange."""
+    from oracle import ref  # the checker
+    worst = 0.0
+    xs_off, ys_off, _, _, span_of = None, None, None, None, None
+    for group in GROUPS:
+        S.project_many_gather(dev, comm, *y_spans[group[0]], [layer0[n] for n in group], x_dev[group[0]], m, [y_dev[n] for n in group])
+    dev.synchronize()
+    dist.barrier()
+    if rank == 0:
+        rng = np.random.default_rng(99)
+        for group in GROUPS:
+            region, span_bytes = y_spans[group[0]]
+            gathered = comm.view(region, world * span_bytes // 4).cpu().numpy().reshape(world, span_bytes // 4)
+            x = x_dev[group[0]].cpu().numpy().reshape(m, -1)
+            at = 0
+            for n in group:
+                name, rows, cols, fmt = next(e for e in LAYER if e[0] == n)
+                per = rows // world
+                y = np.concatenate([gathered[r, at:at + m * per].reshape(m, per) for r in range(world)], axis=1)  # [m, rows]
+                at += (m * per + 3) // 4 * 4
+                pick = np.sort(rng.choice(rows, 16, replace=False))
+                rb = cols // BLOCK[fmt][0] * BLOCK[fmt][1]
+                sub = np.concatenate([full0[n][r * rb:(r + 1) * rb] for r in pick])
+                want = ref.matmul(fmt, sub, len(pick), cols, x, m, mode=0)
+                worst = max(worst, float(np.abs(y[:, pick] - want).max() / np.abs(y).max()))
+    dist.barrier()
+    return {"tp_rel_err": worst, "tp_checked": "layer 0, every input group, 16 sampled rows per matrix against the CPU oracle on the unsharded matrix"}
+
+
+def ep_parity(S, dev, torch, dist, rank, world):
+    """The expert-parallel MoE block (config 3 geometry, 40 tokens) against the single-GPU block on the same
+    weights: bit for bit."""
+    from ferrum_b200 import tp
+    H, E, F, USED, T = 2048, 256, 512, 8, 40
+    local = E // world
+    M = S.Matrix.from_packed
+    full = {k: random_matrix(fmt, rows, cols, seed) for k, (fmt, rows, cols, seed) in
+            dict(gate=(Q4_K, E * F, H, 911), up=(Q4_K, E * F, H, 912), down=(Q6_K, E * H, F, 913)).items()}
+    shared = [M(dev, E, H, 1, Q8_0, random_matrix(Q8_0, E, H, 910)), M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 914)),
+              M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 915)), M(dev, H, F, 1, Q6_K, random_matrix(Q6_K, H, F, 916))]
+    mine = S.MoeFfn(shared[0], M(dev, F, H, local, Q4_K, tp.shard_experts(full["gate"], Q4_K, F, H, E, rank, world)),
+                    M(dev, F, H, local, Q4_K, tp.shard_experts(full["up"], Q4_K, F, H, E, rank, world)),
+                    M(dev, H, F, local, Q6_K, tp.shard_experts(full["down"], Q6_K, H, F, E, rank, world)),
+                    shared[1], shared[2], shared[3], None, E, USED, H, F, F, False, True)
+    torch.manual_seed(11)
+    x = (torch.randn(T * H, device="cuda") * 0.12).contiguous()
+    comm = S.Comm(dev, rank, world, 4096 + T * USED * H * 4)
+    scratch = torch.zeros(S.moe_ffn_scratch_elems(dev, mine, T), dtype=torch.float32, device="cuda")
+    out = torch.zeros(T * H, dtype=torch.float32, device="cuda")
+    S.moe_ffn_ep(dev, comm, 4096, mine, rank * local, x, T, scratch, out)
+    dev.synchronize()
+    equal = True
+    if rank == 0:
+        whole = S.MoeFfn(shared[0], M(dev, F, H, E, Q4_K, full["gate"]), M(dev, F, H, E, Q4_K, full["up"]), M(dev, H, F, E, Q6_K, full["down"]),
+                         shared[1], shared[2], shared[3], None, E, USED, H, F, F, False, True)
+        ref_out = torch.zeros(T * H, dtype=torch.float32, device="cuda")
+        S.moe_ffn(dev, whole, x, T, torch.zeros(S.moe_ffn_scratch_elems(dev, whole, T), dtype=torch.float32, device="cuda"), ref_out)
+        dev.synchronize()
+        equal = bool(torch.equal(out, ref_out))
+    dist.barrier()
+    comm.close()
+    return {"ep_bits_equal": equal, "ep_checked": f"fq_moe_ffn_ep ({E} experts over {world} ranks, {T} tokens) against fq_moe_ffn on rank 0"}
+
+
 def moe_ep_bench(S, dev, stream, torch, dist, timed_ms, rank, world):
     """Config 3 with the 256 experts split over the ranks (router, shared expert and x replicated); the
     expert-sorted rows are exchanged by the peer-push all-gather inside the captured step."""
     H, E, F, USED = 2048, 256, 512, 8
     local = E // world
+    from ferrum_b200 import tp
     M = S.Matrix.from_packed
     f = S.MoeFfn(M(dev, E, H, 1, Q8_0, random_matrix(Q8_0, E, H, 900)),
-                 M(dev, F, H, local, Q4_K, random_matrix(Q4_K, local * F, H, 901 + 16 * rank)),
-                 M(dev, F, H, local, Q4_K, random_matrix(Q4_K, local * F, H, 902 + 16 * rank)),
-                 M(dev, H, F, local, Q6_K, random_matrix(Q6_K, local * H, F, 903 + 16 * rank)),
+                 M(dev, F, H, local, Q4_K, tp.shard_experts(random_matrix(Q4_K, E * F, H, 901), Q4_K, F, H, E, rank, world)),
+                 M(dev, F, H, local, Q4_K, tp.shard_experts(random_matrix(Q4_K, E * F, H, 902), Q4_K, F, H, E, rank, world)),
+                 M(dev, H, F, local, Q6_K, tp.shard_experts(random_matrix(Q6_K, E * H, F, 903), Q6_K, H, F, E, rank, world)),
                  M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 904)), M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 905)),
                  M(dev, H, F, 1, Q6_K, random_matrix(Q6_K, H, F, 906)), None, E, USED, H, F, F, False, True)
-    comm = S.Comm(dev, rank, world, 4096 + 1024 * USED * H * 4)
+    # Two exchange regions used in turn: consecutive exchanges of a communicator may not share a region.
+    region_bytes = 1024 * USED * H * 4
+    comm = S.Comm(dev, rank, world, 4096 + 2 * region_bytes)
     res = {}
     for T in (1, 1024):
         torch.manual_seed(7)  # the same tokens, hence the same routing, on every rank
@@ -435,14 +578,20 @@ def moe_ep_bench(S, dev, stream, torch, dist, timed_ms, rank, world):
         scratch = torch.zeros(S.moe_ffn_scratch_elems(dev, f, T), dtype=torch.float32, device="cuda")
         o = torch.zeros(T * H, dtype=torch.float32, device="cuda")
         torch.cuda.synchronize()
-        dev.capture_begin()
-        S.moe_ffn_ep(dev, comm, 4096, f, rank * local, x, T, scratch, o)
-        g = dev.capture_end()
+        graphs = []
+        for region in (4096, 4096 + region_bytes):
+            dev.capture_begin()
+            S.moe_ffn_ep(dev, comm, region, f, rank * local, x, T, scratch, o)
+            graphs.append(dev.capture_end())
+
+        def pair():
+            graphs[0].launch()
+            graphs[1].launch()
         with torch.cuda.stream(stream):
-            for _ in range(3):
-                g.launch()
-        reps = 10
-        ms = timed_ms(g.launch, reps) / reps
+            for _ in range(2):
+                pair()
+        reps = 5
+        ms = timed_ms(pair, reps) / (2 * reps)
         res[f"t{T}"] = {"us": round(ms * 1e3, 1), "experts_per_rank": local, "exchange_bytes": T * USED * H * 4}
     dev.synchronize()
     dist.barrier()
@@ -530,31 +679,40 @@ def cpu_baseline(m, budget_s):
 
 
 def run_reference(args):
+    """The reference's CPU path for the same step: `--layers` distinct layers of the layer set per step, `--steps`
+    timed steps after `--warmup`, on all host cores (the oracle restatement; the reference itself is a macOS-only
+    Rust/Metal crate and cannot be built here)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import ref  # the reference arm is the CPU oracle, timed
     threads = os.cpu_count() or 1
-    m = args.m
-    mats = cpu_layer()
+    m, layers = args.m, args.layers
+    stack = [cpu_layer(seed0=7 * l) for l in range(layers)]
     rng = np.random.default_rng(1234)
     xs = {c: rng.standard_normal((m, c)).astype(np.float32) for c in (5120, 6144, 17408)}
-    steps, warm = min(args.steps, 10), min(max(args.warmup, 1), 3)
+
+    def step():
+        for mats in stack:
+            cpu_pass(ref, mats, xs, m, threads)
+    steps, warm = args.steps, max(args.warmup, 1)
     for _ in range(warm):
-        cpu_pass(ref, mats, xs, m, threads)
+        step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        cpu_pass(ref, mats, xs, m, threads)
+        step()
     dt = (time.perf_counter() - t0) / steps
-    value = round(LAYER_BYTES / dt / 1e9, 3)
-    sample = (f"each step = one layer ({LAYER_BYTES} packed bytes) at M={m} on the host cores; the C restatement of the "
-              f"reference's CPU dequant + fp32 dot (the reference itself is a macOS-only Rust/Metal crate and cannot be built here)")
+    total = layers * LAYER_BYTES
+    value = round(total / dt / 1e9, 3)
+    sample = (f"each step = {layers} distinct layers ({total} packed bytes) at M={m} on {threads} host threads; the C restatement of "
+              f"the reference's CPU dequant + fp32 dot")
     print(json.dumps({
         "impl": "reference", "metric": "Q4_K_M decode projection weight GB/s (27B-class dense layer set)",
         "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
-        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"cfg1 dense 27B decode projection set, M={m}, CPU sample of one layer per step", "m": m},
+        "config": {"workload": f"cfg1 dense 27B decode projection set (q,k,v,o,gate,up Q4_K; down Q6_K), M={m}, "
+                               f"{layers} distinct layers = {total} packed bytes per step, on the host cores", "m": m, "layers": layers},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -597,7 +755,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--m", type=int, default=1, help="activation rows (1 = decode)")
-    ap.add_argument("--layers", type=int, default=3, help="distinct layers streamed per step and GPU (N GPUs shard layers x N layers by rows)")
+    ap.add_argument("--layers", type=int, default=3, help="one GPU: distinct layers streamed per step")
+    ap.add_argument("--tp-layers", type=int, default=0, help="more GPUs: layers of the row-sharded stack (default 64)")
     ap.add_argument("--eager", action="store_true", help="enqueue every step call by call instead of replaying a graph")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per matrix instead of one per input group")
     ap.add_argument("--nccl", action="store_true", help="multi-GPU: gather with NCCL (torch.distributed) instead of the peer-push kernel")

@@ -35,32 +35,37 @@ def _rank(rank, world, port, out_dir):
         x = torch.from_numpy(np.random.default_rng(6).standard_normal((m, cols)).astype(np.float32)).cuda()
         torch.cuda.synchronize()
         shard_bytes = m * per * 4
-        for step in range(3):  # the same flag words are reused with rising sequence numbers
-            y = comm.view(4096 + rank * shard_bytes, m * per)
+        regions = (4096, 4096 + 8192)  # consecutive exchanges use different regions
+        for step in range(4):  # the same flag words are reused with rising sequence numbers
+            at = regions[step % 2]
+            y = comm.view(at + rank * shard_bytes, m * per)
             S.project(d, w, x * float(step + 1), m, y)
-            comm.all_gather(4096, shard_bytes)
+            comm.all_gather(at, shard_bytes)
             d.synchronize()
-            got = tp.gathered_to_rows(comm.view(4096, world * m * per), m, rows, world).cpu().numpy()
+            got = tp.gathered_to_rows(comm.view(at, world * m * per), m, rows, world).cpu().numpy()
             want = ref.matmul(ref.Q4_K, packed, rows, cols, (x * float(step + 1)).cpu().numpy(), m)
             assert ref.rel_err(got, want) <= 1e-3, (rank, step)
-        # captured: projection + gather replayed twice
-        y = comm.view(4096 + rank * shard_bytes, m * per)
+        # the region of the exchange before is refused
+        with pytest.raises(S.ParameterError):
+            comm.all_gather(regions[1], shard_bytes)
+        # captured: two projections + gathers on alternating regions, replayed twice
         d.capture_begin()
-        S.project(d, w, x, m, y)
-        comm.all_gather(4096, shard_bytes)
+        for at in regions:
+            S.project(d, w, x, m, comm.view(at + rank * shard_bytes, m * per))
+            comm.all_gather(at, shard_bytes)
         g = d.capture_end()
         for _ in range(2):
             g.launch()
             d.synchronize()
-        got = tp.gathered_to_rows(comm.view(4096, world * m * per), m, rows, world).cpu().numpy()
-        assert ref.rel_err(got, ref.matmul(ref.Q4_K, packed, rows, cols, x.cpu().numpy(), m)) <= 1e-3
-        # compute and exchange in one kernel (decode widths), q|k-like pair sharing x; m = 8 takes the
-        # project-then-gather route of the same call
+        for at in regions:
+            got = tp.gathered_to_rows(comm.view(at, world * m * per), m, rows, world).cpu().numpy()
+            assert ref.rel_err(got, ref.matmul(ref.Q4_K, packed, rows, cols, x.cpu().numpy(), m)) <= 1e-3
+        # compute and exchange in one kernel (decode and verify widths), q|k-like pair sharing x
         rows2 = 256
         per2 = rows2 // world
         packed2 = ref.random_matrix(ref.Q4_K, rows2, cols, seed=7)
         w2 = S.Matrix.from_packed(d, per2, cols, 1, ref.Q4_K, tp.shard_packed(packed2, ref.Q4_K, rows2, cols, rank, world))
-        for mm in (1, 4, 8):
+        for mm in (1, 4, 8, 16):
             xm = torch.from_numpy(np.random.default_rng(20 + mm).standard_normal((mm, cols)).astype(np.float32)).cuda()
             shard = mm * (per + per2) * 4  # this rank's slice: [mm][per] then [mm][per2]
             region = 65536
@@ -122,17 +127,17 @@ def _ep_rank(rank, world, port, out_dir):
                         M(d, ef, hidden, local, ref.Q4_K, experts_of(up_e, ref.Q4_K, ef, hidden, first, local)),
                         M(d, hidden, ef, local, ref.Q6_K, experts_of(down_e, ref.Q6_K, hidden, ef, first, local)),
                         shared[1], shared[2], shared[3], None, experts, used, hidden, ef, ef, False, True)
-        comm = S.Comm(d, rank, world, 4096 + 64 * used * hidden * 4)
-        for m in (1, 3, 40):  # per-route GEMVs (m * used <= 32) and the grouped tensor-core GEMM
+        half = 300 * used * hidden * 4
+        comm = S.Comm(d, rank, world, 4096 + 2 * half)
+        for i, m in enumerate((1, 3, 40, 300)):  # per-route GEMVs (m * used <= 32), the grouped integer kernel, the grouped GEMM
             x = torch.from_numpy((np.random.default_rng(m).standard_normal((m, hidden)) * 0.12).astype(np.float32)).cuda()
             n = S.moe_ffn_scratch_elems(d, whole, m)
             want = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
             S.moe_ffn(d, whole, x, m, torch.zeros(n, dtype=torch.float32, device="cuda"), want)
             got = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
-            S.moe_ffn_ep(d, comm, 4096, mine, first, x, m, torch.zeros(n, dtype=torch.float32, device="cuda"), got)
+            S.moe_ffn_ep(d, comm, 4096 + (i % 2) * half, mine, first, x, m, torch.zeros(n, dtype=torch.float32, device="cuda"), got)
             d.synchronize()
             assert torch.equal(got, want), (rank, m)
-            dist.barrier()  # nobody overwrites the symmetric buffer while a peer still combines from it
         open(os.path.join(out_dir, f"ep{rank}"), "w").write("ok")
         comm.close()
     finally:
