@@ -12,8 +12,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libferrum_b200.so")
 
 OK, ERR_SHAPE, ERR_RANGE, ERR_DEVICE, ERR_ALIAS, ERR_WEIGHT, ERR_SYNC, ERR_TIMEOUT, ERR_CUDA, ERR_PARAM, \
-    ERR_UNSUPPORTED = range(11)
-Q8_0, Q4_K, Q6_K = 8, 12, 14
+    ERR_UNSUPPORTED, ERR_GGUF = range(12)
+Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
 F32, BF16 = 0, 30
 
 
@@ -25,6 +25,16 @@ class MatrixInfo(C.Structure):
 class Counters(C.Structure):
     _fields_ = [("dispatches", C.c_uint64), ("synchronizes", C.c_uint64),
                 ("bytes_uploaded", C.c_uint64), ("bytes_downloaded", C.c_uint64)]
+
+
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char * 260), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4), ("type_id", C.c_uint32),
+                ("offset", C.c_uint64), ("byte_len", C.c_uint64)]
+
+
+class GgufInfo(C.Structure):
+    _fields_ = [("version", C.c_uint32), ("alignment", C.c_uint32), ("file_len", C.c_uint64), ("tensor_data_offset", C.c_uint64),
+                ("tensor_count", C.c_uint64), ("metadata_count", C.c_uint64)]
 
 
 class MoeFfnDesc(C.Structure):
@@ -63,6 +73,21 @@ SIGNATURES = {
     "fq_matrix_create": (_I, [_P, _I, _U64, _U64, _U64, _P, _Z, C.POINTER(_P)]),
     "fq_matrix_destroy": (_I, [_P]),
     "fq_matrix_get_info": (_I, [_P, C.POINTER(MatrixInfo)]),
+    "fq_gguf_open": (_I, [C.c_char_p, _I, _U64, C.POINTER(_P), C.c_char_p, _Z]),
+    "fq_gguf_close": (_I, [_P]),
+    "fq_gguf_last_error": (C.c_char_p, [_P]),
+    "fq_gguf_info": (_I, [_P, C.POINTER(GgufInfo)]),
+    "fq_gguf_tensor_by_name": (_I, [_P, C.c_char_p, C.POINTER(GgufTensor)]),
+    "fq_gguf_tensor_by_index": (_I, [_P, _U64, C.POINTER(GgufTensor)]),
+    "fq_gguf_read_tensor": (_I, [_P, C.c_char_p, _P, _Z]),
+    "fq_gguf_metadata_u64": (_I, [_P, C.c_char_p, C.POINTER(_U64)]),
+    "fq_gguf_metadata_f64": (_I, [_P, C.c_char_p, C.POINTER(C.c_double)]),
+    "fq_gguf_metadata_string": (_I, [_P, C.c_char_p, C.c_char_p, _Z]),
+    "fq_gguf_metadata_array": (_I, [_P, C.c_char_p, C.POINTER(_U32), C.POINTER(_U64), C.POINTER(_U64)]),
+    "fq_block_layout": (_I, [_U32, C.POINTER(_U32), C.POINTER(_U32)]),
+    "fq_matrix_from_gguf": (_I, [_P, _P, C.c_char_p, _U64, _U64, _U64, _I, C.POINTER(_P)]),
+    "fq_q3k_to_q6k": (_I, [_P, _Z, _P]),
+    "fq_quantize_q8_0": (_I, [_P, _Z, _P]),
     "fq_project": (_I, [_P, _P, _P, _I, _Z, _Z, _P, _I, _Z]),
     "fq_project_many": (_I, [_P, C.POINTER(_P), _Z, _P, _I, _Z, _Z, C.POINTER(_P), _I]),
     "fq_project_id": (_I, [_P, _P, _P, _Z, _P, _Z, _Z, _P, _Z]),

@@ -42,6 +42,7 @@ extern "C" const char *fq_status_name(int status) {
     case FQ_ERR_CUDA: return "cuda";
     case FQ_ERR_PARAM: return "parameter";
     case FQ_ERR_UNSUPPORTED: return "unsupported";
+    case FQ_ERR_GGUF: return "gguf";
     default: return "unknown";
     }
 }
@@ -377,8 +378,9 @@ static int validate_payload(fq_device *dev, int format, const uint8_t *p, size_t
     for (size_t o = 0; o < len; o += bb) {
         const uint8_t *b = p + o;
         auto half_at = [&](int at) { return half_bits_to_float((uint16_t)(b[at] | (b[at + 1] << 8))); };
-        if (format == FQ_Q4_K) {
-            if (!finite(half_at(0)) || !finite(half_at(2))) return fq_fail(dev, FQ_ERR_WEIGHT, "Q4_K scale must be finite (block %zu)", o / bb);
+        if (format == FQ_Q4_K || format == FQ_Q5_K) {
+            if (!finite(half_at(0)) || !finite(half_at(2)))
+                return fq_fail(dev, FQ_ERR_WEIGHT, "%s scale must be finite (block %zu)", format == FQ_Q4_K ? "Q4_K" : "Q5_K", o / bb);
         } else if (format == FQ_Q6_K) {
             if (!finite(half_at(208))) return fq_fail(dev, FQ_ERR_WEIGHT, "Q6_K scale must be finite (block %zu)", o / bb);
         } else {
@@ -398,6 +400,7 @@ extern "C" int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint6
     uint32_t el, bb;
     switch (format) {
     case FQ_Q4_K: el = 256; bb = 144; break;
+    case FQ_Q5_K: el = 256; bb = 176; break;
     case FQ_Q6_K: el = 256; bb = 210; break;
     case FQ_Q8_0: el = 32; bb = 34; break;
     default: return fq_fail(dev, FQ_ERR_WEIGHT, "GGML type %d has no kernel", format);

@@ -3,6 +3,7 @@
 // Layouts (little-endian, f16 = IEEE binary16), as in the reference's `block_q4_K`, `block_q6_K`,
 // `block_q8_0` (src/metal/shaders/hybrid.metal:23-26) and src/quantization.rs:50-73:
 //   Q4_K  144 B / 256 values: f16 d @0, f16 dmin @2, scales[12] @4, qs[128] @16
+//   Q5_K  176 B / 256 values: f16 d @0, f16 dmin @2, scales[12] @4, qh[32] @16, qs[128] @48
 //   Q6_K  210 B / 256 values: ql[128] @0, qh[64] @128, int8 scales[16] @192, f16 d @208
 //   Q8_0   34 B /  32 values: f16 d @0, int8 qs[32] @2
 //
@@ -19,6 +20,7 @@
 
 template <int FMT> struct BlockTraits;
 template <> struct BlockTraits<FQ_Q4_K> { static constexpr int EL = 256, BB = 144; };
+template <> struct BlockTraits<FQ_Q5_K> { static constexpr int EL = 256, BB = 176; };
 template <> struct BlockTraits<FQ_Q6_K> { static constexpr int EL = 256, BB = 210; };
 template <> struct BlockTraits<FQ_Q8_0> { static constexpr int EL = 32, BB = 34; };
 
@@ -50,7 +52,7 @@ __device__ __forceinline__ float q6k_value(float d, int scale, uint32_t q) {
     return __fmul_rn(__fmul_rn(d, (float)scale), (float)q - 32.0f);
 }
 
-// Device layouts.  Q4_K rows are the GGUF bytes.  Q6_K and Q8_0 rows are the same bytes regrouped by
+// Device layouts.  Q4_K and Q5_K rows are the GGUF bytes.  Q6_K and Q8_0 rows are the same bytes regrouped by
 // field at load time so that every field is 16-byte aligned (210- and 34-byte blocks are not): with nb
 // blocks in the row,
 //   Q6_K: ql of block b at 128 b, qh at 128 nb + 64 b, scales at 192 nb + 16 b, d at 208 nb + 2 b,
@@ -59,6 +61,7 @@ __device__ __forceinline__ float q6k_value(float d, int scale, uint32_t q) {
 __host__ __device__ inline uint32_t fq_row_pitch(int format, uint32_t cols) {
     switch (format) {
     case FQ_Q4_K: return cols / 256 * 144;
+    case FQ_Q5_K: return cols / 256 * 176;
     case FQ_Q6_K: return (cols / 256 * 210 + 15u) & ~15u;
     default: return (cols / 32 * 34 + 15u) & ~15u;
     }
@@ -74,6 +77,18 @@ template <> __device__ __forceinline__ float decode_at<FQ_Q4_K>(const uint8_t *r
     q4k_scale_min(blk + 4, j, sc, mn);
     const uint8_t v = blk[16 + 32 * (j >> 1) + l];
     const uint32_t q = (j & 1) ? (v >> 4) : (v & 0xFu);
+    return q4k_value(load_f16(blk), load_f16(blk + 2), sc, mn, q);
+}
+
+// Q5_K (`q45_k` with the high bits, src/diffusion/tests.rs:811-840): bit j of qh[l] is the fifth bit of value l of
+// sub-block j.
+template <> __device__ __forceinline__ float decode_at<FQ_Q5_K>(const uint8_t *row, uint32_t, uint32_t b, int idx) {
+    const uint8_t *blk = row + (size_t)b * 176;
+    const int j = idx >> 5, l = idx & 31;
+    uint32_t sc, mn;
+    q4k_scale_min(blk + 4, j, sc, mn);
+    const uint8_t v = blk[48 + 32 * (j >> 1) + l];
+    const uint32_t q = ((j & 1) ? (v >> 4) : (v & 0xFu)) + (((blk[16 + l] >> j) & 1u) << 4);
     return q4k_value(load_f16(blk), load_f16(blk + 2), sc, mn, q);
 }
 

@@ -109,6 +109,7 @@ k_get_rows(const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t
 template <typename F> int dispatch_format(fq_device *dev, uint32_t format, F &&f) {
     switch (format) {
     case FQ_Q4_K: f(std::integral_constant<int, FQ_Q4_K>{}); return FQ_OK;
+    case FQ_Q5_K: f(std::integral_constant<int, FQ_Q5_K>{}); return FQ_OK;
     case FQ_Q6_K: f(std::integral_constant<int, FQ_Q6_K>{}); return FQ_OK;
     case FQ_Q8_0: f(std::integral_constant<int, FQ_Q8_0>{}); return FQ_OK;
     default: return fq_fail(dev, FQ_ERR_UNSUPPORTED, "format %u has no kernel", format);

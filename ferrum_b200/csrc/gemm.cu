@@ -150,6 +150,7 @@ __device__ __forceinline__ float small_to_float(uint32_t q, float bias = 0.f) {
 // in flight while the current one is decoded: a thread's stream is otherwise bound by memory latency.
 template <int FMT> struct Raw;
 template <> struct Raw<FQ_Q4_K> { uint4 hdr, q0, q1; };
+template <> struct Raw<FQ_Q5_K> { uint4 hdr, q0, q1, h0, h1; };
 template <> struct Raw<FQ_Q6_K> { uint4 l0, l1, h0, h1; uint32_t sc, d; };
 template <> struct Raw<FQ_Q8_0> { uint32_t q[8]; uint32_t d; };
 
@@ -163,6 +164,15 @@ __device__ __forceinline__ Raw<FMT> load_raw(const uint8_t *rowp, uint32_t nblk,
         r.hdr = *reinterpret_cast<const uint4 *>(blk);
         r.q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c);
         r.q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
+    } else if constexpr (FMT == FQ_Q5_K) {
+        // As Q4_K, with the 32 bytes of fifth bits (bit j of qh[l] belongs to value l of sub-block j).
+        const uint8_t *blk = rowp + (size_t)(kb >> 2) * 176;
+        const uint32_t c = kb & 3;
+        r.hdr = *reinterpret_cast<const uint4 *>(blk);
+        r.h0 = *reinterpret_cast<const uint4 *>(blk + 16);
+        r.h1 = *reinterpret_cast<const uint4 *>(blk + 32);
+        r.q0 = *reinterpret_cast<const uint4 *>(blk + 48 + 32 * c);
+        r.q1 = *reinterpret_cast<const uint4 *>(blk + 64 + 32 * c);
     } else if constexpr (FMT == FQ_Q6_K) {
         // k-block kb of superblock b: half n = (kb % 4) / 2, 32-groups i = 2 h and 2 h + 1 with h = kb % 2;
         // part selects the group.  Device layout of blocks.cuh.
@@ -198,7 +208,7 @@ __device__ __forceinline__ uint32_t pack_term(float a, float b, bool lo) {
 // residue), two per register.
 template <int FMT>
 __device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int part, bool lo, uint32_t (&out)[16]) {
-    if constexpr (FMT == FQ_Q4_K) {
+    if constexpr (FMT == FQ_Q4_K || FMT == FQ_Q5_K) {
         const uint32_t c = kb & 3;
         const uint4 hdr = r.hdr;
         // `get_scale_min_k4` on the three scale words (hdr.y = scales[0..3], .z = [4..7], .w = [8..11]).
@@ -221,7 +231,11 @@ __device__ __forceinline__ void decode_raw(const Raw<FMT> &r, uint32_t kb, int p
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const uint32_t v = part ? (w[i] >> 4) : w[i];
-            const uint32_t n4 = v & 0x0F0F0F0Fu; // one quant per byte; each byte moves into a float mantissa with one PRMT
+            uint32_t n4 = v & 0x0F0F0F0Fu; // one quant per byte; each byte moves into a float mantissa with one PRMT
+            if constexpr (FMT == FQ_Q5_K) {
+                const uint32_t hw = i == 0 ? r.h0.x : i == 1 ? r.h0.y : i == 2 ? r.h0.z : i == 3 ? r.h0.w : i == 4 ? r.h1.x : i == 5 ? r.h1.y : i == 6 ? r.h1.z : r.h1.w;
+                n4 |= ((hw >> j) & 0x01010101u) << 4;
+            }
             const float f0 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7440)), ds23), dm);
             const float f1 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7441)), ds23), dm);
             const float f2 = __fsub_rn(__fmaf_rn(ds, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7442)), ds23), dm);
@@ -651,6 +665,7 @@ template <int BN, typename YT, int MODE>
 int launch_fmt(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uint32_t b_bytes, uint32_t m_rows, const GemmMany &many = GemmMany{}) {
     switch (a.format) {
     case FQ_Q4_K: return launch<FQ_Q4_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev, many);
+    case FQ_Q5_K: return launch<FQ_Q5_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev, many);
     case FQ_Q6_K: return launch<FQ_Q6_K, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev, many);
     default: return launch<FQ_Q8_0, BN, YT, MODE>(dev, a, map, b_bytes, m_rows, dev->status_dev, many);
     }
@@ -689,7 +704,7 @@ static const void *x_as_bf16(fq_device *dev, const void *x, size_t n) {
 // split of k_gemm_tc's MODE 2, in slices of activation rows whose split copy fits the handle's scratch.
 int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
     if (a.x_dtype != a.y_dtype || a.cols % BK || a.ids || a.offsets) return FQ_ERR_UNSUPPORTED;
-    if (a.format != FQ_Q4_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
+    if (a.format != FQ_Q4_K && a.format != FQ_Q5_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
     if (a.format == FQ_Q4_K && (a.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
     if (a.m <= (uint32_t)FQ_GEMV_MAX_M) return FQ_ERR_UNSUPPORTED; // decode and verify widths: the fp32 kernels serve them
     CUtensorMap map;
@@ -730,7 +745,7 @@ int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     if (count < 2 || count > 4) return FQ_ERR_UNSUPPORTED;
     const ProjectArgs &f = a[0];
     if (f.x_dtype != FQ_BF16 || f.y_dtype != FQ_BF16 || f.cols % BK || f.ids || f.offsets) return FQ_ERR_UNSUPPORTED;
-    if (f.format != FQ_Q4_K && f.format != FQ_Q6_K && f.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
+    if (f.format != FQ_Q4_K && f.format != FQ_Q5_K && f.format != FQ_Q6_K && f.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
     if (f.format == FQ_Q4_K && (f.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
     if (f.m <= (uint32_t)FQ_GEMV_MAX_M) return FQ_ERR_UNSUPPORTED;
     GemmMany many{};
@@ -759,7 +774,7 @@ int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
 // handle's scratch first) or BF16; y is F32 or BF16.
 int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t total_rows) {
     if (a.cols % BK || !a.offsets) return FQ_ERR_UNSUPPORTED;
-    if (a.format != FQ_Q4_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
+    if (a.format != FQ_Q4_K && a.format != FQ_Q5_K && a.format != FQ_Q6_K && a.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
     if (a.format == FQ_Q4_K && (a.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
     if (a.groups > 65535 || total_rows == 0) return FQ_ERR_UNSUPPORTED;
     const void *xb = a.x;

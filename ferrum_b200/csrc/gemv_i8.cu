@@ -133,6 +133,22 @@ struct Q4Raw {
         qb = ldw128(blk + 80 + 16 * t);
     }
 };
+// Q5_K: as Q4_K, plus the 16 bytes of qh under this thread's run (bit j of qh[l] = fifth bit of value l of sub-block j).
+struct Q5Raw {
+    uint4 hdr, qa, qb, qh;
+    __device__ __forceinline__ void load(const uint8_t *row, uint32_t, uint32_t b, int t) {
+        const uint8_t *blk = row + (size_t)b * 176;
+        hdr = ldw128(blk);
+        qh = ldw128(blk + 16 + 16 * (t & 1));
+        qa = ldw128(blk + 48 + 16 * t);
+        qb = ldw128(blk + 112 + 16 * t);
+    }
+};
+struct Q6Raw;
+template <int FMT> struct RawOf { using type = Q6Raw; };
+template <> struct RawOf<FQ_Q4_K> { using type = Q4Raw; };
+template <> struct RawOf<FQ_Q5_K> { using type = Q5Raw; };
+template <int FMT> constexpr bool is_k45 = FMT == FQ_Q4_K || FMT == FQ_Q5_K;
 struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
     uint4 q0, q1, qh; // ql of 32-groups 0|2 and 1|3 of half n, qh of half n: run lh (16 bytes each)
     uint2 sc;         // the 8 scales of half t % 2 (the half whose groups this thread sums up)
@@ -153,12 +169,12 @@ struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
 //         feeds (values 64 c + 16 (t % 2) + [0, 16), + 32), sx = sums of sub-blocks 4u .. 4u+3.
 //   Q6_K: xb[i] = the 16 bytes under its run of 32-group i, sx = byte sums of 16-groups 8u .. 8u+7.
 template <int FMT> struct Act {
-    uint4 xb[FMT == FQ_Q4_K ? 2 : 4];
+    uint4 xb[is_k45<FMT> ? 2 : 4];
     uint4 sx;
     float inv;
     __device__ __forceinline__ void load(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) {
         const int plane = g >> 2, u = t & 1;
-        if constexpr (FMT == FQ_Q4_K) {
+        if constexpr (is_k45<FMT>) {
             const bool feeds = (t >> 1) == (g & 1);
             const int chunk = (((g & 3) >> 1) ? 2 : 0) + (t >> 1);
             const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 64 * chunk + 16 * (t & 1);
@@ -185,13 +201,13 @@ __device__ __forceinline__ void superblock_dot(const RawT (&cur)[2], const Act<F
     //   Q6_K: group j = the k slots of quad thread j.
     //   Q4_K: group j = chunk j; thread t holds chunk t / 2 in its first operand word (k slots 4t ..)
     //         and chunk 2 + t / 2 in its second (k slots 16 + 4t ..).
-    const bool second = FMT == FQ_Q4_K && ((g & 3) >> 1); // Q4_K: the group sits in the second operand word
+    const bool second = is_k45<FMT> && ((g & 3) >> 1); // Q4_K / Q5_K: the group sits in the second operand word
     // It reads columns 2t, 2t+1 of the accumulators: scale groups 2 (t & 1), 2 (t & 1) + 1, plane t >> 1.
     const int u = t & 1;
     const float plane_weight = (t >> 1) ? 1.f : 256.f;
     (void)second;
     (void)u;
-    if constexpr (FMT == FQ_Q4_K) {
+    if constexpr (is_k45<FMT>) {
         // The four scales and minimums of sub-blocks 4u .. 4u+3, one per byte.
         uint32_t sc4[2], mn4[2];
         float dsc[2], dmn[2];
@@ -213,6 +229,12 @@ __device__ __forceinline__ void superblock_dot(const RawT (&cur)[2], const Act<F
                 const uint32_t wd = word_of(i < 4 ? cur[r].qa : cur[r].qb, i & 3);
                 lo[r][i] = wd & 0x0F0F0F0Fu;
                 hi[r][i] = (wd >> 4) & 0x0F0F0F0Fu;
+                if constexpr (FMT == FQ_Q5_K) {
+                    // The fifth bits: qa is chunk t / 2 (sub-blocks 2 (t / 2), + 1), qb chunk 2 + t / 2 (four bits on).
+                    const uint32_t v = word_of(cur[r].qh, i & 3) >> (2 * (t >> 1) + (i < 4 ? 0 : 4));
+                    lo[r][i] |= (v << 4) & 0x10101010u;
+                    hi[r][i] |= (v << 3) & 0x10101010u;
+                }
             }
 #pragma unroll
         for (int m = 0; m < MT; m++) {
@@ -290,7 +312,7 @@ template <int FMT, int MT>
 __global__ void __launch_bounds__(MT >= 3 ? 256 : MT == 2 ? 384 : MAX_WARPS * 32)
 k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *__restrict__ prep, PrepI8 L,
           const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts, const __grid_constant__ TpPush P) {
-    using Raw = std::conditional_t<FMT == FQ_Q4_K, Q4Raw, Q6Raw>;
+    using Raw = typename RawOf<FMT>::type;
     __shared__ float red[2][MAX_WARPS - 1][MT * 2][8];
     const int WARPS = blockDim.x >> 5;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -376,7 +398,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
         }
         superblock_dot<FMT, MT>(c, ac, t, g, yacc);
     };
-    if (FMT == FQ_Q4_K && (iters & 1u) == 0) {
+    if (is_k45<FMT> && (iters & 1u) == 0) {
         // An even count: the two register sets swap roles instead of being copied (Q4_K only: with Q6_K's larger
         // register sets the second copy of the loop body spills).
         for (uint32_t it = 0; it < iters; it += 2) {
@@ -488,7 +510,7 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
 int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count) {
     if (count == 0 || count > (uint32_t)MAX_TARGETS) return FQ_ERR_UNSUPPORTED;
     const ProjectArgs &f = a[0];
-    if ((f.format != FQ_Q4_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
+    if ((f.format != FQ_Q4_K && f.format != FQ_Q5_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
     if (f.cols % 256 || f.row_bytes % 16) return FQ_ERR_UNSUPPORTED;
     for (uint32_t i = 1; i < count; i++)
         if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].m != f.m || a[i].ids != f.ids ||
@@ -517,6 +539,7 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
         return rc;
     cudaError_t e;
     if (f.format == FQ_Q4_K) e = launch<FQ_Q4_K, 1>(dev, a, count, prep, L, expert);
+    else if (f.format == FQ_Q5_K) e = launch<FQ_Q5_K, 1>(dev, a, count, prep, L, expert);
     else e = launch<FQ_Q6_K, 1>(dev, a, count, prep, L, expert);
     if (int rc = fq_check_cuda(dev, e, "gemv launch")) return rc;
     return fq_end_enqueue(dev, "gemv_i8", 2);

@@ -41,12 +41,17 @@ using namespace fqk;
 constexpr int NT_MAX_TARGETS = 4;
 constexpr uint32_t NT_SMEM_MAX = 222 * 1024;
 
+// A stage of a warp's ring: the packed bytes of one superblock of 16 weight rows.  ROW = bytes between rows in
+// shared memory (Q4_K: 160, so that the 8-byte reads of rows g .. g + 3 fall on different banks).
 template <int FMT> struct StageNT;
 template <> struct StageNT<FQ_Q4_K> {
-    static constexpr uint32_t ROW = 144, PIECES = 16 * 9, BYTES = 16 * 144;
+    static constexpr uint32_t ROW = 160, SRC = 144, PIECES = 16 * 9, BYTES = 16 * 160;
+};
+template <> struct StageNT<FQ_Q5_K> {
+    static constexpr uint32_t ROW = 176, SRC = 176, PIECES = 16 * 11, BYTES = 16 * 176;
 };
 template <> struct StageNT<FQ_Q6_K> { // per row ql[128] | qh[64] | scales[16]; then 4 bytes per row holding d
-    static constexpr uint32_t ROW = 208, PIECES = 16 * 13, BYTES = 16 * 208 + 64;
+    static constexpr uint32_t ROW = 208, SRC = 210, PIECES = 16 * 13, BYTES = 16 * 208 + 64;
 };
 
 struct NtJob {
@@ -187,8 +192,14 @@ __device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSme
     const uint8_t *fragp[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) fragp[nt] = A.frag + (size_t)(8 * nt + g) * A.row_stride + (size_t)bb * 512 + 16 * t;
-    if constexpr (FMT == FQ_Q4_K) {
-        const uint8_t *r0 = stage + g * 144, *r1 = r0 + 8 * 144;
+    if constexpr (FMT == FQ_Q4_K || FMT == FQ_Q5_K) {
+        constexpr uint32_t ROW = StageNT<FMT>::ROW, QS = FMT == FQ_Q4_K ? 16 : 48;
+        const uint8_t *r0 = stage + g * ROW, *r1 = r0 + 8 * ROW;
+        uint2 h0 = make_uint2(0u, 0u), h1 = make_uint2(0u, 0u); // Q5_K: qh under this thread's eight values of every sub-block
+        if constexpr (FMT == FQ_Q5_K) {
+            h0 = *reinterpret_cast<const uint2 *>(r0 + 16 + 8 * t);
+            h1 = *reinterpret_cast<const uint2 *>(r1 + 16 + 8 * t);
+        }
         // Scales and minimums of sub-blocks 0..3 and 4..7, one per byte (`get_scale_min_k4`).
         uint32_t sc4[2][2], mn4[2][2];
         float d[2], dmin[2];
@@ -220,12 +231,19 @@ __device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSme
         }
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            const uint2 q0 = *reinterpret_cast<const uint2 *>(r0 + 16 + 32 * c + 8 * t), q1 = *reinterpret_cast<const uint2 *>(r1 + 16 + 32 * c + 8 * t);
+            const uint2 q0 = *reinterpret_cast<const uint2 *>(r0 + QS + 32 * c + 8 * t), q1 = *reinterpret_cast<const uint2 *>(r1 + QS + 32 * c + 8 * t);
 #pragma unroll
             for (int half = 0; half < 2; half++) { // low nibbles = sub-block 2c, high nibbles = sub-block 2c + 1
                 const int j = 2 * c + half;
-                const uint32_t a0 = (half ? q0.x >> 4 : q0.x) & 0x0F0F0F0Fu, a1 = (half ? q1.x >> 4 : q1.x) & 0x0F0F0F0Fu;
-                const uint32_t a2 = (half ? q0.y >> 4 : q0.y) & 0x0F0F0F0Fu, a3 = (half ? q1.y >> 4 : q1.y) & 0x0F0F0F0Fu;
+                uint32_t a0 = (half ? q0.x >> 4 : q0.x) & 0x0F0F0F0Fu, a1 = (half ? q1.x >> 4 : q1.x) & 0x0F0F0F0Fu;
+                uint32_t a2 = (half ? q0.y >> 4 : q0.y) & 0x0F0F0F0Fu, a3 = (half ? q1.y >> 4 : q1.y) & 0x0F0F0F0Fu;
+                if constexpr (FMT == FQ_Q5_K) { // bit j of the qh bytes becomes bit 4
+                    auto fifth = [j](uint32_t hw) { return (j < 4 ? hw << (4 - j) : hw >> (j - 4)) & 0x10101010u; };
+                    a0 |= fifth(h0.x);
+                    a1 |= fifth(h1.x);
+                    a2 |= fifth(h0.y);
+                    a3 |= fifth(h1.y);
+                }
                 const int s0 = byte_u(sc4[0][j >> 2], j & 3), s1 = byte_u(sc4[1][j >> 2], j & 3);
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
@@ -408,15 +426,16 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
 
     // Producer side of the warp's ring: item = (tile, superblock of the slice), in the order they are consumed.
     // A lane copies the same 16-byte pieces of every item, so their offsets from the tile's first row are
-    // worked out once per tile.  Q4_K: piece p = lane + 32 i is bytes 16 (p % 9) .. of row p / 9.  Q6_K: pieces
+    // worked out once per tile.  Q4_K (Q5_K): piece p = lane + 32 i is bytes 16 (p % 9) .. of row p / 9 (11).  Q6_K: pieces
     // 0..127 are ql (row p / 8), 128..191 qh (row / 4), 192..207 the scales, 208..223 the 4 bytes holding d.
-    constexpr int NP = FMT == FQ_Q4_K ? 5 : 7;
+    constexpr int NP = FMT == FQ_Q4_K ? 5 : FMT == FQ_Q5_K ? 6 : 7;
+    constexpr uint32_t PER_ROW = St::SRC / 16; // Q4_K / Q5_K: 16-byte pieces per row and superblock
     uint32_t p_tile = first, p_bb = 0, p_stage = 0;
     const uint8_t *p_base = nullptr;
     uint32_t p_off[NP];
     auto piece_row = [&](int i) -> uint32_t {
         const uint32_t p = lane + 32 * i;
-        if constexpr (FMT == FQ_Q4_K) return p / 9;
+        if constexpr (FMT != FQ_Q6_K) return p / PER_ROW;
         return i < 4 ? p / 8 : i < 6 ? (p - 128) / 4 : (lane & 15);
     };
     auto start_tile = [&](uint32_t tile) {
@@ -427,7 +446,7 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
         for (int i = 0; i < NP; i++) {
             const uint32_t p = lane + 32 * i, r = min(piece_row(i), last);
             uint32_t in_row;
-            if constexpr (FMT == FQ_Q4_K) in_row = 16 * (p % 9);
+            if constexpr (FMT != FQ_Q6_K) in_row = 16 * (p % PER_ROW);
             else in_row = i < 4 ? 16 * (p % 8) : i < 6 ? J.nblk * 128 + 16 * (p % 4) : lane < 16 ? J.nblk * 192 : J.nblk * 208;
             p_off[i] = r * J.pitch + in_row;
         }
@@ -440,8 +459,8 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
 #pragma unroll
             for (int i = 0; i < NP; i++) {
                 const uint32_t p = lane + 32 * i;
-                if constexpr (FMT == FQ_Q4_K) {
-                    if (p < St::PIECES) cp_async16(dst + 16 * p, p_base + (p_off[i] + b * 144));
+                if constexpr (FMT != FQ_Q6_K) {
+                    if (p < St::PIECES) cp_async16(dst + St::ROW * (p / PER_ROW) + 16 * (p % PER_ROW), p_base + (p_off[i] + b * St::SRC));
                 } else {
                     if (i < 4) cp_async16(dst + 208 * (p / 8) + 16 * (p % 8), p_base + (p_off[i] + b * 128));
                     else if (i < 6) cp_async16(dst + 208 * ((p - 128) / 4) + 128 + 16 * (p % 4), p_base + (p_off[i] + b * 64));
@@ -618,7 +637,7 @@ uint8_t *launch_prep(fq_device *dev, int format, const ProjectArgs &f, uint32_t 
     dev->xprep_turn ^= 1u;
     uint8_t *prep = (uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0);
     const uint32_t warps = xrows * L.nblk;
-    if (format == FQ_Q4_K)
+    if (format == FQ_Q4_K || format == FQ_Q5_K) // the same fragment order
         e = launch_pdl(k_prep_nt<FQ_Q4_K>, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, xrows, src, src_div, range, range_stride, L, prep);
     else
         e = launch_pdl(k_prep_nt<FQ_Q6_K>, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, xrows, src, src_div, range, range_stride, L, prep);
@@ -667,13 +686,14 @@ template <int FMT, int NT> int launch_dense(fq_device *dev, const ProjectArgs *a
 int fq_launch_gemv_nt_many(fq_device *dev, const ProjectArgs *a, uint32_t count) {
     if (count == 0 || count > (uint32_t)NT_MAX_TARGETS) return FQ_ERR_UNSUPPORTED;
     const ProjectArgs &f = a[0];
-    if ((f.format != FQ_Q4_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
+    if ((f.format != FQ_Q4_K && f.format != FQ_Q5_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
     if (f.cols % 256 || f.row_bytes % 16 || f.ids || f.m < 2 || f.m > 16) return FQ_ERR_UNSUPPORTED;
     for (uint32_t i = 1; i < count; i++)
         if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].m != f.m || a[i].ids ||
             a[i].x_dtype != FQ_F32 || a[i].y_dtype != FQ_F32)
             return FQ_ERR_UNSUPPORTED;
     if (f.format == FQ_Q4_K) return f.m <= 8 ? launch_dense<FQ_Q4_K, 1>(dev, a, count) : launch_dense<FQ_Q4_K, 2>(dev, a, count);
+    if (f.format == FQ_Q5_K) return f.m <= 8 ? launch_dense<FQ_Q5_K, 1>(dev, a, count) : launch_dense<FQ_Q5_K, 2>(dev, a, count);
     return f.m <= 8 ? launch_dense<FQ_Q6_K, 1>(dev, a, count) : launch_dense<FQ_Q6_K, 2>(dev, a, count);
 }
 
@@ -683,7 +703,7 @@ int fq_launch_gemv_nt_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
 int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t count, uint32_t total_rows, const uint32_t *src, uint32_t src_div) {
     if (count == 0 || count > 2) return FQ_ERR_UNSUPPORTED;
     const ProjectArgs &f = a[0];
-    if ((f.format != FQ_Q4_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
+    if ((f.format != FQ_Q4_K && f.format != FQ_Q5_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
     if (f.cols % 256 || f.row_bytes % 16 || !f.offsets || f.groups == 0 || total_rows == 0) return FQ_ERR_UNSUPPORTED;
     for (uint32_t i = 1; i < count; i++)
         if (a[i].format != f.format || a[i].cols != f.cols || a[i].rows != f.rows || a[i].x != f.x || a[i].offsets != f.offsets ||
@@ -708,8 +728,9 @@ int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t cou
     J.groups = f.groups;
     J.total_rows = total_rows;
     NtShape S;
-    const bool q4 = f.format == FQ_Q4_K;
-    if (!(q4 ? nt_shape<FQ_Q4_K, 2>(dev, tiles, J.nblk, true, S) : nt_shape<FQ_Q6_K, 2>(dev, tiles, J.nblk, true, S))) return FQ_ERR_UNSUPPORTED;
+    const bool ok = f.format == FQ_Q4_K ? nt_shape<FQ_Q4_K, 2>(dev, tiles, J.nblk, true, S)
+                  : f.format == FQ_Q5_K ? nt_shape<FQ_Q5_K, 2>(dev, tiles, J.nblk, true, S) : nt_shape<FQ_Q6_K, 2>(dev, tiles, J.nblk, true, S);
+    if (!ok) return FQ_ERR_UNSUPPORTED;
     J.nb_max = S.nb_max;
     cudaError_t e = cudaSuccess;
     // The rows of the experts in `offsets` (a rank's share when the matrices hold only some experts).
@@ -717,7 +738,8 @@ int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t cou
     if (int rc = fq_check_cuda(dev, e, "activation preparation launch")) return rc;
     // Every group has at most ceil(rows / 16) <= rows / 16 + 1 tiles of sixteen rows.
     const uint32_t grid = total_rows / 16 + f.groups;
-    e = q4 ? nt_launch<FQ_Q4_K, 2, true>(dev, J, S, grid, TpPush{}) : nt_launch<FQ_Q6_K, 2, true>(dev, J, S, grid, TpPush{});
+    e = f.format == FQ_Q4_K ? nt_launch<FQ_Q4_K, 2, true>(dev, J, S, grid, TpPush{})
+      : f.format == FQ_Q5_K ? nt_launch<FQ_Q5_K, 2, true>(dev, J, S, grid, TpPush{}) : nt_launch<FQ_Q6_K, 2, true>(dev, J, S, grid, TpPush{});
     if (int rc = fq_check_cuda(dev, e, "grouped gemv launch")) return rc;
     return fq_end_enqueue(dev, "gemv_nt_grouped", 2);
 }

@@ -8,6 +8,7 @@ only as device memory: every computation happens inside ``libferrum_b200.so``.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -63,8 +64,13 @@ class Unsupported(FerrumError):
     status = _lib.ERR_UNSUPPORTED
 
 
+class GgufError(FerrumError):
+    """``Error::Gguf``: a malformed or truncated file, a missing tensor or metadata entry."""
+    status = _lib.ERR_GGUF
+
+
 _BY_STATUS = {c.status: c for c in (ShapeError, RangeError, DeviceMismatch, AliasError, WeightError,
-                                    SynchronizationError, TimeoutError_, CudaError, ParameterError, Unsupported)}
+                                    SynchronizationError, TimeoutError_, CudaError, ParameterError, Unsupported, GgufError)}
 
 
 def _dtype_id(t: torch.Tensor) -> int:
@@ -231,6 +237,106 @@ class Graph:
             pass
 
 
+class GgufFile:
+    """``GgufFile`` (src/loader/gguf.rs:162-530): the checked index of a GGUF file; payloads are read on demand.
+    Needs no GPU."""
+
+    def __init__(self, path: str, require_architecture: bool = True, skip_arrays_over: int = 0):
+        self._L = _lib.load()
+        h = C.c_void_p()
+        err = C.create_string_buffer(512)
+        rc = self._L.fq_gguf_open(os.fsencode(path), int(require_architecture), skip_arrays_over, C.byref(h), err, len(err))
+        if rc != _lib.OK:
+            raise _BY_STATUS.get(rc, FerrumError)(err.value.decode() or self._L.fq_status_name(rc).decode())
+        self.handle = h
+        info = _lib.GgufInfo()
+        self._check(self._L.fq_gguf_info(h, C.byref(info)))
+        self.version, self.alignment = int(info.version), int(info.alignment)
+        self.file_len, self.tensor_data_offset = int(info.file_len), int(info.tensor_data_offset)
+        self.tensor_count, self.metadata_count = int(info.tensor_count), int(info.metadata_count)
+
+    def _check(self, rc: int) -> None:
+        if rc != _lib.OK:
+            raise _BY_STATUS.get(rc, FerrumError)(self._L.fq_gguf_last_error(self.handle).decode())
+
+    @staticmethod
+    def _info(t: "_lib.GgufTensor") -> dict:
+        return {"name": t.name.decode(), "dimensions": [int(t.dims[i]) for i in range(t.n_dims)], "type_id": int(t.type_id),
+                "offset": int(t.offset), "byte_len": int(t.byte_len)}
+
+    def tensor(self, name: str) -> dict:
+        t = _lib.GgufTensor()
+        self._check(self._L.fq_gguf_tensor_by_name(self.handle, name.encode(), C.byref(t)))
+        return self._info(t)
+
+    def tensors(self) -> list:
+        out = []
+        for i in range(self.tensor_count):
+            t = _lib.GgufTensor()
+            self._check(self._L.fq_gguf_tensor_by_index(self.handle, i, C.byref(t)))
+            out.append(self._info(t))
+        return out
+
+    def read_tensor(self, name: str) -> np.ndarray:
+        n = self.tensor(name)["byte_len"]
+        out = np.empty(n, dtype=np.uint8)
+        self._check(self._L.fq_gguf_read_tensor(self.handle, name.encode(), C.c_void_p(out.ctypes.data), n))
+        return out
+
+    def metadata_u64(self, key: str) -> int:
+        v = C.c_uint64()
+        self._check(self._L.fq_gguf_metadata_u64(self.handle, key.encode(), C.byref(v)))
+        return int(v.value)
+
+    def metadata_f64(self, key: str) -> float:
+        v = C.c_double()
+        self._check(self._L.fq_gguf_metadata_f64(self.handle, key.encode(), C.byref(v)))
+        return float(v.value)
+
+    def metadata_string(self, key: str) -> str:
+        buf = C.create_string_buffer(1 << 16)
+        self._check(self._L.fq_gguf_metadata_string(self.handle, key.encode(), buf, len(buf)))
+        return buf.value.decode()
+
+    def metadata_array(self, key: str) -> tuple:
+        """(element type, elements in the file, elements kept)."""
+        et, n, kept = C.c_uint32(), C.c_uint64(), C.c_uint64()
+        self._check(self._L.fq_gguf_metadata_array(self.handle, key.encode(), C.byref(et), C.byref(n), C.byref(kept)))
+        return int(et.value), int(n.value), int(kept.value)
+
+    def close(self) -> None:
+        if self.handle:
+            self._L.fq_gguf_close(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def q3k_to_q6k(q3: np.ndarray) -> np.ndarray:
+    """``q3k_to_q6k`` (src/hybrid/weights.rs:761-805) on host bytes."""
+    q3 = np.ascontiguousarray(q3, dtype=np.uint8)
+    blocks = q3.size // 110
+    out = np.empty(blocks * 210, dtype=np.uint8)
+    rc = _lib.load().fq_q3k_to_q6k(C.c_void_p(q3.ctypes.data), blocks, C.c_void_p(out.ctypes.data))
+    if rc != _lib.OK:
+        raise ParameterError("q3k_to_q6k")
+    return out
+
+
+def quantize_q8_0(x: np.ndarray) -> np.ndarray:
+    """ggml's reference Q8_0 row quantisation (``quantize_row``, src/hybrid/weights.rs:1397-1415) on host floats."""
+    x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    out = np.empty(x.size // 32 * 34, dtype=np.uint8)
+    rc = _lib.load().fq_quantize_q8_0(C.c_void_p(x.ctypes.data), x.size, C.c_void_p(out.ctypes.data))
+    if rc != _lib.OK:
+        raise ParameterError("quantize_q8_0: the length must be a multiple of 32")
+    return out
+
+
 class Matrix:
     """``Matrix`` counterpart (src/hybrid/weights.rs:107-143): immutable packed blocks on the device."""
 
@@ -250,6 +356,13 @@ class Matrix:
         h = C.c_void_p()
         device.check(device._L.fq_matrix_create(device.handle, fmt, rows, cols, experts,
                                                 C.c_void_p(buf.ctypes.data), buf.size, C.byref(h)))
+        return cls(device, h)
+
+    @classmethod
+    def from_gguf(cls, device: Device, file: "GgufFile", name: str, experts: int, rows: int, cols: int, q3k_as_q6k: bool = False) -> "Matrix":
+        """``gguf_matrix`` (src/hybrid/weights.rs:671-736)."""
+        h = C.c_void_p()
+        device.check(device._L.fq_matrix_from_gguf(device.handle, file.handle, name.encode(), experts, rows, cols, int(q3k_as_q6k), C.byref(h)))
         return cls(device, h)
 
     def byte_size(self) -> int:

@@ -30,7 +30,7 @@ extern "C" {
 typedef struct fq_device fq_device;
 typedef struct fq_matrix fq_matrix;
 
-/* src/error.rs: Shape, Range, DeviceMismatch, Dispatch("alias"), Weight, Synchronization. */
+/* src/error.rs: Shape, Range, DeviceMismatch, Dispatch("alias"), Weight, Synchronization, Gguf. */
 typedef enum fq_status {
     FQ_OK = 0,
     FQ_ERR_SHAPE = 1,       /* element counts do not match the matrix geometry */
@@ -42,12 +42,13 @@ typedef enum fq_status {
     FQ_ERR_TIMEOUT = 7,     /* a bounded device-side wait gave up */
     FQ_ERR_CUDA = 8,        /* CUDA runtime error */
     FQ_ERR_PARAM = 9,       /* invalid argument */
-    FQ_ERR_UNSUPPORTED = 10 /* format / dtype combination without a kernel */
+    FQ_ERR_UNSUPPORTED = 10,/* format / dtype combination without a kernel */
+    FQ_ERR_GGUF = 11        /* a GGUF file is malformed, truncated or lacks what was asked for */
 } fq_status;
 
 /* GGML type ids, as in `Format::from_type` (src/hybrid/weights.rs:47-66) and
  * `QuantizationFormat` (src/quantization.rs:24-73). */
-typedef enum fq_format { FQ_Q8_0 = 8, FQ_Q4_K = 12, FQ_Q6_K = 14 } fq_format;
+typedef enum fq_format { FQ_Q8_0 = 8, FQ_Q4_K = 12, FQ_Q5_K = 13, FQ_Q6_K = 14 } fq_format;
 
 /* Activation / output element types (GGML ids of F32 and BF16). */
 typedef enum fq_dtype { FQ_F32 = 0, FQ_BF16 = 30 } fq_dtype;
@@ -124,6 +125,53 @@ int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint64_t cols, u
                      const void *packed, size_t len, fq_matrix **out);
 int fq_matrix_destroy(fq_matrix *w);
 int fq_matrix_get_info(const fq_matrix *w, fq_matrix_info *out);
+
+/* ---- GGUF files ------------------------------------------------------------------------------ */
+
+/* `GgufReader` (src/loader/gguf.rs:162-530): a bounds-checked index of a GGUF v2 / v3 file -- header, metadata,
+ * tensor descriptors with the block layouts of `block_layout` (:87-121), alignment (`general.alignment`,
+ * default 32), every tensor range inside the file and no two overlapping -- and tensor payloads read on demand.
+ * `require_architecture` = 0 is `open_untagged` (tensor-only files: no `general.architecture`, names up to 256
+ * bytes); `skip_arrays_over` > 0 is `from_reader_skipping_arrays` (longer metadata arrays are skipped and read
+ * back empty).  On failure the message goes to `err` (may be NULL) and the status is FQ_ERR_GGUF. */
+typedef struct fq_gguf fq_gguf;
+typedef struct fq_gguf_tensor {
+    char name[260];
+    uint32_t n_dims;
+    uint64_t dims[4];  /* GGUF order: dims[0] is the contiguous dimension */
+    uint32_t type_id;
+    uint64_t offset;   /* relative to the tensor-data section */
+    uint64_t byte_len;
+} fq_gguf_tensor;
+typedef struct fq_gguf_info_t {
+    uint32_t version, alignment;
+    uint64_t file_len, tensor_data_offset, tensor_count, metadata_count;
+} fq_gguf_info_t;
+int fq_gguf_open(const char *path, int require_architecture, uint64_t skip_arrays_over, fq_gguf **out, char *err, size_t err_len);
+int fq_gguf_close(fq_gguf *file);
+const char *fq_gguf_last_error(const fq_gguf *file);
+int fq_gguf_info(const fq_gguf *file, fq_gguf_info_t *out);
+int fq_gguf_tensor_by_name(fq_gguf *file, const char *name, fq_gguf_tensor *out);
+int fq_gguf_tensor_by_index(fq_gguf *file, uint64_t index, fq_gguf_tensor *out); /* in name order */
+/* `read_tensor_into` (src/loader/gguf.rs:474-495): `len` must be the tensor's byte length. */
+int fq_gguf_read_tensor(fq_gguf *file, const char *name, void *dst, size_t len);
+int fq_gguf_metadata_u64(fq_gguf *file, const char *key, uint64_t *out);
+int fq_gguf_metadata_f64(fq_gguf *file, const char *key, double *out);
+int fq_gguf_metadata_string(fq_gguf *file, const char *key, char *out, size_t len);
+int fq_gguf_metadata_array(fq_gguf *file, const char *key, uint32_t *element_type, uint64_t *count, uint64_t *kept);
+/* `block_layout` (src/loader/gguf.rs:87-121): elements and bytes of one block of a GGML type. */
+int fq_block_layout(uint32_t type_id, uint32_t *elements, uint32_t *bytes);
+/* `gguf_matrix` (src/hybrid/weights.rs:671-736): tensor `name` as `experts` stacked [rows, cols] slices
+ * (GGUF dims [cols, rows] or [cols, rows, experts], else FQ_ERR_WEIGHT), in its stored encoding, or -- with
+ * `q3k_as_q6k` -- Q3_K rewritten as Q6_K; then the checks and the upload of `fq_matrix_create`. */
+int fq_matrix_from_gguf(fq_device *dev, fq_gguf *file, const char *name, uint64_t experts, uint64_t rows, uint64_t cols,
+                        int q3k_as_q6k, fq_matrix **out);
+/* `q3k_to_q6k` (src/hybrid/weights.rs:761-805): `blocks` Q3_K blocks (110 bytes) as Q6_K blocks (210 bytes)
+ * that decode to exactly the same values.  Host memory. */
+int fq_q3k_to_q6k(const void *src, size_t blocks, void *dst);
+/* ggml's reference Q8_0 row quantisation as the loader applies it to unquantised tensors
+ * (`quantize_row`, src/hybrid/weights.rs:1397-1415): n floats (a multiple of 32) to n / 32 blocks.  Host memory. */
+int fq_quantize_q8_0(const float *x, size_t n, void *out);
 
 /* ---- the op surface ------------------------------------------------------------------------ */
 

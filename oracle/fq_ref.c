@@ -21,7 +21,9 @@
 #include <string.h>
 
 #define FQO_Q8_0 8
+#define FQO_Q3_K 11
 #define FQO_Q4_K 12
+#define FQO_Q5_K 13
 #define FQO_Q6_K 14
 
 /* ---------------------------------------------------------------- scalar conversions */
@@ -104,6 +106,8 @@ int fqo_block_layout(int format, int *elements, int *bytes) {
     switch (format) {
     case FQO_Q8_0: *elements = 32; *bytes = 34; return 0;
     case FQO_Q4_K: *elements = 256; *bytes = 144; return 0;
+    case FQO_Q5_K: *elements = 256; *bytes = 176; return 0;
+    case FQO_Q3_K: *elements = 256; *bytes = 110; return 0;
     case FQO_Q6_K: *elements = 256; *bytes = 210; return 0;
     default: return -1;
     }
@@ -118,7 +122,9 @@ int fqo_validate(int format, const uint8_t *p, size_t len) {
     if (len % (size_t)bb) return 1;
     for (size_t o = 0; o < len; o += (size_t)bb) {
         const uint8_t *b = p + o;
-        if (format == FQO_Q4_K) {
+        if (format == FQO_Q3_K) {
+            continue; /* no check in the reference: Q3_K is rewritten as Q6_K before it is kept */
+        } else if (format == FQO_Q4_K || format == FQO_Q5_K) {
             if (!isfinite(f16_at(b, 0)) || !isfinite(f16_at(b, 2))) return 2;
         } else if (format == FQO_Q6_K) {
             if (!isfinite(f16_at(b, 208))) return 2;
@@ -170,6 +176,60 @@ static void dequant_q4_k(const uint8_t *b, float *out) {
     }
 }
 
+/* One Q5_K block: src/diffusion/tests.rs:811-840 (`q45_k` with high = true): 32 bytes of fifth bits between the
+ * scales and the nibbles; bit (2 j + half) of qh[l] belongs to value l of that sub-block. */
+static void dequant_q5_k(const uint8_t *b, float *out) {
+    float d = f16_at(b, 0), dmin = f16_at(b, 2);
+    const uint8_t *scales = b + 4, *qh = b + 16, *qs = b + 48;
+    for (int j = 0; j < 4; j++) {
+        const uint8_t *q = qs + 32 * j;
+        for (int half = 0; half < 2; half++) {
+            float sc, m;
+            scale_min(2 * j + half, scales, &sc, &m);
+            uint8_t bit = (uint8_t)(1u << (2 * j + half));
+            for (int l = 0; l < 32; l++) {
+                uint8_t low = half == 0 ? (q[l] & 0xF) : (q[l] >> 4);
+                uint8_t top = (qh[l] & bit) ? 16 : 0;
+                float ds = d * sc;
+                float t = ds * (float)(low + top);
+                float mm = dmin * m;
+                *out++ = t - mm;
+            }
+        }
+    }
+}
+
+/* One Q3_K block (hmask[32], qs[64], scales[12], d): llama.cpp's `dequantize_row_q3_K` as the reference's tests
+ * restate it, src/hybrid/iq_tests.rs:1441-1478.  Used to check the Q3_K -> Q6_K rewrite of the loader. */
+static void dequant_q3_k(const uint8_t *b, float *out) {
+    const uint8_t *hm = b, *q = b + 32;
+    float d_all = f16_at(b, 108);
+    uint32_t aux[4] = {0, 0, 0, 0};
+    for (int k = 0; k < 3; k++) aux[k] = (uint32_t)b[96 + 4 * k] | ((uint32_t)b[97 + 4 * k] << 8) | ((uint32_t)b[98 + 4 * k] << 16) | ((uint32_t)b[99 + 4 * k] << 24);
+    const uint32_t kmask1 = 0x03030303u, kmask2 = 0x0f0f0f0fu, tmp = aux[2];
+    aux[2] = ((aux[0] >> 4) & kmask2) | (((tmp >> 4) & kmask1) << 4);
+    aux[3] = ((aux[1] >> 4) & kmask2) | (((tmp >> 6) & kmask1) << 4);
+    aux[0] = (aux[0] & kmask2) | ((tmp & kmask1) << 4);
+    aux[1] = (aux[1] & kmask2) | (((tmp >> 2) & kmask1) << 4);
+    int8_t scales[16];
+    for (int k = 0; k < 16; k++) scales[k] = (int8_t)((aux[k / 4] >> (8 * (k % 4))) & 0xFF);
+    int is = 0, at = 0;
+    uint8_t m = 1;
+    for (int n = 0; n < 2; n++) {
+        const uint8_t *qq = q + 32 * n;
+        for (int shift = 0; shift < 8; shift += 2) {
+            for (int half = 0; half < 2; half++) {
+                float dl = d_all * ((float)scales[is++] - 32.0f);
+                for (int l = 16 * half; l < 16 * half + 16; l++) {
+                    int v = (int)((qq[l] >> shift) & 3) - ((hm[l] & m) ? 0 : 4);
+                    out[at++] = dl * (float)v;
+                }
+            }
+            m = (uint8_t)(m << 1);
+        }
+    }
+}
+
 /* One Q6_K block: src/diffusion/tests.rs:842-864 (= src/hybrid/iq_tests.rs:1481-1500). */
 static void dequant_q6_k(const uint8_t *b, float *out) {
     const uint8_t *ql0 = b, *qh0 = b + 128;
@@ -210,6 +270,8 @@ int fqo_dequant(int format, const uint8_t *src, size_t blocks, float *out) {
         const uint8_t *b = src + i * (size_t)bb;
         float *o = out + i * (size_t)el;
         if (format == FQO_Q4_K) dequant_q4_k(b, o);
+        else if (format == FQO_Q5_K) dequant_q5_k(b, o);
+        else if (format == FQO_Q3_K) dequant_q3_k(b, o);
         else if (format == FQO_Q6_K) dequant_q6_k(b, o);
         else dequant_q8_0(b, o);
     }

@@ -16,9 +16,9 @@ import subprocess
 
 import numpy as np
 
-Q8_0, Q4_K, Q6_K = 8, 12, 14
-LAYOUT = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}  # format -> (elements, bytes)
-NAME = {Q8_0: "q8_0", Q4_K: "q4_k", Q6_K: "q6_k"}
+Q8_0, Q3_K, Q4_K, Q5_K, Q6_K = 8, 11, 12, 13, 14
+LAYOUT = {Q8_0: (32, 34), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}  # format -> (elements, bytes)
+NAME = {Q8_0: "q8_0", Q3_K: "q3_k", Q4_K: "q4_k", Q5_K: "q5_k", Q6_K: "q6_k"}
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libfq_ref.so")
@@ -228,6 +228,16 @@ def random_blocks(fmt: int, blocks: int, seed: int = 0) -> np.ndarray:
         out[:, 2:4] = dmin.view(np.uint8).reshape(blocks, 2)
         out[:, 4:16] = rng.integers(0, 256, size=(blocks, 12), dtype=np.uint8)
         out[:, 16:144] = rng.integers(0, 256, size=(blocks, 128), dtype=np.uint8)
+    elif fmt == Q5_K:  # as Q4_K, the 32 bytes of fifth bits drawn after the scales
+        d, dmin = half(), half()
+        out[:, 0:2] = d.view(np.uint8).reshape(blocks, 2)
+        out[:, 2:4] = dmin.view(np.uint8).reshape(blocks, 2)
+        out[:, 4:16] = rng.integers(0, 256, size=(blocks, 12), dtype=np.uint8)
+        out[:, 16:48] = rng.integers(0, 256, size=(blocks, 32), dtype=np.uint8)
+        out[:, 48:176] = rng.integers(0, 256, size=(blocks, 128), dtype=np.uint8)
+    elif fmt == Q3_K:  # hmask, qs and the packed scales uniform; d last (src/hybrid/iq_tests.rs:1502-1508)
+        out[:, 0:108] = rng.integers(0, 256, size=(blocks, 108), dtype=np.uint8)
+        out[:, 108:110] = half().view(np.uint8).reshape(blocks, 2)
     elif fmt == Q6_K:
         d = half()
         out[:, 208:210] = d.view(np.uint8).reshape(blocks, 2)
@@ -316,6 +326,39 @@ def qk_q4k_packed(rows: int, cols: int) -> np.ndarray:
             out += qk_scales(row, blk).tobytes()
             out += bytes(qk_qbyte(row, blk, i) for i in range(128))
     return np.frombuffer(bytes(out), dtype=np.uint8).copy()
+
+
+def qk5_parameters(row, block):
+    """`parameters` for Q5_K (src/ops/transformer.rs:2845-2851)."""
+    return np.float32(0.001953125) + np.float32(block) / np.float32(4096.0), np.float32(0.0078125)
+
+
+def qk_q5k_packed(rows: int, cols: int) -> np.ndarray:
+    """The Q5_K branch of `qk_tests::packed` (src/ops/transformer.rs:2879-2896)."""
+    out = bytearray()
+    for row in range(rows):
+        for blk in range(cols // 256):
+            d, dmin = qk5_parameters(row, blk)
+            out += np.float16(d).tobytes() + np.float16(dmin).tobytes()
+            out += qk_scales(row, blk).tobytes()
+            out += bytes(qk_qbyte(row + 7, blk, i) for i in range(32))
+            out += bytes(qk_qbyte(row, blk, i) for i in range(128))
+    return np.frombuffer(bytes(out), dtype=np.uint8).copy()
+
+
+def qk_q5k_value(row: int, column: int) -> np.float32:
+    """`qk_value` for Q5_K (src/ops/transformer.rs:2939-2956)."""
+    blk, within = divmod(column, 256)
+    group, lane = divmod(within, 32)
+    chunk = within // 64
+    packed = qk_qbyte(row, blk, chunk * 32 + lane)
+    nibble = packed & 15 if group % 2 == 0 else packed >> 4
+    high = (qk_qbyte(row + 7, blk, lane) >> group) & 1
+    d, dmin = qk5_parameters(row, blk)
+    d = np.float32(np.float16(d))  # what the block stores
+    scale, minimum = _unpack_scale_min(qk_scales(row, blk), group)
+    return np.float32(np.float32(np.float32(d * np.float32(scale)) * np.float32(nibble | (high << 4)))
+                      - np.float32(dmin * np.float32(minimum)))
 
 
 def qk_q6k_packed(rows: int, cols: int) -> np.ndarray:

@@ -26,6 +26,7 @@ def case(name, fmt, packed, value_fn, x, rows, cols, m):
 
 cases = [
     case("qk_tests Q4_K (5, 512) m=3", "q4_k", ref.qk_q4k_packed(5, 512), ref.qk_q4k_value, ref.qk_input(3, 512), 5, 512, 3),
+    case("qk_tests Q5_K (5, 512) m=3", "q5_k", ref.qk_q5k_packed(5, 512), ref.qk_q5k_value, ref.qk_input(3, 512), 5, 512, 3),
     case("qk_tests Q6_K (5, 512) m=2", "q6_k", ref.qk_q6k_packed(5, 512), ref.qk_q6k_value, ref.qk_input(2, 512), 5, 512, 2),
     case("q6_k_tests (6, 768) m=1", "q6_k", ref.q6_packed(6, 768), ref.q6_value, ref.q6_input(1, 768), 6, 768, 1),
     case("q8_0_tests (7, 128) m=2", "q8_0", ref.q8_packed(7, 128), ref.q8_value, ref.q8_input(2, 128), 7, 128, 2),

@@ -191,3 +191,64 @@ def test_router_refuses_logits_without_a_ranking(device):
     assert (wts.cpu().numpy().reshape(tokens, used)[[1, 3]] == 0).all()
     want_ids, want_w, _ = ref.moe_route(logits[[0, 2, 4]], x[[0, 2, 4]], x[0], experts, used, hidden, 3, False, True, False)
     assert np.array_equal(got_ids[[0, 2, 4]], want_ids.reshape(3, used))
+
+
+def test_matrices_load_from_a_gguf_file(device, tmp_path):
+    """A GGUF file the test writes itself (Q4_K dense, Q5_K dense, Q6_K experts, Q3_K dense): `from_gguf` checks the
+    geometry, reads the payload, rewrites Q3_K as Q6_K, and the projections match the oracle on the stored bytes
+    (src/hybrid/weights.rs:671-736; src/hybrid/iq_tests.rs:1529-1560 for the Q3_K case)."""
+    import struct
+    s = S()
+
+    def gstr(t):
+        b = t.encode()
+        return struct.pack("<Q", len(b)) + b
+    rows, cols, experts = 48, 1024, 3
+    payloads = {"blk.0.attn_q.weight": (ref.Q4_K, [cols, rows], ref.random_matrix(ref.Q4_K, rows, cols, 1)),
+                "blk.0.attn_k.weight": (ref.Q5_K, [cols, rows], ref.random_matrix(ref.Q5_K, rows, cols, 2)),
+                "blk.0.ffn_down_exps.weight": (ref.Q6_K, [cols, rows, experts], ref.random_matrix(ref.Q6_K, experts * rows, cols, 3)),
+                "mtp.ffn_up.weight": (ref.Q3_K, [cols, rows], ref.random_matrix(ref.Q3_K, rows, cols, 4))}
+    md = [gstr("general.architecture") + struct.pack("<I", 8) + gstr("test"), gstr("general.quantization_version") + struct.pack("<II", 4, 2)]
+    head = b"GGUF" + struct.pack("<IQQ", 3, len(payloads), len(md)) + b"".join(md)
+    data, offsets = bytearray(), {}
+    for name, (fmt, dims, packed) in payloads.items():
+        data += b"\0" * ((-len(data)) % 32)
+        offsets[name] = len(data)
+        data += packed.tobytes()
+    for name, (fmt, dims, packed) in payloads.items():
+        head += gstr(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", fmt, offsets[name])
+    head += b"\0" * ((-len(head)) % 32)
+    path = tmp_path / "model.gguf"
+    path.write_bytes(head + bytes(data))
+    f = s.GgufFile(str(path))
+    x = np.random.default_rng(5).standard_normal((2, cols)).astype(np.float32)
+    for name, fmt in (("blk.0.attn_q.weight", ref.Q4_K), ("blk.0.attn_k.weight", ref.Q5_K)):
+        w = s.Matrix.from_gguf(device, f, name, 1, rows, cols)
+        assert (w.rows, w.cols, w.format) == (rows, cols, fmt)
+        y = torch.zeros(2 * rows, dtype=torch.float32, device="cuda")
+        s.project(device, w, dev_f32(x), 2, y)
+        device.synchronize()
+        assert ref.rel_err(host(y).reshape(2, rows), ref.matmul(fmt, payloads[name][2], rows, cols, x, 2)) <= TOL_F32
+    # experts: [experts, rows, cols] stacked
+    we = s.Matrix.from_gguf(device, f, "blk.0.ffn_down_exps.weight", experts, rows, cols)
+    assert (we.rows, we.experts) == (experts * rows, experts)
+    ids = torch.tensor([2, 0], dtype=torch.int32, device="cuda")
+    y = torch.zeros(2 * rows, dtype=torch.float32, device="cuda")
+    s.project_id(device, we, dev_f32(x), ids, 2, 1, y)
+    device.synchronize()
+    want = ref.matmul_id(ref.Q6_K, payloads["blk.0.ffn_down_exps.weight"][2], rows, cols, x, np.array([2, 0], dtype=np.uint32), 1)
+    assert ref.rel_err(host(y).reshape(2, rows), want) <= TOL_F32
+    # Q3_K: refused as it is, loaded as Q6_K on request, equal to the Q3_K CPU dequant
+    with pytest.raises(s.WeightError, match="no kernel"):
+        s.Matrix.from_gguf(device, f, "mtp.ffn_up.weight", 1, rows, cols)
+    w3 = s.Matrix.from_gguf(device, f, "mtp.ffn_up.weight", 1, rows, cols, q3k_as_q6k=True)
+    assert w3.format == ref.Q6_K
+    y = torch.zeros(2 * rows, dtype=torch.float32, device="cuda")
+    s.project(device, w3, dev_f32(x), 2, y)
+    device.synchronize()
+    assert ref.rel_err(host(y).reshape(2, rows), ref.matmul(ref.Q3_K, payloads["mtp.ffn_up.weight"][2], rows, cols, x, 2)) <= TOL_F32
+    # geometry the caller expects must be the file's
+    with pytest.raises(s.WeightError, match="expected GGUF dims"):
+        s.Matrix.from_gguf(device, f, "blk.0.attn_q.weight", 1, rows + 1, cols)
+    with pytest.raises(s.GgufError, match="missing tensor"):
+        s.Matrix.from_gguf(device, f, "blk.9.attn_q.weight", 1, rows, cols)

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 TOL_F32 = 1e-3   # fp32 GEMV / GEMM outputs, relative to max|y|
 TOL_BF16 = 2e-2  # bf16 in / bf16 out
 
-FORMATS = [ref.Q4_K, ref.Q6_K, ref.Q8_0]
+FORMATS = [ref.Q4_K, ref.Q5_K, ref.Q6_K, ref.Q8_0]
 
 
 def S():
@@ -44,7 +44,7 @@ def blocks_for(fmt, rows, cols, kind, seed=0):
             return ref.random_blocks(fmt, n, seed + 100)
         return ref.xorshift_kquant_blocks(fmt, n)
     if kind == "closed":
-        return {ref.Q4_K: ref.qk_q4k_packed, ref.Q6_K: ref.q6_packed, ref.Q8_0: ref.q8_packed}[fmt](rows, cols)
+        return {ref.Q4_K: ref.qk_q4k_packed, ref.Q5_K: ref.qk_q5k_packed, ref.Q6_K: ref.q6_packed, ref.Q8_0: ref.q8_packed}[fmt](rows, cols)
     raise ValueError(kind)
 
 
@@ -448,7 +448,7 @@ def test_errors_follow_the_reference(device):
     with pytest.raises(s.WeightError):  # src/quantization.rs:236-240
         s.Matrix.from_packed(device, 16, 512, 1, ref.Q4_K, bad)
     with pytest.raises(s.WeightError):
-        s.Matrix.from_packed(device, 16, 512, 1, 13, packed)  # Q5_K: no kernel
+        s.Matrix.from_packed(device, 16, 512, 1, 11, packed)  # Q3_K: no kernel (the loader rewrites it as Q6_K)
     s.project(device, w, x, 2, y)  # the handle still works
     device.synchronize()
 

@@ -91,7 +91,7 @@ def test_golden_vectors():
     with open(os.path.join(GOLDEN, "closed_form.json")) as f:
         g = json.load(f)
     for case in g["cases"]:
-        fmt = {"q4_k": ref.Q4_K, "q6_k": ref.Q6_K, "q8_0": ref.Q8_0}[case["format"]]
+        fmt = {"q4_k": ref.Q4_K, "q5_k": ref.Q5_K, "q6_k": ref.Q6_K, "q8_0": ref.Q8_0}[case["format"]]
         packed = np.array(case["packed_u8"], dtype=np.uint8)
         rows, cols, m = case["rows"], case["cols"], case["m"]
         dense = ref.dequant(fmt, packed)
