@@ -90,6 +90,11 @@ SIGNATURES = {
     "fq_quantize_q8_0": (_I, [_P, _Z, _P]),
     "fq_project": (_I, [_P, _P, _P, _I, _Z, _Z, _P, _I, _Z]),
     "fq_project_many": (_I, [_P, C.POINTER(_P), _Z, _P, _I, _Z, _Z, C.POINTER(_P), _I]),
+    "fq_rmsnorm": (_I, [_P, _P, _P, _U32, C.c_float, _U32, _P]),
+    "fq_add_rmsnorm": (_I, [_P, _P, _P, _P, _U32, C.c_float, _U32, _P, _P]),
+    "fq_rmsnorm_project_many": (_I, [_P, C.POINTER(_P), _Z, _P, _P, C.c_float, _Z, _Z, _P, C.POINTER(_P)]),
+    "fq_argmax": (_I, [_P, _P, _U32, _U32, _P]),
+    "fq_topk_blocks": (_I, [_P, _P, _U32, _U32, _P]),
     "fq_project_id": (_I, [_P, _P, _P, _Z, _P, _Z, _Z, _P, _Z]),
     "fq_project_mm_id": (_I, [_P, _P, _P, _I, _Z, _P, _P, _Z, _Z, _P, _I, _Z]),
     "fq_get_rows": (_I, [_P, _P, _P, _Z, _P, _I, _Z]),

@@ -584,6 +584,41 @@ extern "C" int fq_project_many(fq_device *dev, const fq_matrix *const *w, size_t
     return FQ_OK;
 }
 
+// `fq_project_many` on rmsnorm(x) * norm_w (F32 in and out): at decode and verify widths on the K-quant formats the
+// normalisation happens inside the projections' activation preparation; otherwise `fq_rmsnorm` into `scratch`
+// (m * cols floats), then the projections.
+extern "C" int fq_rmsnorm_project_many(fq_device *dev, const fq_matrix *const *w, size_t count, const float *x, const float *norm_w, float eps,
+                                       size_t x_elems, size_t m, float *scratch, void *const *y) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!w || !y || count == 0 || !w[0]) return fq_fail(dev, FQ_ERR_PARAM, "projection list");
+    const size_t cols = w[0]->cols;
+    if (m == 0 || x_elems != m * cols || cols % 4) return fq_fail(dev, FQ_ERR_SHAPE, "normalised projection [%zu, %zu] from %zu values", m, cols, x_elems);
+    if (int rc = fq_check_binding(dev, x, x_elems * 4, "x")) return rc;
+    if (int rc = fq_check_binding(dev, norm_w, cols * 4, "norm_w")) return rc;
+    bool fused = !dev->exact && m <= (size_t)FQ_GEMV_MAX_M && count <= 4;
+    ProjectArgs args[4];
+    for (size_t i = 0; i < count && fused; i++) {
+        if (!w[i] || w[i]->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "matrix belongs to another device handle");
+        fused = w[i]->cols == cols && w[i]->format == w[0]->format && (w[i]->format == FQ_Q4_K || w[i]->format == FQ_Q5_K || w[i]->format == FQ_Q6_K);
+        if (!fused) break;
+        const size_t yb = m * w[i]->rows * 4;
+        if (int rc = fq_check_binding(dev, y[i], yb, "y")) return rc;
+        if (int rc = fq_check_no_alias(dev, y[i], yb, x, x_elems * 4, "y")) return rc;
+        args[i] = base_args(w[i], x, FQ_F32, y[i], FQ_F32);
+        args[i].rows = (uint32_t)w[i]->rows;
+        args[i].m = (uint32_t)m;
+        args[i].norm_w = norm_w;
+        args[i].norm_eps = eps;
+    }
+    if (fused) {
+        const int rc = launch_decode(dev, args, (uint32_t)count);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (!scratch) return fq_fail(dev, FQ_ERR_RANGE, "scratch: these projections need the normalised activations in memory");
+    if (int rc = fq_rmsnorm(dev, x, norm_w, (uint32_t)cols, eps, (uint32_t)m, scratch)) return rc;
+    return fq_project_many(dev, w, count, scratch, FQ_F32, x_elems, m, y, FQ_F32);
+}
+
 // Row-sharded `fq_project_many`: every y[i] lies in this rank's slice [region_offset + rank * shard_bytes,
 // + shard_bytes) of a gathered region of the communicator's symmetric buffer.  Decode widths on the integer
 // kernel exchange inside the projection kernel; anything else projects first and gathers the region with

@@ -133,6 +133,22 @@ __device__ __forceinline__ Quant8 quantize8(const float (&v)[8]) {
     }
     return q;
 }
+// 1 / sqrt(mean(x^2) + eps) of a row of n values (a multiple of 4), by one warp: every lane sums the float4s
+// lane, lane + 32, .. in order and the lanes are added by a butterfly, so any warp that calls this on the same row
+// gets the same bits (the standalone normalisation and the one fused into activation preparation agree).
+__device__ __forceinline__ float row_inv_rms(const float *__restrict__ row, uint32_t n, float eps, uint32_t lane) {
+    float ss = 0.f;
+    for (uint32_t i = lane; i < n / 4; i += 32) {
+        const float4 v = reinterpret_cast<const float4 *>(row)[i];
+        ss = fmaf(v.x, v.x, ss);
+        ss = fmaf(v.y, v.y, ss);
+        ss = fmaf(v.z, v.z, ss);
+        ss = fmaf(v.w, v.w, ss);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    return 1.0f / sqrtf(ss / (float)n + eps);
+}
 __device__ __forceinline__ uint32_t pack4(const uint8_t *p) { return p[0] | (p[1] << 8) | (p[2] << 16) | ((uint32_t)p[3] << 24); }
 
 // Row-sharded launches (TpPush, internal.h).  tp_seq: the sequence number of this exchange, read by every block

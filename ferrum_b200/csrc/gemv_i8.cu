@@ -72,11 +72,20 @@ PrepI8 prep_i8_layout(uint32_t cols) {
 // Superblock b of one activation row, by one warp (lane l owns the eight values at 256 b + 8 l), written in
 // the layout above at `base` (global or shared memory).
 // With `urow` the activations are the gated unit silu(x) * u, x / (1 + exp(-x)) * u as `k_swiglu` computes it.
+// With `norm_w` they are rmsnorm(x) * norm_w (`h_rmsnorm`, src/metal/shaders/hybrid.metal:1563-1575).
 __device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base,
-                                                const float *__restrict__ urow = nullptr) {
+                                                const float *__restrict__ urow = nullptr, const float *__restrict__ norm_w = nullptr, float eps = 0.f) {
     const float4 *src = reinterpret_cast<const float4 *>(xrow + (size_t)b * 256 + lane * 8);
     const float4 v0 = src[0], v1 = src[1];
     float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    if (norm_w) {
+        const float scale = row_inv_rms(xrow, L.cols, eps, lane);
+        const float4 *ws = reinterpret_cast<const float4 *>(norm_w + (size_t)b * 256 + lane * 8);
+        const float4 w0 = ws[0], w1 = ws[1];
+        const float g[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v[i] * scale * g[i];
+    }
     if (urow) {
         const float4 *us = reinterpret_cast<const float4 *>(urow + (size_t)b * 256 + lane * 8);
         const float4 u0 = us[0], u1 = us[1];
@@ -111,13 +120,14 @@ __device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, 
 
 // One warp per (activation row, superblock).
 __global__ void __launch_bounds__(128)
-k_prep_i8(const float *__restrict__ x, const float *__restrict__ x_up, uint32_t xrows, PrepI8 L, uint8_t *__restrict__ out) {
+k_prep_i8(const float *__restrict__ x, const float *__restrict__ x_up, const float *__restrict__ norm_w, float eps, uint32_t xrows, PrepI8 L,
+          uint8_t *__restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const uint32_t xr = warp / L.nblk, b = warp % L.nblk;
     if (xr >= xrows) return;
-    prep_superblock(x + (size_t)xr * L.cols, b, lane, L, out + (size_t)xr * L.token_bytes, x_up ? x_up + (size_t)xr * L.cols : nullptr);
+    prep_superblock(x + (size_t)xr * L.cols, b, lane, L, out + (size_t)xr * L.token_bytes, x_up ? x_up + (size_t)xr * L.cols : nullptr, norm_w, eps);
 }
 
 // ---------------------------------------------------------------- helpers
@@ -513,7 +523,7 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     if ((f.format != FQ_Q4_K && f.format != FQ_Q5_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
     if (f.cols % 256 || f.row_bytes % 16) return FQ_ERR_UNSUPPORTED;
     for (uint32_t i = 1; i < count; i++)
-        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].m != f.m || a[i].ids != f.ids ||
+        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].norm_w != f.norm_w || a[i].m != f.m || a[i].ids != f.ids ||
             a[i].x_div != f.x_div || a[i].experts != f.experts || (f.ids && a[i].rows != f.rows) || a[i].x_dtype != FQ_F32 ||
             a[i].y_dtype != FQ_F32)
             return FQ_ERR_UNSUPPORTED; // with routes the targets are expert stacks of one shape (gate and up)
@@ -534,7 +544,7 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     dev->xprep_turn ^= 1u;
     uint8_t *prep = (uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0);
     const uint32_t warps = xrows * L.nblk;
-    if (int rc = fq_check_cuda(dev, launch_pdl(k_prep_i8, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, xrows, L, prep),
+    if (int rc = fq_check_cuda(dev, launch_pdl(k_prep_i8, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, f.norm_w, f.norm_eps, xrows, L, prep),
                                "activation preparation launch"))
         return rc;
     cudaError_t e;
@@ -639,7 +649,7 @@ extern "C" int fq_gemv_q4k_static(const void *w_packed, uint64_t rows, uint64_t 
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const uint32_t warps = m * L.nblk;
     // Every byte the GEMV reads from the scratch is rewritten here first, so nothing has to start at zero.
-    k_prep_i8<<<(warps + 3) / 4, 128, 0, stream>>>(x, nullptr, m, L, prep);
+    k_prep_i8<<<(warps + 3) / 4, 128, 0, stream>>>(x, nullptr, nullptr, 0.f, m, L, prep);
     if ((e = cudaPeekAtLastError()) != cudaSuccess)
         return static_fail(err, err_len, FQ_ERR_CUDA, "activation preparation launch: %s", cudaGetErrorString(e));
     const uint32_t pitch = (uint32_t)(cols / 256 * 144);

@@ -129,11 +129,13 @@ __host__ __device__ inline uint32_t nt_act_bytes(uint32_t tok, uint32_t nb) {
 // One warp per (activation row, superblock); lane l owns the eight values at 256 b + 8 l.
 //   src    (may be null) row i of the prepared set is row src[i] / src_div of x (expert-sorted routes);
 //   range  (may be null) only rows [range[0], range[range_stride]) are prepared (the experts one rank owns);
-//   x_up   (may be null) the activations are the gated unit silu(x) * x_up, as `k_swiglu` computes it.
+//   x_up   (may be null) the activations are the gated unit silu(x) * x_up, as `k_swiglu` computes it;
+//   norm_w (may be null) the activations are rmsnorm(x) * norm_w.
 template <int FMT>
 __global__ void __launch_bounds__(128)
-k_prep_nt(const float *__restrict__ x, const float *__restrict__ x_up, uint32_t xrows, const uint32_t *__restrict__ src, uint32_t src_div,
-          const uint32_t *__restrict__ range, uint32_t range_stride, PrepNT L, uint8_t *__restrict__ out) {
+k_prep_nt(const float *__restrict__ x, const float *__restrict__ x_up, const float *__restrict__ norm_w, float eps, uint32_t xrows,
+          const uint32_t *__restrict__ src, uint32_t src_div, const uint32_t *__restrict__ range, uint32_t range_stride, PrepNT L,
+          uint8_t *__restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -144,6 +146,14 @@ k_prep_nt(const float *__restrict__ x, const float *__restrict__ x_up, uint32_t 
     const float4 *sp = reinterpret_cast<const float4 *>(x + srow * L.cols + (size_t)b * 256 + lane * 8);
     const float4 v0 = sp[0], v1 = sp[1];
     float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    if (norm_w) { // rmsnorm(x) * norm_w, as `h_rmsnorm` computes it
+        const float scale = row_inv_rms(x + srow * L.cols, L.cols, eps, lane);
+        const float4 *ws = reinterpret_cast<const float4 *>(norm_w + (size_t)b * 256 + lane * 8);
+        const float4 w0 = ws[0], w1 = ws[1];
+        const float g[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v[i] * scale * g[i];
+    }
     if (x_up) {
         const float4 *us = reinterpret_cast<const float4 *>(x_up + srow * L.cols + (size_t)b * 256 + lane * 8);
         const float4 u0 = us[0], u1 = us[1];
@@ -638,9 +648,9 @@ uint8_t *launch_prep(fq_device *dev, int format, const ProjectArgs &f, uint32_t 
     uint8_t *prep = (uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0);
     const uint32_t warps = xrows * L.nblk;
     if (format == FQ_Q4_K || format == FQ_Q5_K) // the same fragment order
-        e = launch_pdl(k_prep_nt<FQ_Q4_K>, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, xrows, src, src_div, range, range_stride, L, prep);
+        e = launch_pdl(k_prep_nt<FQ_Q4_K>, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, f.norm_w, f.norm_eps, xrows, src, src_div, range, range_stride, L, prep);
     else
-        e = launch_pdl(k_prep_nt<FQ_Q6_K>, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, xrows, src, src_div, range, range_stride, L, prep);
+        e = launch_pdl(k_prep_nt<FQ_Q6_K>, dim3((warps + 3) / 4), dim3(128), 0, dev->stream, (const float *)f.x, f.x_up, f.norm_w, f.norm_eps, xrows, src, src_div, range, range_stride, L, prep);
     return prep;
 }
 
@@ -689,7 +699,7 @@ int fq_launch_gemv_nt_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     if ((f.format != FQ_Q4_K && f.format != FQ_Q5_K && f.format != FQ_Q6_K) || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32) return FQ_ERR_UNSUPPORTED;
     if (f.cols % 256 || f.row_bytes % 16 || f.ids || f.m < 2 || f.m > 16) return FQ_ERR_UNSUPPORTED;
     for (uint32_t i = 1; i < count; i++)
-        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].m != f.m || a[i].ids ||
+        if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].norm_w != f.norm_w || a[i].m != f.m || a[i].ids ||
             a[i].x_dtype != FQ_F32 || a[i].y_dtype != FQ_F32)
             return FQ_ERR_UNSUPPORTED;
     if (f.format == FQ_Q4_K) return f.m <= 8 ? launch_dense<FQ_Q4_K, 1>(dev, a, count) : launch_dense<FQ_Q4_K, 2>(dev, a, count);

@@ -99,6 +99,8 @@ struct ProjectArgs {
     uint32_t format, rows, cols, row_bytes; // rows = rows of one expert slice; row_bytes = device row pitch
     const void *x;
     const float *x_up = nullptr; // decode kernels only: the activations are silu(x) * x_up (the gated unit, fused into their preparation)
+    const float *norm_w = nullptr; // decode kernels only: the activations are rmsnorm(x) * norm_w (fused into their preparation)
+    float norm_eps = 0.f;
     void *y;
     int x_dtype, y_dtype;
     uint32_t m;        // activation rows (project) / routes (project_id) / 0 (grouped)

@@ -427,6 +427,40 @@ def project_many_gather(d: Device, comm: "Comm", offset_bytes: int, shard_bytes:
                                         ya, _dtype_id(ys[0])))
 
 
+def rmsnorm(d: Device, x: torch.Tensor, w: torch.Tensor, eps: float, rows: int, y: torch.Tensor) -> None:
+    """``HybridModel::rmsnorm``: y = rmsnorm(x) * w over ``rows`` rows."""
+    _need(d, x, w, y)
+    d.check(d._L.fq_rmsnorm(d.handle, _ptr(x), _ptr(w), w.numel(), eps, rows, _ptr(y)))
+
+
+def add_rmsnorm(d: Device, x, r, w, eps: float, rows: int, h, y) -> None:
+    """``HybridModel::add_rmsnorm``: h = x + r, y = rmsnorm(h) * w."""
+    _need(d, x, r, w, h, y)
+    d.check(d._L.fq_add_rmsnorm(d.handle, _ptr(x), _ptr(r), _ptr(w), w.numel(), eps, rows, _ptr(h), _ptr(y)))
+
+
+def rmsnorm_project_many(d: Device, ws: Sequence[Matrix], x: torch.Tensor, norm_w: torch.Tensor, eps: float, m: int,
+                         ys: Sequence[torch.Tensor], scratch: Optional[torch.Tensor] = None) -> None:
+    """``project_many`` on rmsnorm(x) * norm_w, the normalisation inside the activation preparation where it can be."""
+    _need(d, x, norm_w, scratch, *ys)
+    n = len(ws)
+    wa = (C.c_void_p * n)(*[w.handle for w in ws])
+    ya = (C.c_void_p * n)(*[_ptr(y) for y in ys])
+    d.check(d._L.fq_rmsnorm_project_many(d.handle, wa, n, _ptr(x), _ptr(norm_w), eps, x.numel(), m, _ptr(scratch), ya))
+
+
+def argmax(d: Device, x: torch.Tensor, n: int, rows: int, out: torch.Tensor) -> None:
+    """``h_argmax``: the index of the first maximum of every row."""
+    _need(d, x, out)
+    d.check(d._L.fq_argmax(d.handle, _ptr(x), n, rows, _ptr(out)))
+
+
+def topk_blocks(d: Device, x: torch.Tensor, n: int, rows: int, out: torch.Tensor) -> None:
+    """``h_topk_blocks``: per 1024-value block the 32 largest (value, index) pairs, descending."""
+    _need(d, x, out)
+    d.check(d._L.fq_topk_blocks(d.handle, _ptr(x), n, rows, _ptr(out)))
+
+
 def project_id(d: Device, w: Matrix, x: torch.Tensor, ids: torch.Tensor, routes: int, x_div: int, y: torch.Tensor) -> None:
     """``HybridModel::project_id``: route r uses expert ids[r] on activation row r // x_div."""
     _need(d, x, ids, y)

@@ -189,6 +189,30 @@ int fq_project(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, s
 int fq_project_many(fq_device *dev, const fq_matrix *const *w, size_t count, const void *x, int x_dtype,
                     size_t x_elems, size_t m, void *const *y, int y_dtype);
 
+/* ---- either side of a projection ------------------------------------------------------------ */
+
+/* `HybridModel::rmsnorm` = `h_rmsnorm` (src/hybrid/engine.rs:3301-3320; hybrid.metal:1563-1575):
+ * y[r][i] = x[r][i] * rsqrt(mean_i x[r][i]^2 + eps) * w[i] for `rows` rows of n values (n a multiple of 4). */
+int fq_rmsnorm(fq_device *dev, const float *x, const float *w, uint32_t n, float eps, uint32_t rows, float *y);
+/* `HybridModel::add_rmsnorm` = `h_add_rmsnorm` (src/hybrid/engine.rs:3322-3345; hybrid.metal:1577-1595):
+ * h = x + r (written to h), y = rmsnorm(h) * w. */
+int fq_add_rmsnorm(fq_device *dev, const float *x, const float *r, const float *w, uint32_t n, float eps, uint32_t rows,
+                   float *h, float *y);
+/* `fq_project_many` on rmsnorm(x) * norm_w: the normalisation that produces a projection's input, folded into
+ * the projection.  At 1..16 activation rows on Q4_K / Q5_K / Q6_K matrices of one format it is computed inside
+ * the activation preparation (no launch of its own, no round trip of the normalised row, and bit for bit what
+ * `fq_rmsnorm` followed by `fq_project_many` gives); otherwise `scratch` (m * cols floats, may be NULL when the
+ * fused case is certain) receives the normalised rows first.  F32 in and out. */
+int fq_rmsnorm_project_many(fq_device *dev, const fq_matrix *const *w, size_t count, const float *x, const float *norm_w,
+                            float eps, size_t x_elems, size_t m, float *scratch, void *const *y);
+/* `h_argmax` (hybrid.metal:2214-2243): out[r] = index of the first maximum of row r of n values (the consumer of
+ * the output head's logits under greedy sampling). */
+int fq_argmax(fq_device *dev, const float *x, uint32_t n, uint32_t rows, uint32_t *out);
+/* `h_topk_blocks` (hybrid.metal:3616-3657): per block of 1024 values of each row, the 32 largest (value, index)
+ * pairs in descending order, ties to the lower index; out[(r * ceil(n / 1024) + block) * 32 + k] = {value, index
+ * as the bits of a float}. */
+int fq_topk_blocks(fq_device *dev, const float *x, uint32_t n, uint32_t rows, float *out);
+
 /* `HybridModel::project_id(d, w, x, ids, routes, x_div, y)` (src/hybrid/engine.rs:3114-3147):
  * route r multiplies activation row r / x_div by the rows of expert ids[r]; F32 in and out. */
 int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x, size_t x_elems,

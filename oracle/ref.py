@@ -181,6 +181,36 @@ def swiglu(g, u):
     return y
 
 
+def rmsnorm(x, w, eps) -> np.ndarray:
+    """`reference::rmsnorm` (src/reference.rs:23-36): f64 sum of squares, 1 / sqrt(mean + eps), x * inv * w in f64,
+    cast to f32.  `x` is [rows, n]."""
+    x64, w64 = np.asarray(x, dtype=np.float64), np.asarray(w, dtype=np.float64)
+    inv = 1.0 / np.sqrt((x64 ** 2).sum(axis=-1, keepdims=True) / w64.size + np.float64(np.float32(eps)))
+    return (x64 * inv * w64).astype(np.float32)
+
+
+def argmax_first(x) -> np.ndarray:
+    """`h_argmax` (src/metal/shaders/hybrid.metal:2214-2243): the index of the first maximum of each row."""
+    return np.argmax(np.asarray(x, dtype=np.float32), axis=-1).astype(np.uint32)
+
+
+def topk_blocks(x) -> tuple:
+    """`h_topk_blocks` (hybrid.metal:3616-3657): per 1024-value block of each row the 32 largest values in
+    descending order with their indices, ties to the lower index; blocks past the row's end pad with -inf."""
+    x = np.asarray(x, dtype=np.float32)
+    rows, n = x.shape
+    blocks = (n + 1023) // 1024
+    vals = np.full((rows, blocks, 32), -np.inf, dtype=np.float32)
+    idx = np.zeros((rows, blocks, 32), dtype=np.uint32)
+    for r in range(rows):
+        for b in range(blocks):
+            seg = x[r, b * 1024:(b + 1) * 1024]
+            order = np.lexsort((np.arange(seg.size), -seg.astype(np.float64)))[:32]  # value descending, then index ascending
+            vals[r, b, :order.size] = seg[order]
+            idx[r, b, :order.size] = order + b * 1024
+    return vals, idx
+
+
 def gemv_threads(fmt, packed, rows, cols, x, m, threads) -> np.ndarray:
     p, x = _u8(packed), _f32(x)
     y = np.empty((m, rows), dtype=np.float32)

@@ -252,3 +252,84 @@ def test_matrices_load_from_a_gguf_file(device, tmp_path):
         s.Matrix.from_gguf(device, f, "blk.0.attn_q.weight", 1, rows + 1, cols)
     with pytest.raises(s.GgufError, match="missing tensor"):
         s.Matrix.from_gguf(device, f, "blk.9.attn_q.weight", 1, rows, cols)
+
+
+@pytest.mark.parametrize("rows,n", [(1, 5120), (3, 2048), (40, 1024)])
+def test_rmsnorm_and_add_rmsnorm(device, rows, n):
+    """`h_rmsnorm` / `h_add_rmsnorm` against the reference's CPU rmsnorm (f64), src/reference.rs:23-36."""
+    s = S()
+    rng = np.random.default_rng(rows)
+    x = rng.standard_normal((rows, n)).astype(np.float32) * 3
+    r = rng.standard_normal((rows, n)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    eps = 1e-6
+    y = torch.zeros(rows * n, dtype=torch.float32, device="cuda")
+    s.rmsnorm(device, dev_f32(x), dev_f32(w), eps, rows, y)
+    device.synchronize()
+    want = ref.rmsnorm(x, w, eps)
+    assert np.abs(host(y).reshape(rows, n) - want).max() <= 2e-6 * np.abs(want).max()
+    h = torch.zeros(rows * n, dtype=torch.float32, device="cuda")
+    y2 = torch.zeros(rows * n, dtype=torch.float32, device="cuda")
+    s.add_rmsnorm(device, dev_f32(x), dev_f32(r), dev_f32(w), eps, rows, h, y2)
+    device.synchronize()
+    assert np.array_equal(host(h).reshape(rows, n), x + r)
+    want2 = ref.rmsnorm(x + r, w, eps)
+    assert np.abs(host(y2).reshape(rows, n) - want2).max() <= 2e-6 * np.abs(want2).max()
+
+
+@pytest.mark.parametrize("fmt", [ref.Q4_K, ref.Q6_K])
+@pytest.mark.parametrize("m", [1, 5, 16, 40])
+def test_rmsnorm_folded_into_the_projection(device, fmt, m):
+    """rmsnorm inside the activation preparation (m <= 16) gives the bits of rmsnorm followed by the projections,
+    and both match the oracle; m = 40 takes the two-step route of the same call."""
+    s = S()
+    cols, rows = 2048, (96, 40)
+    packed = [ref.random_matrix(fmt, r, cols, seed=50 + i) for i, r in enumerate(rows)]
+    ws = [s.Matrix.from_packed(device, r, cols, 1, fmt, p) for r, p in zip(rows, packed)]
+    rng = np.random.default_rng(m)
+    x = (rng.standard_normal((m, cols)) * 2).astype(np.float32)
+    nw = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    eps = 1e-5
+    xd, nwd = dev_f32(x), dev_f32(nw)
+    fused = [torch.zeros(m * r, dtype=torch.float32, device="cuda") for r in rows]
+    scratch = torch.zeros(m * cols, dtype=torch.float32, device="cuda")
+    s.rmsnorm_project_many(device, ws, xd, nwd, eps, m, fused, scratch)
+    device.synchronize()
+    normed = torch.zeros(m * cols, dtype=torch.float32, device="cuda")
+    s.rmsnorm(device, xd, nwd, eps, m, normed)
+    two = [torch.zeros(m * r, dtype=torch.float32, device="cuda") for r in rows]
+    s.project_many(device, ws, normed, m, two)
+    device.synchronize()
+    xn = ref.rmsnorm(x, nw, eps)
+    for yf, yt, p, r in zip(fused, two, packed, rows):
+        assert torch.equal(yf, yt)
+        tol = TOL_F32 if m <= 16 else 1e-3
+        assert ref.rel_err(host(yf).reshape(m, r), ref.matmul(fmt, p, r, cols, xn, m)) <= tol
+
+
+def test_argmax_and_topk_blocks(device):
+    """`h_argmax` and `h_topk_blocks`: exact indices, ties to the lower index."""
+    s = S()
+    rng = np.random.default_rng(8)
+    rows, n = 3, 5000
+    x = rng.standard_normal((rows, n)).astype(np.float32)
+    x[0, 77] = x[0, 4000] = 9.5       # a tie for the maximum: the first wins
+    x[1, 1024:1060] = 3.25            # ties inside a block
+    x[2, :] = -np.inf                 # nothing to rank: index 0
+    out = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    s.argmax(device, dev_f32(x), n, rows, out)
+    blocks = (n + 1023) // 1024
+    top = torch.zeros(rows * blocks * 32 * 2, dtype=torch.float32, device="cuda")
+    s.topk_blocks(device, dev_f32(x), n, rows, top)
+    device.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.argmax_first(x))
+    got = top.cpu().numpy().reshape(rows, blocks, 32, 2)
+    vals, idx = ref.topk_blocks(x)
+    assert np.array_equal(got[..., 0].view(np.uint32)[:2], vals.view(np.uint32)[:2])
+    assert np.array_equal(np.ascontiguousarray(got[..., 1]).view(np.uint32)[:2], idx[:2])
+    # the head of the vocabulary for a 65,536-row logit vector, one row
+    big = rng.standard_normal((1, 65536)).astype(np.float32)
+    out1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    s.argmax(device, dev_f32(big), 65536, 1, out1)
+    device.synchronize()
+    assert int(out1.item()) == int(np.argmax(big))
