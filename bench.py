@@ -537,7 +537,7 @@ def ep_parity(S, dev, torch, dist, rank, world):
                     shared[1], shared[2], shared[3], None, E, USED, H, F, F, False, True)
     torch.manual_seed(11)
     x = (torch.randn(T * H, device="cuda") * 0.12).contiguous()
-    comm = S.Comm(dev, rank, world, 4096 + T * USED * H * 4)
+    comm = S.Comm(dev, rank, world, 4096 + T * USED * H * 4 + 64 * H * 4)
     scratch = torch.zeros(S.moe_ffn_scratch_elems(dev, mine, T), dtype=torch.float32, device="cuda")
     out = torch.zeros(T * H, dtype=torch.float32, device="cuda")
     S.moe_ffn_ep(dev, comm, 4096, mine, rank * local, x, T, scratch, out)
@@ -569,7 +569,7 @@ def moe_ep_bench(S, dev, stream, torch, dist, timed_ms, rank, world):
                  M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 904)), M(dev, F, H, 1, Q4_K, random_matrix(Q4_K, F, H, 905)),
                  M(dev, H, F, 1, Q6_K, random_matrix(Q6_K, H, F, 906)), None, E, USED, H, F, F, False, True)
     # Two exchange regions used in turn: consecutive exchanges of a communicator may not share a region.
-    region_bytes = 1024 * USED * H * 4
+    region_bytes = 1024 * USED * H * 4 + 1024 * H * 4  # the expert rows, then the combined outputs
     comm = S.Comm(dev, rank, world, 4096 + 2 * region_bytes)
     res = {}
     for T in (1, 1024):
@@ -592,7 +592,10 @@ def moe_ep_bench(S, dev, stream, torch, dist, timed_ms, rank, world):
                 pair()
         reps = 5
         ms = timed_ms(pair, reps) / (2 * reps)
-        res[f"t{T}"] = {"us": round(ms * 1e3, 1), "experts_per_rank": local, "exchange_bytes": T * USED * H * 4}
+        inbound = (T * USED * H * 4 * (world - 1) // world if T * USED <= 32 else
+                   (T * USED * H * 4 // world + T * H * 4) * (world - 1) // world)
+        res[f"t{T}"] = {"us": round(ms * 1e3, 1), "experts_per_rank": local, "inbound_bytes_per_rank": inbound,
+                        "exchange": "all rows to all ranks" if T * USED <= 32 else "rows to the token's owner, then the outputs gathered"}
     dev.synchronize()
     dist.barrier()
     comm.close()

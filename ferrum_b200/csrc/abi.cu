@@ -3,6 +3,7 @@
 // checks in src/metal/mod.rs:838-897).
 #include <cstdarg>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <utility>
 #include <vector>
@@ -980,10 +981,16 @@ extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset
     MoeScratch s = moe_layout(f, m, scratch);
     if (scratch_elems < s.total) return fq_fail(dev, FQ_ERR_SHAPE, "MoE scratch holds %zu of %zu floats", scratch_elems, s.total);
     const size_t routes = m * used;
-    if (region_offset % 16 || region_offset + routes * hidden * 4 > fq_comm_bytes(comm))
-        return fq_fail(dev, FQ_ERR_RANGE, "%zu expert rows of %zu floats at offset %zu do not fit the symmetric buffer", routes, hidden, region_offset);
-    float *down = (float *)(fq_comm_local(comm) + region_offset);
     const bool narrow = (routes <= MV_ID_MAX_ROUTES && !dev->exact);
+    // Wide inputs combine every token on ONE rank (tokens are split evenly, `per_rank` to a rank, a multiple of 4),
+    // so the symmetric buffer holds the expert rows and, after them, the combined outputs of all tokens.
+    const bool owner_combine = world > 1 && !narrow && !dev->exact;
+    const size_t per_rank = ((m + world - 1) / world + 3) / 4 * 4;
+    const size_t rows_bytes = (routes * hidden * 4 + 255) / 256 * 256, out_bytes = owner_combine ? per_rank * world * hidden * 4 : 0;
+    if (region_offset % 16 || region_offset + rows_bytes + out_bytes > fq_comm_bytes(comm))
+        return fq_fail(dev, FQ_ERR_RANGE, "%zu expert rows of %zu floats (and %zu bytes of outputs) at offset %zu do not fit the symmetric buffer", routes,
+                       hidden, out_bytes, region_offset);
+    float *down = (float *)(fq_comm_local(comm) + region_offset);
     // As in fq_moe_ffn: at decode widths the (replicated) shared expert runs on the side stream.
     SideBranch side = narrow ? side_begin(dev) : SideBranch{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
     int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared);
@@ -1013,6 +1020,21 @@ extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset
     }
     if (int rc2 = side_join(side)) rc = rc ? rc : rc2; // also after an error: a capture must not end with the branch open
     if (rc) return rc;
+    if (owner_combine) {
+        // All-to-all, dispatch half: a row goes only to the rank that combines its token.  That rank then has all
+        // `used` rows of each of its tokens and combines them in the usual order; the outputs are gathered.
+        if (int rc = fq_comm_dispatch_rows(dev, comm, region_offset, hidden * 4, s.offsets, (uint32_t)local, s.sorted, (uint32_t)used,
+                                           (uint32_t)per_rank, routes))
+            return rc;
+        float *outs = (float *)(fq_comm_local(comm) + region_offset + rows_bytes);
+        const size_t token0 = (size_t)rank * per_rank, mine_count = token0 < m ? std::min(per_rank, m - token0) : 0;
+        if (int rc = fq_launch_moe_combine_range(dev, down, s.weights, s.position, s.shared, s.gate, (uint32_t)hidden, (uint32_t)used, (uint32_t)token0,
+                                                 (uint32_t)mine_count, outs))
+            return rc;
+        if (int rc = fq_comm_all_gather(dev, comm, region_offset + rows_bytes, per_rank * hidden * 4)) return rc;
+        if (int rc = fq_begin_enqueue(dev)) return rc;
+        return fq_check_cuda(dev, cudaMemcpyAsync(out, outs, m * hidden * 4, cudaMemcpyDeviceToDevice, dev->stream), "output copy");
+    }
     if (int rc = fq_comm_all_gather_rows(dev, comm, region_offset, hidden * 4, s.offsets, (uint32_t)local, routes)) return rc;
     return fq_moe_combine(dev, down, s.weights, s.position, s.shared, s.gate, (uint32_t)hidden, (uint32_t)used, (uint32_t)m, 0, out);
 }

@@ -41,33 +41,13 @@ struct Peers {
     uint8_t *base[FQ_COMM_MAX_WORLD];
 };
 
-// grid (world - 1, chunks): block (p, c) copies chunk c of the shard to the p-th other rank; chunk 0's block
-// also does the handshake with that rank.
-// With `bounds` (device memory, written by an earlier kernel of the stream) the shards are runs of rows of
-// unequal length: rank r owns rows bounds[r * stride] .. bounds[(r + 1) * stride] of `shard_bytes` bytes each,
-// laid out from region_off in row order (the expert-sorted rows of an expert-parallel MoE block).
-__global__ void __launch_bounds__(256)
-k_all_gather_push(const __grid_constant__ Peers peers, int rank, int world, size_t payload_bytes, size_t region_off,
-                  size_t shard_bytes, const uint32_t *__restrict__ bounds, uint32_t stride, uint32_t slot, uint32_t *seq, uint64_t wait_ns,
-                  int *status) {
-    // Launched with programmatic stream serialization: let the next kernel stage itself, then wait for the
-    // projection that produced the local shard.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int other = (int)blockIdx.x < rank ? (int)blockIdx.x : (int)blockIdx.x + 1;
-    size_t mine = region_off + (size_t)rank * shard_bytes;
-    if (bounds) {
-        const uint32_t lo = bounds[(size_t)rank * stride], hi = bounds[(size_t)(rank + 1) * stride];
-        mine = region_off + (size_t)lo * shard_bytes;
-        shard_bytes *= hi - lo;
-    }
-    const uint4 *src = reinterpret_cast<const uint4 *>(peers.base[rank] + mine);
-    uint4 *dst = reinterpret_cast<uint4 *>(peers.base[other] + mine);
-    const size_t n16 = shard_bytes / 16;
-    for (size_t i = (size_t)blockIdx.y * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.y * blockDim.x) dst[i] = src[i];
+// After the blocks of grid column `other` have stored their share into that peer's buffer: the stores are made
+// visible, the chunks are counted in, and the last chunk's first thread raises this rank's flag in the peer's
+// flag words and waits -- bounded by wall time -- for the peer's flag for the same call site.
+__device__ __forceinline__ void finish_push(const Peers &peers, int rank, int other, size_t payload_bytes, uint32_t slot, uint32_t *seq,
+                                            uint64_t wait_ns, int *status) {
     __threadfence_system();
     __syncthreads();
-    // The chunks of one peer are counted in before the flag is raised.
     __shared__ bool last;
     uint32_t *done = seq + (size_t)FQ_COMM_SLOTS * FQ_COMM_MAX_WORLD * 2 + (size_t)slot * FQ_COMM_MAX_WORLD + other;
     if (threadIdx.x == 0) last = atomicAdd(done, 1u) + 1u == gridDim.y;
@@ -96,6 +76,57 @@ k_all_gather_push(const __grid_constant__ Peers peers, int rank, int world, size
         }
     }
     *(volatile int *)status = (int)FQ_ERR_TIMEOUT; // the peer never arrived: report, do not hang
+}
+
+// grid (world - 1, chunks): block (p, c) copies chunk c of the shard to the p-th other rank; the last chunk's
+// block also does the handshake with that rank.
+// With `bounds` (device memory, written by an earlier kernel of the stream) the shards are runs of rows of
+// unequal length: rank r owns rows bounds[r * stride] .. bounds[(r + 1) * stride] of `shard_bytes` bytes each,
+// laid out from region_off in row order (the expert-sorted rows of an expert-parallel MoE block).
+__global__ void __launch_bounds__(256)
+k_all_gather_push(const __grid_constant__ Peers peers, int rank, int world, size_t payload_bytes, size_t region_off,
+                  size_t shard_bytes, const uint32_t *__restrict__ bounds, uint32_t stride, uint32_t slot, uint32_t *seq, uint64_t wait_ns,
+                  int *status) {
+    // Launched with programmatic stream serialization: let the next kernel stage itself, then wait for the
+    // projection that produced the local shard.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int other = (int)blockIdx.x < rank ? (int)blockIdx.x : (int)blockIdx.x + 1;
+    size_t mine = region_off + (size_t)rank * shard_bytes;
+    if (bounds) {
+        const uint32_t lo = bounds[(size_t)rank * stride], hi = bounds[(size_t)(rank + 1) * stride];
+        mine = region_off + (size_t)lo * shard_bytes;
+        shard_bytes *= hi - lo;
+    }
+    const uint4 *src = reinterpret_cast<const uint4 *>(peers.base[rank] + mine);
+    uint4 *dst = reinterpret_cast<uint4 *>(peers.base[other] + mine);
+    const size_t n16 = shard_bytes / 16;
+    for (size_t i = (size_t)blockIdx.y * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.y * blockDim.x) dst[i] = src[i];
+    finish_push(peers, rank, other, payload_bytes, slot, seq, wait_ns, status);
+}
+
+// The dispatch half of an all-to-all over expert-sorted rows: of this rank's run of rows
+// [bounds[rank * stride], bounds[(rank + 1) * stride]) -- the rows its experts produced -- row p goes ONLY to the
+// rank that owns its token, sorted[p] / used / tokens_per_rank, at the same place in that rank's buffer.  Same
+// grid and handshake as the gather: block (p, c) serves the p-th other rank.
+__global__ void __launch_bounds__(256)
+k_dispatch_rows(const __grid_constant__ Peers peers, int rank, int world, size_t payload_bytes, size_t region_off, size_t row_bytes,
+                const uint32_t *__restrict__ bounds, uint32_t stride, const uint32_t *__restrict__ sorted, uint32_t used, uint32_t tokens_per_rank,
+                uint32_t slot, uint32_t *seq, uint64_t wait_ns, int *status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int other = (int)blockIdx.x < rank ? (int)blockIdx.x : (int)blockIdx.x + 1;
+    const uint32_t lo = bounds[(size_t)rank * stride], hi = bounds[(size_t)(rank + 1) * stride];
+    const size_t n16 = row_bytes / 16;
+    for (uint32_t row = lo + blockIdx.y; row < hi; row += gridDim.y) {
+        const uint32_t owner = min(sorted[row] / used / tokens_per_rank, (uint32_t)world - 1u);
+        if ((int)owner != other) continue;
+        const size_t at = region_off + (size_t)row * row_bytes;
+        const uint4 *src = reinterpret_cast<const uint4 *>(peers.base[rank] + at);
+        uint4 *dst = reinterpret_cast<uint4 *>(peers.base[other] + at);
+        for (size_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+    }
+    finish_push(peers, rank, other, payload_bytes, slot, seq, wait_ns, status);
 }
 
 size_t flag_bytes() { return (size_t)FQ_COMM_SLOTS * FQ_COMM_MAX_WORLD * sizeof(uint32_t); }
@@ -286,6 +317,38 @@ extern "C" int fq_comm_all_gather_rows(fq_device *dev, fq_comm *c, size_t region
     if (c->world == 1) return FQ_OK;
     if (int rc = fq_comm_note_region(dev, c, region_offset, row_bytes * total_rows)) return rc;
     return launch_gather(dev, c, region_offset, row_bytes, bounds, stride, row_bytes * total_rows / c->world);
+}
+
+// Rows of this rank's run to the ranks that own their tokens (see k_dispatch_rows); every rank makes the call.
+int fq_comm_dispatch_rows(fq_device *dev, fq_comm *c, size_t region_offset, size_t row_bytes, const uint32_t *bounds, uint32_t stride,
+                          const uint32_t *sorted, uint32_t used, uint32_t tokens_per_rank, size_t total_rows) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (!c || c->dev != dev) return fq_fail(dev, FQ_ERR_DEVICE, "communicator belongs to another device handle");
+    if (!c->opened) return fq_fail(dev, FQ_ERR_PARAM, "communicator peers are not opened");
+    if (row_bytes == 0 || row_bytes % 16 || region_offset % 16 || stride == 0 || used == 0 || tokens_per_rank == 0 ||
+        region_offset + row_bytes * total_rows > c->bytes)
+        return fq_fail(dev, FQ_ERR_RANGE, "dispatch of %zu rows of %zu bytes at offset %zu does not fit %zu bytes", total_rows, row_bytes, region_offset, c->bytes);
+    if (c->world == 1) return FQ_OK;
+    if (int rc = fq_comm_note_region(dev, c, region_offset, row_bytes * total_rows)) return rc;
+    Peers peers{};
+    for (int r = 0; r < c->world; r++) peers.base[r] = c->peer[r];
+    const uint32_t slot = c->next_slot;
+    c->next_slot = (c->next_slot + 1) % FQ_COMM_SLOTS;
+    const unsigned chunks = (unsigned)std::min<size_t>(64, std::max<size_t>(1, total_rows / c->world / 8));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(c->world - 1, chunks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (int rc = fq_check_cuda(dev, cudaLaunchKernelEx(&cfg, k_dispatch_rows, peers, c->rank, c->world, c->bytes, region_offset, row_bytes, bounds,
+                                                       stride, sorted, used, tokens_per_rank, slot, c->seq, c->wait_ns, dev->status_dev),
+                               "row dispatch launch"))
+        return rc;
+    return fq_end_enqueue(dev, "dispatch_rows", 1);
 }
 
 extern "C" int fq_comm_destroy(fq_comm *c) {

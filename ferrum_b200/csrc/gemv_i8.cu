@@ -28,6 +28,7 @@
 // shared memory in a fixed order, so results are deterministic and a row-sharded matrix gives the
 // same bits as the whole one.
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -573,8 +574,10 @@ namespace {
 // Device address of g_static_scratch per device ordinal.  In host code the array's name is only a
 // stand-in for the symbol; the address a kernel can use comes from cudaGetSymbolAddress, taken once
 // per device with that device current.
+// Published with release / read with acquire: a host thread that sees the address also sees the SM count
+// stored before it, so two threads may make a device's first call at the same time.
 constexpr int MAX_DEVICES = 64;
-uint8_t *g_static_ptr[MAX_DEVICES];
+std::atomic<uint8_t *> g_static_ptr[MAX_DEVICES];
 int g_static_sms[MAX_DEVICES];
 
 int static_fail(char *err, size_t err_len, int status, const char *fmt, ...) {
@@ -609,7 +612,7 @@ cudaError_t launch_static(const uint8_t *w, uint32_t rows, uint32_t pitch, float
         if (waste < best) { best = waste; warps = k; }
     }
     k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u, TpPush{});
-    return cudaPeekAtLastError();
+    return cudaGetLastError();
 }
 
 } // namespace
@@ -629,11 +632,18 @@ extern "C" int fq_gemv_q4k_static(const void *w_packed, uint64_t rows, uint64_t 
         return static_fail(err, err_len, FQ_ERR_SHAPE,
                            "%u rows of %llu activations need %zu bytes of prepared activations; the fixed scratch holds %zu",
                            m, (unsigned long long)cols, (size_t)m * L.token_bytes, STATIC_SCRATCH_BYTES);
+    {
+        // The three bindings must not overlap one another (the handle-based path checks the same).
+        const uintptr_t wa = (uintptr_t)w_packed, wb = wa + (size_t)rows * (cols / 256 * 144), xa = (uintptr_t)x, xb = xa + (size_t)m * cols * 4,
+                        ya = (uintptr_t)y, yb = ya + (size_t)m * rows * 4;
+        if ((ya < xb && xa < yb) || (ya < wb && wa < yb)) return static_fail(err, err_len, FQ_ERR_ALIAS, "the output overlaps an input");
+    }
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
         return static_fail(err, err_len, FQ_ERR_DEVICE, "no current CUDA device: %s", cudaGetErrorString(e));
-    if (!g_static_ptr[dev]) {
+    uint8_t *prep = g_static_ptr[dev].load(std::memory_order_acquire);
+    if (!prep) {
         // First call on this device: resolve the array's device address (and the SM count).
         uint8_t *p = nullptr;
         e = cudaGetSymbolAddress((void **)&p, g_static_scratch);
@@ -643,14 +653,15 @@ extern "C" int fq_gemv_q4k_static(const void *w_packed, uint64_t rows, uint64_t 
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess || sms <= 0) return static_fail(err, err_len, FQ_ERR_CUDA, "SM count: %s", cudaGetErrorString(e));
         g_static_sms[dev] = sms;
-        g_static_ptr[dev] = p;
+        g_static_ptr[dev].store(p, std::memory_order_release);
+        prep = p;
     }
-    uint8_t *prep = g_static_ptr[dev];
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const uint32_t warps = m * L.nblk;
+    cudaGetLastError(); // an error the caller left behind is not this call's
     // Every byte the GEMV reads from the scratch is rewritten here first, so nothing has to start at zero.
     k_prep_i8<<<(warps + 3) / 4, 128, 0, stream>>>(x, nullptr, nullptr, 0.f, m, L, prep);
-    if ((e = cudaPeekAtLastError()) != cudaSuccess)
+    if ((e = cudaGetLastError()) != cudaSuccess)
         return static_fail(err, err_len, FQ_ERR_CUDA, "activation preparation launch: %s", cudaGetErrorString(e));
     const uint32_t pitch = (uint32_t)(cols / 256 * 144);
     const uint8_t *w = (const uint8_t *)w_packed;

@@ -178,6 +178,14 @@ int fq_comm_note_region(fq_device *dev, fq_comm *c, size_t off, size_t bytes);
 int fq_comm_note_graph(fq_device *dev, const struct fq_graph *g);
 fq_device *fq_comm_device(const fq_comm *c);
 int fq_comm_all_gather_unchecked(fq_device *dev, fq_comm *c, size_t region_offset, size_t shard_bytes);
+// The dispatch half of an all-to-all over expert-sorted rows: row p of this rank's run (bounds / stride as in
+// fq_comm_all_gather_rows) goes only to the rank that owns token sorted[p] / used, token t belonging to rank
+// min(t / tokens_per_rank, world - 1).
+int fq_comm_dispatch_rows(fq_device *dev, fq_comm *c, size_t region_offset, size_t row_bytes, const uint32_t *bounds, uint32_t stride,
+                          const uint32_t *sorted, uint32_t used, uint32_t tokens_per_rank, size_t total_rows);
+// `fq_moe_combine` for tokens [token0, token0 + tokens) of a block (internal buffers: no binding checks).
+int fq_launch_moe_combine_range(fq_device *dev, const float *down, const float *weights, const uint32_t *position, const float *shared,
+                                const float *gate, uint32_t hidden, uint32_t used, uint32_t token0, uint32_t tokens, float *out);
 // The symmetric buffer of a communicator and its geometry (comm.cu).
 struct fq_comm;
 uint8_t *fq_comm_local(fq_comm *c);

@@ -362,6 +362,18 @@ extern "C" int fq_moe_gather(fq_device *dev, const float *x, const uint32_t *sor
     return fq_end_enqueue(dev, "moe_gather", 1);
 }
 
+// Tokens [token0, token0 + tokens): out[t] for those tokens only (`out` is indexed by the token, like the rest).
+int fq_launch_moe_combine_range(fq_device *dev, const float *down, const float *weights, const uint32_t *position, const float *shared,
+                                const float *gate, uint32_t hidden, uint32_t used, uint32_t token0, uint32_t tokens, float *out) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (tokens == 0) return FQ_OK;
+    const size_t n = (size_t)tokens * hidden;
+    k_moe_combine<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(down, weights + (size_t)token0 * used, position + (size_t)token0 * used,
+                                                                       shared + (size_t)token0 * hidden, gate + token0, hidden, used, tokens, 0,
+                                                                       out + (size_t)token0 * hidden);
+    return fq_end_enqueue(dev, "moe_combine", 1);
+}
+
 extern "C" int fq_moe_combine(fq_device *dev, const float *down, const float *weights, const uint32_t *position,
                               const float *shared, const float *gate, uint32_t hidden, uint32_t used,
                               uint32_t tokens, int identity, float *out) {

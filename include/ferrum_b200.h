@@ -350,10 +350,14 @@ int fq_project_many_gather(fq_device *dev, fq_comm *comm, size_t region_offset, 
 /* `fq_moe_ffn` with the experts sharded over the ranks of `comm`: rank r stores experts
  * [r E / g, (r + 1) E / g) -- the expert matrices of `f` hold only those (`f->experts` stays E), and
  * `expert_first` = r E / g.  x, the router and the shared expert are replicated.  Every rank routes all
- * tokens, computes the expert-sorted rows of its own experts into the symmetric buffer at `region_offset`
- * (m * used * hidden floats must fit), the runs are exchanged with `fq_comm_all_gather_rows`, and every rank
- * combines: `out` is complete on every rank and equals `fq_moe_ffn` on one GPU bit for bit.  All ranks
- * must make the same calls in the same order.  Scratch as for `fq_moe_ffn`. */
+ * tokens and computes the expert-sorted rows of its own experts into the symmetric buffer at `region_offset`.
+ * With more than 32 routes the exchange is an all-to-all: a row goes only to the rank that owns its token
+ * (tokens are split evenly, ceil(m / g) rounded up to a multiple of 4 to a rank), the owner combines its tokens,
+ * and the combined outputs are gathered; the buffer must hold, from `region_offset`, m * used * hidden floats
+ * (rounded up to 256 bytes) and then g * tokens-per-rank * hidden floats.  With 32 routes or fewer every row is
+ * gathered on every rank (`fq_comm_all_gather_rows`) and every rank combines.  Either way `out` is complete on
+ * every rank and equals `fq_moe_ffn` on one GPU bit for bit.  All ranks must make the same calls in the same
+ * order.  Scratch as for `fq_moe_ffn`. */
 int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset, const fq_moe_ffn_desc *f, uint32_t expert_first,
                   const float *x, size_t m, float *scratch, size_t scratch_elems, float *out);
 

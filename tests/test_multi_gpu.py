@@ -127,9 +127,9 @@ def _ep_rank(rank, world, port, out_dir):
                         M(d, ef, hidden, local, ref.Q4_K, experts_of(up_e, ref.Q4_K, ef, hidden, first, local)),
                         M(d, hidden, ef, local, ref.Q6_K, experts_of(down_e, ref.Q6_K, hidden, ef, first, local)),
                         shared[1], shared[2], shared[3], None, experts, used, hidden, ef, ef, False, True)
-        half = 300 * used * hidden * 4
+        half = 300 * used * hidden * 4 + 304 * hidden * 4 + 4096  # the expert rows, then the combined outputs
         comm = S.Comm(d, rank, world, 4096 + 2 * half)
-        for i, m in enumerate((1, 3, 40, 300)):  # per-route GEMVs (m * used <= 32), the grouped integer kernel, the grouped GEMM
+        for i, m in enumerate((1, 3, 40, 300)):  # per-route GEMVs (m * used <= 32, rows gathered everywhere), then rows sent to the token's owner: grouped integer kernel, grouped GEMM
             x = torch.from_numpy((np.random.default_rng(m).standard_normal((m, hidden)) * 0.12).astype(np.float32)).cuda()
             n = S.moe_ffn_scratch_elems(d, whole, m)
             want = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")

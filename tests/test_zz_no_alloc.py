@@ -30,7 +30,7 @@ def call_static(lib, w_dev, rows, cols, x_dev, m, y_dev, stream):
     return rc, err.value.decode()
 
 
-@pytest.mark.parametrize("m", [1, 3])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
 def test_static_entry_point_matches_project(m):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
@@ -74,3 +74,6 @@ def test_static_entry_point_rejects_what_does_not_fit():
     assert rc == _lib.ERR_SHAPE and "activation rows" in msg
     rc, msg = call_static(lib, buf, 16, 300, buf, 1, buf, 0)    # not whole superblocks
     assert rc == _lib.ERR_SHAPE
+    w = torch.zeros(16 * 288, dtype=torch.uint8, device="cuda")  # 16 rows of 512 Q4_K weights
+    rc, msg = call_static(lib, w, 16, 512, buf, 1, buf[256:], 0)  # the output lies inside the activations
+    assert rc == _lib.ERR_ALIAS and "overlaps" in msg
