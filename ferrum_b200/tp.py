@@ -58,6 +58,21 @@ def shard_experts(packed: np.ndarray, fmt: int, rows_e: int, cols: int, experts:
     return packed[first * per_expert:(first + count) * per_expert]
 
 
+def token_owner_range(tokens: int, rank: int, world: int) -> Tuple[int, int, int]:
+    """Expert parallelism at wide inputs combines every token on one rank: ``ceil(tokens / world)`` rounded up to a
+    multiple of 4 tokens per rank, contiguous.  Returns (tokens per rank, first token of ``rank``, its token count)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} of {world}")
+    per = ((tokens + world - 1) // world + 3) // 4 * 4
+    first = rank * per
+    return per, first, max(0, min(per, tokens - first))
+
+
+def token_owner(token: int, per_rank: int, world: int) -> int:
+    """The rank that combines ``token``."""
+    return min(token // per_rank, world - 1)
+
+
 def gathered_to_rows(gathered, m: int, rows: int, world: int):
     """``all_gather_into_tensor`` concatenates rank outputs ``[world][m][rows / world]``; the projection's
     output is ``[m][rows]``.  Works on torch tensors and numpy arrays (a view plus one transposing copy)."""

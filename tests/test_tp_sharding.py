@@ -91,6 +91,76 @@ def _ep_rank_main(rank, world, port, out_path):
         dist.destroy_process_group()
 
 
+def _ep_all_to_all_main(rank, world, port, out_path):
+    """The wide-input exchange on CPU ranks: a rank's expert rows go only to the ranks that own their tokens, the
+    owners combine their tokens, the outputs are gathered.  The oracle stands in for the kernels; what is under
+    test is who sends what to whom and that every owner ends up with all rows of its tokens."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        experts, used, hidden, m = 12, 2, 64, 11
+        rng = np.random.default_rng(5)
+        logits = rng.standard_normal((m, experts)).astype(np.float32)
+        x = rng.standard_normal((m, hidden)).astype(np.float32)
+        ids, wts, gate = ref.moe_route(logits, x, x[0], experts, used, hidden, m, False, True, False)
+        offsets, sorted_, position = ref.moe_map(ids, experts)
+        routes = m * used
+        # stand-in for the expert projections: row p of the sorted set depends on its route and its expert only
+        sorted_ids = np.asarray(ids).reshape(-1)[np.asarray(sorted_)]
+        all_rows = (np.asarray(sorted_)[:, None] * 1000 + sorted_ids[:, None] * 7 + np.arange(hidden)[None, :]).astype(np.float32)
+        first, count = tp.expert_range(experts, rank, world)
+        lo, hi = int(offsets[first]), int(offsets[first + count])
+        per, token0, mine = tp.token_owner_range(m, rank, world)
+        assert per % 4 == 0 and per * world >= m
+        # dispatch: only to the owner of the row's token
+        outbox = [[] for _ in range(world)]
+        for p in range(lo, hi):
+            outbox[tp.token_owner(int(sorted_[p]) // used, per, world)].append((p, all_rows[p]))
+        gathered = [None] * world
+        dist.all_gather_object(gathered, outbox)  # gloo has no object all-to-all: gather the outboxes, take this rank's column
+        have = np.full((routes, hidden), np.nan, dtype=np.float32)
+        received = 0
+        for sender in range(world):
+            for p, row in gathered[sender][rank]:
+                have[p] = row
+                received += 1
+        assert received == mine * used, "an owner receives exactly the rows of its tokens"
+        zero = np.zeros((m, hidden), dtype=np.float32)
+        part = np.zeros((per, hidden), dtype=np.float32)
+        if mine:
+            sl = slice(token0, token0 + mine)
+            sub_pos = np.asarray(position).reshape(m, used)[sl].reshape(-1)
+            assert np.isfinite(have[sub_pos]).all()
+            # combine the owner's tokens: the oracle on the sub-range, positions unchanged (they index the whole set)
+            full = np.where(np.isfinite(have), have, 0).astype(np.float32)
+            part[:mine] = ref.moe_combine(full, np.asarray(wts).reshape(m, used)[sl].reshape(-1), sub_pos, zero[sl],
+                                          np.asarray(gate)[sl], hidden, used, mine, identity=False)
+        outs = [None] * world
+        dist.all_gather_object(outs, part)
+        got = np.concatenate(outs)[:m]
+        want = ref.moe_combine(all_rows, wts, position, zero, gate, hidden, used, m, identity=False)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        if rank == 0:
+            np.save(out_path, got)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_cpu_ranks_exchange_rows_with_the_token_owners(tmp_path, world):
+    out = str(tmp_path / "a2a.npy")
+    mp.spawn(_ep_all_to_all_main, args=(world, free_port(), out), nprocs=world, join=True)
+    assert np.load(out).shape == (11, 64)
+
+
+def test_token_owner_split():
+    assert tp.token_owner_range(1024, 3, 8) == (128, 384, 128)
+    assert tp.token_owner_range(40, 1, 2) == (20, 20, 20)
+    assert tp.token_owner_range(41, 7, 8) == (8, 56, 0)      # the last ranks may own nothing
+    assert tp.token_owner_range(41, 5, 8) == (8, 40, 1)
+    assert tp.token_owner(40, 8, 8) == 5 and tp.token_owner(1000, 8, 8) == 7
+
+
 def test_two_cpu_ranks_split_the_experts(tmp_path):
     out = str(tmp_path / "moe.npy")
     mp.spawn(_ep_rank_main, args=(2, free_port(), out), nprocs=2, join=True)
