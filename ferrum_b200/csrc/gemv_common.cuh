@@ -202,6 +202,70 @@ __device__ __forceinline__ void tp_finish(const TpPush &P, uint32_t seq) {
     }
 }
 
+// ---------------------------------------------------------------- per-warp weight rings
+//
+// A warp streams the packed superblocks of its 16-row weight tiles through a private ring of stages in shared
+// memory with 16-byte asynchronous copies: several superblocks in flight per warp, no registers held, no
+// block-wide barrier.  A stage holds one superblock of 16 rows, row r at r * ROW (ROW >= the bytes of a row's
+// superblock, padded so that the reads of a kernel's fragment pattern fall on different banks):
+//   Q4_K / Q5_K  the 144 / 176 bytes of the block;
+//   Q6_K         ql[128] | qh[64] | scales[16] of the device layout (blocks.cuh), and after the 16 rows 4 bytes
+//                per row: the aligned word that holds the f16 d of the superblock (its high half for odd b).
+// A lane copies the same pieces of every superblock, so their offsets from the tile's first row are worked out
+// once per tile (`start_tile`); rows past the end of the matrix read its last row.
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int FMT, uint32_t ROW> struct WeightRing {
+    static constexpr uint32_t SRC = FMT == FQ_Q4_K ? 144 : FMT == FQ_Q5_K ? 176 : 208; // bytes copied per row and superblock
+    static constexpr uint32_t PER_ROW = SRC / 16;
+    static constexpr uint32_t PIECES = 16 * PER_ROW;
+    static constexpr int NP = FMT == FQ_Q6_K ? 7 : (int)((PIECES + 31) / 32);
+    static constexpr uint32_t BYTES = 16 * ROW + (FMT == FQ_Q6_K ? 64 : 0);
+    static_assert(ROW >= SRC && ROW % 16 == 0, "stage rows hold a row's superblock and stay 16-byte aligned");
+    const uint8_t *base = nullptr;
+    uint32_t off[NP];
+    // Q6_K: pieces 0..127 are ql (row p / 8), 128..191 qh (row / 4), 192..207 the scales, 208..223 the word with d.
+    __device__ __forceinline__ uint32_t piece_row(int i, uint32_t lane) const {
+        const uint32_t p = lane + 32 * i;
+        if constexpr (FMT != FQ_Q6_K) return p / PER_ROW;
+        return i < 4 ? p / 8 : i < 6 ? (p - 128) / 4 : (lane & 15);
+    }
+    // `first_row`: the tile's first weight row; `last`: index of the matrix's last row relative to it.
+    __device__ __forceinline__ void start_tile(const uint8_t *first_row, uint32_t last, uint32_t pitch, uint32_t nblk, uint32_t lane) {
+        base = first_row;
+#pragma unroll
+        for (int i = 0; i < NP; i++) {
+            const uint32_t p = lane + 32 * i, r = min(piece_row(i, lane), last);
+            uint32_t in_row;
+            if constexpr (FMT != FQ_Q6_K) in_row = 16 * (p % PER_ROW);
+            else in_row = i < 4 ? 16 * (p % 8) : i < 6 ? nblk * 128 + 16 * (p % 4) : lane < 16 ? nblk * 192 : nblk * 208;
+            off[i] = r * pitch + in_row;
+        }
+    }
+    // Superblock b of the tile into the stage at `dst`.
+    __device__ __forceinline__ void issue(uint8_t *dst, uint32_t b, uint32_t lane) const {
+#pragma unroll
+        for (int i = 0; i < NP; i++) {
+            const uint32_t p = lane + 32 * i;
+            if constexpr (FMT != FQ_Q6_K) {
+                if (p < PIECES) cp_async16(dst + ROW * (p / PER_ROW) + 16 * (p % PER_ROW), base + (off[i] + b * SRC));
+            } else {
+                if (i < 4) cp_async16(dst + ROW * (p / 8) + 16 * (p % 8), base + (off[i] + b * 128));
+                else if (i < 6) cp_async16(dst + ROW * ((p - 128) / 4) + 128 + 16 * (p % 4), base + (off[i] + b * 64));
+                else if (lane < 16) cp_async16(dst + ROW * lane + 192, base + (off[i] + b * 16));
+                else cp_async4(dst + 16 * ROW + 4 * (lane - 16), base + (off[i] + (b & ~1u) * 2)); // the aligned 4 bytes that hold d
+            }
+        }
+    }
+};
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg{};

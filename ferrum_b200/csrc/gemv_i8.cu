@@ -58,7 +58,7 @@ struct PrepI8 {
     uint32_t lo_off, sx32_off, sx16_off, isc_off, token_bytes;
 };
 
-PrepI8 prep_i8_layout(uint32_t cols) {
+__host__ __device__ inline PrepI8 prep_i8_layout(uint32_t cols) {
     PrepI8 L;
     L.cols = cols;
     L.nblk = cols / 256;
@@ -74,21 +74,23 @@ PrepI8 prep_i8_layout(uint32_t cols) {
 // the layout above at `base` (global or shared memory).
 // With `urow` the activations are the gated unit silu(x) * u, x / (1 + exp(-x)) * u as `k_swiglu` computes it.
 // With `norm_w` they are rmsnorm(x) * norm_w (`h_rmsnorm`, src/metal/shaders/hybrid.metal:1563-1575).
-__device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base,
-                                                const float *__restrict__ urow = nullptr, const float *__restrict__ norm_w = nullptr, float eps = 0.f) {
-    const float4 *src = reinterpret_cast<const float4 *>(xrow + (size_t)b * 256 + lane * 8);
+// `bsrc` is the superblock of the row that is read, `b` the slot of the layout `L` it is written to (the same
+// unless `L` describes a slice of the row); `norm_scale` = row_inv_rms of the whole row when `norm_w` is given.
+__device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, uint32_t bsrc, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base,
+                                                const float *__restrict__ urow, const float *__restrict__ norm_w, float norm_scale) {
+    const float4 *src = reinterpret_cast<const float4 *>(xrow + (size_t)bsrc * 256 + lane * 8);
     const float4 v0 = src[0], v1 = src[1];
     float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     if (norm_w) {
-        const float scale = row_inv_rms(xrow, L.cols, eps, lane);
-        const float4 *ws = reinterpret_cast<const float4 *>(norm_w + (size_t)b * 256 + lane * 8);
+        const float scale = norm_scale;
+        const float4 *ws = reinterpret_cast<const float4 *>(norm_w + (size_t)bsrc * 256 + lane * 8);
         const float4 w0 = ws[0], w1 = ws[1];
         const float g[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = v[i] * scale * g[i];
     }
     if (urow) {
-        const float4 *us = reinterpret_cast<const float4 *>(urow + (size_t)b * 256 + lane * 8);
+        const float4 *us = reinterpret_cast<const float4 *>(urow + (size_t)bsrc * 256 + lane * 8);
         const float4 u0 = us[0], u1 = us[1];
         const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
@@ -128,7 +130,9 @@ k_prep_i8(const float *__restrict__ x, const float *__restrict__ x_up, const flo
     const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const uint32_t xr = warp / L.nblk, b = warp % L.nblk;
     if (xr >= xrows) return;
-    prep_superblock(x + (size_t)xr * L.cols, b, lane, L, out + (size_t)xr * L.token_bytes, x_up ? x_up + (size_t)xr * L.cols : nullptr, norm_w, eps);
+    const float *xrow = x + (size_t)xr * L.cols;
+    prep_superblock(xrow, b, b, lane, L, out + (size_t)xr * L.token_bytes, x_up ? x_up + (size_t)xr * L.cols : nullptr, norm_w,
+                    norm_w ? row_inv_rms(xrow, L.cols, eps, lane) : 0.f);
 }
 
 // ---------------------------------------------------------------- helpers
@@ -143,6 +147,12 @@ struct Q4Raw {
         qa = ldw128(blk + 16 + 16 * t);
         qb = ldw128(blk + 80 + 16 * t);
     }
+    // From a row of a ring stage (shared memory): the block's 144 bytes.
+    __device__ __forceinline__ void load_staged(const uint8_t *r, uint32_t, int t) {
+        hdr = *reinterpret_cast<const uint4 *>(r);
+        qa = *reinterpret_cast<const uint4 *>(r + 16 + 16 * t);
+        qb = *reinterpret_cast<const uint4 *>(r + 80 + 16 * t);
+    }
 };
 // Q5_K: as Q4_K, plus the 16 bytes of qh under this thread's run (bit j of qh[l] = fifth bit of value l of sub-block j).
 struct Q5Raw {
@@ -153,6 +163,12 @@ struct Q5Raw {
         qh = ldw128(blk + 16 + 16 * (t & 1));
         qa = ldw128(blk + 48 + 16 * t);
         qb = ldw128(blk + 112 + 16 * t);
+    }
+    __device__ __forceinline__ void load_staged(const uint8_t *r, uint32_t, int t) {
+        hdr = *reinterpret_cast<const uint4 *>(r);
+        qh = *reinterpret_cast<const uint4 *>(r + 16 + 16 * (t & 1));
+        qa = *reinterpret_cast<const uint4 *>(r + 48 + 16 * t);
+        qb = *reinterpret_cast<const uint4 *>(r + 112 + 16 * t);
     }
 };
 struct Q6Raw;
@@ -173,6 +189,15 @@ struct Q6Raw { // device layout of blocks.cuh; thread t = (n, lh)
         sc = ldw64(row + (size_t)nblk * 192 + (size_t)b * 16 + 8 * (t & 1));
         d = ldw16(row + (size_t)nblk * 208 + (size_t)b * 2);
     }
+    // From a row of a ring stage: ql[128] | qh[64] | scales[16]; `dword` = the stage's word that holds d.
+    __device__ __forceinline__ void load_staged(const uint8_t *r, uint32_t dword, int t) {
+        const int n = t >> 1, lh = t & 1;
+        q0 = *reinterpret_cast<const uint4 *>(r + 64 * n + 16 * lh);
+        q1 = *reinterpret_cast<const uint4 *>(r + 64 * n + 16 * lh + 32);
+        qh = *reinterpret_cast<const uint4 *>(r + 128 + 32 * n + 16 * lh);
+        sc = *reinterpret_cast<const uint2 *>(r + 192 + 8 * (t & 1));
+        d = dword;
+    }
 };
 
 // The prepared activations of one row that one thread needs for one superblock.
@@ -183,23 +208,27 @@ template <int FMT> struct Act {
     uint4 xb[is_k45<FMT> ? 2 : 4];
     uint4 sx;
     float inv;
-    __device__ __forceinline__ void load(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) {
+    __device__ __forceinline__ void load(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) { load_at<false>(tok, L, b, t, g); }
+    // SH: `tok` is shared memory (plain loads), else global memory written by the kernel before.
+    template <bool SH> __device__ __forceinline__ void load_at(const uint8_t *tok, const PrepI8 &L, uint32_t b, int t, int g) {
+        auto ld128 = [](const uint8_t *p) { return SH ? *reinterpret_cast<const uint4 *>(p) : ldx128(p); };
+        auto ld32 = [](const uint8_t *p) { return SH ? *reinterpret_cast<const uint32_t *>(p) : ldx32(p); };
         const int plane = g >> 2, u = t & 1;
         if constexpr (is_k45<FMT>) {
             const bool feeds = (t >> 1) == (g & 1);
             const int chunk = (((g & 3) >> 1) ? 2 : 0) + (t >> 1);
             const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 64 * chunk + 16 * (t & 1);
 #pragma unroll
-            for (int i = 0; i < 2; i++) xb[i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
-            sx = ldx128(tok + L.sx32_off + (size_t)b * 32 + 16 * u);
+            for (int i = 0; i < 2; i++) xb[i] = feeds ? ld128(src + 32 * i) : make_uint4(0, 0, 0, 0);
+            sx = ld128(tok + L.sx32_off + (size_t)b * 32 + 16 * u);
         } else {
             const bool feeds = (g & 3) == t;
             const uint8_t *src = tok + (plane ? L.lo_off : 0) + (size_t)b * 256 + 128 * (t >> 1) + 16 * (t & 1);
 #pragma unroll
-            for (int i = 0; i < 4; i++) xb[i] = feeds ? ldx128(src + 32 * i) : make_uint4(0, 0, 0, 0);
-            sx = ldx128(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
+            for (int i = 0; i < 4; i++) xb[i] = feeds ? ld128(src + 32 * i) : make_uint4(0, 0, 0, 0);
+            sx = ld128(tok + L.sx16_off + ((t >> 1) ? (L.cols / 16) * 2 : 0) + (size_t)b * 32 + 16 * u);
         }
-        inv = __uint_as_float(ldx32(tok + L.isc_off + (size_t)b * 4));
+        inv = __uint_as_float(ld32(tok + L.isc_off + (size_t)b * 4));
     }
 };
 
@@ -469,6 +498,230 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     if (P.world > 1) tp_finish(P, seq);
 }
 
+// ---------------------------------------------------------------- one activation row, K slices and weight rings
+//
+// The same arithmetic (superblock_dot) organised for latency and balance: a block of 16 warps quantises ONE K
+// slice of the activation row into shared memory itself (no preparation launch: one dependency less between a
+// projection and the kernel that produced its input), every warp then takes 16-row tiles against it, streaming
+// their packed superblocks through a private ring of asynchronous copies (gemv_common.cuh) -- no block-wide
+// barrier in the main loop, the ring running on across tile borders.  K is cut into as many slices as it takes
+// for every SM to get its share of warps when rows are few (the 5120 x 17408 down projection: 320 tiles); with
+// more than one slice the partial sums go to a workspace and the last warp to arrive at a tile adds them in
+// slice order (deterministic).
+template <int FMT> struct Stage1; // bytes between the rows of a stage, chosen for the 16-byte fragment reads
+template <> struct Stage1<FQ_Q4_K> { static constexpr uint32_t ROW = 192; };
+template <> struct Stage1<FQ_Q5_K> { static constexpr uint32_t ROW = 176; };
+template <> struct Stage1<FQ_Q6_K> { static constexpr uint32_t ROW = 224; };
+
+struct SlicedJob {
+    GemvTargets T;         // tile_end in 16-row tiles
+    uint32_t pitch, cols, nblk;
+    const float *x, *x_up, *norm_w;
+    float norm_eps;
+    uint32_t slices, nb_max;
+    float *ws;             // partial sums [tile][slice][16 rows]
+    uint32_t *counters;    // arrivals per tile
+};
+
+template <int FMT, int STAGES>
+__global__ void __launch_bounds__(512, 1)
+k_gemv_i8s(const __grid_constant__ SlicedJob J, const __grid_constant__ TpPush P) {
+    using Raw = typename RawOf<FMT>::type;
+    using Ring = WeightRing<FMT, Stage1<FMT>::ROW>;
+    constexpr uint32_t ROW = Stage1<FMT>::ROW;
+    extern __shared__ __align__(128) uint8_t s1_smem[];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t slice = blockIdx.x % J.slices;
+    const uint32_t b0 = (uint32_t)((uint64_t)slice * J.nblk / J.slices), nb = (uint32_t)((uint64_t)(slice + 1) * J.nblk / J.slices) - b0;
+    const uint32_t first = (blockIdx.x / J.slices) * W + warp, stride = (gridDim.x / J.slices) * W;
+    const uint32_t total_tiles = J.T.tile_end[J.T.count - 1];
+    const PrepI8 L = prep_i8_layout(J.nb_max * 256); // the slice's activations, laid out like a short row
+    uint8_t *act = s1_smem, *ring = s1_smem + L.token_bytes + (size_t)warp * STAGES * Ring::BYTES;
+
+    struct Tile {
+        const uint8_t *w;
+        float *y;
+        uint32_t rows, row0;
+    };
+    auto tile_at = [&](uint32_t tile) {
+        uint32_t which = 0, first_tile = 0;
+#pragma unroll
+        for (int i = 0; i < MAX_TARGETS - 1; i++)
+            if ((uint32_t)i + 1 < J.T.count && tile >= J.T.tile_end[i]) { which = i + 1; first_tile = J.T.tile_end[i]; }
+        Tile q;
+        q.rows = J.T.rows[which];
+        q.row0 = (tile - first_tile) * 16;
+        q.w = J.T.w[which];
+        q.y = J.T.y[which];
+        return q;
+    };
+    // Producer side of the warp's ring: item = (tile, superblock of the slice), in the order they are consumed.
+    Ring wr;
+    uint32_t p_tile = first, p_bb = 0, p_stage = 0;
+    auto start_tile = [&](uint32_t tile) {
+        const Tile q = tile_at(tile);
+        wr.start_tile(q.w + (size_t)q.row0 * J.pitch, q.rows - 1 - q.row0, J.pitch, J.nblk, lane);
+    };
+    if (p_tile < total_tiles) start_tile(p_tile);
+    auto issue = [&]() {
+        if (p_tile < total_tiles) {
+            wr.issue(ring + (size_t)p_stage * Ring::BYTES, b0 + p_bb, lane);
+            if (++p_bb == nb) {
+                p_bb = 0;
+                p_tile += stride;
+                if (p_tile < total_tiles) start_tile(p_tile);
+            }
+        }
+        cp_async_commit();
+        p_stage = p_stage + 1 == STAGES ? 0 : p_stage + 1;
+    };
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; i++) issue();
+    // The copies above read immutable weights only; the rest reads activations and writes y.
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t seq = P.world > 1 ? tp_seq(P) : 0u;
+    {
+        const float scale = J.norm_w ? row_inv_rms(J.x, J.cols, J.norm_eps, lane) : 0.f;
+        for (uint32_t bb = warp; bb < nb; bb += W) prep_superblock(J.x, b0 + bb, bb, lane, L, act, J.x_up, J.norm_w, scale);
+    }
+    __syncthreads();
+
+    uint32_t c_stage = 0;
+    for (uint32_t tile = first; tile < total_tiles; tile += stride) {
+        const Tile here = tile_at(tile);
+        float yacc[1][2] = {{0.f, 0.f}};
+        for (uint32_t bb = 0; bb < nb; bb++) {
+            issue();
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+            const uint8_t *stage = ring + (size_t)c_stage * Ring::BYTES;
+            Raw cur[2];
+            Act<FMT> a[1];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                uint32_t dword = 0;
+                if constexpr (FMT == FQ_Q6_K) {
+                    dword = *reinterpret_cast<const uint32_t *>(stage + 16 * ROW + 4 * (g + 8 * r));
+                    dword = ((b0 + bb) & 1u) ? dword >> 16 : dword & 0xFFFFu;
+                }
+                cur[r].load_staged(stage + (g + 8 * r) * ROW, dword, t);
+            }
+            a[0].template load_at<true>(act, L, bb, t, g);
+            superblock_dot<FMT, 1>(cur, a, t, g, yacc);
+            __syncwarp();
+            c_stage = c_stage + 1 == STAGES ? 0 : c_stage + 1;
+        }
+        // Quad threads hold partial sums of different scale groups and planes.
+        float v[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            v[r] = yacc[0][r];
+            v[r] += __shfl_xor_sync(0xffffffffu, v[r], 1);
+            v[r] += __shfl_xor_sync(0xffffffffu, v[r], 2);
+        }
+        bool store = true;
+        if (J.slices > 1) {
+            float *part = J.ws + (size_t)tile * J.slices * 16;
+            if (t == 0) {
+                part[slice * 16 + g] = v[0];
+                part[slice * 16 + g + 8] = v[1];
+            }
+            __threadfence();
+            __syncwarp();
+            uint32_t arrived = 0;
+            if (lane == 0) arrived = atomicAdd(J.counters + tile, 1u);
+            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+            store = arrived + 1 == J.slices;
+            if (store) {
+                __threadfence();
+                if (lane == 0) J.counters[tile] = 0;
+                v[0] = v[1] = 0.f;
+                if (t == 0)
+                    for (uint32_t s = 0; s < J.slices; s++) {
+                        v[0] += __ldcg(&part[s * 16 + g]);
+                        v[1] += __ldcg(&part[s * 16 + g + 8]);
+                    }
+            }
+        }
+        if (store && t == 0) {
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint32_t row = here.row0 + g + r * 8;
+                if (row < here.rows) {
+                    float *dst = &here.y[row];
+                    *dst = v[r];
+                    if (P.world > 1) tp_store(P, seq, dst, v[r]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    if (P.world > 1) tp_finish(P, seq);
+}
+
+template <int FMT> void (*sliced_kernel(int stages))(SlicedJob, TpPush) {
+    return stages >= 4 ? k_gemv_i8s<FMT, 4> : stages == 3 ? k_gemv_i8s<FMT, 3> : k_gemv_i8s<FMT, 2>;
+}
+
+// One activation row, no routes.  cudaErrorNotSupported when the shape does not fit this kernel.
+template <int FMT> cudaError_t launch_sliced(fq_device *dev, const ProjectArgs *a, uint32_t count) {
+    using Ring = WeightRing<FMT, Stage1<FMT>::ROW>;
+    constexpr uint32_t SMEM_MAX = 222 * 1024, WARPS = 16;
+    SlicedJob J{};
+    J.T.count = count;
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        J.T.w[i] = a[i].w;
+        J.T.y[i] = (float *)a[i].y;
+        J.T.rows[i] = a[i].rows;
+        tiles += (a[i].rows + 15) / 16;
+        J.T.tile_end[i] = tiles;
+    }
+    J.pitch = a[0].row_bytes;
+    J.cols = a[0].cols;
+    J.nblk = a[0].cols / 256;
+    J.x = (const float *)a[0].x;
+    J.x_up = a[0].x_up;
+    J.norm_w = a[0].norm_w;
+    J.norm_eps = a[0].norm_eps;
+    // Slices: estimated time in units of one superblock of one tile = rounds of tiles per warp x (superblocks per
+    // slice + a fixed cost per run, larger when partial sums are exchanged) + the block's preparation of its slice.
+    const uint32_t sms = (uint32_t)dev->sm_count, nblk = J.nblk;
+    double best = 1e30;
+    uint32_t slices = 1;
+    for (uint32_t s = 1; s <= std::min(nblk, sms); s++) {
+        const uint32_t per_slice = (sms / s) * WARPS, nbm = (nblk + s - 1) / s, rounds = (tiles + per_slice - 1) / per_slice;
+        const double cost = rounds * (nbm + (s > 1 ? 1.0 : 0.3)) + 1.3 * ((nbm + WARPS - 1) / WARPS);
+        if (cost < best - 1e-9) { best = cost; slices = s; }
+    }
+    J.slices = slices;
+    J.nb_max = (nblk + slices - 1) / slices;
+    const size_t act = prep_i8_layout(J.nb_max * 256).token_bytes;
+    if (act + (size_t)WARPS * 2 * Ring::BYTES > SMEM_MAX) return cudaErrorNotSupported;
+    const uint32_t stages = (uint32_t)std::min<size_t>(4, (SMEM_MAX - act) / ((size_t)WARPS * Ring::BYTES));
+    const size_t smem = act + (size_t)WARPS * stages * Ring::BYTES;
+    J.ws = (float *)dev->nt_ws;
+    J.counters = dev->nt_counters;
+    if (slices > 1 && ((size_t)tiles * slices * 16 * sizeof(float) > dev->nt_ws_bytes || tiles > dev->nt_counter_count)) return cudaErrorNotSupported;
+    auto kernel = sliced_kernel<FMT>((int)stages);
+    static bool configured[5] = {};
+    if (!configured[stages]) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
+        if (e != cudaSuccess) return e;
+        configured[stages] = true;
+    }
+    TpPush push{};
+    if (dev->tp_push) { // one launch covers every target: it can do the exchange itself
+        push = *dev->tp_push;
+        dev->tp_push = nullptr;
+        dev->tp_pushed = true;
+    }
+    const uint32_t grid = std::max(1u, sms / slices) * slices;
+    return launch_pdl(kernel, dim3(grid), dim3(WARPS * 32), smem, dev->stream, J, push);
+}
+
 template <int FMT, int MT>
 cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const uint8_t *prep, const PrepI8 &L, bool expert) {
     GemvTargets T{};
@@ -537,6 +790,14 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     } else {
         if (f.m != 1) return FQ_ERR_UNSUPPORTED; // 2..16 activation rows: gemv_nt.cu
         xrows = m = f.m;
+    }
+    if (!expert) {
+        const cudaError_t e = f.format == FQ_Q4_K ? launch_sliced<FQ_Q4_K>(dev, a, count)
+                            : f.format == FQ_Q5_K ? launch_sliced<FQ_Q5_K>(dev, a, count) : launch_sliced<FQ_Q6_K>(dev, a, count);
+        if (e != cudaErrorNotSupported) {
+            if (int rc = fq_check_cuda(dev, e, "gemv launch")) return rc;
+            return fq_end_enqueue(dev, "gemv_i8s", 1);
+        }
     }
     const PrepI8 L = prep_i8_layout(f.cols);
     // Successive projections use alternate halves of the scratch, so a preparation kernel that starts

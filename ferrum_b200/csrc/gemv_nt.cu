@@ -45,13 +45,13 @@ constexpr uint32_t NT_SMEM_MAX = 222 * 1024;
 // shared memory (Q4_K: 160, so that the 8-byte reads of rows g .. g + 3 fall on different banks).
 template <int FMT> struct StageNT;
 template <> struct StageNT<FQ_Q4_K> {
-    static constexpr uint32_t ROW = 160, SRC = 144, PIECES = 16 * 9, BYTES = 16 * 160;
+    static constexpr uint32_t ROW = 160, BYTES = WeightRing<FQ_Q4_K, 160>::BYTES;
 };
 template <> struct StageNT<FQ_Q5_K> {
-    static constexpr uint32_t ROW = 176, SRC = 176, PIECES = 16 * 11, BYTES = 16 * 176;
+    static constexpr uint32_t ROW = 176, BYTES = WeightRing<FQ_Q5_K, 176>::BYTES;
 };
 template <> struct StageNT<FQ_Q6_K> { // per row ql[128] | qh[64] | scales[16]; then 4 bytes per row holding d
-    static constexpr uint32_t ROW = 208, SRC = 210, PIECES = 16 * 13, BYTES = 16 * 208 + 64;
+    static constexpr uint32_t ROW = 208, BYTES = WeightRing<FQ_Q6_K, 208>::BYTES;
 };
 
 struct NtJob {
@@ -71,15 +71,6 @@ struct NtJob {
     const uint32_t *offsets, *slots;
     uint32_t groups, total_rows;
 };
-
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void *smem_dst, const void *src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // MMAs whose accumulator starts at zero (the zero register four times: nothing to initialise).
 __device__ __forceinline__ void mma_u8s8_z(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -435,49 +426,16 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
     };
 
     // Producer side of the warp's ring: item = (tile, superblock of the slice), in the order they are consumed.
-    // A lane copies the same 16-byte pieces of every item, so their offsets from the tile's first row are
-    // worked out once per tile.  Q4_K (Q5_K): piece p = lane + 32 i is bytes 16 (p % 9) .. of row p / 9 (11).  Q6_K: pieces
-    // 0..127 are ql (row p / 8), 128..191 qh (row / 4), 192..207 the scales, 208..223 the 4 bytes holding d.
-    constexpr int NP = FMT == FQ_Q4_K ? 5 : FMT == FQ_Q5_K ? 6 : 7;
-    constexpr uint32_t PER_ROW = St::SRC / 16; // Q4_K / Q5_K: 16-byte pieces per row and superblock
+    WeightRing<FMT, St::ROW> wr;
     uint32_t p_tile = first, p_bb = 0, p_stage = 0;
-    const uint8_t *p_base = nullptr;
-    uint32_t p_off[NP];
-    auto piece_row = [&](int i) -> uint32_t {
-        const uint32_t p = lane + 32 * i;
-        if constexpr (FMT != FQ_Q6_K) return p / PER_ROW;
-        return i < 4 ? p / 8 : i < 6 ? (p - 128) / 4 : (lane & 15);
-    };
     auto start_tile = [&](uint32_t tile) {
         const Tile q = tile_at(tile);
-        p_base = q.w + (size_t)q.row0 * J.pitch;
-        const uint32_t last = q.rows - 1 - q.row0; // rows past the end of the target read its last row
-#pragma unroll
-        for (int i = 0; i < NP; i++) {
-            const uint32_t p = lane + 32 * i, r = min(piece_row(i), last);
-            uint32_t in_row;
-            if constexpr (FMT != FQ_Q6_K) in_row = 16 * (p % PER_ROW);
-            else in_row = i < 4 ? 16 * (p % 8) : i < 6 ? J.nblk * 128 + 16 * (p % 4) : lane < 16 ? J.nblk * 192 : J.nblk * 208;
-            p_off[i] = r * J.pitch + in_row;
-        }
+        wr.start_tile(q.w + (size_t)q.row0 * J.pitch, q.rows - 1 - q.row0, J.pitch, J.nblk, lane);
     };
     if (p_tile < total_tiles) start_tile(p_tile);
     auto issue = [&]() {
         if (p_tile < total_tiles) {
-            uint8_t *dst = ring + (size_t)p_stage * St::BYTES;
-            const uint32_t b = b0 + p_bb;
-#pragma unroll
-            for (int i = 0; i < NP; i++) {
-                const uint32_t p = lane + 32 * i;
-                if constexpr (FMT != FQ_Q6_K) {
-                    if (p < St::PIECES) cp_async16(dst + St::ROW * (p / PER_ROW) + 16 * (p % PER_ROW), p_base + (p_off[i] + b * St::SRC));
-                } else {
-                    if (i < 4) cp_async16(dst + 208 * (p / 8) + 16 * (p % 8), p_base + (p_off[i] + b * 128));
-                    else if (i < 6) cp_async16(dst + 208 * ((p - 128) / 4) + 128 + 16 * (p % 4), p_base + (p_off[i] + b * 64));
-                    else if (lane < 16) cp_async16(dst + 208 * lane + 192, p_base + (p_off[i] + b * 16));
-                    else cp_async4(dst + 16 * 208 + 4 * (lane - 16), p_base + (p_off[i] + (b & ~1u) * 2)); // the aligned 4 bytes that hold d
-                }
-            }
+            wr.issue(ring + (size_t)p_stage * St::BYTES, b0 + p_bb, lane);
             if (++p_bb == nb) {
                 p_bb = 0;
                 p_tile += stride;
