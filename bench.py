@@ -345,12 +345,15 @@ def run_ours(args):
         gms = alone(("gate", "up"), m, x_dev, y_dev)
         pair_bytes = 2 * 17408 * 5120 // 256 * 144
         achieved = pair_bytes / (gms * 1e-3) / 1e9
-        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv_i8<Q4_K,1> (gate|up, 2 x 17408 x 5120, one launch)",
+        stream_gbs = read_stream_probe(S, dev, stream, torch, timed)
+        out["roofline"] = {"bound": "hbm", "kernel": "k_gemv_i8s<Q4_K> (gate|up, 2 x 17408 x 5120, M = 1, one launch)",
                            "achieved": round(achieved, 1), "peak": P["hbm_gbs"], "peak_source": P["source"], "unit": "GB/s",
                            "frac": round(achieved / P["hbm_gbs"], 4), "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
+                           # what a kernel that only reads the same bytes reaches here, measured in this run
+                           "read_stream_gbs": stream_gbs, "frac_of_read_stream": round(achieved / stream_gbs, 4),
                            # dram__bytes_read.sum + dram__bytes_write.sum of this launch, from the tracked ncu summary
-                           "traffic": profile_value("gemv_i8_q4k_gate_up_m1.md", "dram_bytes_per_launch"),
-                           "traffic_source": "profiles/gemv_i8_q4k_gate_up_m1.md (one ncu capture of this launch)",
+                           "traffic": profile_value("gemv_i8s_q4k_gate_up_m1.md", "dram_bytes_per_launch"),
+                           "traffic_source": "profiles/gemv_i8s_q4k_gate_up_m1.md (one ncu capture of this launch)",
                            "algorithmic_bytes": pair_bytes, "us_per_launch": round(gms * 1e3, 2)}
         per = {}
         for names in (("q", "k", "v"), ("o",), ("gate", "up"), ("down",)):
@@ -602,6 +605,46 @@ def moe_ep_bench(S, dev, stream, torch, dist, timed_ms, rank, world):
     return res
 
 
+def read_stream_probe(S, dev, stream, torch, timed_ms, verbose=False):
+    """GB/s of a kernel that only reads: four 100 MB buffers in turn (more than L2), the best grid of a few."""
+    n = 100_270_080  # the bytes of the gate|up launch
+    bufs = [torch.full((n,), i + 1, dtype=torch.uint8, device="cuda") for i in range(4)]
+    torch.cuda.synchronize()
+    best, table = 0.0, {}
+    for per_sm in (4, 8, 16, 32):
+        def go(per_sm=per_sm):
+            for b in bufs:
+                dev.probe_read_stream(b, per_sm)
+        with torch.cuda.stream(stream):
+            go()
+        ms = timed_ms(go, 5) / (5 * len(bufs))
+        table[per_sm] = round(n / (ms * 1e-3) / 1e9, 1)
+        best = max(best, table[per_sm])
+    return (best, table) if verbose else best
+
+
+def run_stream_probe(args):
+    import torch
+    from ferrum_b200 import surface as S
+    torch.cuda.set_device(0)
+    dev = S.Device(0, use_torch_stream=False)
+    stream = torch.cuda.ExternalStream(dev.stream_ptr(), device=torch.device("cuda", 0))
+
+    def timed(fn, steps):
+        with torch.cuda.stream(stream):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+    best, table = read_stream_probe(S, dev, stream, torch, timed, verbose=True)
+    print(json.dumps({"probe": "read_stream", "bytes_per_launch": 100270080, "buffers": 4, "gbs_by_blocks_per_sm": table, "best_gbs": best,
+                      "copy_peak_gbs": peaks()["hbm_gbs"]}), flush=True)
+
+
 def moe_bench(S, dev, stream, torch, timed_ms):
     H, E, F, USED = 2048, 256, 512, 8
     M = S.Matrix.from_packed
@@ -764,10 +807,13 @@ def main():
     ap.add_argument("--no-fuse", action="store_true", help="one launch per matrix instead of one per input group")
     ap.add_argument("--nccl", action="store_true", help="multi-GPU: gather with NCCL (torch.distributed) instead of the peer-push kernel")
     ap.add_argument("--quick", action="store_true", help="headline and per-group timings only")
+    ap.add_argument("--stream-probe", action="store_true", help="time a kernel that only reads 100 MB buffers: the read-only streaming ceiling")
     ap.add_argument("--prefill-probe", default=None, metavar="NAME:M",
                     help="time only the bf16 prefill GEMM of one matrix of the layer set (q, k, o, gate, down ...) at M rows")
     args = ap.parse_args()
-    if args.prefill_probe:
+    if args.stream_probe:
+        run_stream_probe(args)
+    elif args.prefill_probe:
         run_prefill_probe(args)
     elif args.impl == "reference":
         run_reference(args)

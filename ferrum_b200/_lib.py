@@ -61,6 +61,7 @@ SIGNATURES = {
     "fq_set_exact": (_I, [_P, _I]),
     "fq_test_fail_after": (_I, [_P, _I]),
     "fq_test_fail_completion": (_I, [_P]),
+    "fq_probe_read_stream": (_I, [_P, _P, _Z, _U32]),
     "fq_capture_begin": (_I, [_P]),
     "fq_capture_end": (_I, [_P, C.POINTER(_P)]),
     "fq_graph_launch": (_I, [_P, _P]),

@@ -174,3 +174,30 @@ int fq_launch_get_rows(fq_device *dev, const fq_matrix *w, const uint32_t *ids, 
                 w->data, (uint32_t)w->rows, (uint32_t)w->cols, (uint32_t)w->pitch, ids, (float *)y);
     });
 }
+
+
+// ------------------------------------------------------------------ read-only stream probe
+//
+// What a kernel that does nothing but read can stream from HBM on this device: every thread reads 16 bytes
+// per step with the loads the projection kernels use for weights, grid-stride, and folds them into one word
+// that is (almost) never written.  The ceiling a weight-streaming projection is measured against, as the
+// reference measures its own (`h_bw_read`, src/hybrid/bench.rs:140-167).
+namespace {
+__global__ void __launch_bounds__(256) k_read_stream(const uint4 *__restrict__ p, size_t n16, uint32_t *sink) {
+    uint32_t acc = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+        uint4 v;
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p + i));
+        acc ^= v.x ^ v.y ^ v.z ^ v.w;
+    }
+    if (acc == 0x9E3779B9u) *sink = acc;
+}
+} // namespace
+
+extern "C" int fq_probe_read_stream(fq_device *dev, const void *data, size_t bytes, uint32_t blocks_per_sm) {
+    if (int rc = fq_begin_enqueue(dev)) return rc;
+    if (bytes < 16 || blocks_per_sm == 0 || blocks_per_sm > 32) return fq_fail(dev, FQ_ERR_PARAM, "stream probe of %zu bytes, %u blocks per SM", bytes, blocks_per_sm);
+    if (int rc = fq_check_binding(dev, data, bytes, "data")) return rc;
+    k_read_stream<<<dev->sm_count * blocks_per_sm, 256, 0, dev->stream>>>((const uint4 *)data, bytes / 16, (uint32_t *)dev->status_dev + 8);
+    return fq_end_enqueue(dev, "read_stream", 1);
+}

@@ -661,14 +661,12 @@ k_gemv_i8s(const __grid_constant__ SlicedJob J, const __grid_constant__ TpPush P
     if (P.world > 1) tp_finish(P, seq);
 }
 
-template <int FMT> void (*sliced_kernel(int stages))(SlicedJob, TpPush) {
-    return stages >= 4 ? k_gemv_i8s<FMT, 4> : stages == 3 ? k_gemv_i8s<FMT, 3> : k_gemv_i8s<FMT, 2>;
-}
-
 // One activation row, no routes.  cudaErrorNotSupported when the shape does not fit this kernel.
 template <int FMT> cudaError_t launch_sliced(fq_device *dev, const ProjectArgs *a, uint32_t count) {
     using Ring = WeightRing<FMT, Stage1<FMT>::ROW>;
-    constexpr uint32_t SMEM_MAX = 222 * 1024, WARPS = 16;
+    // 16 warps in one block per SM and a ring of two stages (one superblock in flight per warp beside the one
+    // being used): deeper rings and smaller blocks measured slower on every shape of the 27B layer set.
+    constexpr uint32_t SMEM_MAX = 222 * 1024, WARPS = 16, STAGES = 2;
     SlicedJob J{};
     J.T.count = count;
     uint32_t tiles = 0;
@@ -699,18 +697,17 @@ template <int FMT> cudaError_t launch_sliced(fq_device *dev, const ProjectArgs *
     J.slices = slices;
     J.nb_max = (nblk + slices - 1) / slices;
     const size_t act = prep_i8_layout(J.nb_max * 256).token_bytes;
-    if (act + (size_t)WARPS * 2 * Ring::BYTES > SMEM_MAX) return cudaErrorNotSupported;
-    const uint32_t stages = (uint32_t)std::min<size_t>(4, (SMEM_MAX - act) / ((size_t)WARPS * Ring::BYTES));
-    const size_t smem = act + (size_t)WARPS * stages * Ring::BYTES;
+    const size_t smem = act + (size_t)WARPS * STAGES * Ring::BYTES;
+    if (smem > SMEM_MAX) return cudaErrorNotSupported;
     J.ws = (float *)dev->nt_ws;
     J.counters = dev->nt_counters;
     if (slices > 1 && ((size_t)tiles * slices * 16 * sizeof(float) > dev->nt_ws_bytes || tiles > dev->nt_counter_count)) return cudaErrorNotSupported;
-    auto kernel = sliced_kernel<FMT>((int)stages);
-    static bool configured[5] = {};
-    if (!configured[stages]) {
+    auto kernel = k_gemv_i8s<FMT, STAGES>;
+    static bool configured = false;
+    if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX);
         if (e != cudaSuccess) return e;
-        configured[stages] = true;
+        configured = true;
     }
     TpPush push{};
     if (dev->tp_push) { // one launch covers every target: it can do the exchange itself

@@ -129,6 +129,10 @@ class Device:
     def fail_completion(self) -> None:
         self.check(self._L.fq_test_fail_completion(self.handle))
 
+    def probe_read_stream(self, data: torch.Tensor, blocks_per_sm: int = 8) -> None:
+        """Enqueue a kernel that only reads ``data`` (the device's read-only streaming ceiling, timed by the caller)."""
+        self.check(self._L.fq_probe_read_stream(self.handle, C.c_void_p(data.data_ptr()), data.numel() * data.element_size(), blocks_per_sm))
+
     def capture_begin(self) -> None:
         """Start recording enqueues (the handle must be on its own stream: ``set_stream(None)``)."""
         self.check(self._L.fq_capture_begin(self.handle))

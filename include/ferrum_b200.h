@@ -90,6 +90,12 @@ int fq_set_exact(fq_device *dev, int on);
 int fq_test_fail_after(fq_device *dev, int n);
 int fq_test_fail_completion(fq_device *dev);
 
+/* Diagnostic: enqueues a kernel that only READS `bytes` bytes at `data` (16 bytes per thread and step, the
+ * weight-streaming loads of the projection kernels, `blocks_per_sm` blocks of 256 threads per SM): timed by the
+ * caller it gives the read-only streaming ceiling of the device, the counterpart of the reference's `h_bw_read`
+ * probe (src/hybrid/bench.rs:140-167). */
+int fq_probe_read_stream(fq_device *dev, const void *data, size_t bytes, uint32_t blocks_per_sm);
+
 /* ---- batched submission ------------------------------------------------------------------- */
 
 /* The reference batches the dispatches of a forward pass into one command epoch
