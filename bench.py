@@ -645,6 +645,28 @@ def run_stream_probe(args):
                       "copy_peak_gbs": peaks()["hbm_gbs"]}), flush=True)
 
 
+def run_moe_probe(args):
+    """Only the MoE block and the Q8_0 head (what the default line reports under `moe`): the command a launch
+    list of the block is taken on."""
+    import torch
+    from ferrum_b200 import surface as S
+    torch.cuda.set_device(0)
+    dev = S.Device(0, use_torch_stream=False)
+    stream = torch.cuda.ExternalStream(dev.stream_ptr(), device=torch.device("cuda", 0))
+
+    def timed(fn, steps):
+        with torch.cuda.stream(stream):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+    print(json.dumps({"probe": "moe", **moe_bench(S, dev, stream, torch, timed)}), flush=True)
+
+
 def moe_bench(S, dev, stream, torch, timed_ms):
     H, E, F, USED = 2048, 256, 512, 8
     M = S.Matrix.from_packed
@@ -808,11 +830,14 @@ def main():
     ap.add_argument("--nccl", action="store_true", help="multi-GPU: gather with NCCL (torch.distributed) instead of the peer-push kernel")
     ap.add_argument("--quick", action="store_true", help="headline and per-group timings only")
     ap.add_argument("--stream-probe", action="store_true", help="time a kernel that only reads 100 MB buffers: the read-only streaming ceiling")
+    ap.add_argument("--moe-probe", action="store_true", help="time only the MoE block (T = 1 and 1024) and the Q8_0 head")
     ap.add_argument("--prefill-probe", default=None, metavar="NAME:M",
                     help="time only the bf16 prefill GEMM of one matrix of the layer set (q, k, o, gate, down ...) at M rows")
     args = ap.parse_args()
     if args.stream_probe:
         run_stream_probe(args)
+    elif args.moe_probe:
+        run_moe_probe(args)
     elif args.prefill_probe:
         run_prefill_probe(args)
     elif args.impl == "reference":
