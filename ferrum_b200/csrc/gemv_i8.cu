@@ -1,13 +1,13 @@
-// Decode projections for 1..4 activation rows on the integer tensor path (F32 in, F32 out).
-// The reference's `h_mv_q4_k` / `h_mv_q6_k` / `h_mvb_*` (src/metal/shaders/hybrid.metal:688-756,
-// 838-897, 1330-1394) and, with routes, `h_mv_id_*` (:2390-2428).
+// Decode projections of ONE activation row, and per-route expert projections, on the integer tensor path
+// (F32 in, F32 out).  The reference's `h_mv_q4_k` / `h_mv_q5_k` / `h_mv_q6_k` (src/metal/shaders/hybrid.metal:
+// 688-897) and, with routes, `h_mv_id_*` (:2390-2428).  Two to sixteen rows run in gemv_nt.cu.
 //
 // A K-quant GEMV on B200 is bound by instruction issue, not by HBM, if every weight costs ALU work.
 // Here the packed quants never leave the integer domain:
 //
 //   A (16 weight rows x 32 k, u8)  = the raw quants: one AND per four Q4_K weights
-//                                    (w & 0x0F0F0F0F, (w >> 4) & 0x0F0F0F0F), one LOP3 select per
-//                                    four Q6_K weights (low nibbles | two high bits);
+//                                    (w & 0x0F0F0F0F, (w >> 4) & 0x0F0F0F0F), one more LOP3 for the fifth
+//                                    bit of Q5_K, one LOP3 select per four Q6_K weights;
 //   B (32 k x 8 columns, s8)       = the activations of ONE row as 16-bit integers
 //                                    x' = round(x * s) = 256 * hi + lo, both halves signed bytes,
 //                                    s a power of two per (row, superblock).  The four threads of a
@@ -16,17 +16,23 @@
 //                                    elsewhere: one mma.sync m16n8k32 yields, per weight row, the
 //                                    integer dot products of four scale groups times two planes;
 //   epilogue (integers)            = sum_groups scale_g * (dot_g [- 32 * sum x' for Q6_K]),
-//                                    Q4_K minus dmin * sum_j m_j * sum x'; one I2F and one FMA with
+//                                    Q4_K / Q5_K minus dmin * sum_j m_j * sum x'; one I2F and one FMA with
 //                                    d / s per row and superblock.
 //
 // The result is the exact dot product of the decoded weights with the activations rounded to 16 bits
 // relative to the largest magnitude of their superblock (error <= 2^-16 of that maximum per
 // activation; llama.cpp's CUDA GEMV, which the reference's kernels derive from, rounds to 8 bits per
-// 32).  Thread (g = lane / 4, t = lane % 4) owns weight rows g, g + 8 of a 16-row tile and the same
-// bytes of every superblock as in gemv.cu (Q4_K: chunk t; Q6_K: half t / 2, run t % 2), read with
-// 128-bit loads, the next superblock always in flight.  Four warps split K; partial sums meet in
-// shared memory in a fixed order, so results are deterministic and a row-sharded matrix gives the
-// same bits as the whole one.
+// 32).  Thread (g = lane / 4, t = lane % 4) owns weight rows g, g + 8 of a 16-row tile.
+//
+// Two kernels share that arithmetic (`superblock_dot`):
+//   k_gemv_i8s  dense matrices, one row: one block of 16 warps per SM; K is cut into slices, a block prepares
+//               its slice of the activation row itself (no preparation launch; optionally with the row's
+//               rmsnorm), every warp walks 16-row tiles with its own cp.async ring of weight stages; with more
+//               than one slice partial sums go through a workspace and the last warp to arrive at a tile adds
+//               them in slice order, so results do not depend on timing;
+//   k_gemv_i8   per-route expert projections (`project_id`) and the allocation-free entry point: activations
+//               prepared by k_prep_i8, weights read with 128-bit loads into registers, warps of a block split K
+//               and meet in shared memory in warp order.
 #include <algorithm>
 #include <atomic>
 #include <cstdarg>

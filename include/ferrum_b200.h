@@ -378,12 +378,17 @@ int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset, const fq_
  *   y[m][rows] = x[m][cols] . W^T,  W = `rows` rows of cols / 256 Q4_K blocks (GGUF bytes), 1 <= m <= 4.
  *
  * All pointers are DEVICE pointers, 16-byte aligned, on the current device; the work is enqueued on
- * `cuda_stream` and is complete when that stream reaches it.  Same kernels and same results as
- * `fq_project` on a Q4_K matrix.  The prepared activations live in a fixed array inside the library
+ * `cuda_stream` and is complete when that stream reaches it.  The arithmetic is that of `fq_project` on a
+ * Q4_K matrix (integer dot products against activations rounded to 16 bits); the summation order over K
+ * differs, so results agree with it to that accuracy (about 1e-5 of the largest output), not bit for bit.
+ * x, y and the weights may not overlap (FQ_ERR_ALIAS).  The status covers this call's own launch only: an
+ * error left pending on the calling thread by earlier CUDA calls is cleared, not reported.  The prepared
+ * activations live in a fixed array inside the library
  * image (FQ_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the process exits);
  * m * (about 2.4 * cols) bytes must fit, otherwise the call returns FQ_ERR_SHAPE and says so in `err`.
  * The call itself uses no cudaMalloc, cudaFree or other allocating routine.  The first call on each
- * device also looks up the array's device address: make that call before any stream capture.  Every
+ * device also looks up the array's device address (first calls from several threads are safe): make that
+ * call before any stream capture.  Every
  * call on a device shares the one array (each call rewrites all of it that it reads, so nothing is
  * carried over), hence two calls whose kernels may overlap on the GPU -- different streams, no
  * ordering -- race; calls on one stream, or ordered by events, are safe.  `err` (may be NULL) receives
