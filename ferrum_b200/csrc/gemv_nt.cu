@@ -70,6 +70,9 @@ struct NtJob {
     // grouped: activation rows [offsets[i], offsets[i + 1]) belong to expert slots ? slots[i] : i
     const uint32_t *offsets, *slots;
     uint32_t groups, total_rows;
+    // grouped: sorted row r reads prepared row src[r] / src_div (the gather of expert-sorted routes), or r itself
+    const uint32_t *src;
+    uint32_t src_div;
 };
 
 // MMAs whose accumulator starts at zero (the zero register four times: nothing to initialise).
@@ -342,7 +345,7 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
     using St = StageNT<FMT>;
     constexpr uint32_t TOK = 8 * NT;
     extern __shared__ __align__(128) uint8_t nt_smem[];
-    __shared__ uint32_t job_group, job_row0, job_cnt;
+    __shared__ uint32_t job_group, job_row0, job_cnt, job_src[TOK];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
 
@@ -382,6 +385,8 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
                 job_row0 = row0;
                 job_cnt = cnt;
             }
+            // The prepared row behind each of the tile's sorted rows.
+            for (uint32_t i = lane; i < TOK; i += 32) job_src[i] = i < cnt ? (J.src ? J.src[row0 + i] / J.src_div : row0 + i) : 0u;
         }
         __syncthreads();
         if (job_group == 0xffffffffu) return; // more blocks than tiles
@@ -461,7 +466,9 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
             const uint32_t tok = i / per_row, p = i - tok * per_row;
             uint8_t *dst = p < 32 * nb ? A.frag + (size_t)tok * A.row_stride + 16 * p : A.rec + (size_t)tok * A.rec_stride + 16 * (p - 32 * nb);
             if (tok < m) {
-                const uint8_t *row = J.prep + (size_t)(xrow0 + tok) * tok_bytes;
+                size_t prow = xrow0 + tok;
+                if constexpr (GROUPED) prow = job_src[tok];
+                const uint8_t *row = J.prep + prow * tok_bytes;
                 cp_async16(dst, p < 32 * nb ? row + (size_t)b0 * 512 + 16 * p : row + (size_t)J.nblk * 512 + (size_t)b0 * 32 + 16 * (p - 32 * nb));
             } else {
                 *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
@@ -701,8 +708,17 @@ int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t cou
     if (!ok) return FQ_ERR_UNSUPPORTED;
     J.nb_max = S.nb_max;
     cudaError_t e = cudaSuccess;
-    // The rows of the experts in `offsets` (a rank's share when the matrices hold only some experts).
-    if (!(J.prep = launch_prep(dev, (int)f.format, f, total_rows, src, src_div ? src_div : 1, f.offsets, f.groups, e))) return FQ_ERR_UNSUPPORTED;
+    // With a gather (`src`) every row of x is prepared once and the blocks pick rows by index; else the rows of
+    // the experts in `offsets` (a rank's share when the matrices hold only some experts).
+    if (src) {
+        if (src_div == 0) return FQ_ERR_UNSUPPORTED;
+        J.src = src;
+        J.src_div = src_div;
+        J.prep = launch_prep(dev, (int)f.format, f, (total_rows + src_div - 1) / src_div, nullptr, 1, nullptr, 0, e);
+    } else {
+        J.prep = launch_prep(dev, (int)f.format, f, total_rows, nullptr, 1, f.offsets, f.groups, e);
+    }
+    if (!J.prep) return FQ_ERR_UNSUPPORTED;
     if (int rc = fq_check_cuda(dev, e, "activation preparation launch")) return rc;
     // Every group has at most ceil(rows / 16) <= rows / 16 + 1 tiles of sixteen rows.
     const uint32_t grid = total_rows / 16 + f.groups;

@@ -7,144 +7,152 @@
 
 namespace {
 
-constexpr int ROUTE_THREADS = 256;
+constexpr int ROUTE_WARPS = 4;    // tokens per block of the routing kernel: one warp each
 constexpr int MAX_EXPERTS = 1024; // the reference's map kernel holds counts[1024]
 
-__device__ __forceinline__ float block_sum(float v, float *scratch) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+__device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    __syncthreads();
-    if (lane == 0) scratch[warp] = v;
-    __syncthreads();
-    float total = 0.f;
-    for (int i = 0; i < warps; i++) total += scratch[i];
-    return total;
+    return v;
 }
 
-__device__ __forceinline__ float block_max(float v, float *scratch) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
-    __syncthreads();
-    if (lane == 0) scratch[warp] = v;
-    __syncthreads();
-    float best = -INFINITY;
-    for (int i = 0; i < warps; i++) best = fmaxf(best, scratch[i]);
-    return best;
-}
-
-// One block per token.  Scores: softmax over the logits (max, exp, sum, divide) or a logistic per
-// logit; `used` rounds of arg-max with ties to the lower index; weights divided by the picked sum
-// when `norm`; shared-expert gate = logistic(dot(x, shared_w)) or 1.
-__global__ void __launch_bounds__(ROUTE_THREADS)
+// One warp per token (no block-wide barrier anywhere: a decode step's single token is one warp's latency).
+// Scores: softmax over the logits (max, exp, sum, divide) or a logistic per logit; `used` rounds of arg-max
+// with ties to the lower index; weights divided by the picked sum when `norm`; shared-expert gate =
+// logistic(dot(x, shared_w)) or 1.  Lane l owns experts l, l + 32, ...
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
 k_moe_route(const float *__restrict__ logits, const float *__restrict__ x, const float *__restrict__ shared_w,
-            uint32_t experts, uint32_t used, uint32_t hidden, int sigmoid, int norm, int shared_gate,
+            uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens, int sigmoid, int norm, int shared_gate,
             uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate, int *status) {
-    __shared__ float prob[MAX_EXPERTS];
-    __shared__ float scratch[ROUTE_THREADS / 32];
-    __shared__ float best_v[ROUTE_THREADS / 32];
-    __shared__ uint32_t best_i[ROUTE_THREADS / 32];
-    __shared__ float picked[64];
-    const uint32_t t = blockIdx.x, tid = threadIdx.x;
+    extern __shared__ float route_smem[]; // [ROUTE_WARPS][experts]
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= tokens) return;
+    float *prob = route_smem + (size_t)warp * experts;
     const float *row = logits + (size_t)t * experts;
     // A NaN or an infinity among the logits has no ranking (the reference's router refuses such a row:
     // "router produced invalid logits", src/nn/moe.rs:392-397): report it through the status word, give the token
     // the first `used` experts with weight zero so that everything downstream stays in range, and stop.
-    {
-        int bad = 0;
-        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) bad |= !(fabsf(row[e]) < INFINITY);
-        if (__syncthreads_or(bad)) {
-            if (tid == 0) {
-                *(volatile int *)status = (int)FQ_ERR_WEIGHT;
-                gate[t] = 0.f;
-            }
-            for (uint32_t k = tid; k < used; k += ROUTE_THREADS) {
-                ids[(size_t)t * used + k] = k;
-                weights[(size_t)t * used + k] = 0.f;
-            }
-            return;
+    int bad = 0;
+    float mx = -INFINITY;
+    for (uint32_t e = lane; e < experts; e += 32) {
+        const float v = row[e];
+        prob[e] = v;
+        bad |= !(fabsf(v) < INFINITY);
+        mx = fmaxf(mx, v);
+    }
+    if (__any_sync(0xffffffffu, bad)) {
+        if (lane == 0) {
+            *(volatile int *)status = (int)FQ_ERR_WEIGHT;
+            gate[t] = 0.f;
         }
+        for (uint32_t k = lane; k < used; k += 32) {
+            ids[(size_t)t * used + k] = k;
+            weights[(size_t)t * used + k] = 0.f;
+        }
+        return;
     }
     if (sigmoid) {
-        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) prob[e] = 1.f / (1.f + expf(-row[e]));
+        for (uint32_t e = lane; e < experts; e += 32) prob[e] = 1.f / (1.f + expf(-prob[e]));
     } else {
-        float mx = -INFINITY;
-        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) mx = fmaxf(mx, row[e]);
-        mx = block_max(mx, scratch);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
         float part = 0.f;
-        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) {
-            const float v = expf(row[e] - mx);
+        for (uint32_t e = lane; e < experts; e += 32) {
+            const float v = expf(prob[e] - mx);
             prob[e] = v;
             part += v;
         }
-        const float total = block_sum(part, scratch);
-        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) prob[e] = prob[e] / total;
+        const float total = warp_sum(part);
+        for (uint32_t e = lane; e < experts; e += 32) prob[e] = prob[e] / total;
     }
-    __syncthreads();
-    float picked_sum = 0.f;
-    for (uint32_t k = 0; k < used; k++) {
-        float bv = -INFINITY;
-        uint32_t bi = 0xffffffffu;
-        for (uint32_t e = tid; e < experts; e += ROUTE_THREADS) {
+    // The lane's best remaining score; recomputed only by the lane whose expert was taken.
+    float bv = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    auto rescan = [&]() {
+        bv = -INFINITY;
+        bi = 0xffffffffu;
+        for (uint32_t e = lane; e < experts; e += 32) {
             const float v = prob[e];
-            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+            if (v > bv) { bv = v; bi = e; } // ascending e: ties keep the lower index
         }
+    };
+    rescan();
+    float picked_sum = 0.f, mine = 0.f; // lane k % 32 keeps the k-th picked score (k < 32; later ones go through `weights`)
+    for (uint32_t k = 0; k < used; k++) {
+        float wv = bv;
+        uint32_t wi = bi;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            const float ov = __shfl_xor_sync(0xffffffffu, wv, off);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, wi, off);
+            if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
         }
-        if ((tid & 31) == 0) { best_v[tid >> 5] = bv; best_i[tid >> 5] = bi; }
-        __syncthreads();
-        bv = best_v[0];
-        bi = best_i[0];
-        for (int i = 1; i < ROUTE_THREADS / 32; i++)
-            if (best_v[i] > bv || (best_v[i] == bv && best_i[i] < bi)) { bv = best_v[i]; bi = best_i[i]; }
-        picked_sum += bv;
-        if (tid == 0) {
-            ids[(size_t)t * used + k] = bi;
-            if (k < 64) picked[k] = bv;
-            else weights[(size_t)t * used + k] = bv;
-            prob[bi] = -1.f; // scores are non-negative, so a taken expert never wins again
+        picked_sum += wv;
+        if (k < 32) {
+            if (lane == k) mine = wv;
+        } else if (lane == 0) {
+            weights[(size_t)t * used + k] = wv;
         }
-        __syncthreads();
+        if (lane == 0) ids[(size_t)t * used + k] = wi;
+        if ((wi & 31u) == lane) {
+            prob[wi] = -1.f; // scores are non-negative, so a taken expert never wins again
+            rescan();
+        }
     }
-    for (uint32_t k = tid; k < used; k += ROUTE_THREADS) {
-        const float v = k < 64 ? picked[k] : weights[(size_t)t * used + k];
+    __syncwarp();
+    for (uint32_t k = lane; k < used; k += 32) {
+        const float v = k < 32 ? mine : weights[(size_t)t * used + k];
         weights[(size_t)t * used + k] = norm ? v / picked_sum : v;
     }
     if (shared_gate) {
         float dot = 0.f;
-        for (uint32_t i = tid; i < hidden; i += ROUTE_THREADS) dot = fmaf(x[(size_t)t * hidden + i], shared_w[i], dot);
-        dot = block_sum(dot, scratch);
-        if (tid == 0) gate[t] = 1.f / (1.f + expf(-dot));
-    } else if (tid == 0) {
+        for (uint32_t i = lane; i < hidden; i += 32) dot = fmaf(x[(size_t)t * hidden + i], shared_w[i], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) gate[t] = 1.f / (1.f + expf(-dot));
+    } else if (lane == 0) {
         gate[t] = 1.f;
     }
 }
 
 // Stable counting sort of routes by expert, one block of 32 warps.  Warp w owns the contiguous
 // slice [w*S, (w+1)*S) of routes; `cnt[w][e]` first holds the slice's count of expert e, then the
-// row where the slice's next route of expert e goes.
+// row where the slice's next route of expert e goes.  Up to 16384 routes a lane keeps its ids in registers
+// (all loads in flight at once, one pass over global memory); beyond, both passes read them again.
+constexpr int MAP_CACHED = 16; // ids per lane held in registers
 __global__ void __launch_bounds__(1024)
 k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, uint32_t *__restrict__ offsets,
           uint32_t *__restrict__ sorted, uint32_t *__restrict__ position) {
     extern __shared__ uint32_t cnt[]; // [32][experts] + [experts + 1]
     uint32_t *total = cnt + 32 * experts;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (uint32_t i = tid; i < 32 * experts + experts + 1; i += 1024) cnt[i] = 0;
-    __syncthreads();
     const uint32_t slice = ((routes + 31) / 32 + 31) / 32 * 32; // multiple of 32 routes per warp
     const uint32_t begin = warp * slice, end = min(routes, begin + slice);
-    for (uint32_t base = begin; base < end; base += 32) {
-        const uint32_t r = base + lane;
-        const bool live = r < end;
-        const uint32_t e = live ? ids[r] : 0xffffffffu;
+    const bool cached = slice <= 32u * MAP_CACHED;
+    uint32_t ev[MAP_CACHED];
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < MAP_CACHED; i++) {
+            const uint32_t r = begin + 32u * i + lane;
+            ev[i] = r < end ? ids[r] : 0xffffffffu;
+        }
+    }
+    for (uint32_t i = tid; i < 32 * experts + experts + 1; i += 1024) cnt[i] = 0;
+    __syncthreads();
+    auto count_one = [&](uint32_t e, bool live) {
         const uint32_t peers = __match_any_sync(0xffffffffu, e);
         if (live && e < experts && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
         __syncwarp();
+    };
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < MAP_CACHED; i++)
+            if (begin + 32u * i < end) count_one(ev[i], begin + 32u * i + lane < end);
+    } else {
+        for (uint32_t base = begin; base < end; base += 32) {
+            const bool live = base + lane < end;
+            count_one(live ? ids[base + lane] : 0xffffffffu, live);
+        }
     }
     __syncthreads();
     // Per expert: totals, then an exclusive scan over experts, then per-warp bases.
@@ -186,10 +194,7 @@ k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, u
         }
     }
     __syncthreads();
-    for (uint32_t base = begin; base < end; base += 32) {
-        const uint32_t r = base + lane;
-        const bool live = r < end;
-        const uint32_t e = live ? ids[r] : 0xffffffffu;
+    auto place_one = [&](uint32_t r, uint32_t e, bool live) {
         const uint32_t peers = __match_any_sync(0xffffffffu, e);
         if (live && e < experts) {
             const uint32_t rank = __popc(peers & ((1u << lane) - 1));
@@ -202,6 +207,16 @@ k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, u
         __syncwarp();
         if (live && e < experts && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
         __syncwarp();
+    };
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < MAP_CACHED; i++)
+            if (begin + 32u * i < end) place_one(begin + 32u * i + lane, ev[i], begin + 32u * i + lane < end);
+    } else {
+        for (uint32_t base = begin; base < end; base += 32) {
+            const bool live = base + lane < end;
+            place_one(base + lane, live ? ids[base + lane] : 0xffffffffu, live);
+        }
     }
     // Rows past the last expert's (only there when some id named no expert) point at route 0.
     for (uint32_t i = total[experts] + tid; i < routes; i += 1024) sorted[i] = 0;
@@ -222,21 +237,47 @@ __global__ void k_moe_gather(const float *__restrict__ x, const uint32_t *__rest
     }
 }
 
-// out[t][i] = sum_s w[t][s] * down[row(t, s)][i] + gate[t] * shared[t][i]
-__global__ void k_moe_combine(const float *__restrict__ down, const float *__restrict__ weights,
-                              const uint32_t *__restrict__ position, const float *__restrict__ shared,
-                              const float *__restrict__ gate, uint32_t hidden, uint32_t used, uint32_t tokens,
-                              int identity, float *__restrict__ out) {
-    const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+// out[t][i] = sum_s w[t][s] * down[row(t, s)][i] + gate[t] * shared[t][i]; VEC values of a token per thread.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+k_moe_combine(const float *__restrict__ down, const float *__restrict__ weights,
+              const uint32_t *__restrict__ position, const float *__restrict__ shared,
+              const float *__restrict__ gate, uint32_t hidden, uint32_t used, uint32_t tokens,
+              int identity, float *__restrict__ out) {
+    const size_t gid = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (gid >= (size_t)tokens * hidden) return;
     const uint32_t t = gid / hidden, i = gid % hidden;
-    float acc = 0.f;
+    float acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; v++) acc[v] = 0.f;
     for (uint32_t s = 0; s < used; s++) {
         const uint32_t r = t * used + s;
         const uint32_t row = identity ? r : position[r];
-        acc = fmaf(weights[r], down[(size_t)row * hidden + i], acc);
+        const float w = weights[r];
+        const float *src = down + (size_t)row * hidden + i;
+        if constexpr (VEC == 4) {
+            const float4 d = *reinterpret_cast<const float4 *>(src);
+            acc[0] = fmaf(w, d.x, acc[0]);
+            acc[1] = fmaf(w, d.y, acc[1]);
+            acc[2] = fmaf(w, d.z, acc[2]);
+            acc[3] = fmaf(w, d.w, acc[3]);
+        } else {
+            acc[0] = fmaf(w, src[0], acc[0]);
+        }
     }
-    out[gid] = acc + gate[t] * shared[gid];
+    const float g = gate[t];
+    if constexpr (VEC == 4) {
+        const float4 sh = *reinterpret_cast<const float4 *>(shared + gid);
+        *reinterpret_cast<float4 *>(out + gid) = make_float4(acc[0] + g * sh.x, acc[1] + g * sh.y, acc[2] + g * sh.z, acc[3] + g * sh.w);
+    } else {
+        out[gid] = acc[0] + g * shared[gid];
+    }
+}
+
+template <typename... Args> void launch_combine(cudaStream_t stream, const float *down, const float *shared, float *out, uint32_t hidden, size_t n, Args... args) {
+    const bool vec = hidden % 4 == 0 && (((uintptr_t)down | (uintptr_t)shared | (uintptr_t)out) & 15) == 0;
+    if (vec) k_moe_combine<4><<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(args...);
+    else k_moe_combine<1><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(args...);
 }
 
 // out = g / (1 + exp(-g)) * u
@@ -327,8 +368,8 @@ extern "C" int fq_moe_route(fq_device *dev, const float *logits, const float *x,
     }
     if (int rc = fq_check_no_alias(dev, ids, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "ids")) return rc;
     if (int rc = fq_check_no_alias(dev, weights, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "weights")) return rc;
-    k_moe_route<<<tokens, ROUTE_THREADS, 0, dev->stream>>>(logits, x, shared_w, experts, used, hidden, sigmoid, norm,
-                                                           shared_gate, ids, weights, gate, dev->status_dev);
+    k_moe_route<<<(tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, (size_t)ROUTE_WARPS * experts * sizeof(float), dev->stream>>>(
+        logits, x, shared_w, experts, used, hidden, tokens, sigmoid, norm, shared_gate, ids, weights, gate, dev->status_dev);
     return fq_end_enqueue(dev, "moe_route", 1);
 }
 
@@ -368,9 +409,9 @@ int fq_launch_moe_combine_range(fq_device *dev, const float *down, const float *
     if (int rc = fq_begin_enqueue(dev)) return rc;
     if (tokens == 0) return FQ_OK;
     const size_t n = (size_t)tokens * hidden;
-    k_moe_combine<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(down, weights + (size_t)token0 * used, position + (size_t)token0 * used,
-                                                                       shared + (size_t)token0 * hidden, gate + token0, hidden, used, tokens, 0,
-                                                                       out + (size_t)token0 * hidden);
+    launch_combine(dev->stream, down, shared + (size_t)token0 * hidden, out + (size_t)token0 * hidden, hidden, n, down,
+                   weights + (size_t)token0 * used, position + (size_t)token0 * used, shared + (size_t)token0 * hidden, gate + token0, hidden, used,
+                   tokens, 0, out + (size_t)token0 * hidden);
     return fq_end_enqueue(dev, "moe_combine", 1);
 }
 
@@ -390,8 +431,7 @@ extern "C" int fq_moe_combine(fq_device *dev, const float *down, const float *we
     if (int rc = fq_check_no_alias(dev, out, (size_t)tokens * hidden * 4, down, routes * hidden * 4, "out")) return rc;
     if (int rc = fq_check_no_alias(dev, out, (size_t)tokens * hidden * 4, shared, (size_t)tokens * hidden * 4, "out")) return rc;
     const size_t n = (size_t)tokens * hidden;
-    k_moe_combine<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(down, weights, position, shared, gate, hidden,
-                                                                       used, tokens, identity, out);
+    launch_combine(dev->stream, down, shared, out, hidden, n, down, weights, position, shared, gate, hidden, used, tokens, identity, out);
     return fq_end_enqueue(dev, "moe_combine", 1);
 }
 
