@@ -740,20 +740,24 @@ int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
     return fq_end_enqueue(dev, "gemm_tc", kernels);
 }
 
-// `a[0..count)` share X, m, format and width (BF16 in / BF16 out, no routes): one launch over all their row tiles.
+// `a[0..count)` share X, m, format and width (no routes): one launch over all their row tiles.  BF16 in / BF16
+// out, or F32 in / F32 out on the three-term split when the split copy of X fits one half of the scratch.
 int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count) {
     if (count < 2 || count > 4) return FQ_ERR_UNSUPPORTED;
     const ProjectArgs &f = a[0];
-    if (f.x_dtype != FQ_BF16 || f.y_dtype != FQ_BF16 || f.cols % BK || f.ids || f.offsets) return FQ_ERR_UNSUPPORTED;
+    const bool wide = f.x_dtype == FQ_F32 && f.y_dtype == FQ_F32;
+    if (!wide && (f.x_dtype != FQ_BF16 || f.y_dtype != FQ_BF16)) return FQ_ERR_UNSUPPORTED;
+    if (f.cols % BK || f.ids || f.offsets) return FQ_ERR_UNSUPPORTED;
     if (f.format != FQ_Q4_K && f.format != FQ_Q5_K && f.format != FQ_Q6_K && f.format != FQ_Q8_0) return FQ_ERR_UNSUPPORTED;
     if (f.format == FQ_Q4_K && (f.row_bytes % 16)) return FQ_ERR_UNSUPPORTED;
     if (f.m <= (uint32_t)FQ_GEMV_MAX_M) return FQ_ERR_UNSUPPORTED;
+    if (wide && (size_t)f.m * f.cols * 3 * sizeof(__nv_bfloat16) > dev->xprep_bytes / 2) return FQ_ERR_UNSUPPORTED;
     GemmMany many{};
     many.count = count;
     uint32_t tx = 0;
     for (uint32_t i = 0; i < count; i++) {
         if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].m != f.m || a[i].ids || a[i].offsets ||
-            a[i].x_dtype != FQ_BF16 || a[i].y_dtype != FQ_BF16 || a[i].row_bytes != f.row_bytes)
+            a[i].x_dtype != f.x_dtype || a[i].y_dtype != f.y_dtype || a[i].row_bytes != f.row_bytes)
             return FQ_ERR_UNSUPPORTED;
         many.w[i] = a[i].w;
         many.y[i] = a[i].y;
@@ -763,6 +767,16 @@ int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     }
     CUtensorMap map;
     uint32_t b_bytes = 0;
+    if (wide) {
+        dev->xprep_turn ^= 1u;
+        __nv_bfloat16 *x3 = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0));
+        const size_t n = (size_t)f.m * f.cols;
+        k_split3<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>((const float *)f.x, x3, f.cols, n);
+        if (int rc = make_map(dev, &map, x3, f.cols * 3, f.m, 256, &b_bytes)) return rc;
+        const int rc = f.m >= 384 ? launch_fmt<512, float, 2>(dev, f, map, b_bytes, f.m, many) : launch_fmt<256, float, 2>(dev, f, map, b_bytes, f.m, many);
+        if (rc != FQ_OK) return rc;
+        return fq_end_enqueue(dev, "gemm_tc", 2);
+    }
     if (int rc = make_map(dev, &map, f.x, f.cols, f.m, 256, &b_bytes)) return rc;
     const int rc = f.m >= 384 ? launch_fmt<512, __nv_bfloat16, 0>(dev, f, map, b_bytes, f.m, many)
                               : launch_fmt<256, __nv_bfloat16, 0>(dev, f, map, b_bytes, f.m, many);

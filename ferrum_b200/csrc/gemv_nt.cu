@@ -30,6 +30,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 
 #include "blocks.cuh"
 #include "gemv_common.cuh"
@@ -251,7 +252,7 @@ __device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSme
                 const int s0 = byte_u(sc4[0][j >> 2], j & 3), s1 = byte_u(sc4[1][j >> 2], j & 3);
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    const uint4 f = *reinterpret_cast<const uint4 *>(fragp[nt] + 64 * j);
+                        const uint4 f = *reinterpret_cast<const uint4 *>(fragp[nt] + 64 * j);
                     int ch[4], cl[4];
                     mma_u8s8_z(ch, a0, a1, a2, a3, f.x, f.y);
                     mma_u8s8_z(cl, a0, a1, a2, a3, f.z, f.w);
@@ -312,7 +313,7 @@ __device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSme
                     const int s0 = byte_s(word_of(sc0, gidx >> 2), gidx & 3), s1 = byte_s(word_of(sc1, gidx >> 2), gidx & 3);
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
-                        int ch[4], cl[4];
+                                int ch[4], cl[4];
                         mma_s8s8_k16_z(ch, a[0], a[1], lh ? f[nt].z : f[nt].x);
                         mma_s8s8_k16_z(cl, a[0], a[1], lh ? f[nt].w : f[nt].y);
                         ah[nt][0] += s0 * ch[0];
@@ -340,7 +341,7 @@ __device__ __forceinline__ void superblock_nt(const uint8_t *stage, const ActSme
 // FMT: FQ_Q4_K / FQ_Q6_K; NT: tiles of eight activation rows; STAGES: superblocks in flight per warp;
 // GROUPED: block = (expert, tile of 8 NT expert-sorted rows), else block = (K slice, share of the row tiles).
 template <int FMT, int NT, int STAGES, bool GROUPED>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(NT > 2 ? 384 : 512, 1)
 k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
     using St = StageNT<FMT>;
     constexpr uint32_t TOK = 8 * NT;
@@ -460,7 +461,9 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
     // The block's resident activations: 16-byte pieces of the prepared rows (per row 32 nb of fragments and
     // 2 nb of records), copied asynchronously; rows the job does not have are zero.
     {
-        const uint32_t per_row = 34 * nb, pieces = TOK * per_row;
+        // Rows the tile loop will read: all of them, or (grouped tiles of 32) as many eights as it will take.
+        const uint32_t rows_used = (GROUPED && NT == 4) ? (m <= 8 ? 8u : m <= 16 ? 16u : 32u) : TOK;
+        const uint32_t per_row = 34 * nb, pieces = rows_used * per_row;
         const size_t tok_bytes = (size_t)J.nblk * 544;
         for (uint32_t i = threadIdx.x; i < pieces; i += blockDim.x) {
             const uint32_t tok = i / per_row, p = i - tok * per_row;
@@ -479,67 +482,79 @@ k_nt(const __grid_constant__ NtJob J, const __grid_constant__ TpPush P) {
     }
     __syncthreads();
 
+    // The tile loop for NTU tiles of eight activation rows.  A grouped block picks NTU by the rows its tile holds
+    // (the resident layout does not depend on it), so a nearly empty tile does not pay for a full one.
     uint32_t c_stage = 0;
-    for (uint32_t tile = first; tile < total_tiles; tile += stride) {
-        const Tile here = tile_at(tile);
-        float yacc[NT][4];
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) yacc[nt][i] = 0.f;
-        for (uint32_t bb = 0; bb < nb; bb++) {
-            issue();
-            cp_async_wait<STAGES - 1>();
-            __syncwarp();
-            superblock_nt<FMT, NT>(ring + (size_t)c_stage * St::BYTES, A, bb, ((b0 + bb) & 1u) != 0, g, t, yacc);
-            __syncwarp();
-            c_stage = c_stage + 1 == STAGES ? 0 : c_stage + 1;
-        }
-        bool store = true;
-        if (!GROUPED && J.slices > 1) {
-            // Partial sums of this slice; the last warp to arrive at the tile adds all slices in slice order.
-            float4 *part = J.ws + ((size_t)tile * J.slices) * 32 * NT;
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) part[((size_t)slice * 32 + lane) * NT + nt] = make_float4(yacc[nt][0], yacc[nt][1], yacc[nt][2], yacc[nt][3]);
-            __threadfence();
-            __syncwarp();
-            uint32_t arrived = 0;
-            if (lane == 0) arrived = atomicAdd(J.counters + tile, 1u);
-            arrived = __shfl_sync(0xffffffffu, arrived, 0);
-            store = arrived + 1 == J.slices;
-            if (store) {
+    auto run = [&](auto ntu) {
+        constexpr int NTU = decltype(ntu)::value;
+        for (uint32_t tile = first; tile < total_tiles; tile += stride) {
+            const Tile here = tile_at(tile);
+            float yacc[NTU][4];
+    #pragma unroll
+            for (int nt = 0; nt < NTU; nt++)
+    #pragma unroll
+                for (int i = 0; i < 4; i++) yacc[nt][i] = 0.f;
+            for (uint32_t bb = 0; bb < nb; bb++) {
+                issue();
+                cp_async_wait<STAGES - 1>();
+                __syncwarp();
+                superblock_nt<FMT, NTU>(ring + (size_t)c_stage * St::BYTES, A, bb, ((b0 + bb) & 1u) != 0, g, t, yacc);
+                __syncwarp();
+                c_stage = c_stage + 1 == STAGES ? 0 : c_stage + 1;
+            }
+            bool store = true;
+            if (!GROUPED && J.slices > 1) {
+                // Partial sums of this slice; the last warp to arrive at the tile adds all slices in slice order.
+                float4 *part = J.ws + ((size_t)tile * J.slices) * 32 * NTU;
+    #pragma unroll
+                for (int nt = 0; nt < NTU; nt++) part[((size_t)slice * 32 + lane) * NTU + nt] = make_float4(yacc[nt][0], yacc[nt][1], yacc[nt][2], yacc[nt][3]);
                 __threadfence();
-                if (lane == 0) J.counters[tile] = 0;
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (uint32_t s = 0; s < J.slices; s++) {
-                        const float4 p = __ldcg(&part[((size_t)s * 32 + lane) * NT + nt]);
-                        acc.x += p.x;
-                        acc.y += p.y;
-                        acc.z += p.z;
-                        acc.w += p.w;
+                __syncwarp();
+                uint32_t arrived = 0;
+                if (lane == 0) arrived = atomicAdd(J.counters + tile, 1u);
+                arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                store = arrived + 1 == J.slices;
+                if (store) {
+                    __threadfence();
+                    if (lane == 0) J.counters[tile] = 0;
+    #pragma unroll
+                    for (int nt = 0; nt < NTU; nt++) {
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (uint32_t s = 0; s < J.slices; s++) {
+                            const float4 p = __ldcg(&part[((size_t)s * 32 + lane) * NTU + nt]);
+                            acc.x += p.x;
+                            acc.y += p.y;
+                            acc.z += p.z;
+                            acc.w += p.w;
+                        }
+                        yacc[nt][0] = acc.x;
+                        yacc[nt][1] = acc.y;
+                        yacc[nt][2] = acc.z;
+                        yacc[nt][3] = acc.w;
                     }
-                    yacc[nt][0] = acc.x;
-                    yacc[nt][1] = acc.y;
-                    yacc[nt][2] = acc.z;
-                    yacc[nt][3] = acc.w;
                 }
             }
-        }
-        if (store) {
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t row = here.row0 + g + (i >> 1) * 8, tok = 8 * nt + 2 * t + (i & 1);
-                    if (row < here.rows && tok < m) {
-                        float *dst = &here.y[(size_t)(xrow0 + tok) * here.rows + row];
-                        *dst = yacc[nt][i];
-                        if (!GROUPED && P.world > 1) tp_store(P, seq, dst, yacc[nt][i]);
+            if (store) {
+    #pragma unroll
+                for (int nt = 0; nt < NTU; nt++)
+    #pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t row = here.row0 + g + (i >> 1) * 8, tok = 8 * nt + 2 * t + (i & 1);
+                        if (row < here.rows && tok < m) {
+                            float *dst = &here.y[(size_t)(xrow0 + tok) * here.rows + row];
+                            *dst = yacc[nt][i];
+                            if (!GROUPED && P.world > 1) tp_store(P, seq, dst, yacc[nt][i]);
+                        }
                     }
-                }
+            }
         }
+    };
+    if constexpr (GROUPED && NT == 4) {
+        if (m <= 8) run(std::integral_constant<int, 1>{});
+        else if (m <= 16) run(std::integral_constant<int, 2>{});
+        else run(std::integral_constant<int, 4>{});
+    } else {
+        run(std::integral_constant<int, NT>{});
     }
     cp_async_wait<0>();
     if (!GROUPED && P.world > 1) tp_finish(P, seq);
@@ -557,7 +572,7 @@ template <int FMT, int NT, bool GROUPED> void (*nt_kernel(int stages))(NtJob, Tp
 template <int FMT, int NT> bool nt_shape(const fq_device *dev, uint32_t tiles16, uint32_t nblk, bool grouped, NtShape &S) {
     using St = StageNT<FMT>;
     constexpr uint32_t TOK = 8 * NT;
-    S.warps = 16;
+    S.warps = NT > 2 ? 12 : 16; // wider tiles hold more accumulators per thread: fewer, fatter warps
     // Fewest slices: a slice of activations must fit beside a ring of two stages per warp.
     const uint32_t ring2 = S.warps * 2 * St::BYTES;
     uint32_t nb_fit = 0;
@@ -703,8 +718,9 @@ int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t cou
     J.groups = f.groups;
     J.total_rows = total_rows;
     NtShape S;
-    const bool ok = f.format == FQ_Q4_K ? nt_shape<FQ_Q4_K, 2>(dev, tiles, J.nblk, true, S)
-                  : f.format == FQ_Q5_K ? nt_shape<FQ_Q5_K, 2>(dev, tiles, J.nblk, true, S) : nt_shape<FQ_Q6_K, 2>(dev, tiles, J.nblk, true, S);
+    constexpr int GNT = 4; // grouped blocks take tiles of 32 expert-sorted rows
+    const bool ok = f.format == FQ_Q4_K ? nt_shape<FQ_Q4_K, GNT>(dev, tiles, J.nblk, true, S)
+                  : f.format == FQ_Q5_K ? nt_shape<FQ_Q5_K, GNT>(dev, tiles, J.nblk, true, S) : nt_shape<FQ_Q6_K, GNT>(dev, tiles, J.nblk, true, S);
     if (!ok) return FQ_ERR_UNSUPPORTED;
     J.nb_max = S.nb_max;
     cudaError_t e = cudaSuccess;
@@ -720,10 +736,10 @@ int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t cou
     }
     if (!J.prep) return FQ_ERR_UNSUPPORTED;
     if (int rc = fq_check_cuda(dev, e, "activation preparation launch")) return rc;
-    // Every group has at most ceil(rows / 16) <= rows / 16 + 1 tiles of sixteen rows.
-    const uint32_t grid = total_rows / 16 + f.groups;
-    e = f.format == FQ_Q4_K ? nt_launch<FQ_Q4_K, 2, true>(dev, J, S, grid, TpPush{})
-      : f.format == FQ_Q5_K ? nt_launch<FQ_Q5_K, 2, true>(dev, J, S, grid, TpPush{}) : nt_launch<FQ_Q6_K, 2, true>(dev, J, S, grid, TpPush{});
+    // Every group has at most ceil(rows / 32) <= rows / 32 + 1 tiles.
+    const uint32_t grid = total_rows / (8 * GNT) + f.groups;
+    e = f.format == FQ_Q4_K ? nt_launch<FQ_Q4_K, GNT, true>(dev, J, S, grid, TpPush{})
+      : f.format == FQ_Q5_K ? nt_launch<FQ_Q5_K, GNT, true>(dev, J, S, grid, TpPush{}) : nt_launch<FQ_Q6_K, GNT, true>(dev, J, S, grid, TpPush{});
     if (int rc = fq_check_cuda(dev, e, "grouped gemv launch")) return rc;
     return fq_end_enqueue(dev, "gemv_nt_grouped", 2);
 }

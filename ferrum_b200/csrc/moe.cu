@@ -139,9 +139,22 @@ k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, u
     }
     for (uint32_t i = tid; i < 32 * experts + experts + 1; i += 1024) cnt[i] = 0;
     __syncthreads();
+    // Lanes of the warp that hold the same (valid) expert id: one ballot per bit of the id.  (The hardware match
+    // instruction measured several times slower on this kernel's single SM.)
+    const int id_bits = 32 - __clz((int)experts - 1);
+    auto same_as = [&](uint32_t e, bool valid) {
+        uint32_t peers = __ballot_sync(0xffffffffu, valid);
+        for (int b = 0; b < id_bits; b++) {
+            const bool bit = (e >> b) & 1u;
+            const uint32_t bal = __ballot_sync(0xffffffffu, bit);
+            peers &= bit ? bal : ~bal;
+        }
+        return peers;
+    };
     auto count_one = [&](uint32_t e, bool live) {
-        const uint32_t peers = __match_any_sync(0xffffffffu, e);
-        if (live && e < experts && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
+        const bool valid = live && e < experts;
+        const uint32_t peers = same_as(e, valid);
+        if (valid && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
         __syncwarp();
     };
     if (cached) {
@@ -195,7 +208,7 @@ k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, u
     }
     __syncthreads();
     auto place_one = [&](uint32_t r, uint32_t e, bool live) {
-        const uint32_t peers = __match_any_sync(0xffffffffu, e);
+        const uint32_t peers = same_as(e, live && e < experts);
         if (live && e < experts) {
             const uint32_t rank = __popc(peers & ((1u << lane) - 1));
             const uint32_t at = cnt[warp * experts + e] + rank;
