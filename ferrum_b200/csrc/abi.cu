@@ -129,7 +129,7 @@ extern "C" int fq_device_create(int ordinal, fq_device **out) {
     if ((e = cudaStreamCreateWithFlags(&dev->side_stream, cudaStreamNonBlocking)) != cudaSuccess) return bail(e, "cudaStreamCreate");
     if ((e = cudaEventCreateWithFlags(&dev->fork_event, cudaEventDisableTiming)) != cudaSuccess) return bail(e, "cudaEventCreate");
     if ((e = cudaEventCreateWithFlags(&dev->join_event, cudaEventDisableTiming)) != cudaSuccess) return bail(e, "cudaEventCreate");
-    dev->side_xprep_bytes = (size_t)4 << 20;
+    dev->side_xprep_bytes = (size_t)64 << 20;
     if ((e = cudaMalloc(&dev->side_xprep, dev->side_xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
     dev->xprep_bytes = FQ_GEMV_SCRATCH_BYTES;
     if ((e = cudaMalloc(&dev->xprep, dev->xprep_bytes)) != cudaSuccess) return bail(e, "activation scratch");
@@ -925,14 +925,24 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
     if (scratch_elems < s.total) return fq_fail(dev, FQ_ERR_SHAPE, "MoE scratch holds %zu of %zu floats", scratch_elems, s.total);
     const size_t routes = m * used;
     const bool identity = routes <= MV_ID_MAX_ROUTES || dev->exact;
-    // The shared expert depends on x only: at decode widths (small kernels, latency-bound) it runs on the side
-    // stream beside the router and the routed experts; at wide inputs its GEMMs share the handle's workspace
-    // with the rest, so it stays in line.
-    SideBranch side = (identity && !dev->exact) ? side_begin(dev) : SideBranch{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
-    int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared);
-    if (int rc2 = side_detach(side)) rc = rc ? rc : rc2;
+    // The shared expert depends on x only and runs on the side stream beside the routed chain: at decode widths
+    // (small kernels, latency-bound) from the start; at wide inputs after the router, whose GEMM shares the
+    // split-K workspace with the shared expert's (the routing, map and grouped expert kernels use none of it).
+    SideBranch side{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
+    int rc = FQ_OK;
+    auto shared_expert = [&]() {
+        if (!dev->exact) side = side_begin(dev);
+        const int r = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared);
+        const int r2 = side_detach(side);
+        return r ? r : r2;
+    };
+    if (identity) rc = shared_expert();
     const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
     if (!rc) rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts);
+    if (!identity) {
+        const int r = shared_expert(); // also after an error: the branch must be detached exactly once
+        rc = rc ? rc : r;
+    }
     if (!rc)
         rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m, f->sigmoid,
                           f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate);
@@ -991,12 +1001,23 @@ extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset
         return fq_fail(dev, FQ_ERR_RANGE, "%zu expert rows of %zu floats (and %zu bytes of outputs) at offset %zu do not fit the symmetric buffer", routes,
                        hidden, out_bytes, region_offset);
     float *down = (float *)(fq_comm_local(comm) + region_offset);
-    // As in fq_moe_ffn: at decode widths the (replicated) shared expert runs on the side stream.
-    SideBranch side = narrow ? side_begin(dev) : SideBranch{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
-    int rc = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared);
-    if (int rc2 = side_detach(side)) rc = rc ? rc : rc2;
+    // As in fq_moe_ffn: the (replicated) shared expert runs on the side stream, from the start at decode widths
+    // and after the router at wide inputs.
+    SideBranch side{dev, dev->stream, dev->xprep, dev->xprep_bytes, false};
+    int rc = FQ_OK;
+    auto shared_expert = [&]() {
+        if (!dev->exact) side = side_begin(dev);
+        const int r = fq_dense_ffn(dev, f->shared_gate, f->shared_up, f->shared_down, x, m, s.shared_tmp, 3 * m * f->shared_ffn, s.shared);
+        const int r2 = side_detach(side);
+        return r ? r : r2;
+    };
+    if (narrow) rc = shared_expert();
     const float *shared_w = f->shared_gate_inp ? f->shared_gate_inp : x;
     if (!rc) rc = fq_project(dev, f->router, x, FQ_F32, m * hidden, m, s.logits, FQ_F32, m * experts);
+    if (!narrow) {
+        const int r = shared_expert();
+        rc = rc ? rc : r;
+    }
     if (!rc)
         rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m, f->sigmoid,
                           f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate);
