@@ -697,6 +697,15 @@ def moe_bench(S, dev, stream, torch, timed_ms):
         flops = 2.0 * T * (USED + 1) * 3 * F * H
         res[f"t{T}"] = {"us": round(ms * 1e3, 1), "weight_gbs": round(touched / (ms * 1e-3) / 1e9, 1),
                         "tflops": round(flops / (ms * 1e-3) / 1e12, 2), "weight_bytes": touched}
+        if T > 1:
+            # Where the block's time goes: the library's own per-operation table over five eager passes (device
+            # time between each operation's first and last kernel; operations on the side stream overlap the rest).
+            dev.set_profiling(True)
+            for _ in range(5):
+                S.moe_ffn(dev, f, x, T, scratch, o)
+            table = dev.take_profile()
+            dev.set_profiling(False)
+            res[f"t{T}"]["profile_us"] = {k: round(v["gpu_ns"] / max(1, v["gpu_samples"]) / 1e3 * (v["calls"] / 5), 1) for k, v in table.items()}
     # The same model's Q8_0 output head at M = 1 (65,536 of its 151,936 rows: 142 MB, larger than L2).
     rows = 65536
     head = M(dev, rows, H, 1, Q8_0, random_matrix(Q8_0, rows, H, 907))

@@ -27,6 +27,11 @@ class Counters(C.Structure):
                 ("bytes_uploaded", C.c_uint64), ("bytes_downloaded", C.c_uint64)]
 
 
+class ProfileEntry(C.Structure):
+    _fields_ = [("name", C.c_char * 48), ("calls", C.c_uint64), ("kernels", C.c_uint64), ("wall_ns", C.c_uint64),
+                ("gpu_ns", C.c_uint64), ("gpu_samples", C.c_uint64)]
+
+
 class GgufTensor(C.Structure):
     _fields_ = [("name", C.c_char * 260), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4), ("type_id", C.c_uint32),
                 ("offset", C.c_uint64), ("byte_len", C.c_uint64)]
@@ -62,6 +67,8 @@ SIGNATURES = {
     "fq_test_fail_after": (_I, [_P, _I]),
     "fq_test_fail_completion": (_I, [_P]),
     "fq_probe_read_stream": (_I, [_P, _P, _Z, _U32]),
+    "fq_set_profiling": (_I, [_P, _I]),
+    "fq_take_profile": (_I, [_P, C.POINTER(ProfileEntry), _Z, C.POINTER(_Z)]),
     "fq_capture_begin": (_I, [_P]),
     "fq_capture_end": (_I, [_P, C.POINTER(_P)]),
     "fq_graph_launch": (_I, [_P, _P]),

@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdlib>
 #include <algorithm>
+#include <ctime>
 #include <cstring>
 #include <utility>
 #include <vector>
@@ -52,6 +53,28 @@ extern "C" const char *fq_last_error(fq_device *dev) { return dev ? dev->error.c
 
 // ------------------------------------------------------------------ enqueue bookkeeping
 
+static uint64_t host_ns() {
+    timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec;
+}
+
+static cudaEvent_t profile_event(fq_device *dev) {
+    if (!dev->profile_free.empty()) {
+        cudaEvent_t e = dev->profile_free.back();
+        dev->profile_free.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return e;
+}
+
+constexpr size_t PROFILE_MAX_PENDING = 1u << 16; // samples kept between two `fq_take_profile`; later calls are counted without a device time
+
 int fq_begin_enqueue(fq_device *dev) {
     if (!dev) return FQ_ERR_PARAM;
     if (dev->failed) return fq_fail(dev, FQ_ERR_SYNC, "device handle holds a failed submission; call fq_device_recover");
@@ -63,17 +86,116 @@ int fq_begin_enqueue(fq_device *dev) {
         }
         dev->fail_after--;
     }
-    return fq_check_cuda(dev, cudaSetDevice(dev->ordinal), "cudaSetDevice");
+    if (int rc = fq_check_cuda(dev, cudaSetDevice(dev->ordinal), "cudaSetDevice")) return rc;
+    if (dev->profiling && (!dev->profile_open || dev->profile_auto)) {
+        // The operation's start: one enqueue may pass here several times (checks, then launchers) before it ends.
+        // A start that the previous operation's end left behind (for launchers that end several operations after
+        // one begin) is replaced, so the host's time between two calls is not charged to the second.
+        if (dev->profile_open && dev->profile_start) dev->profile_free.push_back(dev->profile_start);
+        dev->profile_open = true;
+        dev->profile_auto = false;
+        dev->profile_t0 = host_ns();
+        dev->profile_start = nullptr;
+        if (!dev->capturing && dev->profile_samples.size() < PROFILE_MAX_PENDING && (dev->profile_start = profile_event(dev)))
+            if (cudaEventRecord(dev->profile_start, dev->stream) != cudaSuccess) {
+                cudaGetLastError();
+                dev->profile_free.push_back(dev->profile_start);
+                dev->profile_start = nullptr;
+            }
+    }
+    return FQ_OK;
 }
 
 int fq_end_enqueue(fq_device *dev, const char *what, int kernels) {
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) {
         cudaGetLastError();
+        dev->profile_open = false;
         return fq_fail(dev, FQ_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
     }
     if (dev->capturing) dev->captured_kernels += (uint64_t)kernels;
     else dev->counters.dispatches += (uint64_t)kernels;
+    if (dev->profiling && dev->profile_open) {
+        dev->profile_open = false;
+        fq_device::ProfileTotals &t = dev->profile[what];
+        t.calls++;
+        t.kernels += (uint64_t)kernels;
+        t.wall_ns += host_ns() - dev->profile_t0;
+        if (dev->profile_start) {
+            cudaEvent_t stop = profile_event(dev);
+            if (stop && cudaEventRecord(stop, dev->stream) == cudaSuccess) {
+                dev->profile_samples.push_back({what, dev->profile_start, stop});
+            } else {
+                cudaGetLastError();
+                dev->profile_free.push_back(dev->profile_start);
+                if (stop) dev->profile_free.push_back(stop);
+            }
+            dev->profile_start = nullptr;
+        }
+        // What is enqueued next without a begin of its own starts here.
+        dev->profile_open = dev->profile_auto = true;
+        dev->profile_t0 = host_ns();
+        if (!dev->capturing && dev->profile_samples.size() < PROFILE_MAX_PENDING && (dev->profile_start = profile_event(dev)))
+            if (cudaEventRecord(dev->profile_start, dev->stream) != cudaSuccess) {
+                cudaGetLastError();
+                dev->profile_free.push_back(dev->profile_start);
+                dev->profile_start = nullptr;
+            }
+    }
+    return FQ_OK;
+}
+
+// `MetalDevice::set_profiling` (src/metal/mod.rs:636-639): switches the per-operation table on or off and clears it.
+extern "C" int fq_set_profiling(fq_device *dev, int on) {
+    if (!dev) return FQ_ERR_PARAM;
+    if (dev->capturing) return fq_fail(dev, FQ_ERR_PARAM, "profiling cannot be switched inside a graph capture");
+    for (auto &smp : dev->profile_samples) {
+        dev->profile_free.push_back(smp.start);
+        dev->profile_free.push_back(smp.stop);
+    }
+    dev->profile_samples.clear();
+    dev->profile.clear();
+    if (dev->profile_open && dev->profile_start) dev->profile_free.push_back(dev->profile_start);
+    dev->profile_start = nullptr;
+    dev->profile_open = dev->profile_auto = false;
+    dev->profiling = on != 0;
+    return FQ_OK;
+}
+
+// `MetalDevice::take_profile` (src/metal/mod.rs:649-651): waits for the stream, resolves the pending event pairs
+// into device times, copies the table (in name order, like the reference's BTreeMap) and clears it.
+extern "C" int fq_take_profile(fq_device *dev, fq_profile_entry *out, size_t capacity, size_t *count) {
+    if (!dev || !count || (capacity && !out)) return FQ_ERR_PARAM;
+    if (dev->capturing) return fq_fail(dev, FQ_ERR_PARAM, "the profile cannot be taken inside a graph capture");
+    if (int rc = fq_synchronize(dev)) return rc;
+    if (dev->side_stream) cudaStreamSynchronize(dev->side_stream);
+    for (auto &smp : dev->profile_samples) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, smp.start, smp.stop) == cudaSuccess) {
+            fq_device::ProfileTotals &t = dev->profile[smp.name];
+            t.gpu_ns += (uint64_t)((double)ms * 1e6);
+            t.gpu_samples++;
+        } else {
+            cudaGetLastError();
+        }
+        dev->profile_free.push_back(smp.start);
+        dev->profile_free.push_back(smp.stop);
+    }
+    dev->profile_samples.clear();
+    *count = dev->profile.size();
+    size_t i = 0;
+    for (const auto &kv : dev->profile) {
+        if (i >= capacity) break;
+        fq_profile_entry &e = out[i++];
+        memset(&e, 0, sizeof e);
+        snprintf(e.name, sizeof e.name, "%s", kv.first.c_str());
+        e.calls = kv.second.calls;
+        e.kernels = kv.second.kernels;
+        e.wall_ns = kv.second.wall_ns;
+        e.gpu_ns = kv.second.gpu_ns;
+        e.gpu_samples = kv.second.gpu_samples;
+    }
+    if (capacity >= dev->profile.size()) dev->profile.clear();
     return FQ_OK;
 }
 
@@ -171,6 +293,12 @@ extern "C" int fq_device_destroy(fq_device *dev) {
         cudaStreamSynchronize(dev->side_stream);
         cudaStreamDestroy(dev->side_stream);
     }
+    for (auto &smp : dev->profile_samples) {
+        cudaEventDestroy(smp.start);
+        cudaEventDestroy(smp.stop);
+    }
+    if (dev->profile_start) cudaEventDestroy(dev->profile_start);
+    for (cudaEvent_t e : dev->profile_free) cudaEventDestroy(e);
     if (dev->fork_event) cudaEventDestroy(dev->fork_event);
     if (dev->join_event) cudaEventDestroy(dev->join_event);
     if (dev->staging_dev) cudaFree(dev->staging_dev);

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <map>
 #include <string>
+#include <vector>
 
 #include "../../include/ferrum_b200.h"
 
@@ -33,6 +34,16 @@ struct fq_device {
     int fail_after = -1;          // test hook: enqueues left before an injected failure
     bool fail_completion = false; // test hook: next synchronize reports failure
     fq_counters counters{};
+    // Opt-in per-operation measurements (`fq_set_profiling` / `fq_take_profile`): a pair of events around every
+    // enqueue outside graph capture, resolved into the table when it is taken.
+    struct ProfileSample { const char *name; cudaEvent_t start, stop; };
+    struct ProfileTotals { uint64_t calls = 0, kernels = 0, wall_ns = 0, gpu_ns = 0, gpu_samples = 0; };
+    bool profiling = false, profile_open = false, profile_auto = false;
+    cudaEvent_t profile_start = nullptr;
+    uint64_t profile_t0 = 0;
+    std::vector<ProfileSample> profile_samples;
+    std::vector<cudaEvent_t> profile_free; // events ready for reuse
+    std::map<std::string, ProfileTotals> profile;
     bool capturing = false;       // between fq_capture_begin and fq_capture_end
     const struct TpPush *tp_push = nullptr; // set while a projection that exchanges its own output is enqueued
     bool tp_pushed = false;                 // the kernel that was launched took tp_push

@@ -129,6 +129,20 @@ class Device:
     def fail_completion(self) -> None:
         self.check(self._L.fq_test_fail_completion(self.handle))
 
+    def set_profiling(self, enabled: bool) -> None:
+        """`MetalDevice::set_profiling` (src/metal/mod.rs:636-639): per-operation table on / off, cleared either way."""
+        self.check(self._L.fq_set_profiling(self.handle, 1 if enabled else 0))
+
+    def take_profile(self) -> dict:
+        """`MetalDevice::take_profile` (src/metal/mod.rs:649-651): waits, then returns and clears the table:
+        ``{name: {"calls", "kernels", "wall_ns", "gpu_ns", "gpu_samples"}}`` in name order."""
+        cap = 256
+        buf = (_lib.ProfileEntry * cap)()
+        n = C.c_size_t(0)
+        self.check(self._L.fq_take_profile(self.handle, buf, cap, C.byref(n)))
+        return {buf[i].name.decode(): {k: int(getattr(buf[i], k)) for k in ("calls", "kernels", "wall_ns", "gpu_ns", "gpu_samples")}
+                for i in range(min(n.value, cap))}
+
     def probe_read_stream(self, data: torch.Tensor, blocks_per_sm: int = 8) -> None:
         """Enqueue a kernel that only reads ``data`` (the device's read-only streaming ceiling, timed by the caller)."""
         self.check(self._L.fq_probe_read_stream(self.handle, C.c_void_p(data.data_ptr()), data.numel() * data.element_size(), blocks_per_sm))

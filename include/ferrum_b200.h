@@ -90,6 +90,22 @@ int fq_set_exact(fq_device *dev, int on);
 int fq_test_fail_after(fq_device *dev, int n);
 int fq_test_fail_completion(fq_device *dev);
 
+/* Opt-in per-operation measurements, the counterpart of `set_profiling` / `take_profile` / `ProfileEntry`
+ * (src/metal/mod.rs:636-676, 231-242).  While profiling is on every enqueue is bracketed by a pair of CUDA
+ * events on its stream (outside graph capture; a captured enqueue is counted without a device time) and keyed
+ * by the operation's name ("gemv_i8s", "gemv_nt", "gemm_tc", "moe_route", ...).  `fq_set_profiling` switches it
+ * and clears the table.  `fq_take_profile` waits for the stream, resolves the events, writes up to `capacity`
+ * entries in name order, stores the number of entries the table holds in `*count`, and clears the table when
+ * all of them fitted.  `wall_ns` is host time spent enqueueing, `gpu_ns` the sum over the `gpu_samples` timed
+ * calls of the device time between the operation's first and last kernel (operations of one stream run in
+ * order, so this includes waiting behind the operation before it). */
+typedef struct fq_profile_entry {
+    char name[48];
+    uint64_t calls, kernels, wall_ns, gpu_ns, gpu_samples;
+} fq_profile_entry;
+int fq_set_profiling(fq_device *dev, int on);
+int fq_take_profile(fq_device *dev, fq_profile_entry *out, size_t capacity, size_t *count);
+
 /* Diagnostic: enqueues a kernel that only READS `bytes` bytes at `data` (16 bytes per thread and step, the
  * weight-streaming loads of the projection kernels, `blocks_per_sm` blocks of 256 threads per SM): timed by the
  * caller it gives the read-only streaming ceiling of the device, the counterpart of the reference's `h_bw_read`

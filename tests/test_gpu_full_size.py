@@ -333,3 +333,42 @@ def test_argmax_and_topk_blocks(device):
     s.argmax(device, dev_f32(big), 65536, 1, out1)
     device.synchronize()
     assert int(out1.item()) == int(np.argmax(big))
+
+
+def test_profile_table_names_times_and_clears(device):
+    """`set_profiling` / `take_profile` (src/metal/mod.rs:636-676): per-operation calls and device times keyed by
+    name; taking the table clears it; switching profiling off stops the recording."""
+    s = S()
+    rows, cols = 2048, 2048
+    w = s.Matrix.from_packed(device, rows, cols, 1, ref.Q4_K, ref.random_matrix(ref.Q4_K, rows, cols, seed=41))
+    x1 = dev_f32(np.random.default_rng(5).standard_normal(cols))
+    x8 = dev_f32(np.random.default_rng(6).standard_normal((8, cols)))
+    y1 = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    y8 = torch.zeros(8 * rows, dtype=torch.float32, device="cuda")
+    device.set_profiling(True)
+    for _ in range(3):
+        s.project(device, w, x1, 1, y1)
+    s.project(device, w, x8, 8, y8)
+    s.rmsnorm(device, x8, x1, 1e-6, 8, y8[:8 * cols])
+    table = device.take_profile()
+    assert list(table) == sorted(table)
+    assert table["gemv_i8s"]["calls"] == 3 and table["gemv_i8s"]["gpu_samples"] == 3 and table["gemv_i8s"]["kernels"] == 3
+    assert table["gemv_nt"]["calls"] == 1 and table["gemv_nt"]["kernels"] == 2
+    assert table["rmsnorm"]["calls"] == 1
+    for e in table.values():
+        assert e["gpu_ns"] > 0 and e["wall_ns"] > 0
+        assert e["gpu_ns"] < 50_000_000  # milliseconds at most for these launches
+    assert device.take_profile() == {}
+    device.set_profiling(False)
+    s.project(device, w, x1, 1, y1)
+    assert device.take_profile() == {}
+    # inside a capture an enqueue is counted but has no device time of its own
+    device.set_profiling(True)
+    device.capture_begin()
+    s.project(device, w, x1, 1, y1)
+    g = device.capture_end()
+    g.launch()
+    table = device.take_profile()
+    assert table["gemv_i8s"]["calls"] == 1 and table["gemv_i8s"]["gpu_samples"] == 0
+    device.set_profiling(False)
+    device.synchronize()
