@@ -82,10 +82,17 @@ __host__ __device__ inline PrepI8 prep_i8_layout(uint32_t cols) {
 // With `norm_w` they are rmsnorm(x) * norm_w (`h_rmsnorm`, src/metal/shaders/hybrid.metal:1563-1575).
 // `bsrc` is the superblock of the row that is read, `b` the slot of the layout `L` it is written to (the same
 // unless `L` describes a slice of the row); `norm_scale` = row_inv_rms of the whole row when `norm_w` is given.
-__device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, uint32_t bsrc, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base,
+struct PrepLoad { // the lane's eight values of one superblock, fetched ahead of their use
+    float4 v0, v1;
+    __device__ __forceinline__ void fetch(const float *__restrict__ xrow, uint32_t bsrc, uint32_t lane) {
+        const float4 *src = reinterpret_cast<const float4 *>(xrow + (size_t)bsrc * 256 + lane * 8);
+        v0 = src[0];
+        v1 = src[1];
+    }
+};
+__device__ __forceinline__ void prep_superblock(const PrepLoad &in, uint32_t bsrc, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base,
                                                 const float *__restrict__ urow, const float *__restrict__ norm_w, float norm_scale) {
-    const float4 *src = reinterpret_cast<const float4 *>(xrow + (size_t)bsrc * 256 + lane * 8);
-    const float4 v0 = src[0], v1 = src[1];
+    const float4 v0 = in.v0, v1 = in.v1;
     float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     if (norm_w) {
         const float scale = norm_scale;
@@ -125,6 +132,13 @@ __device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, 
         // A non-finite activation anywhere in the block makes the block's factor NaN.
         reinterpret_cast<float *>(base + L.isc_off)[b] = finite ? ldexpf(1.f, -e) : __int_as_float(0x7fc00000);
     }
+}
+
+__device__ __forceinline__ void prep_superblock(const float *__restrict__ xrow, uint32_t bsrc, uint32_t b, uint32_t lane, const PrepI8 &L, uint8_t *base,
+                                                const float *__restrict__ urow, const float *__restrict__ norm_w, float norm_scale) {
+    PrepLoad in;
+    in.fetch(xrow, bsrc, lane);
+    prep_superblock(in, bsrc, b, lane, L, base, urow, norm_w, norm_scale);
 }
 
 // One warp per (activation row, superblock).
@@ -590,7 +604,16 @@ k_gemv_i8s(const __grid_constant__ SlicedJob J, const __grid_constant__ TpPush P
     const uint32_t seq = P.world > 1 ? tp_seq(P) : 0u;
     {
         const float scale = J.norm_w ? row_inv_rms(J.x, J.cols, J.norm_eps, lane) : 0.f;
-        for (uint32_t bb = warp; bb < nb; bb += W) prep_superblock(J.x, b0 + bb, bb, lane, L, act, J.x_up, J.norm_w, scale);
+        // A warp's superblocks two at a time, both fetched before either is worked on (the fetch is an L2 round
+        // trip; the widest slice of the 27B layer set gives a warp two superblocks).
+        for (uint32_t bb = warp; bb < nb; bb += 2 * W) {
+            PrepLoad in0, in1;
+            const bool two = bb + W < nb;
+            in0.fetch(J.x, b0 + bb, lane);
+            if (two) in1.fetch(J.x, b0 + bb + W, lane);
+            prep_superblock(in0, b0 + bb, bb, lane, L, act, J.x_up, J.norm_w, scale);
+            if (two) prep_superblock(in1, b0 + bb + W, bb + W, lane, L, act, J.x_up, J.norm_w, scale);
+        }
     }
     __syncthreads();
 
