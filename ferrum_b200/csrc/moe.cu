@@ -235,6 +235,36 @@ k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, u
     for (uint32_t i = total[experts] + tid; i < routes; i += 1024) sorted[i] = 0;
 }
 
+// The same map for at most 32 routes (a decode step's), by one warp: lane r ranks its route among the others.
+__global__ void __launch_bounds__(32)
+k_moe_map_small(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, uint32_t *__restrict__ offsets,
+                uint32_t *__restrict__ sorted, uint32_t *__restrict__ position) {
+    const uint32_t lane = threadIdx.x;
+    const bool live = lane < routes;
+    const uint32_t e = live ? ids[lane] : 0xffffffffu;
+    const bool valid = live && e < experts;
+    uint32_t before = 0; // valid routes that sort before this one: a smaller expert, or the same expert and a lower index
+    for (uint32_t l = 0; l < routes; l++) {
+        const uint32_t oe = __shfl_sync(0xffffffffu, e, l);
+        before += (oe < experts) && (oe < e || (oe == e && l < lane));
+    }
+    if (valid) {
+        sorted[before] = lane;
+        position[lane] = before;
+    } else if (live) {
+        position[lane] = 0; // an id that names no expert: the route belongs to no row
+    }
+    const uint32_t placed = __popc(__ballot_sync(0xffffffffu, valid));
+    if (lane >= placed && lane < routes) sorted[lane] = 0; // rows past the last expert's point at route 0
+    // offsets[x] = valid routes whose expert is below x
+    for (uint32_t x0 = 0; x0 <= experts; x0 += 32) { // every lane takes every turn: the shuffles need the whole warp
+        const uint32_t x = x0 + lane;
+        uint32_t n = 0;
+        for (uint32_t l = 0; l < routes; l++) n += __shfl_sync(0xffffffffu, e, l) < x;
+        if (x <= experts) offsets[x] = n;
+    }
+}
+
 // xg[row] = x[sorted[row] / used]
 __global__ void k_moe_gather(const float *__restrict__ x, const uint32_t *__restrict__ sorted, uint32_t hidden,
                              uint32_t used, float *__restrict__ xg) {
@@ -395,6 +425,10 @@ extern "C" int fq_moe_map(fq_device *dev, const uint32_t *ids, uint32_t experts,
     if (int rc = fq_check_binding(dev, offsets, (size_t)(experts + 1) * 4, "offsets")) return rc;
     if (int rc = fq_check_binding(dev, sorted, (size_t)routes * 4, "sorted")) return rc;
     if (int rc = fq_check_binding(dev, position, (size_t)routes * 4, "position")) return rc;
+    if (routes <= 32) {
+        k_moe_map_small<<<1, 32, 0, dev->stream>>>(ids, experts, routes, offsets, sorted, position);
+        return fq_end_enqueue(dev, "moe_map", 1);
+    }
     const size_t smem = ((size_t)33 * experts + 1) * sizeof(uint32_t);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(k_moe_map, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

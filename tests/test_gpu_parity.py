@@ -291,7 +291,7 @@ def test_moe_route_top8_of_256_for_1024_tokens(device):
     assert np.allclose(host(wts).reshape(m, used).sum(1), 1.0, atol=1e-5)
 
 
-@pytest.mark.parametrize("experts,routes", [(3, 8), (256, 8192), (256, 40), (1000, 777)])
+@pytest.mark.parametrize("experts,routes", [(3, 8), (256, 8), (1000, 32), (7, 5), (256, 8192), (256, 40), (1000, 777)])
 def test_moe_map_gather_combine(device, experts, routes):
     s = S()
     rng = np.random.default_rng(routes)
