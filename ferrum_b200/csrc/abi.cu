@@ -199,10 +199,12 @@ extern "C" int fq_take_profile(fq_device *dev, fq_profile_entry *out, size_t cap
     return FQ_OK;
 }
 
-int fq_check_binding(fq_device *dev, const void *p, size_t bytes, const char *name) {
+// `align`: 16 for everything kernels read or write in 16-byte pieces; 4 for arrays of 32-bit indices, which are
+// read one at a time (a rank's slice of the expert offsets starts wherever its first expert falls).
+int fq_check_binding(fq_device *dev, const void *p, size_t bytes, const char *name, uint32_t align) {
     if (!p) return fq_fail(dev, FQ_ERR_RANGE, "%s: null binding", name);
     const uintptr_t a = (uintptr_t)p;
-    if (a & 15u) return fq_fail(dev, FQ_ERR_RANGE, "%s: binding %p is not 16-byte aligned", name, p);
+    if (a & (uintptr_t)(align - 1)) return fq_fail(dev, FQ_ERR_RANGE, "%s: binding %p is not %u-byte aligned", name, p, align);
     // A pointer inside a buffer this handle allocated must stay inside it.
     auto it = dev->allocations.upper_bound(a);
     if (it != dev->allocations.begin()) {
@@ -828,9 +830,9 @@ extern "C" int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *
         return fq_fail(dev, FQ_ERR_SHAPE, "grouped expert projection geometry");
     const size_t xb = x_elems * fq_dtype_size(x_dtype), yb = y_elems * fq_dtype_size(y_dtype);
     if (int rc = fq_check_binding(dev, x, xb, "x")) return rc;
-    if (int rc = fq_check_binding(dev, offsets, (groups + 1) * 4, "offsets")) return rc;
+    if (int rc = fq_check_binding(dev, offsets, (groups + 1) * 4, "offsets", 4)) return rc;
     if (slots)
-        if (int rc = fq_check_binding(dev, slots, groups * 4, "slots")) return rc;
+        if (int rc = fq_check_binding(dev, slots, groups * 4, "slots", 4)) return rc;
     if (int rc = fq_check_binding(dev, y, yb, "y")) return rc;
     if (int rc = fq_check_no_alias(dev, y, yb, x, xb, "y")) return rc;
     ProjectArgs a = base_args(w, x, x_dtype, y, y_dtype);

@@ -98,7 +98,7 @@ int fq_check_cuda(fq_device *dev, cudaError_t e, const char *what);
 int fq_begin_enqueue(fq_device *dev);
 int fq_end_enqueue(fq_device *dev, const char *what, int kernels);
 // Binding checks shared by the op surface (null, alignment, ownership range, overlap).
-int fq_check_binding(fq_device *dev, const void *p, size_t bytes, const char *name);
+int fq_check_binding(fq_device *dev, const void *p, size_t bytes, const char *name, uint32_t align = 16);
 int fq_check_no_alias(fq_device *dev, const void *out, size_t out_bytes, const void *in,
                       size_t in_bytes, const char *name);
 

@@ -243,7 +243,9 @@ int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x, size_t x_e
 /* `HybridModel::project_mm_id_in(d, w, x, offsets, slots, max_rows, y)`
  * (src/hybrid/engine.rs:3164-3224): rows offsets[z]..offsets[z+1] of x and y belong to group z,
  * which uses the expert stored at slots[z] (slots == NULL: expert z).  `groups` is the number of
- * groups (w.experts without a slot table); `max_rows` bounds any group's row count. */
+ * groups (w.experts without a slot table); `max_rows` bounds any group's row count.  `offsets` and `slots`
+ * are read one 32-bit value at a time: 4-byte alignment is enough for them (a rank's window into a larger
+ * table of expert offsets starts wherever its first expert falls). */
 int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems,
                      const uint32_t *offsets, const uint32_t *slots, size_t groups, size_t max_rows,
                      void *y, int y_dtype, size_t y_elems);

@@ -97,7 +97,7 @@ def test_two_ranks_gather_a_sharded_projection(tmp_path):
     assert os.path.exists(tmp_path / "ok0") and os.path.exists(tmp_path / "ok1")
 
 
-def _ep_rank(rank, world, port, out_dir):
+def _ep_rank(rank, world, port, out_dir, experts=16, used=4):
     import torch.distributed as dist
     from ferrum_b200 import surface as S
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -105,7 +105,7 @@ def _ep_rank(rank, world, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         d = S.Device(rank, use_torch_stream=False)
-        experts, used, hidden, ef = 16, 4, 512, 256
+        hidden, ef = 512, 256
         local = experts // world
         M = S.Matrix.from_packed
         gate_e, up_e = ref.random_matrix(ref.Q4_K, experts * ef, hidden, 11), ref.random_matrix(ref.Q4_K, experts * ef, hidden, 12)
@@ -144,10 +144,11 @@ def _ep_rank(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_two_ranks_split_the_experts(tmp_path):
+@pytest.mark.parametrize("experts,used", [(16, 4), (6, 2)])  # 6 experts: three to a rank, the second rank's bounds start at an odd index
+def test_two_ranks_split_the_experts(tmp_path, experts, used):
     """Expert parallelism: each rank stores half of the experts; the exchanged result has the single-GPU bits."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_ep_rank, args=(2, _port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_ep_rank, args=(2, _port(), str(tmp_path), experts, used), nprocs=2, join=True)
     assert os.path.exists(tmp_path / "ep0") and os.path.exists(tmp_path / "ep1")
