@@ -554,7 +554,9 @@ k_gemv_i8s(const __grid_constant__ SlicedJob J, const __grid_constant__ TpPush P
     const int g = lane >> 2, t = lane & 3;
     const uint32_t slice = blockIdx.x % J.slices;
     const uint32_t b0 = (uint32_t)((uint64_t)slice * J.nblk / J.slices), nb = (uint32_t)((uint64_t)(slice + 1) * J.nblk / J.slices) - b0;
-    const uint32_t first = (blockIdx.x / J.slices) * W + warp, stride = (gridDim.x / J.slices) * W;
+    // Tiles are dealt out across the blocks of a slice first, then across their warps: when there are fewer tiles
+    // than warps the idle warps are spread over all SMs instead of leaving whole SMs without work.
+    const uint32_t first = warp * (gridDim.x / J.slices) + blockIdx.x / J.slices, stride = (gridDim.x / J.slices) * W;
     const uint32_t total_tiles = J.T.tile_end[J.T.count - 1];
     const PrepI8 L = prep_i8_layout(J.nb_max * 256); // the slice's activations, laid out like a short row
     uint8_t *act = s1_smem, *ring = s1_smem + L.token_bytes + (size_t)warp * STAGES * Ring::BYTES;
