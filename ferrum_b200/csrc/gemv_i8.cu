@@ -368,11 +368,16 @@ struct GemvTargets {
 
 // FMT: FQ_Q4_K / FQ_Q6_K; MT: activation rows (1..4).  grid.x = persistent blocks over the 16-row tiles of all targets;
 // grid.y = routes in expert mode (route r: expert ids[r], activation row r / x_div, output row r).
-template <int FMT, int MT>
+// INP (routes, one activation row): the block prepares its route's activation row itself into shared memory from
+// `xin` (and `xup`: the gated unit), so no preparation launch precedes the kernel; else `prep` holds prepared rows.
+template <int FMT, int MT, bool INP = false>
 __global__ void __launch_bounds__(MT >= 3 ? 256 : MT == 2 ? 384 : MAX_WARPS * 32)
 k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *__restrict__ prep, PrepI8 L,
-          const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts, const __grid_constant__ TpPush P) {
+          const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts, const __grid_constant__ TpPush P,
+          const float *__restrict__ xin, const float *__restrict__ xup) {
     using Raw = typename RawOf<FMT>::type;
+    static_assert(!INP || MT == 1, "in-kernel preparation serves one activation row per route");
+    extern __shared__ __align__(16) uint8_t own_act[]; // INP: the route's prepared row
     __shared__ float red[2][MAX_WARPS - 1][MT * 2][8];
     const int WARPS = blockDim.x >> 5;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -389,7 +394,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
         const uint32_t e = ids[r];
         if (e >= experts) return;
         expert_off = (size_t)e * T.rows[0] * pitch;
-        prep += (size_t)(r / x_div) * L.token_bytes;
+        if constexpr (!INP) prep += (size_t)(r / x_div) * L.token_bytes;
         y_base = (size_t)r * T.rows[0];
     }
     struct Tile {
@@ -426,6 +431,12 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     pdl_trigger();
     pdl_wait();
     const uint32_t seq = P.world > 1 ? tp_seq(P) : 0u;
+    if constexpr (INP) {
+        const size_t xr = (size_t)(blockIdx.y / x_div) * L.cols;
+        for (uint32_t b = warp; b < nblk; b += WARPS) prep_superblock(xin + xr, b, b, lane, L, own_act, xup ? xup + xr : nullptr, nullptr, 0.f);
+        __syncthreads();
+        prep = own_act;
+    }
 
     // With one activation row its fragments are fetched one superblock ahead, like the weights; with
     // more rows the registers do not allow that and they are fetched at the top of the iteration.
@@ -433,7 +444,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     Act<FMT> acur[MT], anxt[MT]; // anxt is used with AHEAD only
     if (AHEAD && iters > 0) {
 #pragma unroll
-        for (int m = 0; m < MT; m++) acur[m].load(prep + (size_t)m * L.token_bytes, L, block_of(0), t, g);
+        for (int m = 0; m < MT; m++) acur[m].template load_at<INP>(prep + (size_t)m * L.token_bytes, L, block_of(0), t, g);
     }
 
     float yacc[MT][2];
@@ -453,8 +464,8 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
         n[1].load(wrap ? next.rowp[1] : here.rowp[1], nblk, nb_next, t);
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            if (AHEAD) an[m].load(prep + (size_t)m * L.token_bytes, L, nb_next, t, g);
-            else ac[m].load(prep + (size_t)m * L.token_bytes, L, block_of(it), t, g);
+            if (AHEAD) an[m].template load_at<INP>(prep + (size_t)m * L.token_bytes, L, nb_next, t, g);
+            else ac[m].template load_at<INP>(prep + (size_t)m * L.token_bytes, L, block_of(it), t, g);
         }
         superblock_dot<FMT, MT>(c, ac, t, g, yacc);
     };
@@ -750,7 +761,7 @@ template <int FMT> cudaError_t launch_sliced(fq_device *dev, const ProjectArgs *
     return launch_pdl(kernel, dim3(grid), dim3(WARPS * 32), smem, dev->stream, J, push);
 }
 
-template <int FMT, int MT>
+template <int FMT, int MT, bool INP = false>
 cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const uint8_t *prep, const PrepI8 &L, bool expert) {
     GemvTargets T{};
     T.count = count;
@@ -781,7 +792,7 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
     static int occupancy[MAX_WARPS + 1] = {};
     if (!occupancy[warps]) {
         int occ = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_i8<FMT, MT>, (int)warps * 32, 0) != cudaSuccess || occ < 1) occ = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_gemv_i8<FMT, MT, INP>, (int)warps * 32, INP ? L.token_bytes : 0) != cudaSuccess || occ < 1) occ = 1;
         occupancy[warps] = occ;
     }
     const uint32_t resident = (uint32_t)dev->sm_count * (uint32_t)occupancy[warps];
@@ -792,8 +803,8 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
         dev->tp_push = nullptr;
         dev->tp_pushed = true;
     }
-    return launch_pdl(k_gemv_i8<FMT, MT>, grid, dim3(warps * 32), 0, dev->stream, T, a[0].row_bytes, prep, L, a[0].ids, a[0].x_div,
-                      a[0].experts, push);
+    return launch_pdl(k_gemv_i8<FMT, MT, INP>, grid, dim3(warps * 32), INP ? L.token_bytes : 0, dev->stream, T, a[0].row_bytes, prep, L, a[0].ids,
+                      a[0].x_div, a[0].experts, push, (const float *)a[0].x, a[0].x_up);
 }
 
 } // namespace
@@ -828,6 +839,15 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
         }
     }
     const PrepI8 L = prep_i8_layout(f.cols);
+    if (expert && !f.norm_w && L.token_bytes <= 40 * 1024) {
+        // Routes: every block prepares its route's activation row itself (a few KB): one launch, one dependency less.
+        cudaError_t e;
+        if (f.format == FQ_Q4_K) e = launch<FQ_Q4_K, 1, true>(dev, a, count, nullptr, L, true);
+        else if (f.format == FQ_Q5_K) e = launch<FQ_Q5_K, 1, true>(dev, a, count, nullptr, L, true);
+        else e = launch<FQ_Q6_K, 1, true>(dev, a, count, nullptr, L, true);
+        if (int rc = fq_check_cuda(dev, e, "gemv launch")) return rc;
+        return fq_end_enqueue(dev, "gemv_i8", 1);
+    }
     // Successive projections use alternate halves of the scratch, so a preparation kernel that starts
     // early never writes what the previous projection may still be reading from a cache.
     if ((size_t)xrows * L.token_bytes > dev->xprep_bytes / 2) return FQ_ERR_UNSUPPORTED;
@@ -900,7 +920,7 @@ cudaError_t launch_static(const uint8_t *w, uint32_t rows, uint32_t pitch, float
         const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need);
         if (waste < best) { best = waste; warps = k; }
     }
-    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u, TpPush{});
+    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u, TpPush{}, nullptr, nullptr);
     return cudaGetLastError();
 }
 
