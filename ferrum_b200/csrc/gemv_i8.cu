@@ -757,8 +757,13 @@ template <int FMT> cudaError_t launch_sliced(fq_device *dev, const ProjectArgs *
         dev->tp_push = nullptr;
         dev->tp_pushed = true;
     }
-    const uint32_t grid = std::max(1u, sms / slices) * slices;
-    return launch_pdl(kernel, dim3(grid), dim3(WARPS * 32), smem, dev->stream, J, push);
+    // Blocks per slice: every SM's share, unless the tiles fill fewer than half of their warps -- a small matrix
+    // then takes only the blocks it can use and leaves the other SMs to whatever runs beside it (a block of this
+    // kernel takes an SM's whole register file: the shared expert of an MoE block beside the routed chain).
+    uint32_t per = std::max(1u, sms / slices);
+    const uint32_t need = (tiles + WARPS - 1) / WARPS;
+    if (need * 2 <= per) per = need;
+    return launch_pdl(kernel, dim3(per * slices), dim3(WARPS * 32), smem, dev->stream, J, push);
 }
 
 template <int FMT, int MT, bool INP = false>
