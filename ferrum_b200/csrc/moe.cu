@@ -3,6 +3,7 @@
 // h_swiglu (src/metal/shaders/hybrid.metal:2252-2388, 1606-1613).
 #include <cuda_bf16.h>
 
+#include "gemv_common.cuh"
 #include "internal.h"
 
 namespace {
@@ -25,6 +26,8 @@ k_moe_route(const float *__restrict__ logits, const float *__restrict__ x, const
             uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens, int sigmoid, int norm, int shared_gate,
             uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate, int *status) {
     extern __shared__ float route_smem[]; // [ROUTE_WARPS][experts]
+    fqk::pdl_trigger(); // the next kernel may be scheduled now; it waits for this one's results itself
+    fqk::pdl_wait();    // the logits come from the kernel before
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t t = blockIdx.x * ROUTE_WARPS + warp;
     if (t >= tokens) return;
@@ -287,6 +290,8 @@ k_moe_combine(const float *__restrict__ down, const float *__restrict__ weights,
               const uint32_t *__restrict__ position, const float *__restrict__ shared,
               const float *__restrict__ gate, uint32_t hidden, uint32_t used, uint32_t tokens,
               int identity, float *__restrict__ out) {
+    fqk::pdl_trigger();
+    fqk::pdl_wait(); // the expert rows and the shared expert's output come from the kernels before
     const size_t gid = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (gid >= (size_t)tokens * hidden) return;
     const uint32_t t = gid / hidden, i = gid % hidden;
@@ -319,8 +324,8 @@ k_moe_combine(const float *__restrict__ down, const float *__restrict__ weights,
 
 template <typename... Args> void launch_combine(cudaStream_t stream, const float *down, const float *shared, float *out, uint32_t hidden, size_t n, Args... args) {
     const bool vec = hidden % 4 == 0 && (((uintptr_t)down | (uintptr_t)shared | (uintptr_t)out) & 15) == 0;
-    if (vec) k_moe_combine<4><<<(unsigned)((n / 4 + 255) / 256), 256, 0, stream>>>(args...);
-    else k_moe_combine<1><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(args...);
+    if (vec) fqk::launch_pdl(k_moe_combine<4>, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream, args...);
+    else fqk::launch_pdl(k_moe_combine<1>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, args...);
 }
 
 // out = g / (1 + exp(-g)) * u
@@ -411,8 +416,11 @@ extern "C" int fq_moe_route(fq_device *dev, const float *logits, const float *x,
     }
     if (int rc = fq_check_no_alias(dev, ids, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "ids")) return rc;
     if (int rc = fq_check_no_alias(dev, weights, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "weights")) return rc;
-    k_moe_route<<<(tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, (size_t)ROUTE_WARPS * experts * sizeof(float), dev->stream>>>(
-        logits, x, shared_w, experts, used, hidden, tokens, sigmoid, norm, shared_gate, ids, weights, gate, dev->status_dev);
+    if (int rc = fq_check_cuda(dev, fqk::launch_pdl(k_moe_route, dim3((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32),
+                                                    (size_t)ROUTE_WARPS * experts * sizeof(float), dev->stream, logits, x, shared_w, experts, used, hidden,
+                                                    tokens, sigmoid, norm, shared_gate, ids, weights, gate, dev->status_dev),
+                               "moe_route launch"))
+        return rc;
     return fq_end_enqueue(dev, "moe_route", 1);
 }
 
