@@ -31,6 +31,10 @@ def host(t):
     return t.detach().float().cpu().numpy()
 
 
+def dev_u32(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.uint32).view(np.int32)).cuda()
+
+
 def rows_of(packed, fmt, cols, pick):
     rb = ref.row_bytes(fmt, cols)
     return np.concatenate([packed[r * rb:(r + 1) * rb] for r in pick])
@@ -372,3 +376,32 @@ def test_profile_table_names_times_and_clears(device):
     assert table["gemv_i8s"]["calls"] == 1 and table["gemv_i8s"]["gpu_samples"] == 0
     device.set_profiling(False)
     device.synchronize()
+
+
+@pytest.mark.parametrize("fmt,rows_e,cols", [(ref.Q4_K, 512, 2048), (ref.Q6_K, 2048, 512), (ref.Q4_K, 200, 768), (ref.Q6_K, 136, 256)])
+def test_grouped_rows_at_about_thirty_to_an_expert(device, fmt, rows_e, cols):
+    """`project_mm_id` with about 30 rows per expert (config 3's grouped widths) runs on the integer kernel: exact
+    integer products of the decoded weights with 16-bit activations, so the fp32 GEMV bar applies.  Uneven groups,
+    an empty expert, a group of more than 32 rows, weight-row counts that are not a multiple of 16 x 8."""
+    s = S()
+    experts, routes = 24, 24 * 30
+    packed = ref.random_matrix(fmt, experts * rows_e, cols, seed=71)
+    w = s.Matrix.from_packed(device, rows_e, cols, experts, fmt, packed)
+    rng = np.random.default_rng(72)
+    ids = np.sort(rng.integers(0, experts, routes)).astype(np.uint32)
+    ids[ids == 5] = 6   # an expert nobody picked, and one with about twice the rows
+    counts = np.bincount(ids, minlength=experts)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32)
+    x = rng.standard_normal((routes, cols)).astype(np.float32)
+    y = torch.full((routes * rows_e,), float("nan"), dtype=torch.float32, device="cuda")
+    s.project_mm_id(device, w, dev_f32(x), dev_u32(offsets), int(counts.max()), y)
+    device.synchronize()
+    got = host(y).reshape(routes, rows_e)
+    assert np.isfinite(got).all()
+    rb = ref.row_bytes(fmt, cols)
+    worst = 0.0
+    for r in rng.choice(routes, 40, replace=False):
+        e = int(ids[r])
+        want = ref.matmul(fmt, packed[e * rows_e * rb:(e + 1) * rows_e * rb], rows_e, cols, x[r], 1)[0]
+        worst = max(worst, np.abs(got[r] - want).max() / np.abs(want).max())
+    assert worst <= TOL_F32, worst
