@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "libferrum_b200.so")
 
 OK, ERR_SHAPE, ERR_RANGE, ERR_DEVICE, ERR_ALIAS, ERR_WEIGHT, ERR_SYNC, ERR_TIMEOUT, ERR_CUDA, ERR_PARAM, \
     ERR_UNSUPPORTED, ERR_GGUF = range(12)
-Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
+Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS = 8, 12, 13, 14, 20, 23
 F32, BF16 = 0, 30
 
 

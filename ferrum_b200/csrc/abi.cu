@@ -514,6 +514,8 @@ static int validate_payload(fq_device *dev, int format, const uint8_t *p, size_t
                 return fq_fail(dev, FQ_ERR_WEIGHT, "%s scale must be finite (block %zu)", format == FQ_Q4_K ? "Q4_K" : "Q5_K", o / bb);
         } else if (format == FQ_Q6_K) {
             if (!finite(half_at(208))) return fq_fail(dev, FQ_ERR_WEIGHT, "Q6_K scale must be finite (block %zu)", o / bb);
+        } else if (format == FQ_IQ4_NL || format == FQ_IQ4_XS) {
+            if (!finite(half_at(0))) return fq_fail(dev, FQ_ERR_WEIGHT, "%s scale must be finite (block %zu)", format == FQ_IQ4_NL ? "IQ4_NL" : "IQ4_XS", o / bb);
         } else {
             const float s = half_at(0);
             if (!finite(s) || s < 0.0f) return fq_fail(dev, FQ_ERR_WEIGHT, "Q8_0 scale must be finite (block %zu)", o / bb);
@@ -534,6 +536,8 @@ extern "C" int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint6
     case FQ_Q5_K: el = 256; bb = 176; break;
     case FQ_Q6_K: el = 256; bb = 210; break;
     case FQ_Q8_0: el = 32; bb = 34; break;
+    case FQ_IQ4_NL: el = 32; bb = 18; break;
+    case FQ_IQ4_XS: el = 256; bb = 136; break;
     default: return fq_fail(dev, FQ_ERR_WEIGHT, "GGML type %d has no kernel", format);
     }
     if (!packed) return fq_fail(dev, FQ_ERR_PARAM, "null payload");

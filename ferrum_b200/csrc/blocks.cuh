@@ -6,6 +6,8 @@
 //   Q5_K  176 B / 256 values: f16 d @0, f16 dmin @2, scales[12] @4, qh[32] @16, qs[128] @48
 //   Q6_K  210 B / 256 values: ql[128] @0, qh[64] @128, int8 scales[16] @192, f16 d @208
 //   Q8_0   34 B /  32 values: f16 d @0, int8 qs[32] @2
+//   IQ4_NL 18 B /  32 values: f16 d @0, qs[16] @2 (byte j = values j and j + 16, indices into a 16-entry codebook)
+//   IQ4_XS 136 B / 256 values: f16 d @0, u16 scales_h @2, scales_l[4] @4, qs[128] @8 (`block_iq4_xs`, hybrid.metal:27)
 //
 // The decoders reproduce the CPU formulas the reference tests against
 // (src/diffusion/tests.rs:795-864, src/hybrid/draft/gguf.rs:336-343) as explicit round-to-nearest
@@ -23,6 +25,8 @@ template <> struct BlockTraits<FQ_Q4_K> { static constexpr int EL = 256, BB = 14
 template <> struct BlockTraits<FQ_Q5_K> { static constexpr int EL = 256, BB = 176; };
 template <> struct BlockTraits<FQ_Q6_K> { static constexpr int EL = 256, BB = 210; };
 template <> struct BlockTraits<FQ_Q8_0> { static constexpr int EL = 32, BB = 34; };
+template <> struct BlockTraits<FQ_IQ4_NL> { static constexpr int EL = 32, BB = 18; };
+template <> struct BlockTraits<FQ_IQ4_XS> { static constexpr int EL = 256, BB = 136; };
 
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t bits) {
     return __half2float(__ushort_as_half(bits));
@@ -63,6 +67,8 @@ __host__ __device__ inline uint32_t fq_row_pitch(int format, uint32_t cols) {
     case FQ_Q4_K: return cols / 256 * 144;
     case FQ_Q5_K: return cols / 256 * 176;
     case FQ_Q6_K: return (cols / 256 * 210 + 15u) & ~15u;
+    case FQ_IQ4_NL: return cols / 32 * 18;   // the GGUF bytes as they are (read a byte at a time)
+    case FQ_IQ4_XS: return cols / 256 * 136;
     default: return (cols / 32 * 34 + 15u) & ~15u;
     }
 }
@@ -101,6 +107,30 @@ template <> __device__ __forceinline__ float decode_at<FQ_Q6_K>(const uint8_t *r
     const uint32_t hi = (qh[32 * n + l] >> (2 * i)) & 3u;
     const int scale = (int)(int8_t)sc[8 * n + (l >> 4) + 2 * i];
     return q6k_value(load_f16(d), scale, nib | (hi << 4));
+}
+
+// The non-linear 4-bit codebook of the IQ4 formats (`kvalues_iq4nl_f`, hybrid.metal:34-37) as two 64-bit words of
+// signed bytes.
+__device__ __forceinline__ float iq4_value(uint32_t q) {
+    const uint64_t table = q < 8 ? 0xF6EADDCFBFAD9881ull : 0x7159453526190D01ull;
+    return (float)(int)(int8_t)(table >> (8 * (q & 7u)));
+}
+
+// IQ4_NL (`dequant_iq4_nl`, src/hybrid/iq_tests.rs:1606-1618): d * codebook[q], byte j = values j and j + 16.
+template <> __device__ __forceinline__ float decode_at<FQ_IQ4_NL>(const uint8_t *row, uint32_t, uint32_t b, int idx) {
+    const uint8_t *blk = row + (size_t)b * 18;
+    const uint8_t v = blk[2 + (idx & 15)];
+    return __fmul_rn(load_f16(blk), iq4_value(idx < 16 ? (v & 15u) : (v >> 4)));
+}
+
+// IQ4_XS (`dequantize_iq4_xs`, hybrid.metal:580-596): (d * (ls - 32)) * codebook[q] with the sub-block's 6-bit ls.
+template <> __device__ __forceinline__ float decode_at<FQ_IQ4_XS>(const uint8_t *row, uint32_t, uint32_t b, int idx) {
+    const uint8_t *blk = row + (size_t)b * 136;
+    const int ib = idx >> 5, l = idx & 31;
+    const uint32_t scales_h = blk[2] | ((uint32_t)blk[3] << 8);
+    const int ls = (int)((blk[4 + ib / 2] >> (4 * (ib % 2))) & 15u) | (int)(((scales_h >> (2 * ib)) & 3u) << 4);
+    const uint8_t v = blk[8 + 16 * ib + (l & 15)];
+    return __fmul_rn(__fmul_rn(load_f16(blk), (float)(ls - 32)), iq4_value(l < 16 ? (v & 15u) : (v >> 4)));
 }
 
 template <> __device__ __forceinline__ float decode_at<FQ_Q8_0>(const uint8_t *row, uint32_t nb, uint32_t b, int idx) {

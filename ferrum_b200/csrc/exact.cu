@@ -112,6 +112,8 @@ template <typename F> int dispatch_format(fq_device *dev, uint32_t format, F &&f
     case FQ_Q5_K: f(std::integral_constant<int, FQ_Q5_K>{}); return FQ_OK;
     case FQ_Q6_K: f(std::integral_constant<int, FQ_Q6_K>{}); return FQ_OK;
     case FQ_Q8_0: f(std::integral_constant<int, FQ_Q8_0>{}); return FQ_OK;
+    case FQ_IQ4_NL: f(std::integral_constant<int, FQ_IQ4_NL>{}); return FQ_OK;
+    case FQ_IQ4_XS: f(std::integral_constant<int, FQ_IQ4_XS>{}); return FQ_OK;
     default: return fq_fail(dev, FQ_ERR_UNSUPPORTED, "format %u has no kernel", format);
     }
 }

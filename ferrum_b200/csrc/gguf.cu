@@ -507,7 +507,7 @@ extern "C" int fq_matrix_from_gguf(fq_device *dev, fq_gguf *g, const char *name,
     }
     const bool q3k = q3k_as_q6k && t.type_id == 11;
     const uint32_t stored = q3k ? 14u : t.type_id;
-    if (stored != FQ_Q8_0 && stored != FQ_Q4_K && stored != FQ_Q5_K && stored != FQ_Q6_K)
+    if (stored != FQ_Q8_0 && stored != FQ_Q4_K && stored != FQ_Q5_K && stored != FQ_Q6_K && stored != FQ_IQ4_NL && stored != FQ_IQ4_XS)
         return fq_fail(dev, FQ_ERR_WEIGHT, "%s: GGML type %u has no kernel", name, t.type_id);
     uint32_t el = 0, by = 0;
     block_layout(t.type_id, el, by);

@@ -11,7 +11,7 @@ from typing import Tuple
 
 import numpy as np
 
-BLOCK = {8: (32, 34), 12: (256, 144), 14: (256, 210)}  # GGML type id -> (elements, bytes)
+BLOCK = {8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210), 20: (32, 18), 23: (256, 136)}  # GGML type id -> (elements, bytes)
 
 
 def shard_range(rows: int, rank: int, world: int) -> Tuple[int, int]:

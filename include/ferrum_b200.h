@@ -48,7 +48,7 @@ typedef enum fq_status {
 
 /* GGML type ids, as in `Format::from_type` (src/hybrid/weights.rs:47-66) and
  * `QuantizationFormat` (src/quantization.rs:24-73). */
-typedef enum fq_format { FQ_Q8_0 = 8, FQ_Q4_K = 12, FQ_Q5_K = 13, FQ_Q6_K = 14 } fq_format;
+typedef enum fq_format { FQ_Q8_0 = 8, FQ_Q4_K = 12, FQ_Q5_K = 13, FQ_Q6_K = 14, FQ_IQ4_NL = 20, FQ_IQ4_XS = 23 } fq_format;
 
 /* Activation / output element types (GGML ids of F32 and BF16). */
 typedef enum fq_dtype { FQ_F32 = 0, FQ_BF16 = 30 } fq_dtype;

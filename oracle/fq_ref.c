@@ -24,6 +24,8 @@
 #define FQO_Q3_K 11
 #define FQO_Q4_K 12
 #define FQO_Q5_K 13
+#define FQO_IQ4_NL 20
+#define FQO_IQ4_XS 23
 #define FQO_Q6_K 14
 
 /* ---------------------------------------------------------------- scalar conversions */
@@ -109,6 +111,8 @@ int fqo_block_layout(int format, int *elements, int *bytes) {
     case FQO_Q5_K: *elements = 256; *bytes = 176; return 0;
     case FQO_Q3_K: *elements = 256; *bytes = 110; return 0;
     case FQO_Q6_K: *elements = 256; *bytes = 210; return 0;
+    case FQO_IQ4_NL: *elements = 32; *bytes = 18; return 0;   /* src/loader/gguf.rs:110 */
+    case FQO_IQ4_XS: *elements = 256; *bytes = 136; return 0; /* src/loader/gguf.rs:111 */
     default: return -1;
     }
 }
@@ -128,6 +132,8 @@ int fqo_validate(int format, const uint8_t *p, size_t len) {
             if (!isfinite(f16_at(b, 0)) || !isfinite(f16_at(b, 2))) return 2;
         } else if (format == FQO_Q6_K) {
             if (!isfinite(f16_at(b, 208))) return 2;
+        } else if (format == FQO_IQ4_NL || format == FQO_IQ4_XS) {
+            if (!isfinite(f16_at(b, 0))) return 2; /* no check in the reference; the one scale of the block, as for Q4_0 */
         } else {
             float s = f16_at(b, 0);
             if (!isfinite(s) || s < 0.0f) return 2;
@@ -256,6 +262,37 @@ static void dequant_q6_k(const uint8_t *b, float *out) {
     }
 }
 
+/* The non-linear 4-bit codebook of the IQ4 formats (`kvalues_iq4nl`, src/hybrid/iq_tests.rs:1608-1610). */
+static const int8_t IQ4_VALUES[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+/* One IQ4_NL block (d f16, qs[16]): `dequant_iq4_nl`, src/hybrid/iq_tests.rs:1606-1618: byte j holds values j and
+ * j + 16. */
+static void dequant_iq4_nl(const uint8_t *b, float *out) {
+    float d = f16_at(b, 0);
+    for (int j = 0; j < 16; j++) {
+        out[j] = d * (float)IQ4_VALUES[b[2 + j] & 15];
+        out[j + 16] = d * (float)IQ4_VALUES[b[2 + j] >> 4];
+    }
+}
+
+/* One IQ4_XS block (d f16, scales_h u16, scales_l[4], qs[128]): `dequantize_iq4_xs`,
+ * src/metal/shaders/hybrid.metal:580-596: sub-block ib of 32 values has the 6-bit scale
+ * ls = (scales_l[ib / 2] >> 4 (ib % 2) & 15) | (scales_h >> 2 ib & 3) << 4 and the factor d (ls - 32); byte j of
+ * its 16 bytes holds values j and j + 16. */
+static void dequant_iq4_xs(const uint8_t *b, float *out) {
+    float d = f16_at(b, 0);
+    unsigned scales_h = (unsigned)b[2] | ((unsigned)b[3] << 8);
+    for (int ib = 0; ib < 8; ib++) {
+        int ls = (int)((b[4 + ib / 2] >> (4 * (ib % 2))) & 15) | (int)(((scales_h >> (2 * ib)) & 3) << 4);
+        float dl = d * (float)(ls - 32);
+        const uint8_t *q = b + 8 + 16 * ib;
+        for (int j = 0; j < 16; j++) {
+            out[32 * ib + j] = dl * (float)IQ4_VALUES[q[j] & 15];
+            out[32 * ib + j + 16] = dl * (float)IQ4_VALUES[q[j] >> 4];
+        }
+    }
+}
+
 /* One Q8_0 block: src/hybrid/draft/gguf.rs:336-343. */
 static void dequant_q8_0(const uint8_t *b, float *out) {
     float d = f16_at(b, 0);
@@ -273,6 +310,8 @@ int fqo_dequant(int format, const uint8_t *src, size_t blocks, float *out) {
         else if (format == FQO_Q5_K) dequant_q5_k(b, o);
         else if (format == FQO_Q3_K) dequant_q3_k(b, o);
         else if (format == FQO_Q6_K) dequant_q6_k(b, o);
+        else if (format == FQO_IQ4_NL) dequant_iq4_nl(b, o);
+        else if (format == FQO_IQ4_XS) dequant_iq4_xs(b, o);
         else dequant_q8_0(b, o);
     }
     return 0;

@@ -16,9 +16,9 @@ import subprocess
 
 import numpy as np
 
-Q8_0, Q3_K, Q4_K, Q5_K, Q6_K = 8, 11, 12, 13, 14
-LAYOUT = {Q8_0: (32, 34), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}  # format -> (elements, bytes)
-NAME = {Q8_0: "q8_0", Q3_K: "q3_k", Q4_K: "q4_k", Q5_K: "q5_k", Q6_K: "q6_k"}
+Q8_0, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS = 8, 11, 12, 13, 14, 20, 23
+LAYOUT = {Q8_0: (32, 34), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18), IQ4_XS: (256, 136)}  # format -> (elements, bytes)
+NAME = {Q8_0: "q8_0", Q3_K: "q3_k", Q4_K: "q4_k", Q5_K: "q5_k", Q6_K: "q6_k", IQ4_NL: "iq4_nl", IQ4_XS: "iq4_xs"}
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libfq_ref.so")
@@ -277,8 +277,39 @@ def random_blocks(fmt: int, blocks: int, seed: int = 0) -> np.ndarray:
         d = half()
         out[:, 0:2] = d.view(np.uint8).reshape(blocks, 2)
         out[:, 2:34] = rng.integers(-127, 128, size=(blocks, 32), dtype=np.int8).view(np.uint8)
+    elif fmt == IQ4_NL:  # d, then the nibbles
+        out[:, 0:2] = half().view(np.uint8).reshape(blocks, 2)
+        out[:, 2:18] = rng.integers(0, 256, size=(blocks, 16), dtype=np.uint8)
+    elif fmt == IQ4_XS:  # d, then scales_h | scales_l, then the nibbles
+        out[:, 0:2] = half().view(np.uint8).reshape(blocks, 2)
+        out[:, 2:8] = rng.integers(0, 256, size=(blocks, 6), dtype=np.uint8)
+        out[:, 8:136] = rng.integers(0, 256, size=(blocks, 128), dtype=np.uint8)
     else:
         raise ValueError(fmt)
+    return out.reshape(-1)
+
+
+IQ4_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.float32)
+
+
+def iq4_closed_form(fmt: int, packed: np.ndarray) -> np.ndarray:
+    """The IQ4 decoders written from the format definition with array operations, independently of the C loops
+    (IQ4_NL: src/hybrid/iq_tests.rs:1606-1618; IQ4_XS: src/metal/shaders/hybrid.metal:580-596)."""
+    el, bb = LAYOUT[fmt]
+    b = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1, bb)
+    d = b[:, 0:2].copy().view(np.float16).astype(np.float32)  # [blocks, 1]
+    if fmt == IQ4_NL:
+        q = b[:, 2:18]
+        vals = np.concatenate([IQ4_VALUES[q & 15], IQ4_VALUES[q >> 4]], axis=1)
+        return (d * vals).astype(np.float32).reshape(-1)
+    sh = b[:, 2].astype(np.uint32) | (b[:, 3].astype(np.uint32) << 8)
+    out = np.empty((b.shape[0], 256), dtype=np.float32)
+    for ib in range(8):
+        ls = ((b[:, 4 + ib // 2] >> (4 * (ib % 2))) & 15).astype(np.int32) | (((sh >> (2 * ib)) & 3) << 4).astype(np.int32)
+        dl = (d[:, 0] * (ls - 32).astype(np.float32)).astype(np.float32)[:, None]
+        q = b[:, 8 + 16 * ib:24 + 16 * ib]
+        out[:, 32 * ib:32 * ib + 16] = dl * IQ4_VALUES[q & 15]
+        out[:, 32 * ib + 16:32 * ib + 32] = dl * IQ4_VALUES[q >> 4]
     return out.reshape(-1)
 
 

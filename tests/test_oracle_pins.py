@@ -177,3 +177,31 @@ def test_threaded_gemv_agrees_with_the_parity_oracle():
         want = ref.matmul(fmt, packed, 37, 512, x, 3, mode=0)
         got = ref.gemv_threads(fmt, packed, 37, 512, x, 3, threads=3)
         assert ref.rel_err(got, want) < 1e-5
+
+
+@pytest.mark.parametrize("fmt", [ref.IQ4_NL, ref.IQ4_XS])
+def test_iq4_decoders_match_the_format_definition(fmt):
+    """IQ4_NL (`dequant_iq4_nl`, src/hybrid/iq_tests.rs:1606-1618) and IQ4_XS (`dequantize_iq4_xs`,
+    src/metal/shaders/hybrid.metal:580-596): the C block loops against an array restatement, bit for bit, on
+    random blocks and on a block that walks the codebook and every 6-bit scale."""
+    packed = ref.random_blocks(fmt, 64, seed=5)
+    assert np.array_equal(ref.dequant(fmt, packed).view(np.uint32), ref.iq4_closed_form(fmt, packed).view(np.uint32))
+    el, bb = ref.LAYOUT[fmt]
+    if fmt == ref.IQ4_NL:
+        blk = np.zeros(bb, dtype=np.uint8)
+        blk[0:2] = np.array([0.5], dtype=np.float16).view(np.uint8)
+        blk[2:18] = np.arange(16, dtype=np.uint8) | (np.arange(15, -1, -1, dtype=np.uint8) << 4)
+        got = ref.dequant(fmt, blk)
+        assert np.array_equal(got[:16], 0.5 * ref.IQ4_VALUES) and np.array_equal(got[16:], 0.5 * ref.IQ4_VALUES[::-1])
+    else:
+        blk = np.zeros(bb, dtype=np.uint8)
+        blk[0:2] = np.array([0.25], dtype=np.float16).view(np.uint8)
+        ls = np.array([0, 63, 32, 33, 17, 48, 5, 60])  # sub-block scales
+        blk[2:4] = np.array([sum(int(v >> 4) << (2 * i) for i, v in enumerate(ls))], dtype=np.uint16).view(np.uint8)
+        for i in range(4):
+            blk[4 + i] = (ls[2 * i] & 15) | ((ls[2 * i + 1] & 15) << 4)
+        blk[8:136] = np.tile(np.arange(16, dtype=np.uint8) | (np.arange(15, -1, -1, dtype=np.uint8) << 4), 8)
+        got = ref.dequant(fmt, blk).reshape(8, 32)
+        for ib in range(8):
+            want = np.float32(0.25) * np.float32(ls[ib] - 32)
+            assert np.array_equal(got[ib, :16], want * ref.IQ4_VALUES) and np.array_equal(got[ib, 16:], want * ref.IQ4_VALUES[::-1])
