@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libferrum_b200.so")
-SOURCES = ["abi.cu", "exact.cu", "gemv_i8.cu", "gemv_nt.cu", "gemv_q8.cu", "gemm.cu", "moe.cu", "comm.cu", "gguf.cu", "norm.cu"]
+SOURCES = ["abi.cu", "exact.cu", "gemv_i8.cu", "gemv_nt.cu", "gemv_q8.cu", "gemv_iq4.cu", "gemm.cu", "moe.cu", "comm.cu", "gguf.cu", "norm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-Wall,-Wno-unknown-pragmas",

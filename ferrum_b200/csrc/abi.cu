@@ -589,6 +589,19 @@ extern "C" int fq_matrix_create(fq_device *dev, int format, uint64_t rows, uint6
             }
         }
         upload = regrouped.data();
+    } else if (format == FQ_IQ4_NL || format == FQ_IQ4_XS) {
+        // nibbles of all blocks first, then the rest of each block (IQ4_NL: d; IQ4_XS: d | scales_h | scales_l)
+        regrouped.assign(dev_len, 0);
+        const size_t nb = cols / el, qb = el / 2, hb = bb - qb;
+        for (size_t r = 0; r < w->rows; r++) {
+            const uint8_t *src = (const uint8_t *)packed + r * row_bytes;
+            uint8_t *dst = regrouped.data() + r * w->pitch;
+            for (size_t b = 0; b < nb; b++, src += bb) {
+                memcpy(dst + qb * nb + hb * b, src, hb);
+                memcpy(dst + qb * b, src + hb, qb);
+            }
+        }
+        upload = regrouped.data();
     }
     // 256 spare bytes let kernels read whole 16-byte words around the last block.
     cudaError_t e = cudaMalloc((void **)&w->data, dev_len + 256);
@@ -651,6 +664,10 @@ static int check_dtype(fq_device *dev, int dt) {
 static int launch_decode(fq_device *dev, const ProjectArgs *a, uint32_t count) {
     if (count == 1 && a[0].format == FQ_Q8_0) {
         int rc = fq_launch_gemv_q8(dev, a[0]);
+        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (count == 1 && a[0].m == 1 && (a[0].format == FQ_IQ4_NL || a[0].format == FQ_IQ4_XS)) { // more rows: the exact kernel measured faster
+        int rc = fq_launch_gemv_iq4(dev, a[0]);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
     if (a[0].m == 1 || a[0].ids) return fq_launch_gemv_i8_many(dev, a, count);

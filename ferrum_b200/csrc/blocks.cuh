@@ -8,6 +8,8 @@
 //   Q8_0   34 B /  32 values: f16 d @0, int8 qs[32] @2
 //   IQ4_NL 18 B /  32 values: f16 d @0, qs[16] @2 (byte j = values j and j + 16, indices into a 16-entry codebook)
 //   IQ4_XS 136 B / 256 values: f16 d @0, u16 scales_h @2, scales_l[4] @4, qs[128] @8 (`block_iq4_xs`, hybrid.metal:27)
+// On the device Q6_K, Q8_0 and the IQ4 formats are regrouped by field per row (see each decoder), so that the
+// quants can be read with aligned 16-byte loads.
 //
 // The decoders reproduce the CPU formulas the reference tests against
 // (src/diffusion/tests.rs:795-864, src/hybrid/draft/gguf.rs:336-343) as explicit round-to-nearest
@@ -67,8 +69,8 @@ __host__ __device__ inline uint32_t fq_row_pitch(int format, uint32_t cols) {
     case FQ_Q4_K: return cols / 256 * 144;
     case FQ_Q5_K: return cols / 256 * 176;
     case FQ_Q6_K: return (cols / 256 * 210 + 15u) & ~15u;
-    case FQ_IQ4_NL: return cols / 32 * 18;   // the GGUF bytes as they are (read a byte at a time)
-    case FQ_IQ4_XS: return cols / 256 * 136;
+    case FQ_IQ4_NL: return (cols / 32 * 18 + 15u) & ~15u;
+    case FQ_IQ4_XS: return (cols / 256 * 136 + 15u) & ~15u;
     default: return (cols / 32 * 34 + 15u) & ~15u;
     }
 }
@@ -117,20 +119,23 @@ __device__ __forceinline__ float iq4_value(uint32_t q) {
 }
 
 // IQ4_NL (`dequant_iq4_nl`, src/hybrid/iq_tests.rs:1606-1618): d * codebook[q], byte j = values j and j + 16.
-template <> __device__ __forceinline__ float decode_at<FQ_IQ4_NL>(const uint8_t *row, uint32_t, uint32_t b, int idx) {
-    const uint8_t *blk = row + (size_t)b * 18;
-    const uint8_t v = blk[2 + (idx & 15)];
-    return __fmul_rn(load_f16(blk), iq4_value(idx < 16 ? (v & 15u) : (v >> 4)));
+// Device layout of a row: the nibbles of all blocks (16 bytes each), then the f16 scales.
+template <> __device__ __forceinline__ float decode_at<FQ_IQ4_NL>(const uint8_t *row, uint32_t nb, uint32_t b, int idx) {
+    const uint8_t v = row[(size_t)b * 16 + (idx & 15)];
+    return __fmul_rn(load_f16(row + (size_t)nb * 16 + (size_t)b * 2), iq4_value(idx < 16 ? (v & 15u) : (v >> 4)));
 }
 
 // IQ4_XS (`dequantize_iq4_xs`, hybrid.metal:580-596): (d * (ls - 32)) * codebook[q] with the sub-block's 6-bit ls.
-template <> __device__ __forceinline__ float decode_at<FQ_IQ4_XS>(const uint8_t *row, uint32_t, uint32_t b, int idx) {
-    const uint8_t *blk = row + (size_t)b * 136;
+// Device layout of a row: the nibbles of all blocks (128 bytes each), then the 8-byte headers d | scales_h | scales_l.
+__device__ __forceinline__ int iq4xs_scale(const uint8_t *hdr, int ib) {
+    const uint32_t scales_h = hdr[2] | ((uint32_t)hdr[3] << 8);
+    return ((int)((hdr[4 + ib / 2] >> (4 * (ib % 2))) & 15u) | (int)(((scales_h >> (2 * ib)) & 3u) << 4)) - 32;
+}
+template <> __device__ __forceinline__ float decode_at<FQ_IQ4_XS>(const uint8_t *row, uint32_t nb, uint32_t b, int idx) {
+    const uint8_t *hdr = row + (size_t)nb * 128 + (size_t)b * 8;
     const int ib = idx >> 5, l = idx & 31;
-    const uint32_t scales_h = blk[2] | ((uint32_t)blk[3] << 8);
-    const int ls = (int)((blk[4 + ib / 2] >> (4 * (ib % 2))) & 15u) | (int)(((scales_h >> (2 * ib)) & 3u) << 4);
-    const uint8_t v = blk[8 + 16 * ib + (l & 15)];
-    return __fmul_rn(__fmul_rn(load_f16(blk), (float)(ls - 32)), iq4_value(l < 16 ? (v & 15u) : (v >> 4)));
+    const uint8_t v = row[(size_t)b * 128 + 16 * ib + (l & 15)];
+    return __fmul_rn(__fmul_rn(load_f16(hdr), (float)iq4xs_scale(hdr, ib)), iq4_value(l < 16 ? (v & 15u) : (v >> 4)));
 }
 
 template <> __device__ __forceinline__ float decode_at<FQ_Q8_0>(const uint8_t *row, uint32_t nb, uint32_t b, int idx) {

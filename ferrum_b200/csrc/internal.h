@@ -139,6 +139,7 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
 int fq_launch_gemv_nt_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
 // Grouped expert projection over expert-sorted rows (a[i].offsets / slots / groups) for one or two expert stacks
 // of one shape (F32 in and out); row r of the sorted set is row src[r] / src_div of x (src null: row r).
+int fq_launch_gemv_iq4(fq_device *dev, const ProjectArgs &a);
 int fq_launch_gemv_nt_grouped(fq_device *dev, const ProjectArgs *a, uint32_t count, uint32_t total_rows, const uint32_t *src, uint32_t src_div);
 // tcgen05 dequant-GEMM (BF16 in/out); same fallback contract.
 // Q8_0 integer-dot GEMV (M <= FQ_GEMV_MAX_M, F32 in/out, no routes); FQ_ERR_UNSUPPORTED otherwise.
