@@ -68,59 +68,76 @@ k_gemv_iq4(const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t
     }
     __syncthreads();
 
-    // 2. Rows.  A warp takes one weight row at a time, strided over the grid; lane l reads 16 bytes = one run of 32
-    // values (an IQ4_NL block, an IQ4_XS sub-block) of every 1024-value chunk.
-    const uint32_t chunks = (cols + 1023) / 1024;
-    for (uint32_t row = blockIdx.x * WARPS + warp; row < rows; row += gridDim.x * WARPS) {
-        const uint8_t *rp = w + (size_t)row * pitch, *hdr = rp + cols / 2;
-        float acc[MT];
+    // 2. Rows.  A warp takes RPW weight rows at a time, strided over the grid, the loads of all of them in flight
+    // together; lane l reads 16 bytes = one run of 32 values (an IQ4_NL block, an IQ4_XS sub-block) of every
+    // 1024-value chunk.
+    constexpr int RPW = 4;
+    const uint32_t chunks = (cols + 1023) / 1024, groups = (rows + RPW - 1) / RPW;
+    for (uint32_t g = blockIdx.x * WARPS + warp; g < groups; g += gridDim.x * WARPS) {
+        const uint32_t row0 = g * RPW;
+        const uint8_t *rp[RPW];
 #pragma unroll
-        for (int t = 0; t < MT; t++) acc[t] = 0.f;
-#pragma unroll 2
+        for (int r = 0; r < RPW; r++) rp[r] = w + (size_t)min(row0 + r, rows - 1) * pitch;
+        float acc[RPW][MT];
+#pragma unroll
+        for (int r = 0; r < RPW; r++)
+#pragma unroll
+            for (int t = 0; t < MT; t++) acc[r][t] = 0.f;
         for (uint32_t c = 0; c < chunks; c++) {
             const uint32_t run = 32 * c + lane; // index of the 32-value run
             const bool live = run < nb32;
             const uint32_t rr = live ? run : 0;
-            const uint4 q = fqk::ldw128(rp + (size_t)rr * 16);
-            float d;
-            if constexpr (FMT == FQ_IQ4_XS) {
-                const uint8_t *h8 = hdr + (size_t)(rr / 8) * 8;
-                d = load_f16(h8) * (float)iq4xs_scale(h8, (int)(rr % 8));
-            } else {
-                d = load_f16(hdr + (size_t)rr * 2);
-            }
-            // byte pairs of nibbles -> four signed bytes each, in the order the activations were laid down
-            const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-            uint32_t vl[4], vh[4]; // pairs 2 i and 2 i + 1
+            uint4 q[RPW];
+            float d[RPW];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                vl[i] = iq4_lookup4(qw[i]);
-                vh[i] = iq4_lookup4(qw[i] >> 16);
+            for (int r = 0; r < RPW; r++) q[r] = fqk::ldw128(rp[r] + (size_t)rr * 16);
+#pragma unroll
+            for (int r = 0; r < RPW; r++) {
+                const uint8_t *hdr = rp[r] + cols / 2;
+                if constexpr (FMT == FQ_IQ4_XS) {
+                    const uint8_t *h8 = hdr + (size_t)(rr / 8) * 8;
+                    d[r] = load_f16(h8) * (float)iq4xs_scale(h8, (int)(rr % 8));
+                } else {
+                    d[r] = load_f16(hdr + (size_t)rr * 2);
+                }
             }
+#pragma unroll
+            for (int r = 0; r < RPW; r++) {
+                // byte pairs of nibbles -> four signed bytes each, in the order the activations were laid down
+                const uint32_t qw[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
+                uint32_t vl[4], vh[4]; // pairs 2 i and 2 i + 1
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    vl[i] = iq4_lookup4(qw[i]);
+                    vh[i] = iq4_lookup4(qw[i] >> 16);
+                }
+#pragma unroll
+                for (int t = 0; t < MT; t++) {
+                    const int4 *xh = reinterpret_cast<const int4 *>(hi + (size_t)t * cols + (size_t)rr * 32);
+                    const int4 *xl = reinterpret_cast<const int4 *>(lo + (size_t)t * cols + (size_t)rr * 32);
+                    const int4 h0 = xh[0], h1 = xh[1], l0 = xl[0], l1 = xl[1];
+                    int dh = __dp4a((int)vl[0], h0.x, 0), dl = __dp4a((int)vl[0], l0.x, 0);
+                    dh = __dp4a((int)vh[0], h0.y, dh), dl = __dp4a((int)vh[0], l0.y, dl);
+                    dh = __dp4a((int)vl[1], h0.z, dh), dl = __dp4a((int)vl[1], l0.z, dl);
+                    dh = __dp4a((int)vh[1], h0.w, dh), dl = __dp4a((int)vh[1], l0.w, dl);
+                    dh = __dp4a((int)vl[2], h1.x, dh), dl = __dp4a((int)vl[2], l1.x, dl);
+                    dh = __dp4a((int)vh[2], h1.y, dh), dl = __dp4a((int)vh[2], l1.y, dl);
+                    dh = __dp4a((int)vl[3], h1.z, dh), dl = __dp4a((int)vl[3], l1.z, dl);
+                    dh = __dp4a((int)vh[3], h1.w, dh), dl = __dp4a((int)vh[3], l1.w, dl);
+                    const float s = live ? isc[t * nb32 + rr] : 0.f; // lanes past the row's end contribute nothing
+                    acc[r][t] = fmaf((float)(dh * 256 + dl), d[r] * s, acc[r][t]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; r++)
 #pragma unroll
             for (int t = 0; t < MT; t++) {
-                const int4 *xh = reinterpret_cast<const int4 *>(hi + (size_t)t * cols + (size_t)rr * 32);
-                const int4 *xl = reinterpret_cast<const int4 *>(lo + (size_t)t * cols + (size_t)rr * 32);
-                const int4 h0 = xh[0], h1 = xh[1], l0 = xl[0], l1 = xl[1];
-                int dh = __dp4a((int)vl[0], h0.x, 0), dl = __dp4a((int)vl[0], l0.x, 0);
-                dh = __dp4a((int)vh[0], h0.y, dh), dl = __dp4a((int)vh[0], l0.y, dl);
-                dh = __dp4a((int)vl[1], h0.z, dh), dl = __dp4a((int)vl[1], l0.z, dl);
-                dh = __dp4a((int)vh[1], h0.w, dh), dl = __dp4a((int)vh[1], l0.w, dl);
-                dh = __dp4a((int)vl[2], h1.x, dh), dl = __dp4a((int)vl[2], l1.x, dl);
-                dh = __dp4a((int)vh[2], h1.y, dh), dl = __dp4a((int)vh[2], l1.y, dl);
-                dh = __dp4a((int)vl[3], h1.z, dh), dl = __dp4a((int)vl[3], l1.z, dl);
-                dh = __dp4a((int)vh[3], h1.w, dh), dl = __dp4a((int)vh[3], l1.w, dl);
-                const float s = live ? isc[t * nb32 + rr] : 0.f; // lanes past the row's end contribute nothing
-                acc[t] = fmaf((float)(dh * 256 + dl), d * s, acc[t]);
+                float v = acc[r][t];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                if (lane == 0 && row0 + r < rows) y[(size_t)t * rows + row0 + r] = v;
             }
-        }
-#pragma unroll
-        for (int t = 0; t < MT; t++) {
-            float v = acc[t];
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-            if (lane == 0) y[(size_t)t * rows + row] = v;
-        }
     }
 }
 
@@ -133,7 +150,7 @@ template <int FMT, int MT> cudaError_t launch(fq_device *dev, const ProjectArgs 
         if (e != cudaSuccess) return e;
         configured = most;
     }
-    const uint32_t need = (a.rows + WARPS - 1) / WARPS;
+    const uint32_t need = (a.rows + WARPS * 4 - 1) / (WARPS * 4);
     const uint32_t grid = std::min<uint32_t>(need, (uint32_t)dev->sm_count * 4);
     return fqk::launch_pdl(k_gemv_iq4<FMT, MT>, dim3(grid), dim3(WARPS * 32), smem, dev->stream, a.w, a.rows, a.cols, a.row_bytes, x, y);
 }
