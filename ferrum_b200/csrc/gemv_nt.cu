@@ -16,17 +16,19 @@
 // The result is the exact dot product of the decoded weights with activations rounded to 16 bits relative to the
 // largest magnitude of their superblock, as in gemv_i8.cu.
 //
-// Organisation: a block keeps the prepared activations of ONE K slice (dense) or of one tile of sixteen
-// expert-sorted rows (grouped) resident in shared memory -- it quantises them itself from x, so there is no
-// preparation launch -- and its warps each take 16-row weight tiles against them.  A warp streams the packed
-// superblocks of its tiles through a private ring in shared memory with 16-byte asynchronous copies (several
-// superblocks in flight per warp, no registers held, no block-wide barrier in the main loop; the ring runs on
-// across tile borders) and reads MMA fragments from there: thread (g = lane / 4, t = lane % 4) owns weight rows
-// g, g + 8 and, since the k order inside a scale group is free, the bytes 8t.. (Q4_K) or 4t.. (Q6_K) of each run,
-// so that shared-memory reads are conflict-free, and the activations are stored in exactly the order the B
-// fragments want (16 bytes per thread and 32 values).  K is cut into as many slices as it takes for a slice of
-// activations to fit and for every SM to get its share of warps; with more than one slice the partial sums go
-// to a workspace and the last warp to arrive at a tile adds them in slice order (deterministic).
+// Organisation: the activations are prepared once per projection by k_prep_nt (16-bit integers in the order the
+// B fragments are read; optionally the row's rmsnorm, the gated unit of two inputs, or only the rows of the
+// experts a rank owns).  A block keeps the prepared activations of ONE K slice (dense) or of one tile of up to 32
+// expert-sorted rows (grouped: rows picked by index, so the expert-major gather costs nothing) resident in shared
+// memory, copied there asynchronously, and its warps each take 16-row weight tiles against them.  A warp streams
+// the packed superblocks of its tiles through a private ring in shared memory with 16-byte asynchronous copies
+// (several superblocks in flight per warp, no registers held, no block-wide barrier in the main loop; the ring
+// runs on across tile borders) and reads MMA fragments from there: thread (g = lane / 4, t = lane % 4) owns
+// weight rows g, g + 8 and, since the k order inside a scale group is free, the bytes 8t.. (Q4_K) or 4t.. (Q6_K)
+// of each run, so that shared-memory reads are conflict-free.  Dense launches cut K into as many slices as it
+// takes for a slice of activations to fit and for every SM to get its share of warps; with more than one slice
+// the partial sums go to a workspace and the last warp to arrive at a tile adds them in slice order
+// (deterministic).  A grouped block runs the tile loop for 8, 16 or 32 live rows, chosen by the rows its tile holds.
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
