@@ -47,7 +47,9 @@ typedef enum fq_status {
 } fq_status;
 
 /* GGML type ids, as in `Format::from_type` (src/hybrid/weights.rs:47-66) and
- * `QuantizationFormat` (src/quantization.rs:24-73). */
+ * `QuantizationFormat` (src/quantization.rs:24-73).  Q8_0, Q4_K, Q5_K and Q6_K have kernels at every width.
+ * IQ4_NL and IQ4_XS decode exactly everywhere (embedding lookup, every projection entry point) but have a tuned
+ * kernel only for one activation row; at other widths they run on the exact fp32 kernels. */
 typedef enum fq_format { FQ_Q8_0 = 8, FQ_Q4_K = 12, FQ_Q5_K = 13, FQ_Q6_K = 14, FQ_IQ4_NL = 20, FQ_IQ4_XS = 23 } fq_format;
 
 /* Activation / output element types (GGML ids of F32 and BF16). */
