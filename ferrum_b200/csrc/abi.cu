@@ -666,7 +666,7 @@ static int launch_decode(fq_device *dev, const ProjectArgs *a, uint32_t count) {
         int rc = fq_launch_gemv_q8(dev, a[0]);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
-    if (count == 1 && a[0].m == 1 && (a[0].format == FQ_IQ4_NL || a[0].format == FQ_IQ4_XS)) { // more rows: the exact kernel measured faster
+    if (count == 1 && (a[0].m == 1 || a[0].ids) && (a[0].format == FQ_IQ4_NL || a[0].format == FQ_IQ4_XS)) { // dense with more rows: the exact kernel measured faster
         int rc = fq_launch_gemv_iq4(dev, a[0]);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }

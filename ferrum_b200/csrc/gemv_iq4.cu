@@ -34,13 +34,22 @@ __device__ __forceinline__ uint32_t iq4_lookup4(uint32_t n) {
 template <int FMT, int MT>
 __global__ void __launch_bounds__(WARPS * 32)
 k_gemv_iq4(const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t pitch, const float *__restrict__ x,
-           float *__restrict__ y) {
+           float *__restrict__ y, const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts) {
     extern __shared__ __align__(16) uint8_t iq4_smem[];
     int8_t *hi = reinterpret_cast<int8_t *>(iq4_smem), *lo = hi + (size_t)MT * cols;
     float *isc = reinterpret_cast<float *>(lo + (size_t)MT * cols);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nb32 = cols / 32;
     fqk::pdl_trigger();
-    fqk::pdl_wait(); // x may be the output of the kernel before this one
+    fqk::pdl_wait(); // x (and the routing) may be the output of the kernel before this one
+    if (ids) {
+        // Routes (`project_id`, MT = 1): route blockIdx.y uses expert ids[route] (`rows` rows each), activation row
+        // route / x_div, output row route.
+        const uint32_t r = blockIdx.y, e = ids[r];
+        if (e >= experts) return;
+        w += (size_t)e * rows * pitch;
+        x += (size_t)(r / x_div) * cols;
+        y += (size_t)r * rows;
+    }
 
     // 1. Activations -> 16-bit integers, one warp per (activation row, block of 32), lane = value (as in gemv_q8.cu).
     for (uint32_t i = warp; i < MT * nb32; i += WARPS) {
@@ -141,7 +150,7 @@ k_gemv_iq4(const uint8_t *__restrict__ w, uint32_t rows, uint32_t cols, uint32_t
     }
 }
 
-template <int FMT, int MT> cudaError_t launch(fq_device *dev, const ProjectArgs &a, const float *x, float *y) {
+template <int FMT, int MT> cudaError_t launch(fq_device *dev, const ProjectArgs &a, const float *x, float *y, uint32_t routes = 0) {
     const size_t smem = (size_t)2 * MT * a.cols + (size_t)MT * (a.cols / 32) * sizeof(float);
     static size_t configured = 48 * 1024;
     if (smem > configured) {
@@ -152,7 +161,8 @@ template <int FMT, int MT> cudaError_t launch(fq_device *dev, const ProjectArgs 
     }
     const uint32_t need = (a.rows + WARPS * 4 - 1) / (WARPS * 4);
     const uint32_t grid = std::min<uint32_t>(need, (uint32_t)dev->sm_count * 4);
-    return fqk::launch_pdl(k_gemv_iq4<FMT, MT>, dim3(grid), dim3(WARPS * 32), smem, dev->stream, a.w, a.rows, a.cols, a.row_bytes, x, y);
+    return fqk::launch_pdl(k_gemv_iq4<FMT, MT>, dim3(grid, routes ? routes : 1), dim3(WARPS * 32), smem, dev->stream, a.w, a.rows, a.cols, a.row_bytes, x, y,
+                           routes ? a.ids : (const uint32_t *)nullptr, routes ? a.x_div : 1u, a.experts);
 }
 
 template <int FMT> cudaError_t launch_m(fq_device *dev, const ProjectArgs &a, const float *x, float *y, uint32_t mt) {
@@ -166,11 +176,20 @@ template <int FMT> cudaError_t launch_m(fq_device *dev, const ProjectArgs &a, co
 
 } // namespace
 
-// IQ4_NL / IQ4_XS, F32 in / F32 out, up to FQ_GEMV_MAX_M activation rows (four per launch); FQ_ERR_UNSUPPORTED otherwise.
+// IQ4_NL / IQ4_XS, F32 in / F32 out: up to FQ_GEMV_MAX_M activation rows (four per launch), or routes (`a.ids`: one
+// activation row per route, `a.m` routes, `a.rows` rows per expert); FQ_ERR_UNSUPPORTED otherwise.
 int fq_launch_gemv_iq4(fq_device *dev, const ProjectArgs &a) {
-    if ((a.format != FQ_IQ4_NL && a.format != FQ_IQ4_XS) || a.x_dtype != FQ_F32 || a.y_dtype != FQ_F32 || a.ids || a.offsets || a.norm_w || a.x_up)
+    if ((a.format != FQ_IQ4_NL && a.format != FQ_IQ4_XS) || a.x_dtype != FQ_F32 || a.y_dtype != FQ_F32 || a.offsets || a.norm_w || a.x_up)
         return FQ_ERR_UNSUPPORTED;
-    if (a.m == 0 || a.m > (uint32_t)FQ_GEMV_MAX_M || a.cols > MAX_COLS_IQ4 || a.cols % 256 || a.row_bytes % 16) return FQ_ERR_UNSUPPORTED;
+    if (a.m == 0 || a.cols > MAX_COLS_IQ4 || a.cols % 256 || a.row_bytes % 16) return FQ_ERR_UNSUPPORTED;
+    if (a.ids) {
+        if (a.m > 65535 || a.x_div == 0) return FQ_ERR_UNSUPPORTED;
+        const cudaError_t e = a.format == FQ_IQ4_XS ? launch<FQ_IQ4_XS, 1>(dev, a, (const float *)a.x, (float *)a.y, a.m)
+                                                    : launch<FQ_IQ4_NL, 1>(dev, a, (const float *)a.x, (float *)a.y, a.m);
+        if (int rc = fq_check_cuda(dev, e, "gemv_iq4 launch")) return rc;
+        return fq_end_enqueue(dev, "gemv_iq4", 1);
+    }
+    if (a.m > (uint32_t)FQ_GEMV_MAX_M) return FQ_ERR_UNSUPPORTED;
     int launches = 0;
     for (uint32_t m0 = 0; m0 < a.m; m0 += 4, launches++) {
         const uint32_t mt = a.m - m0 < 4 ? a.m - m0 : 4;

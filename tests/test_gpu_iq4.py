@@ -94,3 +94,41 @@ def test_non_finite_scale_is_refused(device, fmt):
     packed[0:2] = np.array([np.inf], dtype=np.float16).view(np.uint8)
     with pytest.raises(s.WeightError):
         s.Matrix.from_packed(device, 4, 256, 1, fmt, packed)
+
+
+def _dense_ffn(fmt, g, u, d, x, m, hidden, ef):
+    gg = ref.matmul(fmt, g, ef, hidden, x, m)
+    uu = ref.matmul(fmt, u, ef, hidden, x, m)
+    return ref.matmul(fmt, d, hidden, ef, ref.swiglu(gg, uu), m)
+
+
+@pytest.mark.parametrize("m", [2, 40])
+def test_moe_block_with_iq4_xs_experts(device, m):
+    """`moe_ffn` with every expert matrix in IQ4_XS (the encoding of the validated 35B-A3B file's experts): the
+    per-route path (m * used <= 32) and the expert-sorted path against the oracle composition."""
+    s = S()
+    fmt = ref.IQ4_XS
+    experts, used, hidden, ef = 16, 4, 512, 256
+    rng = np.random.default_rng(m)
+    router = ref.random_matrix(ref.Q8_0, experts, hidden, 10)
+    gate_e, up_e = ref.random_matrix(fmt, experts * ef, hidden, 11), ref.random_matrix(fmt, experts * ef, hidden, 12)
+    down_e = ref.random_matrix(fmt, experts * hidden, ef, 13)
+    sg, su, sd = ref.random_matrix(fmt, ef, hidden, 14), ref.random_matrix(fmt, ef, hidden, 15), ref.random_matrix(fmt, hidden, ef, 16)
+    x = (rng.standard_normal((m, hidden)) * 0.12).astype(np.float32)
+    M = s.Matrix.from_packed
+    f = s.MoeFfn(M(device, experts, hidden, 1, ref.Q8_0, router), M(device, ef, hidden, experts, fmt, gate_e),
+                 M(device, ef, hidden, experts, fmt, up_e), M(device, hidden, ef, experts, fmt, down_e),
+                 M(device, ef, hidden, 1, fmt, sg), M(device, ef, hidden, 1, fmt, su), M(device, hidden, ef, 1, fmt, sd),
+                 None, experts, used, hidden, ef, ef, False, True)
+    scratch = torch.zeros(s.moe_ffn_scratch_elems(device, f, m), dtype=torch.float32, device="cuda")
+    out = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")
+    s.moe_ffn(device, f, dev_f32(x), m, scratch, out)
+    device.synchronize()
+    logits = ref.matmul(ref.Q8_0, router, experts, hidden, x, m)
+    ids, wts, gate = ref.moe_route(logits, x, x[0], experts, used, hidden, m, False, True, False)
+    shared = _dense_ffn(fmt, sg, su, sd, x, m, hidden, ef)
+    g = ref.matmul_id(fmt, gate_e, ef, hidden, x, ids, used)
+    u = ref.matmul_id(fmt, up_e, ef, hidden, x, ids, used)
+    dn = ref.matmul_id(fmt, down_e, hidden, ef, ref.swiglu(g, u), ids, 1)
+    want = ref.moe_combine(dn, wts, ids, shared, gate, hidden, used, m, identity=True)
+    assert ref.rel_err(host(out).reshape(m, hidden), want) <= 3 * TOL_F32
