@@ -220,7 +220,38 @@ int fq_check_no_alias(fq_device *dev, const void *out, size_t out_bytes, const v
     const uintptr_t o = (uintptr_t)out, i = (uintptr_t)in;
     if (!out || !in) return FQ_OK;
     if (o < i + in_bytes && i < o + out_bytes) return fq_fail(dev, FQ_ERR_ALIAS, "%s: output overlaps an input", name);
+    // What a failed submission wrote is not an input until it has been written again.  Only buffers the handle
+    // allocated itself are tracked (`fq_buffer_alloc`, the counterpart of the reference's device buffers): memory the
+    // caller owns is recycled and rewritten by the caller's allocator without the library seeing it.
+    for (const auto &f : dev->failed_writes)
+        if (i < f.second && f.first < i + in_bytes) return fq_fail(dev, FQ_ERR_SYNC, "%s: input range belongs to a failed submission", name);
+    fq_note_write(dev, out, out_bytes);
     return FQ_OK;
+}
+
+void fq_note_write(fq_device *dev, const void *out, size_t bytes) {
+    if (dev->capturing || dev->allocations.empty()) return;
+    const uintptr_t o = (uintptr_t)out;
+    auto it = dev->allocations.upper_bound(o);
+    if (it == dev->allocations.begin()) return;
+    --it;
+    if (o >= it->first + it->second) return; // not inside a buffer of the handle
+    if ((dev->pending_writes.empty() || dev->pending_writes.back() != std::make_pair(o, o + bytes)) && dev->pending_writes.size() < 4096)
+        dev->pending_writes.emplace_back(o, o + bytes);
+}
+
+// A completion point: a failed one poisons what the submission wrote; a good one clears what it rewrote.
+static void settle_writes(fq_device *dev, bool ok) {
+    if (ok) {
+        for (const auto &w : dev->pending_writes)
+            dev->failed_writes.erase(std::remove_if(dev->failed_writes.begin(), dev->failed_writes.end(),
+                                                    [&](const std::pair<uintptr_t, uintptr_t> &f) { return w.first <= f.first && f.second <= w.second; }),
+                                     dev->failed_writes.end());
+    } else {
+        dev->failed_writes.insert(dev->failed_writes.end(), dev->pending_writes.begin(), dev->pending_writes.end());
+        if (dev->failed_writes.size() > 8192) dev->failed_writes.erase(dev->failed_writes.begin(), dev->failed_writes.begin() + 4096);
+    }
+    dev->pending_writes.clear();
 }
 
 // ------------------------------------------------------------------ device
@@ -329,20 +360,24 @@ extern "C" int fq_synchronize(fq_device *dev) {
     if (dev->fail_completion) {
         dev->fail_completion = false;
         dev->failed = true;
+        settle_writes(dev, false);
         return fq_fail(dev, FQ_ERR_SYNC, "injected completion failure");
     }
     if (e != cudaSuccess) {
         dev->failed = true;
+        settle_writes(dev, false);
         return fq_fail(dev, FQ_ERR_SYNC, "stream failed: %s", cudaGetErrorString(e));
     }
     if (dev->status_host && *dev->status_host != 0) {
         const int st = *dev->status_host;
         *dev->status_host = 0;
         dev->failed = true;
+        settle_writes(dev, false);
         if (st == FQ_ERR_WEIGHT) return fq_fail(dev, FQ_ERR_WEIGHT, "router produced invalid logits");
         return fq_fail(dev, st == FQ_ERR_TIMEOUT ? FQ_ERR_TIMEOUT : FQ_ERR_SYNC, "a kernel gave up a bounded wait (status %d)", st);
     }
     if (dev->failed) return fq_fail(dev, FQ_ERR_SYNC, "device handle holds a failed submission");
+    settle_writes(dev, true);
     return FQ_OK;
 }
 
@@ -462,6 +497,11 @@ extern "C" int fq_buffer_free(fq_device *dev, void *device_ptr) {
     if (it == dev->allocations.end()) return fq_fail(dev, FQ_ERR_RANGE, "%p was not allocated by this handle", device_ptr);
     cudaSetDevice(dev->ordinal);
     cudaStreamSynchronize(dev->stream);
+    // Nothing is remembered about a buffer that is gone.
+    const uintptr_t lo = it->first, hi = it->first + it->second;
+    auto inside = [&](const std::pair<uintptr_t, uintptr_t> &r) { return r.first >= lo && r.second <= hi; };
+    dev->failed_writes.erase(std::remove_if(dev->failed_writes.begin(), dev->failed_writes.end(), inside), dev->failed_writes.end());
+    dev->pending_writes.erase(std::remove_if(dev->pending_writes.begin(), dev->pending_writes.end(), inside), dev->pending_writes.end());
     dev->allocations.erase(it);
     return fq_check_cuda(dev, cudaFree(device_ptr), "cudaFree");
 }
@@ -471,6 +511,7 @@ extern "C" int fq_upload(fq_device *dev, void *device_ptr, const void *host, siz
     if (int rc = fq_begin_enqueue(dev)) return rc;
     if (int rc = fq_check_binding(dev, device_ptr, bytes, "upload destination")) return rc;
     dev->counters.bytes_uploaded += bytes;
+    fq_note_write(dev, device_ptr, bytes);
     return fq_check_cuda(dev, cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, dev->stream), "upload");
 }
 

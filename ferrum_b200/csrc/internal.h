@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <map>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/ferrum_b200.h"
@@ -34,6 +35,10 @@ struct fq_device {
     int fail_after = -1;          // test hook: enqueues left before an injected failure
     bool fail_completion = false; // test hook: next synchronize reports failure
     fq_counters counters{};
+    // Output ranges enqueued since the last completion point, and the ranges a failed submission wrote: an input
+    // that overlaps one of the latter is refused until a later submission that rewrites it has completed
+    // (`Completion::Failed`, src/metal/mod.rs:865-873).
+    std::vector<std::pair<uintptr_t, uintptr_t>> pending_writes, failed_writes;
     // Opt-in per-operation measurements (`fq_set_profiling` / `fq_take_profile`): a pair of events around every
     // enqueue outside graph capture, resolved into the table when it is taken.
     struct ProfileSample { const char *name; cudaEvent_t start, stop; };
@@ -98,6 +103,7 @@ int fq_check_cuda(fq_device *dev, cudaError_t e, const char *what);
 int fq_begin_enqueue(fq_device *dev);
 int fq_end_enqueue(fq_device *dev, const char *what, int kernels);
 // Binding checks shared by the op surface (null, alignment, ownership range, overlap).
+void fq_note_write(fq_device *dev, const void *out, size_t bytes); // an enqueue writes [out, out + bytes)
 int fq_check_binding(fq_device *dev, const void *p, size_t bytes, const char *name, uint32_t align = 16);
 int fq_check_no_alias(fq_device *dev, const void *out, size_t out_bytes, const void *in,
                       size_t in_bytes, const char *name);

@@ -128,7 +128,11 @@ int fq_capture_end(fq_device *dev, fq_graph **out);
 int fq_graph_launch(fq_device *dev, fq_graph *graph);
 int fq_graph_destroy(fq_graph *graph);
 
-/* ---- caller-visible device buffers (src/metal/mod.rs:700-760 `buffer`, Tensor::from_f32) --- */
+/* ---- caller-visible device buffers (src/metal/mod.rs:700-760 `buffer`, Tensor::from_f32) ---
+ * For buffers allocated here the handle remembers what each submission writes: when a completion point
+ * (`fq_synchronize`, `fq_download`) fails, the ranges written since the last one are refused as inputs
+ * (FQ_ERR_SYNC) until a later submission that writes them again has completed -- src/metal/mod.rs:865-873.
+ * Memory allocated elsewhere is accepted everywhere but is not tracked. */
 int fq_buffer_alloc(fq_device *dev, size_t bytes, void **device_ptr);
 int fq_buffer_free(fq_device *dev, void *device_ptr);
 int fq_upload(fq_device *dev, void *device_ptr, const void *host, size_t bytes);

@@ -474,6 +474,51 @@ def test_injected_failures_poison_and_recover(device):
     device.synchronize()
 
 
+class _Owned:
+    """A buffer the device handle allocated (`fq_buffer_alloc`), viewed as a torch tensor of floats."""
+
+    def __init__(self, device, floats):
+        import ctypes as C
+        self.device, self.ptr = device, C.c_void_p()
+        device.check(device._L.fq_buffer_alloc(device.handle, floats * 4, C.byref(self.ptr)))
+        self.__cuda_array_interface__ = {"shape": (floats,), "typestr": "<f4", "data": (self.ptr.value, False), "version": 3}
+        self.tensor = torch.as_tensor(self, device="cuda")
+
+    def free(self):
+        self.device.check(self.device._L.fq_buffer_free(self.device.handle, self.ptr))
+
+
+def test_outputs_of_a_failed_submission_are_refused_as_inputs(device):
+    """What a failed submission wrote into a buffer of the handle may not feed a later dispatch until it has been
+    written again by a submission that completed (`Completion::Failed`, src/metal/mod.rs:865-873); other buffers are
+    unaffected, and so is memory the caller owns."""
+    s = S()
+    w1 = s.Matrix.from_packed(device, 512, 512, 1, ref.Q4_K, ref.random_matrix(ref.Q4_K, 512, 512, 1))
+    packed2 = ref.random_matrix(ref.Q4_K, 16, 512, 2)
+    w2 = s.Matrix.from_packed(device, 16, 512, 1, ref.Q4_K, packed2)
+    x = torch.ones(512, dtype=torch.float32, device="cuda")
+    hb = _Owned(device, 512)
+    h = hb.tensor
+    y = torch.zeros(16, dtype=torch.float32, device="cuda")
+    try:
+        s.project(device, w1, x, 1, h)
+        device.fail_completion()
+        with pytest.raises(s.SynchronizationError):
+            device.synchronize()
+        device.recover()
+        with pytest.raises(s.SynchronizationError):   # h belongs to the failed submission
+            s.project(device, w2, h, 1, y)
+        s.project(device, w2, x, 1, y)                # x does not
+        s.project(device, w1, x, 1, h)                # written again ...
+        device.synchronize()                          # ... by a submission that completed
+        s.project(device, w2, h, 1, y)
+        device.synchronize()
+        want = ref.matmul(ref.Q4_K, packed2, 16, 512, host(h), 1)
+        assert ref.rel_err(host(y).reshape(1, 16), want) <= TOL_F32
+    finally:
+        hb.free()
+
+
 def test_host_buffer_entry_points_match_the_device_path(device):
     s = S()
     rows, cols, m = 96, 1024, 5
