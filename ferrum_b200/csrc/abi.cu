@@ -298,6 +298,8 @@ extern "C" int fq_device_create(int ordinal, fq_device **out) {
     if ((e = cudaMalloc((void **)&dev->side_nt_counters, (size_t)dev->side_nt_counter_count * 4)) != cudaSuccess) return bail(e, "slice counters");
     if ((e = cudaMemset(dev->nt_counters, 0, (size_t)dev->nt_counter_count * 4)) != cudaSuccess) return bail(e, "slice counters");
     if ((e = cudaMemset(dev->side_nt_counters, 0, (size_t)dev->side_nt_counter_count * 4)) != cudaSuccess) return bail(e, "slice counters");
+    if ((e = cudaMalloc((void **)&dev->combine_counters, (size_t)FQ_COMBINE_COUNTERS * 4)) != cudaSuccess) return bail(e, "combine counters");
+    if ((e = cudaMemset(dev->combine_counters, 0, (size_t)FQ_COMBINE_COUNTERS * 4)) != cudaSuccess) return bail(e, "combine counters");
     if ((e = cudaMalloc(&dev->staging_dev, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "device staging");
     if ((e = cudaMallocHost(&dev->staging_host, FQ_HOST_STAGING_BYTES)) != cudaSuccess) return bail(e, "pinned staging");
     dev->gemm_ws_bytes = (size_t)96 << 20;
@@ -322,6 +324,7 @@ extern "C" int fq_device_destroy(fq_device *dev) {
     if (dev->side_nt_ws) cudaFree(dev->side_nt_ws);
     if (dev->nt_counters) cudaFree(dev->nt_counters);
     if (dev->side_nt_counters) cudaFree(dev->side_nt_counters);
+    if (dev->combine_counters) cudaFree(dev->combine_counters);
     if (dev->side_stream) {
         cudaStreamSynchronize(dev->side_stream);
         cudaStreamDestroy(dev->side_stream);
@@ -386,6 +389,8 @@ extern "C" int fq_device_recover(fq_device *dev) {
     cudaSetDevice(dev->ordinal);
     cudaError_t e = cudaStreamSynchronize(dev->stream);
     if (e != cudaSuccess) return fq_fail(dev, FQ_ERR_SYNC, "stream is still failing: %s", cudaGetErrorString(e));
+    // A kernel that gave up a wait may have left arrival counters behind.
+    if (cudaMemset(dev->combine_counters, 0, (size_t)FQ_COMBINE_COUNTERS * 4) != cudaSuccess) cudaGetLastError();
     dev->failed = false;
     dev->error.clear();
     return FQ_OK;
@@ -982,9 +987,12 @@ static int side_join(SideBranch &b) {
 // y = W . (silu(g) * u): at decode widths the gated unit is computed inside the projection's activation
 // preparation (no separate launch, no round trip of `act`); otherwise `fq_glu` into `act`, then the projection.
 // With `ids` (routes, one activation row each) W is an expert stack.
+// `combine` (routes only): the projection also carries out the weighted sum over each token's routes; `*combined`
+// tells whether it did (else the caller combines).
 static int project_gated(fq_device *dev, const fq_matrix *w, const float *g, const float *u, float *act, size_t rows_x, const uint32_t *ids,
-                         float *y) {
+                         float *y, const CombineTail *combine = nullptr, bool *combined = nullptr) {
     const size_t width = w->cols, rows_e = w->expert_rows();
+    if (combined) *combined = false;
     if (!dev->exact) {
         if (int rc = fq_begin_enqueue(dev)) return rc;
         if (int rc = fq_check_binding(dev, g, rows_x * width * 4, "gate")) return rc;
@@ -998,6 +1006,15 @@ static int project_gated(fq_device *dev, const fq_matrix *w, const float *g, con
             a.x_div = 1;
         } else {
             a.rows = (uint32_t)w->rows;
+        }
+        if (ids && combine) {
+            a.combine = combine;
+            const int rc = fq_launch_gemv_i8_many(dev, &a, 1);
+            if (rc != FQ_ERR_UNSUPPORTED) {
+                if (combined) *combined = rc == FQ_OK;
+                return rc;
+            }
+            a.combine = nullptr;
         }
         const int rc = (ids || rows_x == 1) ? fq_launch_gemv_i8_many(dev, &a, 1) : fq_launch_gemv_nt_many(dev, &a, 1);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
@@ -1138,9 +1155,18 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
     if (!rc)
         rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m, f->sigmoid,
                           f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate);
+    bool combined = false;
     if (!rc && identity) {
         rc = project_id_pair(dev, f->gate_exps, f->up_exps, x, m * hidden, s.ids, routes, used, s.g, s.u);
-        if (!rc) rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, s.ids, s.down);
+        // The down projection also combines (the last of a token's route blocks to finish a row tile adds them up),
+        // which takes the shared expert's output: the side stream joins before it instead of before the combine.
+        CombineTail tail{s.weights, s.shared, s.gate, out, dev->combine_counters, (uint32_t)used};
+        const bool fuse = !dev->exact && f->down_exps->expert_rows() == hidden;
+        if (fuse) {
+            if (int rc2 = side_join(side)) rc = rc ? rc : rc2;
+            if (!rc) rc = fq_check_binding(dev, out, m * hidden * 4, "out");
+        }
+        if (!rc) rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, s.ids, s.down, fuse ? &tail : nullptr, &combined);
     } else if (!rc) {
         // Expert-sorted rows through the tensor-core GEMM: activations rounded to bf16 once (at the gather and
         // at the gated unit), fp32 accumulation and fp32 results.
@@ -1157,7 +1183,7 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
         }
     }
     if (int rc2 = side_join(side)) rc = rc ? rc : rc2; // also after an error: a capture must not end with the branch open
-    if (rc) return rc;
+    if (rc || combined) return rc;
     return fq_moe_combine(dev, s.down, s.weights, identity ? s.ids : s.position, s.shared, s.gate, (uint32_t)hidden,
                           (uint32_t)used, (uint32_t)m, identity, out);
 }

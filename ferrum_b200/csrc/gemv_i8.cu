@@ -374,7 +374,7 @@ template <int FMT, int MT, bool INP = false>
 __global__ void __launch_bounds__(MT >= 3 ? 256 : MT == 2 ? 384 : MAX_WARPS * 32)
 k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *__restrict__ prep, PrepI8 L,
           const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts, const __grid_constant__ TpPush P,
-          const float *__restrict__ xin, const float *__restrict__ xup) {
+          const float *__restrict__ xin, const float *__restrict__ xup, const __grid_constant__ CombineTail C) {
     using Raw = typename RawOf<FMT>::type;
     static_assert(!INP || MT == 1, "in-kernel preparation serves one activation row per route");
     extern __shared__ __align__(16) uint8_t own_act[]; // INP: the route's prepared row
@@ -519,6 +519,30 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
                     if (P.world > 1) tp_store(P, seq, dst, v);
                 }
             }
+    }
+    if (C.counters && warp == 0) {
+        // The weighted sum over a token's routes (and the shared expert) for this tile's rows, by the last of the
+        // token's route blocks to get here: in route order, so the result does not depend on which block that is.
+        __threadfence();
+        __syncwarp();
+        const uint32_t token = blockIdx.y / C.used;
+        uint32_t *counter = C.counters + (size_t)token * total_tiles + here.tile0;
+        uint32_t last = 0;
+        if (lane == 0) last = atomicAdd(counter, 1u) + 1 == C.used;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            if (lane == 0) *counter = 0;
+            __threadfence();
+            const uint32_t row = here.tile0 * 16 + lane;
+            if (lane < 16 && row < here.rows) {
+                float acc = 0.f;
+                for (uint32_t s2 = 0; s2 < C.used; s2++) {
+                    const uint32_t r = token * C.used + s2;
+                    acc = fmaf(C.weights[r], __ldcg(&here.y[(size_t)r * here.rows + row]), acc);
+                }
+                C.out[(size_t)token * here.rows + row] = fmaf(C.gate[token], C.shared[(size_t)token * here.rows + row], acc);
+            }
+        }
     }
     if (!more) break;
     tile = next_tile;
@@ -808,8 +832,10 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
         dev->tp_push = nullptr;
         dev->tp_pushed = true;
     }
+    CombineTail tail{};
+    if (expert && a[0].combine) tail = *a[0].combine;
     return launch_pdl(k_gemv_i8<FMT, MT, INP>, grid, dim3(warps * 32), INP ? L.token_bytes : 0, dev->stream, T, a[0].row_bytes, prep, L, a[0].ids,
-                      a[0].x_div, a[0].experts, push, (const float *)a[0].x, a[0].x_up);
+                      a[0].x_div, a[0].experts, push, (const float *)a[0].x, a[0].x_up, tail);
 }
 
 } // namespace
@@ -826,6 +852,9 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
             a[i].y_dtype != FQ_F32)
             return FQ_ERR_UNSUPPORTED; // with routes the targets are expert stacks of one shape (gate and up)
     const bool expert = f.ids != nullptr;
+    if (f.combine && (!expert || count != 1 || f.x_div != 1 || f.norm_w || prep_i8_layout(f.cols).token_bytes > 40 * 1024 ||
+                      (size_t)(f.m / f.combine->used) * ((f.rows + 15) / 16) > FQ_COMBINE_COUNTERS))
+        return FQ_ERR_UNSUPPORTED; // the caller combines with a kernel of its own
     uint32_t xrows, m;
     if (expert) {
         if (f.m > 65535) return FQ_ERR_UNSUPPORTED;
@@ -925,7 +954,7 @@ cudaError_t launch_static(const uint8_t *w, uint32_t rows, uint32_t pitch, float
         const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need);
         if (waste < best) { best = waste; warps = k; }
     }
-    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u, TpPush{}, nullptr, nullptr);
+    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u, TpPush{}, nullptr, nullptr, CombineTail{});
     return cudaGetLastError();
 }
 

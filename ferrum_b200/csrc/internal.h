@@ -68,6 +68,7 @@ struct fq_device {
     void *nt_ws = nullptr, *side_nt_ws = nullptr;
     size_t nt_ws_bytes = 0, side_nt_ws_bytes = 0;
     uint32_t *nt_counters = nullptr, *side_nt_counters = nullptr;
+    uint32_t *combine_counters = nullptr; // FQ_COMBINE_COUNTERS words, zero between launches
     uint32_t nt_counter_count = 0, side_nt_counter_count = 0;
     // Split-K workspace of the prefill GEMM: partial fp32 tiles and one arrival counter per tile.
     float *gemm_ws = nullptr;
@@ -111,6 +112,16 @@ int fq_check_no_alias(fq_device *dev, const void *out, size_t out_bytes, const v
 inline size_t fq_dtype_size(int dtype) { return dtype == FQ_BF16 ? 2 : 4; }
 
 // Kernel launchers (one per translation unit); all enqueue on dev->stream and return a status.
+// `h_moe_combine` (src/metal/shaders/hybrid.metal:2371-2388) carried out by the down projection of per-route
+// experts: the last of a token's `used` route blocks to finish a 16-row tile adds the routes' rows in route order.
+constexpr uint32_t FQ_COMBINE_COUNTERS = 8192;
+struct CombineTail {
+    const float *weights, *shared, *gate; // [tokens][used], [tokens][hidden], [tokens]
+    float *out;                           // [tokens][hidden]
+    uint32_t *counters;                   // [tokens][tiles]: arrivals, back at zero when the kernel ends; null = no tail
+    uint32_t used;
+};
+
 struct ProjectArgs {
     const uint8_t *w;
     uint32_t format, rows, cols, row_bytes; // rows = rows of one expert slice; row_bytes = device row pitch
@@ -128,6 +139,7 @@ struct ProjectArgs {
     const uint32_t *slots = nullptr;
     uint32_t groups = 0, max_rows = 0;
     uint32_t experts = 1;              // expert slices stored in w
+    const CombineTail *combine = nullptr; // project_id of one target, one activation row per route (x_div = 1)
 };
 int fq_launch_project_exact(fq_device *dev, const ProjectArgs &a);
 int fq_launch_project_id_exact(fq_device *dev, const ProjectArgs &a);

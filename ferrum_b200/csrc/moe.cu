@@ -316,9 +316,9 @@ k_moe_combine(const float *__restrict__ down, const float *__restrict__ weights,
     const float g = gate[t];
     if constexpr (VEC == 4) {
         const float4 sh = *reinterpret_cast<const float4 *>(shared + gid);
-        *reinterpret_cast<float4 *>(out + gid) = make_float4(acc[0] + g * sh.x, acc[1] + g * sh.y, acc[2] + g * sh.z, acc[3] + g * sh.w);
+        *reinterpret_cast<float4 *>(out + gid) = make_float4(fmaf(g, sh.x, acc[0]), fmaf(g, sh.y, acc[1]), fmaf(g, sh.z, acc[2]), fmaf(g, sh.w, acc[3]));
     } else {
-        out[gid] = acc[0] + g * shared[gid];
+        out[gid] = fmaf(g, shared[gid], acc[0]);
     }
 }
 
