@@ -880,8 +880,24 @@ extern "C" int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x,
     return fq_end_enqueue(dev, "project_id", 1);
 }
 
-// Average rows per expert up to which grouped F32 projections take the integer kernel of gemv_nt.cu.
+// Grouped F32 projections by average rows per expert: below GROUPED_F16_MIN_AVG_ROWS the integer kernel of
+// gemv_nt.cu (the work is streaming weights; its per-row arithmetic is still small), from there on the fp16
+// tensor-core kernel k_gemm_f16g, which decodes every weight once per 64 rows (measured on the 35B-A3B-class
+// block: 443 against 453 us at 24 rows per expert, 539 against 460 us at 32, 619 against 514 us at 40).  Formats
+// the fp16 kernel does not serve stay on the integer kernel up to GROUPED_NT_MAX_AVG_ROWS.
+constexpr size_t GROUPED_F16_MIN_AVG_ROWS = 28;
 constexpr size_t GROUPED_NT_MAX_AVG_ROWS = 48;
+
+// Arguments as fq_launch_gemv_nt_grouped, and `group_rows`: how many of the rows the groups in `a` cover (all of
+// them, or a rank's expected share); FQ_ERR_UNSUPPORTED when neither kernel serves the shape.
+static int launch_grouped_f32(fq_device *dev, const ProjectArgs *a, uint32_t count, uint32_t total_rows, size_t group_rows, const uint32_t *src,
+                              uint32_t src_div) {
+    int rc = FQ_ERR_UNSUPPORTED;
+    if (group_rows >= GROUPED_F16_MIN_AVG_ROWS * a[0].groups) rc = fq_launch_gemm_f16_grouped(dev, a, count, total_rows, src, src_div);
+    if (rc == FQ_ERR_UNSUPPORTED && group_rows <= GROUPED_NT_MAX_AVG_ROWS * a[0].groups)
+        rc = fq_launch_gemv_nt_grouped(dev, a, count, total_rows, src, src_div);
+    return rc;
+}
 
 extern "C" int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems,
                                 const uint32_t *offsets, const uint32_t *slots, size_t groups, size_t max_rows,
@@ -910,10 +926,9 @@ extern "C" int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *
     if (!dev->exact) {
         const uint32_t total_rows = (uint32_t)(x_elems / w->cols);
         int rc = FQ_ERR_UNSUPPORTED;
-        // Few rows per expert: the problem is weight-streaming, not arithmetic; the integer kernel with the rows
-        // on the MMA's N side unpacks every weight once per sixteen rows.  Otherwise the tcgen05 GEMM.
-        if (x_dtype == FQ_F32 && y_dtype == FQ_F32 && total_rows <= GROUPED_NT_MAX_AVG_ROWS * groups)
-            rc = fq_launch_gemv_nt_grouped(dev, &a, 1, total_rows, nullptr, 1);
+        // F32 callers: the integer kernel or the fp16 tensor-core kernel, by rows per expert; what neither serves
+        // (and BF16 callers) takes the bf16 tcgen05 GEMM.
+        if (x_dtype == FQ_F32 && y_dtype == FQ_F32) rc = launch_grouped_f32(dev, &a, 1, total_rows, total_rows, nullptr, 1);
         if (rc == FQ_ERR_UNSUPPORTED) rc = fq_launch_gemm_tc_grouped(dev, a, total_rows);
         if (rc != FQ_ERR_UNSUPPORTED) return rc;
     }
@@ -1095,11 +1110,11 @@ static MoeScratch moe_layout(const fq_moe_ffn_desc *f, size_t m, float *base) {
     return s;
 }
 
-// Routed experts over expert-sorted rows with few rows per expert: gate and up as two targets of one launch that
-// gathers the rows itself (row r of the sorted set is token sorted[r] / used), then the down projection whose
-// activation preparation computes the gated unit.  `offsets[0 .. groups]` bound the rows of the experts the
+// Routed experts over expert-sorted rows, F32 throughout (the integer kernel or the fp16 tensor-core kernel, by
+// rows per expert): gate and up as two targets of one launch that gathers the rows itself (row r of the sorted set
+// is token sorted[r] / used), then the down projection whose activation preparation computes the gated unit.  `offsets[0 .. groups]` bound the rows of the experts the
 // matrices hold.  FQ_ERR_UNSUPPORTED when the shapes have no such kernel (nothing is enqueued then).
-static int moe_experts_nt(fq_device *dev, const fq_moe_ffn_desc *f, const float *x, const MoeScratch &s, const uint32_t *offsets, uint32_t groups,
+static int moe_experts_f32(fq_device *dev, const fq_moe_ffn_desc *f, const float *x, const MoeScratch &s, const uint32_t *offsets, uint32_t groups,
                           size_t routes, float *down) {
     if (int rc = fq_begin_enqueue(dev)) return rc;
     ProjectArgs gu[2] = {base_args(f->gate_exps, x, FQ_F32, s.g, FQ_F32), base_args(f->up_exps, x, FQ_F32, s.u, FQ_F32)};
@@ -1111,8 +1126,9 @@ static int moe_experts_nt(fq_device *dev, const fq_moe_ffn_desc *f, const float 
     dn.x_up = s.u;
     dn.offsets = offsets;
     dn.groups = groups;
-    if (int rc = fq_launch_gemv_nt_grouped(dev, gu, 2, (uint32_t)routes, s.sorted, f->used)) return rc;
-    return fq_launch_gemv_nt_grouped(dev, &dn, 1, (uint32_t)routes, nullptr, 1);
+    const size_t share = routes * groups / f->experts; // the rows these groups are expected to hold
+    if (int rc = launch_grouped_f32(dev, gu, 2, (uint32_t)routes, share, s.sorted, f->used)) return rc;
+    return launch_grouped_f32(dev, &dn, 1, (uint32_t)routes, share, nullptr, 1);
 }
 
 extern "C" size_t fq_moe_ffn_scratch_elems(const fq_moe_ffn_desc *f, size_t m) {
@@ -1172,7 +1188,7 @@ extern "C" int fq_moe_ffn(fq_device *dev, const fq_moe_ffn_desc *f, const float 
         // at the gated unit), fp32 accumulation and fp32 results.
         rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position);
         int nt = FQ_ERR_UNSUPPORTED;
-        if (!rc && routes <= GROUPED_NT_MAX_AVG_ROWS * experts) nt = moe_experts_nt(dev, f, x, s, s.offsets, (uint32_t)experts, routes, s.down);
+        if (!rc) nt = moe_experts_f32(dev, f, x, s, s.offsets, (uint32_t)experts, routes, s.down);
         if (nt != FQ_ERR_UNSUPPORTED) rc = rc ? rc : nt;
         else {
         if (!rc) rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, nullptr, 0, s.xg);
@@ -1247,9 +1263,8 @@ extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset
         if (!rc) rc = fq_launch_moe_local_ids(dev, s.ids, s.sorted, (uint32_t)routes, expert_first, (uint32_t)local, local_ids);
         if (!rc) rc = project_id_pair(dev, f->gate_exps, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, s.u);
         if (!rc) rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, local_ids, down);
-    } else if (!rc && routes <= GROUPED_NT_MAX_AVG_ROWS * experts &&
-               (rc = moe_experts_nt(dev, f, x, s, mine, (uint32_t)local, routes, down)) != FQ_ERR_UNSUPPORTED) {
-        // done (or failed) on the integer kernel
+    } else if (!rc && (rc = moe_experts_f32(dev, f, x, s, mine, (uint32_t)local, routes, down)) != FQ_ERR_UNSUPPORTED) {
+        // done (or failed) on the integer or the fp16 kernel
     } else if (!rc || rc == FQ_ERR_UNSUPPORTED) {
         rc = fq_launch_moe_gather_bf16(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, mine, (uint32_t)local, s.xg);
         if (!rc) rc = fq_project_mm_id(dev, f->gate_exps, s.xg, FQ_BF16, routes * hidden, mine, nullptr, local, m, s.g, FQ_F32, routes * ef);

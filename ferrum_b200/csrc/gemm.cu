@@ -21,7 +21,11 @@
 // tokens.  Every mbarrier wait is bounded: a wait that gives up records FQ_ERR_TIMEOUT in the status
 // word, the block stops issuing work, waits (bounded) for what it already issued, frees its tensor
 // memory and returns.
+//
+// Further down: k_gemm_f16g, the persistent fp16 kernel for expert-sorted rows of F32 callers (tokens on the MMA's
+// M side as hi + lo terms, 256 weight rows on its N side).
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
 
@@ -86,11 +90,11 @@ __device__ __forceinline__ uint64_t now_ns() {
 }
 // Bounded wait (WAIT_LIMIT_NS of wall time).  On giving up: record the timeout, raise the block's abort
 // flag, report failure.
-template <class SM> __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SM *sm, int *status) {
+template <class SM, uint32_t HINT_NS = WAIT_HINT_NS> __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SM *sm, int *status) {
     if (mbar_try(bar, parity)) return true;
     const uint64_t t0 = now_ns();
     do {
-        if (mbar_try(bar, parity, WAIT_HINT_NS)) return true;
+        if (mbar_try(bar, parity, HINT_NS)) return true;
         if (*(volatile uint32_t *)&sm->abort_flag) return false;
     } while (now_ns() - t0 < WAIT_LIMIT_NS);
     *(volatile int *)status = (int)FQ_ERR_TIMEOUT;
@@ -671,7 +675,8 @@ int launch_fmt(fq_device *dev, const ProjectArgs &a, const CUtensorMap &map, uin
     }
 }
 
-int make_map(fq_device *dev, CUtensorMap *map, const void *x, uint32_t cols, uint32_t m_rows, uint32_t bn, uint32_t *b_bytes) {
+int make_map(fq_device *dev, CUtensorMap *map, const void *x, uint32_t cols, uint32_t m_rows, uint32_t bn, uint32_t *b_bytes,
+             CUtensorMapDataType type = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
     EncodeTiled encode = encode_fn();
     if (!encode) return FQ_ERR_UNSUPPORTED;
     const cuuint64_t dims[2] = {cols, m_rows};
@@ -679,12 +684,502 @@ int make_map(fq_device *dev, CUtensorMap *map, const void *x, uint32_t cols, uin
     // A box may not be taller than the tensor; rows past the end of a later tile are zero-filled.
     const uint32_t box_rows = m_rows < bn ? m_rows : bn;
     const cuuint32_t box[2] = {BK, box_rows}, elem[2] = {1, 1};
-    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), dims, strides, box, elem,
+    CUresult r = encode(map, type, 2, const_cast<void *>(x), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fq_fail(dev, FQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
     *b_bytes = box_rows * BK * 2;
     return FQ_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// Expert tiles on fp16 products: grouped projections of roughly 12 to 64 rows per expert, F32 in and out, for
+// which the integer kernel of gemv_nt.cu repeats its per-(row, sub-block) scale arithmetic too often and the
+// bf16 GEMM above is both too coarse (2^-9 weights, bf16 activations) and organised for many rows per tile.
+//
+//   y[t][n] = (sum_k (hi[t][k] + lo[t][k]) * fp16(W[e][n][k])) / s[t]      hi + lo = s[t] x[t] to 22 bits
+//
+// A tcgen05.mma with M = 128 takes about the same time whatever its N (measured: N = 32, 80 and 128 alike), so the
+// few activation rows go on the M side -- 64 rows, each as two MMA rows (hi, lo) -- and 256 weight rows on the
+// N side: the widest instruction, the most weights per tensor-core cycle.
+//
+// The block is persistent (one per SM) and walks work items (activation tile of <= 64 expert-sorted rows,
+// 256 weight rows of one of up to two matrix sets) in a strided order:
+//
+//   warp 0        builds the table of activation tiles from the group offsets, then one thread issues one TMA
+//                 load per k-block: the tile's rows with their hi and lo terms interleaved (MMA row 2 c is
+//                 activation row c against hi, row 2 c + 1 against lo);
+//   warp 1        one thread issues tcgen05.mma (M = 128, N = 256, K = 16, kind::f16) into one of two
+//                 accumulators in tensor memory, so that the next item's MMAs run under this item's epilogue;
+//   warps 2..17   decode: thread (weight row, group) keeps the packed bytes of its next k-blocks in registers
+//                 (a superblock ahead, across item borders) and writes 32 fp16 weights per k-block in packed half
+//                 arithmetic (g_decode_* below) into the K-major, 128-byte-swizzled tile the MMA reads;
+//   warps 18..21  epilogue: read the accumulator (lane = MMA row), add the hi and lo rows with a shuffle, undo
+//                 the row scale, store y.
+//
+// Every wait is bounded as in k_gemm_tc.
+constexpr int G_PRODUCER_WARPS = 16, G_EPI_WARPS = 4, G_THREADS = (2 + G_PRODUCER_WARPS + G_EPI_WARPS) * 32;
+constexpr int G_STAGES = 4;             // decoded weight tiles in flight
+constexpr int G_X_SLOTS = 3;            // activation tiles in flight
+constexpr uint32_t G_TOK = 64;          // activation rows per tile (128 MMA rows)
+constexpr uint32_t G_BN = 256;          // weight rows per tile (MMA N)
+constexpr uint32_t G_W_BYTES = G_BN * BK * 2, G_X_BYTES = 2 * G_TOK * BK * 2;
+constexpr uint32_t G_MAX_TILES = 1024;  // activation tiles the table holds
+
+struct __align__(1024) GSmem {
+    uint8_t w[G_STAGES][G_W_BYTES];
+    uint8_t x[G_X_SLOTS][G_X_BYTES];
+    uint2 tiles[G_MAX_TILES]; // .x = first sorted row, .y = expert << 8 | rows
+    uint64_t full_w[G_STAGES], empty_w[G_STAGES], full_x[G_X_SLOTS], empty_x[G_X_SLOTS], acc_full[2], acc_empty[2], drain;
+    uint32_t tmem_base, abort_flag, n_tiles;
+};
+
+struct GJob {
+    const uint8_t *w[2]; // matrix sets sharing the rows (gate and up)
+    float *y[2];
+    uint32_t tx_end[2];  // 256-row tiles up to and including set i
+    uint32_t count;
+    uint32_t rows, cols, pitch, experts, groups;
+    uint32_t row_begin, row_end; // the expert-sorted rows this launch serves (the fp16 copy holds only these)
+    const uint32_t *offsets, *slots;
+    const float *inv_scale;      // of rows row_begin ..
+    int *status;
+    uint32_t box_bytes[3]; // of the 32-, 64- and 128-row activation boxes
+};
+
+__device__ __forceinline__ __half2 h2_bits(uint32_t b) { return *reinterpret_cast<__half2 *>(&b); }
+__device__ __forceinline__ uint32_t bits_h2(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+// Two copies of a small unsigned integer as exact halves: 0x6400 | v is 1024 + v.
+__device__ __forceinline__ __half2 small_h2(uint32_t v) {
+    return __hsub2(h2_bits(0x64006400u | v | (v << 16)), h2_bits(0x64006400u));
+}
+// Instruction descriptor, kind::f16: D = F32, A = B = F16, both K-major, M = 128, N = 256.
+constexpr uint32_t G_IDESC = (1u << 4) | ((G_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+// One 32-value group of a superblock as 32 fp16 weights, two per register; `live` false gives zeros (rows past
+// the end of the matrix).  A quant enters as the half 0x6400 | q = 1024 + q (one PRMT per pair).  Q4_K:
+// u = (1024 + q) sc - 1024 sc = q sc in one fused step (exact: below 2048), then w = u d - fp16(dmin m), rounded
+// once.  Q6_K: (1024 + q) - 1056 = q - 32 exactly, times fp16(d scale).  Every weight is within 2^-11 (relative)
+// of its exact value, plus 2^-12 of its sub-block's minimum term.
+//
+// Q4_K: sub-block j = 2 C + part of the superblock (header `hdr`): nibble `part` of the 32 bytes a, b of chunk C.
+template <int C>
+__device__ __forceinline__ void g_decode_q4k(const uint4 &hdr, const uint4 &a, const uint4 &b, uint32_t part, bool live, uint32_t (&out)[16]) {
+    constexpr uint32_t MAGIC = 0x64646464u;
+    const uint32_t sh = 8 * ((2 * C) & 3) + 8 * part; // `get_scale_min_k4`
+    uint32_t sc, mn;
+    if (C < 2) {
+        sc = (hdr.y >> sh) & 63u;
+        mn = (hdr.z >> sh) & 63u;
+    } else {
+        sc = ((hdr.w >> sh) & 0xFu) | ((((hdr.y >> sh) >> 6) & 3u) << 4);
+        mn = (((hdr.w >> sh) >> 4) & 0xFu) | ((((hdr.z >> sh) >> 6) & 3u) << 4);
+    }
+    const uint32_t dd = live ? hdr.x : 0u;
+    const __half2 d2 = h2_bits(__byte_perm(dd, 0, 0x1010)), dmin2 = h2_bits(__byte_perm(dd, 0, 0x3232));
+    const __half2 sc2 = small_h2(sc), nsc = __hmul2(sc2, h2_bits(0xE400E400u)); // -1024 sc, exact
+    const __half2 ndm = __hneg2(__hmul2(dmin2, small_h2(mn)));
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t n4 = (w[i] >> (4 * part)) & 0x0F0F0F0Fu;
+        const __half2 u0 = __hfma2(h2_bits(__byte_perm(n4, MAGIC, 0x4140)), sc2, nsc);
+        const __half2 u1 = __hfma2(h2_bits(__byte_perm(n4, MAGIC, 0x4342)), sc2, nsc);
+        out[2 * i] = bits_h2(__hfma2(u0, d2, ndm));
+        out[2 * i + 1] = bits_h2(__hfma2(u1, d2, ndm));
+    }
+}
+// Q6_K (device layout of blocks.cuh): group i = 2 H + part of a 128-value half: low (H = 0) or high nibbles of the
+// half's ql bytes 32 part .. (l0, l1), bits 2 i .. 2 i + 1 of its 32 qh bytes (h0, h1), the two scales `sc16`
+// (one per sixteen values), d as f16 bits.
+template <int H>
+__device__ __forceinline__ void g_decode_q6k(const uint4 &l0, const uint4 &l1, const uint4 &h0, const uint4 &h1, uint32_t sc16, uint32_t d,
+                                             uint32_t part, bool live, uint32_t (&out)[16]) {
+    constexpr uint32_t MAGIC = 0x64646464u;
+    const uint32_t i = 2 * H + part;
+    const uint32_t s0 = (sc16 & 0xFFu) ^ 0x80u, s1 = ((sc16 >> 8) & 0xFFu) ^ 0x80u; // signed scales + 128
+    const uint32_t dd = live ? d : 0u;
+    const __half2 d2 = h2_bits(dd | (dd << 16)), off = h2_bits(0x64806480u); // 1152 = 1024 + 128
+    const __half2 ds0 = __hmul2(__hsub2(h2_bits(0x64006400u | s0 | (s0 << 16)), off), d2);
+    const __half2 ds1 = __hmul2(__hsub2(h2_bits(0x64006400u | s1 | (s1 << 16)), off), d2);
+    const __half2 bias = h2_bits(0x64206420u); // 1056 = 1024 + 32
+    const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const uint32_t lo4 = H == 0 ? lw[j] : (lw[j] >> 4);
+        const uint32_t q4 = (lo4 & 0x0F0F0F0Fu) | (((hw[j] >> (2 * i)) & 0x03030303u) << 4);
+        const __half2 ds = j < 4 ? ds0 : ds1;
+        out[2 * j] = bits_h2(__hmul2(__hsub2(h2_bits(__byte_perm(q4, MAGIC, 0x4140)), bias), ds));
+        out[2 * j + 1] = bits_h2(__hmul2(__hsub2(h2_bits(__byte_perm(q4, MAGIC, 0x4342)), bias), ds));
+    }
+}
+
+// X (fp32) for the fp16 expert-tile kernel below: row r of the sorted set (row src[r] / src_div of x, or r; gated by x_up as `k_swiglu`
+// does when given) times a power of two s that brings its largest magnitude into [2^13, 2^14), as two fp16
+// terms hi = fp16(s x), lo = fp16(s x - hi) -- 22 bits of every value, no fp16 overflow whatever the row holds.
+// Rows row_begin .. row_end - 1 go to out: [row - row_begin][2][cols] (a row's hi term, then its lo term) and
+// inv_scale[row - row_begin] = 1 / s.  One warp per row; only rows [range[0], range[range_stride]) -- those some
+// group covers -- are written.
+__global__ void __launch_bounds__(256)
+k_split_f16(const float *__restrict__ x, const float *__restrict__ x_up, const uint32_t *__restrict__ src, uint32_t src_div,
+            const uint32_t *__restrict__ range, uint32_t range_stride, uint32_t row_begin, uint32_t row_end, uint32_t cols,
+            __half *__restrict__ out, float *__restrict__ inv_scale) {
+    const uint32_t r = row_begin + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+    if (r >= row_end) return;
+    if (range && (r < range[0] || r >= range[range_stride])) return;
+    const size_t srow = src ? src[r] / src_div : r;
+    const float4 *xp = reinterpret_cast<const float4 *>(x + srow * cols), *up = x_up ? reinterpret_cast<const float4 *>(x_up + srow * cols) : nullptr;
+    auto value = [&](uint32_t i) {
+        float4 v = xp[i];
+        if (up) {
+            const float4 u = up[i];
+            v.x = v.x / (1.f + expf(-v.x)) * u.x;
+            v.y = v.y / (1.f + expf(-v.y)) * u.y;
+            v.z = v.z / (1.f + expf(-v.z)) * u.z;
+            v.w = v.w / (1.f + expf(-v.w)) * u.w;
+        }
+        return v;
+    };
+    float amax = 0.f;
+    for (uint32_t i = lane; i < cols / 4; i += 32) {
+        const float4 v = value(i);
+        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    // fmaxf drops NaNs: a row holding one keeps the scale of its finite values and the NaN travels in hi.
+    int e = 0;
+    if (amax > 0.f && amax <= 3.0e38f) e = min(max(13 - ilogbf(amax), -100), 100);
+    const float s = scalbnf(1.f, e);
+    if (lane == 0) inv_scale[r - row_begin] = scalbnf(1.f, -e);
+    __half *hi = out + (size_t)2 * (r - row_begin) * cols, *lo = hi + cols;
+    for (uint32_t i = lane; i < cols / 4; i += 32) {
+        const float4 v = value(i);
+        const float a[4] = {v.x * s, v.y * s, v.z * s, v.w * s};
+        __half h[4], l[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            h[j] = __float2half_rn(a[j]);
+            l[j] = __float2half_rn(a[j] - __half2float(h[j]));
+        }
+        *reinterpret_cast<uint2 *>(hi + 4 * i) = make_uint2(bits_h2(__halves2half2(h[0], h[1])), bits_h2(__halves2half2(h[2], h[3])));
+        *reinterpret_cast<uint2 *>(lo + 4 * i) = make_uint2(bits_h2(__halves2half2(l[0], l[1])), bits_h2(__halves2half2(l[2], l[3])));
+    }
+}
+
+
+template <int FMT>
+__global__ void __launch_bounds__(G_THREADS, 1)
+k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ CUtensorMap map64, const __grid_constant__ CUtensorMap map128,
+            const __grid_constant__ GJob J) {
+    extern __shared__ uint8_t smem_raw[];
+    GSmem *sm = reinterpret_cast<GSmem *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t nblk = J.cols / 256, k_iters = J.cols / BK, tiles_x = J.tx_end[J.count - 1];
+    constexpr uint32_t TMEM_COLS = 2 * G_BN; // two accumulators
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < G_STAGES; s++) {
+            mbar_init(&sm->full_w[s], G_PRODUCER_WARPS); // one lane arrives for its warp
+            mbar_init(&sm->empty_w[s], 1);
+        }
+        for (int s = 0; s < G_X_SLOTS; s++) {
+            mbar_init(&sm->full_x[s], 1);
+            mbar_init(&sm->empty_x[s], 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&sm->acc_full[i], 1);
+            mbar_init(&sm->acc_empty[i], G_EPI_WARPS * 32);
+        }
+        mbar_init(&sm->drain, 1);
+        sm->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map32) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map64) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map128) : "memory");
+    }
+    if (warp == 0) {
+        // The table of activation tiles: group z contributes ceil(rows / 64) tiles for its rows inside this
+        // launch's range; 32 groups per step, tile counts prefix-summed with shuffles.
+        uint32_t base = 0;
+        for (uint32_t g0 = 0; g0 < J.groups; g0 += 32) {
+            const uint32_t g = g0 + lane;
+            uint32_t first = 0, cnt = 0, e = 0;
+            if (g < J.groups) {
+                const uint32_t end = min(J.offsets[g + 1], J.row_end);
+                first = max(J.offsets[g], J.row_begin);
+                cnt = end > first ? end - first : 0u;
+                e = J.slots ? J.slots[g] : g;
+                if (e >= J.experts) cnt = 0;
+            }
+            const uint32_t t = (cnt + G_TOK - 1) / G_TOK;
+            uint32_t incl = t;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t n = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += n;
+            }
+            for (uint32_t j = 0; j < t; j++) {
+                const uint32_t at = base + incl - t + j;
+                if (at < G_MAX_TILES) sm->tiles[at] = make_uint2(first + j * G_TOK, (e << 8) | min(G_TOK, cnt - j * G_TOK));
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) sm->n_tiles = min(base, G_MAX_TILES); // the launcher admits no more
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *(volatile uint32_t *)&sm->tmem_base;
+    const uint32_t n_items = sm->n_tiles * tiles_x;
+    const uint32_t my_items = n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    // Item i of this block: activation tile, matrix set and first weight row.
+    struct Item {
+        uint32_t m0, cnt, e, set, n0;
+    };
+    auto item_at = [&](uint32_t i) {
+        const uint32_t id = blockIdx.x + i * gridDim.x, a = id / tiles_x;
+        uint32_t tx = id - a * tiles_x;
+        const uint2 t = sm->tiles[a];
+        Item it;
+        it.m0 = t.x;
+        it.cnt = t.y & 0xFFu;
+        it.e = t.y >> 8;
+        it.set = (J.count > 1 && tx >= J.tx_end[0]) ? 1u : 0u;
+        if (it.set) tx -= J.tx_end[0];
+        it.n0 = tx * G_BN;
+        return it;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t ix = 0;
+            bool ok = true;
+            for (uint32_t i = 0; i < my_items && ok; i++) {
+                const Item it = item_at(i);
+                // One box per k-block: the tile's rows with their hi and lo terms interleaved (32, 64 or 128 tensor
+                // rows; a box that runs past the tile reads rows whose results are not stored, or zeros past the
+                // end; MMA rows the box does not cover keep what an earlier tile left there).
+                const CUtensorMap *map = it.cnt <= 16 ? &map32 : it.cnt <= 32 ? &map64 : &map128;
+                const uint32_t bytes = (it.cnt <= 16 ? J.box_bytes[0] : it.cnt <= 32 ? J.box_bytes[1] : J.box_bytes[2]);
+                for (uint32_t k = 0; k < k_iters; k++, ix++) {
+                    const uint32_t s = ix % G_X_SLOTS;
+                    if (!(ok = mbar_wait(&sm->empty_x[s], ((ix / G_X_SLOTS) & 1) ^ 1, sm, J.status))) break;
+                    mbar_expect_tx(&sm->full_x[s], bytes);
+                    tma_load_2d(sm->x[s], map, (int)(k * BK), (int)(2 * (it.m0 - J.row_begin)), &sm->full_x[s]);
+                }
+            }
+            // On an abort the copies already issued still land: wait for them (bounded) before the block's
+            // shared memory goes away.
+            if (*(volatile uint32_t *)&sm->abort_flag)
+                for (uint32_t u = ix > (uint32_t)G_X_SLOTS ? ix - G_X_SLOTS : 0; u < ix; u++)
+                    for (uint32_t n = 0; n < WAIT_LIMIT && !mbar_try(&sm->full_x[u % G_X_SLOTS], (u / G_X_SLOTS) & 1); n++) {}
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t it_n = 0;
+            bool ok = true;
+            for (uint32_t i = 0; i < my_items && ok; i++) {
+                const uint32_t buf = i & 1, acc = tmem + buf * G_BN;
+                if (!(ok = mbar_wait(&sm->acc_empty[buf], ((i >> 1) & 1) ^ 1, sm, J.status))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (uint32_t k = 0; k < k_iters; k++, it_n++) {
+                    const uint32_t sw = it_n % G_STAGES, sx = it_n % G_X_SLOTS;
+                    if (!(ok = mbar_wait(&sm->full_w[sw], (it_n / G_STAGES) & 1, sm, J.status))) break;
+                    if (!(ok = mbar_wait(&sm->full_x[sx], (it_n / G_X_SLOTS) & 1, sm, J.status))) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t adesc = umma_desc(smem_u32(sm->x[sx])), bdesc = umma_desc(smem_u32(sm->w[sw]));
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; kk++) umma_bf16(acc, adesc + 2 * kk, bdesc + 2 * kk, G_IDESC, (k | kk) != 0);
+                    umma_commit(&sm->empty_x[sx]);
+                    umma_commit(&sm->empty_w[sw]);
+                }
+                if (ok) umma_commit(&sm->acc_full[buf]);
+            }
+            umma_commit(&sm->drain); // arrives when every MMA issued so far has completed
+        }
+    } else if (warp < 2 + G_PRODUCER_WARPS) {
+        // Thread p decodes weight row p / 2 of the tile, group p % 2 of every k-block.
+        const uint32_t p = threadIdx.x - 64, r = p >> 1, part = p & 1;
+        auto row_of = [&](uint32_t i) {
+            const Item it = item_at(i);
+            return J.w[it.set] + ((size_t)it.e * J.rows + min(it.n0 + r, J.rows - 1)) * J.pitch;
+        };
+        // The superblock whose bytes are fetched next: one ahead of the one being decoded, across item borders.
+        uint32_t n_i = 0, n_sb = 0;
+        const uint8_t *n_row = my_items ? row_of(0) : nullptr;
+        auto step_next = [&]() {
+            if (++n_sb == nblk) {
+                n_sb = 0;
+                if (++n_i < my_items) n_row = row_of(n_i);
+            }
+        };
+        uint32_t stage = 0, phase = 1;
+        bool go = true, live = false;
+        const uint32_t swz = r & 7;
+        auto emit = [&](const uint32_t (&v)[16]) {
+            // One lane waits and, below, arrives for the warp: hundreds of arrivals on one barrier would
+            // serialise in the shared-memory atomics.
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&sm->empty_w[stage], phase, sm, J.status);
+            if (!__all_sync(0xffffffffu, ok)) { go = false; return; }
+            uint8_t *dst = sm->w[stage] + r * 128;
+#pragma unroll
+            for (int u = 0; u < 4; u++) // the group's four 16-byte chunks, at their swizzled places
+                *reinterpret_cast<uint4 *>(dst + 16 * ((4 * part + u) ^ swz)) = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> tensor-core reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->full_w[stage]);
+            if (++stage == (uint32_t)G_STAGES) {
+                stage = 0;
+                phase ^= 1;
+            }
+        };
+        uint32_t v[16];
+        if constexpr (FMT == FQ_Q4_K) {
+            uint4 hdr = make_uint4(0, 0, 0, 0), hdr_next = hdr, qa[4], qb[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) qa[c] = qb[c] = make_uint4(0, 0, 0, 0);
+            if (my_items) {
+                const uint8_t *blk = n_row;
+                hdr = *reinterpret_cast<const uint4 *>(blk);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    qa[c] = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c);
+                    qb[c] = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
+                }
+                step_next();
+            }
+            const uint8_t *next = n_i < my_items ? n_row + (size_t)n_sb * 144 : nullptr;
+            if (next) hdr_next = *reinterpret_cast<const uint4 *>(next);
+            for (uint32_t i = 0; i < my_items && go; i++) {
+                live = item_at(i).n0 + r < J.rows;
+                for (uint32_t sb = 0; sb < nblk && go; sb++) {
+#define FQ_G_STEP(C)                                                                   \
+    if (go) {                                                                          \
+        g_decode_q4k<C>(hdr, qa[C], qb[C], part, live, v);                             \
+        if (next) {                                                                    \
+            qa[C] = *reinterpret_cast<const uint4 *>(next + 16 + 32 * C);              \
+            qb[C] = *reinterpret_cast<const uint4 *>(next + 32 + 32 * C);              \
+        }                                                                              \
+        emit(v);                                                                       \
+    }
+                    FQ_G_STEP(0) FQ_G_STEP(1) FQ_G_STEP(2) FQ_G_STEP(3)
+#undef FQ_G_STEP
+                    hdr = hdr_next;
+                    if (next) {
+                        step_next();
+                        next = n_i < my_items ? n_row + (size_t)n_sb * 144 : nullptr;
+                        if (next) hdr_next = *reinterpret_cast<const uint4 *>(next);
+                    }
+                }
+            }
+        } else {
+            // Per superblock: the sixteen scales and d; per 128-value half: 32 ql bytes (this group's) and 32 qh bytes.
+            uint4 sc = make_uint4(0, 0, 0, 0), sc_next = sc, ql[2][2], qh[2][2];
+            uint32_t d = 0, d_next = 0;
+#pragma unroll
+            for (int n = 0; n < 2; n++) ql[n][0] = ql[n][1] = qh[n][0] = qh[n][1] = make_uint4(0, 0, 0, 0);
+            auto load_half = [&](const uint8_t *row, uint32_t b, int n) {
+                const uint8_t *l = row + (size_t)b * 128 + 64 * n + 32 * part, *h = row + (size_t)nblk * 128 + (size_t)b * 64 + 32 * n;
+                ql[n][0] = *reinterpret_cast<const uint4 *>(l);
+                ql[n][1] = *reinterpret_cast<const uint4 *>(l + 16);
+                qh[n][0] = *reinterpret_cast<const uint4 *>(h);
+                qh[n][1] = *reinterpret_cast<const uint4 *>(h + 16);
+            };
+            if (my_items) {
+                sc = *reinterpret_cast<const uint4 *>(n_row + (size_t)nblk * 192);
+                d = *reinterpret_cast<const uint16_t *>(n_row + (size_t)nblk * 208);
+                load_half(n_row, 0, 0);
+                load_half(n_row, 0, 1);
+                step_next();
+            }
+            bool has_next = n_i < my_items;
+            const uint8_t *next_row = n_row;
+            uint32_t next_sb = n_sb;
+            if (has_next) {
+                sc_next = *reinterpret_cast<const uint4 *>(next_row + (size_t)nblk * 192 + (size_t)next_sb * 16);
+                d_next = *reinterpret_cast<const uint16_t *>(next_row + (size_t)nblk * 208 + (size_t)next_sb * 2);
+            }
+            for (uint32_t i = 0; i < my_items && go; i++) {
+                live = item_at(i).n0 + r < J.rows;
+                for (uint32_t sb = 0; sb < nblk && go; sb++) {
+                    // scales 8 n + 2 (2 H + part) and + 1: word 2 n + H of the sixteen, half `part` of it
+                    const uint32_t shift = 16 * part;
+#define FQ_G_HALF(N, W0, W1)                                                                                           \
+    if (go) {                                                                                                          \
+        g_decode_q6k<0>(ql[N][0], ql[N][1], qh[N][0], qh[N][1], (W0) >> shift, d, part, live, v);                      \
+        emit(v);                                                                                                       \
+    }                                                                                                                  \
+    if (go) {                                                                                                          \
+        g_decode_q6k<1>(ql[N][0], ql[N][1], qh[N][0], qh[N][1], (W1) >> shift, d, part, live, v);                      \
+        if (has_next) load_half(next_row, next_sb, N);                                                                 \
+        emit(v);                                                                                                       \
+    }
+                    FQ_G_HALF(0, sc.x, sc.y) FQ_G_HALF(1, sc.z, sc.w)
+#undef FQ_G_HALF
+                    sc = sc_next;
+                    d = d_next;
+                    if (has_next) {
+                        step_next();
+                        has_next = n_i < my_items;
+                        next_row = n_row;
+                        next_sb = n_sb;
+                        if (has_next) {
+                            sc_next = *reinterpret_cast<const uint4 *>(next_row + (size_t)nblk * 192 + (size_t)next_sb * 16);
+                            d_next = *reinterpret_cast<const uint16_t *>(next_row + (size_t)nblk * 208 + (size_t)next_sb * 2);
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // Epilogue: a warp may read the 32 tensor-memory lanes of quarter warp % 4: MMA rows 32 quarter + lane, i.e.
+        // activation row 16 quarter + lane / 2, term lane % 2.  Partner lanes exchange halves of each 32-column
+        // chunk, so that the even lane ends up with the sums of columns 0..15 and the odd lane with 16..31.
+        const int quarter = warp & 3;
+        const uint32_t lanes = (uint32_t)(32 * quarter) << 16, trow = 16 * quarter + (lane >> 1), half = lane & 1;
+        for (uint32_t i = 0; i < my_items; i++) {
+            const Item it = item_at(i);
+            const uint32_t buf = i & 1, acc = tmem + buf * G_BN + lanes;
+            if (!mbar_wait(&sm->acc_full[buf], (i >> 1) & 1, sm, J.status)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool valid = trow < it.cnt;
+            const float scale = valid ? __ldg(J.inv_scale + (it.m0 - J.row_begin) + trow) : 0.f;
+            float *yrow = J.y[it.set] + (size_t)(it.m0 + trow) * J.rows + it.n0 + 16 * half;
+            for (uint32_t c0 = 0; c0 < G_BN && it.n0 + c0 < J.rows; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(acc + c0, v);
+                float o[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const float keep = __uint_as_float(half ? v[16 + j] : v[j]), send = __uint_as_float(half ? v[j] : v[16 + j]);
+                    o[j] = (keep + __shfl_xor_sync(0xffffffffu, send, 1)) * scale;
+                }
+                if (valid && it.n0 + c0 + 16 * half < J.rows) { // rows is a multiple of 16
+#pragma unroll
+                    for (int j = 0; j < 4; j++) *reinterpret_cast<float4 *>(yrow + c0 + 4 * j) = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&sm->acc_empty[buf]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        // Outstanding MMAs must have finished before the accumulator columns are released.
+        if (lane == 0)
+            for (uint32_t n = 0; n < WAIT_LIMIT && !mbar_try(&sm->drain, 0); n++) {}
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
 }
 
 } // namespace
@@ -804,4 +1299,73 @@ int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t tot
                                  : launch_fmt<64, __nv_bfloat16, 1>(dev, a, map, b_bytes, total_rows);
     if (rc != FQ_OK) return rc;
     return fq_end_enqueue(dev, "gemm_tc_grouped", kernels);
+}
+
+// Expert-sorted rows, F32 in and out, on k_gemm_f16g: up to two matrix sets of one shape sharing the rows
+// (gate and up); `src`, `src_div`, `a[0].x_up` as for `fq_launch_gemv_nt_grouped`.  The fp16 copy of the rows
+// takes the whole activation scratch (this path enqueues plain launches only, so nothing before it still
+// reads the scratch and nothing after it writes early); more rows than it holds are served in several launches.
+int fq_launch_gemm_f16_grouped(fq_device *dev, const ProjectArgs *a, uint32_t count, uint32_t total_rows, const uint32_t *src, uint32_t src_div) {
+    const ProjectArgs &f = a[0];
+    if (count == 0 || count > 2 || f.cols % 256 || f.row_bytes % 16 || f.rows % 16 || !f.offsets || f.x_dtype != FQ_F32 || f.y_dtype != FQ_F32 || f.norm_w)
+        return FQ_ERR_UNSUPPORTED;
+    if (f.format != FQ_Q4_K && f.format != FQ_Q6_K) return FQ_ERR_UNSUPPORTED;
+    if (f.groups == 0 || f.groups > 65535 || f.experts > 65535 || total_rows < 16 || (src && src_div == 0)) return FQ_ERR_UNSUPPORTED;
+    for (uint32_t i = 1; i < count; i++)
+        if (a[i].format != f.format || a[i].cols != f.cols || a[i].rows != f.rows || a[i].row_bytes != f.row_bytes || a[i].x != f.x ||
+            a[i].x_up != f.x_up || a[i].offsets != f.offsets || a[i].slots != f.slots || a[i].groups != f.groups || a[i].experts != f.experts ||
+            a[i].x_dtype != FQ_F32 || a[i].y_dtype != FQ_F32 || a[i].norm_w)
+            return FQ_ERR_UNSUPPORTED;
+    // The fp16 copy of as many rows as the activation scratch holds at a time (whole 64-row steps; a group that
+    // straddles two launches is served in two parts).
+    const size_t per_row = (size_t)2 * f.cols * sizeof(__half) + sizeof(float);
+    uint32_t chunk = (uint32_t)std::min<size_t>(total_rows, dev->xprep_bytes / per_row);
+    if (chunk < total_rows) chunk &= ~(G_TOK - 1);
+    if (chunk < 16 || (uint64_t)chunk / G_TOK + f.groups > G_MAX_TILES) return FQ_ERR_UNSUPPORTED;
+    __half *xh = (__half *)dev->xprep;
+    float *inv_scale = (float *)((uint8_t *)dev->xprep + (size_t)2 * chunk * f.cols * sizeof(__half));
+    GJob J{};
+    J.count = count;
+    uint32_t tx = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        J.w[i] = a[i].w;
+        J.y[i] = (float *)a[i].y;
+        tx += (a[i].rows + G_BN - 1) / G_BN;
+        J.tx_end[i] = tx;
+    }
+    J.rows = f.rows;
+    J.cols = f.cols;
+    J.pitch = f.row_bytes;
+    J.experts = f.experts;
+    J.groups = f.groups;
+    J.offsets = f.offsets;
+    J.slots = f.slots;
+    J.inv_scale = inv_scale;
+    J.status = dev->status_dev;
+    const size_t smem = sizeof(GSmem) + 1024;
+    auto kernel = f.format == FQ_Q4_K ? k_gemm_f16g<FQ_Q4_K> : k_gemm_f16g<FQ_Q6_K>;
+    static bool configured[2] = {};
+    bool &done = configured[f.format == FQ_Q4_K ? 0 : 1];
+    if (!done) {
+        if (int rc = fq_check_cuda(dev, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemm shared memory")) return rc;
+        done = true;
+    }
+    int kernels = 0;
+    for (uint32_t r0 = 0; r0 < total_rows; r0 += chunk) {
+        const uint32_t r1 = std::min(total_rows, r0 + chunk), n = r1 - r0;
+        if (n < 16) { // too few rows for a TMA box: the last rows again with the ones before them
+            r0 = r1 - 16;
+        }
+        J.row_begin = r0;
+        J.row_end = r1;
+        k_split_f16<<<(r1 - r0 + 7) / 8, 256, 0, dev->stream>>>((const float *)f.x, f.x_up, src, src_div, f.offsets, f.groups, r0, r1, f.cols, xh, inv_scale);
+        CUtensorMap maps[3];
+        for (int i = 0; i < 3; i++)
+            if (int rc = make_map(dev, &maps[i], xh, f.cols, 2 * (r1 - r0), 32u << i, &J.box_bytes[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16)) return rc;
+        kernel<<<(unsigned)dev->sm_count, G_THREADS, smem, dev->stream>>>(maps[0], maps[1], maps[2], J);
+        if (int rc = fq_check_cuda(dev, cudaGetLastError(), "grouped fp16 gemm launch")) return rc;
+        kernels += 2;
+        if (r1 == total_rows) break;
+    }
+    return fq_end_enqueue(dev, "gemm_f16_grouped", kernels);
 }

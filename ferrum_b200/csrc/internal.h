@@ -167,6 +167,8 @@ int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a);
 int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count);
 // The same over expert-sorted activation rows (a.offsets / a.slots / a.groups / a.max_rows); F32 or BF16.
 int fq_launch_gemm_tc_grouped(fq_device *dev, const ProjectArgs &a, uint32_t total_rows);
+// The same rows on fp16 products with fp32-level activations (F32 in and out); arguments as fq_launch_gemv_nt_grouped.
+int fq_launch_gemm_f16_grouped(fq_device *dev, const ProjectArgs *a, uint32_t count, uint32_t total_rows, const uint32_t *src, uint32_t src_div);
 // Expert-sorted activations and the gated unit with bf16 results (inputs of the grouped tensor-core GEMM).
 // `range` (may be null) limits the work to rows [range[0], range[stride]): the experts one rank owns.
 int fq_launch_moe_gather_bf16(fq_device *dev, const float *x, const uint32_t *sorted, uint32_t hidden, uint32_t used, uint32_t routes,
