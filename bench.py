@@ -159,6 +159,11 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
     if world > 1:
+        # stdout carries one JSON line: whatever libraries print meanwhile (NCCL's version banner when NCCL_DEBUG
+        # asks for one) goes to stderr, until the line itself is printed.
+        sys.stdout.flush()
+        stdout_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     # The library enqueues on its own stream; torch sees that stream as an ExternalStream so that
     # CUDA events are recorded on the stream the kernels are launched on.
@@ -495,6 +500,10 @@ def run_ours(args):
             out["e2e"] = e2e
             out["tp_m8"] = tp_m8
             out["moe_ffn_ep"] = ep
+    if world > 1:
+        sys.stdout.flush()
+        os.dup2(stdout_fd, 1)
+        os.close(stdout_fd)
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
@@ -535,10 +544,10 @@ def tp_parity(S, dev, torch, dist, comm, layer0, full0, x_host, x_dev, y_dev, y_
 
 
 def ep_parity(S, dev, torch, dist, rank, world):
-    """The expert-parallel MoE block (config 3 geometry, 40 tokens) against the single-GPU block on the same
-    weights: bit for bit."""
+    """The expert-parallel MoE block (config 3 geometry; 40 tokens: the integer grouped kernel, and 1024 tokens:
+    the fp16 tensor-core one) against the single-GPU block on the same weights: bit for bit."""
     from ferrum_b200 import tp
-    H, E, F, USED, T = 2048, 256, 512, 8, 40
+    H, E, F, USED = 2048, 256, 512, 8
     local = E // world
     M = S.Matrix.from_packed
     full = {k: random_matrix(fmt, rows, cols, seed) for k, (fmt, rows, cols, seed) in
@@ -549,24 +558,29 @@ def ep_parity(S, dev, torch, dist, rank, world):
                     M(dev, F, H, local, Q4_K, tp.shard_experts(full["up"], Q4_K, F, H, E, rank, world)),
                     M(dev, H, F, local, Q6_K, tp.shard_experts(full["down"], Q6_K, H, F, E, rank, world)),
                     shared[1], shared[2], shared[3], None, E, USED, H, F, F, False, True)
-    torch.manual_seed(11)
-    x = (torch.randn(T * H, device="cuda") * 0.12).contiguous()
-    comm = S.Comm(dev, rank, world, 4096 + T * USED * H * 4 + 64 * H * 4)
-    scratch = torch.zeros(S.moe_ffn_scratch_elems(dev, mine, T), dtype=torch.float32, device="cuda")
-    out = torch.zeros(T * H, dtype=torch.float32, device="cuda")
-    S.moe_ffn_ep(dev, comm, 4096, mine, rank * local, x, T, scratch, out)
-    dev.synchronize()
-    equal = True
+    whole = None
     if rank == 0:
         whole = S.MoeFfn(shared[0], M(dev, F, H, E, Q4_K, full["gate"]), M(dev, F, H, E, Q4_K, full["up"]), M(dev, H, F, E, Q6_K, full["down"]),
                          shared[1], shared[2], shared[3], None, E, USED, H, F, F, False, True)
-        ref_out = torch.zeros(T * H, dtype=torch.float32, device="cuda")
-        S.moe_ffn(dev, whole, x, T, torch.zeros(S.moe_ffn_scratch_elems(dev, whole, T), dtype=torch.float32, device="cuda"), ref_out)
+    widths = (40, 1024)
+    equal = True
+    for T in widths:
+        torch.manual_seed(11 + T)
+        x = (torch.randn(T * H, device="cuda") * 0.12).contiguous()
+        comm = S.Comm(dev, rank, world, 8192 + T * USED * H * 4 + (T + 8 * world) * H * 4)
+        scratch = torch.zeros(S.moe_ffn_scratch_elems(dev, mine, T), dtype=torch.float32, device="cuda")
+        out = torch.zeros(T * H, dtype=torch.float32, device="cuda")
+        S.moe_ffn_ep(dev, comm, 4096, mine, rank * local, x, T, scratch, out)
         dev.synchronize()
-        equal = bool(torch.equal(out, ref_out))
-    dist.barrier()
-    comm.close()
-    return {"ep_bits_equal": equal, "ep_checked": f"fq_moe_ffn_ep ({E} experts over {world} ranks, {T} tokens) against fq_moe_ffn on rank 0"}
+        if rank == 0:
+            ref_out = torch.zeros(T * H, dtype=torch.float32, device="cuda")
+            S.moe_ffn(dev, whole, x, T, torch.zeros(S.moe_ffn_scratch_elems(dev, whole, T), dtype=torch.float32, device="cuda"), ref_out)
+            dev.synchronize()
+            equal = equal and bool(torch.equal(out, ref_out))
+        dist.barrier()
+        comm.close()
+    return {"ep_bits_equal": equal,
+            "ep_checked": f"fq_moe_ffn_ep ({E} experts over {world} ranks, {' and '.join(str(t) for t in widths)} tokens) against fq_moe_ffn on rank 0"}
 
 
 def moe_ep_bench(S, dev, stream, torch, dist, timed_ms, rank, world):
