@@ -572,18 +572,26 @@ __global__ void k_to_bf16(const float *__restrict__ x, __nv_bfloat16 *__restrict
 }
 
 // X (fp32) as two bf16 terms laid out for MODE 2: k-block b of a row becomes the three 64-wide blocks
-// hi, lo, hi at 3 b, 3 b + 1, 3 b + 2, with hi = bf16(x) and lo = bf16(x - hi).
+// hi, lo, hi at 3 b, 3 b + 1, 3 b + 2, with hi = bf16(x) and lo = bf16(x - hi).  One thread per eight
+// consecutive values (cols is a multiple of 64): two 16-byte loads, three 16-byte stores.
 __global__ void k_split3(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, uint32_t cols, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (i >= n) return;
     const size_t row = i / cols;
     const uint32_t k = (uint32_t)(i % cols), b = k / BK, j = k % BK;
-    const float v = x[i];
-    const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+    const float4 v0 = *reinterpret_cast<const float4 *>(x + i), v1 = *reinterpret_cast<const float4 *>(x + i + 4);
+    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * u]), h1 = __float2bfloat16_rn(v[2 * u + 1]);
+        hi[u] = pack_bf16(__bfloat162float(h0), __bfloat162float(h1));
+        lo[u] = pack_bf16(v[2 * u] - __bfloat162float(h0), v[2 * u + 1] - __bfloat162float(h1));
+    }
     __nv_bfloat16 *dst = out + row * (size_t)cols * 3 + (size_t)b * 3 * BK + j;
-    dst[0] = hi;
-    dst[BK] = lo;
-    dst[2 * BK] = hi;
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4 *>(dst + BK) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    *reinterpret_cast<uint4 *>(dst + 2 * BK) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
 }
 
 // The tiles that were split along K: their fp32 partial sums added in split order (deterministic), rounded and
@@ -1223,7 +1231,7 @@ int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
         dev->xprep_turn ^= 1u;
         __nv_bfloat16 *x3 = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? half : 0));
         const size_t n = (size_t)mm * a.cols;
-        k_split3<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>((const float *)a.x + (size_t)m0 * a.cols, x3, a.cols, n);
+        k_split3<<<(unsigned)((n / 8 + 255) / 256), 256, 0, dev->stream>>>((const float *)a.x + (size_t)m0 * a.cols, x3, a.cols, n);
         if (int rc = make_map(dev, &map, x3, a.cols * 3, mm, 256, &b_bytes)) return rc;
         ProjectArgs s = a;
         s.m = mm;
@@ -1266,7 +1274,7 @@ int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
         dev->xprep_turn ^= 1u;
         __nv_bfloat16 *x3 = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0));
         const size_t n = (size_t)f.m * f.cols;
-        k_split3<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>((const float *)f.x, x3, f.cols, n);
+        k_split3<<<(unsigned)((n / 8 + 255) / 256), 256, 0, dev->stream>>>((const float *)f.x, x3, f.cols, n);
         if (int rc = make_map(dev, &map, x3, f.cols * 3, f.m, 256, &b_bytes)) return rc;
         const int rc = f.m >= 384 ? launch_fmt<512, float, 2>(dev, f, map, b_bytes, f.m, many) : launch_fmt<256, float, 2>(dev, f, map, b_bytes, f.m, many);
         if (rc != FQ_OK) return rc;
