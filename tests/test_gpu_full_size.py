@@ -92,10 +92,12 @@ def config3():
     return experts, used, hidden, ef, mats
 
 
-@pytest.mark.parametrize("tokens", [1, 1024])
+@pytest.mark.parametrize("tokens", [1, 640, 1024, 2048])
 def test_config3_moe_block(device, config3, tokens):
     """35B-A3B-class block: 256 experts + shared, top-8, hidden 2048, expert width 512.  T = 1 takes the per-route
-    projections, T = 1024 the grouped kernel over expert-sorted rows; sampled tokens against the oracle."""
+    projections, T = 640 (20 rows per expert) the integer grouped kernel over expert-sorted rows, T = 1024 the fp16
+    tensor-core grouped kernel, T = 2048 the same in two launches (the fp16 copy of the 16384 gathered rows does not
+    fit the activation scratch at once); sampled tokens against the oracle."""
     s = S()
     experts, used, hidden, ef, mats = config3
     M = s.Matrix.from_packed
@@ -380,9 +382,11 @@ def test_profile_table_names_times_and_clears(device):
 
 @pytest.mark.parametrize("fmt,rows_e,cols", [(ref.Q4_K, 512, 2048), (ref.Q6_K, 2048, 512), (ref.Q4_K, 200, 768), (ref.Q6_K, 136, 256)])
 def test_grouped_rows_at_about_thirty_to_an_expert(device, fmt, rows_e, cols):
-    """`project_mm_id` with about 30 rows per expert (config 3's grouped widths) runs on the integer kernel: exact
-    integer products of the decoded weights with 16-bit activations, so the fp32 GEMV bar applies.  Uneven groups,
-    an empty expert, a group of more than 32 rows, weight-row counts that are not a multiple of 16 x 8."""
+    """`project_mm_id` with about 30 rows per expert (config 3's grouped widths): the fp16 tensor-core kernel
+    (weights within 2^-11 of their value, activations to 22 bits) where the weight-row count is a multiple of 16,
+    the integer kernel (exact integer products with 16-bit activations) elsewhere; the fp32 GEMV bar applies to
+    both.  Uneven groups, an empty expert, a group of more than 32 rows, weight-row counts that are not a
+    multiple of 16 x 8."""
     s = S()
     experts, routes = 24, 24 * 30
     packed = ref.random_matrix(fmt, experts * rows_e, cols, seed=71)
@@ -402,6 +406,36 @@ def test_grouped_rows_at_about_thirty_to_an_expert(device, fmt, rows_e, cols):
     worst = 0.0
     for r in rng.choice(routes, 40, replace=False):
         e = int(ids[r])
+        want = ref.matmul(fmt, packed[e * rows_e * rb:(e + 1) * rows_e * rb], rows_e, cols, x[r], 1)[0]
+        worst = max(worst, np.abs(got[r] - want).max() / np.abs(want).max())
+    assert worst <= TOL_F32, worst
+
+
+@pytest.mark.parametrize("fmt,rows_e,cols", [(ref.Q4_K, 512, 2048), (ref.Q6_K, 208, 512), (ref.Q4_K, 400, 256)])
+def test_grouped_rows_on_the_fp16_kernel(device, fmt, rows_e, cols):
+    """`project_mm_id` at about 70 rows per expert: groups of more than 64 rows (two activation tiles), of exactly
+    64, of one row, an empty one; weight-row counts that end inside a 256-row tile; expert slots.  fp32 GEMV bar."""
+    s = S()
+    experts = 12
+    counts = np.array([70, 0, 150, 64, 1, 65, 33, 128, 90, 17, 100, 122], dtype=np.int64)
+    routes = int(counts.sum())
+    packed = ref.random_matrix(fmt, experts * rows_e, cols, seed=81)
+    w = s.Matrix.from_packed(device, rows_e, cols, experts, fmt, packed)
+    rng = np.random.default_rng(82)
+    slots = rng.permutation(experts).astype(np.uint32)   # group z is served by expert slots[z]
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32)
+    group_of = np.repeat(np.arange(experts), counts)
+    x = (rng.standard_normal((routes, cols)) * np.exp(rng.uniform(-6, 6, (routes, 1)))).astype(np.float32)  # rows of very different scale
+    y = torch.full((routes * rows_e,), float("nan"), dtype=torch.float32, device="cuda")
+    s.project_mm_id_in(device, w, dev_f32(x), dev_u32(offsets), (dev_u32(slots), experts), int(counts.max()), y)
+    device.synchronize()
+    got = host(y).reshape(routes, rows_e)
+    assert np.isfinite(got).all()
+    rb = ref.row_bytes(fmt, cols)
+    worst = 0.0
+    picks = list(rng.choice(routes, 30, replace=False)) + [int(offsets[2]), int(offsets[3]) - 1, int(offsets[4]), routes - 1]
+    for r in picks:
+        e = int(slots[group_of[r]])
         want = ref.matmul(fmt, packed[e * rows_e * rb:(e + 1) * rows_e * rb], rows_e, cols, x[r], 1)[0]
         worst = max(worst, np.abs(got[r] - want).max() / np.abs(want).max())
     assert worst <= TOL_F32, worst
