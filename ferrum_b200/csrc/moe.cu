@@ -1,6 +1,7 @@
 // Mixture-of-experts glue: routing, expert-major map, gather, combine and the gated unit.
 // Contracts follow the reference kernels h_moe_route / h_moe_map / h_moe_gather / h_moe_combine /
 // h_swiglu (src/metal/shaders/hybrid.metal:2252-2388, 1606-1613).
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
 #include "gemv_common.cuh"
@@ -238,6 +239,142 @@ k_moe_map(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, u
     for (uint32_t i = total[experts] + tid; i < routes; i += 1024) sorted[i] = 0;
 }
 
+// The same map for many routes: a cluster of MAP_CLUSTER blocks, block c owning the contiguous run
+// [c * S, (c + 1) * S) of routes (S a multiple of 1024) and its warps contiguous slices of that, so that the order of
+// equal experts is the order of the routes, as above.  Every block counts its own routes, the blocks read one
+// another's per-expert totals through distributed shared memory, and each then knows where its warps' routes go.
+constexpr int MAP_CLUSTER = 8;
+constexpr uint32_t MAP_CLUSTER_MIN_ROUTES = 4096;
+__global__ void __cluster_dims__(MAP_CLUSTER, 1, 1) __launch_bounds__(1024)
+k_moe_map_cluster(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, uint32_t *__restrict__ offsets,
+                  uint32_t *__restrict__ sorted, uint32_t *__restrict__ position) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ uint32_t cnt[]; // [32][experts], block totals [experts], expert offsets [experts + 1]
+    uint32_t *mine = cnt + 32 * experts, *total = mine + experts;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, rank = cluster.block_rank();
+    const uint32_t per_block = ((routes + MAP_CLUSTER - 1) / MAP_CLUSTER + 1023) / 1024 * 1024, slice = per_block / 32;
+    const uint32_t begin = min(routes, rank * per_block + warp * slice), end = min(routes, begin + slice);
+    const bool cached = slice <= 32u * MAP_CACHED;
+    uint32_t ev[MAP_CACHED];
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < MAP_CACHED; i++) {
+            const uint32_t r = begin + 32u * i + lane;
+            ev[i] = r < end ? ids[r] : 0xffffffffu;
+        }
+    }
+    for (uint32_t i = tid; i < 32 * experts; i += 1024) cnt[i] = 0;
+    __syncthreads();
+    const int id_bits = 32 - __clz((int)experts - 1);
+    auto same_as = [&](uint32_t e, bool valid) { // lanes of the warp that hold the same (valid) expert id
+        uint32_t peers = __ballot_sync(0xffffffffu, valid);
+        for (int b = 0; b < id_bits; b++) {
+            const bool bit = (e >> b) & 1u;
+            const uint32_t bal = __ballot_sync(0xffffffffu, bit);
+            peers &= bit ? bal : ~bal;
+        }
+        return peers;
+    };
+    auto count_one = [&](uint32_t e, bool live) {
+        const bool valid = live && e < experts;
+        const uint32_t peers = same_as(e, valid);
+        if (valid && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
+        __syncwarp();
+    };
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < MAP_CACHED; i++)
+            if (begin + 32u * i < end) count_one(ev[i], begin + 32u * i + lane < end);
+    } else {
+        for (uint32_t base = begin; base < end; base += 32) {
+            const bool live = base + lane < end;
+            count_one(live ? ids[base + lane] : 0xffffffffu, live);
+        }
+    }
+    __syncthreads();
+    for (uint32_t e = tid; e < experts; e += 1024) {
+        uint32_t n = 0;
+        for (int w = 0; w < 32; w++) n += cnt[w * experts + e];
+        mine[e] = n;
+    }
+    cluster.sync(); // every block's totals are in place
+    // Per expert: the routes of all blocks, and of the blocks before this one.
+    uint32_t before = 0, all = 0; // of expert tid (experts <= 1024 = the block's threads)
+    if (tid < experts) {
+        for (uint32_t c = 0; c < (uint32_t)MAP_CLUSTER; c++) {
+            const uint32_t n = cluster.map_shared_rank(mine, c)[tid];
+            if (c < rank) before += n;
+            all += n;
+        }
+    }
+    // Exclusive scan of `all` over the experts: within warps by shuffles, across warps through `total`.
+    uint32_t incl = all;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= (uint32_t)off) incl += o;
+    }
+    __shared__ uint32_t warp_sum_of[32];
+    if (lane == 31) warp_sum_of[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t v = warp_sum_of[lane], inc = v;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= (uint32_t)off) inc += o;
+        }
+        warp_sum_of[lane] = inc - v;
+    }
+    __syncthreads();
+    const uint32_t first = warp_sum_of[warp] + incl - all; // the expert's first row
+    if (tid < experts) {
+        total[tid] = first;
+        if (rank == 0) offsets[tid] = first;
+    }
+    if (tid == experts - 1) {
+        total[experts] = first + all;
+        if (rank == 0) offsets[experts] = first + all;
+    }
+    // Where each warp's next route of the expert goes.
+    if (tid < experts) {
+        uint32_t at = first + before;
+        for (int w = 0; w < 32; w++) {
+            const uint32_t n = cnt[w * experts + tid];
+            cnt[w * experts + tid] = at;
+            at += n;
+        }
+    }
+    __syncthreads();
+    auto place_one = [&](uint32_t r, uint32_t e, bool live) {
+        const uint32_t peers = same_as(e, live && e < experts);
+        if (live && e < experts) {
+            const uint32_t at = cnt[warp * experts + e] + __popc(peers & ((1u << lane) - 1));
+            sorted[at] = r;
+            position[r] = at;
+        } else if (live) {
+            position[r] = 0; // an id that names no expert: the route belongs to no row
+        }
+        __syncwarp();
+        if (live && e < experts && lane == (uint32_t)(__ffs(peers) - 1)) cnt[warp * experts + e] += __popc(peers);
+        __syncwarp();
+    };
+    if (cached) {
+#pragma unroll
+        for (int i = 0; i < MAP_CACHED; i++)
+            if (begin + 32u * i < end) place_one(begin + 32u * i + lane, ev[i], begin + 32u * i + lane < end);
+    } else {
+        for (uint32_t base = begin; base < end; base += 32) {
+            const bool live = base + lane < end;
+            place_one(base + lane, live ? ids[base + lane] : 0xffffffffu, live);
+        }
+    }
+    // Rows past the last expert's (only there when some id named no expert) point at route 0.
+    for (uint32_t i = total[experts] + rank * 1024 + tid; i < routes; i += MAP_CLUSTER * 1024) sorted[i] = 0;
+    cluster.sync(); // no block leaves while another may still read its totals
+}
+
 // The same map for at most 32 routes (a decode step's), by one warp: lane r ranks its route among the others.
 __global__ void __launch_bounds__(32)
 k_moe_map_small(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, uint32_t *__restrict__ offsets,
@@ -435,6 +572,18 @@ extern "C" int fq_moe_map(fq_device *dev, const uint32_t *ids, uint32_t experts,
     if (int rc = fq_check_binding(dev, position, (size_t)routes * 4, "position")) return rc;
     if (routes <= 32) {
         k_moe_map_small<<<1, 32, 0, dev->stream>>>(ids, experts, routes, offsets, sorted, position);
+        return fq_end_enqueue(dev, "moe_map", 1);
+    }
+    if (routes >= MAP_CLUSTER_MIN_ROUTES) { // enough routes for eight blocks to beat one
+        const size_t smem = ((size_t)34 * experts + 1) * sizeof(uint32_t);
+        static bool configured = false;
+        if (smem > 48 * 1024 && !configured) {
+            cudaError_t e = cudaFuncSetAttribute(k_moe_map_cluster, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return fq_check_cuda(dev, e, "moe_map shared memory");
+            configured = true;
+        }
+        k_moe_map_cluster<<<MAP_CLUSTER, 1024, smem, dev->stream>>>(ids, experts, routes, offsets, sorted, position);
+        if (int rc = fq_check_cuda(dev, cudaGetLastError(), "moe_map launch")) return rc;
         return fq_end_enqueue(dev, "moe_map", 1);
     }
     const size_t smem = ((size_t)33 * experts + 1) * sizeof(uint32_t);

@@ -291,7 +291,34 @@ def test_moe_route_top8_of_256_for_1024_tokens(device):
     assert np.allclose(host(wts).reshape(m, used).sum(1), 1.0, atol=1e-5)
 
 
-@pytest.mark.parametrize("experts,routes", [(3, 8), (256, 8), (1000, 32), (7, 5), (256, 8192), (256, 40), (1000, 777)])
+@pytest.mark.parametrize("routes", [24, 40, 3000, 6000, 66000])
+def test_moe_map_with_ids_that_name_no_expert(device, routes):
+    """Routes whose id is not an expert belong to no row: position 0, and the rows past the last expert's point at
+    route 0 (one warp, one block and the cluster of blocks)."""
+    s = S()
+    experts = 19
+    rng = np.random.default_rng(routes)
+    ids = rng.integers(0, experts, routes).astype(np.uint32)
+    bad = rng.choice(routes, max(1, routes // 7), replace=False)
+    ids[bad] = rng.integers(experts, 2**32 - 1, bad.size, dtype=np.uint64).astype(np.uint32)
+    offsets = torch.full((experts + 1,), -1, dtype=torch.int32, device="cuda")
+    sorted_ = torch.full((routes,), -1, dtype=torch.int32, device="cuda")
+    position = torch.full((routes,), -1, dtype=torch.int32, device="cuda")
+    s.moe_map(device, dev_u32(ids), experts, routes, offsets, sorted_, position)
+    device.synchronize()
+    valid = ids < experts
+    order = np.argsort(ids[valid], kind="stable")
+    want_sorted = np.flatnonzero(valid)[order].astype(np.uint32)
+    got_o, got_s, got_p = (t.cpu().numpy().view(np.uint32) for t in (offsets, sorted_, position))
+    assert np.array_equal(got_o, np.concatenate([[0], np.cumsum(np.bincount(ids[valid], minlength=experts))]).astype(np.uint32))
+    assert np.array_equal(got_s[:want_sorted.size], want_sorted)
+    assert not got_s[want_sorted.size:].any()
+    assert np.array_equal(got_p[want_sorted], np.arange(want_sorted.size, dtype=np.uint32))
+    assert not got_p[~valid].any()
+
+
+@pytest.mark.parametrize("experts,routes", [(3, 8), (256, 8), (1000, 32), (7, 5), (256, 8192), (256, 40), (1000, 777), (256, 4096),
+                                            (1000, 5000), (37, 70001), (5, 300000)])
 def test_moe_map_gather_combine(device, experts, routes):
     s = S()
     rng = np.random.default_rng(routes)
