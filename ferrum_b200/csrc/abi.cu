@@ -1004,10 +1004,15 @@ static int side_join(SideBranch &b) {
 // With `ids` (routes, one activation row each) W is an expert stack.
 // `combine` (routes only): the projection also carries out the weighted sum over each token's routes; `*combined`
 // tells whether it did (else the caller combines).
+// `route_map` (with `ids`; may be null): output row r takes the expert ids[route_map[r]] - id_base, rows whose expert
+// the matrix does not hold are skipped; only the decode kernel does that (FQ_ERR_UNSUPPORTED otherwise, nothing
+// enqueued).
 static int project_gated(fq_device *dev, const fq_matrix *w, const float *g, const float *u, float *act, size_t rows_x, const uint32_t *ids,
-                         float *y, const CombineTail *combine = nullptr, bool *combined = nullptr) {
+                         float *y, const CombineTail *combine = nullptr, bool *combined = nullptr, const uint32_t *route_map = nullptr,
+                         uint32_t id_base = 0) {
     const size_t width = w->cols, rows_e = w->expert_rows();
     if (combined) *combined = false;
+    if (route_map && (dev->exact || !ids)) return FQ_ERR_UNSUPPORTED;
     if (!dev->exact) {
         if (int rc = fq_begin_enqueue(dev)) return rc;
         if (int rc = fq_check_binding(dev, g, rows_x * width * 4, "gate")) return rc;
@@ -1019,9 +1024,12 @@ static int project_gated(fq_device *dev, const fq_matrix *w, const float *g, con
         if (ids) {
             a.ids = ids;
             a.x_div = 1;
+            a.route_map = route_map;
+            a.id_base = id_base;
         } else {
             a.rows = (uint32_t)w->rows;
         }
+        if (route_map) return fq_launch_gemv_i8_many(dev, &a, 1);
         if (ids && combine) {
             a.combine = combine;
             const int rc = fq_launch_gemv_i8_many(dev, &a, 1);
@@ -1040,22 +1048,30 @@ static int project_gated(fq_device *dev, const fq_matrix *w, const float *g, con
 }
 
 // Two expert stacks of one shape (gate and up) on the same routes: one launch at decode widths.
+// `route_map` (may be null): output row r takes route route_map[r] -- its activation row route_map[r] / x_div and
+// the expert ids[route_map[r]] - id_base; rows whose expert the matrices do not hold are skipped.  Only the decode
+// kernel does that (FQ_ERR_UNSUPPORTED otherwise, nothing enqueued).
 static int project_id_pair(fq_device *dev, const fq_matrix *w0, const fq_matrix *w1, const float *x, size_t x_elems, const uint32_t *ids,
-                           size_t routes, size_t x_div, float *y0, float *y1) {
-    if (!dev->exact && w0->format == w1->format && w0->cols == w1->cols && w0->expert_rows() == w1->expert_rows() && w0->experts == w1->experts) {
+                           size_t routes, size_t x_div, float *y0, float *y1, const uint32_t *route_map = nullptr, uint32_t id_base = 0) {
+    const bool alike = w0->format == w1->format && w0->cols == w1->cols && w0->expert_rows() == w1->expert_rows() && w0->experts == w1->experts;
+    if (route_map && (dev->exact || !alike)) return FQ_ERR_UNSUPPORTED;
+    if (!dev->exact && alike) {
         if (int rc = fq_begin_enqueue(dev)) return rc;
         ProjectArgs a[2] = {base_args(w0, x, FQ_F32, y0, FQ_F32), base_args(w1, x, FQ_F32, y1, FQ_F32)};
         for (ProjectArgs &p : a) {
             p.m = (uint32_t)routes;
             p.ids = ids;
             p.x_div = (uint32_t)x_div;
+            p.route_map = route_map;
+            p.id_base = id_base;
+            p.map_x = route_map != nullptr;
         }
         if (int rc = fq_check_binding(dev, x, x_elems * 4, "x")) return rc;
         if (int rc = fq_check_binding(dev, ids, routes * 4, "ids")) return rc;
         if (int rc = fq_check_binding(dev, y0, routes * w0->expert_rows() * 4, "y")) return rc;
         if (int rc = fq_check_binding(dev, y1, routes * w1->expert_rows() * 4, "y")) return rc;
         const int rc = fq_launch_gemv_i8_many(dev, a, 2);
-        if (rc != FQ_ERR_UNSUPPORTED) return rc;
+        if (rc != FQ_ERR_UNSUPPORTED || route_map) return rc;
     }
     if (int rc = fq_project_id(dev, w0, x, x_elems, ids, routes, x_div, y0, routes * w0->expert_rows())) return rc;
     return fq_project_id(dev, w1, x, x_elems, ids, routes, x_div, y1, routes * w1->expert_rows());
@@ -1253,16 +1269,27 @@ extern "C" int fq_moe_ffn_ep(fq_device *dev, fq_comm *comm, size_t region_offset
         rc = rc ? rc : r;
     }
     if (!rc)
-        rc = fq_moe_route(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m, f->sigmoid,
-                          f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate);
-    if (!rc) rc = fq_moe_map(dev, s.ids, (uint32_t)experts, (uint32_t)routes, s.offsets, s.sorted, s.position);
+        rc = fq_moe_route_map(dev, s.logits, x, shared_w, (uint32_t)experts, (uint32_t)used, (uint32_t)hidden, (uint32_t)m, f->sigmoid,
+                              f->norm_weights, f->shared_gate_inp != nullptr, s.ids, s.weights, s.gate, s.offsets, s.sorted, s.position);
     const uint32_t *mine = s.offsets + expert_first; // mine[0] .. mine[local]: this rank's run of rows
     if (!rc && (routes <= MV_ID_MAX_ROUTES || dev->exact)) {
-        uint32_t *local_ids = (uint32_t *)s.logits; // the logits are consumed by now, and routes <= m * experts
-        rc = fq_moe_gather(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg);
-        if (!rc) rc = fq_launch_moe_local_ids(dev, s.ids, s.sorted, (uint32_t)routes, expert_first, (uint32_t)local, local_ids);
-        if (!rc) rc = project_id_pair(dev, f->gate_exps, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, s.u);
-        if (!rc) rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, local_ids, down);
+        // The decode kernel reads the map itself: sorted row r is route sorted[r] (token sorted[r] / used, expert
+        // ids[sorted[r]] - expert_first), and rows of other ranks' experts are skipped.  Where it does not serve the
+        // shapes: gather the rows and translate the ids first.
+        int fast = project_id_pair(dev, f->gate_exps, f->up_exps, x, m * hidden, s.ids, routes, used, s.g, s.u, s.sorted, expert_first);
+        if (fast == FQ_OK) {
+            fast = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, s.ids, down, nullptr, nullptr, s.sorted, expert_first);
+            if (fast != FQ_ERR_UNSUPPORTED) rc = fast;
+        } else if (fast != FQ_ERR_UNSUPPORTED) {
+            rc = fast;
+        }
+        if (fast == FQ_ERR_UNSUPPORTED) {
+            uint32_t *local_ids = (uint32_t *)s.logits; // the logits are consumed by now, and routes <= m * experts
+            rc = fq_moe_gather(dev, x, s.sorted, (uint32_t)hidden, (uint32_t)used, (uint32_t)routes, s.xg);
+            if (!rc) rc = fq_launch_moe_local_ids(dev, s.ids, s.sorted, (uint32_t)routes, expert_first, (uint32_t)local, local_ids);
+            if (!rc) rc = project_id_pair(dev, f->gate_exps, f->up_exps, s.xg, routes * hidden, local_ids, routes, 1, s.g, s.u);
+            if (!rc) rc = project_gated(dev, f->down_exps, s.g, s.u, s.act, routes, local_ids, down);
+        }
     } else if (!rc && (rc = moe_experts_f32(dev, f, x, s, mine, (uint32_t)local, routes, down)) != FQ_ERR_UNSUPPORTED) {
         // done (or failed) on the integer or the fp16 kernel
     } else if (!rc || rc == FQ_ERR_UNSUPPORTED) {

@@ -374,7 +374,8 @@ template <int FMT, int MT, bool INP = false>
 __global__ void __launch_bounds__(MT >= 3 ? 256 : MT == 2 ? 384 : MAX_WARPS * 32)
 k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *__restrict__ prep, PrepI8 L,
           const uint32_t *__restrict__ ids, uint32_t x_div, uint32_t experts, const __grid_constant__ TpPush P,
-          const float *__restrict__ xin, const float *__restrict__ xup, const __grid_constant__ CombineTail C) {
+          const float *__restrict__ xin, const float *__restrict__ xup, const __grid_constant__ CombineTail C,
+          const uint32_t *__restrict__ route_map, uint32_t id_base, bool map_x) {
     using Raw = typename RawOf<FMT>::type;
     static_assert(!INP || MT == 1, "in-kernel preparation serves one activation row per route");
     extern __shared__ __align__(16) uint8_t own_act[]; // INP: the route's prepared row
@@ -388,13 +389,15 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     // already in flight while the current one is reduced and stored.
     const uint32_t total_tiles = T.tile_end[T.count - 1];
     size_t expert_off = 0, y_base = 0;
+    uint32_t x_row = 0; // the route's activation row
     if (ids) {
-        pdl_wait(); // the routing that wrote `ids` must have completed
-        const uint32_t r = blockIdx.y;
-        const uint32_t e = ids[r];
+        pdl_wait(); // the routing that wrote `ids` (and the map) must have completed
+        const uint32_t r = blockIdx.y, src = route_map ? route_map[r] : r;
+        const uint32_t e = ids[src] - id_base; // wraps to a value no matrix has when the expert is below id_base
         if (e >= experts) return;
         expert_off = (size_t)e * T.rows[0] * pitch;
-        if constexpr (!INP) prep += (size_t)(r / x_div) * L.token_bytes;
+        x_row = (map_x ? src : r) / x_div;
+        if constexpr (!INP) prep += (size_t)x_row * L.token_bytes;
         y_base = (size_t)r * T.rows[0];
     }
     struct Tile {
@@ -432,7 +435,7 @@ k_gemv_i8(const __grid_constant__ GemvTargets T, uint32_t pitch, const uint8_t *
     pdl_wait();
     const uint32_t seq = P.world > 1 ? tp_seq(P) : 0u;
     if constexpr (INP) {
-        const size_t xr = (size_t)(blockIdx.y / x_div) * L.cols;
+        const size_t xr = (size_t)x_row * L.cols;
         for (uint32_t b = warp; b < nblk; b += WARPS) prep_superblock(xin + xr, b, b, lane, L, own_act, xup ? xup + xr : nullptr, nullptr, 0.f);
         __syncthreads();
         prep = own_act;
@@ -835,7 +838,7 @@ cudaError_t launch(fq_device *dev, const ProjectArgs *a, uint32_t count, const u
     CombineTail tail{};
     if (expert && a[0].combine) tail = *a[0].combine;
     return launch_pdl(k_gemv_i8<FMT, MT, INP>, grid, dim3(warps * 32), INP ? L.token_bytes : 0, dev->stream, T, a[0].row_bytes, prep, L, a[0].ids,
-                      a[0].x_div, a[0].experts, push, (const float *)a[0].x, a[0].x_up, tail);
+                      a[0].x_div, a[0].experts, push, (const float *)a[0].x, a[0].x_up, tail, a[0].route_map, a[0].id_base, a[0].map_x);
 }
 
 } // namespace
@@ -849,9 +852,10 @@ int fq_launch_gemv_i8_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
     for (uint32_t i = 1; i < count; i++)
         if (a[i].format != f.format || a[i].cols != f.cols || a[i].x != f.x || a[i].x_up != f.x_up || a[i].norm_w != f.norm_w || a[i].m != f.m || a[i].ids != f.ids ||
             a[i].x_div != f.x_div || a[i].experts != f.experts || (f.ids && a[i].rows != f.rows) || a[i].x_dtype != FQ_F32 ||
-            a[i].y_dtype != FQ_F32)
+            a[i].y_dtype != FQ_F32 || a[i].route_map != f.route_map || a[i].id_base != f.id_base || a[i].map_x != f.map_x)
             return FQ_ERR_UNSUPPORTED; // with routes the targets are expert stacks of one shape (gate and up)
     const bool expert = f.ids != nullptr;
+    if (!expert && (f.route_map || f.id_base)) return FQ_ERR_UNSUPPORTED;
     if (f.combine && (!expert || count != 1 || f.x_div != 1 || f.norm_w || prep_i8_layout(f.cols).token_bytes > 40 * 1024 ||
                       (size_t)(f.m / f.combine->used) * ((f.rows + 15) / 16) > FQ_COMBINE_COUNTERS))
         return FQ_ERR_UNSUPPORTED; // the caller combines with a kernel of its own
@@ -954,7 +958,8 @@ cudaError_t launch_static(const uint8_t *w, uint32_t rows, uint32_t pitch, float
         const uint64_t per = (nblk + k - 1) / k, waste = (per * k - nblk) * 1000 / nblk + (k - need);
         if (waste < best) { best = waste; warps = k; }
     }
-    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u, TpPush{}, nullptr, nullptr, CombineTail{});
+    k_gemv_i8<FQ_Q4_K, MT><<<dim3(blocks, 1), dim3(warps * 32), 0, stream>>>(T, pitch, prep, L, nullptr, 1u, 1u, TpPush{}, nullptr, nullptr, CombineTail{},
+                                                                             nullptr, 0u, false);
     return cudaGetLastError();
 }
 

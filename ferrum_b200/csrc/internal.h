@@ -127,6 +127,12 @@ struct ProjectArgs {
     uint32_t format, rows, cols, row_bytes; // rows = rows of one expert slice; row_bytes = device row pitch
     const void *x;
     const float *x_up = nullptr; // decode kernels only: the activations are silu(x) * x_up (the gated unit, fused into their preparation)
+    // Per-route expert projections over a permutation of the routes (an expert-parallel rank's expert-sorted rows):
+    // output row r takes the expert ids[route_map[r]] - id_base (a value outside the matrix's experts: the row is
+    // another rank's and is skipped) and, with map_x, the activation row route_map[r] / x_div (else r / x_div).
+    const uint32_t *route_map = nullptr;
+    uint32_t id_base = 0;
+    bool map_x = false;
     const float *norm_w = nullptr; // decode kernels only: the activations are rmsnorm(x) * norm_w (fused into their preparation)
     float norm_eps = 0.f;
     void *y;
@@ -173,6 +179,10 @@ int fq_launch_gemm_f16_grouped(fq_device *dev, const ProjectArgs *a, uint32_t co
 // `range` (may be null) limits the work to rows [range[0], range[stride]): the experts one rank owns.
 int fq_launch_moe_gather_bf16(fq_device *dev, const float *x, const uint32_t *sorted, uint32_t hidden, uint32_t used, uint32_t routes,
                               const uint32_t *range, uint32_t stride, void *xg);
+// Routing and, with `offsets`, the expert-major map of the routes (fq_moe_map's outputs); one launch at decode widths.
+int fq_moe_route_map(fq_device *dev, const float *logits, const float *x, const float *shared_w, uint32_t experts, uint32_t used,
+                     uint32_t hidden, uint32_t tokens, int sigmoid, int norm, int shared_gate, uint32_t *ids, float *weights, float *gate,
+                     uint32_t *offsets, uint32_t *sorted, uint32_t *position);
 int fq_launch_glu_bf16(fq_device *dev, const float *gate, const float *up, size_t n, const uint32_t *range, uint32_t stride, uint32_t width,
                        void *out);
 // out[row] = expert of expert-sorted row `row` minus `first`, or an id that names no expert when it is not one

@@ -22,13 +22,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Scores: softmax over the logits (max, exp, sum, divide) or a logistic per logit; `used` rounds of arg-max
 // with ties to the lower index; weights divided by the picked sum when `norm`; shared-expert gate =
 // logistic(dot(x, shared_w)) or 1.  Lane l owns experts l, l + 32, ...
-__global__ void __launch_bounds__(ROUTE_WARPS * 32)
-k_moe_route(const float *__restrict__ logits, const float *__restrict__ x, const float *__restrict__ shared_w,
-            uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens, int sigmoid, int norm, int shared_gate,
-            uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate, int *status) {
-    extern __shared__ float route_smem[]; // [ROUTE_WARPS][experts]
-    fqk::pdl_trigger(); // the next kernel may be scheduled now; it waits for this one's results itself
-    fqk::pdl_wait();    // the logits come from the kernel before
+__device__ __forceinline__ void route_token(float *route_smem, const float *__restrict__ logits, const float *__restrict__ x,
+                                            const float *__restrict__ shared_w, uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens,
+                                            int sigmoid, int norm, int shared_gate, uint32_t *__restrict__ ids, float *__restrict__ weights,
+                                            float *__restrict__ gate, int *status) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t t = blockIdx.x * ROUTE_WARPS + warp;
     if (t >= tokens) return;
@@ -116,6 +113,52 @@ k_moe_route(const float *__restrict__ logits, const float *__restrict__ x, const
         if (lane == 0) gate[t] = 1.f / (1.f + expf(-dot));
     } else if (lane == 0) {
         gate[t] = 1.f;
+    }
+}
+
+// The map of at most 32 routes by one warp: lane r ranks its route among the others.
+__device__ __forceinline__ void map_small(const uint32_t *ids, uint32_t experts, uint32_t routes, uint32_t *__restrict__ offsets,
+                                          uint32_t *__restrict__ sorted, uint32_t *__restrict__ position) {
+    const uint32_t lane = threadIdx.x & 31;
+    const bool live = lane < routes;
+    const uint32_t e = live ? ids[lane] : 0xffffffffu;
+    const bool valid = live && e < experts;
+    uint32_t before = 0; // valid routes that sort before this one: a smaller expert, or the same expert and a lower index
+    for (uint32_t l = 0; l < routes; l++) {
+        const uint32_t oe = __shfl_sync(0xffffffffu, e, l);
+        before += (oe < experts) && (oe < e || (oe == e && l < lane));
+    }
+    if (valid) {
+        sorted[before] = lane;
+        position[lane] = before;
+    } else if (live) {
+        position[lane] = 0; // an id that names no expert: the route belongs to no row
+    }
+    const uint32_t placed = __popc(__ballot_sync(0xffffffffu, valid));
+    if (lane >= placed && lane < routes) sorted[lane] = 0; // rows past the last expert's point at route 0
+    // offsets[x] = valid routes whose expert is below x
+    for (uint32_t x0 = 0; x0 <= experts; x0 += 32) { // every lane takes every turn: the shuffles need the whole warp
+        const uint32_t x = x0 + lane;
+        uint32_t n = 0;
+        for (uint32_t l = 0; l < routes; l++) n += __shfl_sync(0xffffffffu, e, l) < x;
+        if (x <= experts) offsets[x] = n;
+    }
+}
+
+// `offsets` (may be null; with it the grid is one block and tokens * used <= 32): the expert-major map of the
+// routes just written, by the block's first warp -- a decode step's routing and map are then one launch.
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+k_moe_route(const float *__restrict__ logits, const float *__restrict__ x, const float *__restrict__ shared_w,
+            uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens, int sigmoid, int norm, int shared_gate,
+            uint32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate, int *status,
+            uint32_t *__restrict__ offsets, uint32_t *__restrict__ sorted, uint32_t *__restrict__ position) {
+    extern __shared__ float route_smem[]; // [ROUTE_WARPS][experts]
+    fqk::pdl_trigger(); // the next kernel may be scheduled now; it waits for this one's results itself
+    fqk::pdl_wait();    // the logits come from the kernel before
+    route_token(route_smem, logits, x, shared_w, experts, used, hidden, tokens, sigmoid, norm, shared_gate, ids, weights, gate, status);
+    if (offsets) {
+        __syncthreads(); // the block's ids are written
+        if (threadIdx.x < 32) map_small(ids, experts, tokens * used, offsets, sorted, position);
     }
 }
 
@@ -379,30 +422,7 @@ k_moe_map_cluster(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t r
 __global__ void __launch_bounds__(32)
 k_moe_map_small(const uint32_t *__restrict__ ids, uint32_t experts, uint32_t routes, uint32_t *__restrict__ offsets,
                 uint32_t *__restrict__ sorted, uint32_t *__restrict__ position) {
-    const uint32_t lane = threadIdx.x;
-    const bool live = lane < routes;
-    const uint32_t e = live ? ids[lane] : 0xffffffffu;
-    const bool valid = live && e < experts;
-    uint32_t before = 0; // valid routes that sort before this one: a smaller expert, or the same expert and a lower index
-    for (uint32_t l = 0; l < routes; l++) {
-        const uint32_t oe = __shfl_sync(0xffffffffu, e, l);
-        before += (oe < experts) && (oe < e || (oe == e && l < lane));
-    }
-    if (valid) {
-        sorted[before] = lane;
-        position[lane] = before;
-    } else if (live) {
-        position[lane] = 0; // an id that names no expert: the route belongs to no row
-    }
-    const uint32_t placed = __popc(__ballot_sync(0xffffffffu, valid));
-    if (lane >= placed && lane < routes) sorted[lane] = 0; // rows past the last expert's point at route 0
-    // offsets[x] = valid routes whose expert is below x
-    for (uint32_t x0 = 0; x0 <= experts; x0 += 32) { // every lane takes every turn: the shuffles need the whole warp
-        const uint32_t x = x0 + lane;
-        uint32_t n = 0;
-        for (uint32_t l = 0; l < routes; l++) n += __shfl_sync(0xffffffffu, e, l) < x;
-        if (x <= experts) offsets[x] = n;
-    }
+    map_small(ids, experts, routes, offsets, sorted, position);
 }
 
 // xg[row] = x[sorted[row] / used]
@@ -540,7 +560,23 @@ int fq_launch_moe_local_ids(fq_device *dev, const uint32_t *ids, const uint32_t 
 extern "C" int fq_moe_route(fq_device *dev, const float *logits, const float *x, const float *shared_w,
                             uint32_t experts, uint32_t used, uint32_t hidden, uint32_t tokens, int sigmoid,
                             int norm, int shared_gate, uint32_t *ids, float *weights, float *gate) {
+    return fq_moe_route_map(dev, logits, x, shared_w, experts, used, hidden, tokens, sigmoid, norm, shared_gate, ids, weights, gate, nullptr, nullptr,
+                            nullptr);
+}
+
+// Routing and, with `offsets`, the expert-major map of the routes (fq_moe_map's outputs): one launch when the
+// routes are a decode step's (one block routes them all), else two.
+int fq_moe_route_map(fq_device *dev, const float *logits, const float *x, const float *shared_w, uint32_t experts, uint32_t used,
+                     uint32_t hidden, uint32_t tokens, int sigmoid, int norm, int shared_gate, uint32_t *ids, float *weights, float *gate,
+                     uint32_t *offsets, uint32_t *sorted, uint32_t *position) {
     if (int rc = fq_begin_enqueue(dev)) return rc;
+    const bool fused = offsets && tokens <= (uint32_t)ROUTE_WARPS && (size_t)tokens * used <= 32;
+    if (fused) {
+        const size_t routes = (size_t)tokens * used;
+        if (int rc = fq_check_binding(dev, offsets, (size_t)(experts + 1) * 4, "offsets")) return rc;
+        if (int rc = fq_check_binding(dev, sorted, routes * 4, "sorted")) return rc;
+        if (int rc = fq_check_binding(dev, position, routes * 4, "position")) return rc;
+    }
     if (experts == 0 || experts > MAX_EXPERTS || used == 0 || used > experts || tokens == 0)
         return fq_fail(dev, FQ_ERR_SHAPE, "routing %u of %u experts for %u tokens", used, experts, tokens);
     if (int rc = fq_check_binding(dev, logits, (size_t)tokens * experts * 4, "logits")) return rc;
@@ -555,10 +591,13 @@ extern "C" int fq_moe_route(fq_device *dev, const float *logits, const float *x,
     if (int rc = fq_check_no_alias(dev, weights, (size_t)tokens * used * 4, logits, (size_t)tokens * experts * 4, "weights")) return rc;
     if (int rc = fq_check_cuda(dev, fqk::launch_pdl(k_moe_route, dim3((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32),
                                                     (size_t)ROUTE_WARPS * experts * sizeof(float), dev->stream, logits, x, shared_w, experts, used, hidden,
-                                                    tokens, sigmoid, norm, shared_gate, ids, weights, gate, dev->status_dev),
+                                                    tokens, sigmoid, norm, shared_gate, ids, weights, gate, dev->status_dev, fused ? offsets : nullptr,
+                                                    fused ? sorted : nullptr, fused ? position : nullptr),
                                "moe_route launch"))
         return rc;
-    return fq_end_enqueue(dev, "moe_route", 1);
+    if (int rc = fq_end_enqueue(dev, "moe_route", 1)) return rc;
+    if (offsets && !fused) return fq_moe_map(dev, ids, experts, tokens * used, offsets, sorted, position);
+    return FQ_OK;
 }
 
 extern "C" int fq_moe_map(fq_device *dev, const uint32_t *ids, uint32_t experts, uint32_t routes,
