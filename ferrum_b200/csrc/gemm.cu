@@ -572,26 +572,18 @@ __global__ void k_to_bf16(const float *__restrict__ x, __nv_bfloat16 *__restrict
 }
 
 // X (fp32) as two bf16 terms laid out for MODE 2: k-block b of a row becomes the three 64-wide blocks
-// hi, lo, hi at 3 b, 3 b + 1, 3 b + 2, with hi = bf16(x) and lo = bf16(x - hi).  One thread per eight
-// consecutive values (cols is a multiple of 64): two 16-byte loads, three 16-byte stores.
+// hi, lo, hi at 3 b, 3 b + 1, 3 b + 2, with hi = bf16(x) and lo = bf16(x - hi).
 __global__ void k_split3(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, uint32_t cols, size_t n) {
-    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const size_t row = i / cols;
     const uint32_t k = (uint32_t)(i % cols), b = k / BK, j = k % BK;
-    const float4 v0 = *reinterpret_cast<const float4 *>(x + i), v1 = *reinterpret_cast<const float4 *>(x + i + 4);
-    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    uint32_t hi[4], lo[4];
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-        const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * u]), h1 = __float2bfloat16_rn(v[2 * u + 1]);
-        hi[u] = pack_bf16(__bfloat162float(h0), __bfloat162float(h1));
-        lo[u] = pack_bf16(v[2 * u] - __bfloat162float(h0), v[2 * u + 1] - __bfloat162float(h1));
-    }
+    const float v = x[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v), lo = __float2bfloat16_rn(v - __bfloat162float(hi));
     __nv_bfloat16 *dst = out + row * (size_t)cols * 3 + (size_t)b * 3 * BK + j;
-    *reinterpret_cast<uint4 *>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-    *reinterpret_cast<uint4 *>(dst + BK) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    *reinterpret_cast<uint4 *>(dst + 2 * BK) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    dst[0] = hi;
+    dst[BK] = lo;
+    dst[2 * BK] = hi;
 }
 
 // The tiles that were split along K: their fp32 partial sums added in split order (deterministic), rounded and
@@ -720,27 +712,51 @@ int make_map(fq_device *dev, CUtensorMap *map, const void *x, uint32_t cols, uin
 //                 activation row c against hi, row 2 c + 1 against lo);
 //   warp 1        one thread issues tcgen05.mma (M = 128, N = 256, K = 16, kind::f16) into one of two
 //                 accumulators in tensor memory, so that the next item's MMAs run under this item's epilogue;
-//   warps 2..17   decode: thread (weight row, group) keeps the packed bytes of its next k-blocks in registers
-//                 (a superblock ahead, across item borders) and writes 32 fp16 weights per k-block in packed half
-//                 arithmetic (g_decode_* below) into the K-major, 128-byte-swizzled tile the MMA reads;
-//   warps 18..21  epilogue: read the accumulator (lane = MMA row), add the hi and lo rows with a shuffle, undo
+//   warp 2        (Q4_K) one thread asks the TMA for the packed bytes of the item's 256 weight rows, half a superblock
+//                 at a time (plain boxes of the matrix as bytes), three stages ahead, across item borders: loads
+//                 by the decoding threads themselves queue behind the SM's load unit and hold up their proxy fences;
+//   warps 3..18   decode: a warp owns sixteen weight rows; lane (row, group) reads its packed bytes from the staged
+//                 half superblock (Q6_K, whose items here are two superblocks long: from global memory, a
+//                 superblock ahead) and writes 32 fp16 weights per k-block in packed half arithmetic (g_decode_*
+//                 below) into the K-major, 128-byte-swizzled tile the MMA reads;
+//   warps 19..22  epilogue: read the accumulator (lane = MMA row), add the hi and lo rows with a shuffle, undo
 //                 the row scale, store y.
 //
 // Every wait is bounded as in k_gemm_tc.
-constexpr int G_PRODUCER_WARPS = 16, G_EPI_WARPS = 4, G_THREADS = (2 + G_PRODUCER_WARPS + G_EPI_WARPS) * 32;
-constexpr int G_STAGES = 4;             // decoded weight tiles in flight
-constexpr int G_X_SLOTS = 3;            // activation tiles in flight
+constexpr int G_PRODUCER_WARPS = 16, G_EPI_WARPS = 4, G_THREADS = (3 + G_PRODUCER_WARPS + G_EPI_WARPS) * 32;
 constexpr uint32_t G_TOK = 64;          // activation rows per tile (128 MMA rows)
 constexpr uint32_t G_BN = 256;          // weight rows per tile (MMA N)
 constexpr uint32_t G_W_BYTES = G_BN * BK * 2, G_X_BYTES = 2 * G_TOK * BK * 2;
-constexpr uint32_t G_MAX_TILES = 1024;  // activation tiles the table holds
+constexpr uint32_t G_MAX_TILES = 512;   // activation tiles the table holds
 
-struct __align__(1024) GSmem {
-    uint8_t w[G_STAGES][G_W_BYTES];
-    uint8_t x[G_X_SLOTS][G_X_BYTES];
+// Q4_K: the packed bytes of a tile's 256 weight rows are staged by TMA half a superblock (two k-blocks) at a time, as
+// plain row-major boxes of the matrix seen as bytes: the 16-byte header and the 64 bytes of two chunks per row.
+// W_STAGES / X_SLOTS: decoded weight tiles and activation tiles in flight (what fits beside the rest).
+template <int FMT> struct GRaw;
+template <> struct GRaw<FQ_Q4_K> {
+    static constexpr int STAGES = 3, W_STAGES = 4, X_SLOTS = 2;
+    static constexpr uint32_t QS = G_BN * 16, BYTES = QS + G_BN * 64;
+};
+template <> struct GRaw<FQ_Q6_K> { // not staged: the decoding threads fetch their own bytes (see the kernel)
+    static constexpr int STAGES = 1, W_STAGES = 4, X_SLOTS = 3;
+    static constexpr uint32_t BYTES = 128;
+};
+
+template <int FMT> struct __align__(1024) GSmem {
+    uint8_t w[GRaw<FMT>::W_STAGES][G_W_BYTES];
+    uint8_t x[GRaw<FMT>::X_SLOTS][G_X_BYTES];
+    uint8_t raw[GRaw<FMT>::STAGES][GRaw<FMT>::BYTES];
     uint2 tiles[G_MAX_TILES]; // .x = first sorted row, .y = expert << 8 | rows
-    uint64_t full_w[G_STAGES], empty_w[G_STAGES], full_x[G_X_SLOTS], empty_x[G_X_SLOTS], acc_full[2], acc_empty[2], drain;
+    uint64_t full_w[GRaw<FMT>::W_STAGES], empty_w[GRaw<FMT>::W_STAGES], full_x[GRaw<FMT>::X_SLOTS], empty_x[GRaw<FMT>::X_SLOTS], acc_full[2], acc_empty[2], drain;
+    uint64_t raw_full[GRaw<FMT>::STAGES], raw_empty[GRaw<FMT>::STAGES];
     uint32_t tmem_base, abort_flag, n_tiles;
+};
+
+// Tensor maps: the activations, and (Q4_K) the packed weights as bytes ([experts * rows][pitch]) per matrix set, 256
+// rows a box: [0] = 16-byte (header), [1] = 64-byte (two chunks) boxes.
+struct alignas(64) GMaps {
+    CUtensorMap x[3];    // activations: 32-, 64- and 128-row boxes
+    CUtensorMap w[2][2];
 };
 
 struct GJob {
@@ -771,10 +787,12 @@ constexpr uint32_t G_IDESC = (1u << 4) | ((G_BN >> 3) << 17) | ((uint32_t)(128 >
 // once.  Q6_K: (1024 + q) - 1056 = q - 32 exactly, times fp16(d scale).  Every weight is within 2^-11 (relative)
 // of its exact value, plus 2^-12 of its sub-block's minimum term.
 //
-// Q4_K: sub-block j = 2 C + part of the superblock (header `hdr`): nibble `part` of the 32 bytes a, b of chunk C.
+// Q4_K: the row's staged header and the 32 bytes of chunk C; sub-block j = 2 C + part is nibble `part` of the chunk.
 template <int C>
-__device__ __forceinline__ void g_decode_q4k(const uint4 &hdr, const uint4 &a, const uint4 &b, uint32_t part, bool live, uint32_t (&out)[16]) {
+__device__ __forceinline__ void g_decode_q4k(const uint8_t *hdrp, const uint8_t *chunk, uint32_t part, bool live, uint32_t (&out)[16]) {
     constexpr uint32_t MAGIC = 0x64646464u;
+    const uint4 hdr = *reinterpret_cast<const uint4 *>(hdrp);
+    const uint4 a = *reinterpret_cast<const uint4 *>(chunk), b = *reinterpret_cast<const uint4 *>(chunk + 16);
     const uint32_t sh = 8 * ((2 * C) & 3) + 8 * part; // `get_scale_min_k4`
     uint32_t sc, mn;
     if (C < 2) {
@@ -880,20 +898,20 @@ k_split_f16(const float *__restrict__ x, const float *__restrict__ x_up, const u
 
 template <int FMT>
 __global__ void __launch_bounds__(G_THREADS, 1)
-k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ CUtensorMap map64, const __grid_constant__ CUtensorMap map128,
-            const __grid_constant__ GJob J) {
+k_gemm_f16g(const __grid_constant__ GMaps M, const __grid_constant__ GJob J) {
     extern __shared__ uint8_t smem_raw[];
-    GSmem *sm = reinterpret_cast<GSmem *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    GSmem<FMT> *sm = reinterpret_cast<GSmem<FMT> *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t nblk = J.cols / 256, k_iters = J.cols / BK, tiles_x = J.tx_end[J.count - 1];
     constexpr uint32_t TMEM_COLS = 2 * G_BN; // two accumulators
+    constexpr int W_STAGES = GRaw<FMT>::W_STAGES;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < G_STAGES; s++) {
+        for (int s = 0; s < W_STAGES; s++) {
             mbar_init(&sm->full_w[s], G_PRODUCER_WARPS); // one lane arrives for its warp
             mbar_init(&sm->empty_w[s], 1);
         }
-        for (int s = 0; s < G_X_SLOTS; s++) {
+        for (int s = 0; s < GRaw<FMT>::X_SLOTS; s++) {
             mbar_init(&sm->full_x[s], 1);
             mbar_init(&sm->empty_x[s], 1);
         }
@@ -902,11 +920,15 @@ k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ C
             mbar_init(&sm->acc_empty[i], G_EPI_WARPS * 32);
         }
         mbar_init(&sm->drain, 1);
+        for (int s = 0; s < GRaw<FMT>::STAGES; s++) {
+            mbar_init(&sm->raw_full[s], 1);
+            mbar_init(&sm->raw_empty[s], G_PRODUCER_WARPS);
+        }
         sm->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map32) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map64) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map128) : "memory");
+        for (int i = 0; i < 3; i++) asm volatile("prefetch.tensormap [%0];" ::"l"(&M.x[i]) : "memory");
+        if (FMT == FQ_Q4_K)
+            for (uint32_t i = 0; i < J.count; i++) asm volatile("prefetch.tensormap [%0];" ::"l"(&M.w[i][0]) : "memory");
     }
     if (warp == 0) {
         // The table of activation tiles: group z contributes ceil(rows / 64) tiles for its rows inside this
@@ -974,11 +996,11 @@ k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ C
                 // One box per k-block: the tile's rows with their hi and lo terms interleaved (32, 64 or 128 tensor
                 // rows; a box that runs past the tile reads rows whose results are not stored, or zeros past the
                 // end; MMA rows the box does not cover keep what an earlier tile left there).
-                const CUtensorMap *map = it.cnt <= 16 ? &map32 : it.cnt <= 32 ? &map64 : &map128;
+                const CUtensorMap *map = it.cnt <= 16 ? &M.x[0] : it.cnt <= 32 ? &M.x[1] : &M.x[2];
                 const uint32_t bytes = (it.cnt <= 16 ? J.box_bytes[0] : it.cnt <= 32 ? J.box_bytes[1] : J.box_bytes[2]);
                 for (uint32_t k = 0; k < k_iters; k++, ix++) {
-                    const uint32_t s = ix % G_X_SLOTS;
-                    if (!(ok = mbar_wait(&sm->empty_x[s], ((ix / G_X_SLOTS) & 1) ^ 1, sm, J.status))) break;
+                    const uint32_t s = ix % GRaw<FMT>::X_SLOTS;
+                    if (!(ok = mbar_wait(&sm->empty_x[s], ((ix / GRaw<FMT>::X_SLOTS) & 1) ^ 1, sm, J.status))) break;
                     mbar_expect_tx(&sm->full_x[s], bytes);
                     tma_load_2d(sm->x[s], map, (int)(k * BK), (int)(2 * (it.m0 - J.row_begin)), &sm->full_x[s]);
                 }
@@ -986,8 +1008,8 @@ k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ C
             // On an abort the copies already issued still land: wait for them (bounded) before the block's
             // shared memory goes away.
             if (*(volatile uint32_t *)&sm->abort_flag)
-                for (uint32_t u = ix > (uint32_t)G_X_SLOTS ? ix - G_X_SLOTS : 0; u < ix; u++)
-                    for (uint32_t n = 0; n < WAIT_LIMIT && !mbar_try(&sm->full_x[u % G_X_SLOTS], (u / G_X_SLOTS) & 1); n++) {}
+                for (uint32_t u = ix > (uint32_t)GRaw<FMT>::X_SLOTS ? ix - GRaw<FMT>::X_SLOTS : 0; u < ix; u++)
+                    for (uint32_t n = 0; n < WAIT_LIMIT && !mbar_try(&sm->full_x[u % GRaw<FMT>::X_SLOTS], (u / GRaw<FMT>::X_SLOTS) & 1); n++) {}
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -998,9 +1020,9 @@ k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ C
                 if (!(ok = mbar_wait(&sm->acc_empty[buf], ((i >> 1) & 1) ^ 1, sm, J.status))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 for (uint32_t k = 0; k < k_iters; k++, it_n++) {
-                    const uint32_t sw = it_n % G_STAGES, sx = it_n % G_X_SLOTS;
-                    if (!(ok = mbar_wait(&sm->full_w[sw], (it_n / G_STAGES) & 1, sm, J.status))) break;
-                    if (!(ok = mbar_wait(&sm->full_x[sx], (it_n / G_X_SLOTS) & 1, sm, J.status))) break;
+                    const uint32_t sw = it_n % W_STAGES, sx = it_n % GRaw<FMT>::X_SLOTS;
+                    if (!(ok = mbar_wait(&sm->full_w[sw], (it_n / W_STAGES) & 1, sm, J.status))) break;
+                    if (!(ok = mbar_wait(&sm->full_x[sx], (it_n / GRaw<FMT>::X_SLOTS) & 1, sm, J.status))) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t adesc = umma_desc(smem_u32(sm->x[sx])), bdesc = umma_desc(smem_u32(sm->w[sw]));
 #pragma unroll
@@ -1012,22 +1034,36 @@ k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ C
             }
             umma_commit(&sm->drain); // arrives when every MMA issued so far has completed
         }
-    } else if (warp < 2 + G_PRODUCER_WARPS) {
-        // Thread p decodes weight row p / 2 of the tile, group p % 2 of every k-block.
-        const uint32_t p = threadIdx.x - 64, r = p >> 1, part = p & 1;
-        auto row_of = [&](uint32_t i) {
-            const Item it = item_at(i);
-            return J.w[it.set] + ((size_t)it.e * J.rows + min(it.n0 + r, J.rows - 1)) * J.pitch;
-        };
-        // The superblock whose bytes are fetched next: one ahead of the one being decoded, across item borders.
-        uint32_t n_i = 0, n_sb = 0;
-        const uint8_t *n_row = my_items ? row_of(0) : nullptr;
-        auto step_next = [&]() {
-            if (++n_sb == nblk) {
-                n_sb = 0;
-                if (++n_i < my_items) n_row = row_of(n_i);
+    } else if (warp == 2) {
+        // Q4_K: one thread asks the TMA for every half superblock of every item's 256 rows, as many stages ahead as
+        // the ring holds.  The decoding threads so have no loads of their own in flight (their
+        // proxy fence would wait for them), and the copies do not queue behind the SM's load unit.
+        if constexpr (FMT == FQ_Q4_K) {
+        if (lane == 0) {
+            constexpr int RAW = GRaw<FMT>::STAGES;
+            uint32_t ir = 0;
+            bool ok = true;
+            for (uint32_t i = 0; i < my_items && ok; i++) {
+                const Item it = item_at(i);
+                const int y = (int)(it.e * J.rows + it.n0);
+                const CUtensorMap *maps = M.w[it.set];
+                for (uint32_t hb = 0; hb < 2 * nblk; hb++, ir++) { // half superblocks
+                    const uint32_t s = ir % RAW, sb = hb >> 1, half = hb & 1;
+                    if (!(ok = mbar_wait(&sm->raw_empty[s], ((ir / RAW) & 1) ^ 1, sm, J.status))) break;
+                    mbar_expect_tx(&sm->raw_full[s], GRaw<FMT>::BYTES);
+                    uint8_t *dst = sm->raw[s];
+                    tma_load_2d(dst, &maps[0], (int)(sb * 144), y, &sm->raw_full[s]);
+                    tma_load_2d(dst + GRaw<FMT>::QS, &maps[1], (int)(sb * 144 + 16 + 64 * half), y, &sm->raw_full[s]);
+                }
             }
-        };
+            if (*(volatile uint32_t *)&sm->abort_flag) // copies already issued still land: wait for them (bounded)
+                for (uint32_t u = ir > (uint32_t)RAW ? ir - RAW : 0; u < ir; u++)
+                    for (uint32_t n = 0; n < WAIT_LIMIT && !mbar_try(&sm->raw_full[u % RAW], (u / RAW) & 1); n++) {}
+        }
+        }
+    } else if (warp < 3 + G_PRODUCER_WARPS) {
+        // Decoding warp pw owns weight rows 16 pw .. 16 pw + 15 of every tile; lane = (row, group of the k-block).
+        const uint32_t pw = warp - 3, lrow = lane >> 1, part = lane & 1, r = 16 * pw + lrow;
         uint32_t stage = 0, phase = 1;
         bool go = true, live = false;
         const uint32_t swz = r & 7;
@@ -1044,51 +1080,54 @@ k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ C
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> tensor-core reads
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm->full_w[stage]);
-            if (++stage == (uint32_t)G_STAGES) {
+            if (++stage == (uint32_t)W_STAGES) {
                 stage = 0;
                 phase ^= 1;
             }
         };
         uint32_t v[16];
         if constexpr (FMT == FQ_Q4_K) {
-            uint4 hdr = make_uint4(0, 0, 0, 0), hdr_next = hdr, qa[4], qb[4];
-#pragma unroll
-            for (int c = 0; c < 4; c++) qa[c] = qb[c] = make_uint4(0, 0, 0, 0);
-            if (my_items) {
-                const uint8_t *blk = n_row;
-                hdr = *reinterpret_cast<const uint4 *>(blk);
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    qa[c] = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * c);
-                    qb[c] = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * c);
-                }
-                step_next();
-            }
-            const uint8_t *next = n_i < my_items ? n_row + (size_t)n_sb * 144 : nullptr;
-            if (next) hdr_next = *reinterpret_cast<const uint4 *>(next);
+            constexpr int RAW = GRaw<FMT>::STAGES;
+            uint32_t ir = 0;
             for (uint32_t i = 0; i < my_items && go; i++) {
                 live = item_at(i).n0 + r < J.rows;
-                for (uint32_t sb = 0; sb < nblk && go; sb++) {
-#define FQ_G_STEP(C)                                                                   \
-    if (go) {                                                                          \
-        g_decode_q4k<C>(hdr, qa[C], qb[C], part, live, v);                             \
-        if (next) {                                                                    \
-            qa[C] = *reinterpret_cast<const uint4 *>(next + 16 + 32 * C);              \
-            qb[C] = *reinterpret_cast<const uint4 *>(next + 32 + 32 * C);              \
-        }                                                                              \
-        emit(v);                                                                       \
-    }
-                    FQ_G_STEP(0) FQ_G_STEP(1) FQ_G_STEP(2) FQ_G_STEP(3)
-#undef FQ_G_STEP
-                    hdr = hdr_next;
-                    if (next) {
-                        step_next();
-                        next = n_i < my_items ? n_row + (size_t)n_sb * 144 : nullptr;
-                        if (next) hdr_next = *reinterpret_cast<const uint4 *>(next);
+                for (uint32_t hb = 0; hb < 2 * nblk && go; hb++, ir++) { // half superblocks: two k-blocks each
+                    const uint32_t rs = ir % RAW, sb = hb >> 1;
+                    bool ok = true;
+                    if (lane == 0) ok = mbar_wait(&sm->raw_full[rs], (ir / RAW) & 1, sm, J.status);
+                    if (!__all_sync(0xffffffffu, ok)) { go = false; break; }
+                    const uint8_t *st = sm->raw[rs];
+                    const uint8_t *hdrp = st + 16 * r, *qs = st + GRaw<FMT>::QS + 64 * r;
+                    if (hb & 1) {
+                        g_decode_q4k<2>(hdrp, qs, part, live, v);
+                        emit(v);
+                        if (go) { g_decode_q4k<3>(hdrp, qs + 32, part, live, v); emit(v); }
+                    } else {
+                        g_decode_q4k<0>(hdrp, qs, part, live, v);
+                        emit(v);
+                        if (go) { g_decode_q4k<1>(hdrp, qs + 32, part, live, v); emit(v); }
                     }
+                    __syncwarp(); // every lane is done with the stage
+                    if (lane == 0) mbar_arrive(&sm->raw_empty[rs]);
                 }
             }
         } else {
+            // Q6_K: thread (row, group) fetches its own packed bytes, a superblock ahead and across item borders
+            // (items of this format are short -- K = 512 is two superblocks -- and the staging ring above would
+            // restart with every item).
+            auto row_of = [&](uint32_t i) {
+                const Item it = item_at(i);
+                return J.w[it.set] + ((size_t)it.e * J.rows + min(it.n0 + r, J.rows - 1)) * J.pitch;
+            };
+            // The superblock whose bytes are fetched next: one ahead of the one being decoded, across item borders.
+            uint32_t n_i = 0, n_sb = 0;
+            const uint8_t *n_row = my_items ? row_of(0) : nullptr;
+            auto step_next = [&]() {
+                if (++n_sb == nblk) {
+                    n_sb = 0;
+                    if (++n_i < my_items) n_row = row_of(n_i);
+                }
+            };
             // Per superblock: the sixteen scales and d; per 128-value half: 32 ql bytes (this group's) and 32 qh bytes.
             uint4 sc = make_uint4(0, 0, 0, 0), sc_next = sc, ql[2][2], qh[2][2];
             uint32_t d = 0, d_next = 0;
@@ -1190,6 +1229,20 @@ k_gemm_f16g(const __grid_constant__ CUtensorMap map32, const __grid_constant__ C
     }
 }
 
+// The packed rows of a matrix (or a stack of experts) as a [rows][pitch] tensor of bytes, boxes of `box_bytes` x 256
+// rows, no swizzle: what k_gemm_f16g stages per superblock.
+int make_byte_map(fq_device *dev, CUtensorMap *map, const void *w, uint32_t pitch, uint64_t rows, uint32_t box_bytes) {
+    EncodeTiled encode = encode_fn();
+    if (!encode) return FQ_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {pitch, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {box_bytes, (cuuint32_t)std::min<uint64_t>(rows, 256)}, elem[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(w), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fq_fail(dev, FQ_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return FQ_OK;
+}
+
 } // namespace
 
 // X as bf16 in the handle's scratch (the halves of which successive calls alternate between), or null if
@@ -1231,7 +1284,7 @@ int fq_launch_gemm_tc(fq_device *dev, const ProjectArgs &a) {
         dev->xprep_turn ^= 1u;
         __nv_bfloat16 *x3 = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? half : 0));
         const size_t n = (size_t)mm * a.cols;
-        k_split3<<<(unsigned)((n / 8 + 255) / 256), 256, 0, dev->stream>>>((const float *)a.x + (size_t)m0 * a.cols, x3, a.cols, n);
+        k_split3<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>((const float *)a.x + (size_t)m0 * a.cols, x3, a.cols, n);
         if (int rc = make_map(dev, &map, x3, a.cols * 3, mm, 256, &b_bytes)) return rc;
         ProjectArgs s = a;
         s.m = mm;
@@ -1274,7 +1327,7 @@ int fq_launch_gemm_tc_many(fq_device *dev, const ProjectArgs *a, uint32_t count)
         dev->xprep_turn ^= 1u;
         __nv_bfloat16 *x3 = (__nv_bfloat16 *)((uint8_t *)dev->xprep + (dev->xprep_turn ? dev->xprep_bytes / 2 : 0));
         const size_t n = (size_t)f.m * f.cols;
-        k_split3<<<(unsigned)((n / 8 + 255) / 256), 256, 0, dev->stream>>>((const float *)f.x, x3, f.cols, n);
+        k_split3<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>((const float *)f.x, x3, f.cols, n);
         if (int rc = make_map(dev, &map, x3, f.cols * 3, f.m, 256, &b_bytes)) return rc;
         const int rc = f.m >= 384 ? launch_fmt<512, float, 2>(dev, f, map, b_bytes, f.m, many) : launch_fmt<256, float, 2>(dev, f, map, b_bytes, f.m, many);
         if (rc != FQ_OK) return rc;
@@ -1319,6 +1372,7 @@ int fq_launch_gemm_f16_grouped(fq_device *dev, const ProjectArgs *a, uint32_t co
         return FQ_ERR_UNSUPPORTED;
     if (f.format != FQ_Q4_K && f.format != FQ_Q6_K) return FQ_ERR_UNSUPPORTED;
     if (f.groups == 0 || f.groups > 65535 || f.experts > 65535 || total_rows < 16 || (src && src_div == 0)) return FQ_ERR_UNSUPPORTED;
+    if (f.format == FQ_Q4_K && (uint64_t)f.experts * f.rows < G_BN) return FQ_ERR_UNSUPPORTED; // a TMA box of 256 weight rows must fit the stack
     for (uint32_t i = 1; i < count; i++)
         if (a[i].format != f.format || a[i].cols != f.cols || a[i].rows != f.rows || a[i].row_bytes != f.row_bytes || a[i].x != f.x ||
             a[i].x_up != f.x_up || a[i].offsets != f.offsets || a[i].slots != f.slots || a[i].groups != f.groups || a[i].experts != f.experts ||
@@ -1328,8 +1382,10 @@ int fq_launch_gemm_f16_grouped(fq_device *dev, const ProjectArgs *a, uint32_t co
     // straddles two launches is served in two parts).
     const size_t per_row = (size_t)2 * f.cols * sizeof(__half) + sizeof(float);
     uint32_t chunk = (uint32_t)std::min<size_t>(total_rows, dev->xprep_bytes / per_row);
+    if (f.groups + 8 > G_MAX_TILES) return FQ_ERR_UNSUPPORTED;
+    chunk = std::min<uint32_t>(chunk, (G_MAX_TILES - f.groups) * G_TOK); // the kernel's table of activation tiles holds G_MAX_TILES
     if (chunk < total_rows) chunk &= ~(G_TOK - 1);
-    if (chunk < 16 || (uint64_t)chunk / G_TOK + f.groups > G_MAX_TILES) return FQ_ERR_UNSUPPORTED;
+    if (chunk < 16) return FQ_ERR_UNSUPPORTED;
     __half *xh = (__half *)dev->xprep;
     float *inv_scale = (float *)((uint8_t *)dev->xprep + (size_t)2 * chunk * f.cols * sizeof(__half));
     GJob J{};
@@ -1350,7 +1406,15 @@ int fq_launch_gemm_f16_grouped(fq_device *dev, const ProjectArgs *a, uint32_t co
     J.slots = f.slots;
     J.inv_scale = inv_scale;
     J.status = dev->status_dev;
-    const size_t smem = sizeof(GSmem) + 1024;
+    const size_t smem = (f.format == FQ_Q4_K ? sizeof(GSmem<FQ_Q4_K>) : sizeof(GSmem<FQ_Q6_K>)) + 1024;
+    GMaps maps;
+    for (uint32_t i = 0; i < count; i++) {
+        const uint64_t wrows = (uint64_t)a[i].experts * a[i].rows;
+        if (f.format == FQ_Q4_K) { // the packed bytes are staged by TMA
+            if (int rc = make_byte_map(dev, &maps.w[i][0], a[i].w, f.row_bytes, wrows, 16)) return rc;
+            if (int rc = make_byte_map(dev, &maps.w[i][1], a[i].w, f.row_bytes, wrows, 64)) return rc;
+        }
+    }
     auto kernel = f.format == FQ_Q4_K ? k_gemm_f16g<FQ_Q4_K> : k_gemm_f16g<FQ_Q6_K>;
     static bool configured[2] = {};
     bool &done = configured[f.format == FQ_Q4_K ? 0 : 1];
@@ -1367,10 +1431,9 @@ int fq_launch_gemm_f16_grouped(fq_device *dev, const ProjectArgs *a, uint32_t co
         J.row_begin = r0;
         J.row_end = r1;
         k_split_f16<<<(r1 - r0 + 7) / 8, 256, 0, dev->stream>>>((const float *)f.x, f.x_up, src, src_div, f.offsets, f.groups, r0, r1, f.cols, xh, inv_scale);
-        CUtensorMap maps[3];
         for (int i = 0; i < 3; i++)
-            if (int rc = make_map(dev, &maps[i], xh, f.cols, 2 * (r1 - r0), 32u << i, &J.box_bytes[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16)) return rc;
-        kernel<<<(unsigned)dev->sm_count, G_THREADS, smem, dev->stream>>>(maps[0], maps[1], maps[2], J);
+            if (int rc = make_map(dev, &maps.x[i], xh, f.cols, 2 * (r1 - r0), 32u << i, &J.box_bytes[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16)) return rc;
+        kernel<<<(unsigned)dev->sm_count, G_THREADS, smem, dev->stream>>>(maps, J);
         if (int rc = fq_check_cuda(dev, cudaGetLastError(), "grouped fp16 gemm launch")) return rc;
         kernels += 2;
         if (r1 == total_rows) break;
