@@ -883,9 +883,10 @@ extern "C" int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x,
 // Grouped F32 projections by average rows per expert: below GROUPED_F16_MIN_AVG_ROWS the integer kernel of
 // gemv_nt.cu (the work is streaming weights; its per-row arithmetic is still small), from there on the fp16
 // tensor-core kernel k_gemm_f16g, which decodes every weight once per 64 rows (measured on the 35B-A3B-class
-// block: 443 against 453 us at 24 rows per expert, 539 against 460 us at 32, 619 against 514 us at 40).  Formats
-// the fp16 kernel does not serve stay on the integer kernel up to GROUPED_NT_MAX_AVG_ROWS.
-constexpr size_t GROUPED_F16_MIN_AVG_ROWS = 28;
+// block, integer against fp16 kernel: 378 / 385 us at 14 rows per expert, 406 / 384 at 16, 425 / 394 at 20,
+// 446 / 421 at 24, 538 / 452 at 32, 702 / 578 at 48).  Formats the fp16 kernel does not serve stay on the integer
+// kernel up to GROUPED_NT_MAX_AVG_ROWS.
+constexpr size_t GROUPED_F16_MIN_AVG_ROWS = 16;
 constexpr size_t GROUPED_NT_MAX_AVG_ROWS = 48;
 
 // Arguments as fq_launch_gemv_nt_grouped, and `group_rows`: how many of the rows the groups in `a` cover (all of

@@ -252,7 +252,7 @@ int fq_project_id(fq_device *dev, const fq_matrix *w, const float *x, size_t x_e
  * groups (w.experts without a slot table); `max_rows` bounds any group's row count.  `offsets` and `slots`
  * are read one 32-bit value at a time: 4-byte alignment is enough for them (a rank's window into a larger
  * table of expert offsets starts wherever its first expert falls).  F32 callers get fp32-level results at every
- * width (the integer kernel below about 28 rows per group on average; from there on fp16 tensor-core products of
+ * width (the integer kernel below about 16 rows per group on average; from there on fp16 tensor-core products of
  * weights rounded to fp16 and activations carried to 22 bits: within 1e-3 of the largest output, 4e-4 measured);
  * BF16 callers the bf16 contract of the prefill GEMM. */
 int fq_project_mm_id(fq_device *dev, const fq_matrix *w, const void *x, int x_dtype, size_t x_elems,

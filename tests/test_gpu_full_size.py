@@ -92,10 +92,10 @@ def config3():
     return experts, used, hidden, ef, mats
 
 
-@pytest.mark.parametrize("tokens", [1, 640, 1024, 2048])
+@pytest.mark.parametrize("tokens", [1, 384, 1024, 2048])
 def test_config3_moe_block(device, config3, tokens):
     """35B-A3B-class block: 256 experts + shared, top-8, hidden 2048, expert width 512.  T = 1 takes the per-route
-    projections, T = 640 (20 rows per expert) the integer grouped kernel over expert-sorted rows, T = 1024 the fp16
+    projections, T = 384 (12 rows per expert) the integer grouped kernel over expert-sorted rows, T = 1024 the fp16
     tensor-core grouped kernel, T = 2048 the same in two launches (the fp16 copy of the 16384 gathered rows does not
     fit the activation scratch at once); sampled tokens against the oracle."""
     s = S()
