@@ -734,7 +734,7 @@ constexpr uint32_t G_MAX_TILES = 512;   // activation tiles the table holds
 // W_STAGES / X_SLOTS: decoded weight tiles and activation tiles in flight (what fits beside the rest).
 template <int FMT> struct GRaw;
 template <> struct GRaw<FQ_Q4_K> {
-    static constexpr int STAGES = 3, W_STAGES = 4, X_SLOTS = 2;
+    static constexpr int STAGES = 3, W_STAGES = 3, X_SLOTS = 3;
     static constexpr uint32_t QS = G_BN * 16, BYTES = QS + G_BN * 64;
 };
 template <> struct GRaw<FQ_Q6_K> { // not staged: the decoding threads fetch their own bytes (see the kernel)
