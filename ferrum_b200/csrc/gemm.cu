@@ -694,7 +694,7 @@ int make_map(fq_device *dev, CUtensorMap *map, const void *x, uint32_t cols, uin
 
 
 // ---------------------------------------------------------------------------------------------------------
-// Expert tiles on fp16 products: grouped projections of roughly 12 to 64 rows per expert, F32 in and out, for
+// Expert tiles on fp16 products: grouped projections of sixteen rows per expert or more, F32 in and out, for
 // which the integer kernel of gemv_nt.cu repeats its per-(row, sub-block) scale arithmetic too often and the
 // bf16 GEMM above is both too coarse (2^-9 weights, bf16 activations) and organised for many rows per tile.
 //
